@@ -1,0 +1,46 @@
+"""The paged-attention backend: one implementation for prefill, chunked extend over a cached
+prefix, decode, and speculative verification (plain or with a tree mask). All of them read K
+and V from the paged pool after the fused norm/RoPE/store kernel has written this step's
+rows, so a cached prefix needs no special path. The reference keeps several backends
+(python/minisgl/attention/__init__.py:19-98); on sm_100a one suffices.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..core import Batch, get_global_ctx
+from .base import AttnMetadata, BaseAttnBackend
+
+
+class PagedAttentionBackend(BaseAttnBackend):
+    def __init__(self, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
+                 max_batch: int = 0) -> None:
+        self.hq, self.hk, self.d = num_q_heads, num_kv_heads, head_dim
+        self.device = device
+        self._workspace: Optional[torch.Tensor] = None
+        if torch.device(device).type == "cuda":
+            from ..ops import cuda as K
+
+            self._workspace = K.attention_workspace(max(max_batch, 1), num_q_heads, head_dim, device)
+
+    def prepare_metadata(self, batch: Batch, block_table, cu_q, seq_lens, max_q: int, max_kv: int,
+                         causal: bool = True, mask: Optional[torch.Tensor] = None) -> None:
+        batch.attn_metadata = AttnMetadata(
+            cu_q=cu_q, seq_lens=seq_lens, block_table=block_table, max_q=max_q, max_kv=max_kv,
+            decode=(max_q == 1), causal=causal, mask=mask, workspace=self._workspace,
+        )
+
+    def forward(self, q, layer: int, batch: Batch, *, scale: float, window: int = 0):
+        md = batch.attn_metadata
+        pool = get_global_ctx().kv_cache
+        fp8 = getattr(pool, "fp8", False)
+        return ops.paged_attention(
+            q, pool.k_cache(layer), pool.v_cache(layer), md.block_table, md.cu_q, md.seq_lens, scale,
+            causal=md.causal, window=window, mask=md.mask,
+            k_scale=pool.k_scale[layer] if fp8 else None,
+            v_scale=pool.v_scale[layer] if fp8 else None,
+            max_q=md.max_q, max_kv=md.max_kv, decode=md.decode, workspace=md.workspace,
+        )

@@ -1,0 +1,371 @@
+"""Per-rank engine: owns the model, the KV pool, the token pool, the attention backend, the
+sampler and the CUDA graphs, and runs one forward step for the scheduler.
+
+Boot order follows python/minisgl/engine/engine.py:217-845: rank info → device/stream →
+communication → model on the target device → weights (checkpoint or random) → post-load
+repack → KV sizing (min over ranks) → pools → attention backend → sampler → graph capture.
+
+Host→device traffic of a step is one pinned int32 staging buffer (gather indices, positions,
+KV slots, lengths, block table, sample rows); device→host traffic is the sampled ids.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from datetime import timedelta
+from typing import List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..attention import create_attention_backend
+from ..config import EngineConfig
+from ..core import Batch, Context, set_global_ctx
+from ..env import ENV
+from ..kvcache import MHAKVCache
+from ..models import create_model
+from ..models.config import NAMED_CONFIGS, ModelConfig
+from ..parallel import comm as comm_mod
+from ..parallel.info import set_dp_info, set_ep, set_tp_info
+from ..utils import cdiv, div_even, init_logger
+from .sample import BatchSamplingArgs, SampleOutput, Sampler
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class StepPlan:
+    """Host-side description of one forward step (all int32 NumPy arrays)."""
+
+    token_idx: np.ndarray      # [T] flat index into the token pool of every input token
+    positions: np.ndarray      # [T]
+    out_loc: np.ndarray        # [T] KV slot of every input token
+    cu_q: np.ndarray           # [B+1]
+    seq_lens: np.ndarray       # [B]
+    block_table: np.ndarray    # [B, P]
+    sample_rows: np.ndarray    # [S] rows of the packed hidden states that are sampled
+    write_idx: np.ndarray      # [S] flat token-pool index receiving each sampled token
+    max_q: int = 1
+    max_kv: int = 1
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.token_idx.shape[0])
+
+    @property
+    def h2d_bytes(self) -> int:
+        return 4 * (3 * self.token_idx.size + self.cu_q.size + self.seq_lens.size
+                    + self.block_table.size + self.sample_rows.size + self.write_idx.size)
+
+
+@dataclass
+class ForwardOutput:
+    tokens_gpu: torch.Tensor
+    tokens_cpu: torch.Tensor
+    event: Optional["torch.cuda.Event"]
+    sample: Optional[SampleOutput] = None
+    logits: Optional[torch.Tensor] = None
+
+    def wait(self) -> torch.Tensor:
+        if self.event is not None:
+            self.event.synchronize()
+        return self.tokens_cpu
+
+
+def _resolve_dtype(cfg: EngineConfig, model_cfg: ModelConfig, device: str) -> torch.dtype:
+    name = cfg.dtype
+    if name == "auto":
+        name = "fp32" if device == "cpu" else model_cfg.torch_dtype
+    table = {"fp16": torch.float16, "float16": torch.float16, "half": torch.float16,
+             "bf16": torch.bfloat16, "bfloat16": torch.bfloat16,
+             "fp32": torch.float32, "float32": torch.float32, "float": torch.float32}
+    dt = table[name]
+    if device == "cuda" and dt == torch.float32:
+        dt = torch.bfloat16
+    return dt
+
+
+def resolve_model_config(cfg: EngineConfig) -> ModelConfig:
+    if cfg.model_config is not None:
+        mc = cfg.model_config
+    elif cfg.model_path in NAMED_CONFIGS:
+        mc = NAMED_CONFIGS[cfg.model_path]()
+    else:
+        mc = ModelConfig.from_hf(cfg.model_path)
+    if cfg.quantization and mc.quant is None:
+        from ..quant.config import QuantConfig
+
+        qc = {
+            "mxfp4": {"quant_method": "mxfp4"},
+            "fp8": {"quant_method": "compressed-tensors", "config_groups": {"g": {
+                "weights": {"num_bits": 8, "type": "float", "strategy": "channel"}, "targets": ["Linear"]}},
+                "ignore": ["lm_head"]},
+            "fp8_block": {"quant_method": "fp8", "weight_block_size": [128, 128]},
+            "nvfp4": {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized", "config_groups": {"g": {
+                "weights": {"num_bits": 4, "type": "float", "group_size": 16}, "targets": ["Linear"]}},
+                "ignore": ["lm_head"]},
+            "int4": {"quant_method": "gptq", "bits": 4, "group_size": 128, "sym": True},
+        }[cfg.quantization]
+        mc = mc.with_quant(QuantConfig.from_hf(qc))
+    return mc
+
+
+class Engine:
+    def __init__(self, config: EngineConfig) -> None:
+        self.config = config
+        set_tp_info(config.tp_rank, config.tp_size)
+        set_dp_info(config.dp_rank, config.dp_size)
+        set_ep(config.enable_ep, over_tp=(config.dp_size == 1))
+        dev_kind = config.resolve_device()
+        if dev_kind == "cuda":
+            local = int(os.environ.get("LOCAL_RANK", config.device_id)) if "LOCAL_RANK" in os.environ else config.device_id
+            self.device = torch.device("cuda", local)
+            torch.cuda.set_device(self.device)
+            self.stream = torch.cuda.Stream(self.device)
+        else:
+            self.device = torch.device("cpu")
+            self.stream = None
+        self.model_config = resolve_model_config(config)
+        self.dtype = _resolve_dtype(config, self.model_config, dev_kind)
+        self.cpu_group: Optional[dist.ProcessGroup] = None
+        self.tp_group: Optional[dist.ProcessGroup] = None
+        self._init_communication()
+
+        free_before = self._free_memory()
+        self.model = create_model(self.model_config, self.dtype, self.device)
+        if config.use_dummy_weight or not config.model_path or config.model_path in NAMED_CONFIGS:
+            gen_dev = "cuda" if dev_kind == "cuda" else "cpu"
+            self.model.init_dummy(config.seed, gen_device=gen_dev)
+        else:
+            from ..models.weight import load_weights
+
+            load_weights(self.model, config.model_path, self.model_config, self.device)
+        self.model.post_load()
+        if dev_kind == "cuda":
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        self.model_bytes = max(free_before - self._free_memory(), 0)
+
+        # ---- KV pool ----
+        mc = self.model_config
+        self.page_size = config.page_size
+        self.kv_heads_local = div_even(mc.num_kv_heads, config.tp_size, allow_replicate=True)
+        self.q_heads_local = div_even(mc.num_qo_heads, config.tp_size)
+        kv_fp8 = config.kv_cache_dtype == "fp8" or (config.kv_cache_dtype == "auto" and (
+            ENV.KV_FP8.value or (mc.quant is not None and mc.quant.kv_cache_fp8)))
+        self.kv_fp8 = bool(kv_fp8)
+        self.num_pages = self._determine_num_pages()
+        self.max_seq_len = self._resolve_max_seq_len()
+        self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
+        self.kv_cache = MHAKVCache(
+            mc.num_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
+            self.dtype, self.device, fp8=self.kv_fp8,
+        )
+        # slot max_running_req is the dummy request used to pad graph batches
+        self.num_slots = config.max_running_req + 1
+        self.token_pool = torch.zeros((self.num_slots, self.max_seq_len), dtype=torch.int32, device=self.device)
+        self.ctx = Context(page_size=self.page_size)
+        self.ctx.kv_cache = self.kv_cache
+        self.ctx.attn_backend = create_attention_backend(
+            config.attention_backend, self.q_heads_local, self.kv_heads_local, mc.head_dim, self.device,
+            max_batch=config.max_running_req,
+        )
+        self.ctx.comm = comm_mod.get_comm()
+        set_global_ctx(self.ctx)
+        self.sampler = Sampler(self.device, mc.vocab_size, mc.final_logit_softcapping, seed=config.seed)
+        self._staging_cap = 0
+        self._staging_host: Optional[torch.Tensor] = None
+        self._staging_dev: Optional[torch.Tensor] = None
+        self._out_host = torch.empty(max(config.max_running_req * 8, 64), dtype=torch.int32,
+                                     pin_memory=(dev_kind == "cuda"))
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.steps = 0
+        self.graph_runner = None
+        if dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0:
+            from .graph import GraphRunner
+
+            self.graph_runner = GraphRunner(self)
+        logger.info_rank0(
+            "engine ready: %s, %d pages x %d tokens, max_seq_len %d, dtype %s, kv %s",
+            mc.model_type, self.num_pages, self.page_size, self.max_seq_len, self.dtype,
+            "fp8" if self.kv_fp8 else str(self.dtype))
+
+    # ------------------------------------------------------------------ boot helpers
+    def _init_communication(self) -> None:
+        cfg = self.config
+        comm = comm_mod.reset_comm()
+        world = cfg.tp_size * cfg.dp_size
+        if world == 1:
+            return
+        timeout = timedelta(seconds=cfg.distributed_timeout)
+        backend = "nccl" if self.device.type == "cuda" else "gloo"
+        if not dist.is_initialized():
+            if "RANK" in os.environ and "MASTER_ADDR" in os.environ:
+                dist.init_process_group(backend, timeout=timeout,
+                                        device_id=self.device if backend == "nccl" else None)
+            else:
+                dist.init_process_group(backend, init_method=cfg.world_addr, rank=cfg.global_rank,
+                                        world_size=world, timeout=timeout,
+                                        device_id=self.device if backend == "nccl" else None)
+        # one TP group per replica; every rank must create all of them
+        for r in range(cfg.dp_size):
+            ranks = list(range(r * cfg.tp_size, (r + 1) * cfg.tp_size))
+            g = dist.new_group(ranks, backend=backend, timeout=timeout)
+            c = dist.new_group(ranks, backend="gloo", timeout=timeout)
+            if r == cfg.dp_rank:
+                self.tp_group, self.cpu_group = g, c
+        self.dp_group = self.dp_cpu_group = None
+        if cfg.dp_size > 1:
+            for t in range(cfg.tp_size):
+                ranks = [r * cfg.tp_size + t for r in range(cfg.dp_size)]
+                g = dist.new_group(ranks, backend=backend, timeout=timeout)
+                c = dist.new_group(ranks, backend="gloo", timeout=timeout)
+                if t == cfg.tp_rank:
+                    self.dp_group, self.dp_cpu_group = g, c
+        if cfg.tp_size > 1:
+            comm.register(comm_mod.TorchCollectives(self.tp_group))
+            if self.device.type == "cuda" and not ENV.DISABLE_FUSED_COMM.value:
+                try:
+                    from ..parallel.symm import SymmetricCollectives
+
+                    comm.register(SymmetricCollectives(self.tp_group, self.cpu_group, self.device,
+                                                       cfg.tp_rank, cfg.tp_size))
+                except Exception as exc:  # falls back to the NCCL data plane, loudly
+                    logger.warning("symmetric-memory collectives unavailable (%s); using NCCL only", exc)
+
+    def _free_memory(self) -> int:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            return torch.cuda.mem_get_info(self.device)[0]
+        return 0
+
+    def _determine_num_pages(self) -> int:
+        """Pages that fit in ``memory_ratio`` of the device after the model, minus room for
+        activations and graphs; the minimum over tensor-parallel ranks is used
+        (python/minisgl/engine/engine.py:1828-2093)."""
+        cfg, mc = self.config, self.model_config
+        if cfg.num_page_override is not None:
+            return int(cfg.num_page_override)
+        itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
+        per_page = MHAKVCache.token_bytes(mc.num_layers, self.kv_heads_local, mc.head_dim, itemsize) * self.page_size
+        if self.device.type != "cuda":
+            return 2048
+        free, total = torch.cuda.mem_get_info(self.device)
+        # activation reserve: the widest intermediates of one prefill chunk
+        chunk = getattr(cfg, "max_extend_tokens", 8192)
+        widest = max(2 * mc.intermediate_size // cfg.tp_size, mc.q_size + 2 * mc.kv_size, mc.hidden_size * 4)
+        act_reserve = chunk * widest * 2 * 4 + (2 << 30)
+        budget = int(total * cfg.memory_ratio) - (total - free) - act_reserve
+        pages = budget // per_page
+        if self.cpu_group is not None:
+            t = torch.tensor([pages], dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.cpu_group)
+            pages = int(t.item())
+        if pages < 16:
+            raise RuntimeError(f"not enough memory for the KV cache ({pages} pages)")
+        return int(pages)
+
+    def _resolve_max_seq_len(self) -> int:
+        cfg, mc = self.config, self.model_config
+        limit = cfg.max_seq_len_override or mc.max_position_embeddings
+        limit = min(limit, mc.rotary_config.max_position, self.num_pages * self.page_size)
+        return int(limit // self.page_size * self.page_size) or self.page_size
+
+    # ------------------------------------------------------------------ step
+    def _stage(self, plan: StepPlan):
+        """Pack the plan into one pinned buffer and start a single H2D copy; returns device
+        views in plan order."""
+        parts = [plan.token_idx, plan.positions, plan.out_loc, plan.cu_q, plan.seq_lens,
+                 plan.block_table.reshape(-1), plan.sample_rows, plan.write_idx]
+        total = sum(int(p.size) for p in parts)
+        if total > self._staging_cap:
+            self._staging_cap = max(total * 2, 1 << 16)
+            self._staging_host = torch.empty(self._staging_cap, dtype=torch.int32,
+                                             pin_memory=(self.device.type == "cuda"))
+            self._staging_dev = torch.empty(self._staging_cap, dtype=torch.int32, device=self.device)
+            self._staging_np = self._staging_host.numpy()
+        off, views = 0, []
+        for p in parts:
+            n = int(p.size)
+            self._staging_np[off : off + n] = p.reshape(-1)
+            views.append((off, n))
+            off += n
+        if self.device.type == "cuda":
+            self._staging_dev[:total].copy_(self._staging_host[:total], non_blocking=True)
+            src = self._staging_dev
+        else:
+            src = self._staging_host.clone()
+        self.h2d_bytes += 4 * total
+        out = [src[o : o + n] for o, n in views]
+        out[5] = out[5].view(plan.block_table.shape)
+        return out
+
+    def forward_batch(self, batch: Batch, plan: StepPlan, args: BatchSamplingArgs,
+                      return_logits: bool = False) -> ForwardOutput:
+        """Run one step: gather ids, model forward, LM head on the sampled rows, sample, write
+        the new ids back into the token pool and start their device→host copy."""
+        if self.stream is not None:
+            with torch.cuda.stream(self.stream):
+                return self._forward_impl(batch, plan, args, return_logits)
+        return self._forward_impl(batch, plan, args, return_logits)
+
+    def _forward_impl(self, batch, plan, args, return_logits) -> ForwardOutput:
+        token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
+        batch.positions = positions
+        batch.out_loc = out_loc
+        n_sample = int(plan.sample_rows.size)
+        use_graph = (self.graph_runner is not None and batch.is_decode and not batch.spec_verify
+                     and plan.max_q == 1 and self.graph_runner.can_run(batch.size)
+                     and batch.capture_layers is None)
+        if use_graph:
+            logits = self.graph_runner.replay(batch, token_idx, positions, out_loc, seq_lens, block_table, plan)
+        else:
+            batch.input_ids = self.token_pool.view(-1)[token_idx.long()]
+            self.ctx.attn_backend.prepare_metadata(
+                batch, block_table, cu_q, seq_lens, plan.max_q, plan.max_kv,
+                causal=True, mask=batch.tree_mask)
+            with self.ctx.forward_batch(batch):
+                hidden = self.model.forward(batch.input_ids)
+                if n_sample == 0:
+                    logits = None
+                else:
+                    rows = hidden if n_sample == hidden.shape[0] else hidden[sample_rows.long()]
+                    logits = self.model.lm_head.forward(rows)
+        self.steps += 1
+        if n_sample == 0:
+            empty = torch.empty(0, dtype=torch.int32)
+            return ForwardOutput(empty.to(self.device), empty, None)
+        sample = self.sampler.sample(logits, args)
+        tokens = sample.tokens
+        tokens = self._agree_tokens(tokens)
+        self.token_pool.view(-1)[write_idx.long()] = tokens
+        host = self._out_host[:n_sample] if n_sample <= self._out_host.numel() else torch.empty(
+            n_sample, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        event = None
+        if self.device.type == "cuda":
+            host.copy_(tokens, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            host_out = host
+        else:
+            host_out = tokens.clone()
+        self.d2h_bytes += 4 * n_sample
+        return ForwardOutput(tokens, host_out, event, sample, logits if return_logits else None)
+
+    def _agree_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
+        """All tensor-parallel ranks adopt rank 0's ids
+        (python/minisgl/engine/sample.py:252-277)."""
+        if self.config.tp_size == 1 or self.tp_group is None:
+            return tokens
+        dist.broadcast(tokens, src=self.config.dp_rank * self.config.tp_size, group=self.tp_group)
+        return tokens
+
+    def shutdown(self) -> None:
+        set_global_ctx(None)
+        if dist.is_initialized() and self.config.world_size > 1:
+            try:
+                dist.barrier(group=self.cpu_group)
+            except Exception:
+                pass

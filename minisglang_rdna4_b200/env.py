@@ -1,0 +1,161 @@
+"""Typed environment-variable registry.
+
+Every tunable that is read from the process environment is declared here exactly once,
+with a type, a default and a one-line description. The reference reads seven variables
+through a typed singleton (python/minisgl/env.py:58-87) and about 260 more through ad hoc
+``os.environ`` lookups scattered over the tree; this build keeps one registry so that
+``python -m minisglang_rdna4_b200 --print-env`` can list every knob.
+
+Names use the ``MSGL_`` prefix. For drop-in use, a variable that is not set under
+``MSGL_X`` is also looked up as ``MINISGL_X`` (the reference's prefix).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Generic, TypeVar
+
+T = TypeVar("T")
+
+_TRUE = {"1", "true", "yes", "on", "y", "t"}
+_FALSE = {"0", "false", "no", "off", "n", "f", ""}
+
+
+def _parse_bool(text: str) -> bool:
+    low = text.strip().lower()
+    if low in _TRUE:
+        return True
+    if low in _FALSE:
+        return False
+    raise ValueError(f"not a boolean: {text!r}")
+
+
+def _parse_int(text: str) -> int:
+    return int(text.strip(), 0)
+
+
+def _parse_float(text: str) -> float:
+    return float(text.strip())
+
+
+def _parse_str(text: str) -> str:
+    return text
+
+
+@dataclass
+class EnvVar(Generic[T]):
+    """One declared variable. ``value`` re-reads the environment on each access so tests
+    can monkeypatch ``os.environ`` without resetting a cache."""
+
+    name: str
+    default: T
+    parser: Callable[[str], T]
+    doc: str = ""
+
+    def raw(self) -> str | None:
+        for prefix in ("MSGL_", "MINISGL_"):
+            text = os.environ.get(prefix + self.name)
+            if text is not None:
+                return text
+        return None
+
+    @property
+    def value(self) -> T:
+        text = self.raw()
+        if text is None or text.strip() == "":
+            # An empty string means "unset" (python/minisgl/kvcache/_envutil.py tolerates the
+            # same: compose files export VAR= for knobs that are switched off).
+            return self.default
+        try:
+            return self.parser(text)
+        except ValueError as exc:  # pragma: no cover - message path
+            raise ValueError(f"environment variable {self.name}: {exc}") from None
+
+    def __bool__(self) -> bool:
+        return bool(self.value)
+
+
+class EnvRegistry:
+    """Attribute-style access to the declared variables: ``ENV.KV_FP8.value``."""
+
+    def __init__(self) -> None:
+        self._vars: Dict[str, EnvVar[Any]] = {}
+
+    def _add(self, var: EnvVar[Any]) -> EnvVar[Any]:
+        if var.name in self._vars:
+            raise KeyError(f"duplicate env declaration {var.name}")
+        self._vars[var.name] = var
+        setattr(self, var.name, var)
+        return var
+
+    def flag(self, name: str, default: bool = False, doc: str = "") -> EnvVar[bool]:
+        return self._add(EnvVar(name, default, _parse_bool, doc))
+
+    def int(self, name: str, default: int, doc: str = "") -> EnvVar[int]:
+        return self._add(EnvVar(name, default, _parse_int, doc))
+
+    def float(self, name: str, default: float, doc: str = "") -> EnvVar[float]:
+        return self._add(EnvVar(name, default, _parse_float, doc))
+
+    def str(self, name: str, default: str = "", doc: str = "") -> EnvVar[str]:
+        return self._add(EnvVar(name, default, _parse_str, doc))
+
+    def items(self):
+        return sorted(self._vars.items())
+
+    def describe(self) -> str:
+        lines = []
+        for name, var in self.items():
+            lines.append(f"MSGL_{name:<28} = {var.value!r:<12} (default {var.default!r})  {var.doc}")
+        return "\n".join(lines)
+
+
+ENV = EnvRegistry()
+
+# --- engine -------------------------------------------------------------------------------
+ENV.flag("KV_FP8", False, "store the paged KV pool as e4m3 with per-(layer,head) scales")
+ENV.flag("DISABLE_OVERLAP", False, "run the synchronous scheduler loop instead of the overlapped one")
+ENV.flag("DISABLE_GRAPH", False, "never capture CUDA graphs (eager decode)")
+ENV.int("GRAPH_MAX_BS", 0, "largest decode batch captured as a CUDA graph (0 = auto)")
+ENV.int("EXIT_AFTER_STEPS", 0, "stop the scheduler loop after this many forward steps (0 = never)")
+ENV.flag("SANITIZE_LOGITS", False, "replace NaN/Inf logits before sampling and count them")
+ENV.flag("CHECK_BOUNDS", False, "kernels validate page/token/expert ids and record bad ones instead of using them")
+ENV.flag("DISPATCH_LEDGER", False, "log once per op which sm_100a kernel served it")
+ENV.str("PROFILE", "", "path of a torch.profiler chrome trace to write around the profiled steps")
+ENV.int("PROFILE_SKIP", 8, "forward steps to skip before the profiler window opens")
+ENV.int("PROFILE_STEPS", 8, "forward steps inside the profiler window")
+ENV.flag("HOSTPROF", False, "print a host-side stage breakdown of the scheduler loop")
+ENV.flag("GRAPH_TIMING", False, "time every graph replay with CUDA events")
+ENV.flag("SPEC_TIMING", False, "time the stages of a speculative decode step")
+ENV.flag("FEEDBACK_CHECK", False, "verify that the token fed to step n+1 is the token sampled at step n")
+# --- distributed --------------------------------------------------------------------------
+ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")
+ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
+ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
+ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger use two-shot")
+ENV.int("COMM_WAIT_US", 2_000_000, "bound of every device-side flag wait, in microseconds")
+ENV.flag("TP_OVERLAP", False, "overlap row-parallel all-reduce with compute on a side stream (eager prefill)")
+# --- speculative decode -------------------------------------------------------------------
+ENV.flag("SPEC_SAMPLED", False, "verify drafts by rejection sampling instead of greedy prefix match")
+ENV.int("SPEC_MAX_BS", 0, "largest batch that still runs a speculative step (0 = per-algorithm default)")
+ENV.flag("SPEC_ADAPTIVE_WIDTH", True, "choose the verify width from the running acceptance rate")
+# --- quantization -------------------------------------------------------------------------
+ENV.flag("MOE_W4A16", False, "run int4/fp4 expert weights against 16-bit activations")
+ENV.flag("FORCE_BF16_DEQUANT", False, "dequantise quantised checkpoints to bf16 at load (debug)")
+# --- server -------------------------------------------------------------------------------
+ENV.flag("METRICS", True, "collect Prometheus metrics")
+ENV.int("DEFAULT_MAX_TOKENS", 1024, "max_tokens applied to a request that gives none")
+ENV.str("SHELL_SYSTEM_PROMPT", "", "system prompt of the interactive shell")
+ENV.flag("LOG_REQUESTS", False, "log one line per admitted and finished request")
+
+
+def env_int(name: str, default: int) -> int:
+    """Read an undeclared integer knob, treating an empty string as unset."""
+    for prefix in ("MSGL_", "MINISGL_"):
+        text = os.environ.get(prefix + name)
+        if text is not None and text.strip() != "":
+            return int(text, 0)
+    return default
+
+
+__all__ = ["ENV", "EnvVar", "EnvRegistry", "env_int"]

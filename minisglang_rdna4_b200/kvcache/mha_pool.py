@@ -1,0 +1,101 @@
+"""Paged multi-head KV pool.
+
+Layout ``[2, layers, pages, kv_heads, page_size, head_dim]`` (head-major inside a page) so
+that one (page, head) tile is a contiguous ``page_size x head_dim`` block: the decode and
+extend attention kernels fetch it with one bulk copy. With ``fp8`` storage the pool holds
+e4m3 bytes and a float32 descale per (layer, kv head) for K and for V
+(``value = byte * descale``; python/minisgl/kvcache/mha_pool.py:37-43,55-270 keeps the same
+per-head scales). Page ``num_pages`` (one past the end) is a scratch page for padded
+requests of a captured graph.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import BaseKVCachePool
+
+
+class MHAKVCache(BaseKVCachePool):
+    def __init__(
+        self,
+        num_layers: int,
+        num_pages: int,
+        page_size: int,
+        num_kv_heads: int,
+        head_dim: int,
+        dtype: torch.dtype,
+        device: torch.device,
+        fp8: bool = False,
+    ) -> None:
+        self.num_layers = num_layers
+        self.num_pages = num_pages
+        self.page_size = page_size
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.compute_dtype = dtype
+        self.fp8 = fp8
+        store_dtype = torch.float8_e4m3fn if fp8 else dtype
+        # +1: the dummy page written by padded rows of a graph replay
+        self._buf = torch.zeros(
+            (2, num_layers, num_pages + 1, num_kv_heads, page_size, head_dim),
+            dtype=store_dtype,
+            device=device,
+        )
+        self.k_scale = torch.ones((num_layers, num_kv_heads), dtype=torch.float32, device=device)
+        self.v_scale = torch.ones((num_layers, num_kv_heads), dtype=torch.float32, device=device)
+
+    # ---- accessors ----
+    @property
+    def dummy_page(self) -> int:
+        return self.num_pages
+
+    def k_cache(self, layer: int) -> torch.Tensor:
+        return self._buf[0, layer]
+
+    def v_cache(self, layer: int) -> torch.Tensor:
+        return self._buf[1, layer]
+
+    @property
+    def device(self) -> torch.device:
+        return self._buf.device
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self._buf.dtype
+
+    @property
+    def bytes_per_token(self) -> int:
+        return 2 * self.num_layers * self.num_kv_heads * self.head_dim * self._buf.element_size()
+
+    @staticmethod
+    def token_bytes(num_layers: int, kv_heads: int, head_dim: int, itemsize: int) -> int:
+        return 2 * num_layers * kv_heads * head_dim * itemsize
+
+    def set_scales(self, k_scale: torch.Tensor, v_scale: torch.Tensor) -> None:
+        """Install per-(layer, head) descales (amax / 448)."""
+        self.k_scale.copy_(k_scale.to(self.k_scale))
+        self.v_scale.copy_(v_scale.to(self.v_scale))
+
+    # ---- writes ----
+    def store_kv(self, k: torch.Tensor, v: torch.Tensor, out_loc: torch.Tensor, layer: int) -> None:
+        """Scatter ``k``/``v`` rows ``[T, kv_heads, head_dim]`` to token slots ``out_loc``."""
+        from ..ops import store_kv
+
+        store_kv(
+            k, v, self._buf[0, layer], self._buf[1, layer], out_loc,
+            self.k_scale[layer] if self.fp8 else None,
+            self.v_scale[layer] if self.fp8 else None,
+        )
+
+    # ---- reads (reference path and tests) ----
+    def gather(self, layer: int, slots: torch.Tensor, which: int) -> torch.Tensor:
+        """Rows ``[len(slots), kv_heads, head_dim]`` in compute precision."""
+        page = slots // self.page_size
+        off = slots % self.page_size
+        rows = self._buf[which, layer][page, :, off]  # [n, heads, dim]
+        if self.fp8:
+            scale = (self.k_scale if which == 0 else self.v_scale)[layer]
+            return rows.to(torch.float32) * scale[None, :, None]
+        return rows

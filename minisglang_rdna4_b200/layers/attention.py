@@ -1,0 +1,48 @@
+"""Attention layer: fused QK-norm + RoPE + KV store, then paged attention through the
+backend in the global context (python/minisgl/layers/attention.py:19-141)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..core import get_global_ctx
+from ..models.config import RotaryConfig
+from .base import BaseOP
+from .rotary import get_rope_cache
+
+
+class AttentionLayer(BaseOP):
+    _non_persistent = ("_cos_sin",)
+
+    def __init__(self, layer_id: int, num_q_local: int, num_kv_local: int, head_dim: int,
+                 rotary: RotaryConfig, eps: float, dtype, device,
+                 window: int = 0, scale: Optional[float] = None) -> None:
+        self._layer_id = layer_id
+        self._hq, self._hk, self._d = num_q_local, num_kv_local, head_dim
+        self._rotary = rotary
+        self._eps = eps
+        self._window = window
+        self._scale = scale if scale is not None else head_dim ** -0.5
+        self._device = device
+        self._cos_sin: Optional[torch.Tensor] = None
+
+    def forward(self, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None,
+                k_norm_w: Optional[torch.Tensor] = None) -> torch.Tensor:
+        ctx = get_global_ctx()
+        batch = ctx.batch
+        if self._cos_sin is None:
+            self._cos_sin = get_rope_cache(self._rotary, qkv.device)
+        pool = ctx.kv_cache
+        layer = self._layer_id
+        k_scale = pool.k_scale[layer] if pool.fp8 else None
+        v_scale = pool.v_scale[layer] if pool.fp8 else None
+        q = ops.qk_norm_rope_store(
+            qkv, q_norm_w, k_norm_w,
+            batch.positions, self._cos_sin, self._hq, self._hk, self._d, self._rotary.rotary_dim,
+            self._eps, pool.k_cache(layer), pool.v_cache(layer), batch.out_loc, k_scale, v_scale,
+            self._rotary.interleaved,
+        )
+        out = ctx.attn_backend.forward(q, layer, batch, scale=self._scale, window=self._window)
+        return out.reshape(out.shape[0], self._hq * self._d)

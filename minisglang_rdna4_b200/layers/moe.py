@@ -1,0 +1,69 @@
+"""Mixture-of-experts layer: router → top-k → grouped expert MLP → weighted combine, with
+tensor-parallel (intermediate dimension sharded) and expert-parallel (whole experts sharded)
+placements (python/minisgl/layers/moe.py:1008-1446).
+
+Expert weights are stacked: ``w13 [E_local, 2I, H]`` (gate rows then up rows) and
+``w2 [E_local, H, I]``. Under expert parallelism every rank runs the router on its own
+tokens; ``parallel/ep.py`` moves token rows to the ranks that own the selected experts and
+brings the weighted results back.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..core import try_global_ctx
+from ..parallel.info import ep_enabled, get_ep_info, get_tp_info
+from ..utils import div_even
+from .base import BaseOP
+from .linear import ReplicatedLinear
+
+
+class MoELayer(BaseOP):
+    def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, renormalize: bool,
+                 dtype, device, scoring: str = "softmax", routed_scale: float = 1.0,
+                 scheme=None) -> None:
+        tp = get_tp_info()
+        ep = get_ep_info()
+        self._ep = ep if ep_enabled() else None
+        self._E, self._k = num_experts, top_k
+        self._renorm, self._scoring, self._routed_scale = renormalize, scoring, routed_scale
+        if self._ep is not None:
+            self._e_local = div_even(num_experts, self._ep.size)
+            self._e_start = self._ep.rank * self._e_local
+            self._i_local = inter
+        else:
+            self._e_local, self._e_start = num_experts, 0
+            self._i_local = div_even(inter, tp.size)
+        self._hidden = hidden
+        self._compute_dtype = dtype
+        self.gate = ReplicatedLinear(hidden, num_experts, dtype, device, None)
+        self.w13 = torch.empty((self._e_local, 2 * self._i_local, hidden), dtype=dtype, device=device)
+        self.w2 = torch.empty((self._e_local, hidden, self._i_local), dtype=dtype, device=device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Returns this rank's partial result (tensor-parallel partial sum when the
+        intermediate dimension is sharded; complete under expert parallelism)."""
+        logits = self.gate.forward(x)
+        topk_w, topk_ids = ops.moe_route(logits, self._k, self._renorm, self._scoring, None,
+                                         self._routed_scale)
+        ctx = try_global_ctx()
+        if self._ep is not None and ctx is not None and ctx.ep is not None:
+            return ctx.ep.dispatch_compute_combine(self, x, topk_w, topk_ids)
+        return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
+
+    def local_experts(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
+
+    @property
+    def needs_tp_reduce(self) -> bool:
+        return self._ep is None and get_tp_info().size > 1
+
+    def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
+        for name in ("w13", "w2"):
+            t = getattr(self, name)
+            w = torch.randn(t.shape, generator=gen, device=gen.device, dtype=torch.float32) * std
+            setattr(self, name, w.to(t.device, t.dtype))
+        self.gate.init_dummy(gen, std)

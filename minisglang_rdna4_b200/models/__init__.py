@@ -1,0 +1,33 @@
+"""Model registry: architecture string → constructor (python/minisgl/models/register.py:5-34)."""
+from __future__ import annotations
+
+import torch
+
+from ..utils import Registry
+from .config import NAMED_CONFIGS, ModelConfig, RotaryConfig
+
+MODEL_REGISTRY: Registry = Registry("model architecture")
+
+
+def _register_defaults() -> None:
+    from .transformer import CausalLM
+
+    for arch in (
+        "LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM",
+        "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM",
+    ):
+        if arch not in MODEL_REGISTRY:
+            MODEL_REGISTRY.register(arch)(CausalLM)
+
+
+def create_model(cfg: ModelConfig, dtype: torch.dtype, device):
+    """Instantiate the model for ``cfg`` with uninitialised (or meta) parameters."""
+    _register_defaults()
+    for arch in cfg.architectures:
+        if arch in MODEL_REGISTRY:
+            return MODEL_REGISTRY[arch](cfg, dtype, device)
+    raise KeyError(f"no model registered for architectures {cfg.architectures}; "
+                   f"known: {MODEL_REGISTRY.names()}")
+
+
+__all__ = ["MODEL_REGISTRY", "create_model", "ModelConfig", "RotaryConfig", "NAMED_CONFIGS"]

@@ -1,0 +1,298 @@
+"""Model hyper-parameters, normalised from a Hugging Face ``config.json``.
+
+Covers the dense Llama/Mistral/Qwen2/Qwen3 families, the Qwen2/Qwen3 MoE families, MLA
+(DeepSeek/GLM-lite style latent attention) and sliding-window fields. The reference does the
+same normalisation in python/minisgl/models/config.py:144-1273.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field, replace
+from typing import Any, Dict, List, Optional, Tuple
+
+from ..quant.config import QuantConfig
+
+
+@dataclass(frozen=True)
+class RotaryConfig:
+    head_dim: int
+    rotary_dim: int
+    max_position: int
+    base: float
+    scaling: Optional[Dict[str, Any]] = None  # llama3 / yarn / linear / dynamic parameters
+    interleaved: bool = False                 # GPT-J pairing (x0,x1) instead of NeoX halves
+
+    def key(self) -> Tuple:
+        return (
+            self.head_dim,
+            self.rotary_dim,
+            self.max_position,
+            self.base,
+            json.dumps(self.scaling, sort_keys=True) if self.scaling else None,
+            self.interleaved,
+        )
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    num_layers: int
+    num_qo_heads: int
+    num_kv_heads: int
+    head_dim: int
+    hidden_size: int
+    vocab_size: int
+    intermediate_size: int
+    rms_norm_eps: float
+    rotary_config: RotaryConfig
+    hidden_act: str = "silu"
+    tie_word_embeddings: bool = False
+    model_type: str = "llama"
+    architectures: Tuple[str, ...] = ("LlamaForCausalLM",)
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False
+    # mixture of experts
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0
+    shared_expert_gate: bool = False
+    decoder_sparse_step: int = 1
+    mlp_only_layers: Tuple[int, ...] = ()
+    first_k_dense_replace: int = 0
+    n_shared_experts: int = 0
+    routed_scaling_factor: float = 1.0
+    scoring_func: str = "softmax"
+    n_group: int = 1
+    topk_group: int = 1
+    # latent attention
+    kv_lora_rank: Optional[int] = None
+    q_lora_rank: Optional[int] = None
+    qk_nope_head_dim: Optional[int] = None
+    qk_rope_head_dim: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    # misc
+    sliding_window: Optional[int] = None
+    layer_types: Optional[Tuple[str, ...]] = None
+    final_logit_softcapping: Optional[float] = None
+    num_nextn_predict_layers: int = 0
+    eos_token_ids: Tuple[int, ...] = ()
+    bos_token_id: Optional[int] = None
+    torch_dtype: str = "bfloat16"
+    max_position_embeddings: int = 32768
+    quant: Optional[QuantConfig] = None
+    # EAGLE3 draft head fields
+    draft_vocab_size: Optional[int] = None
+    eagle_aux_layers: Optional[Tuple[int, ...]] = None
+
+    # ---- derived ----
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank is not None
+
+    @property
+    def q_size(self) -> int:
+        return self.num_qo_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    def layer_is_moe(self, layer: int) -> bool:
+        if not self.is_moe or layer in self.mlp_only_layers:
+            return False
+        if layer < self.first_k_dense_replace:
+            return False
+        return (layer + 1) % max(self.decoder_sparse_step, 1) == 0
+
+    def with_quant(self, quant: Optional[QuantConfig]) -> "ModelConfig":
+        return replace(self, quant=quant)
+
+    def param_count(self) -> int:
+        """Parameter count of the unquantised model (used for memory planning)."""
+        h, v = self.hidden_size, self.vocab_size
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        total = v * h * (1 if self.tie_word_embeddings else 2)
+        for layer in range(self.num_layers):
+            total += attn + 2 * h
+            if self.layer_is_moe(layer):
+                total += self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+                total += 3 * h * self.shared_expert_intermediate_size
+            else:
+                total += 3 * h * self.intermediate_size
+        return total
+
+    # ---- construction ----
+    @staticmethod
+    def from_hf(cfg: Any) -> "ModelConfig":
+        """Build from a dict, a ``transformers`` config object or a path to ``config.json``."""
+        if isinstance(cfg, (str, os.PathLike)):
+            path = os.fspath(cfg)
+            if os.path.isdir(path):
+                path = os.path.join(path, "config.json")
+            with open(path) as fh:
+                cfg = json.load(fh)
+        if not isinstance(cfg, dict):
+            cfg = cfg.to_dict()
+        if "text_config" in cfg and isinstance(cfg["text_config"], dict):
+            inner = dict(cfg["text_config"])
+            for key in ("quantization_config", "architectures", "torch_dtype", "tie_word_embeddings"):
+                if key in cfg and key not in inner:
+                    inner[key] = cfg[key]
+            cfg = inner
+        g = cfg.get
+        model_type = g("model_type", "llama")
+        archs = tuple(g("architectures") or _default_arch(model_type))
+        heads = int(g("num_attention_heads"))
+        hidden = int(g("hidden_size"))
+        head_dim = int(g("head_dim") or hidden // heads)
+        kv_heads = int(g("num_key_value_heads") or heads)
+        max_pos = int(g("max_position_embeddings", 32768))
+        rope_params = g("rope_parameters") or {}
+        scaling = g("rope_scaling") or ({k: v for k, v in rope_params.items() if k != "rope_theta"} or None)
+        if scaling and scaling.get("rope_type", scaling.get("type", "default")) in ("default", None):
+            scaling = None
+        theta = float(g("rope_theta") or rope_params.get("rope_theta") or 10000.0)
+        partial = float(g("partial_rotary_factor", 1.0) or 1.0)
+        rope_dim = int(g("qk_rope_head_dim") or 0) or int(head_dim * partial)
+        rotary = RotaryConfig(
+            head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta, scaling=scaling
+        )
+        eos = g("eos_token_id")
+        eos_ids = tuple(eos) if isinstance(eos, (list, tuple)) else (() if eos is None else (int(eos),))
+        num_experts = int(g("num_experts") or g("num_local_experts") or g("n_routed_experts") or 0)
+        quant = QuantConfig.from_hf(g("quantization_config")) if g("quantization_config") else None
+        layer_types = g("layer_types")
+        qk_norm = model_type in ("qwen3", "qwen3_moe") or bool(g("use_qk_norm", False))
+        attn_bias = bool(g("attention_bias", model_type in ("qwen2", "qwen2_moe")))
+        return ModelConfig(
+            num_layers=int(g("num_hidden_layers")),
+            num_qo_heads=heads,
+            num_kv_heads=kv_heads,
+            head_dim=head_dim,
+            hidden_size=hidden,
+            vocab_size=int(g("vocab_size")),
+            intermediate_size=int(g("intermediate_size") or 0),
+            rms_norm_eps=float(g("rms_norm_eps", 1e-6)),
+            rotary_config=rotary,
+            hidden_act=g("hidden_act", "silu"),
+            tie_word_embeddings=bool(g("tie_word_embeddings", False)),
+            model_type=model_type,
+            architectures=archs,
+            attention_bias=attn_bias,
+            mlp_bias=bool(g("mlp_bias", False)),
+            qk_norm=qk_norm,
+            num_experts=num_experts,
+            num_experts_per_tok=int(g("num_experts_per_tok") or 0),
+            moe_intermediate_size=int(g("moe_intermediate_size") or 0),
+            norm_topk_prob=bool(g("norm_topk_prob", True)),
+            shared_expert_intermediate_size=int(g("shared_expert_intermediate_size") or 0),
+            shared_expert_gate=model_type == "qwen2_moe",
+            decoder_sparse_step=int(g("decoder_sparse_step") or 1),
+            mlp_only_layers=tuple(g("mlp_only_layers") or ()),
+            first_k_dense_replace=int(g("first_k_dense_replace") or 0),
+            n_shared_experts=int(g("n_shared_experts") or 0),
+            routed_scaling_factor=float(g("routed_scaling_factor") or 1.0),
+            scoring_func=g("scoring_func", "softmax"),
+            n_group=int(g("n_group") or 1),
+            topk_group=int(g("topk_group") or 1),
+            kv_lora_rank=g("kv_lora_rank"),
+            q_lora_rank=g("q_lora_rank"),
+            qk_nope_head_dim=g("qk_nope_head_dim"),
+            qk_rope_head_dim=g("qk_rope_head_dim"),
+            v_head_dim=g("v_head_dim"),
+            sliding_window=g("sliding_window") if g("use_sliding_window", True) else None,
+            layer_types=tuple(layer_types) if layer_types else None,
+            final_logit_softcapping=g("final_logit_softcapping"),
+            num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
+            eos_token_ids=eos_ids,
+            bos_token_id=g("bos_token_id"),
+            torch_dtype=str(g("torch_dtype") or g("dtype") or "bfloat16").replace("torch.", ""),
+            max_position_embeddings=max_pos,
+            quant=quant,
+            draft_vocab_size=g("draft_vocab_size"),
+            eagle_aux_layers=tuple(g("eagle_aux_hidden_state_layer_ids") or ()) or None,
+        )
+
+
+def _default_arch(model_type: str) -> List[str]:
+    return {
+        "llama": ["LlamaForCausalLM"],
+        "mistral": ["MistralForCausalLM"],
+        "qwen2": ["Qwen2ForCausalLM"],
+        "qwen2_moe": ["Qwen2MoeForCausalLM"],
+        "qwen3": ["Qwen3ForCausalLM"],
+        "qwen3_moe": ["Qwen3MoeForCausalLM"],
+    }.get(model_type, ["LlamaForCausalLM"])
+
+
+# --------------------------------------------------------------------------------------------
+# Named shapes used by the benchmark configurations (random-init, no checkpoint on disk).
+# --------------------------------------------------------------------------------------------
+def _rot(head_dim: int, theta: float, max_pos: int = 40960) -> RotaryConfig:
+    return RotaryConfig(head_dim=head_dim, rotary_dim=head_dim, max_position=max_pos, base=theta)
+
+
+def tiny_llama_config() -> ModelConfig:
+    """2 layers, hidden 256, 4 q / 2 kv heads of 64, SwiGLU 512, vocab 1024 (CPU oracle run)."""
+    return ModelConfig(
+        num_layers=2, num_qo_heads=4, num_kv_heads=2, head_dim=64, hidden_size=256,
+        vocab_size=1024, intermediate_size=512, rms_norm_eps=1e-6,
+        rotary_config=_rot(64, 1e6, 4096), model_type="llama", torch_dtype="float32",
+        max_position_embeddings=4096,
+    )
+
+
+def qwen3_4b_config(quant: Optional[QuantConfig] = None) -> ModelConfig:
+    return ModelConfig(
+        num_layers=36, num_qo_heads=32, num_kv_heads=8, head_dim=128, hidden_size=2560,
+        vocab_size=151936, intermediate_size=9728, rms_norm_eps=1e-6,
+        rotary_config=_rot(128, 1e6), model_type="qwen3",
+        architectures=("Qwen3ForCausalLM",), qk_norm=True, tie_word_embeddings=True,
+        max_position_embeddings=40960, quant=quant,
+    )
+
+
+def qwen3_8b_config(quant: Optional[QuantConfig] = None) -> ModelConfig:
+    return ModelConfig(
+        num_layers=36, num_qo_heads=32, num_kv_heads=8, head_dim=128, hidden_size=4096,
+        vocab_size=151936, intermediate_size=12288, rms_norm_eps=1e-6,
+        rotary_config=_rot(128, 1e6), model_type="qwen3",
+        architectures=("Qwen3ForCausalLM",), qk_norm=True, max_position_embeddings=40960,
+        quant=quant,
+    )
+
+
+def qwen3_30b_a3b_config(quant: Optional[QuantConfig] = None) -> ModelConfig:
+    return ModelConfig(
+        num_layers=48, num_qo_heads=32, num_kv_heads=4, head_dim=128, hidden_size=2048,
+        vocab_size=151936, intermediate_size=6144, rms_norm_eps=1e-6,
+        rotary_config=_rot(128, 1e6), model_type="qwen3_moe",
+        architectures=("Qwen3MoeForCausalLM",), qk_norm=True, num_experts=128,
+        num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
+        max_position_embeddings=40960, quant=quant,
+    )
+
+
+def llama3_70b_config(quant: Optional[QuantConfig] = None) -> ModelConfig:
+    return ModelConfig(
+        num_layers=80, num_qo_heads=64, num_kv_heads=8, head_dim=128, hidden_size=8192,
+        vocab_size=128256, intermediate_size=28672, rms_norm_eps=1e-5,
+        rotary_config=_rot(128, 5e5, 8192), model_type="llama",
+        architectures=("LlamaForCausalLM",), max_position_embeddings=8192, quant=quant,
+    )
+
+
+NAMED_CONFIGS = {
+    "tiny-llama": tiny_llama_config,
+    "qwen3-4b": qwen3_4b_config,
+    "qwen3-8b": qwen3_8b_config,
+    "qwen3-30b-a3b": qwen3_30b_a3b_config,
+    "llama3-70b": llama3_70b_config,
+}

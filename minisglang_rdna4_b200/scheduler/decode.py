@@ -1,0 +1,39 @@
+"""The set of requests in the decode phase (python/minisgl/scheduler/decode.py:10-71)."""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional
+
+from ..core import Batch, Req
+
+
+class DecodeManager:
+    def __init__(self, page_size: int = 1) -> None:
+        self.running: Dict[int, Req] = {}
+        self.page_size = page_size
+
+    def add_reqs(self, reqs: Iterable[Req]) -> None:
+        for r in reqs:
+            if r.can_decode and not r.finished:
+                self.running[r.uid] = r
+
+    def remove(self, req: Req) -> None:
+        self.running.pop(req.uid, None)
+
+    def filter_finished(self) -> None:
+        for uid in [u for u, r in self.running.items() if r.finished or not r.can_decode]:
+            del self.running[uid]
+
+    @property
+    def inflight_tokens(self) -> int:
+        """Tokens the running set may still append (reserved when admitting new prefills)."""
+        return sum(r.remain_len for r in self.running.values())
+
+    @property
+    def runnable(self) -> bool:
+        return bool(self.running)
+
+    def schedule_next_batch(self) -> Optional[Batch]:
+        if not self.running:
+            return None
+        reqs = sorted(self.running.values(), key=lambda r: r.uid)
+        return Batch(reqs=reqs, phase="decode")

@@ -1,0 +1,137 @@
+"""Chunked-prefill packing under a per-step token budget
+(python/minisgl/scheduler/prefill.py:43-276).
+
+Rules kept from the reference: FIFO admission that stops at the first request that does not
+fit; admission needs ``extend + output + reserved <= free + evictable`` both before and
+after locking the matched prefix; a chunk that does not finish its prompt leaves 256 tokens
+of the budget to requests queued behind it when the budget exceeds 512; a partially
+prefilled request stays at the head of the queue and is never sampled.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
+from ..core import Batch, ChunkedReq, Req, SamplingParams
+from .cache import CacheManager
+from .decode import DecodeManager
+from .table import TableManager
+
+SHORT_REQ_RESERVE = 256
+MIN_CHUNK = 256
+
+
+@dataclass
+class PendingReq:
+    uid: int
+    input_ids: torch.Tensor
+    sampling_params: SamplingParams
+    chunked: Optional[ChunkedReq] = None
+
+    @property
+    def input_len(self) -> int:
+        return int(self.input_ids.numel())
+
+    @property
+    def output_len(self) -> int:
+        return self.sampling_params.max_tokens
+
+
+class PrefillAdder:
+    def __init__(self, token_budget: int, reserved_tokens: int, cache: CacheManager,
+                 table: TableManager, others_waiting: int = 0) -> None:
+        self.token_budget = token_budget
+        self.reserved = reserved_tokens
+        self.cache = cache
+        self.table = table
+        self.others_waiting = others_waiting
+        self.new_slots: List[Tuple[int, torch.Tensor, int]] = []  # (slot, prompt ids, cached_len)
+
+    def _chunk(self, remain: int) -> int:
+        chunk = min(self.token_budget, remain)
+        if chunk < remain and self.others_waiting > 0 and self.token_budget > 2 * SHORT_REQ_RESERVE:
+            chunk = max(MIN_CHUNK, chunk - SHORT_REQ_RESERVE)
+        return chunk
+
+    def try_add(self, pending: PendingReq) -> Optional[Req]:
+        if self.token_budget <= 0:
+            return None
+        ps = self.cache.page_size
+        if pending.chunked is not None:
+            prev = pending.chunked
+            slot, handle, cached = prev.table_idx, prev.cache_handle, prev.cached_len
+        else:
+            if self.table.available_size == 0:
+                return None
+            handle, pages = self.cache.match_req(pending.input_ids)
+            cached = handle.cached_len
+            need = pending.input_len - cached + pending.output_len
+            if need + self.reserved > self.cache.available_tokens:
+                return None
+            self.cache.lock(handle)
+            if need + self.reserved > self.cache.available_tokens:
+                self.cache.unlock(handle)
+                return None
+            slot = self.table.allocate()
+            self.cache.set_prefix_pages(slot, pages)
+            self.cache.prefix_hit_tokens += cached
+            self.cache.prefix_query_tokens += pending.input_len
+            self.new_slots.append((slot, pending.input_ids, cached))
+            self.reserved += need
+        remain = pending.input_len - cached
+        chunk = self._chunk(remain)
+        self.token_budget -= chunk
+        final = chunk == remain
+        cls = Req if final else ChunkedReq
+        req = cls(
+            input_ids=pending.input_ids[: cached + chunk], table_idx=slot, cached_len=cached,
+            output_len=pending.output_len if final else pending.input_len - (cached + chunk) + pending.output_len,
+            uid=pending.uid, sampling_params=pending.sampling_params, cache_handle=handle,
+        )
+        if final:
+            # the request object that lives on: full prompt, output budget
+            req.max_device_len = pending.input_len + pending.output_len
+        pending.chunked = None if final else req  # type: ignore[assignment]
+        return req
+
+
+class PrefillManager:
+    def __init__(self, cache: CacheManager, table: TableManager, decode: DecodeManager) -> None:
+        self.cache, self.table, self.decode = cache, table, decode
+        self.pending: List[PendingReq] = []
+
+    def add_one_req(self, uid: int, input_ids: torch.Tensor, params: SamplingParams) -> None:
+        self.pending.append(PendingReq(uid, input_ids, params))
+
+    def abort(self, uid: int) -> Optional[PendingReq]:
+        for i, p in enumerate(self.pending):
+            if p.uid == uid:
+                return self.pending.pop(i)
+        return None
+
+    @property
+    def runnable(self) -> bool:
+        return bool(self.pending)
+
+    def schedule_next_batch(self, token_budget: int):
+        """Returns ``(batch, adder)`` or ``(None, None)``."""
+        if not self.pending:
+            return None, None
+        adder = PrefillAdder(token_budget, self.decode.inflight_tokens, self.cache, self.table,
+                             others_waiting=len(self.pending) - 1)
+        reqs: List[Req] = []
+        done = 0
+        for pending in self.pending:
+            req = adder.try_add(pending)
+            if req is None:
+                break
+            reqs.append(req)
+            if pending.chunked is not None:
+                break  # the partially prefilled request keeps the head of the queue
+            done += 1
+        if not reqs:
+            return None, None
+        self.pending = self.pending[done:]
+        return Batch(reqs=reqs, phase="prefill"), adder

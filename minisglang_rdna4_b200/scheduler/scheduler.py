@@ -1,0 +1,345 @@
+"""Per-rank scheduler: admits requests, packs prefill chunks and decode batches, drives the
+engine, commits sampled tokens and replies.
+
+Loop structure follows python/minisgl/scheduler/scheduler.py (:1101 overlap loop, :1161
+normal loop, :1458 result processing, :1596 message handling, :1647 resource release):
+
+* ``overlap_loop``: while the GPU runs step *n* the host receives messages, plans step
+  *n+1* and launches it, and only then blocks on the tokens of step *n*. Length bookkeeping
+  (``complete_one``) happens at launch time because it does not depend on token values; the
+  sampled ids reach the next step through the device-resident token pool.
+* ``normal_loop``: the synchronous variant (one step fully processed before the next).
+
+Speculative decoding and expert-parallel lockstep are mixed in from ``spec_step.py`` and
+``ep.py``.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..config import SchedulerConfig
+from ..core import Batch, ChunkedReq, Req, SamplingParams
+from ..engine import BatchSamplingArgs, Engine, ForwardOutput, StepPlan
+from ..env import ENV
+from ..message import AbortBackendMsg, BaseMsg, BatchMsg, DetokenizeMsg, ExitMsg, StatsMsg, UserMsg
+from ..utils import cdiv, init_logger
+from .cache import CacheManager
+from .decode import DecodeManager
+from .prefill import PrefillManager
+from .table import TableManager
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class Ongoing:
+    batch: Batch
+    sampled: List[Req]
+    output: ForwardOutput
+    launched_at: float
+
+
+class RequestAllFinished(Exception):
+    """Raised by an offline receive hook when no work is left."""
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, engine: Optional[Engine] = None) -> None:
+        self.config = config
+        self.engine = engine if engine is not None else Engine(config)
+        eng = self.engine
+        self.page_size = eng.page_size
+        self.table = TableManager(config.max_running_req)
+        self.cache = CacheManager(eng.num_pages, eng.page_size, eng.num_slots, eng.max_pages_per_seq,
+                                  config.cache_type)
+        self.decode = DecodeManager(eng.page_size)
+        self.prefill = PrefillManager(self.cache, self.table, self.decode)
+        self.max_seq_len = eng.max_seq_len
+        self.eos_ids = set(eng.model_config.eos_token_ids)
+        self.reqs: Dict[int, Req] = {}
+        self.alloc_len: Dict[int, int] = {}      # uid -> token positions that own a KV slot
+        self.prefix_len: Dict[int, int] = {}     # uid -> cached tokens at admission (reporting)
+        self.finished_uids: set = set()
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "finished": 0,
+                      "spec_drafted": 0, "spec_accepted": 0, "spec_emitted": 0, "spec_steps": 0}
+        self._exit = False
+        self._last_stats_flush = time.monotonic()
+        self._dummy_slot = eng.num_slots - 1
+        self._use_overlap = not (config.disable_overlap or ENV.DISABLE_OVERLAP.value) and eng.device.type == "cuda"
+        self.proposer = None
+        if config.spec_algorithm != "none":
+            from ..spec import make_proposer
+
+            self.proposer = make_proposer(config, self)
+            self._use_overlap = False
+
+    # ------------------------------------------------------------------ I/O hooks
+    def receive_msg(self, blocking: bool) -> List[BaseMsg]:
+        raise NotImplementedError
+
+    def send_result(self, replies: List[DetokenizeMsg]) -> None:
+        raise NotImplementedError
+
+    # ------------------------------------------------------------------ messages
+    def _process_one_msg(self, msg: BaseMsg) -> None:
+        if isinstance(msg, BatchMsg):
+            for m in msg.data:
+                self._process_one_msg(m)
+        elif isinstance(msg, ExitMsg):
+            self._exit = True
+        elif isinstance(msg, UserMsg):
+            self._admit(msg)
+        elif isinstance(msg, AbortBackendMsg):
+            self._abort(msg.uid)
+        else:
+            logger.warning("ignoring unknown message %r", type(msg).__name__)
+
+    def _admit(self, msg: UserMsg) -> None:
+        ids = msg.input_ids.to(torch.int32).reshape(-1)
+        n = int(ids.numel())
+        params = msg.sampling_params
+        # an over-long prompt is answered with an error, it never crashes the rank
+        # (python/minisgl/scheduler/scheduler.py:1616-1630)
+        if n == 0 or n >= self.max_seq_len:
+            self.send_result([DetokenizeMsg(msg.uid, 0, True, "error",
+                                            error=f"prompt of {n} tokens exceeds the limit {self.max_seq_len - 1}")])
+            return
+        max_new = min(params.max_tokens, self.max_seq_len - n)
+        if max_new != params.max_tokens:
+            import dataclasses as _dc
+
+            params = _dc.replace(params, max_tokens=max_new)
+        need_pages = cdiv(n + max_new, self.page_size)
+        if need_pages > self.cache.num_pages:
+            self.send_result([DetokenizeMsg(msg.uid, 0, True, "error",
+                                            error="request does not fit in the KV cache")])
+            return
+        self.prefill.add_one_req(msg.uid, ids, params)
+
+    def _abort(self, uid: int) -> None:
+        pending = self.prefill.abort(uid)
+        if pending is not None:
+            if pending.chunked is not None:
+                self._free_req_resources(pending.chunked, insert=False)
+            return
+        req = self.reqs.get(uid)
+        if req is not None and not req.finished:
+            req.finished = True
+            req.finish_reason = "abort"
+            self._free_req_resources(req, insert=True)
+
+    # ------------------------------------------------------------------ planning
+    def _prefill_budget_now(self) -> int:
+        return self.config.max_extend_tokens
+
+    def _schedule_next_batch(self) -> Optional[Batch]:
+        batch, adder = self.prefill.schedule_next_batch(self._prefill_budget_now())
+        if batch is not None:
+            pool = self.engine.token_pool
+            for slot, ids, _cached in adder.new_slots:
+                src = ids.pin_memory() if pool.is_cuda else ids
+                pool[slot, : ids.numel()].copy_(src, non_blocking=True)
+                self.engine.h2d_bytes += 4 * int(ids.numel())
+            for req in batch.reqs:
+                self.reqs[req.uid] = req
+                self.prefix_len.setdefault(req.uid, req.cached_len)
+            return batch
+        return self.decode.schedule_next_batch()
+
+    def _make_plan(self, batch: Batch, extra_rows: int = 0) -> StepPlan:
+        """Allocate pages and build the step's index arrays. ``extra_rows`` > 0 plans a
+        verify step: every request feeds ``1 + extra_rows`` tokens."""
+        ps = self.page_size
+        msl = self.max_seq_len
+        reqs = batch.reqs
+        b = len(reqs)
+        slots = np.fromiter((r.table_idx for r in reqs), dtype=np.int64, count=b)
+        starts = np.fromiter((r.cached_len for r in reqs), dtype=np.int64, count=b)
+        ends = np.fromiter((r.device_len for r in reqs), dtype=np.int64, count=b) + extra_rows
+        for r, end in zip(reqs, ends.tolist()):
+            have = self.alloc_len.get(r.uid, r.cache_handle.cached_len)
+            if end > have:
+                first, last = cdiv(have, ps), cdiv(end, ps)
+                if last > first:
+                    self.cache.page_table[r.table_idx, first:last] = self.cache._take(last - first)
+                self.alloc_len[r.uid] = end
+        q_lens = ends - starts
+        cu_q = np.zeros(b + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=cu_q[1:])
+        total = int(cu_q[-1])
+        if int(q_lens.max()) == 1:
+            pos = starts
+            row = slots
+        else:
+            row = np.repeat(slots, q_lens)
+            pos = np.arange(total, dtype=np.int64) - np.repeat(cu_q[:-1].astype(np.int64), q_lens) + np.repeat(starts, q_lens)
+        token_idx = (row * msl + pos).astype(np.int32)
+        pages = self.cache.page_table[row, pos // ps].astype(np.int64)
+        out_loc = (pages * ps + pos % ps).astype(np.int32)
+        max_kv = int(ends.max())
+        n_pages = cdiv(max_kv, ps)
+        block_table = self.cache.page_table[slots, :n_pages]
+        if batch.spec_verify:
+            sample_rows = np.arange(total, dtype=np.int32)
+            write_idx = np.zeros(0, dtype=np.int32)
+        else:
+            keep = np.fromiter((not isinstance(r, ChunkedReq) for r in reqs), dtype=bool, count=b)
+            sample_rows = (cu_q[1:] - 1)[keep].astype(np.int32)
+            write_idx = (slots * msl + ends)[keep].astype(np.int32)
+        return StepPlan(
+            token_idx=token_idx, positions=pos.astype(np.int32), out_loc=out_loc, cu_q=cu_q,
+            seq_lens=ends.astype(np.int32), block_table=np.ascontiguousarray(block_table, dtype=np.int32),
+            sample_rows=sample_rows, write_idx=write_idx, max_q=int(q_lens.max()), max_kv=max_kv,
+        )
+
+    # ------------------------------------------------------------------ forward
+    def _forward(self, batch: Batch) -> Ongoing:
+        plan = self._make_plan(batch)
+        sampled = [r for r in batch.reqs if not isinstance(r, ChunkedReq)]
+        args = self.engine.sampler.prepare(sampled) if sampled else BatchSamplingArgs()
+        self._attach_constraints(sampled, args)
+        out = self.engine.forward_batch(batch, plan, args)
+        n_tok = plan.num_tokens
+        if batch.is_prefill:
+            self.stats["prefill_tokens"] += n_tok
+        else:
+            self.stats["decode_tokens"] += n_tok
+        self.stats["steps"] += 1
+        # length bookkeeping does not need token values
+        for r in batch.reqs:
+            if isinstance(r, ChunkedReq):
+                r.cached_len = r.device_len
+            else:
+                r.complete_one()
+        if batch.is_prefill:
+            self.decode.add_reqs(sampled)
+        self.decode.filter_finished()
+        return Ongoing(batch, sampled, out, time.monotonic())
+
+    def _attach_constraints(self, reqs: Sequence[Req], args: BatchSamplingArgs) -> None:
+        """Hook for grammar bitmasks (installed by the grammar backend when present)."""
+        return None
+
+    # ------------------------------------------------------------------ results
+    def _process_last_data(self, ongoing: Optional[Ongoing]) -> None:
+        if ongoing is None:
+            return
+        tokens = ongoing.output.wait()
+        sample = ongoing.output.sample
+        lp = sample.logprobs.tolist() if sample is not None and sample.logprobs is not None else None
+        tlp = tids = None
+        if sample is not None and sample.top_logprobs is not None:
+            tlp, tids = sample.top_logprobs.tolist(), sample.top_ids.tolist()
+        replies: List[DetokenizeMsg] = []
+        toks = tokens.tolist()
+        for i, req in enumerate(ongoing.sampled):
+            if req.finished:
+                continue  # finished or aborted while this step was in flight
+            tok = int(toks[i])
+            req.append_host(tokens[i : i + 1])
+            reason = None
+            if not req.sampling_params.ignore_eos and tok in self.eos_ids:
+                reason = "stop"
+            elif req.num_generated >= req.sampling_params.max_tokens:
+                reason = "length"
+            msg = DetokenizeMsg(req.uid, tok, reason is not None, reason,
+                                prompt_tokens=req.prompt_len, cached_tokens=self.prefix_len.get(req.uid, 0))
+            if lp is not None and req.sampling_params.logprobs > 0:
+                msg.logprob = lp[i]
+                n = req.sampling_params.logprobs
+                msg.top_logprobs = [[tids[i][j], tlp[i][j]] for j in range(n)]
+            replies.append(msg)
+            if reason is not None:
+                req.finished = True
+                req.finish_reason = reason
+                self._free_req_resources(req, insert=True)
+        if replies:
+            self.send_result(replies)
+
+    def _free_req_resources(self, req: Req, insert: bool) -> None:
+        if req.resources_freed:  # several paths can reach a request; free exactly once
+            return
+        req.resources_freed = True
+        self.decode.remove(req)
+        alloc = self.alloc_len.pop(req.uid, req.cache_handle.cached_len)
+        # KV is valid for tokens that were both fed and known on the host
+        req.cached_len = min(req.cached_len, int(req.input_ids.numel()))
+        self.cache.finish_req(req, alloc, insert=insert)
+        self.table.free(req.table_idx)
+        self.reqs.pop(req.uid, None)
+        self.prefix_len.pop(req.uid, None)
+        self.stats["finished"] += 1
+
+    # ------------------------------------------------------------------ loops
+    @property
+    def has_work(self) -> bool:
+        return self.prefill.runnable or self.decode.runnable
+
+    def overlap_loop(self) -> None:
+        last: Optional[Ongoing] = None
+        while not self._exit:
+            blocking = not self.has_work and last is None
+            for msg in self.receive_msg(blocking):
+                self._process_one_msg(msg)
+            batch = self._schedule_next_batch()
+            ongoing = self._forward(batch) if batch is not None else None
+            self._process_last_data(last)
+            last = ongoing
+            self._maybe_exit_after_steps()
+        self._process_last_data(last)
+
+    def normal_loop(self) -> None:
+        while not self._exit:
+            for msg in self.receive_msg(blocking=not self.has_work):
+                self._process_one_msg(msg)
+            if self.proposer is not None and not self.prefill.runnable and self.decode.runnable:
+                self._spec_decode_step()
+            else:
+                batch = self._schedule_next_batch()
+                if batch is not None:
+                    ongoing = self._forward(batch)
+                    self._process_last_data(ongoing)
+                    if self.proposer is not None and batch.is_prefill:
+                        self.proposer.on_prefill(ongoing.sampled)
+            self._maybe_exit_after_steps()
+
+    def _maybe_exit_after_steps(self) -> None:
+        limit = ENV.EXIT_AFTER_STEPS.value
+        if limit and self.stats["steps"] >= limit:
+            self._exit = True
+
+    def run_forever(self) -> None:
+        try:
+            if self.config.enable_ep and self.config.dp_size > 1:
+                from .ep import ep_lockstep_loop
+
+                ep_lockstep_loop(self)
+            elif self._use_overlap:
+                self.overlap_loop()
+            else:
+                self.normal_loop()
+        except RequestAllFinished:
+            pass
+
+    # ------------------------------------------------------------------ spec decode
+    def _spec_decode_step(self) -> None:
+        from .spec_step import spec_decode_step
+
+        spec_decode_step(self)
+
+    # ------------------------------------------------------------------ metrics
+    def stats_snapshot(self) -> StatsMsg:
+        info = self.cache.prefix_cache.size_info
+        vals = dict(self.stats)
+        vals.update(
+            running=len(self.decode.running), waiting=len(self.prefill.pending),
+            kv_tokens_used=self.cache.used_tokens, kv_tokens_total=self.cache.num_pages * self.page_size,
+            prefix_hit_tokens=self.cache.prefix_hit_tokens, prefix_query_tokens=self.cache.prefix_query_tokens,
+            evictable_pages=info.evictable_pages, protected_pages=info.protected_pages,
+        )
+        return StatsMsg(dp_rank=self.config.dp_rank, values={k: float(v) for k, v in vals.items()})

@@ -1,0 +1,71 @@
+"""Tiny-Llama plumbing run on CPU fp32: scheduler + radix cache + paged KV must reproduce a
+straight (no cache, no paging) transformer's greedy tokens."""
+import torch
+
+from minisglang_rdna4_b200 import SamplingParams
+from minisglang_rdna4_b200.llm import LLM
+from minisglang_rdna4_b200.models.config import tiny_llama_config
+from minisglang_rdna4_b200.ops import ref
+
+
+def _dense_greedy(model, cfg, prompt, n_new):
+    """Recompute the whole sequence every step with plain attention."""
+    ids = list(prompt)
+    body = model.model
+    cos_sin = ref.build_cos_sin_cache(cfg.head_dim, 4096, cfg.rotary_config.base)
+    out = []
+    for _ in range(n_new):
+        t = len(ids)
+        x = body.embed_tokens.weight[torch.tensor(ids)]
+        pos = torch.arange(t)
+        for layer in body.layers:
+            h = ref.rms_norm(x, layer.input_layernorm.weight, cfg.rms_norm_eps)
+            qkv = h @ layer.self_attn.qkv_proj.weight.t()
+            qs, ks = cfg.num_qo_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+            q, k, v = qkv.split([qs, ks, ks], -1)
+            q, k = ref.qk_norm_rope(q, k, None, None, pos, cos_sin, cfg.head_dim, cfg.head_dim, 1e-6)
+            q = q.view(t, cfg.num_qo_heads, cfg.head_dim).transpose(0, 1)
+            k = k.view(t, cfg.num_kv_heads, cfg.head_dim).transpose(0, 1).repeat_interleave(2, 0)
+            v = v.view(t, cfg.num_kv_heads, cfg.head_dim).transpose(0, 1).repeat_interleave(2, 0)
+            s = (q @ k.transpose(1, 2)) * cfg.head_dim ** -0.5
+            s = s.masked_fill(torch.triu(torch.ones(t, t, dtype=torch.bool), 1), float("-inf"))
+            o = (torch.softmax(s, -1) @ v).transpose(0, 1).reshape(t, -1)
+            x = x + o @ layer.self_attn.o_proj.weight.t()
+            h = ref.rms_norm(x, layer.post_attention_layernorm.weight, cfg.rms_norm_eps)
+            gu = h @ layer.mlp.gate_up_proj.weight.t()
+            x = x + ref.silu_and_mul(gu) @ layer.mlp.down_proj.weight.t()
+        h = ref.rms_norm(x[-1:], body.norm.weight, cfg.rms_norm_eps)
+        tok = int((h @ model.lm_head.weight.t()).argmax(-1))
+        out.append(tok)
+        ids.append(tok)
+    return out
+
+
+def test_tiny_llama_matches_dense_oracle_and_hits_prefix_cache():
+    cfg = tiny_llama_config()
+    llm = LLM(model_config=cfg, use_dummy_weight=True, device="cpu", page_size=16,
+              max_running_req=8, num_page_override=256, max_extend_tokens=96, seed=0)
+    g = torch.Generator().manual_seed(1)
+    shared = torch.randint(0, cfg.vocab_size, (32,), generator=g).tolist()
+    prompts = []
+    for i in range(8):
+        n = int(torch.randint(32, 129, (1,), generator=g))
+        body = torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+        prompts.append(shared + body[: max(n - 32, 1)] if i < 4 else body)
+    sp = SamplingParams(temperature=0.0, max_tokens=32, ignore_eos=True)
+    # first pass caches the shared prefix; second pass must hit it
+    first = llm.generate(prompts[:1], sp)
+    outs = llm.generate(prompts, sp)
+    assert sum(o.cached_tokens for o in outs[:4]) >= 4 * 32
+    assert llm.cache.prefix_hit_tokens >= 4 * 32
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 32 and o.finish_reason == "length"
+    for idx in (0, 3, 5):
+        want = _dense_greedy(llm.engine.model, cfg, prompts[idx], 32)
+        assert outs[idx].token_ids == want, idx
+    assert first[0].token_ids == outs[0].token_ids
+    llm.cache.check_integrity()
+    # every page is either free or owned by the prefix cache once all requests are done
+    info = llm.cache.prefix_cache.size_info
+    assert llm.cache.free_pages + info.total_pages == llm.cache.num_pages
+    assert info.protected_pages == 0

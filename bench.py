@@ -1,0 +1,284 @@
+"""Serving benchmark: output tokens per second of the named workload on N GPUs of one node.
+
+Workload (the quantised dense configuration of the baseline description): a Qwen3-4B-shaped
+decoder (36 layers, hidden 2560, 32 q / 8 kv heads of 128, QK-norm, SwiGLU 9728, vocab
+151936, tied embeddings), MXFP4 weights run W4A8 with per-token e4m3 activations, e4m3 KV
+cache, random-init weights (seed 1), tensor parallel over the N GPUs; 256 concurrent
+requests of uniform-random token ids with lengths uniform in [512, 2048], 256 greedy output
+tokens each. One *step* is one full pass of that workload through the public offline API
+(``LLM.generate``); every pass draws fresh prompts, so the prefix cache never skips work.
+
+Reported: ``value`` = output tokens / device time of the forward steps (CUDA events around
+every engine step, max over ranks); ``e2e`` = output tokens / time of the whole
+``generate`` call, which stages every step's index arrays and prompt ids from pinned host
+memory and reads the sampled ids back each step.
+
+Launch: ``python bench.py --gpus 1`` or, for N > 1,
+``python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1
+--master-port P bench.py --gpus N``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOK_S = None  # the reference publishes no B200 number for this configuration
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-4b")
+    ap.add_argument("--quant", default="mxfp4")
+    ap.add_argument("--kv", default="fp8")
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--in-min", type=int, default=512)
+    ap.add_argument("--in-max", type=int, default=2048)
+    ap.add_argument("--out-len", type=int, default=256)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-extend", type=int, default=8192)
+    ap.add_argument("--memory-ratio", type=float, default=0.85)
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    clocks.append(float(parts[1]))
+                    mx = float(parts[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            # the median over samples taken under load (the upper half of the samples)
+            clocks.sort()
+            out["sm_mhz"] = statistics.median(clocks)
+        out["sm_max_mhz"] = mx
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(clocks)
+        return out
+
+
+def run_reference(args) -> None:
+    """The reference arm: the unmodified reference, installed under ``baseline/_ref``, through
+    its own offline API. Its layer package imports the out-of-tree gfx1201 HIP kernel
+    packages unconditionally, so on an NVIDIA box the import itself fails; the arm reports
+    that instead of substituting any code of this repository."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref_dir, "minisgl")):
+        why = "the reference is not installed under baseline/_ref"
+    else:
+        probe = subprocess.run(
+            [sys.executable, "-c", "from minisgl.llm import LLM"], capture_output=True, text=True,
+            env=dict(os.environ, PYTHONPATH=ref_dir), timeout=600)
+        if probe.returncode != 0:
+            last = [ln for ln in probe.stderr.strip().splitlines() if ln.strip()][-1:]
+            why = ("the unmodified reference does not import on this box: " + (last[0] if last else "import failed")
+                   + " (its kernels are out-of-tree gfx1201 HIP packages; it has no NVIDIA path for W4A8 / fp8 KV)")
+        else:
+            why = ("the reference imports, but it has no quantised (W4A8 MXFP4, fp8 KV) execution path on NVIDIA "
+                   "GPUs for the named configuration")
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import cuda as K
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+
+    llm = LLM(
+        model_path=args.model, use_dummy_weight=True, quantization=None if args.quant == "none" else args.quant,
+        kv_cache_dtype=args.kv, tp_size=world, tp_rank=rank, page_size=args.page_size,
+        max_running_req=args.requests, max_extend_tokens=args.max_extend, memory_ratio=args.memory_ratio,
+        seed=1, cuda_graph_max_bs=(-1 if args.no_graph else None), max_seq_len_override=4096,
+    )
+    eng = llm.engine
+    vocab = eng.model_config.vocab_size
+    sp = SamplingParams(temperature=0.0, max_tokens=args.out_len, ignore_eos=True)
+
+    # per-step device timing: events around every engine forward
+    step_events = []
+    orig_forward = eng.forward_batch
+
+    def timed_forward(batch, plan, sargs, return_logits=False):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream = eng.stream
+        s.record(stream)
+        out = orig_forward(batch, plan, sargs, return_logits)
+        e.record(stream)
+        step_events.append((s, e, batch.phase, plan.num_tokens))
+        return out
+
+    eng.forward_batch = timed_forward
+
+    def make_prompts(seed: int):
+        g = np.random.default_rng(seed)
+        lens = g.integers(args.in_min, args.in_max + 1, size=args.requests)
+        return [g.integers(0, vocab, size=int(n), dtype=np.int32) for n in lens]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_pass(seed: int):
+        prompts = make_prompts(seed)  # identical on every rank
+        step_events.clear()
+        t_first = {}
+        t_last = {}
+        orig_send = llm.send_result
+
+        def send(replies):
+            now = time.perf_counter()
+            for r in replies:
+                t_first.setdefault(r.uid, now)
+                t_last[r.uid] = now
+            orig_send(replies)
+
+        llm.send_result = send
+        h2d0, d2h0, l0 = eng.h2d_bytes, eng.d2h_bytes, K.LAUNCHES
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(eng.stream)
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, sp)
+        ev1.record(eng.stream)
+        barrier()
+        llm.send_result = orig_send
+        wall_ms = ev0.elapsed_time(ev1)
+        dev_ms = sum(s.elapsed_time(e) for s, e, _, _ in step_events)
+        prefill_ms = sum(s.elapsed_time(e) for s, e, ph, _ in step_events if ph == "prefill")
+        n_out = sum(len(o.token_ids) for o in outs)
+        assert n_out == args.requests * args.out_len, (n_out, args.requests * args.out_len)
+        ttft = sorted((t_first[u] - t0) * 1e3 for u in t_first)
+        tpot = sorted((t_last[u] - t_first[u]) * 1e3 / max(args.out_len - 1, 1) for u in t_first)
+        n_steps = len(step_events)
+        return dict(wall_ms=wall_ms, dev_ms=dev_ms, prefill_ms=prefill_ms, n_out=n_out, steps=n_steps,
+                    h2d=(eng.h2d_bytes - h2d0) / max(n_steps, 1), d2h=(eng.d2h_bytes - d2h0) / max(n_steps, 1),
+                    launches=K.LAUNCHES - l0, ttft_p50=ttft[len(ttft) // 2], tpot_p50=tpot[len(tpot) // 2],
+                    in_tokens=sum(len(p) for p in prompts))
+
+    for w in range(args.warmup):
+        one_pass(1000 + w)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    results = [one_pass(2000 + i) for i in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else {}
+
+    def reduce_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev_ms = reduce_max(sum(r["dev_ms"] for r in results))
+    wall_ms = reduce_max(sum(r["wall_ms"] for r in results))
+    n_out = sum(r["n_out"] for r in results)
+    value = n_out / (dev_ms / 1e3)
+    e2e = n_out / (wall_ms / 1e3)
+    last = results[-1]
+    if rank == 0:
+        line = {
+            "metric": "output tok/s (device-timed, max over ranks)",
+            "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / BASELINE_TOK_S) if BASELINE_TOK_S else None,
+            "dtype": f"w4a8-mxfp4+{args.kv}-kv" if args.quant == "mxfp4" else ("bf16" if args.quant == "none" else args.quant),
+            "data": "synthetic (uniform-random token ids, random-init weights seed 1)",
+            "impl": "ours",
+            "config": {
+                "model": f"{args.model}-shaped dense, {args.quant} W4A8, {args.kv} KV",
+                "global_batch": args.requests, "seq_len": f"in U[{args.in_min},{args.in_max}], out {args.out_len}",
+                "parallelism": f"tp{world}", "step": "one full pass of the workload (prefill + decode)",
+                "l2": "inputs larger than L2 (weights + KV pool >> 126 MB)",
+                "p50_ttft_ms": last["ttft_p50"], "p50_tpot_ms": last["tpot_p50"],
+                "prefill_ms_per_pass": last["prefill_ms"], "engine_steps_per_pass": last["steps"],
+                "prompt_tokens_per_pass": last["in_tokens"], "cuda_graphs": not args.no_graph,
+            },
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": last["h2d"],
+                    "d2h_bytes_per_step": last["d2h"], "ms_per_pass": wall_ms / args.steps},
+            "gpu_launches": sum(r["launches"] for r in results),
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    llm.shutdown()
+    if world > 1 and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,258 @@
+// Peer-memory collectives over NVLink / NVSwitch, fused with the ops that follow them.
+//
+//   * symmetric buffers: cudaMalloc'd per rank, exported with CUDA IPC handles, mapped by every
+//     peer (the handle exchange runs over the gloo control plane in parallel/symm.py);
+//   * one-shot all-reduce fused with residual add + RMSNorm (+ per-token e4m3 producer):
+//     every rank pushes its partial row straight into each peer's slot (P2P stores), raises a
+//     per-row sequence flag, waits for the peers' flags and reduces the rows that are now in
+//     its own memory, in rank order, so every rank computes bit-identical sums;
+//   * the same kernel without the norm serves as a plain in-place all-reduce.
+//
+// Replaces the reference's custom_ar package (one_shot_ar, one_shot_ar_push;
+// python/minisgl/distributed/impl.py:178-209,351-392), which is limited to two PCIe peers, and
+// the rms_norm_add that followed it. No load ever targets peer memory and nothing here uses
+// TMA: peers are written with plain st.global, flags with st.release.sys / ld.acquire.sys.
+//
+// Every wait is bounded: after `wait_ns` a row gives up, records a status code and still runs
+// to completion on whatever data it has, so the context stays usable and the host can fall
+// back to the NCCL path.
+#include "common.cuh"
+
+#include <string.h>
+
+using namespace msgl;
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+
+struct ArArgs {
+  const void* x;             // [rows, hidden] local partial
+  void* residual;            // [rows, hidden] in/out, or nullptr (plain all-reduce)
+  const void* weight;        // [hidden] or nullptr
+  void* out;                 // [rows, hidden] 16-bit result (normed, or the sum for a plain AR)
+  uint8_t* out_q;            // optional e4m3 result
+  float* out_scale;          // [rows]
+  void* slots[kMaxRanks];    // slots[p]: base of rank p's data region (peer-mapped)
+  uint32_t* flags[kMaxRanks];  // flags[p]: base of rank p's flag region
+  uint32_t* seq;             // [max_rows] local per-row sequence counters
+  int* status;
+  int rank, nranks, rows, hidden, max_rows;
+  long long slot_stride;     // elements between consecutive (parity, src) planes = max_rows * max_hidden
+  int max_hidden;
+  float eps, w_offset;
+  unsigned long long wait_ns;
+};
+
+__device__ int g_comm_status = 0;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// One CTA per row. NORM: residual add + RMSNorm after the reduction. QUANT: e4m3 output.
+template <typename T, bool NORM, bool QUANT>
+__global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const int H = a.hidden;
+  const uint32_t seq = a.seq[row] + 1u;
+  const int parity = (int)(seq & 1u);
+  const T* xr = reinterpret_cast<const T*>(a.x) + (size_t)row * H;
+
+  // 1. push this rank's partial row into every rank's slot (its own included)
+  for (int p = 0; p < a.nranks; ++p) {
+    T* dst = reinterpret_cast<T*>(a.slots[p]) + (size_t)(parity * a.nranks + a.rank) * a.slot_stride +
+             (size_t)row * a.max_hidden;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8)
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(xr + i);
+  }
+  __syncthreads();
+  // 2. raise the flag on every peer, then wait for every peer's flag here
+  if (threadIdx.x < a.nranks) {
+    const int p = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(a.flags[p] + (size_t)a.rank * a.max_rows + row, seq);
+    const uint32_t* mine = a.flags[a.rank] + (size_t)p * a.max_rows + row;
+    if ((int)(ld_acquire_sys(mine) - seq) < 0) {
+      const unsigned long long t0 = gtimer();
+      while ((int)(ld_acquire_sys(mine) - seq) < 0) {
+        if (gtimer() - t0 > a.wait_ns) {
+          atomicCAS(a.status, 0, 300 + p);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // 3. reduce in rank order (identical on every rank), add the residual, normalise
+  const T* base = reinterpret_cast<const T*>(a.slots[a.rank]) + (size_t)(parity * a.nranks) * a.slot_stride +
+                  (size_t)row * a.max_hidden;
+  T* rr = NORM ? reinterpret_cast<T*>(a.residual) + (size_t)row * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int q = 0; q < a.nranks; ++q) {
+      float v[8];
+      load8(base + (size_t)q * a.slot_stride + i, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    if (NORM) {
+      float r[8];
+      load8(rr + i, r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += r[k];
+      store8(rr + i, acc);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        acc[k] = to_float(from_float<T>(acc[k]));
+        ss += acc[k] * acc[k];
+        row_s[i + k] = acc[k];
+      }
+    } else {
+      store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, acc);
+    }
+  }
+  if (NORM) {
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)H + a.eps);
+    const T* w = reinterpret_cast<const T*>(a.weight);
+    float amax = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float wv[8], y[8];
+      load8(w + i, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + a.w_offset)));
+        if (QUANT) {
+          amax = fmaxf(amax, fabsf(y[k]));
+          row_s[i + k] = y[k];
+        }
+      }
+      if (!QUANT) store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, y);
+    }
+    if (QUANT) {
+      amax = block_max(amax, scratch);
+      const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+      if (threadIdx.x == 0) a.out_scale[row] = scale;
+      for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+        float y[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
+        *reinterpret_cast<uint2*>(a.out_q + (size_t)row * H + i) = pack8_e4m3(y, scale);
+      }
+    }
+  }
+  if (threadIdx.x == 0) a.seq[row] = seq;
+}
+
+template <typename T>
+int launch_ar(const ArArgs& a, cudaStream_t stream) {
+  int threads = ((a.hidden / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32 * ((a.nranks + 31) / 32)) threads = 32;
+  const bool norm = a.residual != nullptr, quant = a.out_q != nullptr;
+  const size_t smem = norm ? (size_t)a.hidden * sizeof(float) : 0;
+#define AR_LAUNCH(N, Q)                                                                                      \
+  do {                                                                                                        \
+    if (smem > 48 * 1024)                                                                                     \
+      cudaFuncSetAttribute(ar_oneshot_kernel<T, N, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    ar_oneshot_kernel<T, N, Q><<<a.rows, threads, smem, stream>>>(a);                                          \
+  } while (0)
+  if (norm && quant) AR_LAUNCH(true, true);
+  else if (norm) AR_LAUNCH(true, false);
+  else AR_LAUNCH(false, false);
+#undef AR_LAUNCH
+  MSGL_CHECK_LAUNCH("ar_oneshot");
+  return MSGL_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- symmetric memory plumbing
+MSGL_API void* msgl_symm_alloc(long long bytes) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) { msgl_set_error("symm_alloc", e); return nullptr; }
+  e = cudaMemset(p, 0, (size_t)bytes);
+  if (e != cudaSuccess) { msgl_set_error("symm_alloc memset", e); cudaFree(p); return nullptr; }
+  return p;
+}
+MSGL_API int msgl_symm_free(void* p) {
+  cudaError_t e = cudaFree(p);
+  if (e != cudaSuccess) { msgl_set_error("symm_free", e); return MSGL_CUDA_ERROR; }
+  return MSGL_OK;
+}
+MSGL_API int msgl_ipc_get_handle(void* p, void* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { msgl_set_error("ipc_get_handle", e); return MSGL_CUDA_ERROR; }
+  memcpy(out64, &h, sizeof(h));
+  return MSGL_OK;
+}
+MSGL_API void* msgl_ipc_open(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { msgl_set_error("ipc_open", e); return nullptr; }
+  return p;
+}
+MSGL_API int msgl_ipc_close(void* p) {
+  cudaError_t e = cudaIpcCloseMemHandle(p);
+  if (e != cudaSuccess) { msgl_set_error("ipc_close", e); return MSGL_CUDA_ERROR; }
+  return MSGL_OK;
+}
+
+// slots / flags: arrays of `nranks` device pointers (this rank's own buffer at index `rank`).
+// residual == nullptr: plain all-reduce into `out`. out_q != nullptr: e4m3 row + scale.
+MSGL_API int msgl_ar_oneshot(const void* x, void* residual, const void* weight, void* out, void* out_q,
+                             void* out_scale, void* const* slots, void* const* flags, void* seq, int rank,
+                             int nranks, int rows, int hidden, int max_rows, int max_hidden, float eps,
+                             int plus_one, long long wait_us, int dtype, cudaStream_t stream) {
+  if (rows == 0) return MSGL_OK;
+  if (nranks > kMaxRanks || rows > max_rows || hidden > max_hidden || hidden % 8 || hidden > 48 * 1024) {
+    msgl_set_error_text("ar_oneshot: message does not fit the symmetric slots");
+    return MSGL_BAD_ARG;
+  }
+  ArArgs a;
+  a.x = x; a.residual = residual; a.weight = weight; a.out = out;
+  a.out_q = (uint8_t*)out_q; a.out_scale = (float*)out_scale;
+  for (int p = 0; p < nranks; ++p) { a.slots[p] = slots[p]; a.flags[p] = (uint32_t*)flags[p]; }
+  a.seq = (uint32_t*)seq;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_comm_status);
+  a.status = status;
+  a.rank = rank; a.nranks = nranks; a.rows = rows; a.hidden = hidden; a.max_rows = max_rows;
+  a.max_hidden = max_hidden;
+  a.slot_stride = (long long)max_rows * max_hidden;
+  a.eps = eps; a.w_offset = plus_one ? 1.f : 0.f;
+  a.wait_ns = (unsigned long long)wait_us * 1000ull;
+  if (dtype == MSGL_BF16) return launch_ar<__nv_bfloat16>(a, stream);
+  if (dtype == MSGL_F16) return launch_ar<__half>(a, stream);
+  return MSGL_BAD_ARG;
+}
+
+MSGL_API int msgl_comm_status(int reset) {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_comm_status, sizeof(int));
+  if (reset && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_comm_status, &z, sizeof(int));
+  }
+  return v;
+}

@@ -1,0 +1,129 @@
+// Shared device helpers for the sm_100a kernels: vector access, reductions, fp8 conversion,
+// launch-error reporting. Everything here is header-only.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MSGL_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side
+enum MsglDtype : int { MSGL_BF16 = 0, MSGL_F16 = 1, MSGL_F32 = 2, MSGL_E4M3 = 3 };
+
+// Status codes returned by the C entry points. 0 = launched.
+enum MsglStatus : int {
+  MSGL_OK = 0,
+  MSGL_BAD_ARG = 1,       // shape / alignment / dtype the kernel does not support
+  MSGL_CUDA_ERROR = 2,    // a CUDA runtime or driver call failed; see msgl_last_error()
+  MSGL_TIMEOUT = 3,       // a bounded device-side wait gave up (read from the status word)
+};
+
+namespace msgl {
+
+constexpr float kFp8Max = 448.0f;
+
+template <typename T> struct Vec8;  // eight 16-bit elements = 16 bytes
+template <> struct alignas(16) Vec8<__nv_bfloat16> { __nv_bfloat162 v[4]; };
+template <> struct alignas(16) Vec8<__half> { __half2 v[4]; };
+
+__device__ __forceinline__ float2 to_float2(__nv_bfloat162 x) { return __bfloat1622float2(x); }
+__device__ __forceinline__ float2 to_float2(__half2 x) { return __half22float2(x); }
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ type make(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+template <> struct Pack2<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ type make(float a, float b) { return __floats2half2_rn(a, b); }
+};
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_float(float x) { return x; }
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&out)[8]) {
+  Vec8<T> v = *reinterpret_cast<const Vec8<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = to_float2(v.v[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&in)[8]) {
+  Vec8<T> v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.v[i] = Pack2<T>::make(in[2 * i], in[2 * i + 1]);
+  *reinterpret_cast<Vec8<T>*>(p) = v;
+}
+
+// e4m3 pair from two floats, saturating to +-448
+__device__ __forceinline__ uint16_t float2_to_e4m3x2(float a, float b) {
+  return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint8_t float_to_e4m3(float a) {
+  return (uint8_t)__nv_cvt_float_to_fp8(a, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ float e4m3_to_float(uint8_t x) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(x, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+// eight floats -> eight e4m3 bytes (one 8-byte store). True division by the scale: a reciprocal
+// multiply lands on the other side of a rounding boundary often enough to differ from x / scale.
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&x)[8], float scale) {
+  uint32_t lo = (uint32_t)float2_to_e4m3x2(__fdiv_rn(x[0], scale), __fdiv_rn(x[1], scale)) |
+                ((uint32_t)float2_to_e4m3x2(__fdiv_rn(x[2], scale), __fdiv_rn(x[3], scale)) << 16);
+  uint32_t hi = (uint32_t)float2_to_e4m3x2(__fdiv_rn(x[4], scale), __fdiv_rn(x[5], scale)) |
+                ((uint32_t)float2_to_e4m3x2(__fdiv_rn(x[6], scale), __fdiv_rn(x[7], scale)) << 16);
+  return make_uint2(lo, hi);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide reductions; `scratch` holds 32 floats. Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? scratch[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? scratch[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+}  // namespace msgl
+
+// Host side: remember the last CUDA error text for msgl_last_error().
+void msgl_set_error(const char* where, cudaError_t err);
+void msgl_set_error_text(const char* text);
+#define MSGL_CHECK_LAUNCH(where)                      \
+  do {                                                \
+    cudaError_t _e = cudaGetLastError();              \
+    if (_e != cudaSuccess) {                          \
+      msgl_set_error(where, _e);                      \
+      return MSGL_CUDA_ERROR;                         \
+    }                                                 \
+  } while (0)

@@ -1,0 +1,293 @@
+// Elementwise / row-wise kernels: embedding gather, RMSNorm (+residual add) (+per-token e4m3
+// producer), gated activations (+quant), stand-alone activation quantisers.
+//
+// Replaces the reference's tail_hip package (rms_norm, rms_norm_add, rms_norm_quant,
+// rms_norm_add_quant, silu_and_mul, gelu_and_mul; python/minisgl/layers/norm.py:16-168,
+// python/minisgl/layers/activation.py:25-64) and its embedding gather
+// (python/minisgl/kernel/csrc/jit/index.cu:31-96). All kernels are memory-bound: they read
+// each input once with 16-byte accesses and keep the row in shared memory between the
+// reduction and the write.
+#include "common.cuh"
+
+#include <string>
+
+using namespace msgl;
+
+static thread_local std::string g_last_error;
+void msgl_set_error(const char* where, cudaError_t err) {
+  g_last_error = std::string(where) + ": " + cudaGetErrorString(err);
+}
+void msgl_set_error_text(const char* text) { g_last_error = text; }
+MSGL_API const char* msgl_last_error() { return g_last_error.c_str(); }
+
+// ------------------------------------------------------------------------------------------
+// embedding: out[i, :] = (start <= ids[i] < start + len) ? W[ids[i] - start, :] : 0
+// ------------------------------------------------------------------------------------------
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* __restrict__ w,
+                                 uint4* __restrict__ out, int row_vecs, int start, int len) {
+  int row = blockIdx.x;
+  int id = ids[row] - start;
+  bool inside = id >= 0 && id < len;
+  const uint4* src = w + (size_t)(inside ? id : 0) * row_vecs;
+  uint4* dst = out + (size_t)row * row_vecs;
+  for (int i = threadIdx.x; i < row_vecs; i += blockDim.x)
+    dst[i] = inside ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+}
+
+MSGL_API int msgl_embedding(const void* ids, const void* w, void* out, int rows, int hidden_bytes,
+                            int start, int len, cudaStream_t stream) {
+  if (hidden_bytes % 16) return MSGL_BAD_ARG;
+  if (rows == 0) return MSGL_OK;
+  int vecs = hidden_bytes / 16;
+  int threads = vecs < 256 ? ((vecs + 31) / 32) * 32 : 256;
+  embedding_kernel<<<rows, threads, 0, stream>>>((const int32_t*)ids, (const uint4*)w, (uint4*)out, vecs,
+                                                 start, len);
+  MSGL_CHECK_LAUNCH("embedding");
+  return MSGL_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm family. One CTA per row; the (summed) row lives in shared memory as fp32.
+//   ADD   : residual += x (stored back, rounded to T), norm of the sum
+//   QUANT : emit e4m3 row + fp32 scale (amax/448) instead of T
+// ------------------------------------------------------------------------------------------
+template <typename T, bool ADD, bool QUANT>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                        const T* __restrict__ w, T* __restrict__ out,
+                                                        uint8_t* __restrict__ out_q, float* __restrict__ out_scale,
+                                                        int hidden, float eps, float w_offset) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const T* xr = x + (size_t)row * hidden;
+  T* rr = ADD ? residual + (size_t)row * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    float v[8];
+    load8(xr + i, v);
+    if (ADD) {
+      float r[8];
+      load8(rr + i, r);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] += r[k];
+      store8(rr + i, v);
+      // the norm sees the rounded residual, exactly what the next layer will read
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = to_float(from_float<T>(v[k]));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      ss += v[k] * v[k];
+      row_s[i + k] = v[k];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    float wv[8], y[8];
+    load8(w + i, wv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      // round to T as the unfused op would, so the quantised row matches norm -> quant
+      y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + w_offset)));
+      if (QUANT) {
+        amax = fmaxf(amax, fabsf(y[k]));
+        row_s[i + k] = y[k];
+      }
+    }
+    if (!QUANT) store8(out + (size_t)row * hidden + i, y);
+  }
+  if (QUANT) {
+    amax = block_max(amax, scratch);
+    const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+    if (threadIdx.x == 0) out_scale[row] = scale;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+      float y[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
+      *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + i) = pack8_e4m3(y, scale);
+    }
+  }
+}
+
+template <typename T>
+static int launch_rms(const void* x, void* residual, const void* w, void* out, void* out_q, void* out_scale,
+                      int rows, int hidden, float eps, int plus_one, cudaStream_t s) {
+  int threads = ((hidden / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  size_t smem = (size_t)hidden * sizeof(float);
+  float off = plus_one ? 1.f : 0.f;
+  bool add = residual != nullptr, quant = out_q != nullptr;
+#define RMS_LAUNCH(A, Q)                                                                                   \
+  do {                                                                                                     \
+    if (smem > 48 * 1024)                                                                                  \
+      cudaFuncSetAttribute(rms_norm_kernel<T, A, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rms_norm_kernel<T, A, Q><<<rows, threads, smem, s>>>((const T*)x, (T*)residual, (const T*)w, (T*)out,  \
+                                                         (uint8_t*)out_q, (float*)out_scale, hidden, eps, off); \
+  } while (0)
+  if (add && quant) RMS_LAUNCH(true, true);
+  else if (add) RMS_LAUNCH(true, false);
+  else if (quant) RMS_LAUNCH(false, true);
+  else RMS_LAUNCH(false, false);
+#undef RMS_LAUNCH
+  MSGL_CHECK_LAUNCH("rms_norm");
+  return MSGL_OK;
+}
+
+// residual == nullptr: plain norm. out_q != nullptr: quantised output (out may be nullptr).
+MSGL_API int msgl_rms_norm(const void* x, void* residual, const void* w, void* out, void* out_q,
+                           void* out_scale, int rows, int hidden, float eps, int plus_one, int dtype,
+                           cudaStream_t stream) {
+  if (hidden % 8 || hidden > 48 * 1024) return MSGL_BAD_ARG;
+  if (rows == 0) return MSGL_OK;
+  if (dtype == MSGL_BF16)
+    return launch_rms<__nv_bfloat16>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, plus_one, stream);
+  if (dtype == MSGL_F16)
+    return launch_rms<__half>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, plus_one, stream);
+  return MSGL_BAD_ARG;
+}
+
+// ------------------------------------------------------------------------------------------
+// gated activation: out[m, i] = act(x[m, i]) * x[m, I + i]
+// ------------------------------------------------------------------------------------------
+enum ActKind : int { ACT_SILU = 0, ACT_GELU = 1, ACT_GELU_TANH = 2 };
+__device__ __forceinline__ float act_fn(float g, int kind) {
+  if (kind == ACT_SILU) return g / (1.f + __expf(-g));
+  if (kind == ACT_GELU) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g)));
+}
+
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, size_t total_vecs,
+                               int kind) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total_vecs) return;
+  int vecs_per_row = inter / 8;
+  size_t row = idx / vecs_per_row;
+  int col = (int)(idx % vecs_per_row) * 8;
+  const T* g = x + row * 2 * inter + col;
+  float a[8], b[8], y[8];
+  load8(g, a);
+  load8(g + inter, b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) y[k] = act_fn(a[k], kind) * b[k];
+  store8(out + row * inter + col, y);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) act_mul_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q,
+                                                             float* __restrict__ out_scale, int inter, int kind) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const T* g = x + (size_t)row * 2 * inter;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
+    float a[8], b[8];
+    load8(g + i, a);
+    load8(g + inter + i, b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float y = to_float(from_float<T>(act_fn(a[k], kind) * b[k]));
+      amax = fmaxf(amax, fabsf(y));
+      row_s[i + k] = y;
+    }
+  }
+  amax = block_max(amax, scratch);
+  const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+  if (threadIdx.x == 0) out_scale[row] = scale;
+  for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
+    float y[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
+    *reinterpret_cast<uint2*>(out_q + (size_t)row * inter + i) = pack8_e4m3(y, scale);
+  }
+}
+
+MSGL_API int msgl_act_and_mul(const void* x, void* out, void* out_q, void* out_scale, int rows, int inter,
+                              int kind, int dtype, cudaStream_t stream) {
+  if (inter % 8) return MSGL_BAD_ARG;
+  if (rows == 0) return MSGL_OK;
+  if (out_q == nullptr) {
+    size_t vecs = (size_t)rows * (inter / 8);
+    int threads = 256;
+    unsigned blocks = (unsigned)((vecs + threads - 1) / threads);
+    if (dtype == MSGL_BF16)
+      act_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                                                                    inter, vecs, kind);
+    else if (dtype == MSGL_F16)
+      act_mul_kernel<__half><<<blocks, threads, 0, stream>>>((const __half*)x, (__half*)out, inter, vecs, kind);
+    else
+      return MSGL_BAD_ARG;
+  } else {
+    size_t smem = (size_t)inter * sizeof(float);
+    if (smem > 200 * 1024) return MSGL_BAD_ARG;
+    int threads = ((inter / 8 + 31) / 32) * 32;
+    if (threads > 1024) threads = 1024;
+    if (dtype == MSGL_BF16) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(act_mul_quant_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      act_mul_quant_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out_q,
+                                                                           (float*)out_scale, inter, kind);
+    } else if (dtype == MSGL_F16) {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(act_mul_quant_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      act_mul_quant_kernel<__half><<<rows, threads, smem, stream>>>((const __half*)x, (uint8_t*)out_q,
+                                                                    (float*)out_scale, inter, kind);
+    } else {
+      return MSGL_BAD_ARG;
+    }
+  }
+  MSGL_CHECK_LAUNCH("act_and_mul");
+  return MSGL_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// stand-alone activation quantisers: per token (group == hidden) or per `group` elements
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q,
+                                   float* __restrict__ out_scale, int group, size_t total_groups) {
+  // one warp per group; groups are contiguous runs of `group` elements (group % 8 == 0)
+  const size_t gidx = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gidx >= total_groups) return;
+  const int lane = threadIdx.x & 31;
+  const T* src = x + gidx * group;
+  float amax = 0.f;
+  for (int i = lane * 8; i < group; i += 256) {
+    float v[8];
+    load8(src + i, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+  }
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+  if (lane == 0) out_scale[gidx] = scale;
+  for (int i = lane * 8; i < group; i += 256) {
+    float v[8];
+    load8(src + i, v);
+    *reinterpret_cast<uint2*>(out_q + gidx * group + i) = pack8_e4m3(v, scale);
+  }
+}
+
+MSGL_API int msgl_quant_fp8(const void* x, void* out_q, void* out_scale, int rows, int hidden, int group,
+                            int dtype, cudaStream_t stream) {
+  if (group <= 0) group = hidden;
+  if (hidden % group || group % 8) return MSGL_BAD_ARG;
+  if (rows == 0) return MSGL_OK;
+  size_t total = (size_t)rows * (hidden / group);
+  int warps = 8;
+  unsigned blocks = (unsigned)((total + warps - 1) / warps);
+  if (dtype == MSGL_BF16)
+    quant_group_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out_q,
+                                                                        (float*)out_scale, group, total);
+  else if (dtype == MSGL_F16)
+    quant_group_kernel<__half><<<blocks, warps * 32, 0, stream>>>((const __half*)x, (uint8_t*)out_q,
+                                                                 (float*)out_scale, group, total);
+  else
+    return MSGL_BAD_ARG;
+  MSGL_CHECK_LAUNCH("quant_fp8");
+  return MSGL_OK;
+}

@@ -1,0 +1,481 @@
+// Dense GEMM family on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T with fp32
+// accumulation in tensor memory.
+//
+//   kind 0/1  f16 / bf16 operands                       (tcgen05.mma.kind::f16)
+//   kind 2    e4m3 x e4m3, per-token x per-channel scales in the epilogue (W8A8)
+//             (tcgen05.mma.kind::f8f6f4)
+//   kind 3    e4m3 activations x packed e2m1 weights with a UE8M0 scale per 32 K elements
+//             (W4A8 MXFP4; tcgen05.mma.kind::mxf8f6f4.block_scale), per-token scale in the
+//             epilogue. The weights stay 4-bit in HBM; TMA expands them to the padded
+//             one-element-per-byte shared-memory form the instruction wants.
+//
+// Replaces the reference's fp8_wmma / dense_gemm packages (mmq_fp8_gemm, mmq_w8a8_gemm,
+// dense_gemm*, dense_bf16_gemv; python/minisgl/quant/kernels.py:1686-1830,
+// python/minisgl/layers/minv.py:223-398) and its cuBLAS calls.
+//
+// Structure: persistent CTAs (one per SM), 6 warps. Warp 0 drives TMA into a ring of
+// 128-byte-swizzled stages; warp 1 issues the MMAs and owns tensor memory; warps 2-5 drain
+// the accumulator (two accumulator buffers, so the epilogue of tile i overlaps the main loop
+// of tile i+1). Full K per output tile, no split-K: a row's result does not depend on M, so a
+// verify batch (M = K+1) reproduces the decode result (M = 1) bit for bit.
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+using namespace msgl;
+using namespace msgl::ptx;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int kThreads = 192;
+
+enum GemmKind : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_F8 = 2, KIND_MXF4 = 3 };
+
+struct GemmArgs {
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  const float* a_scale;    // [M] or nullptr
+  const float* b_scale;    // [N] or nullptr
+  const void* bias;        // [N] in the compute dtype, or nullptr
+  void* c;
+  long long ldc;
+  int out_dtype;           // MSGL_BF16 / MSGL_F16 / MSGL_F32
+  int bias_dtype;
+  const uint8_t* sfb;      // scale-factor atoms [n_atoms][k_atoms][512] (kind 3)
+  int sf_k_atoms;
+  int* status;
+};
+
+__device__ int g_gemm_status = 0;
+
+template <int KIND> struct KindTraits;
+template <> struct KindTraits<KIND_F16> { static constexpr int BKE = 64; };
+template <> struct KindTraits<KIND_BF16> { static constexpr int BKE = 64; };
+template <> struct KindTraits<KIND_F8> { static constexpr int BKE = 128; };
+template <> struct KindTraits<KIND_MXF4> { static constexpr int BKE = 128; };
+
+template <int KIND, int BN> struct TmemCols {
+  static constexpr int need = 2 * BN + (KIND == KIND_MXF4 ? 8 : 0);
+  static constexpr int value = need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+};
+
+template <int BN, int STAGES> struct SmemLayout {
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SF_BYTES = 512;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * A_BYTES;
+  static constexpr int off_sf = off_b + STAGES * B_BYTES;
+  static constexpr int off_sfa = off_sf + STAGES * SF_BYTES;
+  static constexpr int off_bar = off_sfa + 512;
+  static constexpr int total = off_bar + (2 * STAGES + 4) * 8 + 16;
+};
+
+__device__ __forceinline__ void store_out8(void* c, int out_dtype, size_t idx, const float (&v)[8]) {
+  if (out_dtype == MSGL_BF16) {
+    store8(reinterpret_cast<__nv_bfloat16*>(c) + idx, v);
+  } else if (out_dtype == MSGL_F16) {
+    store8(reinterpret_cast<__half*>(c) + idx, v);
+  } else {
+    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + idx);
+    p[0] = make_float4(v[0], v[1], v[2], v[3]);
+    p[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmArgs args) {
+  using L = SmemLayout<BN, STAGES>;
+  using KT = KindTraits<KIND>;
+  constexpr int NCOLS = TmemCols<KIND, BN>::value;
+  // TMA counts the packed source bytes of a 4-bit tile (64 per row), not its padded
+  // one-element-per-byte footprint in shared memory (128 per row)
+  constexpr uint32_t STAGE_TX =
+      KIND == KIND_MXF4 ? L::A_BYTES + L::B_BYTES / 2 + L::SF_BYTES : L::A_BYTES + L::B_BYTES;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // the dynamic segment is only guaranteed 16-byte aligned: round up to the swizzle period
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + L::off_bar;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_bar + (2 * STAGES + 4) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_bar + (2 * STAGES + 4) * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = args.m_tiles * args.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+  }
+  if (KIND == KIND_MXF4) {
+    // activation block scales are all 2^0: the per-token fp32 scale is applied in the epilogue
+    for (int i = threadIdx.x; i < 128; i += blockDim.x)
+      reinterpret_cast<uint32_t*>(smem + L::off_sfa)[i] = 0x7F7F7F7Fu;
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), NCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+        const int n0 = n_tile * BN;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 101)) break;
+          mbar_expect_tx(full_bar(stage), STAGE_TX);
+          tma_load_2d(s_base + L::off_a + stage * L::A_BYTES, &tma_a, full_bar(stage), kb * KT::BKE, m_tile * BM);
+          tma_load_2d(s_base + L::off_b + stage * L::B_BYTES, &tma_b, full_bar(stage), kb * KT::BKE, n0);
+          if (KIND == KIND_MXF4) {
+            const uint8_t* src = args.sfb + ((size_t)(n0 / 128) * args.sf_k_atoms + kb) * 512;
+            bulk_load(s_base + L::off_sf + stage * L::SF_BYTES, src, 512, full_bar(stage));
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (*abort_flag) {  // give copies that are still in flight time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t sfa_tmem = tmem_base + 2 * BN;
+      const uint32_t sfb_tmem = tmem_base + 2 * BN + 4;
+      if (KIND == KIND_MXF4) tmem_cp_32x128b_warpx4(sfa_tmem, smem_desc_sf(s_base + L::off_sfa));
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const int n0 = (tile / args.m_tiles) * BN;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 102)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 103)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_s = s_base + L::off_a + stage * L::A_BYTES;
+          const uint32_t b_s = s_base + L::off_b + stage * L::B_BYTES;
+          if (KIND == KIND_MXF4)
+            tmem_cp_32x128b_warpx4(sfb_tmem, smem_desc_sf(s_base + L::off_sf + stage * L::SF_BYTES));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t a_desc = smem_desc_sw128(a_s + k * 32);
+            const uint64_t b_desc = smem_desc_sw128(b_s + k * 32);
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (KIND == KIND_F16) {
+              mma_f16(d_tmem, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
+            } else if (KIND == KIND_BF16) {
+              mma_f16(d_tmem, a_desc, b_desc, idesc_dense(1, 1, BM, BN), accum);
+            } else if (KIND == KIND_F8) {
+              mma_f8f6f4(d_tmem, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
+            } else {
+              mma_mxf8f6f4(d_tmem, a_desc, b_desc, idesc_block_scaled(0, 5, BM, BN, 0, (uint32_t)k), accum,
+                           sfa_tmem, sfb_tmem + (uint32_t)((n0 & 127) >> 5));
+            }
+          }
+          tc_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
+      tc_fence_after();
+      const int row = m_tile * BM + q * 32 + lane;
+      const bool row_ok = row < args.M;
+      const float a_s = (args.a_scale != nullptr && row_ok) ? args.a_scale[row] : 1.f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+        tmem_ld_wait();
+        const int col0 = n_tile * BN + c * 32;
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = col0 + j * 8;
+            if (col < args.N) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float x = __uint_as_float(r[j * 8 + e]) * a_s;
+                if (args.b_scale != nullptr) x *= __ldg(args.b_scale + col + e);
+                if (args.bias != nullptr) {
+                  x += args.bias_dtype == MSGL_BF16
+                           ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col + e])
+                           : (args.bias_dtype == MSGL_F16
+                                  ? __half2float(reinterpret_cast<const __half*>(args.bias)[col + e])
+                                  : reinterpret_cast<const float*>(args.bias)[col + e]);
+                }
+                v[e] = x;
+              }
+              store_out8(args.c, args.out_dtype, (size_t)row * args.ldc + col, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, NCOLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, stride;
+  uint32_t b0, b1;
+  int dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 &&
+           dtype == o.dtype;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    auto mix = [&](uint64_t v) { h ^= std::hash<uint64_t>()(v) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.d0); mix(k.d1); mix(k.stride); mix(k.b0); mix(k.b1); mix((uint64_t)k.dtype);
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+std::mutex g_map_mutex;
+
+// 2-D K-major tensor map: dims {inner (elements), rows}, box {box_inner, box_rows}, 128B swizzle
+int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint64_t inner, uint64_t rows,
+                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, bool cache) {
+  MapKey key{ptr, inner, rows, row_stride_bytes, box_inner, box_rows, (int)dt};
+  if (cache) {
+    std::lock_guard<std::mutex> g(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) { *out = it->second; return MSGL_OK; }
+  }
+  msgl_encode_tiled_fn enc = msgl_get_encode_tiled();
+  if (enc == nullptr) return MSGL_CUDA_ERROR;
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    msgl_set_error_text(("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r)).c_str());
+    return MSGL_CUDA_ERROR;
+  }
+  if (cache) {
+    std::lock_guard<std::mutex> g(g_map_mutex);
+    if (g_map_cache.size() > 16384) g_map_cache.clear();
+    g_map_cache[key] = *out;
+  }
+  return MSGL_OK;
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int KIND, int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int smem = L::total + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { msgl_set_error("gemm smem attribute", e); return MSGL_CUDA_ERROR; }
+    configured = true;
+  }
+  int total = args.m_tiles * args.n_tiles;
+  int grid = total < max_ctas ? total : max_ctas;
+  gemm_tcgen05_kernel<KIND, BN, STAGES><<<grid, kThreads, smem, stream>>>(ma, mb, args);
+  MSGL_CHECK_LAUNCH("gemm_tcgen05");
+  return MSGL_OK;
+}
+
+template <int KIND>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& args, int max_ctas,
+                cudaStream_t stream) {
+  switch (bn) {
+    case 128: return launch<KIND, 128, 6>(ma, mb, args, max_ctas, stream);
+    case 64: return launch<KIND, 64, 8>(ma, mb, args, max_ctas, stream);
+    case 32: return launch<KIND, 32, 8>(ma, mb, args, max_ctas, stream);
+    default: return MSGL_BAD_ARG;
+  }
+}
+
+}  // namespace
+
+msgl_encode_tiled_fn msgl_get_encode_tiled() {
+  static msgl_encode_tiled_fn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<msgl_encode_tiled_fn>(p);
+    else msgl_set_error_text("cuTensorMapEncodeTiled is not available from the driver");
+  }
+  return fn;
+}
+
+// Pick the N tile so that the grid fills the GPU when the problem allows it.
+static int choose_bn(int m_tiles, int n, int sms, int smallest) {
+  const int cands[3] = {128, 64, 32};
+  for (int i = 0; i < 3; ++i) {
+    int bn = cands[i];
+    int tiles = m_tiles * ((n + bn - 1) / bn);
+    if (tiles >= sms || bn == smallest) return bn;
+  }
+  return smallest;
+}
+
+// a: [M, K] (kind 0/1: 16-bit, kind 2/3: e4m3 bytes), row stride lda elements
+// b: [N, K] (kind 0/1: 16-bit, kind 2: e4m3 bytes, kind 3: packed e2m1 [N, K/2])
+// c: [M, N] out_dtype, row stride ldc elements
+// bn_override: 0 = automatic, else 32 / 64 / 128; max_ctas: 0 = one per SM
+MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
+                       int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
+                       const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? MSGL_OK : MSGL_BAD_ARG;
+  if (N % 8) { msgl_set_error_text("gemm: N must be a multiple of 8"); return MSGL_BAD_ARG; }
+  const int esize_a = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
+  if ((lda * esize_a) % 16 || (uintptr_t)a % 16 || (uintptr_t)b % 16 || (uintptr_t)c % 16) {
+    msgl_set_error_text("gemm: operands must be 16-byte aligned with 16-byte row strides");
+    return MSGL_BAD_ARG;
+  }
+  if (kind == KIND_MXF4 && (K % 32 || sf_atoms == nullptr || (uintptr_t)b % 32)) {
+    msgl_set_error_text("gemm: MXFP4 needs K % 32 == 0, 32-byte aligned weights and scale atoms");
+    return MSGL_BAD_ARG;
+  }
+  if ((kind == KIND_F16 || kind == KIND_BF16) ? (K % 8) : (K % 16)) {
+    msgl_set_error_text("gemm: K row bytes must be a multiple of 16");
+    return MSGL_BAD_ARG;
+  }
+  const int sms = num_sms();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+  const int bke = (kind == KIND_F16 || kind == KIND_BF16) ? 64 : 128;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K;
+  args.m_tiles = (M + BM - 1) / BM;
+  // The block-scaled instruction takes its weight scale factors from tensor-memory columns in
+  // steps of 64 rows (two columns), so the MXFP4 kind has no 32-wide N tile.
+  const int bn = bn_override ? bn_override : choose_bn(args.m_tiles, N, sms, kind == KIND_MXF4 ? 64 : 32);
+  if (kind == KIND_MXF4 && bn == 32) {
+    msgl_set_error_text("gemm: the MXFP4 kind supports N tiles of 64 and 128 only");
+    return MSGL_BAD_ARG;
+  }
+  args.n_tiles = (N + bn - 1) / bn;
+  args.k_blocks = (K + bke - 1) / bke;
+  args.a_scale = (const float*)a_scale;
+  args.b_scale = (const float*)b_scale;
+  args.bias = bias;
+  args.bias_dtype = bias_dtype;
+  args.c = c;
+  args.ldc = ldc;
+  args.out_dtype = out_dtype;
+  args.sfb = (const uint8_t*)sf_atoms;
+  args.sf_k_atoms = (K + 127) / 128;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_gemm_status);
+  args.status = status;
+
+  CUtensorMap ma, mb;
+  int rc;
+  if (kind == KIND_F16 || kind == KIND_BF16) {
+    CUtensorMapDataType dt = kind == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    rc = make_map_2d(&ma, a, dt, K, M, (uint64_t)lda * 2, 64, BM, false);
+    if (rc) return rc;
+    rc = make_map_2d(&mb, b, dt, K, N, (uint64_t)K * 2, 64, bn, true);
+  } else if (kind == KIND_F8) {
+    rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
+    if (rc) return rc;
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, N, (uint64_t)K, 128, bn, true);
+  } else if (kind == KIND_MXF4) {
+    rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
+    if (rc) return rc;
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, N, (uint64_t)K / 2, 128, bn, true);
+  } else {
+    return MSGL_BAD_ARG;
+  }
+  if (rc) return rc;
+  switch (kind) {
+    case KIND_F16: return dispatch_bn<KIND_F16>(bn, ma, mb, args, max_ctas, stream);
+    case KIND_BF16: return dispatch_bn<KIND_BF16>(bn, ma, mb, args, max_ctas, stream);
+    case KIND_F8: return dispatch_bn<KIND_F8>(bn, ma, mb, args, max_ctas, stream);
+    default: return dispatch_bn<KIND_MXF4>(bn, ma, mb, args, max_ctas, stream);
+  }
+}
+
+// 0 when no bounded wait of a GEMM kernel has run out since the last reset; else a code
+// (101 producer / 102 accumulator-free / 103 stage-full / 104 epilogue wait).
+MSGL_API int msgl_gemm_status(int reset) {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));
+  if (reset && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_gemm_status, &z, sizeof(int));
+  }
+  return v;
+}

@@ -175,10 +175,10 @@ class Engine:
         set_global_ctx(self.ctx)
         self.sampler = Sampler(self.device, mc.vocab_size, mc.final_logit_softcapping, seed=config.seed)
         self._staging_cap = 0
-        self._staging_host: Optional[torch.Tensor] = None
-        self._staging_dev: Optional[torch.Tensor] = None
-        self._out_host = torch.empty(max(config.max_running_req * 8, 64), dtype=torch.int32,
-                                     pin_memory=(dev_kind == "cuda"))
+        self._ring = 4
+        self._ring_pos = 0
+        self._out_pos = 0
+        self._out_ring = [None] * self._ring
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.steps = 0
@@ -276,31 +276,58 @@ class Engine:
     # ------------------------------------------------------------------ step
     def _stage(self, plan: StepPlan):
         """Pack the plan into one pinned buffer and start a single H2D copy; returns device
-        views in plan order."""
+        views in plan order. The pinned side is a ring: with overlapped scheduling the host
+        fills the plan of step n+1 while the copy of step n may still be queued behind
+        kernels, so a slot is reused only after the event recorded behind its copy."""
         parts = [plan.token_idx, plan.positions, plan.out_loc, plan.cu_q, plan.seq_lens,
                  plan.block_table.reshape(-1), plan.sample_rows, plan.write_idx]
         total = sum(int(p.size) for p in parts)
+        cuda = self.device.type == "cuda"
         if total > self._staging_cap:
+            if cuda:
+                torch.cuda.synchronize(self.device)
             self._staging_cap = max(total * 2, 1 << 16)
-            self._staging_host = torch.empty(self._staging_cap, dtype=torch.int32,
-                                             pin_memory=(self.device.type == "cuda"))
-            self._staging_dev = torch.empty(self._staging_cap, dtype=torch.int32, device=self.device)
-            self._staging_np = self._staging_host.numpy()
+            self._staging_ring = [
+                torch.empty(self._staging_cap, dtype=torch.int32, pin_memory=cuda) for _ in range(self._ring)]
+            self._staging_dev_ring = [
+                torch.empty(self._staging_cap, dtype=torch.int32, device=self.device) for _ in range(self._ring)]
+            self._staging_events = [None] * self._ring
+        slot = self._ring_pos % self._ring
+        self._ring_pos += 1
+        ev = self._staging_events[slot]
+        if ev is not None:
+            ev.synchronize()
+        host = self._staging_ring[slot]
+        host_np = host.numpy()
         off, views = 0, []
         for p in parts:
             n = int(p.size)
-            self._staging_np[off : off + n] = p.reshape(-1)
+            host_np[off : off + n] = p.reshape(-1)
             views.append((off, n))
             off += n
-        if self.device.type == "cuda":
-            self._staging_dev[:total].copy_(self._staging_host[:total], non_blocking=True)
-            src = self._staging_dev
+        if cuda:
+            dev = self._staging_dev_ring[slot]
+            dev[:total].copy_(host[:total], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._staging_events[slot] = ev
+            src = dev
         else:
-            src = self._staging_host.clone()
+            src = host.clone()
         self.h2d_bytes += 4 * total
         out = [src[o : o + n] for o, n in views]
         out[5] = out[5].view(plan.block_table.shape)
         return out
+
+    def _out_buffer(self, n: int) -> torch.Tensor:
+        """Pinned landing buffer for the sampled ids of one step (ring, see ``_stage``)."""
+        slot = self._out_pos % self._ring
+        self._out_pos += 1
+        buf = self._out_ring[slot]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 64), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._out_ring[slot] = buf
+        return buf[:n]
 
     def forward_batch(self, batch: Batch, plan: StepPlan, args: BatchSamplingArgs,
                       return_logits: bool = False) -> ForwardOutput:
@@ -312,15 +339,26 @@ class Engine:
         return self._forward_impl(batch, plan, args, return_logits)
 
     def _forward_impl(self, batch, plan, args, return_logits) -> ForwardOutput:
+        n_sample = int(plan.sample_rows.size)
+        bs = batch.size
+        use_graph = (self.graph_runner is not None and batch.is_decode and not batch.spec_verify
+                     and plan.max_q == 1 and self.graph_runner.can_run(bs)
+                     and batch.capture_layers is None and n_sample == bs)
+        if use_graph:
+            gr = self.graph_runner
+            bucket = gr.bucket_of(bs)
+            if bucket != bs:
+                tok, pos, loc, lens = gr.pad_plan_arrays(bs, bucket, plan.token_idx, plan.positions,
+                                                         plan.out_loc, plan.seq_lens)
+                bt = np.full((bucket, plan.block_table.shape[1]), self.kv_cache.dummy_page, dtype=np.int32)
+                bt[:bs] = plan.block_table
+                plan = StepPlan(tok, pos, loc, plan.cu_q, lens, bt, plan.sample_rows, plan.write_idx,
+                                plan.max_q, plan.max_kv)
         token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
         batch.positions = positions
         batch.out_loc = out_loc
-        n_sample = int(plan.sample_rows.size)
-        use_graph = (self.graph_runner is not None and batch.is_decode and not batch.spec_verify
-                     and plan.max_q == 1 and self.graph_runner.can_run(batch.size)
-                     and batch.capture_layers is None)
         if use_graph:
-            logits = self.graph_runner.replay(batch, token_idx, positions, out_loc, seq_lens, block_table, plan)
+            logits = self.graph_runner.replay(bs, token_idx, positions, out_loc, seq_lens, block_table)
         else:
             batch.input_ids = self.token_pool.view(-1)[token_idx.long()]
             self.ctx.attn_backend.prepare_metadata(
@@ -341,8 +379,7 @@ class Engine:
         tokens = sample.tokens
         tokens = self._agree_tokens(tokens)
         self.token_pool.view(-1)[write_idx.long()] = tokens
-        host = self._out_host[:n_sample] if n_sample <= self._out_host.numel() else torch.empty(
-            n_sample, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        host = self._out_buffer(n_sample)
         event = None
         if self.device.type == "cuda":
             host.copy_(tokens, non_blocking=True)

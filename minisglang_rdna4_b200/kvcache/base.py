@@ -49,6 +49,8 @@ class SizeInfo(NamedTuple):
 
 
 class BasePrefixCache(ABC):
+    retains = True  # False for a cache that never keeps inserted pages
+
     @abstractmethod
     def match_prefix(self, input_ids: torch.Tensor) -> Tuple[BaseCacheHandle, torch.Tensor]:
         """Longest cached page-aligned prefix of ``input_ids``: handle plus its page ids."""

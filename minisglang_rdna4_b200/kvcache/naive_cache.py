@@ -16,6 +16,8 @@ class NaiveHandle(BaseCacheHandle):
 
 
 class NaivePrefixCache(BasePrefixCache):
+    retains = False
+
     def __init__(self, page_size: int) -> None:
         self.page_size = page_size
         self._empty = torch.empty(0, dtype=torch.int32)

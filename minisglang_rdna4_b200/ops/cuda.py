@@ -1,0 +1,331 @@
+"""Python wrappers of the sm_100a kernels. Every function validates shapes/dtypes, allocates
+the output with PyTorch's caching allocator and launches on the current stream.
+
+``LAUNCHES`` counts kernel launches made through this module (the benchmark reports it);
+``LEDGER`` remembers which kernel served which op (printed once per op when
+``MSGL_DISPATCH_LEDGER=1``, the equivalent of the reference's ``[hip-engage]`` lines,
+python/minisgl/_hip_engage.py:49-71).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..env import ENV
+from . import ref
+from ._lib import check, lib
+
+LAUNCHES = 0
+LEDGER: Dict[str, str] = {}
+
+_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def _count(op: str, kernel: str, n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+    if op not in LEDGER:
+        LEDGER[op] = kernel
+        if ENV.DISPATCH_LEDGER.value:
+            print(f"[sm100-engage] {op} -> {kernel}", flush=True)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype} for the CUDA kernels") from None
+
+
+# ------------------------------------------------------------------------------------------ elementwise
+def embedding(ids, weight, vocab_start=0, vocab_len=None):
+    ids = ids.to(torch.int32) if ids.dtype != torch.int32 else ids
+    n = weight.shape[0] if vocab_len is None else vocab_len
+    out = torch.empty((ids.numel(), weight.shape[1]), dtype=weight.dtype, device=weight.device)
+    check(lib().msgl_embedding(_p(ids), _p(weight), _p(out), ids.numel(), weight.shape[1] * weight.element_size(),
+                               vocab_start, n, _stream()), "embedding")
+    _count("embedding", "embedding_kernel")
+    return out
+
+
+def _rms(x, residual, w, eps, plus_one, quant):
+    assert x.is_contiguous() and x.dim() == 2
+    rows, hidden = x.shape
+    out = out_q = out_s = None
+    if quant:
+        out_q = torch.empty((rows, hidden), dtype=torch.float8_e4m3fn, device=x.device)
+        out_s = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    else:
+        out = torch.empty_like(x)
+    if residual is not None:
+        assert residual.is_contiguous() and residual.shape == x.shape and residual.dtype == x.dtype
+    check(lib().msgl_rms_norm(_p(x), _p(residual), _p(w), _p(out), _p(out_q), _p(out_s), rows, hidden, eps,
+                              int(plus_one), _dt(x), _stream()), "rms_norm")
+    _count("rms_norm" + ("_add" if residual is not None else "") + ("_quant" if quant else ""), "rms_norm_kernel")
+    return (out_q, out_s) if quant else out
+
+
+def rms_norm(x, w, eps, plus_one=False):
+    shape = x.shape
+    return _rms(x.reshape(-1, shape[-1]), None, w, eps, plus_one, False).view(shape)
+
+
+def rms_norm_add(x, residual, w, eps, plus_one=False):
+    return _rms(x, residual, w, eps, plus_one, False)
+
+
+def rms_norm_quant(x, w, eps, residual=None, plus_one=False):
+    return _rms(x, residual, w, eps, plus_one, True)
+
+
+def per_token_quant_fp8(x):
+    return per_group_quant_fp8(x, 0)
+
+
+def per_group_quant_fp8(x, group):
+    assert x.is_contiguous() and x.dim() == 2
+    rows, hidden = x.shape
+    g = group or hidden
+    q = torch.empty((rows, hidden), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows, hidden // g) if group else (rows,), dtype=torch.float32, device=x.device)
+    check(lib().msgl_quant_fp8(_p(x), _p(q), _p(s), rows, hidden, g, _dt(x), _stream()), "quant_fp8")
+    _count("quant_fp8", "quant_group_kernel")
+    return q, s
+
+
+_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 2}
+
+
+def act_and_mul(x, kind="silu"):
+    assert x.is_contiguous() and x.dim() == 2
+    rows, two_i = x.shape
+    out = torch.empty((rows, two_i // 2), dtype=x.dtype, device=x.device)
+    check(lib().msgl_act_and_mul(_p(x), _p(out), None, None, rows, two_i // 2, _ACT[kind], _dt(x), _stream()),
+          "act_and_mul")
+    _count("act_and_mul", "act_mul_kernel")
+    return out
+
+
+def silu_and_mul_quant(x):
+    assert x.is_contiguous() and x.dim() == 2
+    rows, two_i = x.shape
+    q = torch.empty((rows, two_i // 2), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    check(lib().msgl_act_and_mul(_p(x), None, _p(q), _p(s), rows, two_i // 2, 0, _dt(x), _stream()),
+          "silu_and_mul_quant")
+    _count("silu_and_mul_quant", "act_mul_quant_kernel")
+    return q, s
+
+
+# ------------------------------------------------------------------------------------------ rope / kv
+def qk_norm_rope_store(qkv, q_w, k_w, positions, cos_sin, hq, hk, head_dim, rotary_dim, eps, k_cache, v_cache,
+                       out_loc, k_scale=None, v_scale=None, interleaved=False):
+    assert qkv.is_contiguous()
+    t = qkv.shape[0]
+    q_out = torch.empty((t, hq, head_dim), dtype=qkv.dtype, device=qkv.device)
+    page_size = k_cache.shape[2]
+    fp8 = k_cache.dtype == torch.float8_e4m3fn
+    num_slots = k_cache.shape[0] * page_size
+    check(lib().msgl_qk_norm_rope_store(
+        _p(qkv), _p(q_w), _p(k_w), _p(positions), _p(cos_sin), _p(q_out), _p(k_cache), _p(v_cache), _p(out_loc),
+        _p(k_scale), _p(v_scale), t, hq, hk, head_dim, rotary_dim, page_size, eps, int(interleaved), int(fp8),
+        cos_sin.shape[0], num_slots, _dt(qkv), _stream()), "qk_norm_rope_store")
+    _count("qk_norm_rope_store", "qk_norm_rope_store_kernel")
+    return q_out
+
+
+def store_kv(k, v, k_cache, v_cache, out_loc, k_scale=None, v_scale=None):
+    hk, page_size, d = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    t = out_loc.numel()
+    k = k.reshape(t, hk, d).contiguous()
+    v = v.reshape(t, hk, d).contiguous()
+    fp8 = k_cache.dtype == torch.float8_e4m3fn
+    check(lib().msgl_store_kv(_p(k), _p(v), _p(k_cache), _p(v_cache), _p(out_loc), _p(k_scale), _p(v_scale), t, hk,
+                              d, page_size, int(fp8), k_cache.shape[0] * page_size, _dt(k), _stream()), "store_kv")
+    _count("store_kv", "store_kv_kernel")
+
+
+# ------------------------------------------------------------------------------------------ attention
+_KV_MAPS: Dict[Tuple, Tuple[np.ndarray, object]] = {}
+
+
+def _kv_map(k_cache: torch.Tensor):
+    """TMA descriptor over the pool buffer that ``k_cache`` (one layer's K plane) is a view of.
+    Returns ``(descriptor bytes, layer index, number of layers)``."""
+    base = k_cache._base if k_cache._base is not None else k_cache
+    pages_p1, hk, ps, d = k_cache.shape
+    if base.dim() == 6:
+        two, layers = base.shape[0], base.shape[1]
+        plane_elems = pages_p1 * hk * ps * d
+        layer = (k_cache.data_ptr() - base.data_ptr()) // (plane_elems * base.element_size())
+        layer = int(layer) % layers
+        root = base
+    else:  # a stand-alone [pages, hk, ps, d] K tensor followed by nothing: treat as one layer
+        raise ValueError("paged_attention expects k_cache / v_cache to be planes of one pool buffer")
+    key = (root.data_ptr(), tuple(root.shape), root.dtype)
+    hit = _KV_MAPS.get(key)
+    if hit is None:
+        buf = np.zeros(128, dtype=np.uint8)
+        check(lib().msgl_attn_make_kv_map(buf.ctypes.data, root.data_ptr(), root.element_size(), d, ps, hk,
+                                          pages_p1, 2 * layers), "attn_make_kv_map")
+        if len(_KV_MAPS) > 64:
+            _KV_MAPS.clear()
+        hit = (buf, root)
+        _KV_MAPS[key] = hit
+    return hit[0], layer, layers
+
+
+def make_pool_buffer(num_layers, pages_plus_one, hk, page_size, d, dtype, device):
+    return torch.zeros((2, num_layers, pages_plus_one, hk, page_size, d), dtype=dtype, device=device)
+
+
+def attention_workspace(max_rows, hq, d, device, max_splits=16):
+    return torch.empty(max_splits * max_rows * hq * (d + 1), dtype=torch.float32, device=device)
+
+
+def choose_splits(batch, hk, max_kv, decode):
+    if not decode:
+        return 1
+    ctas = batch * hk
+    want = -(-592 // ctas)
+    by_len = max(1, max_kv // 256)
+    return int(max(1, min(want, by_len, 16)))
+
+
+def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, causal=True, window=0, mask=None,
+                    k_scale=None, v_scale=None, max_q=0, max_kv=0, decode=False, workspace=None, splits=None):
+    t, hq, d = q.shape
+    pages_p1, hk, ps, _ = k_cache.shape
+    desc, layer, layers = _kv_map(k_cache)
+    b = seq_lens.numel()
+    if max_q <= 0:
+        max_q = int((cu_q[1:] - cu_q[:-1]).max())
+    if max_kv <= 0:
+        max_kv = int(seq_lens.max())
+    if splits is None:
+        splits = choose_splits(b, hk, max_kv, decode or max_q == 1)
+    if splits > 1:
+        need = int(lib().msgl_attn_workspace_floats(t, hq, d, splits))
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q)
+    fp8 = k_cache.dtype == torch.float8_e4m3fn
+    if mask is not None:
+        assert mask.dtype == torch.float32 and mask.stride(-1) == 1
+    check(lib().msgl_paged_attention(
+        desc.ctypes.data, _p(q), _p(out), _p(block_table), block_table.stride(0), _p(cu_q), _p(seq_lens),
+        _p(k_scale), _p(v_scale), _p(mask), mask.stride(0) if mask is not None else 0, _p(workspace) if splits > 1 else None,
+        b, t, max_q, hq, hk, d, ps, pages_p1 - 1, layer, layers, int(fp8), int(causal), int(window), splits,
+        float(scale), _dt(q), _stream()), "paged_attention")
+    _count("paged_attention", "paged_attention_kernel", 2 if splits > 1 else 1)
+    return out
+
+
+# ------------------------------------------------------------------------------------------ GEMM
+KIND_F16, KIND_BF16, KIND_F8, KIND_MXF4 = 0, 1, 2, 3
+
+
+def _gemm(kind, a, b, n, k, out_dtype, a_scale=None, b_scale=None, bias=None, sf_atoms=None, bn=0, max_ctas=0):
+    assert a.dim() == 2 and a.stride(1) == 1 and b.is_contiguous()
+    m = a.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if m == 0:
+        return out
+    check(lib().msgl_gemm(kind, _p(a), a.stride(0), _p(b), _p(out), n, m, n, k, _p(a_scale), _p(b_scale), _p(bias),
+                          _DT[bias.dtype] if bias is not None else 0, _p(sf_atoms), _DT[out_dtype], bn, max_ctas,
+                          _stream()), "gemm")
+    _count(("gemm_f16", "gemm_bf16", "gemm_w8a8", "gemm_w4a8_mxfp4")[kind], "gemm_tcgen05_kernel")
+    return out
+
+
+def gemm(x, w, bias=None, out_dtype=None, bn=0, max_ctas=0):
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    kind = KIND_BF16 if x2.dtype == torch.bfloat16 else KIND_F16
+    if w.dtype != x2.dtype:
+        raise TypeError(f"gemm: activation {x2.dtype} vs weight {w.dtype}")
+    n, k = w.shape
+    if n % 8:
+        raise ValueError("gemm: N must be a multiple of 8")
+    out = _gemm(kind, x2, w, n, k, out_dtype or x.dtype, bias=bias, bn=bn, max_ctas=max_ctas)
+    return out.view(*shape[:-1], n)
+
+
+def gemm_w8a8(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16, bias=None, bn=0):
+    n, k = w_q.shape
+    return _gemm(KIND_F8, x_q, w_q, n, k, out_dtype, a_scale=x_scale, b_scale=w_scale, bias=bias, bn=bn)
+
+
+def gemm_w4a8_mxfp4(x_q, x_scale, w_packed, sf_atoms, out_dtype=torch.bfloat16, bias=None, bn=0):
+    n, k = w_packed.shape[0], w_packed.shape[1] * 2
+    if sf_atoms is None:
+        raise ValueError("gemm_w4a8_mxfp4 needs the packed scale atoms (quant.mxfp4.pack_sf_atoms)")
+    return _gemm(KIND_MXF4, x_q, w_packed, n, k, out_dtype, a_scale=x_scale, bias=bias, sf_atoms=sf_atoms, bn=bn)
+
+
+def gemm_fp8_block(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16):
+    """128x128-block fp8: one tensor-core GEMM per 128-deep K block would need partial-sum
+    promotion; until that kernel exists the block scales are folded into 16-bit operands and
+    the product runs on the bf16 tensor-core path."""
+    n, k = w_q.shape
+    ws = w_scale.repeat_interleave(128, 0).repeat_interleave(128, 1)[:n, :k]
+    w = (w_q.float() * ws).to(out_dtype)
+    xs = x_scale.repeat_interleave(128, 1)[:, :k]
+    x = (x_q.float() * xs).to(out_dtype)
+    return gemm(x, w, None, out_dtype)
+
+
+def gemm_status(reset=True) -> int:
+    return int(lib().msgl_gemm_status(int(reset)))
+
+
+def attn_status(reset=True) -> int:
+    return int(lib().msgl_attn_status(int(reset)))
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def argmax(logits):
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1
+    rows, vocab = logits.shape
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib().msgl_argmax(_p(logits), _p(out), rows, vocab, logits.stride(0), _stream()), "argmax")
+    _count("argmax", "argmax_kernel")
+    return out
+
+
+def sample(logits, temperatures, top_k=None, top_p=None, min_p=None, generator=None, uniform=None):
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1
+    rows, vocab = logits.shape
+    if uniform is None:
+        uniform = torch.rand((rows,), dtype=torch.float32, device=logits.device, generator=generator)
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib().msgl_sample(_p(logits), logits.stride(0), _p(temperatures), _p(top_k), _p(top_p), _p(min_p),
+                            _p(uniform), _p(out), rows, vocab, _stream()), "sample")
+    _count("sample", "sample_kernel")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ MoE (composed)
+def moe_route(router_logits, top_k, renormalize, scoring="softmax", bias=None, scale=1.0):
+    from . import moe_cuda
+
+    return moe_cuda.moe_route(router_logits, top_k, renormalize, scoring, bias, scale)
+
+
+def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
+    from . import moe_cuda
+
+    return moe_cuda.moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset)

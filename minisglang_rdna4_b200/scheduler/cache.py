@@ -120,8 +120,9 @@ class CacheManager:
         ids = req.input_ids[:valid_len]
         if not (insert and req.sampling_params.cache_output):
             ids = ids[: min(valid_len, req.prompt_len)]
-        keep_pages = len(ids) // ps
         old_prefix_pages = handle.cached_len // ps
+        # a cache that retains nothing (naive) takes ownership of no page
+        keep_pages = len(ids) // ps if self.prefix_cache.retains else old_prefix_pages
         if keep_pages > old_prefix_pages:
             already = self.prefix_cache.insert_prefix(ids[: keep_pages * ps], torch.from_numpy(pages[:keep_pages]))
             already_pages = already // ps

@@ -140,16 +140,27 @@ class Scheduler:
     def _schedule_next_batch(self) -> Optional[Batch]:
         batch, adder = self.prefill.schedule_next_batch(self._prefill_budget_now())
         if batch is not None:
-            pool = self.engine.token_pool
-            for slot, ids, _cached in adder.new_slots:
-                src = ids.pin_memory() if pool.is_cuda else ids
-                pool[slot, : ids.numel()].copy_(src, non_blocking=True)
-                self.engine.h2d_bytes += 4 * int(ids.numel())
+            self._upload_prompts(adder.new_slots)
             for req in batch.reqs:
                 self.reqs[req.uid] = req
                 self.prefix_len.setdefault(req.uid, req.cached_len)
             return batch
         return self.decode.schedule_next_batch()
+
+    def _upload_prompts(self, new_slots) -> None:
+        """Copy newly admitted prompts from pinned host memory into the token pool, on the
+        engine's stream so the copy is ordered before the forward that reads it."""
+        pool = self.engine.token_pool
+        if not new_slots:
+            return
+        if pool.is_cuda:
+            with torch.cuda.stream(self.engine.stream):
+                for slot, ids, _cached in new_slots:
+                    pool[slot, : ids.numel()].copy_(ids.pin_memory(), non_blocking=True)
+                    self.engine.h2d_bytes += 4 * int(ids.numel())
+        else:
+            for slot, ids, _cached in new_slots:
+                pool[slot, : ids.numel()].copy_(ids)
 
     def _make_plan(self, batch: Batch, extra_rows: int = 0) -> StepPlan:
         """Allocate pages and build the step's index arrays. ``extra_rows`` > 0 plans a

@@ -1,0 +1,460 @@
+"""OpenAI-compatible HTTP frontend (python/minisgl/server/api_server.py): ``/generate``,
+``/v1/chat/completions``, ``/v1/completions``, ``/v1/models``, ``/health``, ``/metrics``.
+
+The frontend owns no model state. It turns a request into a ``TokenizeMsg`` for the tokenizer
+worker, then demultiplexes ``UserReply`` text deltas into per-request queues and renders them
+as JSON or server-sent events. A client that disconnects mid-stream aborts its request.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+from dataclasses import replace
+from typing import Any, AsyncIterator, Dict, List, Optional, Union
+
+from fastapi import FastAPI, HTTPException, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+from pydantic import BaseModel, Field, model_validator
+
+from ..config import ServerArgs
+from ..core import SamplingParams
+from ..env import ENV
+from ..message import AbortMsg, StatsMsg, TokenizeMsg, UserReply
+from ..utils import init_logger
+from .metrics import FrontendMetrics
+from .reasoning import ReasoningParser, ReasoningStreamState, resolve_reasoning_parser
+from .tools import ToolCallStreamState, grammar_from_tools, parse_tool_calls, tool_openers_closers
+
+logger = init_logger(__name__)
+
+
+# ------------------------------------------------------------------------------------------ schemas
+class GenerateRequest(BaseModel):
+    prompt: str
+    max_tokens: int = Field(default_factory=lambda: ENV.DEFAULT_MAX_TOKENS.value)
+    ignore_eos: bool = False
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = -1
+    min_p: float = 0.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    seed: Optional[int] = None
+
+
+class ChatMessage(BaseModel):
+    role: str
+    content: Union[str, List[Dict[str, Any]], None] = None
+    name: Optional[str] = None
+    tool_calls: Optional[List[Dict[str, Any]]] = None
+    tool_call_id: Optional[str] = None
+    reasoning_content: Optional[str] = None
+
+
+class OpenAICompletionRequest(BaseModel):
+    model: Optional[str] = None
+    prompt: Union[str, List[int], None] = None
+    messages: Optional[List[ChatMessage]] = None
+    max_tokens: Optional[int] = None
+    max_completion_tokens: Optional[int] = None
+    temperature: Optional[float] = None
+    top_k: Optional[int] = None
+    top_p: Optional[float] = None
+    min_p: Optional[float] = None
+    n: int = 1
+    stream: bool = False
+    stream_options: Optional[Dict[str, Any]] = None
+    stop: Union[str, List[str], None] = None
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    response_format: Optional[Dict[str, Any]] = None
+    ignore_eos: bool = False
+    tools: Optional[List[Dict[str, Any]]] = None
+    tool_choice: Any = None
+    chat_template_kwargs: Optional[Dict[str, Any]] = None
+    enable_thinking: Optional[bool] = None
+    reasoning_max_tokens: Optional[int] = None
+    reasoning_effort: Optional[str] = None
+    logprobs: Union[bool, int, None] = None
+    top_logprobs: Optional[int] = None
+    seed: Optional[int] = None
+    # accepted and ignored
+    user: Optional[str] = None
+    store: Optional[bool] = None
+    metadata: Optional[Dict[str, Any]] = None
+    service_tier: Optional[str] = None
+    parallel_tool_calls: Optional[bool] = None
+    # rejected when set to something the engine cannot honour
+    logit_bias: Optional[Dict[str, float]] = None
+    echo: Optional[bool] = None
+    suffix: Optional[str] = None
+    best_of: Optional[int] = None
+
+    @model_validator(mode="after")
+    def _check(self):
+        if self.messages is None and self.prompt is None:
+            raise ValueError("either `messages` or `prompt` is required")
+        mt = self.max_completion_tokens if self.max_completion_tokens is not None else self.max_tokens
+        if mt is not None and mt < 1:
+            raise ValueError("max_tokens must be at least 1")
+        if self.n != 1:
+            raise ValueError("only n=1 is supported")
+        if self.logit_bias:
+            raise ValueError("logit_bias is not supported")
+        if self.echo:
+            raise ValueError("echo is not supported")
+        if self.suffix:
+            raise ValueError("suffix is not supported")
+        if self.best_of not in (None, 1):
+            raise ValueError("best_of is not supported")
+        return self
+
+    def resolved_max_tokens(self) -> int:
+        mt = self.max_completion_tokens if self.max_completion_tokens is not None else self.max_tokens
+        return int(mt) if mt is not None else ENV.DEFAULT_MAX_TOKENS.value
+
+
+# ------------------------------------------------------------------------------------------ frontend
+class FrontendManager:
+    """Owns the ZMQ links of the frontend and the per-request reply queues."""
+
+    def __init__(self, args: ServerArgs, send_queue=None, recv_queue=None) -> None:
+        self.args = args
+        self.send_queue = send_queue
+        self.recv_queue = recv_queue
+        self.queues: Dict[int, asyncio.Queue] = {}
+        self.uid = 0
+        self.metrics = FrontendMetrics(args.model_name)
+        self._listener: Optional[asyncio.Task] = None
+
+    def new_user(self) -> int:
+        self.uid += 1
+        self.queues[self.uid] = asyncio.Queue()
+        self.metrics.on_request(self.uid)
+        return self.uid
+
+    async def send_one(self, msg) -> None:
+        await self.send_queue.put(msg)
+
+    async def listen(self) -> None:
+        while True:
+            msg = await self.recv_queue.get()
+            if isinstance(msg, StatsMsg):
+                self.metrics.on_scheduler_stats(msg.dp_rank, msg.values)
+            elif isinstance(msg, UserReply):
+                q = self.queues.get(msg.uid)
+                if q is not None:
+                    q.put_nowait(msg)
+
+    def ensure_listener(self) -> None:
+        if self._listener is None and self.recv_queue is not None:
+            self._listener = asyncio.get_event_loop().create_task(self.listen())
+
+    async def replies(self, uid: int) -> AsyncIterator[UserReply]:
+        q = self.queues[uid]
+        try:
+            while True:
+                msg: UserReply = await q.get()
+                self.metrics.on_token(uid, len(msg.token_ids) or 1)
+                yield msg
+                if msg.finished:
+                    self.metrics.on_finish(uid, msg.finish_reason, msg.prompt_tokens, msg.cached_tokens)
+                    return
+        finally:
+            self.queues.pop(uid, None)
+
+    async def abort_user(self, uid: int) -> None:
+        if uid in self.queues:
+            self.queues.pop(uid, None)
+            self.metrics.on_finish(uid, "abort")
+            await self.send_one(AbortMsg(uid))
+
+
+# ------------------------------------------------------------------------------------------ helpers
+def sampling_from_request(req: OpenAICompletionRequest, reasoning: Optional[ReasoningParser],
+                          chat_template: Optional[str]) -> SamplingParams:
+    stop = [req.stop] if isinstance(req.stop, str) else list(req.stop or [])
+    logprobs = 0
+    if req.logprobs:
+        logprobs = int(req.top_logprobs or (req.logprobs if isinstance(req.logprobs, int) and not isinstance(req.logprobs, bool) else 1))
+        logprobs = max(1, min(logprobs, 20))
+    grammar, required = None, False
+    if req.response_format:
+        kind = req.response_format.get("type")
+        if kind == "json_object":
+            grammar, required = "json", True
+        elif kind == "json_schema":
+            schema = (req.response_format.get("json_schema") or {}).get("schema") or req.response_format.get("schema")
+            grammar, required = json.dumps(schema or {}), True
+        elif kind not in (None, "text"):
+            raise ValueError(f"unsupported response_format type {kind!r}")
+    openers: List[str] = []
+    closers: List[str] = []
+    if req.tools:
+        forced = grammar_from_tools(req.tools, req.tool_choice)
+        if forced is not None and grammar is None:
+            grammar, required = forced, True
+        openers, closers = tool_openers_closers(chat_template)
+    thinking = req.enable_thinking
+    if thinking is None and req.chat_template_kwargs:
+        thinking = req.chat_template_kwargs.get("enable_thinking")
+    sp = SamplingParams(
+        temperature=0.0 if req.temperature is None else float(req.temperature),
+        top_k=-1 if req.top_k is None else int(req.top_k),
+        top_p=1.0 if req.top_p is None else float(req.top_p),
+        min_p=0.0 if req.min_p is None else float(req.min_p),
+        ignore_eos=req.ignore_eos, max_tokens=req.resolved_max_tokens(), logprobs=logprobs,
+        presence_penalty=req.presence_penalty, frequency_penalty=req.frequency_penalty, stop=stop,
+        grammar=grammar, grammar_required=required, seed=req.seed,
+        tool_call_openers=openers, tool_call_closers=closers,
+    )
+    if reasoning is not None and thinking is not False:
+        sp = replace(sp, think_close_delim=reasoning.close, think_span_open=reasoning.starts_open,
+                     think_budget=int(req.reasoning_max_tokens or 0), think_tool_release=list(openers))
+    return sp
+
+
+def _sse(obj: Any) -> str:
+    return "data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n"
+
+
+def _usage(prompt: int, completion: int, cached: int) -> Dict[str, Any]:
+    return {"prompt_tokens": prompt, "completion_tokens": completion, "total_tokens": prompt + completion,
+            "prompt_tokens_details": {"cached_tokens": cached}}
+
+
+async def stream_with_cancellation(request: Request, gen: AsyncIterator[str], on_cancel) -> AsyncIterator[str]:
+    """Forward ``gen`` while polling the connection; a vanished client triggers ``on_cancel``."""
+    try:
+        async for chunk in gen:
+            if await request.is_disconnected():
+                await on_cancel()
+                return
+            yield chunk
+    except asyncio.CancelledError:
+        await on_cancel()
+        raise
+
+
+# ------------------------------------------------------------------------------------------ app
+def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat_template: Optional[str] = None
+               ) -> FastAPI:
+    app = FastAPI(title="minisglang-rdna4 b200")
+    state = manager or FrontendManager(args)
+    app.state.manager = state
+    reasoning = resolve_reasoning_parser(args.reasoning_parser, chat_template)
+    created = int(time.time())
+
+    @app.on_event("startup")
+    async def _startup() -> None:  # pragma: no cover - needs a running loop with sockets
+        state.ensure_listener()
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/v1")
+    async def v1_root():
+        return {"status": "ok", "model": args.model_name}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": args.model_name, "object": "model", "created": created,
+                                            "owned_by": "minisglang_rdna4_b200"}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(state.metrics.render(), media_type="text/plain; version=0.0.4")
+
+    @app.post("/generate")
+    async def generate(req: GenerateRequest, request: Request):
+        state.ensure_listener()
+        uid = state.new_user()
+        sp = SamplingParams(temperature=req.temperature, top_k=req.top_k, top_p=req.top_p, min_p=req.min_p,
+                            ignore_eos=req.ignore_eos, max_tokens=req.max_tokens, seed=req.seed,
+                            presence_penalty=req.presence_penalty, frequency_penalty=req.frequency_penalty)
+        await state.send_one(TokenizeMsg(uid, req.prompt, sp))
+
+        async def gen():
+            async for reply in state.replies(uid):
+                if reply.error:
+                    yield _sse({"error": reply.error})
+                    break
+                if reply.incremental_output:
+                    yield _sse(reply.incremental_output)
+            yield _sse("[DONE]")
+
+        return StreamingResponse(stream_with_cancellation(request, gen(), lambda: state.abort_user(uid)),
+                                 media_type="text/event-stream")
+
+    async def _run(req: OpenAICompletionRequest, request: Request, chat: bool):
+        state.ensure_listener()
+        try:
+            sp = sampling_from_request(req, reasoning if chat else None, chat_template)
+        except ValueError as exc:
+            raise HTTPException(status_code=400, detail=str(exc))
+        uid = state.new_user()
+        if chat:
+            if req.messages is None:
+                raise HTTPException(status_code=400, detail="`messages` is required")
+            payload: Any = [m.model_dump(exclude_none=True) for m in req.messages]
+        else:
+            payload = req.prompt if req.prompt is not None else [m.model_dump(exclude_none=True) for m in req.messages]
+        kwargs = dict(req.chat_template_kwargs or {})
+        if req.enable_thinking is not None:
+            kwargs.setdefault("enable_thinking", req.enable_thinking)
+        await state.send_one(TokenizeMsg(uid, payload, sp, kwargs or None, req.tools))
+        rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
+        model = req.model or args.model_name
+        obj = "chat.completion" if chat else "text_completion"
+        use_reasoning = chat and reasoning is not None and req.enable_thinking is not False
+        want_tools = chat and bool(req.tools) and req.tool_choice != "none"
+
+        if req.stream:
+            include_usage = bool((req.stream_options or {}).get("include_usage"))
+
+            async def gen():
+                rstate = ReasoningStreamState(reasoning, reasoning.starts_open) if use_reasoning else None
+                tstate = ToolCallStreamState() if want_tools else None
+                n_tok = prompt_tok = cached = 0
+                finish = None
+                if chat:
+                    yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model,
+                                "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
+                                             "finish_reason": None}]})
+                async for reply in state.replies(uid):
+                    if reply.error:
+                        yield _sse({"error": {"message": reply.error, "type": "invalid_request_error"}})
+                        finish = "error"
+                        break
+                    n_tok += len(reply.token_ids)
+                    prompt_tok, cached = reply.prompt_tokens, reply.cached_tokens
+                    text = reply.incremental_output
+                    r_delta, c_delta = ("", text)
+                    if rstate is not None:
+                        r_delta, c_delta = rstate.feed(text)
+                        if reply.finished:
+                            r2, c2 = rstate.flush()
+                            r_delta, c_delta = r_delta + r2, c_delta + c2
+                    if tstate is not None:
+                        c_delta = tstate.feed(c_delta)
+                    delta: Dict[str, Any] = {}
+                    if r_delta:
+                        delta["reasoning_content"] = r_delta
+                    if c_delta:
+                        delta["content" if chat else "text"] = c_delta
+                    if reply.logprobs:
+                        delta_lp = {"content": reply.logprobs}
+                    else:
+                        delta_lp = None
+                    if delta:
+                        choice = ({"index": 0, "delta": delta, "finish_reason": None} if chat
+                                  else {"index": 0, "text": c_delta, "finish_reason": None})
+                        if delta_lp:
+                            choice["logprobs"] = delta_lp
+                        yield _sse({"id": rid, "object": obj + (".chunk" if chat else ""), "created": created,
+                                    "model": model, "choices": [choice]})
+                    if reply.finished:
+                        finish = reply.finish_reason or "stop"
+                calls: List[Dict[str, Any]] = []
+                if tstate is not None:
+                    rest, calls = tstate.finish()
+                    if rest:
+                        yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model,
+                                    "choices": [{"index": 0, "delta": {"content": rest}, "finish_reason": None}]})
+                    for i, call in enumerate(calls):
+                        yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model,
+                                    "choices": [{"index": 0, "delta": {"tool_calls": [dict(call, index=i)]},
+                                                 "finish_reason": None}]})
+                if calls and finish in (None, "stop"):
+                    finish = "tool_calls"
+                final = ({"index": 0, "delta": {}, "finish_reason": finish or "stop"} if chat
+                         else {"index": 0, "text": "", "finish_reason": finish or "stop"})
+                yield _sse({"id": rid, "object": obj + (".chunk" if chat else ""), "created": created, "model": model,
+                            "choices": [final]})
+                if include_usage:
+                    yield _sse({"id": rid, "object": obj + (".chunk" if chat else ""), "created": created,
+                                "model": model, "choices": [], "usage": _usage(prompt_tok, n_tok, cached)})
+                yield _sse("[DONE]")
+
+            return StreamingResponse(stream_with_cancellation(request, gen(), lambda: state.abort_user(uid)),
+                                     media_type="text/event-stream")
+
+        # ---- non-streaming
+        text_parts: List[str] = []
+        lp_records: List[Dict[str, Any]] = []
+        n_tok = prompt_tok = cached = 0
+        finish = "stop"
+        try:
+            async for reply in state.replies(uid):
+                if await request.is_disconnected():
+                    await state.abort_user(uid)
+                    raise HTTPException(status_code=499, detail="client disconnected")
+                if reply.error:
+                    raise HTTPException(status_code=400, detail=reply.error)
+                text_parts.append(reply.incremental_output)
+                n_tok += len(reply.token_ids)
+                prompt_tok, cached = reply.prompt_tokens, reply.cached_tokens
+                if reply.logprobs:
+                    lp_records.extend(reply.logprobs)
+                if reply.finished:
+                    finish = reply.finish_reason or "stop"
+        except asyncio.CancelledError:
+            await state.abort_user(uid)
+            raise
+        text = "".join(text_parts)
+        if chat:
+            reasoning_text = None
+            if use_reasoning:
+                reasoning_text, text = reasoning.split(text)
+            calls: List[Dict[str, Any]] = []
+            if want_tools:
+                text, calls = parse_tool_calls(text)
+            message: Dict[str, Any] = {"role": "assistant", "content": text if (text or not calls) else None}
+            if reasoning_text:
+                message["reasoning_content"] = reasoning_text
+            if calls:
+                message["tool_calls"] = calls
+                if finish == "stop":
+                    finish = "tool_calls"
+            choice: Dict[str, Any] = {"index": 0, "message": message, "finish_reason": finish}
+        else:
+            choice = {"index": 0, "text": text, "finish_reason": finish}
+        if lp_records:
+            choice["logprobs"] = {"content": lp_records}
+        return JSONResponse({"id": rid, "object": obj, "created": created, "model": model, "choices": [choice],
+                             "usage": _usage(prompt_tok, n_tok, cached)})
+
+    @app.post("/v1/chat/completions")
+    async def v1_chat_completions(req: OpenAICompletionRequest, request: Request):
+        return await _run(req, request, chat=True)
+
+    @app.post("/v1/completions")
+    async def v1_completions(req: OpenAICompletionRequest, request: Request):
+        return await _run(req, request, chat=False)
+
+    return app
+
+
+def run_api_server(args: ServerArgs, start_backend=None) -> None:
+    """Create the ZMQ links, start the backend processes and serve with uvicorn."""
+    import uvicorn
+
+    from ..utils.mp import ZmqAsyncPullQueue, ZmqAsyncPushQueue
+    from ..tokenizer.simple import load_tokenizer
+
+    manager = FrontendManager(
+        args, send_queue=ZmqAsyncPushQueue(args.zmq_tokenizer_addr, create=False),
+        recv_queue=ZmqAsyncPullQueue(args.zmq_frontend_addr, create=True))
+    template = args.chat_template
+    if template is None:
+        try:
+            template = getattr(load_tokenizer(args.model_path), "chat_template", None)
+        except Exception:
+            template = None
+    if start_backend is not None:
+        start_backend()
+    app = create_app(args, manager, template if isinstance(template, str) else None)
+    uvicorn.run(app, host=args.host, port=args.port, log_level="warning")

@@ -1,0 +1,254 @@
+"""Numerics of every sm_100a kernel against the fp32 PyTorch restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from minisglang_rdna4_b200.ops import cuda
+
+    return cuda
+
+
+def _ref():
+    from minisglang_rdna4_b200.ops import ref
+
+    return ref
+
+
+def _close(a, b, rtol, atol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())}/{bad.numel()} off, max err {float(err.max()):.4g}"
+
+
+# ------------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_embedding(K, dtype):
+    w = torch.randn(1000, 256, device="cuda").to(dtype)
+    ids = torch.randint(0, 1000, (77,), device="cuda", dtype=torch.int32)
+    assert torch.equal(K.embedding(ids, w), w[ids.long()])
+    out = K.embedding(ids, w[:300], 100, 300)
+    assert torch.equal(out, _ref().embedding(ids, w[:300], 100, 300))
+
+
+@pytest.mark.parametrize("hidden", [256, 2560, 8192])
+@pytest.mark.parametrize("rows", [1, 7, 300])
+def test_rms_norm_family(K, hidden, rows):
+    R = _ref()
+    x = torch.randn(rows, hidden, device="cuda").bfloat16()
+    res = torch.randn(rows, hidden, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda")).bfloat16()
+    _close(K.rms_norm(x, w, 1e-6), R.rms_norm(x, w, 1e-6), 1e-2, 1e-2, "rms_norm")
+    r1, r2 = res.clone(), res.clone()
+    y1 = K.rms_norm_add(x, r1, w, 1e-6)
+    y2 = R.rms_norm_add(x, r2, w, 1e-6)
+    assert torch.equal(r1, r2)
+    _close(y1, y2, 1e-2, 1e-2, "rms_norm_add")
+    r1, r2 = res.clone(), res.clone()
+    q1, s1 = K.rms_norm_quant(x, w, 1e-6, r1)
+    q2, s2 = R.per_token_quant_fp8(R.rms_norm_add(x, r2, w, 1e-6))
+    assert torch.equal(r1, r2)
+    _close(s1, s2, 1e-2, 0, "scale")
+    # a bf16 rounding flip before the quantiser moves a value by one e4m3 step (12.5 % at most)
+    _close(q1.float() * s1[:, None], q2.float() * s2[:, None], 0.14, 0.02, "rms_norm_add_quant")
+    assert float((q1.float() != q2.float()).float().mean()) < 0.01
+
+
+def test_act_and_quant(K):
+    R = _ref()
+    x = torch.randn(130, 2 * 9728, device="cuda").bfloat16()
+    _close(K.act_and_mul(x), R.silu_and_mul(x), 1e-2, 1e-2, "silu_and_mul")
+    _close(K.act_and_mul(x, "gelu_tanh"), R.gelu_and_mul(x, True), 1e-2, 1e-2, "gelu_tanh")
+    q, s = K.silu_and_mul_quant(x)
+    q2, s2 = R.per_token_quant_fp8(R.silu_and_mul(x))
+    _close(s, s2, 1e-2, 0, "scale")
+    _close(q.float() * s[:, None], q2.float() * s2[:, None], 0.14, 0.02, "silu_quant")
+    y = torch.randn(33, 4096, device="cuda").bfloat16()
+    q, s = K.per_token_quant_fp8(y)
+    q2, s2 = R.per_token_quant_fp8(y)
+    assert torch.equal(s, s2) and float((q.float() - q2.float()).abs().max()) <= 32
+    q, s = K.per_group_quant_fp8(y, 128)
+    q2, s2 = R.per_group_quant_fp8(y, 128)
+    _close(s, s2, 1e-6, 0, "group scale")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_qk_norm_rope_store(K, fp8, qk_norm):
+    R = _ref()
+    t, hq, hk, d, ps, pages = 37, 8, 2, 128, 16, 12
+    qkv = torch.randn(t, (hq + 2 * hk) * d, device="cuda").bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16() if qk_norm else None
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16() if qk_norm else None
+    pos = torch.randint(0, 500, (t,), device="cuda", dtype=torch.int32)
+    cs = R.build_cos_sin_cache(d, 512, 1e6).cuda()
+    loc = torch.randperm(pages * ps, device="cuda")[:t].to(torch.int32)
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    pool1 = torch.zeros(2, 1, pages + 1, hk, ps, d, device="cuda", dtype=dt)
+    pool2 = torch.zeros_like(pool1)
+    ks = (0.5 + torch.rand(hk, device="cuda")) / 40 if fp8 else None
+    vs = (0.5 + torch.rand(hk, device="cuda")) / 40 if fp8 else None
+    q1 = K.qk_norm_rope_store(qkv, qw, kw, pos, cs, hq, hk, d, d, 1e-6, pool1[0, 0], pool1[1, 0], loc, ks, vs)
+    q, k, v = qkv.split([hq * d, hk * d, hk * d], -1)
+    q2, k2 = R.qk_norm_rope(q, k, qw, kw, pos, cs, d, d, 1e-6)
+    R.store_kv(k2, v, pool2[0, 0], pool2[1, 0], loc, ks, vs)
+    _close(q1.view(t, -1), q2, 2e-2, 2e-2, "q")
+    if fp8:
+        diff = (pool1.float() - pool2.float()).abs()
+        assert float((diff > 0).float().mean()) < 0.02  # rounding-boundary flips only
+    else:
+        _close(pool1, pool2, 2e-2, 2e-2, "kv")
+    # stand-alone store
+    pool3 = torch.zeros_like(pool1)
+    K.store_kv(k2.contiguous(), v.contiguous(), pool3[0, 0], pool3[1, 0], loc, ks, vs)
+    assert torch.equal(pool3[1].view(torch.uint8) if fp8 else pool3[1], pool2[1].view(torch.uint8) if fp8 else pool2[1])
+
+
+# ------------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (5, 512, 320), (128, 256, 256), (300, 1024, 2560), (2048, 6144, 2560)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_16bit(K, m, n, k, dtype):
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(dtype)
+    for bn in (0, 32, 64, 128):
+        y = K.gemm(x, w, bn=bn)
+        assert K.gemm_status() == 0
+        _close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"gemm bn={bn}")
+    y32 = K.gemm(x, w, out_dtype=torch.float32)
+    _close(y32, x.float() @ w.float().t(), 1e-3, 1e-3, "gemm f32 out")
+    bias = torch.randn(n, device="cuda").to(dtype)
+    _close(K.gemm(x, w, bias), x.float() @ w.float().t() + bias.float(), 2e-2, 2e-2, "bias")
+
+
+def test_gemm_m_invariance(K):
+    x = torch.randn(64, 2560, device="cuda").bfloat16()
+    w = (torch.randn(4096, 2560, device="cuda") / 50).bfloat16()
+    full = K.gemm(x, w)
+    for m in (1, 5, 17):
+        assert torch.equal(K.gemm(x[:m].contiguous(), w), full[:m])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (7, 512, 384), (256, 2560, 4096), (1000, 1024, 2560)])
+def test_gemm_w8a8(K, m, n, k):
+    R = _ref()
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda") / math.sqrt(k)
+    ws = w.abs().amax(-1) / 448
+    wq = (w / ws[:, None]).to(torch.float8_e4m3fn)
+    xq, xs = K.per_token_quant_fp8(x)
+    for bn in (0, 32, 64, 128):
+        y = K.gemm_w8a8(xq, xs, wq, ws.float(), bn=bn)
+        assert K.gemm_status() == 0
+        _close(y, R.gemm_w8a8(xq, xs, wq, ws), 2e-2, 2e-2, f"w8a8 bn={bn}")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (9, 256, 256), (256, 2560, 4096), (700, 6144, 2560), (64, 320, 1024)])
+def test_gemm_w4a8_mxfp4(K, m, n, k):
+    R = _ref()
+    from minisglang_rdna4_b200.quant import mxfp4
+
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda") * 0.02
+    packed, sf = mxfp4.quantize_mxfp4(w)
+    atoms = mxfp4.pack_sf_atoms(sf)
+    assert torch.equal(mxfp4.unpack_sf_atoms(atoms, n, k // 32), sf)
+    xq, xs = K.per_token_quant_fp8(x)
+    want = R.gemm_w4a8_mxfp4(xq, xs, packed, sf)
+    for bn in (128, 64, 0):
+        y = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms, bn=bn)
+        assert K.gemm_status() == 0
+        _close(y, want, 2e-2, 2e-2, f"mxfp4 bn={bn}")
+
+
+# ------------------------------------------------------------------------------------------ attention
+def _attn_case(K, fp8, b, q_lens, kv_lens, hq, hk, d, ps, causal=True, window=0, mask=False, dtype=torch.bfloat16,
+               splits=None):
+    R = _ref()
+    torch.manual_seed(0)
+    pages = sum(-(-n // ps) for n in kv_lens) + 3
+    dt = torch.float8_e4m3fn if fp8 else dtype
+    pool = (torch.randn(2, 1, pages + 1, hk, ps, d, device="cuda") * (8 if fp8 else 1)).to(dt)
+    perm = torch.randperm(pages, device="cuda").to(torch.int32)
+    maxp = max(-(-n // ps) for n in kv_lens)
+    bt = torch.zeros(b, maxp, dtype=torch.int32, device="cuda")
+    off = 0
+    for i, n in enumerate(kv_lens):
+        np_ = -(-n // ps)
+        bt[i, :np_] = perm[off : off + np_]
+        off += np_
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    sl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    t = int(cu[-1])
+    q = torch.randn(t, hq, d, device="cuda").to(dtype)
+    ks = (0.5 + torch.rand(hk, device="cuda")) / 8 if fp8 else None
+    vs = (0.5 + torch.rand(hk, device="cuda")) / 8 if fp8 else None
+    m = None
+    if mask:
+        m = torch.where(torch.rand(t, max(kv_lens), device="cuda") < 0.7, 0.0, float("-inf")).float()
+        m[:, 0] = 0.0
+    scale = d ** -0.5
+    out = K.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, scale, causal=causal, window=window, mask=m,
+                            k_scale=ks, v_scale=vs, max_q=max(q_lens), max_kv=max(kv_lens), splits=splits)
+    assert K.attn_status() == 0
+    want = R.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, scale, causal, window, m, ks, vs)
+    _close(out, want, 3e-2, 3e-2, f"attention fp8={fp8}")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_decode(K, fp8):
+    _attn_case(K, fp8, 5, [1] * 5, [1, 17, 64, 333, 1500], 8, 2, 128, 16)
+    _attn_case(K, fp8, 3, [1] * 3, [700, 65, 2048], 32, 8, 128, 16, splits=4)
+    _attn_case(K, fp8, 2, [1] * 2, [100, 257], 8, 1, 128, 64, splits=2)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_prefill_and_extend(K, fp8):
+    _attn_case(K, fp8, 3, [5, 130, 64], [5, 130, 64], 8, 2, 128, 16)           # pure prefill
+    _attn_case(K, fp8, 3, [7, 33, 100], [200, 33, 1000], 16, 4, 128, 16)       # extend over a cached prefix
+    _attn_case(K, fp8, 2, [40, 9], [300, 90], 8, 8, 128, 32, window=64)        # sliding window, MHA
+    _attn_case(K, fp8, 2, [5, 5], [77, 300], 8, 2, 128, 16, mask=True)         # tree-mask verify
+    _attn_case(K, fp8, 2, [20, 12], [20, 50], 8, 2, 128, 16, causal=False)     # bidirectional
+
+
+def test_attention_head_dim_64_and_fp16(K):
+    _attn_case(K, False, 2, [9, 1], [40, 200], 4, 2, 64, 16)
+    _attn_case(K, False, 2, [9, 1], [40, 200], 8, 2, 128, 16, dtype=torch.float16)
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def test_argmax_and_sampling(K):
+    R = _ref()
+    logits = torch.randn(9, 151936, device="cuda")
+    assert torch.equal(K.argmax(logits), logits.argmax(-1).int())
+    sub = logits[:, :1000]  # strided rows
+    assert torch.equal(K.argmax(sub), sub.argmax(-1).int())
+    # sampling: the kept set must match the reference's and the draw must follow the distribution
+    lg = torch.randn(4, 4096, device="cuda") * 3
+    temps = torch.tensor([0.0, 0.7, 1.0, 1.3], device="cuda")
+    top_k = torch.tensor([0, 20, 0, 50], device="cuda", dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.8], device="cuda")
+    counts = torch.zeros(4, 4096, device="cuda")
+    n = 400
+    for i in range(n):
+        u = torch.rand(4, device="cuda")
+        tok = K.sample(lg, temps, top_k, top_p, None, uniform=u)
+        counts[torch.arange(4), tok.long()] += 1
+    assert int(counts[0].argmax()) == int(lg[0].argmax()) and counts[0].max() == n
+    probs = torch.softmax(lg / temps.clamp_min(1e-6)[:, None], -1)
+    sp, si = probs.sort(-1, descending=True)
+    for r in (1, 2, 3):
+        keep = torch.ones(4096, dtype=torch.bool, device="cuda")
+        if top_k[r] > 0:
+            keep &= torch.arange(4096, device="cuda") < top_k[r]
+        keep &= (sp[r].cumsum(0) - sp[r]) <= top_p[r]
+        allowed = torch.zeros(4096, dtype=torch.bool, device="cuda")
+        allowed[si[r][keep]] = True
+        assert counts[r][~allowed].sum() == 0, f"row {r} drew a filtered token"
+        assert counts[r][si[r][0]] > 0

@@ -17,9 +17,15 @@ from .base import AttnMetadata, BaseAttnBackend
 
 class PagedAttentionBackend(BaseAttnBackend):
     def __init__(self, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
-                 max_batch: int = 0) -> None:
+                 max_batch: int = 0, max_seq_len: int = 0, single_split: bool = False) -> None:
         self.hq, self.hk, self.d = num_q_heads, num_kv_heads, head_dim
         self.device = device
+        # The number of KV splits of a decode step depends only on the batch size and the
+        # longest sequence the pool can hold, never on the lengths in the batch: a captured
+        # graph and an eager step then reduce in the same order and agree bit for bit.
+        # ``single_split`` pins it to one (speculative verification must reproduce decode).
+        self.max_seq_len = max_seq_len
+        self.single_split = single_split
         self._workspace: Optional[torch.Tensor] = None
         if torch.device(device).type == "cuda":
             from ..ops import cuda as K
@@ -37,10 +43,15 @@ class PagedAttentionBackend(BaseAttnBackend):
         md = batch.attn_metadata
         pool = get_global_ctx().kv_cache
         fp8 = getattr(pool, "fp8", False)
+        splits = 1
+        if md.decode and not self.single_split and q.is_cuda:
+            from ..ops.cuda import choose_splits
+
+            splits = choose_splits(md.seq_lens.numel(), self.hk, self.max_seq_len or md.max_kv, True)
         return ops.paged_attention(
             q, pool.k_cache(layer), pool.v_cache(layer), md.block_table, md.cu_q, md.seq_lens, scale,
             causal=md.causal, window=window, mask=md.mask,
             k_scale=pool.k_scale[layer] if fp8 else None,
             v_scale=pool.v_scale[layer] if fp8 else None,
-            max_q=md.max_q, max_kv=md.max_kv, decode=md.decode, workspace=md.workspace,
+            max_q=md.max_q, max_kv=md.max_kv, decode=md.decode, workspace=md.workspace, splits=splits,
         )

@@ -53,7 +53,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Wait for `parity` of `bar` for at most `limit_ns`. Returns false when the CTA has been told
 // to abort or the limit ran out (in which case it sets *abort_flag and *status).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code, uint64_t limit_ns = 2000000000ull) {
+                                          int* status, int code, uint64_t limit_ns = 400000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {

@@ -169,7 +169,8 @@ class Engine:
         self.ctx.kv_cache = self.kv_cache
         self.ctx.attn_backend = create_attention_backend(
             config.attention_backend, self.q_heads_local, self.kv_heads_local, mc.head_dim, self.device,
-            max_batch=config.max_running_req,
+            max_batch=config.max_running_req, max_seq_len=self.max_seq_len,
+            single_split=config.spec_algorithm != "none",
         )
         self.ctx.comm = comm_mod.get_comm()
         set_global_ctx(self.ctx)
@@ -375,6 +376,10 @@ class Engine:
         if n_sample == 0:
             empty = torch.empty(0, dtype=torch.int32)
             return ForwardOutput(empty.to(self.device), empty, None)
+        if batch.spec_verify:
+            # the verify step decides acceptance itself from the logits of every row
+            empty = torch.empty(0, dtype=torch.int32)
+            return ForwardOutput(empty.to(self.device), empty, None, None, logits)
         sample = self.sampler.sample(logits, args)
         tokens = sample.tokens
         tokens = self._agree_tokens(tokens)

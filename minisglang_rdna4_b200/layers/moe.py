@@ -59,7 +59,15 @@ class MoELayer(BaseOP):
 
     @property
     def needs_tp_reduce(self) -> bool:
-        return self._ep is None and get_tp_info().size > 1
+        """True when ``forward`` returns a partial sum over the tensor-parallel group: the
+        intermediate dimension is sharded, or whole experts are sharded over the TP ranks (every
+        rank sees every token, computes its own experts, and the sum over ranks completes it;
+        python/minisgl/layers/moe.py:1258-1269)."""
+        from ..parallel.info import ep_over_tp
+
+        if get_tp_info().size == 1:
+            return False
+        return self._ep is None or ep_over_tp()
 
     def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
         for name in ("w13", "w2"):

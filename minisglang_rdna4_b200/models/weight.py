@@ -153,12 +153,12 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             continue
         if name.endswith(".mlp.gate.weight") and (name[: -len(".gate.weight")] + ".experts") in modules:
             moe = modules[name[: -len(".gate.weight")] + ".experts"]
-            assign(moe.gate, "weight", tensor, name)
+            assign(moe.gate, "weight", tensor, name[: -len(".gate.weight")] + ".experts.gate.weight")
             continue
         if name.endswith(".mlp.shared_expert_gate.weight"):
             blk = modules.get(name[: -len(".shared_expert_gate.weight")])
             if blk is not None and hasattr(blk, "shared_expert_gate"):
-                assign(blk, "shared_expert_gate", tensor, name)
+                assign(blk, "shared_expert_gate", tensor, name[: -len(".weight")])
             continue
         # ---- embeddings / head
         if name == "model.embed_tokens.weight":

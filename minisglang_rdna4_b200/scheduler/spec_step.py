@@ -1,0 +1,142 @@
+"""One speculative decode step: propose → stage → verify → accept → commit
+(python/minisgl/scheduler/scheduler.py:4755-5629).
+
+Every running request feeds ``1 + K_i`` rows to one verify forward: its last committed token
+followed by its draft. The target's arg-max (or distribution) of every row decides how many
+draft tokens stand. Rejected rows leave stale KV behind; it is overwritten when those
+positions are fed again, so only the length bookkeeping rolls back.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import numpy as np
+import torch
+
+from ..core import Batch, Req
+from ..engine import BatchSamplingArgs
+from ..env import ENV
+from ..message import DetokenizeMsg
+from ..spec.accept import accept_greedy, accept_rejection_sampling, eos_truncate
+from ..spec.width import AdaptiveWidth
+
+
+def spec_decode_step(sched) -> None:
+    proposer = sched.proposer
+    reqs: List[Req] = sorted(sched.decode.running.values(), key=lambda r: r.uid)
+    if not reqs:
+        return
+    limit = ENV.SPEC_MAX_BS.value or proposer.max_batch
+    if len(reqs) > limit:
+        batch = sched.decode.schedule_next_batch()
+        sched._process_last_data(sched._forward(batch))
+        return
+    if not hasattr(sched, "_spec_width"):
+        sched._spec_width = AdaptiveWidth(proposer.num_draft)
+    drafts = proposer.propose(reqs)
+    width = sched._spec_width.choose() if ENV.SPEC_ADAPTIVE_WIDTH.value else proposer.num_draft
+    drafts = [d[: min(width, proposer.budget(r))] for d, r in zip(drafts, reqs)]
+    eng = sched.engine
+    msl = sched.max_seq_len
+
+    # stage the draft tokens behind each request's last token in the token pool
+    flat_idx, flat_tok = [], []
+    for r, d in zip(reqs, drafts):
+        for j, t in enumerate(d):
+            flat_idx.append(r.table_idx * msl + r.device_len + j)
+            flat_tok.append(t)
+    if flat_idx:
+        idx = torch.tensor(flat_idx, dtype=torch.int64)
+        tok = torch.tensor(flat_tok, dtype=torch.int32)
+        if eng.device.type == "cuda":
+            with torch.cuda.stream(eng.stream):
+                eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
+        else:
+            eng.token_pool.view(-1)[idx] = tok
+
+    batch = Batch(reqs=reqs, phase="decode")
+    batch.spec_verify = True
+    plan = _verify_plan(sched, batch, drafts)
+    sampled = any(not r.sampling_params.is_greedy for r in reqs) and ENV.SPEC_SAMPLED.value
+    args = BatchSamplingArgs()
+    out = eng.forward_batch(batch, plan, args, return_logits=True)
+    logits = eng.sampler.condition_logits(out.logits, args)
+    target = logits.argmax(-1).to(torch.int32).cpu().tolist()
+    sched.stats["steps"] += 1
+    sched.stats["spec_steps"] += 1
+    sched.stats["decode_tokens"] += plan.num_tokens
+
+    replies: List[DetokenizeMsg] = []
+    cu = plan.cu_q.tolist()
+    total_accept = 0
+    for i, (r, d) in enumerate(zip(reqs, drafts)):
+        rows = target[cu[i]:cu[i + 1]]
+        if sampled and not r.sampling_params.is_greedy:
+            temp = max(r.sampling_params.temperature, 1e-6)
+            probs = torch.softmax(logits[cu[i]:cu[i + 1]].float() / temp, -1)
+            emitted = accept_rejection_sampling(probs, None, d)
+        else:
+            emitted = accept_greedy(rows, d)
+        emitted = emitted[: max(1, min(len(emitted), r.sampling_params.max_tokens - r.num_generated))]
+        emitted, hit_eos = eos_truncate(emitted, sched.eos_ids, r.sampling_params.ignore_eos)
+        n = len(emitted)
+        total_accept += n - 1
+        sched.stats["spec_drafted"] += len(d)
+        sched.stats["spec_accepted"] += n - 1
+        sched.stats["spec_emitted"] += n
+        # commit: tokens to the host buffer and (bonus token) to the token pool
+        r.append_host(torch.tensor(emitted, dtype=torch.int32))
+        pos = r.table_idx * msl + r.device_len
+        eng.token_pool.view(-1)[pos:pos + n] = torch.tensor(emitted, dtype=torch.int32).to(eng.device)
+        r.complete_many(n)
+        proposer.on_accept(r, emitted)
+        finished = hit_eos or r.num_generated >= r.sampling_params.max_tokens
+        reason = "stop" if hit_eos else ("length" if finished else None)
+        for j, t in enumerate(emitted):
+            last = j == n - 1
+            replies.append(DetokenizeMsg(r.uid, t, finished and last, reason if last else None,
+                                         prompt_tokens=r.prompt_len, cached_tokens=sched.prefix_len.get(r.uid, 0)))
+        if finished:
+            r.finished, r.finish_reason = True, reason
+            proposer.on_finish(r)
+            sched._free_req_resources(r, insert=True)
+    sched._spec_width.update(total_accept / max(len(reqs), 1))
+    sched.decode.filter_finished()
+    if replies:
+        sched.send_result(replies)
+
+
+def _verify_plan(sched, batch: Batch, drafts):
+    """Like ``Scheduler._make_plan`` but request i feeds ``1 + len(drafts[i])`` rows and every
+    row is sampled."""
+    from ..engine import StepPlan
+    from ..utils import cdiv
+
+    ps, msl = sched.page_size, sched.max_seq_len
+    reqs = batch.reqs
+    b = len(reqs)
+    slots = np.fromiter((r.table_idx for r in reqs), dtype=np.int64, count=b)
+    starts = np.fromiter((r.cached_len for r in reqs), dtype=np.int64, count=b)
+    ends = np.fromiter((r.device_len + len(d) for r, d in zip(reqs, drafts)), dtype=np.int64, count=b)
+    for r, end in zip(reqs, ends.tolist()):
+        have = sched.alloc_len.get(r.uid, r.cache_handle.cached_len)
+        if end > have:
+            first, last = cdiv(have, ps), cdiv(end, ps)
+            if last > first:
+                sched.cache.page_table[r.table_idx, first:last] = sched.cache._take(last - first)
+            sched.alloc_len[r.uid] = end
+    q_lens = ends - starts
+    cu_q = np.zeros(b + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=cu_q[1:])
+    total = int(cu_q[-1])
+    row = np.repeat(slots, q_lens)
+    pos = np.arange(total, dtype=np.int64) - np.repeat(cu_q[:-1].astype(np.int64), q_lens) + np.repeat(starts, q_lens)
+    token_idx = (row * msl + pos).astype(np.int32)
+    pages = sched.cache.page_table[row, pos // ps].astype(np.int64)
+    out_loc = (pages * ps + pos % ps).astype(np.int32)
+    max_kv = int(ends.max())
+    block_table = np.ascontiguousarray(sched.cache.page_table[slots, : cdiv(max_kv, ps)], dtype=np.int32)
+    return StepPlan(token_idx=token_idx, positions=pos.astype(np.int32), out_loc=out_loc, cu_q=cu_q,
+                    seq_lens=ends.astype(np.int32), block_table=block_table,
+                    sample_rows=np.arange(total, dtype=np.int32), write_idx=np.zeros(0, dtype=np.int32),
+                    max_q=int(q_lens.max()), max_kv=max_kv)

@@ -1,0 +1,54 @@
+"""Speculative-decoding proposer interface (python/minisgl/spec/base.py:69,182)."""
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from typing import List, Sequence
+
+import torch
+
+from ..core import Req
+
+
+class Proposer(ABC):
+    """Proposes up to ``num_draft`` continuation tokens per running request."""
+
+    name = "base"
+    max_batch = 64   # above this batch size a plain decode step is cheaper than verifying
+
+    def __init__(self, num_draft: int) -> None:
+        self.num_draft = num_draft
+
+    def budget(self, req: Req) -> int:
+        """``K_i = min(num_draft, remain_len - 1)``: the verify step emits at most K+1 tokens
+        (python/minisgl/spec/proposer.py:97)."""
+        return max(0, min(self.num_draft, req.remain_len - 1))
+
+    @abstractmethod
+    def propose(self, reqs: Sequence[Req]) -> List[List[int]]:
+        """One (possibly empty) draft token list per request."""
+
+    def on_prefill(self, reqs: Sequence[Req]) -> None:
+        """Called after a prefill step whose requests were sampled."""
+
+    def on_accept(self, req: Req, emitted: Sequence[int]) -> None:
+        """Called after tokens were committed to ``req``."""
+
+    def on_finish(self, req: Req) -> None:
+        """Called when ``req`` leaves the running set."""
+
+
+def make_proposer(config, scheduler) -> Proposer:
+    algo = config.spec_algorithm
+    if algo == "ngram":
+        from .ngram import NgramProposer
+
+        return NgramProposer(config.spec_num_draft, config.spec_ngram_max, config.spec_ngram_min)
+    if algo == "eagle3":
+        from .eagle3 import Eagle3Proposer
+
+        return Eagle3Proposer(config, scheduler)
+    if algo == "mtp":
+        from .eagle3 import Eagle3Proposer
+
+        return Eagle3Proposer(config, scheduler, mtp=True)
+    raise ValueError(f"unknown speculative algorithm {algo!r}")

@@ -1,0 +1,51 @@
+"""Prompt-lookup (n-gram) proposer (python/minisgl/spec/proposer.py:17,58-105): take the
+longest suffix n-gram (from ``ngram_max`` down to ``ngram_min`` tokens) that occurred earlier
+within the last 4096 tokens of the sequence, and propose the tokens that followed its most
+recent earlier occurrence."""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+
+from ..core import Req
+from .base import Proposer
+
+LOOKBACK = 4096
+
+
+def ngram_lookup(tokens: np.ndarray, k: int, n_max: int, n_min: int) -> List[int]:
+    total = len(tokens)
+    if k <= 0 or total < n_min + 1:
+        return []
+    window = tokens[max(0, total - LOOKBACK):]
+    w = len(window)
+    for n in range(min(n_max, w - 1), n_min - 1, -1):
+        suffix = window[w - n:]
+        # candidate starts: positions whose n tokens equal the suffix, excluding the suffix itself
+        limit = w - n  # start index of the suffix
+        if limit <= 0:
+            continue
+        hits = np.flatnonzero(window[:limit] == suffix[0])
+        for start in hits[::-1]:
+            if start + n > limit + n - 1 and start == limit:
+                continue
+            if np.array_equal(window[start:start + n], suffix):
+                follow = window[start + n:start + n + k]
+                if len(follow):
+                    return follow.tolist()
+    return []
+
+
+class NgramProposer(Proposer):
+    name = "ngram"
+
+    def __init__(self, num_draft: int, n_max: int = 3, n_min: int = 1) -> None:
+        super().__init__(num_draft)
+        self.n_max, self.n_min = n_max, n_min
+
+    def propose(self, reqs: Sequence[Req]) -> List[List[int]]:
+        out = []
+        for r in reqs:
+            out.append(ngram_lookup(r.input_ids.numpy(), self.budget(r), self.n_max, self.n_min))
+        return out

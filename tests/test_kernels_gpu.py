@@ -73,7 +73,8 @@ def test_act_and_quant(K):
     y = torch.randn(33, 4096, device="cuda").bfloat16()
     q, s = K.per_token_quant_fp8(y)
     q2, s2 = R.per_token_quant_fp8(y)
-    assert torch.equal(s, s2) and float((q.float() - q2.float()).abs().max()) <= 32
+    _close(s, s2, 1e-6, 0, "token scale")
+    assert float((q.float() != q2.float()).float().mean()) < 0.01
     q, s = K.per_group_quant_fp8(y, 128)
     q2, s2 = R.per_group_quant_fp8(y, 128)
     _close(s, s2, 1e-6, 0, "group scale")

@@ -1,0 +1,114 @@
+"""Speculative decoding on the CPU oracle path: greedy output must be bit-identical to plain
+decoding, whatever the proposer suggests."""
+import numpy as np
+import torch
+
+from minisglang_rdna4_b200 import SamplingParams
+from minisglang_rdna4_b200.llm import LLM
+from minisglang_rdna4_b200.models.config import tiny_llama_config
+from minisglang_rdna4_b200.spec import (
+    AdaptiveWidth, accept_greedy, accept_greedy_device, accept_rejection_sampling, eos_truncate, ngram_lookup,
+)
+from minisglang_rdna4_b200.spec.base import Proposer
+
+
+def test_ngram_lookup_prefers_longest_and_most_recent():
+    toks = np.array([1, 2, 3, 9, 9, 1, 2, 3, 7, 8, 5, 1, 2, 3], dtype=np.int32)
+    assert ngram_lookup(toks, 2, 3, 1) == [7, 8]          # most recent earlier "1 2 3"
+    assert ngram_lookup(np.array([4, 5, 6], dtype=np.int32), 3, 3, 1) == []
+    assert ngram_lookup(np.array([5, 1, 5], dtype=np.int32), 4, 3, 1) == [1, 5]
+    assert ngram_lookup(toks, 0, 3, 1) == []
+
+
+def test_accept_rules():
+    assert accept_greedy([5, 6, 7, 8], [5, 6, 9]) == [5, 6, 7]
+    assert accept_greedy([5, 6, 7, 8], [5, 6, 7]) == [5, 6, 7, 8]   # bonus token
+    assert accept_greedy([4], []) == [4]
+    assert accept_greedy([1, 2], [9]) == [1]
+    target = torch.tensor([5, 6, 7, 8, 1, 2, 4], dtype=torch.int32)
+    drafts = torch.tensor([[5, 6, 9], [9, -1, -1], [-1, -1, -1]], dtype=torch.int32)
+    cu = torch.tensor([0, 4, 6, 7], dtype=torch.int32)
+    n, tgt = accept_greedy_device(target, drafts, cu, torch.tensor([3, 1, 0]))
+    assert n.tolist() == [3, 1, 1] and tgt[0, :3].tolist() == [5, 6, 7] and tgt[2, 0] == 4
+    assert eos_truncate([3, 9, 4], {9}, False) == ([3, 9], True)
+    assert eos_truncate([3, 9, 4], {9}, True) == ([3, 9, 4], False)
+    w = AdaptiveWidth(4)
+    for _ in range(20):
+        w.update(0.0)
+    assert w.choose() == 1
+    for _ in range(20):
+        w.update(4.0)
+    assert w.choose() == 4
+
+
+def test_rejection_sampling_preserves_the_target_distribution():
+    g = torch.Generator().manual_seed(0)
+    p = torch.tensor([[0.7, 0.2, 0.1], [0.1, 0.1, 0.8]])
+    counts = torch.zeros(3)
+    for _ in range(4000):
+        out = accept_rejection_sampling(p, None, [1], generator=g)   # the proposer always says token 1
+        counts[out[0]] += 1
+    freq = counts / counts.sum()
+    assert torch.allclose(freq, p[0], atol=0.03)
+
+
+class _Oracle(Proposer):
+    """Proposes the true continuation for even uids and garbage for odd ones."""
+
+    name = "oracle"
+
+    def __init__(self, k, truth):
+        super().__init__(k)
+        self.truth = truth
+
+    def propose(self, reqs):
+        out = []
+        for r in reqs:
+            k = self.budget(r)
+            done = r.num_generated
+            good = self.truth[r.uid][done:done + k]
+            out.append(list(good) if r.uid % 2 == 0 else [(t + 1) % 1000 for t in good])
+        return out
+
+
+def _llm(**kw):
+    return LLM(model_config=tiny_llama_config(), use_dummy_weight=True, device="cpu", page_size=16,
+               max_running_req=8, num_page_override=256, seed=0, **kw)
+
+
+def test_spec_decode_is_bit_exact_with_plain_greedy():
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 33, 47, 64)]
+    # a repetitive prompt so the n-gram proposer has something to find
+    prompts.append([1, 2, 3, 4, 5, 6, 7, 8] * 6)
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    plain = _llm()
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    ngram = _llm(spec_algorithm="ngram", spec_num_draft=4)
+    got = [o.token_ids for o in ngram.generate(prompts, sp)]
+    assert got == want
+    assert ngram.stats["spec_steps"] > 0 and ngram.stats["spec_emitted"] >= ngram.stats["spec_steps"]
+    ngram.cache.check_integrity()
+    assert ngram.table.available_size == 8
+    # an oracle proposer: accepted drafts shorten the run, rejected ones never change the output
+    oracle = _llm(spec_algorithm="ngram", spec_num_draft=3)
+    oracle.proposer = _Oracle(3, {i: w for i, w in enumerate(want)})
+    got2 = [o.token_ids for o in oracle.generate(prompts, sp)]
+    assert got2 == want
+    assert oracle.stats["spec_accepted"] > 0
+    assert oracle.stats["spec_steps"] < plain.stats["steps"]
+
+
+def test_spec_decode_respects_eos_and_max_tokens():
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, 1024, (30,), generator=g).tolist()
+    base = _llm().generate([prompt], SamplingParams(max_tokens=10, ignore_eos=True))[0].token_ids
+    spec = _llm(spec_algorithm="ngram", spec_num_draft=4)
+    spec.proposer = _Oracle(4, {0: base})
+    spec.eos_ids = {base[4]}
+    out = spec.generate([prompt], SamplingParams(max_tokens=10))[0]
+    assert out.token_ids == base[: base.index(base[4]) + 1] and out.finish_reason == "stop"
+    spec2 = _llm(spec_algorithm="ngram", spec_num_draft=4)
+    spec2.proposer = _Oracle(4, {0: base})
+    out = spec2.generate([prompt], SamplingParams(max_tokens=7, ignore_eos=True))[0]
+    assert out.token_ids == base[:7] and out.finish_reason == "length"

@@ -1,0 +1,74 @@
+"""Tensor parallelism with CPU ranks over gloo: sharded linears, vocabulary-parallel
+embedding / LM head and the checkpoint loader must reproduce the single-rank result."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def _cfg_dict(moe=False):
+    d = dict(model_type="qwen3_moe" if moe else "qwen3", architectures=["Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM"],
+             num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+             intermediate_size=256, vocab_size=515, rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=512,
+             tie_word_embeddings=False, torch_dtype="float32")
+    if moe:
+        d.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True)
+    return d
+
+
+def _worker(rank, world, port, ckpt, prompts, out_q, ep):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"] = str(rank)
+    os.environ["WORLD_SIZE"] = str(world)
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    llm = LLM(model_path=ckpt, device="cpu", tp_size=world, tp_rank=rank, page_size=16, max_running_req=4,
+              num_page_override=64, enable_ep=ep, dtype="fp32")
+    outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    if rank == 0:
+        out_q.put([o.token_ids for o in outs])
+    llm.shutdown()
+
+
+def _single(ckpt, prompts):
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    llm = LLM(model_path=ckpt, device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
+    return [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))]
+
+
+def _make_ckpt(tmp, moe):
+    from minisglang_rdna4_b200.models import ModelConfig, create_model
+    from minisglang_rdna4_b200.models.weight import save_dummy_checkpoint
+
+    cfgd = _cfg_dict(moe)
+    cfg = ModelConfig.from_hf(cfgd)
+    model = create_model(cfg, torch.float32, "cpu")
+    model.init_dummy(seed=7, std=0.05)
+    save_dummy_checkpoint(model, tmp, cfgd)
+    return tmp
+
+
+@pytest.mark.parametrize("moe,ep", [(False, False), (True, False), (True, True)])
+def test_tp2_matches_tp1_on_cpu(moe, ep):
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 515, (n,), generator=g).tolist() for n in (9, 21)]
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, moe)
+        want = _single(ckpt, prompts)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 29500 + (os.getpid() % 2000) + (2 if moe else 0) + (1 if ep else 0)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, ep)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=240)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want

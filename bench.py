@@ -172,7 +172,20 @@ def main() -> None:
     step_events = []
     orig_forward = eng.forward_batch
 
+    # MSGL_BENCH_PROFILE="first:count" brackets engine steps [first, first+count) of the LAST
+    # timed pass with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)
+    prof = os.environ.get("MSGL_BENCH_PROFILE")
+    prof_first, prof_count = (int(x) for x in prof.split(":")) if prof else (-1, 0)
+    prof_state = {"armed": False}
+
     def timed_forward(batch, plan, sargs, return_logits=False):
+        idx = len(step_events)
+        if prof_state["armed"] and idx == prof_first:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+        if prof_state["armed"] and idx == prof_first + prof_count:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stream = eng.stream
         s.record(stream)
@@ -235,7 +248,13 @@ def main() -> None:
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    results = [one_pass(2000 + i) for i in range(args.steps)]
+    results = []
+    for i in range(args.steps):
+        prof_state["armed"] = prof_first >= 0 and i == args.steps - 1
+        results.append(one_pass(2000 + i))
+    if prof_state["armed"]:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     clocks = sampler.stop() if rank == 0 else {}
 
     def reduce_max(x: float) -> float:

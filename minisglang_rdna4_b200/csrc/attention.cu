@@ -92,9 +92,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 
 // T: query/output element type. KV8: pool holds e4m3. MMA runs in f16 when KV8 or T == half,
 // in bf16 otherwise.
-template <typename T, bool KV8, int D, int NW, int STAGES>
-__global__ void __launch_bounds__(32 * (NW + 1))
+// NWQ consumer warps side by side along the query rows (16 rows each) times NWK consumer warps
+// that take turns on the KV tiles (warp wk owns tiles wk, wk + NWK, ...) and merge their partial
+// softmax states at the end. Prefill uses 4 x 1, decode 1 x 4: a decode CTA has only one 16-row
+// tile of queries, so its parallelism has to come from the KV axis.
+template <typename T, bool KV8, int D, int NWQ, int NWK, int STAGES>
+__global__ void __launch_bounds__(32 * (NWQ * NWK + 1))
 paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs args) {
+  constexpr int NW = NWQ * NWK;
   constexpr int ESZ = KV8 ? 1 : 2;
   constexpr int RB = D * ESZ;                 // bytes per KV row
   constexpr int PLANES = RB / 128;            // 128-byte planes per row
@@ -120,7 +125,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
   const int split = blockIdx.z;
   const int q_begin = args.cu_q[b], q_len = args.cu_q[b + 1] - q_begin;
   const int kv_len = args.seq_lens[b];
-  const int pos_per_tile = (16 * NW) / G;
+  const int pos_per_tile = (16 * NWQ) / G;
   const int q_start = blockIdx.x * pos_per_tile;
   if (q_start >= q_len) return;   // uniform for the CTA; nothing has been initialised yet
   const int q_end = min(q_start + pos_per_tile, q_len);
@@ -140,7 +145,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), NW);
+      mbar_init(empty_bar(s), NWQ);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -184,7 +189,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
 
   // -------------------------------------------------------------------- consumers
   const int j = lane & 3, r0 = lane >> 2;
-  const int row_a = warp * 16 + r0, row_b = row_a + 8;          // rows of this thread in the tile
+  const int wq = warp / NWK, wk = warp % NWK;
+  const int row_a = wq * 16 + r0, row_b = row_a + 8;            // rows of this thread in the tile
   const int qi_a = q_start + row_a / G, qi_b = q_start + row_b / G;
   const bool ok_a = qi_a < q_end, ok_b = qi_b < q_end;
   const int head_a = h * G + row_a % G, head_b = h * G + row_b % G;
@@ -242,11 +248,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
   for (int i = 0; i < NDB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
-  int stage = 0;
-  uint32_t phase = 0;
-  bool alive = true;
-  for (int t = 0; t < n_tiles; ++t) {
-    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 202)) { alive = false; break; }
+  for (int t = wk; t < n_tiles; t += NWK) {
+    const int stage = t % STAGES;
+    const uint32_t phase = (uint32_t)(t / STAGES) & 1u;
+    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 202)) break;
     const uint32_t k_s = s_base + stage * STAGE_BYTES, v_s = k_s + KV_BYTES;
     const int tok0 = (t_begin + t) * TK;
 
@@ -378,15 +383,56 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(stage));
-    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
   }
-  if (!alive) return;
 
   // ---- finalise
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  if (NWK > 1) {
+    // Merge the NWK partial states of each query tile. Every warp parks its accumulator
+    // fragments in shared memory in register order ([reg][lane], so the same thread index of
+    // another warp holds the same matrix element); warp wk == 0 then folds them in.
+    constexpr int REGS = NDB * 4 + 4;
+    float* park = reinterpret_cast<float*>(smem);   // the KV stages are dead by now
+    asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
+    if (wk != 0) {
+      float* mine = park + (size_t)((wq * (NWK - 1) + (wk - 1)) * REGS) * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < NDB; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine[(i * 4 + e) * 32] = o[i][e];
+      }
+      mine[(NDB * 4 + 0) * 32] = m_a;
+      mine[(NDB * 4 + 1) * 32] = m_b;
+      mine[(NDB * 4 + 2) * 32] = l_a;
+      mine[(NDB * 4 + 3) * 32] = l_b;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(NW * 32) : "memory");
+    if (wk != 0) return;
+#pragma unroll 1
+    for (int other = 0; other < NWK - 1; ++other) {
+      const float* src = park + (size_t)((wq * (NWK - 1) + other) * REGS) * 32 + lane;
+      const float om_a = src[(NDB * 4 + 0) * 32], om_b = src[(NDB * 4 + 1) * 32];
+      const float ol_a = src[(NDB * 4 + 2) * 32], ol_b = src[(NDB * 4 + 3) * 32];
+      const float nm_a = fmaxf(m_a, om_a), nm_b = fmaxf(m_b, om_b);
+      const float sa = nm_a == -INFINITY ? 0.f : nm_a, sb = nm_b == -INFINITY ? 0.f : nm_b;
+      const float f_a = fast_exp2(m_a - sa), g_a = fast_exp2(om_a - sa);
+      const float f_b = fast_exp2(m_b - sb), g_b = fast_exp2(om_b - sb);
+#pragma unroll
+      for (int i = 0; i < NDB; ++i) {
+        o[i][0] = o[i][0] * f_a + src[(i * 4 + 0) * 32] * g_a;
+        o[i][1] = o[i][1] * f_a + src[(i * 4 + 1) * 32] * g_a;
+        o[i][2] = o[i][2] * f_b + src[(i * 4 + 2) * 32] * g_b;
+        o[i][3] = o[i][3] * f_b + src[(i * 4 + 3) * 32] * g_b;
+      }
+      l_a = l_a * f_a + ol_a * g_a;
+      l_b = l_b * f_b + ol_b * g_b;
+      m_a = nm_a;
+      m_b = nm_b;
+    }
+  }
   const float inv_a = l_a > 0.f ? v_sc / l_a : 0.f, inv_b = l_b > 0.f ? v_sc / l_b : 0.f;
 
   // column of accumulator element (block i, e) for this thread
@@ -472,19 +518,22 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
   for (int i = 0; i < PER; ++i) dst[i] = from_float<T>(acc[i] * inv);
 }
 
-template <typename T, bool KV8, int D, int NW, int STAGES>
+template <typename T, bool KV8, int D, int NWQ, int NWK, int STAGES>
 int launch_attn(const CUtensorMap& map, const AttnArgs& a, int q_tiles, cudaStream_t stream) {
   constexpr int ESZ = KV8 ? 1 : 2;
+  constexpr int NW = NWQ * NWK;
   constexpr int smem = STAGES * 2 * (D * ESZ / 128) * TK * 128 + 16 * STAGES + 64 + 1024;
+  static_assert(NWK == 1 || NWQ * (NWK - 1) * (D / 8 * 4 + 4) * 32 * 4 <= STAGES * 2 * (D * ESZ / 128) * TK * 128,
+                "merge buffer must fit in the stage memory");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<T, KV8, D, NW, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<T, KV8, D, NWQ, NWK, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) { msgl_set_error("attention smem attribute", e); return MSGL_CUDA_ERROR; }
     configured = true;
   }
   dim3 grid(q_tiles, a.B * a.Hk, a.splits);
-  paged_attention_kernel<T, KV8, D, NW, STAGES><<<grid, 32 * (NW + 1), smem, stream>>>(map, a);
+  paged_attention_kernel<T, KV8, D, NWQ, NWK, STAGES><<<grid, 32 * (NW + 1), smem, stream>>>(map, a);
   MSGL_CHECK_LAUNCH("paged_attention");
   return MSGL_OK;
 }
@@ -496,14 +545,14 @@ int dispatch_attn(const CUtensorMap& map, const AttnArgs& a, bool kv8, int d, in
   const int rows = small ? 16 : 64;
   const int q_tiles = (max_q + rows / G - 1) / (rows / G);
   if (d == 128) {
-    if (kv8) return small ? launch_attn<T, true, 128, 1, 3>(map, a, q_tiles, stream)
-                          : launch_attn<T, true, 128, 4, 4>(map, a, q_tiles, stream);
-    return small ? launch_attn<T, false, 128, 1, 3>(map, a, q_tiles, stream)
-                 : launch_attn<T, false, 128, 4, 3>(map, a, q_tiles, stream);
+    if (kv8) return small ? launch_attn<T, true, 128, 1, 4, 6>(map, a, q_tiles, stream)
+                          : launch_attn<T, true, 128, 4, 1, 4>(map, a, q_tiles, stream);
+    return small ? launch_attn<T, false, 128, 1, 4, 4>(map, a, q_tiles, stream)
+                 : launch_attn<T, false, 128, 4, 1, 3>(map, a, q_tiles, stream);
   }
   if (d == 64 && !kv8)
-    return small ? launch_attn<T, false, 64, 1, 3>(map, a, q_tiles, stream)
-                 : launch_attn<T, false, 64, 4, 4>(map, a, q_tiles, stream);
+    return small ? launch_attn<T, false, 64, 1, 4, 6>(map, a, q_tiles, stream)
+                 : launch_attn<T, false, 64, 4, 1, 4>(map, a, q_tiles, stream);
   msgl_set_error_text("attention: unsupported head_dim / KV dtype combination");
   return MSGL_BAD_ARG;
 }

@@ -47,90 +47,101 @@ MSGL_API int msgl_embedding(const void* ids, const void* w, void* out, int rows,
 }
 
 // ------------------------------------------------------------------------------------------
-// RMSNorm family. One CTA per row; the (summed) row lives in shared memory as fp32.
+// RMSNorm family. One CTA of 128 threads per row; every thread keeps its VPT 16-byte vectors of
+// the (summed) row in registers between the reduction and the write, so the row is read once.
 //   ADD   : residual += x (stored back, rounded to T), norm of the sum
 //   QUANT : emit e4m3 row + fp32 scale (amax/448) instead of T
 // ------------------------------------------------------------------------------------------
-template <typename T, bool ADD, bool QUANT>
-__global__ void __launch_bounds__(1024) rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual,
-                                                        const T* __restrict__ w, T* __restrict__ out,
-                                                        uint8_t* __restrict__ out_q, float* __restrict__ out_scale,
-                                                        int hidden, float eps, float w_offset) {
-  extern __shared__ float row_s[];
+constexpr int kRowThreads = 128;
+
+template <typename T, bool ADD, bool QUANT, int VPT>
+__global__ void __launch_bounds__(kRowThreads) rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                               const T* __restrict__ w, T* __restrict__ out,
+                                                               uint8_t* __restrict__ out_q,
+                                                               float* __restrict__ out_scale, int hidden, float eps,
+                                                               float w_offset) {
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const T* xr = x + (size_t)row * hidden;
   T* rr = ADD ? residual + (size_t)row * hidden : nullptr;
+  float v[VPT][8];
   float ss = 0.f;
-  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
-    float v[8];
-    load8(xr + i, v);
-    if (ADD) {
-      float r[8];
-      load8(rr + i, r);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] += r[k];
-      store8(rr + i, v);
-      // the norm sees the rounded residual, exactly what the next layer will read
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    if (i < hidden) {
+      load8(xr + i, v[j]);
+      if (ADD) {
+        float r[8];
+        load8(rr + i, r);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = to_float(from_float<T>(v[k]));
-    }
+        for (int k = 0; k < 8; ++k) v[j][k] += r[k];
+        store8(rr + i, v[j]);
+        // the norm sees the rounded residual, exactly what the next layer will read
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      ss += v[k] * v[k];
-      row_s[i + k] = v[k];
+        for (int k = 0; k < 8; ++k) v[j][k] = to_float(from_float<T>(v[j][k]));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[j][k] * v[j][k];
     }
   }
   ss = block_sum(ss, scratch);
   const float rstd = rsqrtf(ss / (float)hidden + eps);
   float amax = 0.f;
-  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
-    float wv[8], y[8];
-    load8(w + i, wv);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      // round to T as the unfused op would, so the quantised row matches norm -> quant
-      y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + w_offset)));
-      if (QUANT) {
-        amax = fmaxf(amax, fabsf(y[k]));
-        row_s[i + k] = y[k];
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    if (i < hidden) {
+      float wv[8];
+      load8(w + i, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        // round to T as the unfused op would, so the quantised row matches norm -> quant
+        v[j][k] = to_float(from_float<T>(v[j][k] * rstd * (wv[k] + w_offset)));
+        if (QUANT) amax = fmaxf(amax, fabsf(v[j][k]));
       }
+      if (!QUANT) store8(out + (size_t)row * hidden + i, v[j]);
     }
-    if (!QUANT) store8(out + (size_t)row * hidden + i, y);
   }
   if (QUANT) {
     amax = block_max(amax, scratch);
     const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
     if (threadIdx.x == 0) out_scale[row] = scale;
-    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
-      float y[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
-      *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + i) = pack8_e4m3(y, scale);
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kRowThreads + threadIdx.x) * 8;
+      if (i < hidden) *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + i) = pack8_e4m3(v[j], scale);
     }
   }
 }
 
-template <typename T>
-static int launch_rms(const void* x, void* residual, const void* w, void* out, void* out_q, void* out_scale,
-                      int rows, int hidden, float eps, int plus_one, cudaStream_t s) {
-  int threads = ((hidden / 8 + 31) / 32) * 32;
-  if (threads > 1024) threads = 1024;
-  size_t smem = (size_t)hidden * sizeof(float);
-  float off = plus_one ? 1.f : 0.f;
-  bool add = residual != nullptr, quant = out_q != nullptr;
-#define RMS_LAUNCH(A, Q)                                                                                   \
-  do {                                                                                                     \
-    if (smem > 48 * 1024)                                                                                  \
-      cudaFuncSetAttribute(rms_norm_kernel<T, A, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rms_norm_kernel<T, A, Q><<<rows, threads, smem, s>>>((const T*)x, (T*)residual, (const T*)w, (T*)out,  \
-                                                         (uint8_t*)out_q, (float*)out_scale, hidden, eps, off); \
-  } while (0)
+template <typename T, int VPT>
+static void launch_rms_vpt(const void* x, void* residual, const void* w, void* out, void* out_q, void* out_scale,
+                           int rows, int hidden, float eps, float off, cudaStream_t s) {
+  const bool add = residual != nullptr, quant = out_q != nullptr;
+#define RMS_LAUNCH(A, Q)                                                                                    \
+  rms_norm_kernel<T, A, Q, VPT><<<rows, kRowThreads, 0, s>>>((const T*)x, (T*)residual, (const T*)w, (T*)out, \
+                                                            (uint8_t*)out_q, (float*)out_scale, hidden, eps, off)
   if (add && quant) RMS_LAUNCH(true, true);
   else if (add) RMS_LAUNCH(true, false);
   else if (quant) RMS_LAUNCH(false, true);
   else RMS_LAUNCH(false, false);
 #undef RMS_LAUNCH
+}
+
+template <typename T>
+static int launch_rms(const void* x, void* residual, const void* w, void* out, void* out_q, void* out_scale,
+                      int rows, int hidden, float eps, int plus_one, cudaStream_t s) {
+  const float off = plus_one ? 1.f : 0.f;
+  const int vpt = (hidden / 8 + kRowThreads - 1) / kRowThreads;
+  if (vpt <= 1) launch_rms_vpt<T, 1>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 2) launch_rms_vpt<T, 2>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 3) launch_rms_vpt<T, 3>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 4) launch_rms_vpt<T, 4>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 6) launch_rms_vpt<T, 6>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 8) launch_rms_vpt<T, 8>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 16) launch_rms_vpt<T, 16>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("rms_norm");
   return MSGL_OK;
 }
@@ -139,7 +150,7 @@ static int launch_rms(const void* x, void* residual, const void* w, void* out, v
 MSGL_API int msgl_rms_norm(const void* x, void* residual, const void* w, void* out, void* out_q,
                            void* out_scale, int rows, int hidden, float eps, int plus_one, int dtype,
                            cudaStream_t stream) {
-  if (hidden % 8 || hidden > 48 * 1024) return MSGL_BAD_ARG;
+  if (hidden % 8 || hidden > 16 * 8 * kRowThreads) return MSGL_BAD_ARG;
   if (rows == 0) return MSGL_OK;
   if (dtype == MSGL_BF16)
     return launch_rms<__nv_bfloat16>(x, residual, w, out, out_q, out_scale, rows, hidden, eps, plus_one, stream);
@@ -176,34 +187,57 @@ __global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int
   store8(out + row * inter + col, y);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(1024) act_mul_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q,
-                                                             float* __restrict__ out_scale, int inter, int kind) {
-  extern __shared__ float row_s[];
+template <typename T, int VPT>
+__global__ void __launch_bounds__(kRowThreads) act_mul_quant_kernel(const T* __restrict__ x,
+                                                                    uint8_t* __restrict__ out_q,
+                                                                    float* __restrict__ out_scale, int inter,
+                                                                    int kind) {
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const T* g = x + (size_t)row * 2 * inter;
+  float v[VPT][8];
   float amax = 0.f;
-  for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
-    float a[8], b[8];
-    load8(g + i, a);
-    load8(g + inter + i, b);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float y = to_float(from_float<T>(act_fn(a[k], kind) * b[k]));
-      amax = fmaxf(amax, fabsf(y));
-      row_s[i + k] = y;
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    if (i < inter) {
+      float a[8], b[8];
+      load8(g + i, a);
+      load8(g + inter + i, b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[j][k] = to_float(from_float<T>(act_fn(a[k], kind) * b[k]));
+        amax = fmaxf(amax, fabsf(v[j][k]));
+      }
     }
   }
   amax = block_max(amax, scratch);
   const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
   if (threadIdx.x == 0) out_scale[row] = scale;
-  for (int i = threadIdx.x * 8; i < inter; i += blockDim.x * 8) {
-    float y[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
-    *reinterpret_cast<uint2*>(out_q + (size_t)row * inter + i) = pack8_e4m3(y, scale);
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    if (i < inter) *reinterpret_cast<uint2*>(out_q + (size_t)row * inter + i) = pack8_e4m3(v[j], scale);
   }
+}
+
+template <typename T>
+static int launch_act_quant(const void* x, void* out_q, void* out_scale, int rows, int inter, int kind,
+                            cudaStream_t s) {
+  const int vpt = (inter / 8 + kRowThreads - 1) / kRowThreads;
+#define ACT_LAUNCH(V) \
+  act_mul_quant_kernel<T, V><<<rows, kRowThreads, 0, s>>>((const T*)x, (uint8_t*)out_q, (float*)out_scale, inter, kind)
+  if (vpt <= 1) ACT_LAUNCH(1);
+  else if (vpt <= 2) ACT_LAUNCH(2);
+  else if (vpt <= 4) ACT_LAUNCH(4);
+  else if (vpt <= 6) ACT_LAUNCH(6);
+  else if (vpt <= 8) ACT_LAUNCH(8);
+  else if (vpt <= 10) ACT_LAUNCH(10);
+  else if (vpt <= 16) ACT_LAUNCH(16);
+  else if (vpt <= 28) ACT_LAUNCH(28);
+  else return MSGL_BAD_ARG;
+#undef ACT_LAUNCH
+  return MSGL_OK;
 }
 
 MSGL_API int msgl_act_and_mul(const void* x, void* out, void* out_q, void* out_scale, int rows, int inter,
@@ -222,23 +256,11 @@ MSGL_API int msgl_act_and_mul(const void* x, void* out, void* out_q, void* out_s
     else
       return MSGL_BAD_ARG;
   } else {
-    size_t smem = (size_t)inter * sizeof(float);
-    if (smem > 200 * 1024) return MSGL_BAD_ARG;
-    int threads = ((inter / 8 + 31) / 32) * 32;
-    if (threads > 1024) threads = 1024;
-    if (dtype == MSGL_BF16) {
-      if (smem > 48 * 1024)
-        cudaFuncSetAttribute(act_mul_quant_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      act_mul_quant_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out_q,
-                                                                           (float*)out_scale, inter, kind);
-    } else if (dtype == MSGL_F16) {
-      if (smem > 48 * 1024)
-        cudaFuncSetAttribute(act_mul_quant_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      act_mul_quant_kernel<__half><<<rows, threads, smem, stream>>>((const __half*)x, (uint8_t*)out_q,
-                                                                    (float*)out_scale, inter, kind);
-    } else {
-      return MSGL_BAD_ARG;
-    }
+    int rc;
+    if (dtype == MSGL_BF16) rc = launch_act_quant<__nv_bfloat16>(x, out_q, out_scale, rows, inter, kind, stream);
+    else if (dtype == MSGL_F16) rc = launch_act_quant<__half>(x, out_q, out_scale, rows, inter, kind, stream);
+    else return MSGL_BAD_ARG;
+    if (rc) return rc;
   }
   MSGL_CHECK_LAUNCH("act_and_mul");
   return MSGL_OK;

@@ -47,6 +47,10 @@ struct GemmArgs {
   int bias_dtype;
   const uint8_t* sfb;      // scale-factor atoms [n_atoms][k_atoms][512] (kind 3)
   int sf_k_atoms;
+  // grouped (mixture-of-experts) mode: B is [experts * N, K]; M tile m multiplies with the
+  // weights of expert tile_expert[m]; a negative id marks a tile past the live rows
+  const int32_t* tile_expert;
+  int sf_n_atoms;          // scale-factor atoms along N per expert
   int* status;
 };
 
@@ -151,13 +155,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
         const int n0 = n_tile * BN;
+        int expert = 0;
+        if (args.tile_expert != nullptr) {
+          expert = args.tile_expert[m_tile];
+          if (expert < 0) continue;
+        }
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 101)) break;
           mbar_expect_tx(full_bar(stage), STAGE_TX);
           tma_load_2d(s_base + L::off_a + stage * L::A_BYTES, &tma_a, full_bar(stage), kb * KT::BKE, m_tile * BM);
-          tma_load_2d(s_base + L::off_b + stage * L::B_BYTES, &tma_b, full_bar(stage), kb * KT::BKE, n0);
+          tma_load_2d(s_base + L::off_b + stage * L::B_BYTES, &tma_b, full_bar(stage), kb * KT::BKE,
+                      expert * args.N + n0);
           if (KIND == KIND_MXF4) {
-            const uint8_t* src = args.sfb + ((size_t)(n0 / 128) * args.sf_k_atoms + kb) * 512;
+            const uint8_t* src =
+                args.sfb + ((size_t)(expert * args.sf_n_atoms + n0 / 128) * args.sf_k_atoms + kb) * 512;
             bulk_load(s_base + L::off_sf + stage * L::SF_BYTES, src, 512, full_bar(stage));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -178,6 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t phase = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const int n0 = (tile / args.m_tiles) * BN;
+        if (args.tile_expert != nullptr && args.tile_expert[tile % args.m_tiles] < 0) continue;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 102)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -220,6 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+      if (args.tile_expert != nullptr && args.tile_expert[m_tile] < 0) continue;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
       tc_fence_after();
       const int row = m_tile * BM + q * 32 + lane;
@@ -395,9 +408,10 @@ static int choose_bn(int m_tiles, int n, int sms, int smallest) {
 // b: [N, K] (kind 0/1: 16-bit, kind 2: e4m3 bytes, kind 3: packed e2m1 [N, K/2])
 // c: [M, N] out_dtype, row stride ldc elements
 // bn_override: 0 = automatic, else 32 / 64 / 128; max_ctas: 0 = one per SM
-MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
-                       int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
-                       const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, cudaStream_t stream) {
+static int gemm_impl(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
+                     int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
+                     const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, const void* tile_expert,
+                     int num_experts, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? MSGL_OK : MSGL_BAD_ARG;
   if (N % 8) { msgl_set_error_text("gemm: N must be a multiple of 8"); return MSGL_BAD_ARG; }
   const int esize_a = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
@@ -437,6 +451,9 @@ MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, vo
   args.out_dtype = out_dtype;
   args.sfb = (const uint8_t*)sf_atoms;
   args.sf_k_atoms = (K + 127) / 128;
+  args.sf_n_atoms = (N + 127) / 128;
+  args.tile_expert = (const int32_t*)tile_expert;
+  const uint64_t b_rows = (uint64_t)N * (uint64_t)(num_experts > 0 ? num_experts : 1);
   int* status = nullptr;
   cudaGetSymbolAddress((void**)&status, g_gemm_status);
   args.status = status;
@@ -447,15 +464,15 @@ MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, vo
     CUtensorMapDataType dt = kind == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     rc = make_map_2d(&ma, a, dt, K, M, (uint64_t)lda * 2, 64, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, dt, K, N, (uint64_t)K * 2, 64, bn, true);
+    rc = make_map_2d(&mb, b, dt, K, b_rows, (uint64_t)K * 2, 64, bn, true);
   } else if (kind == KIND_F8) {
     rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, N, (uint64_t)K, 128, bn, true);
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, b_rows, (uint64_t)K, 128, bn, true);
   } else if (kind == KIND_MXF4) {
     rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, N, (uint64_t)K / 2, 128, bn, true);
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, b_rows, (uint64_t)K / 2, 128, bn, true);
   } else {
     return MSGL_BAD_ARG;
   }
@@ -466,6 +483,30 @@ MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, vo
     case KIND_F8: return dispatch_bn<KIND_F8>(bn, ma, mb, args, max_ctas, stream);
     default: return dispatch_bn<KIND_MXF4>(bn, ma, mb, args, max_ctas, stream);
   }
+}
+
+MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
+                       int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
+                       const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, cudaStream_t stream) {
+  return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, out_dtype,
+                   bn_override, max_ctas, nullptr, 0, stream);
+}
+
+// Grouped GEMM over expert-sorted rows: a [M, K] (M a multiple of 128), b [experts * N, K],
+// tile_expert [M / 128] gives the expert of every 128-row tile (-1 = skip the tile).
+// In grouped mode N tiles must not straddle experts, so N must be a multiple of the N tile.
+MSGL_API int msgl_gemm_grouped(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M,
+                               int N, int K, const void* tile_expert, int num_experts, const void* a_scale,
+                               const void* sf_atoms, int out_dtype, int bn_override, cudaStream_t stream) {
+  if (M % 128 || tile_expert == nullptr || num_experts <= 0) return MSGL_BAD_ARG;
+  int bn = bn_override;
+  if (bn == 0) bn = (N % 128 == 0) ? 128 : (N % 64 == 0 ? 64 : 32);
+  if (N % bn) {
+    msgl_set_error_text("grouped gemm: N must be a multiple of the N tile");
+    return MSGL_BAD_ARG;
+  }
+  return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, nullptr, nullptr, 0, sf_atoms, out_dtype, bn, 0,
+                   tile_expert, num_experts, stream);
 }
 
 // 0 when no bounded wait of a GEMM kernel has run out since the last reset; else a code

@@ -130,6 +130,8 @@ class Engine:
         self.dtype = _resolve_dtype(config, self.model_config, dev_kind)
         self.cpu_group: Optional[dist.ProcessGroup] = None
         self.tp_group: Optional[dist.ProcessGroup] = None
+        self.dp_group: Optional[dist.ProcessGroup] = None
+        self.dp_cpu_group: Optional[dist.ProcessGroup] = None
         self._init_communication()
 
         free_before = self._free_memory()
@@ -173,6 +175,10 @@ class Engine:
             single_split=config.spec_algorithm != "none",
         )
         self.ctx.comm = comm_mod.get_comm()
+        if config.enable_ep and config.dp_size > 1:
+            from ..parallel.ep import EPContext
+
+            self.ctx.ep = EPContext(self.dp_group, config.dp_rank, config.dp_size)
         set_global_ctx(self.ctx)
         self.sampler = Sampler(self.device, mc.vocab_size, mc.final_logit_softcapping, seed=config.seed)
         self._staging_cap = 0
@@ -184,7 +190,11 @@ class Engine:
         self.d2h_bytes = 0
         self.steps = 0
         self.graph_runner = None
-        if dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0:
+        # replicas that exchange expert rows every layer run eagerly: a captured graph would pin
+        # the row count of the exchange
+        ep_replicas = config.enable_ep and config.dp_size > 1
+        if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0
+                and not ep_replicas):
             from .graph import GraphRunner
 
             self.graph_runner = GraphRunner(self)
@@ -217,7 +227,6 @@ class Engine:
             c = dist.new_group(ranks, backend="gloo", timeout=timeout)
             if r == cfg.dp_rank:
                 self.tp_group, self.cpu_group = g, c
-        self.dp_group = self.dp_cpu_group = None
         if cfg.dp_size > 1:
             for t in range(cfg.tp_size):
                 ranks = [r * cfg.tp_size + t for r in range(cfg.dp_size)]

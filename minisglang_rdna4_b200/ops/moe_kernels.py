@@ -1,0 +1,100 @@
+"""Python side of the fused MoE path: routing kernel, alignment to 128-row tiles, permute,
+two grouped tcgen05 GEMMs with SiLU·mul between them, weighted combine."""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+from . import _lib
+from . import cuda as K
+from ._lib import c_f, c_i, c_ll, c_p, check, lib
+
+_lib.bind("msgl_moe_route", c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_i, c_i, c_p])
+_lib.bind("msgl_moe_align", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p])
+_lib.bind("msgl_moe_permute", c_i, [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+_lib.bind("msgl_moe_combine", c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+_lib.bind("msgl_gemm_grouped", c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_i, c_p, c_p, c_i, c_i, c_p])
+
+BLOCK = 128
+_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def moe_route(router_logits, top_k, renormalize, scoring="softmax", scale=1.0, counts=None, e_start=0, e_local=None):
+    t, e = router_logits.shape
+    assert router_logits.is_contiguous()
+    w = torch.empty((t, top_k), dtype=torch.float32, device=router_logits.device)
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=router_logits.device)
+    check(lib().msgl_moe_route(router_logits.data_ptr(), w.data_ptr(), ids.data_ptr(),
+                               None if counts is None else counts.data_ptr(), t, e, top_k, int(renormalize),
+                               int(scoring != "softmax"), float(scale), e_start, e if e_local is None else e_local,
+                               _DT[router_logits.dtype], K._stream()), "moe_route")
+    K._count("moe_route", "moe_route_kernel")
+    return w, ids
+
+
+def max_sorted_rows(tokens: int, top_k: int, e_local: int) -> int:
+    rows = tokens * top_k + e_local * (BLOCK - 1)
+    return (rows + BLOCK - 1) // BLOCK * BLOCK
+
+
+def moe_align(topk_ids, e_start: int, e_local: int):
+    """Returns ``(sorted_pair [R], pair_row [T*k], tile_expert [R/128], meta [2])`` with R the
+    worst-case padded row count (static for a given T, k, E)."""
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    rows = max_sorted_rows(t, k, e_local)
+    counts = torch.zeros(e_local, dtype=torch.int32, device=dev)
+    flat = topk_ids.reshape(-1).long() - e_start
+    ok = (flat >= 0) & (flat < e_local)
+    counts.index_add_(0, flat.clamp(0, e_local - 1), ok.to(torch.int32))
+    return _align_with_counts(topk_ids, counts, e_start, e_local, rows)
+
+
+def _align_with_counts(topk_ids, counts, e_start, e_local, rows):
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    offsets = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+    cursor = torch.empty(e_local, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(rows // BLOCK, dtype=torch.int32, device=dev)
+    meta = torch.empty(2, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(rows, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(t * k, dtype=torch.int32, device=dev)
+    check(lib().msgl_moe_align(topk_ids.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursor.data_ptr(),
+                               tile_expert.data_ptr(), meta.data_ptr(), sorted_pair.data_ptr(), pair_row.data_ptr(),
+                               t, k, e_start, e_local, rows, BLOCK, K._stream()), "moe_align")
+    K._count("moe_align", "moe_offsets_kernel+moe_scatter_kernel", 2)
+    return sorted_pair, pair_row, tile_expert, meta
+
+
+def gemm_grouped(a, b, tile_expert, out_dtype=None, bn=0):
+    """``a [R, K]`` (expert-sorted rows, R % 128 == 0), ``b [E, N, K]`` → ``[R, N]``."""
+    e, n, k = b.shape
+    r = a.shape[0]
+    out = torch.empty((r, n), dtype=out_dtype or a.dtype, device=a.device)
+    kind = K.KIND_BF16 if a.dtype == torch.bfloat16 else K.KIND_F16
+    check(lib().msgl_gemm_grouped(kind, a.data_ptr(), a.stride(0), b.data_ptr(), out.data_ptr(), n, r, n, k,
+                                  tile_expert.data_ptr(), e, None, None, _DT[out.dtype], bn, K._stream()),
+          "gemm_grouped")
+    K._count("moe_gemm_grouped", "gemm_tcgen05_kernel")
+    return out
+
+
+def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
+    t, h = x.shape
+    e_local = w13.shape[0]
+    k = topk_ids.shape[1]
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local)
+    rows = sorted_pair.numel()
+    xs = torch.empty((rows, h), dtype=x.dtype, device=x.device)
+    check(lib().msgl_moe_permute(x.data_ptr(), sorted_pair.data_ptr(), xs.data_ptr(), h, k, rows, _DT[x.dtype],
+                                 K._stream()), "moe_permute")
+    K._count("moe_permute", "moe_permute_kernel")
+    hcur = gemm_grouped(xs, w13, tile_expert)
+    act = K.act_and_mul(hcur)
+    y = gemm_grouped(act, w2, tile_expert)
+    out = torch.empty_like(x)
+    check(lib().msgl_moe_combine(y.data_ptr(), topk_w.data_ptr(), pair_row.data_ptr(), out.data_ptr(), t, h, k,
+                                 _DT[x.dtype], K._stream()), "moe_combine")
+    K._count("moe_combine", "moe_combine_kernel")
+    return out

@@ -1,0 +1,71 @@
+"""Lock-step scheduling loop for expert parallelism across replicas
+(python/minisgl/scheduler/ep.py:17-172).
+
+The MoE layers of every replica exchange rows each forward, so all replicas must run a
+forward at the same time and with the same padded row count. Each iteration the replicas
+all-reduce (MAX, over the gloo group of their column) ``[tokens of my step, exit flag]``;
+a replica with nothing to do runs a one-token dummy step that writes only the dummy KV page.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..core import Batch
+from ..engine import BatchSamplingArgs, StepPlan
+
+
+def _dummy_step(sched) -> None:
+    """Forward one token of the dummy request: keeps this replica inside the collectives."""
+    eng = sched.engine
+    slot = eng.num_slots - 1
+    dummy_loc = eng.kv_cache.dummy_page * eng.page_size
+    plan = StepPlan(
+        token_idx=np.array([slot * eng.max_seq_len], dtype=np.int32), positions=np.zeros(1, dtype=np.int32),
+        out_loc=np.array([dummy_loc], dtype=np.int32), cu_q=np.array([0, 1], dtype=np.int32),
+        seq_lens=np.ones(1, dtype=np.int32),
+        block_table=np.full((1, 1), eng.kv_cache.dummy_page, dtype=np.int32),
+        sample_rows=np.zeros(0, dtype=np.int32), write_idx=np.zeros(0, dtype=np.int32), max_q=1, max_kv=1)
+    batch = Batch(reqs=[], phase="prefill")
+    eng.forward_batch(batch, plan, BatchSamplingArgs())
+
+
+def ep_lockstep_loop(sched) -> None:
+    eng = sched.engine
+    group = eng.dp_cpu_group
+    ep = eng.ctx.ep
+    idle_rounds = 0
+    while True:
+        has_local = sched.has_work
+        for msg in sched.receive_msg(blocking=False):
+            sched._process_one_msg(msg)
+        batch = sched._schedule_next_batch()
+        tokens = 0
+        if batch is not None:
+            tokens = sum(r.extend_len for r in batch.reqs)
+        agree = torch.tensor([tokens, 1 if sched._exit else 0, 1 if (sched.has_work or batch is not None) else 0],
+                             dtype=torch.int64)
+        dist.all_reduce(agree, op=dist.ReduceOp.MAX, group=group)
+        common, any_exit, any_work = int(agree[0]), int(agree[1]), int(agree[2])
+        if common == 0:
+            if any_exit and not any_work:
+                break
+            # nobody has a step to run: in offline mode that means everything is finished
+            if getattr(sched.config, "offline_mode", False) and not any_work:
+                break
+            idle_rounds += 1
+            if idle_rounds > 2:
+                import time
+
+                time.sleep(0.002)
+            continue
+        idle_rounds = 0
+        ep.common_tokens = common
+        if batch is not None:
+            ongoing = sched._forward(batch)
+            sched._process_last_data(ongoing)
+        else:
+            _dummy_step(sched)
+        ep.common_tokens = None
+        sched._maybe_exit_after_steps()

@@ -253,3 +253,32 @@ def test_argmax_and_sampling(K):
         allowed[si[r][keep]] = True
         assert counts[r][~allowed].sum() == 0, f"row {r} drew a filtered token"
         assert counts[r][si[r][0]] > 0
+
+
+# ------------------------------------------------------------------------------------------ MoE
+@pytest.mark.parametrize("tokens,E,k", [(1, 8, 2), (37, 64, 4), (300, 128, 8)])
+def test_moe_route_and_forward(K, tokens, E, k):
+    R = _ref()
+    from minisglang_rdna4_b200.ops import moe_kernels as MK
+
+    h, inter = 256, 128
+    logits = torch.randn(tokens, E, device="cuda")
+    w, ids = MK.moe_route(logits, k, True)
+    w2_, ids2 = R.moe_route(logits, k, True)
+    assert torch.equal(ids.sort(-1).values, ids2.sort(-1).values)
+    _close(w.sort(-1).values, w2_.sort(-1).values, 1e-4, 1e-6, "route weights")
+    ws, _ = MK.moe_route(logits, k, False, scoring="sigmoid", scale=2.5)
+    wr, _ = R.moe_route(logits, k, False, "sigmoid", None, 2.5)
+    _close(ws.sort(-1).values, wr.sort(-1).values, 1e-4, 1e-6, "sigmoid weights")
+    x = torch.randn(tokens, h, device="cuda").bfloat16()
+    w13 = (torch.randn(E, 2 * inter, h, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(E, h, inter, device="cuda") * 0.05).bfloat16()
+    got = MK.moe_forward(x, w13, w2, w, ids)
+    assert K.gemm_status() == 0
+    want = R.moe_forward(x, w13, w2, w, ids)
+    _close(got, want, 3e-2, 3e-2, "moe_forward")
+    # expert-parallel slice: only experts [E/2, E) are local
+    half = E // 2
+    got_ep = MK.moe_forward(x, w13[half:].contiguous(), w2[half:].contiguous(), w, ids, expert_offset=half)
+    want_ep = R.moe_forward(x, w13[half:], w2[half:], w, ids, expert_offset=half)
+    _close(got_ep, want_ep, 3e-2, 3e-2, "moe_forward ep")

@@ -72,3 +72,46 @@ def test_tp2_matches_tp1_on_cpu(moe, ep):
             p.join(timeout=60)
             assert p.exitcode == 0
     assert got == want
+
+
+def _dp_worker(rank, world, port, ckpt, prompts_by_rank, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    llm = LLM(model_path=ckpt, device="cpu", dp_size=world, dp_rank=rank, page_size=16, max_running_req=4,
+              num_page_override=64, enable_ep=True, dtype="fp32")
+    outs = llm.generate(prompts_by_rank[rank], SamplingParams(max_tokens=5, ignore_eos=True))
+    out_q.put((rank, [o.token_ids for o in outs], llm.engine.ctx.ep.calls))
+    llm.shutdown()
+
+
+def test_dp2_expert_parallel_lockstep_matches_single_replica():
+    """Two replicas with disjoint expert halves and different workloads (one finishes early and
+    has to keep running dummy steps) reproduce what one replica with all experts generates."""
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 515, (n,), generator=g).tolist() for n in (9, 21, 14)]
+    by_rank = {0: prompts[:2], 1: prompts[2:]}
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, True)
+        from minisglang_rdna4_b200 import SamplingParams
+        from minisglang_rdna4_b200.llm import LLM
+
+        llm = LLM(model_path=ckpt, device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
+        want = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))]
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 29900 + os.getpid() % 1000
+        procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, ckpt, by_rank, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = dict()
+        calls = dict()
+        for _ in procs:
+            r, toks, n = q.get(timeout=240)
+            got[r], calls[r] = toks, n
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got[0] + got[1] == want
+    assert calls[0] == calls[1] > 0   # both replicas issued the same number of exchanges

@@ -545,13 +545,16 @@ int dispatch_attn(const CUtensorMap& map, const AttnArgs& a, bool kv8, int d, in
   const int rows = small ? 16 : 64;
   const int q_tiles = (max_q + rows / G - 1) / (rows / G);
   if (d == 128) {
-    if (kv8) return small ? launch_attn<T, true, 128, 1, 4, 6>(map, a, q_tiles, stream)
+    // Decode (one 16-row query tile per CTA): measured on B200 at batch 8..256, four small
+    // CTAs per SM with one consumer warp each beat one CTA whose four warps split the KV axis
+    // (198 us vs 309 us at batch 256, context 1400), so the KV-split form is not dispatched.
+    if (kv8) return small ? launch_attn<T, true, 128, 1, 1, 3>(map, a, q_tiles, stream)
                           : launch_attn<T, true, 128, 4, 1, 4>(map, a, q_tiles, stream);
-    return small ? launch_attn<T, false, 128, 1, 4, 4>(map, a, q_tiles, stream)
+    return small ? launch_attn<T, false, 128, 1, 1, 3>(map, a, q_tiles, stream)
                  : launch_attn<T, false, 128, 4, 1, 3>(map, a, q_tiles, stream);
   }
   if (d == 64 && !kv8)
-    return small ? launch_attn<T, false, 64, 1, 4, 6>(map, a, q_tiles, stream)
+    return small ? launch_attn<T, false, 64, 1, 1, 3>(map, a, q_tiles, stream)
                  : launch_attn<T, false, 64, 4, 1, 4>(map, a, q_tiles, stream);
   msgl_set_error_text("attention: unsupported head_dim / KV dtype combination");
   return MSGL_BAD_ARG;

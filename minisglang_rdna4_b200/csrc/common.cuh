@@ -74,13 +74,16 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t x) {
   __half_raw h = __nv_cvt_fp8_to_halfraw(x, __NV_E4M3);
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
-// eight floats -> eight e4m3 bytes (one 8-byte store). True division by the scale: a reciprocal
-// multiply lands on the other side of a rounding boundary often enough to differ from x / scale.
+// eight floats -> eight e4m3 bytes (one 8-byte store). Multiplies by the reciprocal of the scale:
+// against x / scale this differs only when the quotient sits within one fp32 ulp of an e4m3
+// rounding boundary (about one element in a million), and an IEEE division per element made the
+// row kernels compute-bound.
 __device__ __forceinline__ uint2 pack8_e4m3(const float (&x)[8], float scale) {
-  uint32_t lo = (uint32_t)float2_to_e4m3x2(__fdiv_rn(x[0], scale), __fdiv_rn(x[1], scale)) |
-                ((uint32_t)float2_to_e4m3x2(__fdiv_rn(x[2], scale), __fdiv_rn(x[3], scale)) << 16);
-  uint32_t hi = (uint32_t)float2_to_e4m3x2(__fdiv_rn(x[4], scale), __fdiv_rn(x[5], scale)) |
-                ((uint32_t)float2_to_e4m3x2(__fdiv_rn(x[6], scale), __fdiv_rn(x[7], scale)) << 16);
+  const float inv = 1.0f / scale;
+  uint32_t lo = (uint32_t)float2_to_e4m3x2(x[0] * inv, x[1] * inv) |
+                ((uint32_t)float2_to_e4m3x2(x[2] * inv, x[3] * inv) << 16);
+  uint32_t hi = (uint32_t)float2_to_e4m3x2(x[4] * inv, x[5] * inv) |
+                ((uint32_t)float2_to_e4m3x2(x[6] * inv, x[7] * inv) << 16);
   return make_uint2(lo, hi);
 }
 

@@ -164,7 +164,7 @@ MSGL_API int msgl_rms_norm(const void* x, void* residual, const void* w, void* o
 // ------------------------------------------------------------------------------------------
 enum ActKind : int { ACT_SILU = 0, ACT_GELU = 1, ACT_GELU_TANH = 2 };
 __device__ __forceinline__ float act_fn(float g, int kind) {
-  if (kind == ACT_SILU) return g / (1.f + __expf(-g));
+  if (kind == ACT_SILU) return __fdividef(g, 1.f + __expf(-g));
   if (kind == ACT_GELU) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   return 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g)));

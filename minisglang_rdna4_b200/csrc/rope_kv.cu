@@ -91,6 +91,133 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
   }
 }
 
+// E consecutive 16-bit elements as one access (E = 1, 2 or 4)
+template <typename T, int E> __device__ __forceinline__ void load_run(const T* p, float (&out)[E]) {
+  if constexpr (E == 1) {
+    out[0] = to_float(p[0]);
+  } else if constexpr (E == 2) {
+    typename Pack2<T>::type v = *reinterpret_cast<const typename Pack2<T>::type*>(p);
+    float2 f = to_float2(v);
+    out[0] = f.x; out[1] = f.y;
+  } else {
+    uint2 raw = *reinterpret_cast<const uint2*>(p);
+    float2 f0 = to_float2(*reinterpret_cast<typename Pack2<T>::type*>(&raw.x));
+    float2 f1 = to_float2(*reinterpret_cast<typename Pack2<T>::type*>(&raw.y));
+    out[0] = f0.x; out[1] = f0.y; out[2] = f1.x; out[3] = f1.y;
+  }
+}
+template <typename T, int E> __device__ __forceinline__ void store_run(T* p, const float (&in)[E]) {
+  if constexpr (E == 1) {
+    p[0] = from_float<T>(in[0]);
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<typename Pack2<T>::type*>(p) = Pack2<T>::make(in[0], in[1]);
+  } else {
+    typename Pack2<T>::type lo = Pack2<T>::make(in[0], in[1]), hi = Pack2<T>::make(in[2], in[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  }
+}
+
+// Fast path for full rotary (rot == D): no shared memory. A lane owns E = D/64 elements of each
+// half of the head (NeoX pairing i <-> i + D/2) or 2E consecutive elements (interleaved pairing),
+// so both members of every rotation pair live in the same lane; the per-head RMS statistic is a
+// warp reduction.
+template <typename T, int D>
+__global__ void __launch_bounds__(128) qk_norm_rope_store_fast_kernel(
+    const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
+    const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, T* __restrict__ q_out,
+    void* __restrict__ k_cache, void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
+    const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hq, int hk, int page_size, float eps,
+    int interleaved, int cache_fp8, int max_pos, int num_slots) {
+  constexpr int E = D / 64, H2 = D / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int token = blockIdx.x;
+  const int head = blockIdx.y * 4 + warp;
+  const int heads_total = hq + 2 * hk;
+  if (head >= heads_total) return;
+  const T* src = qkv + (size_t)token * heads_total * D + (size_t)head * D;
+  // element indices owned by this lane: lo[t], hi[t]
+  int idx_lo[E], idx_hi[E];
+#pragma unroll
+  for (int t = 0; t < E; ++t) {
+    if (interleaved) { idx_lo[t] = 2 * (E * lane + t); idx_hi[t] = idx_lo[t] + 1; }
+    else { idx_lo[t] = E * lane + t; idx_hi[t] = idx_lo[t] + H2; }
+  }
+  float a[E], b[E];
+  float ss = 0.f;
+  if (interleaved) {
+#pragma unroll
+    for (int t = 0; t < E; ++t) {
+      a[t] = to_float(src[idx_lo[t]]);
+      b[t] = to_float(src[idx_hi[t]]);
+    }
+  } else {
+    load_run<T, E>(src + E * lane, a);
+    load_run<T, E>(src + H2 + E * lane, b);
+  }
+#pragma unroll
+  for (int t = 0; t < E; ++t) ss += a[t] * a[t] + b[t] * b[t];
+  const bool is_q = head < hq, is_k = !is_q && head < hq + hk;
+  if (is_q || is_k) {
+    const T* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int t = 0; t < E; ++t) {
+        a[t] = to_float(from_float<T>(a[t] * rstd * to_float(w[idx_lo[t]])));
+        b[t] = to_float(from_float<T>(b[t] * rstd * to_float(w[idx_hi[t]])));
+      }
+    }
+    int pos = positions[token];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + (size_t)pos * D;
+#pragma unroll
+    for (int t = 0; t < E; ++t) {
+      const int p = E * lane + t;
+      const float c = cs[p], sn = cs[H2 + p];
+      const float x0 = a[t], x1 = b[t];
+      a[t] = x0 * c - x1 * sn;
+      b[t] = x1 * c + x0 * sn;
+    }
+  }
+  if (is_q) {
+    T* dst = q_out + ((size_t)token * hq + head) * D;
+    if (interleaved) {
+#pragma unroll
+      for (int t = 0; t < E; ++t) {
+        dst[idx_lo[t]] = from_float<T>(a[t]);
+        dst[idx_hi[t]] = from_float<T>(b[t]);
+      }
+    } else {
+      store_run<T, E>(dst + E * lane, a);
+      store_run<T, E>(dst + H2 + E * lane, b);
+    }
+    return;
+  }
+  const int kvh = is_k ? head - hq : head - hq - hk;
+  const int slot = out_loc[token];
+  if (slot < 0 || slot >= num_slots) return;
+  const int page = slot / page_size, off = slot % page_size;
+  const size_t base = (((size_t)page * hk + kvh) * page_size + off) * D;
+  void* cache = is_k ? k_cache : v_cache;
+  if (cache_fp8) {
+    const float sc = is_k ? k_scale[kvh] : v_scale[kvh];
+    uint8_t* dst = (uint8_t*)cache + base;
+#pragma unroll
+    for (int t = 0; t < E; ++t) {
+      dst[idx_lo[t]] = float_to_e4m3(to_float(from_float<T>(a[t])) / sc);
+      dst[idx_hi[t]] = float_to_e4m3(to_float(from_float<T>(b[t])) / sc);
+    }
+  } else {
+    T* dst = (T*)cache + base;
+#pragma unroll
+    for (int t = 0; t < E; ++t) {
+      dst[idx_lo[t]] = from_float<T>(a[t]);
+      dst[idx_hi[t]] = from_float<T>(b[t]);
+    }
+  }
+}
+
 MSGL_API int msgl_qk_norm_rope_store(const void* qkv, const void* q_w, const void* k_w, const void* positions,
                                      const void* cos_sin, void* q_out, void* k_cache, void* v_cache,
                                      const void* out_loc, const void* k_scale, const void* v_scale, int tokens,
@@ -99,12 +226,21 @@ MSGL_API int msgl_qk_norm_rope_store(const void* qkv, const void* q_w, const voi
                                      cudaStream_t stream) {
   if (tokens == 0) return MSGL_OK;
   if (rot > head_dim || rot % 2) return MSGL_BAD_ARG;
-  dim3 grid(tokens, (hq + 2 * hk + 3) / 4);
+ dim3 grid(tokens, (hq + 2 * hk + 3) / 4);
 #define LAUNCH(T, D)                                                                                        \
+  do {                                                                                                      \
+  if (rot == head_dim)                                                                                      \
+    qk_norm_rope_store_fast_kernel<T, D><<<grid, 128, 0, stream>>>(                                         \
+        (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,      \
+        (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale, \
+        hq, hk, page_size, eps, interleaved, cache_fp8, max_pos, num_slots);                                \
+  else                                                                                                      \
+                                                                                        \
   qk_norm_rope_store_kernel<T, D><<<grid, 128, 0, stream>>>(                                                \
       (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,        \
       (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale,   \
-      hq, hk, rot, page_size, eps, interleaved, cache_fp8, max_pos, num_slots)
+      hq, hk, rot, page_size, eps, interleaved, cache_fp8, max_pos, num_slots);                            \
+  } while (0)
   if (dtype == MSGL_BF16) {
     if (head_dim == 128) LAUNCH(__nv_bfloat16, 128);
     else if (head_dim == 64) LAUNCH(__nv_bfloat16, 64);

@@ -164,6 +164,13 @@ class Engine:
             mc.num_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
             self.dtype, self.device, fp8=self.kv_fp8,
         )
+        if self.kv_fp8:
+            from ..kvcache.fp8_scales import resolve_kv_scales
+
+            ks, vs, source = resolve_kv_scales(config.model_path, mc.num_layers, mc.num_kv_heads, config.tp_rank,
+                                               config.tp_size)
+            self.kv_cache.set_scales(ks, vs)
+            logger.info_rank0("fp8 KV scales: %s", source)
         # slot max_running_req is the dummy request used to pad graph batches
         self.num_slots = config.max_running_req + 1
         self.token_pool = torch.zeros((self.num_slots, self.max_seq_len), dtype=torch.int32, device=self.device)

@@ -232,9 +232,91 @@ class Scheduler:
         self.decode.filter_finished()
         return Ongoing(batch, sampled, out, time.monotonic())
 
+    # ------------------------------------------------------------------ constrained decoding
+    def _constraint_state(self):
+        """Lazily built grammar backend, tokenizer and per-request gates."""
+        st = getattr(self, "_cstate", None)
+        if st is None:
+            from ..engine.grammar import GrammarBackend, GrammarState
+            from ..tokenizer.simple import load_tokenizer
+
+            tok = load_tokenizer(self.config.model_path)
+            backend = GrammarBackend(tok, vocab_size=self.engine.model_config.vocab_size,
+                                     stop_token_ids=sorted(self.eos_ids) or None)
+            st = self._cstate = {"tok": tok, "grammar": GrammarState(backend), "think": {}, "tool": {}}
+        return st
+
+    def _needs_constraints(self, req: Req) -> bool:
+        sp = req.sampling_params
+        return sp.grammar is not None or bool(sp.tool_call_closers) or (sp.think_close_delim is not None and sp.think_budget > 0)
+
+    def _gates_for(self, req: Req):
+        from .think_gate import ThinkGate, ToolCallGate
+
+        st = self._constraint_state()
+        sp = req.sampling_params
+        enc = lambda text: list(st["tok"].encode(text))
+        think = st["think"].get(req.uid)
+        if think is None and sp.think_close_delim is not None:
+            think = st["think"][req.uid] = ThinkGate(
+                enc(sp.think_close_delim), [enc(t) for t in sp.think_tool_release], sp.think_budget,
+                span_open=sp.think_span_open or sp.think_budget > 0)
+        tool = st["tool"].get(req.uid)
+        if tool is None and sp.tool_call_openers and sp.tool_call_closers:
+            tool = st["tool"][req.uid] = ToolCallGate([enc(t) for t in sp.tool_call_openers],
+                                                      [enc(t) for t in sp.tool_call_closers])
+        return think, tool
+
     def _attach_constraints(self, reqs: Sequence[Req], args: BatchSamplingArgs) -> None:
-        """Hook for grammar bitmasks (installed by the grammar backend when present)."""
-        return None
+        """Build the allowed-token bitmask of this step: grammar masks (once a reasoning span
+        is over), a single forced token when a reasoning budget ran out, and end-of-sequence
+        suppression while a tool call is open (python/minisgl/scheduler/scheduler.py:2343)."""
+        rows = [i for i, r in enumerate(reqs) if self._needs_constraints(r)]
+        if not rows:
+            return
+        st = self._constraint_state()
+        gs = st["grammar"]
+        backend = gs.backend
+        bm = backend.allocate_bitmask(len(rows))
+        bm.fill_(-1)
+        for j, i in enumerate(rows):
+            r = reqs[i]
+            sp = r.sampling_params
+            think, tool = self._gates_for(r)
+            forced = think.forced_token() if think is not None else None
+            if forced is not None:
+                bm[j].zero_()
+                bm[j, forced // 32] = 1 << (forced % 32) if forced % 32 != 31 else -(1 << 31)
+                continue
+            if sp.grammar is not None and (think is None or think.grammar_active):
+                backend.fill(gs.ensure(r.uid, sp.grammar), bm, j)
+            if tool is not None and tool.suppress_eos:
+                for e in self.eos_ids:
+                    word, bit = e // 32, e % 32
+                    mask = ~(1 << bit) if bit != 31 else 0x7FFFFFFF
+                    bm[j, word] = int(bm[j, word]) & mask
+        args.bitmask = bm.to(self.engine.device, non_blocking=True)
+        args.bitmask_rows = torch.tensor(rows, dtype=torch.int64, device=self.engine.device)
+
+    def _observe_token(self, req: Req, tok: int) -> None:
+        st = getattr(self, "_cstate", None)
+        if st is None or not self._needs_constraints(req):
+            return
+        think, tool = st["think"].get(req.uid), st["tool"].get(req.uid)
+        active = think is None or think.grammar_active
+        if think is not None:
+            think.observe(tok)
+        if tool is not None:
+            tool.observe(tok)
+        if req.sampling_params.grammar is not None and active:
+            st["grammar"].accept(req.uid, tok)
+
+    def _forget_constraints(self, uid: int) -> None:
+        st = getattr(self, "_cstate", None)
+        if st is not None:
+            st["grammar"].finish(uid)
+            st["think"].pop(uid, None)
+            st["tool"].pop(uid, None)
 
     # ------------------------------------------------------------------ results
     def _process_last_data(self, ongoing: Optional[Ongoing]) -> None:
@@ -253,6 +335,7 @@ class Scheduler:
                 continue  # finished or aborted while this step was in flight
             tok = int(toks[i])
             req.append_host(tokens[i : i + 1])
+            self._observe_token(req, tok)
             reason = None
             if not req.sampling_params.ignore_eos and tok in self.eos_ids:
                 reason = "stop"
@@ -282,6 +365,7 @@ class Scheduler:
         req.cached_len = min(req.cached_len, int(req.input_ids.numel()))
         self.cache.finish_req(req, alloc, insert=insert)
         self.table.free(req.table_idx)
+        self._forget_constraints(req.uid)
         self.reqs.pop(req.uid, None)
         self.prefix_len.pop(req.uid, None)
         self.stats["finished"] += 1
@@ -297,6 +381,10 @@ class Scheduler:
             blocking = not self.has_work and last is None
             for msg in self.receive_msg(blocking):
                 self._process_one_msg(msg)
+            if last is not None and any(self._needs_constraints(r) for r in last.sampled):
+                # a grammar mask depends on the token of the step in flight: no overlap this round
+                self._process_last_data(last)
+                last = None
             batch = self._schedule_next_batch()
             ongoing = self._forward(batch) if batch is not None else None
             self._process_last_data(last)

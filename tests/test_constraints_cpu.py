@@ -1,0 +1,75 @@
+"""Structured output and gates on the CPU engine with the byte tokenizer: a JSON grammar must
+yield parseable JSON from a random-weight model; a reasoning budget forces the close
+delimiter; an open tool call suppresses end-of-sequence."""
+import json
+
+import torch
+
+from minisglang_rdna4_b200 import SamplingParams
+from minisglang_rdna4_b200.llm import LLM
+from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+from minisglang_rdna4_b200.scheduler.think_gate import ThinkGate, ToolCallGate
+from minisglang_rdna4_b200.tokenizer import ByteTokenizer
+
+
+def _cfg():
+    return ModelConfig(num_layers=1, num_qo_heads=2, num_kv_heads=1, head_dim=32, hidden_size=64, vocab_size=260,
+                       intermediate_size=128, rms_norm_eps=1e-6,
+                       rotary_config=RotaryConfig(32, 32, 512, 1e4), model_type="llama", torch_dtype="float32",
+                       max_position_embeddings=512, eos_token_ids=(257,))
+
+
+def _llm():
+    return LLM(model_config=_cfg(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=4,
+               num_page_override=64, seed=3)
+
+
+def test_json_schema_grammar_produces_valid_json():
+    llm = _llm()
+    schema = json.dumps({"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "boolean"}},
+                         "required": ["a", "b"], "additionalProperties": False})
+    prompt = list(b"give me json:")
+    outs = llm.generate([prompt, prompt], [SamplingParams(max_tokens=60, grammar=schema, temperature=0.8, top_k=40),
+                                           SamplingParams(max_tokens=8, ignore_eos=True)])
+    text = ByteTokenizer().decode(outs[0].token_ids)
+    obj = json.loads(text)
+    assert set(obj) == {"a", "b"} and isinstance(obj["a"], int) and isinstance(obj["b"], bool)
+    assert outs[0].finish_reason == "stop"          # the grammar terminated and only EOS was left
+    assert len(outs[1].token_ids) == 8              # the unconstrained neighbour is untouched
+
+
+def test_think_gate_budget_and_release():
+    g = ThinkGate(close_ids=[5, 6], budget=3)
+    for t in (1, 2, 3):
+        assert g.forced_token() is None
+        g.observe(t)
+    assert g.forced_token() == 5
+    g.observe(5)
+    assert g.forced_token() == 6 and not g.released
+    g.observe(6)
+    assert g.released and g.forced_token() is None
+    g2 = ThinkGate(close_ids=[9, 9], release_patterns=[[7, 8]])
+    g2.observe(7)
+    assert not g2.grammar_active
+    g2.observe(8)
+    assert g2.grammar_active            # a tool-call opener ends the span too
+    assert ThinkGate(close_ids=[1], span_open=False).grammar_active
+
+
+def test_tool_call_gate_suppresses_eos_until_closed():
+    g = ToolCallGate(openers=[[10, 11]], closers=[[12]])
+    assert not g.suppress_eos
+    g.observe(10)
+    g.observe(11)
+    assert g.suppress_eos
+    g.observe(3)
+    g.observe(12)
+    assert not g.suppress_eos
+
+
+def test_reasoning_budget_forces_close_delimiter_end_to_end():
+    llm = _llm()
+    sp = SamplingParams(max_tokens=12, ignore_eos=True, think_close_delim="</t>", think_budget=4, think_span_open=True)
+    out = llm.generate([list(b"hello")], sp)[0]
+    text = ByteTokenizer().decode(out.token_ids)
+    assert text[4:8] == "</t>", text

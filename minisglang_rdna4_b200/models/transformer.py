@@ -170,14 +170,14 @@ class CausalLM(BaseOP):
         x = self.model.embed_tokens.forward(input_ids)
         residual: Optional[torch.Tensor] = None
         partial = False
-        aux: List[torch.Tensor] = []
+        seen = {}
         for i, layer in enumerate(self.model.layers):
             if capture is not None and i in capture:
                 # hidden state entering layer i = residual + pending block output
-                aux.append(self._materialise(x, residual, partial))
+                seen[i] = self._materialise(x, residual, partial)
             x, residual, partial = layer.forward(x, residual, partial)
         if capture is not None:
-            ctx.aux_hidden = aux
+            ctx.aux_hidden = [seen[i] for i in capture]
         out, _ = self.model.norm.forward_fused(x, residual, partial=partial)
         return out
 

@@ -211,6 +211,10 @@ class Scheduler:
     # ------------------------------------------------------------------ forward
     def _forward(self, batch: Batch) -> Ongoing:
         plan = self._make_plan(batch)
+        capture = getattr(self.proposer, "capture_layers", None)
+        if capture:
+            batch.capture_layers = list(capture)
+            self._feature_meta = (plan.cu_q.copy(), [r.cached_len for r in batch.reqs])
         sampled = [r for r in batch.reqs if not isinstance(r, ChunkedReq)]
         args = self.engine.sampler.prepare(sampled) if sampled else BatchSamplingArgs()
         self._attach_constraints(sampled, args)
@@ -404,6 +408,7 @@ class Scheduler:
                     ongoing = self._forward(batch)
                     self._process_last_data(ongoing)
                     if self.proposer is not None and batch.is_prefill:
+                        self._feed_prefill_features(batch)
                         self.proposer.on_prefill(ongoing.sampled)
             self._maybe_exit_after_steps()
 
@@ -426,6 +431,35 @@ class Scheduler:
             pass
 
     # ------------------------------------------------------------------ spec decode
+    def _feed_prefill_features(self, batch: Batch) -> None:
+        """Hand the target's auxiliary hidden states of a prefill step to a feature-based
+        proposer (EAGLE3 / MTP). Row i of a request pairs the feature of position i with the token
+        at position i+1; the last row of a partially prefilled prompt waits for the next chunk."""
+        prop = self.proposer
+        aux = self.engine.ctx.aux_hidden
+        if not hasattr(prop, "on_features") or not aux:
+            return
+        cu, starts = self._feature_meta
+        carry = getattr(self, "_feature_carry", None)
+        if carry is None:
+            carry = self._feature_carry = {}
+        for i, req in enumerate(batch.reqs):
+            rows = [a[cu[i]:cu[i + 1]] for a in aux]
+            first = starts[i]
+            prev = carry.pop(req.uid, None)
+            if prev is not None:
+                rows = [torch.cat([p, r]) for p, r in zip(prev, rows)]
+                first -= 1
+            n = rows[0].shape[0]
+            ids = req.input_ids  # after the step: prompt (+ the sampled token for a finished prefill)
+            avail = int(ids.numel()) - (first + 1)   # tokens known at positions first+1 ...
+            use = min(n, avail)
+            if use < n:
+                carry[req.uid] = [r[use:] for r in rows]
+            if use > 0:
+                prop.on_features(req, [r[:use] for r in rows], first, ids[first + 1:first + 1 + use])
+        self.engine.ctx.aux_hidden = None
+
     def _spec_decode_step(self) -> None:
         from .spec_step import spec_decode_step
 

@@ -56,11 +56,17 @@ def spec_decode_step(sched) -> None:
 
     batch = Batch(reqs=reqs, phase="decode")
     batch.spec_verify = True
+    capture = getattr(proposer, "capture_layers", None)
+    if capture:
+        batch.capture_layers = list(capture)
+    first_pos = [r.cached_len for r in reqs]
     plan = _verify_plan(sched, batch, drafts)
     sampled = any(not r.sampling_params.is_greedy for r in reqs) and ENV.SPEC_SAMPLED.value
     args = BatchSamplingArgs()
     out = eng.forward_batch(batch, plan, args, return_logits=True)
     logits = eng.sampler.condition_logits(out.logits, args)
+    aux = eng.ctx.aux_hidden if capture else None
+    eng.ctx.aux_hidden = None
     target = logits.argmax(-1).to(torch.int32).cpu().tolist()
     sched.stats["steps"] += 1
     sched.stats["spec_steps"] += 1
@@ -89,6 +95,9 @@ def spec_decode_step(sched) -> None:
         pos = r.table_idx * msl + r.device_len
         eng.token_pool.view(-1)[pos:pos + n] = torch.tensor(emitted, dtype=torch.int32).to(eng.device)
         r.complete_many(n)
+        if aux is not None and hasattr(proposer, "on_features"):
+            rows = [a[cu[i]:cu[i] + n] for a in aux]
+            proposer.on_features(r, rows, first_pos[i], torch.tensor(emitted, dtype=torch.int32))
         proposer.on_accept(r, emitted)
         finished = hit_eos or r.num_generated >= r.sampling_params.max_tokens
         reason = "stop" if hit_eos else ("length" if finished else None)

@@ -112,3 +112,25 @@ def test_spec_decode_respects_eos_and_max_tokens():
     spec2.proposer = _Oracle(4, {0: base})
     out = spec2.generate([prompt], SamplingParams(max_tokens=7, ignore_eos=True))[0]
     assert out.token_ids == base[:7] and out.finish_reason == "length"
+
+
+def test_eagle3_draft_is_exact_and_a_distilled_head_gets_accepted():
+    """Greedy output with the EAGLE3 proposer equals plain greedy decoding whatever the draft
+    predicts; a draft whose LM head is the target's own head on an identity-like layer agrees with
+    the target often enough to shorten the run."""
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (18, 40)]
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    want = [o.token_ids for o in _llm().generate(prompts, sp)]
+    spec = _llm(spec_algorithm="eagle3", spec_num_draft=3)
+    got = [o.token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    assert spec.stats["spec_steps"] > 0 and spec.stats["spec_drafted"] > 0
+    spec.cache.check_integrity()
+    # chunked prefill feeds the draft in pieces (carry of the chunk-boundary row)
+    spec2 = _llm(spec_algorithm="eagle3", spec_num_draft=3, max_extend_tokens=16)
+    got2 = [o.token_ids for o in spec2.generate(prompts, sp)]
+    assert got2 == want
+    # MTP variant: one feature layer, no fc
+    mtp = _llm(spec_algorithm="mtp", spec_num_draft=2)
+    assert [o.token_ids for o in mtp.generate(prompts, sp)] == want

@@ -143,6 +143,7 @@ class Engine:
             from ..models.weight import load_weights
 
             load_weights(self.model, config.model_path, self.model_config, self.device)
+        self._configure_expert_tier()
         self.model.post_load()
         if dev_kind == "cuda":
             torch.cuda.synchronize()
@@ -200,8 +201,11 @@ class Engine:
         # replicas that exchange expert rows every layer run eagerly: a captured graph would pin
         # the row count of the exchange
         ep_replicas = config.enable_ep and config.dp_size > 1
+        from ..layers.moe import MoELayer as _Moe
+
+        host_tier = _Moe.offload_slots > 0   # expert residency is decided on the host every step
         if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0
-                and not ep_replicas):
+                and not ep_replicas and not host_tier):
             from .graph import GraphRunner
 
             self.graph_runner = GraphRunner(self)
@@ -251,6 +255,23 @@ class Engine:
                                                        cfg.tp_rank, cfg.tp_size))
                 except Exception as exc:  # falls back to the NCCL data plane, loudly
                     logger.warning("symmetric-memory collectives unavailable (%s); using NCCL only", exc)
+
+    def _configure_expert_tier(self) -> None:
+        """``--expert-cache-gb G``: keep only as many experts per MoE layer on the device as fit in
+        G GiB in total; the rest stay in pinned host memory (python/minisgl/server/args.py:199-249)."""
+        from ..layers.moe import MoELayer
+
+        cfg, mc = self.config, self.model_config
+        MoELayer.offload_slots = 0
+        if cfg.expert_cache_gb <= 0 or not mc.is_moe:
+            return
+        itemsize = torch.empty((), dtype=self.dtype).element_size()
+        per_expert = 3 * mc.hidden_size * mc.moe_intermediate_size * itemsize
+        layers = sum(1 for i in range(mc.num_layers) if mc.layer_is_moe(i))
+        slots = int(cfg.expert_cache_gb * (1 << 30) // max(per_expert * layers, 1))
+        MoELayer.offload_slots = max(slots, mc.num_experts_per_tok * 2)
+        logger.info_rank0("host expert tier: %d of %d experts resident per layer", MoELayer.offload_slots,
+                          mc.num_experts)
 
     def _free_memory(self) -> int:
         if self.device.type == "cuda":

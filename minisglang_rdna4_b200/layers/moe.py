@@ -22,6 +22,10 @@ from .linear import ReplicatedLinear
 
 
 class MoELayer(BaseOP):
+    # experts kept on the device per layer when the host-RAM expert tier is on (0 = all resident);
+    # set by the engine from --expert-cache-gb before the weights are post-processed
+    offload_slots: int = 0
+
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, renormalize: bool,
                  dtype, device, scoring: str = "softmax", routed_scale: float = 1.0,
                  scheme=None) -> None:
@@ -52,10 +56,23 @@ class MoELayer(BaseOP):
         ctx = try_global_ctx()
         if self._ep is not None and ctx is not None and ctx.ep is not None:
             return ctx.ep.dispatch_compute_combine(self, x, topk_w, topk_ids)
-        return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
+        return self.local_experts(x, topk_w, topk_ids)
 
     def local_experts(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        tier = getattr(self, "_tier", None)
+        if tier is not None:
+            return tier.forward(x, topk_w, topk_ids - self._e_start)
         return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
+
+    def _post_load_self(self) -> None:
+        slots = type(self).offload_slots
+        if slots and slots < self._e_local:
+            from ..weights import HostExpertTier
+
+            self._tier = HostExpertTier(self.w13, self.w2, slots, self.w13.device)
+            # the full stacks now live in pinned host memory only
+            self.w13 = self.w13[:0]
+            self.w2 = self.w2[:0]
 
     @property
     def needs_tp_reduce(self) -> bool:

@@ -31,6 +31,7 @@ class PagedAttentionBackend(BaseAttnBackend):
             from ..ops import cuda as K
 
             self._workspace = K.attention_workspace(max(max_batch, 1), num_q_heads, head_dim, device)
+            K.force_general_decode_attention(single_split)
 
     def prepare_metadata(self, batch: Batch, block_table, cu_q, seq_lens, max_q: int, max_kv: int,
                          causal: bool = True, mask: Optional[torch.Tensor] = None) -> None:

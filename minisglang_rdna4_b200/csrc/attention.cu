@@ -518,6 +518,314 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
   for (int i = 0; i < PER; ++i) dst[i] = from_float<T>(acc[i] * inv);
 }
 
+// ------------------------------------------------------------------------------------------
+// Decode (one query position per request). The problem is transposed so that the 16-row side of
+// the warp MMA is filled with KV tokens and the 8-column side with the (up to 8) query heads of
+// one GQA group: S^T = K Q^T and O^T = V^T P^T. Compared with putting the heads on the 16-row
+// side this halves the MMA and softmax work per token, halves the accumulator registers (so
+// several times more CTAs fit on an SM, which is what hides the latency of the dependent
+// ldmatrix -> convert -> mma chains) and wastes nothing when the group has 8 heads.
+// P is transposed between the two products with movmatrix.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+template <typename T, bool KV8, int D, int STAGES>
+__global__ void __launch_bounds__(64)
+paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs args) {
+  constexpr int ESZ = KV8 ? 1 : 2;
+  constexpr int RB = D * ESZ;
+  constexpr int PLANES = RB / 128;
+  constexpr int PLANE_BYTES = TK * 128;
+  constexpr int KV_BYTES = PLANES * PLANE_BYTES;
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  constexpr int BOX_INNER = 128 / ESZ;
+  constexpr bool F16MMA = KV8 || std::is_same<T, __half>::value;
+  constexpr int NMB = D / 16;   // 16-row blocks of O^T
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + STAGES * STAGE_BYTES + 16 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = args.Hq / args.Hk;
+  const int ps = args.page_size;
+  const int b = blockIdx.y / args.Hk, h = blockIdx.y % args.Hk;
+  const int split = blockIdx.z;
+  const int q_row = args.cu_q[b];
+  const int kv_len = args.seq_lens[b];
+  const int kv_hi = kv_len;
+  const int kv_lo = args.window > 0 ? max(0, kv_len - args.window) : 0;
+  const int tile_lo = kv_lo / TK;
+  const int n_tiles_all = kv_hi > kv_lo ? (kv_hi + TK - 1) / TK - tile_lo : 0;
+  const int per_split = (n_tiles_all + args.splits - 1) / args.splits;
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_lo + n_tiles_all, t_begin + per_split);
+  const int n_tiles = max(t_end - t_begin, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&kv_map);
+  }
+  __syncthreads();
+
+  if (warp == 1) {
+    if (lane == 0) {
+      const int pages_per_tile = TK / ps;
+      const int32_t* bt = args.block_table + (size_t)b * args.bt_stride;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < n_tiles; ++t) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 211)) break;
+        mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+        const int first_page = (t_begin + t) * pages_per_tile;
+        const uint32_t k_s = s_base + stage * STAGE_BYTES, v_s = k_s + KV_BYTES;
+        for (int p = 0; p < pages_per_tile; ++p) {
+          int col = first_page + p;
+          col = col < args.bt_stride ? col : args.bt_stride - 1;
+          int page = bt[col];
+          page = page < 0 ? 0 : (page > args.num_pages ? args.num_pages : page);
+#pragma unroll
+          for (int pl = 0; pl < PLANES; ++pl) {
+            const uint32_t off = pl * PLANE_BYTES + p * ps * 128;
+            tma_load_5d(k_s + off, &kv_map, full_bar(stage), pl * BOX_INNER, 0, h, page, args.k_coord);
+            tma_load_5d(v_s + off, &kv_map, full_bar(stage), pl * BOX_INNER, 0, h, page, args.v_coord);
+          }
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------------- consumer warp
+  const int j = lane & 3, g = lane >> 2;
+  const int mi = lane >> 3;
+  // Q^T fragments (B operand): column n = g is head h*G + g
+  uint32_t qb[NMB][2];
+  {
+    const bool head_ok = g < G;
+    const T* qp = reinterpret_cast<const T*>(args.q) + ((size_t)q_row * args.Hq + h * G + (head_ok ? g : 0)) * D;
+#pragma unroll
+    for (int c = 0; c < NMB; ++c) {
+      float x[4];
+      if (KV8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) x[e] = head_ok ? to_float(qp[c * 16 + 4 * j + e]) : 0.f;
+      } else {
+        x[0] = head_ok ? to_float(qp[c * 16 + 2 * j]) : 0.f;
+        x[1] = head_ok ? to_float(qp[c * 16 + 2 * j + 1]) : 0.f;
+        x[2] = head_ok ? to_float(qp[c * 16 + 8 + 2 * j]) : 0.f;
+        x[3] = head_ok ? to_float(qp[c * 16 + 8 + 2 * j + 1]) : 0.f;
+      }
+      qb[c][0] = F16MMA ? pack_f16x2(x[0], x[1]) : pack_bf16x2(x[0], x[1]);
+      qb[c][1] = F16MMA ? pack_f16x2(x[2], x[3]) : pack_bf16x2(x[2], x[3]);
+    }
+  }
+  const float k_sc = args.k_scale != nullptr ? args.k_scale[h] : 1.f;
+  const float v_sc = args.v_scale != nullptr ? args.v_scale[h] : 1.f;
+  const float sm_scale = args.scale * k_sc * kLog2e;
+
+  float ot[NMB][4];
+#pragma unroll
+  for (int i = 0; i < NMB; ++i) { ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // heads 2j and 2j+1
+
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int t = 0; t < n_tiles; ++t) {
+    if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 212)) break;
+    const uint32_t k_s = s_base + stage * STAGE_BYTES, v_s = k_s + KV_BYTES;
+    const int tok0 = (t_begin + t) * TK;
+
+    // ---- S^T = K Q^T : four blocks of 16 tokens x 8 heads
+    float st[TK / 16][4];
+#pragma unroll
+    for (int tb = 0; tb < TK / 16; ++tb) {
+      st[tb][0] = st[tb][1] = st[tb][2] = st[tb][3] = 0.f;
+      const int trow = tb * 16 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int cp = 0; cp < RB / 32; ++cp) {
+        const int chunk = 2 * cp + (mi >> 1);
+        uint32_t r[4];
+        ldmatrix_x4(k_s + (chunk >> 3) * PLANE_BYTES + trow * 128 + (((chunk & 7) ^ (trow & 7)) << 4), r);
+        if (KV8) {
+          // one 16-byte chunk = 16 d = one k-step; the pair of chunks gives two k-steps
+          uint32_t a[4] = {e4m3x2_to_f16x2(r[0]), e4m3x2_to_f16x2(r[1]), e4m3x2_to_f16x2(r[0] >> 16),
+                           e4m3x2_to_f16x2(r[1] >> 16)};
+          mma_16816_f16(st[tb], a, qb[2 * cp][0], qb[2 * cp][1]);
+          uint32_t a2[4] = {e4m3x2_to_f16x2(r[2]), e4m3x2_to_f16x2(r[3]), e4m3x2_to_f16x2(r[2] >> 16),
+                            e4m3x2_to_f16x2(r[3] >> 16)};
+          mma_16816_f16(st[tb], a2, qb[2 * cp + 1][0], qb[2 * cp + 1][1]);
+        } else {
+          // two 16-byte chunks = 16 d = one k-step
+          if (F16MMA) mma_16816_f16(st[tb], r, qb[cp][0], qb[cp][1]);
+          else mma_16816_bf16(st[tb], r, qb[cp][0], qb[cp][1]);
+        }
+      }
+    }
+
+    // ---- scale, mask, online softmax over the token axis (per head column)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int tb = 0; tb < TK / 16; ++tb) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int tok = tok0 + tb * 16 + g + 8 * hf;
+        const bool ok = tok >= kv_lo && tok < kv_hi;
+        const float a0 = ok ? st[tb][2 * hf] * sm_scale : -INFINITY;
+        const float a1 = ok ? st[tb][2 * hf + 1] * sm_scale : -INFINITY;
+        st[tb][2 * hf] = a0;
+        st[tb][2 * hf + 1] = a1;
+        mx0 = fmaxf(mx0, a0);
+        mx1 = fmaxf(mx1, a1);
+      }
+    }
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float al0 = fast_exp2(m0 - ms0), al1 = fast_exp2(m1 - ms1);
+    m0 = mn0;
+    m1 = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int tb = 0; tb < TK / 16; ++tb) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const float p0 = fast_exp2(st[tb][2 * hf] - ms0), p1 = fast_exp2(st[tb][2 * hf + 1] - ms1);
+        st[tb][2 * hf] = p0;
+        st[tb][2 * hf + 1] = p1;
+        sum0 += p0;
+        sum1 += p1;
+      }
+    }
+    l0 = l0 * al0 + sum0;
+    l1 = l1 * al1 + sum1;
+#pragma unroll
+    for (int i = 0; i < NMB; ++i) {
+      ot[i][0] *= al0; ot[i][1] *= al1;
+      ot[i][2] *= al0; ot[i][3] *= al1;
+    }
+
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int tb = 0; tb < TK / 16; ++tb) {
+      uint32_t p01, p23;
+      if (F16MMA) { p01 = pack_f16x2(st[tb][0], st[tb][1]); p23 = pack_f16x2(st[tb][2], st[tb][3]); }
+      else { p01 = pack_bf16x2(st[tb][0], st[tb][1]); p23 = pack_bf16x2(st[tb][2], st[tb][3]); }
+      const uint32_t pb0 = movmatrix_trans(p01), pb1 = movmatrix_trans(p23);
+      if (KV8) {
+        const int trow = tb * 16 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int cp = 0; cp < D / 32; ++cp) {
+          const int chunk = 2 * cp + (mi >> 1);
+          uint32_t r[4];
+          ldmatrix_x4_trans(v_s + (chunk >> 3) * PLANE_BYTES + trow * 128 + (((chunk & 7) ^ (trow & 7)) << 4), r);
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            // rows 0..7 of the block are the even d of the chunk, rows 8..15 the odd d
+            const uint32_t we = __byte_perm(r[2 * c2], r[2 * c2 + 1], 0x6420);
+            const uint32_t wo = __byte_perm(r[2 * c2], r[2 * c2 + 1], 0x7531);
+            uint32_t a[4] = {e4m3x2_to_f16x2(we), e4m3x2_to_f16x2(wo), e4m3x2_to_f16x2(we >> 16),
+                             e4m3x2_to_f16x2(wo >> 16)};
+            mma_16816_f16(ot[2 * cp + c2], a, pb0, pb1);
+          }
+        }
+      } else {
+        const int trow = tb * 16 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int mb = 0; mb < NMB; ++mb) {
+          const int chunk = 2 * mb + (mi & 1);
+          uint32_t r[4];
+          ldmatrix_x4_trans(v_s + (chunk >> 3) * PLANE_BYTES + trow * 128 + (((chunk & 7) ^ (trow & 7)) << 4), r);
+          if (F16MMA) mma_16816_f16(ot[mb], r, pb0, pb1);
+          else mma_16816_bf16(ot[mb], r, pb0, pb1);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(stage));
+    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+  }
+
+  // ---- finalise: sums over the token lanes, then write heads 2j and 2j+1
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+  }
+  const float inv0 = l0 > 0.f ? v_sc / l0 : 0.f, inv1 = l1 > 0.f ? v_sc / l1 : 0.f;
+  const bool ok0 = 2 * j < G, ok1 = 2 * j + 1 < G;
+  const int head0 = h * G + 2 * j, head1 = head0 + 1;
+  if (args.splits == 1) {
+    T* o0 = reinterpret_cast<T*>(args.out) + ((size_t)q_row * args.Hq + head0) * D;
+    T* o1 = reinterpret_cast<T*>(args.out) + ((size_t)q_row * args.Hq + head1) * D;
+#pragma unroll
+    for (int c = 0; c < NMB; ++c) {
+      if (KV8) {
+        // this thread holds d = 16c + 2g and 16c + 2g + 1 of both heads
+        if (ok0) *reinterpret_cast<typename Pack2<T>::type*>(o0 + c * 16 + 2 * g) = Pack2<T>::make(ot[c][0] * inv0, ot[c][2] * inv0);
+        if (ok1) *reinterpret_cast<typename Pack2<T>::type*>(o1 + c * 16 + 2 * g) = Pack2<T>::make(ot[c][1] * inv1, ot[c][3] * inv1);
+      } else {
+        if (ok0) { o0[c * 16 + g] = from_float<T>(ot[c][0] * inv0); o0[c * 16 + 8 + g] = from_float<T>(ot[c][2] * inv0); }
+        if (ok1) { o1[c * 16 + g] = from_float<T>(ot[c][1] * inv1); o1[c * 16 + 8 + g] = from_float<T>(ot[c][3] * inv1); }
+      }
+    }
+  } else {
+    const size_t plane = (size_t)args.total_q * args.Hq;
+    float* w0 = args.ws_o + ((size_t)split * plane + (size_t)q_row * args.Hq + head0) * D;
+    float* w1 = args.ws_o + ((size_t)split * plane + (size_t)q_row * args.Hq + head1) * D;
+#pragma unroll
+    for (int c = 0; c < NMB; ++c) {
+      const int d0 = KV8 ? c * 16 + 2 * g : c * 16 + g;
+      const int d1 = KV8 ? d0 + 1 : d0 + 8;
+      if (ok0) { w0[d0] = ot[c][0] * inv0; w0[d1] = ot[c][2] * inv0; }
+      if (ok1) { w1[d0] = ot[c][1] * inv1; w1[d1] = ot[c][3] * inv1; }
+    }
+    if (g == 0) {
+      if (ok0) args.ws_lse[(size_t)split * plane + (size_t)q_row * args.Hq + head0] = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
+      if (ok1) args.ws_lse[(size_t)split * plane + (size_t)q_row * args.Hq + head1] = l1 > 0.f ? m1 + log2f(l1) : -INFINITY;
+    }
+  }
+}
+
+template <typename T, bool KV8, int D, int STAGES>
+int launch_decode(const CUtensorMap& map, const AttnArgs& a, cudaStream_t stream) {
+  constexpr int ESZ = KV8 ? 1 : 2;
+  constexpr int smem = STAGES * 2 * (D * ESZ / 128) * TK * 128 + 16 * STAGES + 64 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<T, KV8, D, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { msgl_set_error("decode attention smem attribute", e); return MSGL_CUDA_ERROR; }
+    configured = true;
+  }
+  dim3 grid(1, a.B * a.Hk, a.splits);
+  paged_decode_kernel<T, KV8, D, STAGES><<<grid, 64, smem, stream>>>(map, a);
+  MSGL_CHECK_LAUNCH("paged_decode");
+  return MSGL_OK;
+}
+
 template <typename T, bool KV8, int D, int NWQ, int NWK, int STAGES>
 int launch_attn(const CUtensorMap& map, const AttnArgs& a, int q_tiles, cudaStream_t stream) {
   constexpr int ESZ = KV8 ? 1 : 2;
@@ -538,9 +846,18 @@ int launch_attn(const CUtensorMap& map, const AttnArgs& a, int q_tiles, cudaStre
   return MSGL_OK;
 }
 
+bool g_force_general_decode = false;
+
 template <typename T>
 int dispatch_attn(const CUtensorMap& map, const AttnArgs& a, bool kv8, int d, int max_q, cudaStream_t stream) {
   const int G = a.Hq / a.Hk;
+  if (max_q == 1 && G <= 8 && a.mask == nullptr && !g_force_general_decode) {
+    if (d == 128) {
+      if (kv8) return launch_decode<T, true, 128, 2>(map, a, stream);
+      return launch_decode<T, false, 128, 2>(map, a, stream);
+    }
+    if (d == 64 && !kv8) return launch_decode<T, false, 64, 3>(map, a, stream);
+  }
   const bool small = max_q * G <= 16;
   const int rows = small ? 16 : 64;
   const int q_tiles = (max_q + rows / G - 1) / (rows / G);
@@ -640,6 +957,9 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
   }
   return MSGL_OK;
 }
+
+// Test hook: route decode batches through the general (prefill/verify) kernel.
+MSGL_API void msgl_attn_force_general_decode(int on) { g_force_general_decode = on != 0; }
 
 MSGL_API int msgl_attn_status(int reset) {
   int v = 0;

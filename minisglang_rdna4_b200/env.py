@@ -133,7 +133,7 @@ ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-re
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger use two-shot")
-ENV.int("COMM_WAIT_US", 2_000_000, "bound of every device-side flag wait, in microseconds")
+ENV.int("COMM_WAIT_US", 500_000, "bound of every device-side flag wait, in microseconds")
 ENV.flag("TP_OVERLAP", False, "overlap row-parallel all-reduce with compute on a side stream (eager prefill)")
 # --- speculative decode -------------------------------------------------------------------
 ENV.flag("SPEC_SAMPLED", False, "verify drafts by rejection sampling instead of greedy prefix match")

@@ -292,6 +292,13 @@ def gemm_status(reset=True) -> int:
     return int(lib().msgl_gemm_status(int(reset)))
 
 
+def force_general_decode_attention(on: bool) -> None:
+    """Route single-query batches through the general attention kernel. Speculative decoding
+    sets this: verification rows run on the general kernel, and greedy output is only
+    bit-identical to plain decoding when the decode rows take the same code path."""
+    lib().msgl_attn_force_general_decode(int(on))
+
+
 def attn_status(reset=True) -> int:
     return int(lib().msgl_attn_status(int(reset)))
 

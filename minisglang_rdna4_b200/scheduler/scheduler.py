@@ -327,6 +327,7 @@ class Scheduler:
         if ongoing is None:
             return
         tokens = ongoing.output.wait()
+        self._check_comm_health()
         sample = ongoing.output.sample
         lp = sample.logprobs.tolist() if sample is not None and sample.logprobs is not None else None
         tlp = tids = None
@@ -358,6 +359,22 @@ class Scheduler:
                 self._free_req_resources(req, insert=True)
         if replies:
             self.send_result(replies)
+
+    def _check_comm_health(self) -> None:
+        """Every few steps read the status word of the peer-memory collectives (the host has just
+        synchronised with the device anyway). A wait that ran out means a peer is missing or slow:
+        the fused path is switched off for the rest of the process and decode leaves its captured
+        graphs, which contain the fused kernels, for eager steps on the NCCL path. A peer that is
+        really gone is then caught by the process-group timeout and the crash watchdog."""
+        if self.config.tp_size == 1 or self.stats["steps"] % 16 != 0:
+            return
+        from ..parallel.comm import get_comm
+
+        for impl in get_comm().impls:
+            check = getattr(impl, "check_health", None)
+            if check is not None and getattr(impl, "healthy", True) and not check():
+                logger.warning("peer-memory collectives disabled after a device-side timeout")
+                self.engine.graph_runner = None
 
     def _free_req_resources(self, req: Req, insert: bool) -> None:
         if req.resources_freed:  # several paths can reach a request; free exactly once

@@ -218,6 +218,21 @@ def test_attention_prefill_and_extend(K, fp8):
     _attn_case(K, fp8, 2, [20, 12], [20, 50], 8, 2, 128, 16, causal=False)     # bidirectional
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_decode_kernels_agree(K, fp8):
+    """The transposed decode kernel and the general kernel are two code paths for the same math."""
+    try:
+        K.force_general_decode_attention(True)
+        _attn_case(K, fp8, 4, [1] * 4, [50, 700, 64, 1333], 32, 8, 128, 16)
+        _attn_case(K, fp8, 3, [1] * 3, [300, 20, 901], 8, 1, 128, 16, splits=3)     # group of 8
+        _attn_case(K, fp8, 2, [1] * 2, [400, 100], 8, 2, 128, 16, window=128)
+    finally:
+        K.force_general_decode_attention(False)
+    _attn_case(K, fp8, 3, [1] * 3, [300, 20, 901], 8, 1, 128, 16, splits=3)
+    _attn_case(K, fp8, 2, [1] * 2, [400, 100], 8, 2, 128, 16, window=128)
+    _attn_case(K, fp8, 2, [1] * 2, [400, 100], 16, 16, 128, 16)                     # MHA, group of 1
+
+
 def test_attention_head_dim_64_and_fp16(K):
     _attn_case(K, False, 2, [9, 1], [40, 200], 4, 2, 64, 16)
     _attn_case(K, False, 2, [9, 1], [40, 200], 8, 2, 128, 16, dtype=torch.float16)

@@ -294,9 +294,13 @@ def main() -> None:
             "clocks": clocks,
         }
         print(json.dumps(line))
+    sys.stdout.flush()
     llm.shutdown()
-    if world > 1 and dist.is_initialized():
-        dist.destroy_process_group()
+    # The result line is out and every rank has passed the shutdown barrier. Leave without the
+    # interpreter's teardown: destroying NCCL communicators that captured graphs still reference
+    # has been seen to block one rank forever, which would stall the launcher.
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,301 @@
+// Expert-parallel all-to-all over NVLink peer memory, fused with the routing-side work.
+//
+//   ep_dispatch      (source rank)  for every (token, k) pair: pick the rank that owns the expert,
+//                                   claim a slot in that rank's receive region and store the token
+//                                   row there with P2P stores, together with (local expert id,
+//                                   pair index); the last CTA publishes the per-destination counts
+//                                   and raises the sequence flags
+//   ep_recv_prepare  (owner rank)   bounded wait for every source's flag; expand counts into a
+//                                   flat expert-id list (-1 past the count) that the local
+//                                   align / permute / grouped-GEMM pipeline consumes
+//   ep_return        (owner rank)   store every expert output row back into the source rank's
+//                                   return region (same slot it arrived in), then raise flags
+//   ep_combine       (source rank)  bounded wait for the owners' flags; out[t] = sum_k w[t,k] *
+//                                   returned row of pair (t,k)   (gate-weighted sum fused in)
+//
+// Replaces the reference's gather-everything exchange (all_gather of an (N, 2H + 8k) byte blob
+// and an all_reduce of (ep*N, H); python/minisgl/layers/moe.py:1244-1311): only the rows an
+// expert owner needs cross the links, once in each direction. Regions are sized for the worst
+// case (every pair of a source going to one owner) so shapes are static under CUDA graphs.
+// Peer memory is only ever written; every wait is bounded and reports through a status word.
+#include "common.cuh"
+
+using namespace msgl;
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+
+struct EpBuffers {
+  // per-rank symmetric region layout (byte offsets from the region base)
+  //   recv_rows [R][cap][H]      T
+  //   ret_rows  [R][cap][H]      T
+  //   recv_meta [R][cap][2]      int32 (local expert id, source pair index)
+  //   recv_count[R], recv_flag[R], ret_flag[R]   uint32
+  unsigned char* base[kMaxRanks];
+  long long off_recv_rows, off_ret_rows, off_recv_meta, off_recv_count, off_recv_flag, off_ret_flag;
+  int rank, nranks, cap, hidden;
+};
+
+__device__ int g_ep_status = 0;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t seq, unsigned long long limit_ns, int code) {
+  if ((int)(ld_acquire_sys(p) - seq) >= 0) return true;
+  const unsigned long long t0 = gtimer();
+  while ((int)(ld_acquire_sys(p) - seq) < 0) {
+    if (gtimer() - t0 > limit_ns) {
+      atomicCAS(&g_ep_status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+// grid = tokens, block = 128. state: [0..R) cursors, [R] done counter, [R+1] sequence (device-resident)
+template <typename T>
+__global__ void ep_dispatch_kernel(EpBuffers b, const T* __restrict__ x, const int32_t* __restrict__ topk_ids,
+                                   int32_t* __restrict__ send_slot, uint32_t* __restrict__ state, int tokens, int k,
+                                   int experts_per_rank) {
+  __shared__ int s_slot[16];
+  __shared__ int s_dst[16];
+  const int t = blockIdx.x;
+  if (threadIdx.x < k) {
+    const int e = topk_ids[(size_t)t * k + threadIdx.x];
+    int dst = -1, slot = -1;
+    if (e >= 0 && e < experts_per_rank * b.nranks) {
+      dst = e / experts_per_rank;
+      slot = (int)atomicAdd(&state[dst], 1u);
+      if (slot >= b.cap) { slot = -1; dst = -1; }   // cannot happen with cap = tokens * k
+      else {
+        int32_t* meta = reinterpret_cast<int32_t*>(b.base[dst] + b.off_recv_meta) +
+                        ((size_t)b.rank * b.cap + slot) * 2;
+        meta[0] = e % experts_per_rank;
+        meta[1] = t * k + threadIdx.x;
+      }
+    }
+    s_dst[threadIdx.x] = dst;
+    s_slot[threadIdx.x] = slot;
+    send_slot[(size_t)t * k + threadIdx.x] = dst < 0 ? -1 : dst * b.cap + slot;
+  }
+  __syncthreads();
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * b.hidden);
+  const int vecs = b.hidden / 8;
+  for (int kk = 0; kk < k; ++kk) {
+    const int dst = s_dst[kk];
+    if (dst < 0) continue;
+    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<T*>(b.base[dst] + b.off_recv_rows) +
+                                          ((size_t)b.rank * b.cap + s_slot[kk]) * b.hidden);
+    for (int i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = src[i];
+  }
+  // last CTA publishes counts and flags
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool s_last;
+  if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks], 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last && threadIdx.x < b.nranks) {
+    const int dst = threadIdx.x;
+    const uint32_t seq = state[b.nranks + 1] + 1u;
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(b.base[dst] + b.off_recv_count) + b.rank;
+    *cnt = atomicAdd(&state[dst], 0u);
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(b.base[dst] + b.off_recv_flag) + b.rank, seq);
+  }
+  if (s_last) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int r = 0; r < b.nranks; ++r) state[r] = 0u;   // ready for the next call
+      state[b.nranks] = 0u;
+      state[b.nranks + 1] += 1u;
+    }
+  }
+}
+
+// grid = R * ceil(cap/256); expert_ids [R*cap] <- local expert id or -1
+__global__ void ep_recv_prepare_kernel(EpBuffers b, int32_t* __restrict__ expert_ids, const uint32_t* __restrict__ seq_ptr,
+                                       unsigned long long limit_ns) {
+  const int blocks_per_src = (b.cap + 255) / 256;
+  const int src = blockIdx.x / blocks_per_src;
+  const int pos = (blockIdx.x % blocks_per_src) * 256 + threadIdx.x;
+  __shared__ uint32_t s_count;
+  if (threadIdx.x == 0) {
+    const uint32_t seq = *seq_ptr;   // the local dispatch of this step has already advanced it
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(b.base[b.rank] + b.off_recv_flag) + src;
+    const bool ok = wait_flag(flag, seq, limit_ns, 400 + src);
+    s_count = ok ? reinterpret_cast<const uint32_t*>(b.base[b.rank] + b.off_recv_count)[src] : 0u;
+  }
+  __syncthreads();
+  if (pos >= b.cap) return;
+  const int32_t* meta = reinterpret_cast<const int32_t*>(b.base[b.rank] + b.off_recv_meta) + ((size_t)src * b.cap + pos) * 2;
+  expert_ids[(size_t)src * b.cap + pos] = pos < (int)s_count ? meta[0] : -1;
+}
+
+// grid = R * cap rows (one CTA per received slot); y_sorted rows are addressed through pair_row
+template <typename T>
+__global__ void ep_return_kernel(EpBuffers b, const T* __restrict__ y_sorted, const int32_t* __restrict__ pair_row,
+                                 uint32_t* __restrict__ state, const uint32_t* __restrict__ seq_ptr) {
+  const int idx = blockIdx.x;           // src * cap + pos
+  const int src = idx / b.cap, pos = idx % b.cap;
+  const int row = pair_row[idx];
+  if (row >= 0) {
+    const uint4* in = reinterpret_cast<const uint4*>(y_sorted + (size_t)row * b.hidden);
+    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<T*>(b.base[src] + b.off_ret_rows) +
+                                          ((size_t)b.rank * b.cap + pos) * b.hidden);
+    for (int i = threadIdx.x; i < b.hidden / 8; i += blockDim.x) out[i] = in[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool s_last;
+  if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks + 2], 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < b.nranks)
+      st_release_sys(reinterpret_cast<uint32_t*>(b.base[threadIdx.x] + b.off_ret_flag) + b.rank, *seq_ptr);
+    __syncthreads();
+    if (threadIdx.x == 0) state[b.nranks + 2] = 0u;
+  }
+}
+
+// grid = tokens
+template <typename T>
+__global__ void ep_combine_kernel(EpBuffers b, const float* __restrict__ topk_w, const int32_t* __restrict__ send_slot,
+                                  T* __restrict__ out, const uint32_t* __restrict__ seq_ptr, int k,
+                                  unsigned long long limit_ns) {
+  const int t = blockIdx.x;
+  if (threadIdx.x < b.nranks) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(b.base[b.rank] + b.off_ret_flag) + threadIdx.x;
+    wait_flag(flag, *seq_ptr, limit_ns, 420 + threadIdx.x);
+  }
+  __syncthreads();
+  const T* ret = reinterpret_cast<const T*>(b.base[b.rank] + b.off_ret_rows);
+  for (int i = threadIdx.x * 8; i < b.hidden; i += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int kk = 0; kk < k; ++kk) {
+      const int slot = send_slot[(size_t)t * k + kk];
+      if (slot < 0) continue;
+      const float w = topk_w[(size_t)t * k + kk];
+      float v[8];
+      load8(ret + (size_t)slot * b.hidden + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += w * v[e];
+    }
+    store8(out + (size_t)t * b.hidden + i, acc);
+  }
+}
+
+EpBuffers make_buffers(void* const* bases, int rank, int nranks, int cap, int hidden, int esize) {
+  EpBuffers b;
+  for (int r = 0; r < nranks; ++r) b.base[r] = (unsigned char*)bases[r];
+  b.rank = rank; b.nranks = nranks; b.cap = cap; b.hidden = hidden;
+  const long long rows = (long long)nranks * cap * hidden * esize;
+  b.off_recv_rows = 0;
+  b.off_ret_rows = rows;
+  b.off_recv_meta = 2 * rows;
+  b.off_recv_count = b.off_recv_meta + (long long)nranks * cap * 8;
+  b.off_recv_flag = b.off_recv_count + 256;
+  b.off_ret_flag = b.off_recv_flag + 256;
+  return b;
+}
+
+}  // namespace
+
+MSGL_API long long msgl_ep_region_bytes(int nranks, int cap, int hidden, int esize) {
+  return 2ll * nranks * cap * hidden * esize + (long long)nranks * cap * 8 + 3 * 256;
+}
+
+// state: device array of nranks + 4 uint32, zero-initialised once
+MSGL_API int msgl_ep_dispatch(void* const* bases, int rank, int nranks, int cap, const void* x, const void* topk_ids,
+                              void* send_slot, void* state, int tokens, int hidden, int k, int experts_per_rank,
+                              int dtype, cudaStream_t stream) {
+  if (nranks > kMaxRanks || k > 16 || hidden % 8 || tokens * k > cap) {
+    msgl_set_error_text("ep_dispatch: shape does not fit the exchange regions");
+    return MSGL_BAD_ARG;
+  }
+  if (tokens == 0) return MSGL_BAD_ARG;   // every rank must take part: pad to at least one token
+  EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
+  if (dtype == MSGL_BF16)
+    ep_dispatch_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(b, (const __nv_bfloat16*)x, (const int32_t*)topk_ids,
+                                                                  (int32_t*)send_slot, (uint32_t*)state, tokens, k,
+                                                                  experts_per_rank);
+  else if (dtype == MSGL_F16)
+    ep_dispatch_kernel<__half><<<tokens, 128, 0, stream>>>(b, (const __half*)x, (const int32_t*)topk_ids,
+                                                           (int32_t*)send_slot, (uint32_t*)state, tokens, k,
+                                                           experts_per_rank);
+  else
+    return MSGL_BAD_ARG;
+  MSGL_CHECK_LAUNCH("ep_dispatch");
+  return MSGL_OK;
+}
+
+MSGL_API int msgl_ep_recv_prepare(void* const* bases, int rank, int nranks, int cap, int hidden, void* expert_ids,
+                                  void* state, long long wait_us, cudaStream_t stream) {
+  EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
+  const int blocks = nranks * ((cap + 255) / 256);
+  ep_recv_prepare_kernel<<<blocks, 256, 0, stream>>>(b, (int32_t*)expert_ids, (const uint32_t*)state + nranks + 1,
+                                                     (unsigned long long)wait_us * 1000ull);
+  MSGL_CHECK_LAUNCH("ep_recv_prepare");
+  return MSGL_OK;
+}
+
+MSGL_API int msgl_ep_return(void* const* bases, int rank, int nranks, int cap, int hidden, const void* y_sorted,
+                            const void* pair_row, void* state, int dtype, cudaStream_t stream) {
+  EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
+  const int blocks = nranks * cap;
+  if (dtype == MSGL_BF16)
+    ep_return_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(b, (const __nv_bfloat16*)y_sorted,
+                                                               (const int32_t*)pair_row, (uint32_t*)state,
+                                                               (const uint32_t*)state + nranks + 1);
+  else if (dtype == MSGL_F16)
+    ep_return_kernel<__half><<<blocks, 128, 0, stream>>>(b, (const __half*)y_sorted, (const int32_t*)pair_row,
+                                                        (uint32_t*)state, (const uint32_t*)state + nranks + 1);
+  else
+    return MSGL_BAD_ARG;
+  MSGL_CHECK_LAUNCH("ep_return");
+  return MSGL_OK;
+}
+
+MSGL_API int msgl_ep_combine(void* const* bases, int rank, int nranks, int cap, int hidden, const void* topk_w,
+                             const void* send_slot, void* out, void* state, int tokens, int k, long long wait_us,
+                             int dtype, cudaStream_t stream) {
+  EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
+  int threads = hidden / 8 < 256 ? ((hidden / 8 + 31) / 32) * 32 : 256;
+  if (threads < 32) threads = 32;
+  if (dtype == MSGL_BF16)
+    ep_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(b, (const float*)topk_w, (const int32_t*)send_slot,
+                                                                    (__nv_bfloat16*)out,
+                                                                    (const uint32_t*)state + nranks + 1, k,
+                                                                    (unsigned long long)wait_us * 1000ull);
+  else if (dtype == MSGL_F16)
+    ep_combine_kernel<__half><<<tokens, threads, 0, stream>>>(b, (const float*)topk_w, (const int32_t*)send_slot,
+                                                             (__half*)out, (const uint32_t*)state + nranks + 1, k,
+                                                             (unsigned long long)wait_us * 1000ull);
+  else
+    return MSGL_BAD_ARG;
+  MSGL_CHECK_LAUNCH("ep_combine");
+  return MSGL_OK;
+}
+
+MSGL_API int msgl_ep_status(int reset) {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_ep_status, sizeof(int));
+  if (reset && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_ep_status, &z, sizeof(int));
+  }
+  return v;
+}

@@ -394,14 +394,22 @@ msgl_encode_tiled_fn msgl_get_encode_tiled() {
 }
 
 // Pick the N tile so that the grid fills the GPU when the problem allows it.
-static int choose_bn(int m_tiles, int n, int sms, int smallest) {
+// Pick the N tile that minimises (waves over the SMs) x (bytes a CTA stages per K block): a tile
+// twice as wide costs 1.2-1.5x the bytes per K block but halves the tile count, so it wins
+// whenever the narrower tile would need an extra wave.
+static int choose_bn(int m_tiles, int n, int sms, int smallest, int b_row_bytes) {
   const int cands[3] = {128, 64, 32};
+  int best = smallest;
+  long long best_cost = -1;
   for (int i = 0; i < 3; ++i) {
-    int bn = cands[i];
-    int tiles = m_tiles * ((n + bn - 1) / bn);
-    if (tiles >= sms || bn == smallest) return bn;
+    const int bn = cands[i];
+    if (bn < smallest) continue;
+    const long long tiles = (long long)m_tiles * ((n + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const long long cost = waves * (128 * 128 + (long long)bn * b_row_bytes);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
-  return smallest;
+  return best;
 }
 
 // a: [M, K] (kind 0/1: 16-bit, kind 2/3: e4m3 bytes), row stride lda elements
@@ -435,7 +443,7 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.m_tiles = (M + BM - 1) / BM;
   // The block-scaled instruction takes its weight scale factors from tensor-memory columns in
   // steps of 64 rows (two columns), so the MXFP4 kind has no 32-wide N tile.
-  const int bn = bn_override ? bn_override : choose_bn(args.m_tiles, N, sms, kind == KIND_MXF4 ? 64 : 32);
+  const int bn = bn_override ? bn_override : choose_bn(args.m_tiles, N, sms, kind == KIND_MXF4 ? 64 : 32, kind == KIND_MXF4 ? 64 : 128);
   if (kind == KIND_MXF4 && bn == 32) {
     msgl_set_error_text("gemm: the MXFP4 kind supports N tiles of 64 and 128 only");
     return MSGL_BAD_ARG;

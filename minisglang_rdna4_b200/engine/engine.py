@@ -184,9 +184,19 @@ class Engine:
         )
         self.ctx.comm = comm_mod.get_comm()
         if config.enable_ep and config.dp_size > 1:
-            from ..parallel.ep import EPContext
+            from ..parallel.ep import EPContext, FusedEPContext
 
-            self.ctx.ep = EPContext(self.dp_group, config.dp_rank, config.dp_size)
+            self.ctx.ep = None
+            if dev_kind == "cuda" and mc.is_moe and not ENV.DISABLE_FUSED_COMM.value:
+                try:
+                    self.ctx.ep = FusedEPContext(
+                        self.dp_group, self.dp_cpu_group, config.dp_rank, config.dp_size, self.device,
+                        mc.hidden_size, mc.num_experts_per_tok, mc.num_experts // config.dp_size,
+                        max_tokens=min(config.max_running_req, 512))
+                except Exception as exc:
+                    logger.warning("fused expert-parallel exchange unavailable (%s); using NCCL", exc)
+            if self.ctx.ep is None:
+                self.ctx.ep = EPContext(self.dp_group, config.dp_rank, config.dp_size)
         set_global_ctx(self.ctx)
         self.sampler = Sampler(self.device, mc.vocab_size, mc.final_logit_softcapping, seed=config.seed)
         self._staging_cap = 0
@@ -442,9 +452,34 @@ class Engine:
         return tokens
 
     def shutdown(self) -> None:
+        """Release what would keep a process-group teardown waiting: captured graphs (they hold
+        NCCL kernels), peer-memory mappings, then meet the other ranks at a CPU barrier."""
+        import gc
+
         set_global_ctx(None)
+        if self.graph_runner is not None:
+            self.graph_runner.graphs.clear()
+            self.graph_runner.logits.clear()
+            self.graph_runner = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        for impl in comm_mod.get_comm().impls:
+            close = getattr(impl, "close", None)
+            if close is not None:
+                try:
+                    close()
+                except Exception:
+                    pass
+        ep = getattr(self.ctx, "ep", None)
+        if ep is not None and hasattr(ep, "close"):
+            try:
+                ep.close()
+            except Exception:
+                pass
+        comm_mod.reset_comm()
+        gc.collect()
         if dist.is_initialized() and self.config.world_size > 1:
             try:
-                dist.barrier(group=self.cpu_group)
+                dist.barrier(group=self.cpu_group if self.cpu_group is not None else self.dp_cpu_group)
             except Exception:
                 pass

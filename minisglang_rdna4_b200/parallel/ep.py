@@ -49,3 +49,92 @@ class EPContext:
         dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         self.calls += 1
         return y[self.rank * n : self.rank * n + n_local]
+
+
+class FusedEPContext(EPContext):
+    """Expert-parallel exchange on the peer-memory kernels of ``csrc/ep_a2a.cu``: only the rows
+    an expert owner needs are stored into its receive region (dispatch), and only the expert
+    outputs go back (combine, with the gate-weighted sum applied on arrival). Used for steps of
+    up to ``max_tokens`` rows per rank (decode and small prefills); larger steps take the
+    gather/reduce baseline of the parent class. Works for DP+EP (ranks = replicas) and for
+    EP over TP (ranks = tensor-parallel ranks, every rank dispatching only its own row slice)."""
+
+    def __init__(self, group, cpu_group, rank: int, size: int, device, hidden: int, top_k: int,
+                 experts_per_rank: int, max_tokens: int = 256) -> None:
+        super().__init__(group, rank, size)
+        import ctypes
+
+        from ..env import ENV
+        from ..ops._lib import bind, c_i, c_ll, c_p, lib
+        from .symm import SymmetricHeap
+
+        bind("msgl_ep_region_bytes", c_ll, [c_i, c_i, c_i, c_i])
+        bind("msgl_ep_dispatch", c_i, [c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p])
+        bind("msgl_ep_recv_prepare", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_ll, c_p])
+        bind("msgl_ep_return", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p])
+        bind("msgl_ep_combine", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_p])
+        bind("msgl_ep_status", c_i, [c_i])
+        self.device = torch.device(device)
+        self.hidden, self.top_k, self.experts_per_rank = hidden, top_k, experts_per_rank
+        self.max_tokens = max_tokens
+        self.cap = max_tokens * top_k
+        nbytes = int(lib().msgl_ep_region_bytes(size, self.cap, hidden, 2))
+        self.heap = SymmetricHeap(nbytes, cpu_group, rank, size)
+        self._bases = (ctypes.c_void_p * size)(*self.heap.ptrs)
+        self._state = torch.zeros(size + 4, dtype=torch.int32, device=self.device)
+        self.wait_us = ENV.COMM_WAIT_US.value
+        self.healthy = True
+        self.fused_calls = 0
+
+    def dispatch_compute_combine(self, moe, x, topk_w, topk_ids):
+        n = x.shape[0]
+        if (not self.healthy or not x.is_cuda or n > self.max_tokens or n == 0 or x.dtype not in (
+                torch.bfloat16, torch.float16)):
+            return super().dispatch_compute_combine(moe, x, topk_w, topk_ids)
+        from ..ops import cuda as K
+        from ..ops import moe_kernels as MK
+        from ..ops._lib import check, lib
+
+        L = lib()
+        dt = 0 if x.dtype == torch.bfloat16 else 1
+        st = K._stream()
+        x = x.contiguous()
+        ids = topk_ids.contiguous()
+        send_slot = torch.empty(n * self.top_k, dtype=torch.int32, device=x.device)
+        check(L.msgl_ep_dispatch(self._bases, self.rank, self.size, self.cap, x.data_ptr(), ids.data_ptr(),
+                                 send_slot.data_ptr(), self._state.data_ptr(), n, self.hidden, self.top_k,
+                                 self.experts_per_rank, dt, st), "ep_dispatch")
+        flat = self.size * self.cap
+        expert_ids = torch.empty(flat, dtype=torch.int32, device=x.device)
+        check(L.msgl_ep_recv_prepare(self._bases, self.rank, self.size, self.cap, self.hidden, expert_ids.data_ptr(),
+                                     self._state.data_ptr(), self.wait_us, st), "ep_recv_prepare")
+        sorted_pair, pair_row, tile_expert, _meta = MK.moe_align(expert_ids.view(-1, 1), 0, self.experts_per_rank)
+        rows = sorted_pair.numel()
+        xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=x.device)
+        check(L.msgl_moe_permute(self.heap.local, sorted_pair.data_ptr(), xs.data_ptr(), self.hidden, 1, rows, dt, st),
+              "ep permute")
+        tier_w13, tier_w2 = moe.w13, moe.w2
+        hcur = MK.gemm_grouped(xs, tier_w13, tile_expert)
+        act = K.act_and_mul(hcur)
+        y = MK.gemm_grouped(act, tier_w2, tile_expert)
+        check(L.msgl_ep_return(self._bases, self.rank, self.size, self.cap, self.hidden, y.data_ptr(),
+                               pair_row.data_ptr(), self._state.data_ptr(), dt, st), "ep_return")
+        out = torch.empty_like(x)
+        check(L.msgl_ep_combine(self._bases, self.rank, self.size, self.cap, self.hidden, topk_w.contiguous().data_ptr(),
+                                send_slot.data_ptr(), out.data_ptr(), self._state.data_ptr(), n, self.top_k,
+                                self.wait_us, dt, st), "ep_combine")
+        K._count("ep_all_to_all", "ep_dispatch+ep_recv_prepare+ep_return+ep_combine", 4)
+        self.fused_calls += 1
+        self.calls += 1
+        return out
+
+    def check_health(self) -> bool:
+        from ..ops._lib import lib
+
+        code = int(lib().msgl_ep_status(1))
+        if code != 0:
+            self.healthy = False
+        return self.healthy
+
+    def close(self) -> None:
+        self.heap.close()

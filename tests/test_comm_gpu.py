@@ -146,3 +146,66 @@ def test_bounded_wait_reports_and_returns():
     assert flag_bytes > 0
     L.msgl_symm_free(a)
     L.msgl_symm_free(b)
+
+
+def _ep_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    cpu = dist.new_group(list(range(world)), backend="gloo")
+    from minisglang_rdna4_b200.ops import moe_kernels as MK
+    from minisglang_rdna4_b200.ops import ref
+    from minisglang_rdna4_b200.parallel.ep import FusedEPContext
+
+    e, h, inter, k = 16, 256, 128, 4
+    e_local = e // world
+    g = torch.Generator().manual_seed(5)
+    w13 = (torch.randn(e, 2 * inter, h, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(e, h, inter, generator=g) * 0.05).bfloat16()
+
+    class Moe:
+        pass
+
+    moe = Moe()
+    moe.w13 = w13[rank * e_local:(rank + 1) * e_local].contiguous().to(dev)
+    moe.w2 = w2[rank * e_local:(rank + 1) * e_local].contiguous().to(dev)
+    ctx = FusedEPContext(dist.group.WORLD, cpu, rank, world, dev, h, k, e_local, max_tokens=64)
+    ok, msgs = True, []
+    for it, n in enumerate([1, 17, 64, 5]):
+        gi = torch.Generator().manual_seed(100 * it + rank)
+        x = torch.randn(n, h, generator=gi).bfloat16()
+        logits = torch.randn(n, e, generator=gi)
+        tw, ids = ref.moe_route(logits, k, True)
+        got = ctx.dispatch_compute_combine(moe, x.to(dev), tw.to(dev), ids.to(dev))
+        want = ref.moe_forward(x, w13, w2, tw, ids)
+        err = float((got.cpu().float() - want.float()).abs().max())
+        if err > 0.05:
+            ok = False
+            msgs.append(f"iteration {it}: max err {err}")
+    torch.cuda.synchronize()
+    if ctx.fused_calls != 4 or not ctx.check_health():
+        ok = False
+        msgs.append(f"fused_calls={ctx.fused_calls} healthy={ctx.healthy}")
+    dist.barrier()
+    q.put((rank, ok, msgs))
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_expert_parallel_exchange_two_gpus():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 1000
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok, msgs in results:
+        assert ok, f"rank {rank}: {msgs}"

@@ -970,3 +970,59 @@ MSGL_API int msgl_attn_status(int reset) {
   }
   return v;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (see no_alloc.h): the split-KV partials live in an array that is part
+// of the library image instead of a caller-provided workspace.
+// ------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// In host code this name is only a handle for the runtime; the usable device address comes from
+// cudaGetSymbolAddress below. Handing the name itself to a kernel would pass a host address.
+static __device__ __align__(256) unsigned char g_attn_noalloc_ws[MSGL_ATTN_NOALLOC_WS_BYTES];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_ws_addr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace
+
+int msgl_paged_attention_noalloc(const void* kv_map, const void* q, void* out, const void* block_table,
+                                 int bt_stride, const void* cu_q, const void* seq_lens, const void* k_scale,
+                                 const void* v_scale, const void* mask, long long mask_stride, int B, int total_q,
+                                 int max_q, int hq, int hk, int head_dim, int page_size, int num_pages, int layer,
+                                 int num_layers, int kv_fp8, int causal, int window, int splits, float scale,
+                                 int dtype, cudaStream_t stream) {
+  if (splits < 1) splits = 1;
+  void* ws = nullptr;
+  if (splits > 1) {
+    const long long need = msgl_attn_workspace_floats(total_q, hq, head_dim, splits) * (long long)sizeof(float);
+    if (need > (long long)MSGL_ATTN_NOALLOC_WS_BYTES) {
+      msgl_set_error_text(("paged_attention_noalloc: the split partials need " + std::to_string(need) +
+                           " bytes but the built-in scratch holds " + std::to_string(MSGL_ATTN_NOALLOC_WS_BYTES) +
+                           "; use fewer splits or a smaller batch")
+                              .c_str());
+      return MSGL_BAD_ARG;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { msgl_set_error("paged_attention_noalloc: cudaGetDevice", e); return MSGL_CUDA_ERROR; }
+    if (dev < 0 || dev >= kNoAllocMaxDevices) {
+      msgl_set_error_text("paged_attention_noalloc: device index out of range");
+      return MSGL_BAD_ARG;
+    }
+    if (g_noalloc_ws_addr[dev] == nullptr) {
+      // once per device, with that device current: resolve the array's address on this GPU
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_attn_noalloc_ws);
+      if (e != cudaSuccess || p == nullptr) {
+        msgl_set_error("paged_attention_noalloc: cudaGetSymbolAddress", e);
+        return MSGL_CUDA_ERROR;
+      }
+      g_noalloc_ws_addr[dev] = p;
+    }
+    ws = g_noalloc_ws_addr[dev];
+  }
+  return msgl_paged_attention(kv_map, q, out, block_table, bt_stride, cu_q, seq_lens, k_scale, v_scale, mask,
+                              mask_stride, ws, B, total_q, max_q, hq, hk, head_dim, page_size, num_pages, layer,
+                              num_layers, kv_fp8, causal, window, splits, scale, dtype, stream);
+}

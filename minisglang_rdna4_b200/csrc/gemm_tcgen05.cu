@@ -284,6 +284,280 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------
+// CTA-pair variant for large M: a cluster of two CTAs on neighbouring SMs computes one
+// 256 x 256 output tile with cta_group::2 MMAs. Each CTA stages 128 rows of A and 128 rows of B
+// per K block and gets 128 x 256 of output for them, so a byte brought into shared memory feeds
+// twice the math of the 128 x 128 single-CTA tile; that tile is bound by shared-memory traffic
+// (tensor pipe under 30 % busy on the prefill projections), this one is not.
+//
+// Barriers: full[s] lives in the even CTA and counts the bytes of both CTAs' copies; empty[s],
+// tfull[a] exist in both CTAs and are signalled together by a multicast commit; tempty[a] lives
+// in the even CTA and collects the epilogue warps of both. 10 warps: TMA, MMA, 8 epilogue
+// (two per tensor-memory lane quarter, 128 columns each). The epilogue packs its columns into
+// registers, frees the accumulator, then stores, so the block-scaled kind, whose scale factors
+// leave room for one 256-column accumulator only, still overlaps its stores with the next tile.
+// ------------------------------------------------------------------------------------------
+constexpr int kPairThreads = 320;
+constexpr int kPairBN = 256;
+
+template <int KIND> struct PairCfg {
+  static constexpr int NACC = KIND == KIND_MXF4 ? 1 : 2;
+  static constexpr int STAGES = 6;
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = 128 * 128;
+  static constexpr int SF_BYTES = 1024;  // two 128-row scale atoms: every CTA needs all 256 columns' scales
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * A_BYTES;
+  static constexpr int off_sf = off_b + STAGES * B_BYTES;
+  static constexpr int off_sfa = off_sf + STAGES * SF_BYTES;
+  static constexpr int off_bar = off_sfa + 512;
+  static constexpr int n_bars = 2 * STAGES + 2 * NACC;
+  static constexpr int total = off_bar + n_bars * 8 + 16;
+  static constexpr uint32_t STAGE_TX =
+      KIND == KIND_MXF4 ? A_BYTES + B_BYTES / 2 + SF_BYTES : A_BYTES + B_BYTES;
+};
+
+__device__ __forceinline__ uint32_t pack2_out(int out_dtype, float x0, float x1) {
+  if (out_dtype == MSGL_BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(x0, x1);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(x0, x1);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kPairThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_sf, const GemmArgs args) {
+  using L = PairCfg<KIND>;
+  using KT = KindTraits<KIND>;
+  constexpr int NACC = L::NACC;
+  constexpr int STAGES = L::STAGES;
+  constexpr int NCOLS = 512;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_base = s_base + L::off_bar;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + NACC + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_bar + L::n_bars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_bar + L::n_bars * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int total_tiles = args.m_tiles * args.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < NACC; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 16);  // 8 epilogue warps in each of the two CTAs
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tma_a);
+    prefetch_tensormap(&tma_b);
+    if (KIND == KIND_MXF4) prefetch_tensormap(&tma_sf);
+  }
+  if (KIND == KIND_MXF4) {
+    for (int i = threadIdx.x; i < 128; i += blockDim.x)
+      reinterpret_cast<uint32_t*>(smem + L::off_sfa)[i] = 0x7F7F7F7Fu;
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), NCOLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the other CTA's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += num_pairs) {
+        const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+        const int m0 = m_tile * 256 + (int)rank * 128;
+        const int n0 = n_tile * kPairBN + (int)rank * 128;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 111)) break;
+          const uint32_t lead_full = mapa_cluster(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * L::STAGE_TX);
+          tma_load_2d_pair(s_base + L::off_a + stage * L::A_BYTES, &tma_a, lead_full, kb * KT::BKE, m0);
+          tma_load_2d_pair(s_base + L::off_b + stage * L::B_BYTES, &tma_b, lead_full, kb * KT::BKE, n0);
+          if (KIND == KIND_MXF4) {
+            const int atom0 = (n_tile * 2) * args.sf_k_atoms + kb;
+            tma_load_2d_pair(s_base + L::off_sf + stage * L::SF_BYTES, &tma_sf, lead_full, 0, atom0);
+            tma_load_2d_pair(s_base + L::off_sf + stage * L::SF_BYTES + 512, &tma_sf, lead_full, 0,
+                             atom0 + args.sf_k_atoms);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t sfa_tmem = tmem_base + NACC * kPairBN;
+      const uint32_t sfb_tmem = sfa_tmem + 4;
+      if (KIND == KIND_MXF4) tmem_cp_32x128b_warpx4_pair(sfa_tmem, smem_desc_sf(s_base + L::off_sfa));
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += num_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 112)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairBN;
+        bool ok = true;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 113)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_s = s_base + L::off_a + stage * L::A_BYTES;
+          const uint32_t b_s = s_base + L::off_b + stage * L::B_BYTES;
+          if (KIND == KIND_MXF4) {
+            const uint32_t sf_s = s_base + L::off_sf + stage * L::SF_BYTES;
+            tmem_cp_32x128b_warpx4_pair(sfb_tmem, smem_desc_sf(sf_s));
+            tmem_cp_32x128b_warpx4_pair(sfb_tmem + 4, smem_desc_sf(sf_s + 512));
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t a_desc = smem_desc_sw128(a_s + k * 32);
+            const uint64_t b_desc = smem_desc_sw128(b_s + k * 32);
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (KIND == KIND_F16) {
+              mma_f16_pair(d_tmem, a_desc, b_desc, idesc_dense(0, 0, 256, kPairBN), accum);
+            } else if (KIND == KIND_BF16) {
+              mma_f16_pair(d_tmem, a_desc, b_desc, idesc_dense(1, 1, 256, kPairBN), accum);
+            } else if (KIND == KIND_F8) {
+              mma_f8f6f4_pair(d_tmem, a_desc, b_desc, idesc_dense(0, 0, 256, kPairBN), accum);
+            } else {
+              mma_mxf8f6f4_pair(d_tmem, a_desc, b_desc, idesc_block_scaled(0, 5, 256, kPairBN, 0, (uint32_t)k),
+                                accum, sfa_tmem, sfb_tmem);
+            }
+          }
+          tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(acc), 3);
+        if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int q = warp & 3;          // tensor-memory lane quarter this warp may read
+    const int h = (warp - 2) >> 2;   // which 128 of the tile's 256 columns
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t lead_tempty0 = mapa_cluster(tempty_bar(0), 0);
+    for (int tile = pair; tile < total_tiles; tile += num_pairs) {
+      const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 114)) break;
+      tc_fence_after();
+      const int row = m_tile * 256 + (int)rank * 128 + q * 32 + lane;
+      const bool row_ok = row < args.M;
+      const float a_s = (args.a_scale != nullptr && row_ok) ? args.a_scale[row] : 1.f;
+      const int colbase = n_tile * kPairBN + h * 128;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + h * 128);
+      auto finish = [&](float x, int col) -> float {
+        x *= a_s;
+        if (args.b_scale != nullptr) x *= __ldg(args.b_scale + col);
+        if (args.bias != nullptr) {
+          x += args.bias_dtype == MSGL_BF16
+                   ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
+                   : (args.bias_dtype == MSGL_F16 ? __half2float(reinterpret_cast<const __half*>(args.bias)[col])
+                                                  : reinterpret_cast<const float*>(args.bias)[col]);
+        }
+        return x;
+      };
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+      };
+      if (args.out_dtype == MSGL_F32) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int col = colbase + c * 32 + j * 4;
+              if (col < args.N) {
+                float4 v;
+                v.x = finish(__uint_as_float(r[j * 4 + 0]), col + 0);
+                v.y = finish(__uint_as_float(r[j * 4 + 1]), col + 1);
+                v.z = finish(__uint_as_float(r[j * 4 + 2]), col + 2);
+                v.w = finish(__uint_as_float(r[j * 4 + 3]), col + 3);
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + col) = v;
+              }
+            }
+          }
+        }
+        release();
+      } else {
+        uint32_t packed[64];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = colbase + c * 32 + j * 8;
+            if (col < args.N) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                packed[c * 16 + j * 4 + e] =
+                    pack2_out(args.out_dtype, finish(__uint_as_float(r[j * 8 + 2 * e]), col + 2 * e),
+                              finish(__uint_as_float(r[j * 8 + 2 * e + 1]), col + 2 * e + 1));
+              }
+            }
+          }
+        }
+        release();
+        if (row_ok) {
+          uint16_t* crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
+#pragma unroll
+          for (int g = 0; g < 16; ++g) {
+            const int col = colbase + g * 8;
+            if (col < args.N)
+              *reinterpret_cast<uint4*>(crow + col) =
+                  make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+          }
+        }
+      }
+      if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, NCOLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
 struct MapKey {
@@ -309,8 +583,9 @@ std::mutex g_map_mutex;
 
 // 2-D K-major tensor map: dims {inner (elements), rows}, box {box_inner, box_rows}, 128B swizzle
 int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint64_t inner, uint64_t rows,
-                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, bool cache) {
-  MapKey key{ptr, inner, rows, row_stride_bytes, box_inner, box_rows, (int)dt};
+                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, bool cache,
+                bool swizzle = true) {
+  MapKey key{ptr, inner, rows, row_stride_bytes, box_inner, box_rows, (int)dt + (swizzle ? 0 : 1000)};
   if (cache) {
     std::lock_guard<std::mutex> g(g_map_mutex);
     auto it = g_map_cache.find(key);
@@ -323,7 +598,8 @@ int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint6
   cuuint32_t box[2] = {box_inner, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     msgl_set_error_text(("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r)).c_str());
@@ -376,6 +652,42 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& 
     default: return MSGL_BAD_ARG;
   }
 }
+
+// Launch the CTA-pair kernel: clusters of two, one cluster per pair of SMs, persistent over tiles.
+template <int KIND>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msf, GemmArgs& args, int max_ctas,
+                cudaStream_t stream) {
+  using L = PairCfg<KIND>;
+  constexpr int smem = L::total + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { msgl_set_error("pair gemm smem attribute", e); return MSGL_CUDA_ERROR; }
+    configured = true;
+  }
+  const int total = args.m_tiles * args.n_tiles;
+  int pairs = max_ctas / 2;
+  if (pairs > total) pairs = total;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND>, ma, mb, msf, args);
+  if (e != cudaSuccess) { msgl_set_error("gemm_pair launch", e); return MSGL_CUDA_ERROR; }
+  return MSGL_OK;
+}
+
+int g_pair_mode = 0;  // 0 = by size, 1 = never, 2 = whenever the arguments allow
 
 }  // namespace
 
@@ -443,7 +755,20 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.m_tiles = (M + BM - 1) / BM;
   // The block-scaled instruction takes its weight scale factors from tensor-memory columns in
   // steps of 64 rows (two columns), so the MXFP4 kind has no 32-wide N tile.
-  const int bn = bn_override ? bn_override : choose_bn(args.m_tiles, N, sms, kind == KIND_MXF4 ? 64 : 32, kind == KIND_MXF4 ? 64 : 128);
+  // Above 256 rows the CTA-pair kernel (256 x 256 tiles) takes over; below, a pair tile would be
+  // mostly padding and too few tiles would exist to fill the GPU.
+  const bool pair_ok = tile_expert == nullptr && (uintptr_t)sf_atoms % 16 == 0;
+  const bool use_pair =
+      pair_ok && (bn_override == 256 || (bn_override == 0 && g_pair_mode != 1 && (M > 256 || g_pair_mode == 2)));
+  if (bn_override == 256 && !pair_ok) {
+    msgl_set_error_text("gemm: the 256-wide CTA-pair tile does not support grouped operands");
+    return MSGL_BAD_ARG;
+  }
+  const int bn = use_pair ? 256
+                 : bn_override ? bn_override
+                               : choose_bn(args.m_tiles, N, sms, kind == KIND_MXF4 ? 64 : 32, kind == KIND_MXF4 ? 64 : 128);
+  if (use_pair) args.m_tiles = (M + 255) / 256;
+  const int b_box = use_pair ? 128 : bn;
   if (kind == KIND_MXF4 && bn == 32) {
     msgl_set_error_text("gemm: the MXFP4 kind supports N tiles of 64 and 128 only");
     return MSGL_BAD_ARG;
@@ -472,19 +797,34 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
     CUtensorMapDataType dt = kind == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     rc = make_map_2d(&ma, a, dt, K, M, (uint64_t)lda * 2, 64, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, dt, K, b_rows, (uint64_t)K * 2, 64, bn, true);
+    rc = make_map_2d(&mb, b, dt, K, b_rows, (uint64_t)K * 2, 64, b_box, true);
   } else if (kind == KIND_F8) {
     rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, b_rows, (uint64_t)K, 128, bn, true);
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, b_rows, (uint64_t)K, 128, b_box, true);
   } else if (kind == KIND_MXF4) {
     rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, b_rows, (uint64_t)K / 2, 128, bn, true);
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, b_rows, (uint64_t)K / 2, 128, b_box, true);
   } else {
     return MSGL_BAD_ARG;
   }
   if (rc) return rc;
+  if (use_pair) {
+    CUtensorMap msf = ma;  // placeholder for the kinds without scale atoms
+    if (kind == KIND_MXF4) {
+      // scale atoms as rows of 128 words: one tensor copy per 512-byte atom
+      const uint64_t atoms = (uint64_t)args.sf_n_atoms * (uint64_t)args.sf_k_atoms;
+      rc = make_map_2d(&msf, sf_atoms, CU_TENSOR_MAP_DATA_TYPE_UINT32, 128, atoms, 512, 128, 1, true, false);
+      if (rc) return rc;
+    }
+    switch (kind) {
+      case KIND_F16: return launch_pair<KIND_F16>(ma, mb, msf, args, max_ctas, stream);
+      case KIND_BF16: return launch_pair<KIND_BF16>(ma, mb, msf, args, max_ctas, stream);
+      case KIND_F8: return launch_pair<KIND_F8>(ma, mb, msf, args, max_ctas, stream);
+      default: return launch_pair<KIND_MXF4>(ma, mb, msf, args, max_ctas, stream);
+    }
+  }
   switch (kind) {
     case KIND_F16: return dispatch_bn<KIND_F16>(bn, ma, mb, args, max_ctas, stream);
     case KIND_BF16: return dispatch_bn<KIND_BF16>(bn, ma, mb, args, max_ctas, stream);
@@ -517,8 +857,17 @@ MSGL_API int msgl_gemm_grouped(int kind, const void* a, long long lda, const voi
                    tile_expert, num_experts, stream);
 }
 
+// Tile-shape policy of msgl_gemm when bn_override is 0: 0 = CTA-pair kernel above 256 rows,
+// 1 = single-CTA kernel always, 2 = CTA-pair kernel always. Returns the previous value.
+MSGL_API int msgl_gemm_pair_mode(int mode) {
+  const int prev = g_pair_mode;
+  if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+  return prev;
+}
+
 // 0 when no bounded wait of a GEMM kernel has run out since the last reset; else a code
-// (101 producer / 102 accumulator-free / 103 stage-full / 104 epilogue wait).
+// (101 producer / 102 accumulator-free / 103 stage-full / 104 epilogue wait; 111-114 the same
+// four waits of the CTA-pair kernel).
 MSGL_API int msgl_gemm_status(int reset) {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int));

@@ -292,6 +292,13 @@ def gemm_status(reset=True) -> int:
     return int(lib().msgl_gemm_status(int(reset)))
 
 
+def gemm_pair_mode(mode: int) -> int:
+    """Tile policy of the GEMM family: 0 = CTA-pair kernel (256 x 256 tiles, two SMs per tile)
+    above 256 rows, 1 = single-CTA kernel always, 2 = CTA-pair kernel always. Returns the
+    previous setting."""
+    return int(lib().msgl_gemm_pair_mode(int(mode)))
+
+
 def force_general_decode_attention(on: bool) -> None:
     """Route single-query batches through the general attention kernel. Speculative decoding
     sets this: verification rows run on the general kernel, and greedy output is only

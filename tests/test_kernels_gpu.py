@@ -118,14 +118,34 @@ def test_qk_norm_rope_store(K, fp8, qk_norm):
 def test_gemm_16bit(K, m, n, k, dtype):
     x = torch.randn(m, k, device="cuda").to(dtype)
     w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(dtype)
-    for bn in (0, 32, 64, 128):
+    for bn in (0, 32, 64, 128, 256):
         y = K.gemm(x, w, bn=bn)
         assert K.gemm_status() == 0
         _close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"gemm bn={bn}")
-    y32 = K.gemm(x, w, out_dtype=torch.float32)
-    _close(y32, x.float() @ w.float().t(), 1e-3, 1e-3, "gemm f32 out")
     bias = torch.randn(n, device="cuda").to(dtype)
-    _close(K.gemm(x, w, bias), x.float() @ w.float().t() + bias.float(), 2e-2, 2e-2, "bias")
+    for bn in (0, 128, 256):
+        y32 = K.gemm(x, w, out_dtype=torch.float32, bn=bn)
+        _close(y32, x.float() @ w.float().t(), 1e-3, 1e-3, f"gemm f32 out bn={bn}")
+        _close(K.gemm(x, w, bias, bn=bn), x.float() @ w.float().t() + bias.float(), 2e-2, 2e-2, f"bias bn={bn}")
+    assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(640, 1024, 2560), (257, 6144, 512), (4096, 2560, 9728)])
+def test_gemm_pair_kernel_matches_single_cta(K, m, n, k):
+    """The 256 x 256 CTA-pair tiles and the 128-wide single-CTA tiles accumulate every output
+    over the same K order in fp32, so the two kernels agree to the last bit."""
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).bfloat16()
+    single = K.gemm(x, w, bn=128)
+    pair = K.gemm(x, w, bn=256)
+    assert K.gemm_status() == 0
+    _close(pair, x.float() @ w.float().t(), 2e-2, 2e-2, "pair vs fp32")
+    assert torch.equal(pair, single)
+    prev = K.gemm_pair_mode(1)
+    try:
+        assert torch.equal(K.gemm(x, w), single)
+    finally:
+        K.gemm_pair_mode(prev)
 
 
 def test_gemm_m_invariance(K):
@@ -144,13 +164,14 @@ def test_gemm_w8a8(K, m, n, k):
     ws = w.abs().amax(-1) / 448
     wq = (w / ws[:, None]).to(torch.float8_e4m3fn)
     xq, xs = K.per_token_quant_fp8(x)
-    for bn in (0, 32, 64, 128):
+    for bn in (0, 32, 64, 128, 256):
         y = K.gemm_w8a8(xq, xs, wq, ws.float(), bn=bn)
         assert K.gemm_status() == 0
         _close(y, R.gemm_w8a8(xq, xs, wq, ws), 2e-2, 2e-2, f"w8a8 bn={bn}")
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (9, 256, 256), (256, 2560, 4096), (700, 6144, 2560), (64, 320, 1024)])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (9, 256, 256), (256, 2560, 4096), (700, 6144, 2560), (64, 320, 1024),
+                                   (2100, 2560, 9728)])
 def test_gemm_w4a8_mxfp4(K, m, n, k):
     R = _ref()
     from minisglang_rdna4_b200.quant import mxfp4
@@ -162,7 +183,7 @@ def test_gemm_w4a8_mxfp4(K, m, n, k):
     assert torch.equal(mxfp4.unpack_sf_atoms(atoms, n, k // 32), sf)
     xq, xs = K.per_token_quant_fp8(x)
     want = R.gemm_w4a8_mxfp4(xq, xs, packed, sf)
-    for bn in (128, 64, 0):
+    for bn in (128, 64, 0, 256):
         y = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms, bn=bn)
         assert K.gemm_status() == 0
         _close(y, want, 2e-2, 2e-2, f"mxfp4 bn={bn}")

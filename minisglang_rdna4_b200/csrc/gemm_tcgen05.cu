@@ -75,20 +75,18 @@ template <int BN, int STAGES> struct SmemLayout {
   static constexpr int off_b = off_a + STAGES * A_BYTES;
   static constexpr int off_sf = off_b + STAGES * B_BYTES;
   static constexpr int off_sfa = off_sf + STAGES * SF_BYTES;
-  static constexpr int off_bar = off_sfa + 512;
+  static constexpr int off_colv = off_sfa + 512;  // 4 epilogue warps x (BN scales + BN biases) fp32
+  static constexpr int off_bar = off_colv + 4 * 2 * BN * 4;
   static constexpr int total = off_bar + (2 * STAGES + 4) * 8 + 16;
 };
 
-__device__ __forceinline__ void store_out8(void* c, int out_dtype, size_t idx, const float (&v)[8]) {
+__device__ __forceinline__ uint32_t pack2_out(int out_dtype, float x0, float x1) {
   if (out_dtype == MSGL_BF16) {
-    store8(reinterpret_cast<__nv_bfloat16*>(c) + idx, v);
-  } else if (out_dtype == MSGL_F16) {
-    store8(reinterpret_cast<__half*>(c) + idx, v);
-  } else {
-    float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + idx);
-    p[0] = make_float4(v[0], v[1], v[2], v[3]);
-    p[1] = make_float4(v[4], v[5], v[6], v[7]);
+    __nv_bfloat162 v = __floats2bfloat162_rn(x0, x1);
+    return *reinterpret_cast<uint32_t*>(&v);
   }
+  __half2 v = __floats2half2_rn(x0, x1);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int KIND, int BN, int STAGES>
@@ -230,47 +228,95 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    // per-warp staging of the tile's column scales and bias: [0,BN) scale, [BN,2BN) bias
+    float* colv = reinterpret_cast<float*>(smem + L::off_colv) + (warp - 2) * 2 * BN;
+    const bool has_colv = args.b_scale != nullptr || args.bias != nullptr;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
       if (args.tile_expert != nullptr && args.tile_expert[m_tile] < 0) continue;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
-      tc_fence_after();
       const int row = m_tile * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
-      const float a_s = (args.a_scale != nullptr && row_ok) ? args.a_scale[row] : 1.f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
-        tmem_ld_wait();
-        const int col0 = n_tile * BN + c * 32;
-        if (row_ok) {
+      const int colbase = n_tile * BN;
+      // everything that does not depend on the accumulator is fetched before waiting for it
+      const float a_s = (args.a_scale != nullptr && row_ok) ? __ldg(args.a_scale + row) : 1.f;
+      if (has_colv) {
+        __syncwarp();
+        for (int i = lane; i < BN; i += 32) {
+          const int col = colbase + i;
+          float sc = 1.f, bi = 0.f;
+          if (col < args.N) {
+            if (args.b_scale != nullptr) sc = __ldg(args.b_scale + col);
+            if (args.bias != nullptr)
+              bi = args.bias_dtype == MSGL_BF16
+                       ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
+                       : (args.bias_dtype == MSGL_F16 ? __half2float(reinterpret_cast<const __half*>(args.bias)[col])
+                                                      : reinterpret_cast<const float*>(args.bias)[col]);
+          }
+          colv[i] = sc;
+          colv[BN + i] = bi;
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      if (args.out_dtype != MSGL_F32) {
+        // pack the whole row segment, hand the accumulator back, then store in one burst
+        // (stores interleaved with the conversion measured 2x slower)
+        uint32_t packed[BN / 2];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = col0 + j * 8;
-            if (col < args.N) {
-              float v[8];
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float x = __uint_as_float(r[j * 8 + e]) * a_s;
-                if (args.b_scale != nullptr) x *= __ldg(args.b_scale + col + e);
-                if (args.bias != nullptr) {
-                  x += args.bias_dtype == MSGL_BF16
-                           ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col + e])
-                           : (args.bias_dtype == MSGL_F16
-                                  ? __half2float(reinterpret_cast<const __half*>(args.bias)[col + e])
-                                  : reinterpret_cast<const float*>(args.bias)[col + e]);
-                }
-                v[e] = x;
-              }
-              store_out8(args.c, args.out_dtype, (size_t)row * args.ldc + col, v);
+          for (int e = 0; e < 16; ++e) {
+            const int lc = c * 32 + 2 * e;
+            float x0 = __uint_as_float(r[2 * e]) * a_s, x1 = __uint_as_float(r[2 * e + 1]) * a_s;
+            if (has_colv) {
+              x0 = fmaf(x0, colv[lc], colv[BN + lc]);
+              x1 = fmaf(x1, colv[lc + 1], colv[BN + lc + 1]);
             }
+            packed[c * 16 + e] = pack2_out(args.out_dtype, x0, x1);
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (row_ok) {
+          uint16_t* crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
+#pragma unroll
+          for (int g = 0; g < BN / 8; ++g) {
+            const int col = colbase + g * 8;
+            if (col < args.N)
+              *reinterpret_cast<uint4*>(crow + col) =
+                  make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float x = __uint_as_float(r[e]) * a_s;
+            if (has_colv) x = fmaf(x, colv[c * 32 + e], colv[BN + c * 32 + e]);
+            r[e] = __float_as_uint(x);
+          }
+          if (row_ok) {
+            float* crow = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + colbase + c * 32;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (colbase + c * 32 + g * 4 < args.N)
+                *reinterpret_cast<uint4*>(crow + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -310,21 +356,13 @@ template <int KIND> struct PairCfg {
   static constexpr int off_b = off_a + STAGES * A_BYTES;
   static constexpr int off_sf = off_b + STAGES * B_BYTES;
   static constexpr int off_sfa = off_sf + STAGES * SF_BYTES;
-  static constexpr int off_bar = off_sfa + 512;
+  static constexpr int off_colv = off_sfa + 512;       // 8 epilogue warps x (128 scales + 128 biases) fp32
+  static constexpr int off_bar = off_colv + 8 * 256 * 4;
   static constexpr int n_bars = 2 * STAGES + 2 * NACC;
   static constexpr int total = off_bar + n_bars * 8 + 16;
   static constexpr uint32_t STAGE_TX =
       KIND == KIND_MXF4 ? A_BYTES + B_BYTES / 2 + SF_BYTES : A_BYTES + B_BYTES;
 };
-
-__device__ __forceinline__ uint32_t pack2_out(int out_dtype, float x0, float x1) {
-  if (out_dtype == MSGL_BF16) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(x0, x1);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-  __half2 v = __floats2half2_rn(x0, x1);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 template <int KIND>
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -465,74 +503,67 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t lead_tempty0 = mapa_cluster(tempty_bar(0), 0);
+    // per-warp staging of the tile's column scales and bias: [0,128) scale, [128,256) bias
+    float* colv = reinterpret_cast<float*>(smem + L::off_colv) + (warp - 2) * 256;
+    const bool has_colv = args.b_scale != nullptr || args.bias != nullptr;
     for (int tile = pair; tile < total_tiles; tile += num_pairs) {
       const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 114)) break;
-      tc_fence_after();
       const int row = m_tile * 256 + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < args.M;
-      const float a_s = (args.a_scale != nullptr && row_ok) ? args.a_scale[row] : 1.f;
       const int colbase = n_tile * kPairBN + h * 128;
-      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + h * 128);
-      auto finish = [&](float x, int col) -> float {
-        x *= a_s;
-        if (args.b_scale != nullptr) x *= __ldg(args.b_scale + col);
-        if (args.bias != nullptr) {
-          x += args.bias_dtype == MSGL_BF16
-                   ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
-                   : (args.bias_dtype == MSGL_F16 ? __half2float(reinterpret_cast<const __half*>(args.bias)[col])
-                                                  : reinterpret_cast<const float*>(args.bias)[col]);
+      // everything that does not depend on the accumulator is fetched before waiting for it
+      const float a_s = (args.a_scale != nullptr && row_ok) ? __ldg(args.a_scale + row) : 1.f;
+      if (has_colv) {
+        __syncwarp();  // the previous tile's readers are done with the staging rows
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = colbase + i * 32 + lane;
+          float sc = 1.f, bi = 0.f;
+          if (col < args.N) {
+            if (args.b_scale != nullptr) sc = __ldg(args.b_scale + col);
+            if (args.bias != nullptr)
+              bi = args.bias_dtype == MSGL_BF16
+                       ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
+                       : (args.bias_dtype == MSGL_F16 ? __half2float(reinterpret_cast<const __half*>(args.bias)[col])
+                                                      : reinterpret_cast<const float*>(args.bias)[col]);
+          }
+          colv[i * 32 + lane] = sc;
+          colv[128 + i * 32 + lane] = bi;
         }
-        return x;
-      };
-      auto release = [&]() {
+        __syncwarp();
+      }
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 114)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + h * 128);
+      // Drain two 32-column loads at a time, fold the scales in and pack to the output type, hand
+      // the accumulator back, and only then store: 16 back-to-back 16-byte stores per thread
+      // (256 contiguous bytes of one row). Stores interleaved with the conversion measured 2x slower.
+      if (args.out_dtype != MSGL_F32) {
+        uint32_t packed[64];
+        uint32_t r0[32], r1[32];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          tmem_ld_32x32b_x32(t_addr + hh * 64, r0);
+          tmem_ld_32x32b_x32(t_addr + hh * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int c0 = hh * 64 + 2 * e, c1 = c0 + 32;
+            float x0 = __uint_as_float(r0[2 * e]) * a_s, x1 = __uint_as_float(r0[2 * e + 1]) * a_s;
+            float y0 = __uint_as_float(r1[2 * e]) * a_s, y1 = __uint_as_float(r1[2 * e + 1]) * a_s;
+            if (has_colv) {
+              x0 = fmaf(x0, colv[c0], colv[128 + c0]);
+              x1 = fmaf(x1, colv[c0 + 1], colv[128 + c0 + 1]);
+              y0 = fmaf(y0, colv[c1], colv[128 + c1]);
+              y1 = fmaf(y1, colv[c1 + 1], colv[128 + c1 + 1]);
+            }
+            packed[hh * 32 + e] = pack2_out(args.out_dtype, x0, x1);
+            packed[hh * 32 + 16 + e] = pack2_out(args.out_dtype, y0, y1);
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
-      };
-      if (args.out_dtype == MSGL_F32) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_addr + c * 32, r);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int col = colbase + c * 32 + j * 4;
-              if (col < args.N) {
-                float4 v;
-                v.x = finish(__uint_as_float(r[j * 4 + 0]), col + 0);
-                v.y = finish(__uint_as_float(r[j * 4 + 1]), col + 1);
-                v.z = finish(__uint_as_float(r[j * 4 + 2]), col + 2);
-                v.w = finish(__uint_as_float(r[j * 4 + 3]), col + 3);
-                *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + col) = v;
-              }
-            }
-          }
-        }
-        release();
-      } else {
-        uint32_t packed[64];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = colbase + c * 32 + j * 8;
-            if (col < args.N) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                packed[c * 16 + j * 4 + e] =
-                    pack2_out(args.out_dtype, finish(__uint_as_float(r[j * 8 + 2 * e]), col + 2 * e),
-                              finish(__uint_as_float(r[j * 8 + 2 * e + 1]), col + 2 * e + 1));
-              }
-            }
-          }
-        }
-        release();
         if (row_ok) {
           uint16_t* crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
 #pragma unroll
@@ -542,6 +573,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               *reinterpret_cast<uint4*>(crow + col) =
                   make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
           }
+        }
+      } else {
+        // fp32 output (logits): all 128 columns stay in registers until the burst of stores
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tmem_ld_32x32b_x32(t_addr, r0);
+        tmem_ld_32x32b_x32(t_addr + 32, r1);
+        tmem_ld_32x32b_x32(t_addr + 64, r2);
+        tmem_ld_32x32b_x32(t_addr + 96, r3);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
+        auto scale_in_place = [&](uint32_t (&r)[32], int c) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float x = __uint_as_float(r[e]) * a_s;
+            if (has_colv) x = fmaf(x, colv[c * 32 + e], colv[128 + c * 32 + e]);
+            r[e] = __float_as_uint(x);
+          }
+        };
+        scale_in_place(r0, 0);
+        scale_in_place(r1, 1);
+        scale_in_place(r2, 2);
+        scale_in_place(r3, 3);
+        if (row_ok) {
+          float* crow = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + colbase;
+          auto burst = [&](const uint32_t (&r)[32], int c) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (colbase + c * 32 + g * 4 < args.N)
+                *reinterpret_cast<uint4*>(crow + c * 32 + g * 4) =
+                    make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          };
+          burst(r0, 0);
+          burst(r1, 1);
+          burst(r2, 2);
+          burst(r3, 3);
         }
       }
       if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }

@@ -181,6 +181,162 @@ int launch_ar(const ArArgs& a, cudaStream_t stream) {
   return MSGL_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Reduce-scatter consumer fused with residual add + RMSNorm (+ e4m3 producer) + all-gather.
+//
+// The row-parallel GEMM before this kernel pushed its partial rows straight into the slots of
+// the rank that owns each row (gemm_tcgen05.cu, rs_* arguments). 128-row block b belongs to rank
+// b % nranks and is its local block b / nranks. One CTA per owned row: wait (bounded) until all sources have delivered the
+// row's 128-row block, sum the partials in rank order, add the residual (kept only for owned
+// rows: the residual stream is sharded by rows between these calls), normalise, and store the
+// normed row into EVERY rank's activation buffer (P2P stores). The CTA that completes a
+// 128-row block raises that block's ready flag on every rank; the next column-parallel GEMM
+// waits on those flags block by block in its TMA producer, so the gather overlaps its math.
+// ------------------------------------------------------------------------------------------
+struct RsArgs {
+  const void* slots;          // local: [src][local block][128][ld]
+  const uint32_t* flags;      // local: [src][flag_stride]
+  void* residual;             // [M, hidden]; rows of this rank are read and rewritten
+  const void* weight;
+  void* out[kMaxRanks];       // per destination: 16-bit [M, hidden] (when not quantising)
+  uint8_t* out_q[kMaxRanks];  // per destination: e4m3 [M, hidden]
+  float* out_scale[kMaxRanks];
+  uint32_t* ready[kMaxRanks];  // per destination: [M / 128]
+  uint32_t* count;            // local self-resetting per-block row counters
+  int* status;
+  long long plane;
+  int ld, rank, nranks, flag_stride, hidden;
+  uint32_t rs_seq, ag_seq;
+  float eps, w_offset;
+  unsigned long long wait_ns;
+};
+
+template <typename T, bool QUANT>
+__global__ void __launch_bounds__(1024) rs_norm_ag_kernel(const RsArgs a) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[32];
+  const int lrow = blockIdx.x;
+  const int lblk = lrow >> 7;
+  const int gblk = lblk * a.nranks + a.rank;
+  const int grow = (gblk << 7) + (lrow & 127);
+  const int H = a.hidden;
+  if (threadIdx.x < a.nranks) {
+    const uint32_t* f = a.flags + (size_t)threadIdx.x * a.flag_stride + lblk;
+    if ((int)(ld_acquire_sys(f) - a.rs_seq) < 0) {
+      const unsigned long long t0 = gtimer();
+      while ((int)(ld_acquire_sys(f) - a.rs_seq) < 0) {
+        if (gtimer() - t0 > a.wait_ns) {
+          atomicCAS(a.status, 0, 320 + threadIdx.x);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const T* base = reinterpret_cast<const T*>(a.slots) + (size_t)lrow * a.ld;
+  T* rr = reinterpret_cast<T*>(a.residual) + (size_t)grow * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float acc[8], r[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int q = 0; q < a.nranks; ++q) {
+      float v[8];
+      load8(base + (size_t)q * a.plane + i, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    load8(rr + i, r);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] += r[k];
+    store8(rr + i, acc);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      acc[k] = to_float(from_float<T>(acc[k]));
+      ss += acc[k] * acc[k];
+      row_s[i + k] = acc[k];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + a.eps);
+  const T* w = reinterpret_cast<const T*>(a.weight);
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float wv[8], y[8];
+    load8(w + i, wv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + a.w_offset)));
+      if (QUANT) {
+        amax = fmaxf(amax, fabsf(y[k]));
+        row_s[i + k] = y[k];
+      }
+    }
+    if (!QUANT) {
+      for (int p = 0; p < a.nranks; ++p) store8(reinterpret_cast<T*>(a.out[p]) + (size_t)grow * H + i, y);
+    }
+  }
+  if (QUANT) {
+    amax = block_max(amax, scratch);
+    const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+    if (threadIdx.x < a.nranks) a.out_scale[threadIdx.x][grow] = scale;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float y[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
+      const uint2 packed = pack8_e4m3(y, scale);
+      for (int p = 0; p < a.nranks; ++p) *reinterpret_cast<uint2*>(a.out_q[p] + (size_t)grow * H + i) = packed;
+    }
+  }
+  // publish: every thread's peer stores are fenced before the row is counted; the CTA that
+  // completes the 128-row block raises the block's flag everywhere
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t seen = atomicAdd(a.count + lblk, 1u);
+    if (seen + 1u == 128u) {
+      a.count[lblk] = 0u;
+      __threadfence_system();
+      for (int p = 0; p < a.nranks; ++p) st_release_sys(a.ready[p] + gblk, a.ag_seq);
+    }
+  }
+}
+
+// Bounded wait until flags[0..n) have all reached `seq`: for consumers of gathered rows that
+// are not a GEMM with its own per-block wait.
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t seq, unsigned long long wait_ns,
+                                  int* status) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    if ((int)(ld_acquire_sys(flags + i) - seq) >= 0) continue;
+    const unsigned long long t0 = gtimer();
+    while ((int)(ld_acquire_sys(flags + i) - seq) < 0) {
+      if (gtimer() - t0 > wait_ns) {
+        atomicCAS(status, 0, 340);
+        break;
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_rs(const RsArgs& a, int owned_rows, bool quant, cudaStream_t stream) {
+  int threads = ((a.hidden / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  const size_t smem = (size_t)a.hidden * sizeof(float);
+  if (quant) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(rs_norm_ag_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rs_norm_ag_kernel<T, true><<<owned_rows, threads, smem, stream>>>(a);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(rs_norm_ag_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rs_norm_ag_kernel<T, false><<<owned_rows, threads, smem, stream>>>(a);
+  }
+  MSGL_CHECK_LAUNCH("rs_norm_ag");
+  return MSGL_OK;
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- symmetric memory plumbing
@@ -245,6 +401,52 @@ MSGL_API int msgl_ar_oneshot(const void* x, void* residual, const void* weight, 
   if (dtype == MSGL_BF16) return launch_ar<__nv_bfloat16>(a, stream);
   if (dtype == MSGL_F16) return launch_ar<__half>(a, stream);
   return MSGL_BAD_ARG;
+}
+
+// Consumer of a GEMM -> reduce-scatter push (see rs_norm_ag_kernel). slots / flags / count are
+// this rank's own regions; out / out_q / out_scale / ready are arrays of `nranks` peer-mapped
+// pointers. quant != 0 writes e4m3 rows + scales, else 16-bit rows.
+MSGL_API int msgl_rs_norm_ag(const void* slots, const void* flags, void* residual, const void* weight,
+                             void* const* out, void* const* out_q, void* const* out_scale, void* const* ready,
+                             void* count, long long plane, int ld, int rank, int nranks, int rows,
+                             int flag_stride, int hidden, unsigned int rs_seq, unsigned int ag_seq, float eps, int plus_one,
+                             int quant, long long wait_us, int dtype, cudaStream_t stream) {
+  if (nranks > kMaxRanks || hidden % 8 || hidden > 48 * 1024 || rows <= 0 || rows % 128) {
+    msgl_set_error_text("rs_norm_ag: unsupported shape");
+    return MSGL_BAD_ARG;
+  }
+  const int blocks = rows / 128;
+  const int owned_blocks = (blocks - rank + nranks - 1) / nranks;  // blocks rank, rank + nranks, ...
+  if (owned_blocks <= 0) return MSGL_OK;
+  const int owned_rows = owned_blocks * 128;
+  RsArgs a;
+  a.slots = slots; a.flags = (const uint32_t*)flags; a.residual = residual; a.weight = weight;
+  for (int p = 0; p < nranks; ++p) {
+    a.out[p] = out ? out[p] : nullptr;
+    a.out_q[p] = out_q ? (uint8_t*)out_q[p] : nullptr;
+    a.out_scale[p] = out_scale ? (float*)out_scale[p] : nullptr;
+    a.ready[p] = (uint32_t*)ready[p];
+  }
+  a.count = (uint32_t*)count;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_comm_status);
+  a.status = status;
+  a.plane = plane; a.ld = ld; a.rank = rank; a.nranks = nranks; a.flag_stride = flag_stride; a.hidden = hidden;
+  a.rs_seq = rs_seq; a.ag_seq = ag_seq; a.eps = eps; a.w_offset = plus_one ? 1.f : 0.f;
+  a.wait_ns = (unsigned long long)wait_us * 1000ull;
+  if (dtype == MSGL_BF16) return launch_rs<__nv_bfloat16>(a, owned_rows, quant != 0, stream);
+  if (dtype == MSGL_F16) return launch_rs<__half>(a, owned_rows, quant != 0, stream);
+  return MSGL_BAD_ARG;
+}
+
+MSGL_API int msgl_wait_flags(const void* flags, int n, unsigned int seq, long long wait_us, cudaStream_t stream) {
+  if (n <= 0) return MSGL_OK;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_comm_status);
+  wait_flags_kernel<<<1, 256, 0, stream>>>((const uint32_t*)flags, n, seq, (unsigned long long)wait_us * 1000ull,
+                                           status);
+  MSGL_CHECK_LAUNCH("wait_flags");
+  return MSGL_OK;
 }
 
 MSGL_API int msgl_comm_status(int reset) {

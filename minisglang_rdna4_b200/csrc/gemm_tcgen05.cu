@@ -52,9 +52,49 @@ struct GemmArgs {
   const int32_t* tile_expert;
   int sf_n_atoms;          // scale-factor atoms along N per expert
   int* status;
+  // ---- tensor-parallel fusion (CTA-pair kernel only) -------------------------------------
+  // Row-parallel GEMM -> reduce-scatter: instead of writing C locally, the epilogue stores each
+  // partial row into the slot of the rank that owns that row (peer memory, plain st.global).
+  // When the last warp of a 128-row block has stored, that rank's flag for (this rank, block)
+  // is set to rs_seq.
+  // 128-row block b of M belongs to rank b % world and is that rank's local block b / world.
+  void* rs_slots[8];        // rs_slots[o]: owner o's region [src][local block][128][rs_ld] (16-bit)
+  uint32_t* rs_flags[8];    // rs_flags[o]: owner o's flags [src][rs_flag_stride]
+  uint32_t* rs_count;       // local self-resetting arrival counters, one per 128-row block of M
+  long long rs_plane;       // elements between source planes of a slot region
+  int rs_world, rs_rank, rs_flag_stride, rs_ld;
+  uint32_t rs_seq, rs_arrivals;  // arrivals per block = 8 warps x N tiles
+  // All-gather -> column-parallel GEMM: A rows arrive from their owners; a_ready[b] reaches
+  // a_ready_seq once 128-row block b is complete in local memory.
+  const uint32_t* a_ready;
+  uint32_t a_ready_seq;
+  unsigned long long comm_wait_ns;
+  int tile_order;           // 0: M fastest; w > 1: N fastest with M tiles interleaved over w owners
 };
 
 __device__ int g_gemm_status = 0;
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// tile index -> (m_tile, n_tile). order 0: M fastest (weights reused across a wave). order 1:
+// N fastest, so that 128-row blocks complete (and are needed) one after the other; row blocks
+// belong to the ranks round-robin, so consecutive M tiles also alternate between owners.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int order, int& m_tile,
+                                            int& n_tile) {
+  if (order <= 0) {
+    m_tile = tile % m_tiles;
+    n_tile = tile / m_tiles;
+  } else {
+    m_tile = tile / n_tiles;
+    n_tile = tile % n_tiles;
+  }
+}
 
 template <int KIND> struct KindTraits;
 template <> struct KindTraits<KIND_F16> { static constexpr int BKE = 64; };
@@ -426,9 +466,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = pair; tile < total_tiles && !*abort_flag; tile += num_pairs) {
-        const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+        int m_tile, n_tile;
+        tile_coords(tile, args.m_tiles, args.n_tiles, args.tile_order, m_tile, n_tile);
         const int m0 = m_tile * 256 + (int)rank * 128;
         const int n0 = n_tile * kPairBN + (int)rank * 128;
+        if (args.a_ready != nullptr && m0 < args.M) {
+          // the 128 rows this CTA stages are written by their owner rank: wait (bounded) for them
+          const uint32_t* flag = args.a_ready + (m0 >> 7);
+          if ((int)(ld_acquire_sys_u32(flag) - args.a_ready_seq) < 0) {
+            const uint64_t t0 = globaltimer_ns();
+            while ((int)(ld_acquire_sys_u32(flag) - args.a_ready_seq) < 0) {
+              if (*abort_flag) break;
+              if (globaltimer_ns() - t0 > args.comm_wait_ns) {
+                *abort_flag = 1;
+                atomicCAS(args.status, 0, 115);
+                break;
+              }
+            }
+            if (*abort_flag) break;
+          }
+          // rows stored by a peer through the generic proxy are about to be read by TMA
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 111)) break;
           const uint32_t lead_full = mapa_cluster(full_bar(stage), 0);
@@ -507,12 +566,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     float* colv = reinterpret_cast<float*>(smem + L::off_colv) + (warp - 2) * 256;
     const bool has_colv = args.b_scale != nullptr || args.bias != nullptr;
     for (int tile = pair; tile < total_tiles; tile += num_pairs) {
-      const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+      int m_tile, n_tile;
+      tile_coords(tile, args.m_tiles, args.n_tiles, args.tile_order, m_tile, n_tile);
       const int row = m_tile * 256 + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < args.M;
       const int colbase = n_tile * kPairBN + h * 128;
       // everything that does not depend on the accumulator is fetched before waiting for it
-      const float a_s = (args.a_scale != nullptr && row_ok) ? __ldg(args.a_scale + row) : 1.f;
+      // (rows that are still arriving from a peer have their scale read after the wait instead)
+      float a_s = (args.a_scale != nullptr && row_ok && args.a_ready == nullptr) ? __ldg(args.a_scale + row) : 1.f;
       if (has_colv) {
         __syncwarp();  // the previous tile's readers are done with the staging rows
 #pragma unroll
@@ -534,6 +595,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 114)) break;
       tc_fence_after();
+      if (args.a_ready != nullptr && args.a_scale != nullptr && row_ok)
+        a_s = *reinterpret_cast<const volatile float*>(args.a_scale + row);
       const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + h * 128);
       // Drain two 32-column loads at a time, fold the scales in and pack to the output type, hand
       // the accumulator back, and only then store: 16 back-to-back 16-byte stores per thread
@@ -565,13 +628,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
         if (row_ok) {
-          uint16_t* crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
+          uint16_t* crow;
+          if (args.rs_world > 0) {
+            const int blk = row >> 7;
+            const int owner = blk % args.rs_world;
+            crow = reinterpret_cast<uint16_t*>(args.rs_slots[owner]) + (size_t)args.rs_rank * args.rs_plane +
+                   (size_t)((blk / args.rs_world) * 128 + (row & 127)) * args.rs_ld;
+          } else {
+            crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
+          }
 #pragma unroll
           for (int g = 0; g < 16; ++g) {
             const int col = colbase + g * 8;
             if (col < args.N)
               *reinterpret_cast<uint4*>(crow + col) =
                   make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+          }
+        }
+        if (args.rs_world > 0) {
+          // Count this warp's 32 rows x 128 columns as delivered. The warp that completes the
+          // 128-row block tells the owner; the counter resets itself for the next call.
+          __threadfence_system();
+          __syncwarp();
+          const int blk = (m_tile * 256 + (int)rank * 128) >> 7;
+          if (lane == 0 && (blk << 7) < args.M) {
+            const uint32_t seen = atomicAdd(args.rs_count + blk, 1u);
+            if (seen + 1u == args.rs_arrivals) {
+              args.rs_count[blk] = 0u;
+              __threadfence_system();
+              const int owner = blk % args.rs_world;
+              st_release_sys_u32(args.rs_flags[owner] + (size_t)args.rs_rank * args.rs_flag_stride + blk / args.rs_world,
+                                 args.rs_seq);
+            }
           }
         }
       } else {
@@ -792,6 +880,21 @@ static int choose_bn(int m_tiles, int n, int sms, int smallest, int b_row_bytes)
   return best;
 }
 
+// Tensor-parallel fusion arguments of msgl_gemm_tp (mirrored by a ctypes.Structure).
+struct MsglGemmTp {
+  void* rs_slots[8];       // per owner rank: slot region base for this call's parity (peer-mapped)
+  void* rs_flags[8];       // per owner rank: flag region base
+  void* rs_count;          // local arrival counters [M / 128], zero between calls
+  long long rs_plane;      // elements between source planes
+  int rs_world;            // 0: write C locally; > 0: push row blocks to their owners (block b -> rank b % world)
+  int rs_rank, rs_flag_stride, rs_ld;
+  unsigned int rs_seq;
+  unsigned int a_ready_seq;
+  const void* a_ready;     // nullptr: A is local and complete
+  long long wait_us;       // bound of the device-side flag waits
+  int order_world;         // > 1: N-fastest tile walk (row blocks complete / are needed in order)
+};
+
 // a: [M, K] (kind 0/1: 16-bit, kind 2/3: e4m3 bytes), row stride lda elements
 // b: [N, K] (kind 0/1: 16-bit, kind 2: e4m3 bytes, kind 3: packed e2m1 [N, K/2])
 // c: [M, N] out_dtype, row stride ldc elements
@@ -799,8 +902,15 @@ static int choose_bn(int m_tiles, int n, int sms, int smallest, int b_row_bytes)
 static int gemm_impl(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
                      int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
                      const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, const void* tile_expert,
-                     int num_experts, cudaStream_t stream) {
+                     int num_experts, cudaStream_t stream, const MsglGemmTp* tp = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? MSGL_OK : MSGL_BAD_ARG;
+  if (tp != nullptr) {
+    if (tile_expert != nullptr || M % 128 || (tp->rs_world > 0 && out_dtype == MSGL_F32)) {
+      msgl_set_error_text("gemm_tp: needs M a multiple of 128, 16-bit output and ungrouped operands");
+      return MSGL_BAD_ARG;
+    }
+    bn_override = 256;
+  }
   if (N % 8) { msgl_set_error_text("gemm: N must be a multiple of 8"); return MSGL_BAD_ARG; }
   const int esize_a = (kind == KIND_F16 || kind == KIND_BF16) ? 2 : 1;
   if ((lda * esize_a) % 16 || (uintptr_t)a % 16 || (uintptr_t)b % 16 || (uintptr_t)c % 16) {
@@ -854,6 +964,28 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.sf_k_atoms = (K + 127) / 128;
   args.sf_n_atoms = (N + 127) / 128;
   args.tile_expert = (const int32_t*)tile_expert;
+  args.rs_world = 0;
+  args.a_ready = nullptr;
+  args.tile_order = 0;
+  args.comm_wait_ns = 0;
+  if (tp != nullptr) {
+    for (int i = 0; i < 8; ++i) {
+      args.rs_slots[i] = tp->rs_slots[i];
+      args.rs_flags[i] = (uint32_t*)tp->rs_flags[i];
+    }
+    args.rs_count = (uint32_t*)tp->rs_count;
+    args.rs_plane = tp->rs_plane;
+    args.rs_world = tp->rs_world;
+    args.rs_rank = tp->rs_rank;
+    args.rs_flag_stride = tp->rs_flag_stride;
+    args.rs_ld = tp->rs_ld;
+    args.rs_seq = tp->rs_seq;
+    args.rs_arrivals = 8u * (uint32_t)((N + 255) / 256);
+    args.a_ready = (const uint32_t*)tp->a_ready;
+    args.a_ready_seq = tp->a_ready_seq;
+    args.comm_wait_ns = (unsigned long long)(tp->wait_us > 0 ? tp->wait_us : 500000) * 1000ull;
+    args.tile_order = tp->order_world > 1 ? 1 : 0;
+  }
   const uint64_t b_rows = (uint64_t)N * (uint64_t)(num_experts > 0 ? num_experts : 1);
   int* status = nullptr;
   cudaGetSymbolAddress((void**)&status, g_gemm_status);
@@ -906,6 +1038,17 @@ MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, vo
                        const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, cudaStream_t stream) {
   return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, out_dtype,
                    bn_override, max_ctas, nullptr, 0, stream);
+}
+
+// msgl_gemm with the tensor-parallel fusions of the CTA-pair kernel: the epilogue can push its
+// partial rows to the ranks that own them (GEMM -> reduce-scatter), and the producer can wait
+// for A row blocks that other ranks are still delivering (all-gather -> GEMM).
+MSGL_API int msgl_gemm_tp(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
+                          int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
+                          const void* sf_atoms, int out_dtype, const MsglGemmTp* tp, cudaStream_t stream) {
+  if (tp == nullptr) return MSGL_BAD_ARG;
+  return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, out_dtype, 256, 0,
+                   nullptr, 0, stream, tp);
 }
 
 // Grouped GEMM over expert-sorted rows: a [M, K] (M a multiple of 128), b [experts * N, K],

@@ -261,8 +261,12 @@ class Engine:
                 try:
                     from ..parallel.symm import SymmetricCollectives
 
-                    comm.register(SymmetricCollectives(self.tp_group, self.cpu_group, self.device,
-                                                       cfg.tp_rank, cfg.tp_size))
+                    symm = SymmetricCollectives(self.tp_group, self.cpu_group, self.device, cfg.tp_rank, cfg.tp_size)
+                    comm.register(symm)
+                    if not ENV.DISABLE_ROW_SHARD.value and not self.model_config.is_moe:
+                        # prefill chunks: GEMM -> reduce-scatter -> add + norm -> all-gather -> GEMM
+                        symm.enable_row_shard(int(getattr(cfg, "max_extend_tokens", 8192)),
+                                              self.model_config.hidden_size)
                 except Exception as exc:  # falls back to the NCCL data plane, loudly
                     logger.warning("symmetric-memory collectives unavailable (%s); using NCCL only", exc)
 
@@ -402,6 +406,19 @@ class Engine:
                 bt[:bs] = plan.block_table
                 plan = StepPlan(tok, pos, loc, plan.cu_q, lens, bt, plan.sample_rows, plan.write_idx,
                                 plan.max_q, plan.max_kv)
+        elif self._row_shard_rows(int(plan.token_idx.size)):
+            # Tensor-parallel prefill: the fused reduce-scatter / all-gather GEMMs move rows in
+            # blocks of 128, so the step is padded with rows that belong to no request (dummy
+            # token, dummy KV slot; attention never looks at them, nothing samples them).
+            t = int(plan.token_idx.size)
+            pad = (-t) % 128
+            if pad:
+                d_tok = np.full(pad, (self.num_slots - 1) * self.max_seq_len, dtype=np.int32)
+                d_loc = np.full(pad, self.kv_cache.dummy_page * self.page_size, dtype=np.int32)
+                plan = StepPlan(np.concatenate([plan.token_idx, d_tok]),
+                                np.concatenate([plan.positions, np.zeros(pad, dtype=np.int32)]),
+                                np.concatenate([plan.out_loc, d_loc]), plan.cu_q, plan.seq_lens, plan.block_table,
+                                plan.sample_rows, plan.write_idx, plan.max_q, plan.max_kv)
         token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
         batch.positions = positions
         batch.out_loc = out_loc
@@ -442,6 +459,16 @@ class Engine:
             host_out = tokens.clone()
         self.d2h_bytes += 4 * n_sample
         return ForwardOutput(tokens, host_out, event, sample, logits if return_logits else None)
+
+    def _row_shard_rows(self, tokens: int) -> bool:
+        """Whether a step of ``tokens`` rows takes the row-sharded tensor-parallel path."""
+        if self.config.tp_size == 1 or self.model_config.is_moe:
+            return False
+        for impl in comm_mod.get_comm().impls:
+            rs = getattr(impl, "row_shard", None)
+            if rs is not None:
+                return impl.max_rows < tokens <= rs.max_rows
+        return False
 
     def _agree_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
         """All tensor-parallel ranks adopt rank 0's ids

@@ -131,6 +131,7 @@ ENV.flag("FEEDBACK_CHECK", False, "verify that the token fed to step n+1 is the 
 # --- distributed --------------------------------------------------------------------------
 ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
+ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of the fused reduce-scatter / all-gather GEMMs")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger use two-shot")
 ENV.int("COMM_WAIT_US", 500_000, "bound of every device-side flag wait, in microseconds")

@@ -43,6 +43,16 @@ class _LinearBase(BaseOP):
         self._method.process_after_load(self)
 
     def _mm(self, x: LinearInput) -> torch.Tensor:
+        ready = getattr(x, "ready", None)
+        if ready is not None:
+            # rows that peers are still delivering: the GEMM waits per 128-row block
+            from ..ops import cuda as K
+
+            K.set_next_gemm_tp(ready.gemm_args())
+            y = self._method.apply(self, x, getattr(self, "bias", None))
+            if K.take_pending_gemm_tp() is not None:
+                raise RuntimeError("linear method did not consume the pending all-gather arguments")
+            return y
         return self._method.apply(self, x, getattr(self, "bias", None))
 
     def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
@@ -104,10 +114,23 @@ class RowParallelLinear(_LinearBase):
         super().__init__(n, div_even(k, tp.size), dtype, device, scheme, bias)
         self._tp_rank = tp.rank
 
-    def forward(self, x: LinearInput, reduce: bool = False) -> torch.Tensor:
+    def forward(self, x: LinearInput, reduce: bool = False):
         # the bias must be added once, not once per rank
-        if hasattr(self, "bias") and self._tp_rank != 0:
-            y = self._method.apply(self, x, None)
-        else:
-            y = self._mm(x)
-        return get_comm().all_reduce(y) if reduce else y
+        bias = getattr(self, "bias", None) if self._tp_rank == 0 else None
+        comm = get_comm()
+        if not reduce and comm.size > 1:
+            rows = x.shape[0] if len(x.shape) == 2 else 0
+            plan = comm.rs_begin(rows, self._n, self._compute_dtype) if rows else None
+            if plan is not None:
+                # GEMM -> reduce-scatter: the epilogue stores every partial row block into the
+                # memory of the rank that owns it; nothing is written locally
+                from ..ops import cuda as K
+                from ..parallel.symm import PushedPartial
+
+                K.set_next_gemm_tp(comm.rs_gemm_args(plan))
+                self._method.apply(self, x, bias)
+                if K.take_pending_gemm_tp() is not None:
+                    raise RuntimeError("linear method did not consume the pending reduce-scatter arguments")
+                return PushedPartial(plan, (rows, self._n), self._compute_dtype)
+        y = self._method.apply(self, x, bias)
+        return comm.all_reduce(y) if reduce else y

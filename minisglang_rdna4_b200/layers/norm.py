@@ -24,11 +24,29 @@ class RMSNorm(BaseOP):
         return ops.rms_norm(x, self.weight, self._eps, self._plus_one)
 
     def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor], *, partial: bool = False,
-                      quant: bool = False) -> Tuple[Union[torch.Tensor, ActQ], torch.Tensor]:
+                      quant: bool = False, to_gemm: bool = False) -> Tuple[Union[torch.Tensor, ActQ], torch.Tensor]:
         """Returns ``(normed, residual)``. ``residual`` None: the stream starts here
         (residual = x). ``partial``: ``x`` still needs the tensor-parallel all-reduce, which is
-        fused with the add and the norm. ``quant``: return an ``ActQ`` pair instead of 16-bit."""
+        fused with the add and the norm. ``quant``: return an ``ActQ`` pair instead of 16-bit.
+
+        ``x`` may be a ``PushedPartial`` (the row-parallel GEMM already pushed its rows to their
+        owners): this rank then reduces, adds and normalises only the rows it owns and stores
+        the result into every rank's buffer. ``residual`` is from then on valid for owned rows
+        only. With ``to_gemm`` the caller promises that the normed rows go straight into a
+        linear layer, which waits for them block by block; otherwise the wait happens here."""
         comm = get_comm()
+        if not isinstance(x, torch.Tensor):  # PushedPartial
+            if residual is None:
+                raise ValueError("a pushed partial sum needs a residual stream")
+            q, s, ready = comm.rs_finish(x.plan, residual, self.weight, self._eps, quant, self._plus_one)
+            if not to_gemm:
+                comm.wait_ready(ready)
+                ready = None
+            if quant:
+                return ActQ(q, s, ready), residual
+            if ready is not None:
+                q.ready = ready
+            return q, residual
         if residual is None:
             if partial and comm.size > 1:
                 x = comm.all_reduce(x)

@@ -129,14 +129,14 @@ class DecoderLayer(BaseOP):
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor], partial: bool):
         h, residual = self.input_layernorm.forward_fused(
-            x, residual, partial=partial, quant=self.self_attn.qkv_proj.wants_act_quant)
+            x, residual, partial=partial, quant=self.self_attn.qkv_proj.wants_act_quant, to_gemm=True)
         h = self.self_attn.forward(h)
         if self._is_moe:
             h, residual = self.post_attention_layernorm.forward_fused(h, residual, partial=True)
             h, part = self.mlp.forward(h)
             return h, residual, part
         h, residual = self.post_attention_layernorm.forward_fused(
-            h, residual, partial=True, quant=self.mlp.gate_up_proj.wants_act_quant)
+            h, residual, partial=True, quant=self.mlp.gate_up_proj.wants_act_quant, to_gemm=True)
         h = self.mlp.forward(h)
         return h, residual, True
 
@@ -170,6 +170,9 @@ class CausalLM(BaseOP):
         x = self.model.embed_tokens.forward(input_ids)
         residual: Optional[torch.Tensor] = None
         partial = False
+        # the row-sharded prefill path needs every row-parallel output of the pass to end in a
+        # fused add + norm: dense layers only, no hidden-state capture
+        get_comm().row_shard_ok = capture is None and not any(l._is_moe for l in self.model.layers)
         seen = {}
         for i, layer in enumerate(self.model.layers):
             if capture is not None and i in capture:

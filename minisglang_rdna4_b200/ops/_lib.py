@@ -27,6 +27,7 @@ _SIGNATURES = {
     "msgl_qk_norm_rope_store": (c_i, [c_p] * 11 + [c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_i, c_i, c_i, c_i, c_p]),
     "msgl_store_kv": (c_i, [c_p] * 7 + [c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
     "msgl_gemm": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_i, c_i, c_p]),
+    "msgl_gemm_tp": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_p, c_p]),
     "msgl_gemm_status": (c_i, [c_i]),
     "msgl_gemm_pair_mode": (c_i, [c_i]),
     "msgl_attn_make_kv_map": (c_i, [c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_i]),

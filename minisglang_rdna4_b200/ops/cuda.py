@@ -236,9 +236,36 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, 
 KIND_F16, KIND_BF16, KIND_F8, KIND_MXF4 = 0, 1, 2, 3
 
 
+_PENDING_TP = None
+
+
+def set_next_gemm_tp(args) -> None:
+    """Tensor-parallel fusion arguments (``parallel.symm.GemmTpArgs``) for the next GEMM call of
+    this thread: push the output rows to their owner ranks and / or wait for A rows that peers
+    are still delivering. Consumed by exactly one call."""
+    global _PENDING_TP
+    _PENDING_TP = args
+
+
+def take_pending_gemm_tp():
+    global _PENDING_TP
+    args, _PENDING_TP = _PENDING_TP, None
+    return args
+
+
 def _gemm(kind, a, b, n, k, out_dtype, a_scale=None, b_scale=None, bias=None, sf_atoms=None, bn=0, max_ctas=0):
     assert a.dim() == 2 and a.stride(1) == 1 and b.is_contiguous()
     m = a.shape[0]
+    tp = take_pending_gemm_tp()
+    if tp is not None:
+        pushes = tp.rs_world > 0
+        out = None if pushes else torch.empty((m, n), dtype=out_dtype, device=a.device)
+        check(lib().msgl_gemm_tp(kind, _p(a), a.stride(0), _p(b), _p(out), n, m, n, k, _p(a_scale), _p(b_scale),
+                                 _p(bias), _DT[bias.dtype] if bias is not None else 0, _p(sf_atoms), _DT[out_dtype],
+                                 ctypes.byref(tp), _stream()), "gemm_tp")
+        _count(("gemm_f16", "gemm_bf16", "gemm_w8a8", "gemm_w4a8_mxfp4")[kind] + ("_rs" if pushes else "_ag"),
+               "gemm_pair_kernel")
+        return out
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if m == 0:
         return out
@@ -261,7 +288,7 @@ def gemm(x, w, bias=None, out_dtype=None, bn=0, max_ctas=0):
     if n % 8:
         raise ValueError("gemm: N must be a multiple of 8")
     out = _gemm(kind, x2, w, n, k, out_dtype or x.dtype, bias=bias, bn=bn, max_ctas=max_ctas)
-    return out.view(*shape[:-1], n)
+    return out.view(*shape[:-1], n) if out is not None else None
 
 
 def gemm_w8a8(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16, bias=None, bn=0):

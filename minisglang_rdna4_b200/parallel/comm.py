@@ -51,6 +51,10 @@ class Communicator:
     def __init__(self) -> None:
         self.impls: List[object] = []
         self.calls = {"all_reduce": 0, "all_gather": 0, "fused_ar_norm": 0}
+        # set per forward pass by the model: True only for passes in which every row-parallel
+        # output feeds a fused add + norm (dense layers, no hidden-state capture)
+        self.row_shard_ok = False
+        self._rs_impl = None
 
     @property
     def size(self) -> int:
@@ -64,6 +68,34 @@ class Communicator:
             if hasattr(impl, method) and impl.accepts(x):
                 return impl
         raise RuntimeError(f"no collective implementation registered for {method}")
+
+    # ---- prefill path: GEMM -> reduce-scatter -> add + norm -> all-gather -> GEMM ----
+    def rs_begin(self, rows: int, hidden: int, dtype):
+        """A plan for pushing a row-parallel GEMM's partial rows to their owner ranks, or None
+        when this forward pass keeps the all-reduce formulation. The decision is the same at
+        every fused site of a pass (same rows, same hidden): the residual stream is sharded by
+        rows between those sites and must not meet the all-reduce formulation half-way."""
+        if self.size == 1 or not self.row_shard_ok:
+            return None
+        for impl in reversed(self.impls):
+            fn = getattr(impl, "rs_begin", None)
+            if fn is not None:
+                plan = fn(rows, hidden, dtype)
+                if plan is not None:
+                    plan_impl = impl
+                    self._rs_impl = plan_impl
+                    self.calls["fused_rs_ag"] = self.calls.get("fused_rs_ag", 0) + 1
+                    return plan
+        return None
+
+    def rs_gemm_args(self, plan, a_ready=None):
+        return self._rs_impl.row_shard.gemm_args(plan, a_ready)
+
+    def rs_finish(self, plan, residual, weight, eps, quant=False, plus_one=False):
+        return self._rs_impl.row_shard.finish(plan, residual, weight, eps, quant, plus_one)
+
+    def wait_ready(self, ready) -> None:
+        self._rs_impl.wait_ready(ready)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:

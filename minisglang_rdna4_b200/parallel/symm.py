@@ -139,6 +139,27 @@ class SymmetricCollectives:
         self._launch(x, residual, weight, out, None, None, eps)
         return out
 
+    # ---- prefill-sized messages: reduce-scatter / all-gather fused into the GEMMs ----
+    def enable_row_shard(self, max_rows: int, hidden: int) -> None:
+        """Collective: allocates and maps the buffers of the GEMM -> reduce-scatter -> norm ->
+        all-gather -> GEMM path for up to ``max_rows`` token rows of ``hidden`` elements."""
+        if getattr(self, "row_shard", None) is None and max_rows >= 128 * self.world:
+            self.row_shard = RowShardFusion(self.cpu_group, self.device, self.rank, self.world, max_rows, hidden,
+                                            self.wait_us)
+
+    def rs_begin(self, rows: int, hidden: int, dtype):
+        rs = getattr(self, "row_shard", None)
+        if rs is None or not self.healthy or dtype not in _DT or rows <= self.max_rows or not rs.accepts(rows, hidden):
+            return None
+        return rs.begin(rows, dtype)
+
+    def wait_ready(self, ready) -> None:
+        from ..ops import cuda as K
+
+        check(lib().msgl_wait_flags(ready.flags_ptr, ready.blocks,
+                                    ready.seq, ready.wait_us, torch.cuda.current_stream().cuda_stream), "wait_flags")
+        K._count("wait_ready", "wait_flags_kernel")
+
     def check_health(self) -> bool:
         code = int(lib().msgl_comm_status(1))
         if code != 0:
@@ -147,4 +168,180 @@ class SymmetricCollectives:
         return self.healthy
 
     def close(self) -> None:
+        rs = getattr(self, "row_shard", None)
+        if rs is not None:
+            rs.close()
+            self.row_shard = None
         self.heap.close()
+
+
+# ------------------------------------------------------------------------------------------
+# Prefill-sized messages: GEMM -> reduce-scatter -> (add + RMSNorm) -> all-gather -> GEMM
+# ------------------------------------------------------------------------------------------
+_lib.bind("msgl_rs_norm_ag", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_ll, c_i, c_i, c_i, c_i, c_i, c_i,
+                                   ctypes.c_uint, ctypes.c_uint, c_f, c_i, c_i, c_ll, c_i, c_p])
+
+
+_lib.bind("msgl_wait_flags", c_i, [c_p, c_i, ctypes.c_uint, c_ll, c_p])
+
+
+class GemmTpArgs(ctypes.Structure):
+    """Mirror of ``MsglGemmTp`` (csrc/gemm_tcgen05.cu)."""
+
+    _fields_ = [("rs_slots", ctypes.c_void_p * 8), ("rs_flags", ctypes.c_void_p * 8), ("rs_count", ctypes.c_void_p),
+                ("rs_plane", ctypes.c_longlong), ("rs_world", ctypes.c_int), ("rs_rank", ctypes.c_int),
+                ("rs_flag_stride", ctypes.c_int), ("rs_ld", ctypes.c_int), ("rs_seq", ctypes.c_uint),
+                ("a_ready_seq", ctypes.c_uint), ("a_ready", ctypes.c_void_p), ("wait_us", ctypes.c_longlong),
+                ("order_world", ctypes.c_int)]
+
+
+class ReadyRows:
+    """Rows of an activation that peers are still delivering: the consumer GEMM waits for
+    ``flags[block] >= seq`` per 128-row block before it stages that block."""
+
+    __slots__ = ("flags_ptr", "seq", "world", "wait_us", "blocks")
+
+    def __init__(self, flags_ptr: int, seq: int, world: int, wait_us: int, blocks: int) -> None:
+        self.flags_ptr, self.seq, self.world, self.wait_us, self.blocks = flags_ptr, seq, world, wait_us, blocks
+
+    def gemm_args(self) -> GemmTpArgs:
+        a = GemmTpArgs()
+        a.rs_world = 0
+        a.a_ready = self.flags_ptr
+        a.a_ready_seq = self.seq
+        a.wait_us = self.wait_us
+        a.order_world = self.world
+        return a
+
+
+class PushedPartial:
+    """Stand-in for the output of a row-parallel GEMM whose epilogue pushed the partial rows to
+    their owner ranks instead of writing a local tensor."""
+
+    __slots__ = ("plan", "shape", "dtype")
+
+    def __init__(self, plan: "RowShardPlan", shape, dtype) -> None:
+        self.plan, self.shape, self.dtype = plan, shape, dtype
+
+
+class RowShardPlan:
+    __slots__ = ("rows", "hidden", "parity", "rs_seq", "dtype")
+
+    def __init__(self, rows: int, hidden: int, parity: int, rs_seq: int, dtype) -> None:
+        self.rows, self.hidden, self.parity, self.rs_seq, self.dtype = rows, hidden, parity, rs_seq, dtype
+
+
+class RowShardFusion:
+    """Symmetric buffers and sequence numbers of the prefill path. 128-row block ``b`` of the
+    token rows belongs to rank ``b % world`` (its local block ``b // world``), so any row count
+    that is a multiple of 128 splits evenly enough and consecutive blocks alternate owners.
+
+    Per-rank symmetric region (``max_rows`` token rows of ``hidden`` 16-bit elements)::
+
+        slots   2 (parity) x world (src) x blocks_per_rank x 128 x hidden 16-bit   partial rows pushed by GEMM epilogues
+        rsflag  world (src) x blocks_per_rank uint32                              set by the pushing ranks
+        act     2 (parity) x max_rows x hidden 16-bit (e4m3 uses the first half)  gathered normed rows
+        scale   2 (parity) x max_rows fp32                                        gathered per-token scales
+        ready   max_rows/128 uint32                                               set by the owning ranks
+    """
+
+    def __init__(self, cpu_group, device, rank: int, world: int, max_rows: int, hidden: int, wait_us: int) -> None:
+        self.rank, self.world, self.hidden, self.wait_us = rank, world, hidden, wait_us
+        self.device = torch.device(device)
+        self.max_rows = (max_rows + 127) // 128 * 128
+        blocks = self.max_rows // 128
+        self.bpr = (blocks + world - 1) // world            # blocks per rank (upper bound)
+        al = lambda n: (n + 255) // 256 * 256
+        self.slot_plane = self.bpr * 128 * hidden           # elements per source plane
+        self.slot_parity_bytes = world * self.slot_plane * 2
+        self.off_slots = 0
+        self.off_rsflag = al(2 * self.slot_parity_bytes)
+        self.off_act = self.off_rsflag + al(world * self.bpr * 4)
+        self.act_parity_bytes = al(self.max_rows * hidden * 2)
+        self.off_scale = self.off_act + 2 * self.act_parity_bytes
+        self.scale_parity_bytes = al(self.max_rows * 4)
+        self.off_ready = self.off_scale + 2 * self.scale_parity_bytes
+        total = self.off_ready + al(blocks * 4)
+        self.heap = SymmetricHeap(total, cpu_group, rank, world)
+        self.rs_count = torch.zeros(blocks + 2, dtype=torch.int32, device=self.device)
+        self.blk_count = torch.zeros(self.bpr, dtype=torch.int32, device=self.device)
+        self.rs_seq = 0
+        self.ag_seq = 0
+        self.parity = 0
+        self.PtrArr = ctypes.c_void_p * world
+        logger.info_rank0("row-shard fusion ready: %d ranks, %d rows x %d, heap %.1f MiB", world, self.max_rows,
+                          hidden, total / 2 ** 20)
+
+    def accepts(self, rows: int, hidden: int) -> bool:
+        return hidden == self.hidden and 0 < rows <= self.max_rows and rows % 128 == 0
+
+    # ---- producer side: arguments for the row-parallel GEMM ----
+    def begin(self, rows: int, dtype) -> RowShardPlan:
+        self.rs_seq = (self.rs_seq + 1) & 0xFFFFFFFF
+        self.parity ^= 1
+        return RowShardPlan(rows, self.hidden, self.parity, self.rs_seq, dtype)
+
+    def gemm_args(self, plan: RowShardPlan, a_ready: Optional[ReadyRows] = None) -> GemmTpArgs:
+        a = GemmTpArgs()
+        for p in range(self.world):
+            a.rs_slots[p] = self.heap.ptrs[p] + self.off_slots + plan.parity * self.slot_parity_bytes
+            a.rs_flags[p] = self.heap.ptrs[p] + self.off_rsflag
+        a.rs_count = self.rs_count.data_ptr()
+        a.rs_plane = self.slot_plane
+        a.rs_world, a.rs_rank, a.rs_flag_stride, a.rs_ld = self.world, self.rank, self.bpr, self.hidden
+        a.rs_seq = plan.rs_seq
+        a.wait_us = self.wait_us
+        a.order_world = self.world
+        if a_ready is not None:
+            a.a_ready, a.a_ready_seq = a_ready.flags_ptr, a_ready.seq
+        return a
+
+    # ---- consumer side ----
+    def finish(self, plan: RowShardPlan, residual: torch.Tensor, weight: torch.Tensor, eps: float, quant: bool,
+               plus_one: bool = False):
+        from ..ops import cuda as K
+
+        rows, H = plan.rows, self.hidden
+        self.ag_seq = (self.ag_seq + 1) & 0xFFFFFFFF
+        par = self.ag_seq & 1
+        act = [p + self.off_act + par * self.act_parity_bytes for p in self.heap.ptrs]
+        scl = [p + self.off_scale + par * self.scale_parity_bytes for p in self.heap.ptrs]
+        rdy = [p + self.off_ready for p in self.heap.ptrs]
+        none = self.PtrArr(*([None] * self.world))
+        check(lib().msgl_rs_norm_ag(
+            self.heap.local + self.off_slots + plan.parity * self.slot_parity_bytes, self.heap.local + self.off_rsflag,
+            residual.data_ptr(), weight.data_ptr(), none if quant else self.PtrArr(*act),
+            self.PtrArr(*act) if quant else none, self.PtrArr(*scl) if quant else none, self.PtrArr(*rdy),
+            self.blk_count.data_ptr(), self.slot_plane, H, self.rank, self.world, rows, self.bpr, H, plan.rs_seq,
+            self.ag_seq,
+            eps, int(plus_one), int(quant), self.wait_us, _DT[plan.dtype], torch.cuda.current_stream().cuda_stream),
+            "rs_norm_ag")
+        K._count("fused_rs_norm_ag", "rs_norm_ag_kernel")
+        ready = ReadyRows(self.heap.local + self.off_ready, self.ag_seq, self.world, self.wait_us, rows // 128)
+        local_act = self.heap.local + self.off_act + par * self.act_parity_bytes
+        if quant:
+            q = _view(local_act, (rows, H), torch.float8_e4m3fn, self.device)
+            s = _view(self.heap.local + self.off_scale + par * self.scale_parity_bytes, (rows,), torch.float32,
+                      self.device)
+            return q, s, ready
+        return _view(local_act, (rows, H), plan.dtype, self.device), None, ready
+
+    def close(self) -> None:
+        self.heap.close()
+
+
+class _DevicePtr:
+    """Minimal ``__cuda_array_interface__`` carrier: lets torch alias raw device memory."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def _view(ptr: int, shape, dtype, device) -> torch.Tensor:
+    """A tensor over raw device memory of the symmetric heap (which outlives every step)."""
+    n = 1
+    for d in shape:
+        n *= d
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    raw = torch.as_tensor(_DevicePtr(ptr, nbytes), device=device)
+    return raw.view(dtype).view(*shape)

@@ -43,6 +43,9 @@ class ActQ:
 
     q: torch.Tensor
     scale: torch.Tensor
+    # set when peers are still delivering the rows (parallel.symm.ReadyRows): the consuming
+    # GEMM waits per 128-row block; any other consumer calls get_comm().wait_ready first
+    ready: object = None
 
     @property
     def shape(self):

@@ -209,3 +209,107 @@ def test_fused_expert_parallel_exchange_two_gpus():
         p.join(timeout=60)
     for rank, ok, msgs in results:
         assert ok, f"rank {rank}: {msgs}"
+
+
+def _row_shard_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    import math
+    import time
+
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    cpu = dist.new_group(list(range(world)), backend="gloo")
+    from minisglang_rdna4_b200.ops import cuda as K
+    from minisglang_rdna4_b200.ops import ref
+    from minisglang_rdna4_b200.parallel.symm import SymmetricCollectives
+    from minisglang_rdna4_b200.quant.method import ActQ
+
+    comm = SymmetricCollectives(dist.group.WORLD, cpu, dev, rank, world, max_rows=256, max_hidden=4096)
+    hidden, k_local, n2 = 1024, 768, 1536
+    comm.enable_row_shard(2048, hidden)
+    ok, msgs = True, []
+    for it, rows in enumerate([512, 2048, 1152, 384]):
+        g = torch.Generator(device="cpu").manual_seed(7 * rows + it)
+        a_parts = [torch.randn(rows, k_local, generator=g).bfloat16() for _ in range(world)]
+        w_parts = [(torch.randn(hidden, k_local, generator=g) / math.sqrt(k_local * world)).bfloat16()
+                   for _ in range(world)]
+        res0 = torch.randn(rows, hidden, generator=g).bfloat16()
+        nw = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16()
+        w2 = torch.randn(n2, hidden, generator=g) / math.sqrt(hidden)
+        w2s = w2.abs().amax(-1) / 448
+        w2q = (w2 / w2s[:, None]).to(torch.float8_e4m3fn)
+        # fp32 reference of the whole chain
+        partials = [(a_parts[r].float() @ w_parts[r].float().t()).bfloat16() for r in range(world)]
+        total = sum(p.float() for p in partials)
+        want_res = (total + res0.float()).bfloat16()
+        want_norm = ref.rms_norm(want_res, nw, 1e-6).float()
+        want_y = want_norm @ (w2q.float() * w2s[:, None]).t()
+
+        a = a_parts[rank].to(dev)
+        w = w_parts[rank].to(dev)
+        res = res0.clone().to(dev)
+        if rank == 1 and it == 1:
+            time.sleep(0.05)  # a lagging rank: the peers' waits must simply take longer
+        for quant in (True, False):
+            res.copy_(res0)
+            plan = comm.rs_begin(rows, hidden, torch.bfloat16)
+            if plan is None:
+                ok = False
+                msgs.append(f"no plan for rows={rows}")
+                break
+            K.set_next_gemm_tp(comm.row_shard.gemm_args(plan))
+            assert K.gemm(a, w) is None  # nothing is written locally
+            qv, sc, ready = comm.row_shard.finish(plan, res, nw.to(dev), 1e-6, quant)
+            torch.cuda.synchronize()
+            own = torch.arange(rows).view(-1, 128)[rank::world].reshape(-1)  # blocks rank, rank + world, ...
+            if not torch.equal(res.cpu()[own], want_res[own]):
+                ok = False
+                msgs.append(f"owned residual rows differ rows={rows} quant={quant}")
+            if quant:
+                # all-gather -> GEMM: the consumer waits for the rows block by block
+                K.set_next_gemm_tp(ready.gemm_args())
+                y = K.gemm_w8a8(qv, sc, w2q.to(dev), w2s.float().to(dev))
+                err = float((y.float().cpu() - want_y).abs().max()) / float(want_y.abs().max())
+                if err > 0.08:
+                    ok = False
+                    msgs.append(f"gathered GEMM mismatch rows={rows} err={err:.3f}")
+            else:
+                comm.wait_ready(ready)
+                torch.cuda.synchronize()
+                if float((qv.float().cpu() - want_norm).abs().max()) > 0.06:
+                    ok = False
+                    msgs.append(f"gathered norm mismatch rows={rows}")
+            dist.barrier()
+    torch.cuda.synchronize()
+    if K.gemm_status() != 0:
+        ok = False
+        msgs.append("a GEMM wait timed out")
+    if not comm.check_health():
+        ok = False
+        msgs.append("a device wait timed out")
+    dist.barrier()
+    q.put((rank, ok, msgs))
+    comm.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gemm_reduce_scatter_norm_allgather_gemm_two_gpus():
+    """Row-parallel GEMM whose epilogue pushes partial rows to their owners, the owner-side
+    reduce + residual add + RMSNorm (+ e4m3) that stores into every rank, and a column-parallel
+    GEMM that waits for the gathered rows per 128-row block, against an fp32 reference."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 1000
+    procs = [ctx.Process(target=_row_shard_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok, msgs in results:
+        assert ok, f"rank {rank}: {msgs}"

@@ -61,3 +61,31 @@ def test_engine_with_host_expert_tier_matches_resident_engine():
     assert len(tiers) == 2 and all(t.slots < 16 for t in tiers) and sum(t.cache.misses for t in tiers) > 0
     from minisglang_rdna4_b200.layers.moe import MoELayer
     MoELayer.offload_slots = 0
+
+
+def test_cpu_expert_tier_matches_fp32_reference():
+    """The host library's e2m1 expert MLPs (fp32-activation and int8-activation inner products)
+    against the PyTorch restatement, including a skipped (negative) expert id."""
+    import torch
+
+    from minisglang_rdna4_b200.quant import mxfp4
+    from minisglang_rdna4_b200.weights.cpu_experts import CpuExpertTier
+
+    torch.manual_seed(0)
+    experts, hidden, inter = 6, 256, 128
+    tier = CpuExpertTier(experts, hidden, inter, group=32, threads=4)
+    for e in range(experts - 1):  # the last expert is not resident on the host
+        w13, sf13 = mxfp4.quantize_mxfp4(torch.randn(2 * inter, hidden) * 0.05)
+        w2, sf2 = mxfp4.quantize_mxfp4(torch.randn(hidden, inter) * 0.05)
+        tier.set_expert(e, w13, torch.pow(2.0, sf13.float() - 127), w2, torch.pow(2.0, sf2.float() - 127))
+    x = torch.randn(9, hidden)
+    ids = torch.randint(0, experts, (9, 3), dtype=torch.int32)
+    ids[0, 0] = -1
+    w = torch.softmax(torch.randn(9, 3), -1)
+    want = tier.reference(x, ids, w)
+    got = tier.forward(x, ids, w)
+    assert float((got - want).abs().max()) < 1e-4 * max(1.0, float(want.abs().max()))
+    got8 = tier.forward(x, ids, w, int8_activations=True)
+    assert float((got8 - want).abs().max()) < 0.05 * float(want.abs().max())
+    assert tier.isa in ("scalar", "avx512-fp32", "avx512-vnni-int8")
+    tier.close()

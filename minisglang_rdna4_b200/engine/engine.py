@@ -419,6 +419,8 @@ class Engine:
                                 np.concatenate([plan.positions, np.zeros(pad, dtype=np.int32)]),
                                 np.concatenate([plan.out_loc, d_loc]), plan.cu_q, plan.seq_lens, plan.block_table,
                                 plan.sample_rows, plan.write_idx, plan.max_q, plan.max_kv)
+        if ENV.CHECK_BOUNDS.value:
+            self._check_plan_bounds(plan)
         token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
         batch.positions = positions
         batch.out_loc = out_loc
@@ -459,6 +461,22 @@ class Engine:
             host_out = tokens.clone()
         self.d2h_bytes += 4 * n_sample
         return ForwardOutput(tokens, host_out, event, sample, logits if return_logits else None)
+
+    def _check_plan_bounds(self, plan: StepPlan) -> None:
+        """``MSGL_CHECK_BOUNDS=1``: every index a kernel will dereference is range-checked on the
+        host first, so a scheduler bug shows up as an exception naming the array instead of as a
+        device fault (the reference builds its kernels with bounds checks for the same purpose)."""
+        pool = self.num_slots * self.max_seq_len
+        slots = (self.kv_cache.dummy_page + 1) * self.page_size
+        checks = [("token_idx", plan.token_idx, pool), ("write_idx", plan.write_idx, pool),
+                  ("out_loc", plan.out_loc, slots), ("block_table", plan.block_table, self.kv_cache.dummy_page + 1),
+                  ("sample_rows", plan.sample_rows, max(int(plan.token_idx.size), 1)),
+                  ("positions", plan.positions, self.max_seq_len)]
+        for name, arr, hi in checks:
+            if arr.size and (int(arr.min()) < 0 or int(arr.max()) >= hi):
+                raise IndexError(f"step plan: {name} outside [0, {hi}): min {int(arr.min())} max {int(arr.max())}")
+        if int(plan.cu_q[-1]) > int(plan.token_idx.size) or np.any(np.diff(plan.cu_q) < 0):
+            raise IndexError("step plan: cu_q is not a prefix sum within the token rows")
 
     def _row_shard_rows(self, tokens: int) -> bool:
         """Whether a step of ``tokens`` rows takes the row-sharded tensor-parallel path."""

@@ -49,6 +49,9 @@ class GraphRunner:
         self.kernels_per_graph: Dict[int, int] = {}
         self.pool = None
         self.replays = 0
+        from ..utils.tracing import GraphTimer
+
+        self.timer = GraphTimer()
         if self.buckets:
             self._capture_all()
 
@@ -126,7 +129,9 @@ class GraphRunner:
         self.out_loc[:bucket].copy_(out_loc)
         self.seq_lens[:bucket].copy_(seq_lens)
         self.block_table[:bucket, : block_table.shape[1]].copy_(block_table)
+        tok = self.timer.begin(bucket)
         self.graphs[bucket].replay()
+        self.timer.end(tok)
         K.LAUNCHES += self.kernels_per_graph[bucket]
         self.replays += 1
         return self.logits[bucket][:bs]

@@ -119,15 +119,13 @@ ENV.flag("DISABLE_GRAPH", False, "never capture CUDA graphs (eager decode)")
 ENV.int("GRAPH_MAX_BS", 0, "largest decode batch captured as a CUDA graph (0 = auto)")
 ENV.int("EXIT_AFTER_STEPS", 0, "stop the scheduler loop after this many forward steps (0 = never)")
 ENV.flag("SANITIZE_LOGITS", False, "replace NaN/Inf logits before sampling and count them")
-ENV.flag("CHECK_BOUNDS", False, "kernels validate page/token/expert ids and record bad ones instead of using them")
+ENV.flag("CHECK_BOUNDS", False, "validate every step's token / KV-slot / page ids on the host before they reach a kernel")
 ENV.flag("DISPATCH_LEDGER", False, "log once per op which sm_100a kernel served it")
 ENV.str("PROFILE", "", "path of a torch.profiler chrome trace to write around the profiled steps")
 ENV.int("PROFILE_SKIP", 8, "forward steps to skip before the profiler window opens")
 ENV.int("PROFILE_STEPS", 8, "forward steps inside the profiler window")
 ENV.flag("HOSTPROF", False, "print a host-side stage breakdown of the scheduler loop")
 ENV.flag("GRAPH_TIMING", False, "time every graph replay with CUDA events")
-ENV.flag("SPEC_TIMING", False, "time the stages of a speculative decode step")
-ENV.flag("FEEDBACK_CHECK", False, "verify that the token fed to step n+1 is the token sampled at step n")
 # --- distributed --------------------------------------------------------------------------
 ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
@@ -135,7 +133,6 @@ ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of t
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger use two-shot")
 ENV.int("COMM_WAIT_US", 500_000, "bound of every device-side flag wait, in microseconds")
-ENV.flag("TP_OVERLAP", False, "overlap row-parallel all-reduce with compute on a side stream (eager prefill)")
 # --- speculative decode -------------------------------------------------------------------
 ENV.flag("SPEC_SAMPLED", False, "verify drafts by rejection sampling instead of greedy prefix match")
 ENV.int("SPEC_MAX_BS", 0, "largest batch that still runs a speculative step (0 = per-algorithm default)")

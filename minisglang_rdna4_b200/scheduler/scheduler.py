@@ -69,6 +69,10 @@ class Scheduler:
                       "spec_drafted": 0, "spec_accepted": 0, "spec_emitted": 0, "spec_steps": 0}
         self._exit = False
         self._last_stats_flush = time.monotonic()
+        from ..utils.tracing import HostStages, StepProfiler
+
+        self._step_profiler = StepProfiler(getattr(config, "tp_rank", 0))
+        self._host_stages = HostStages()
         self._dummy_slot = eng.num_slots - 1
         self._use_overlap = not (config.disable_overlap or ENV.DISABLE_OVERLAP.value) and eng.device.type == "cuda"
         self.proposer = None
@@ -120,6 +124,9 @@ class Scheduler:
                                             error="request does not fit in the KV cache")])
             return
         self.prefill.add_one_req(msg.uid, ids, params)
+        from ..utils.tracing import log_request
+
+        log_request("admit", msg.uid, prompt=n, max_new=max_new)
 
     def _abort(self, uid: int) -> None:
         pending = self.prefill.abort(uid)
@@ -390,6 +397,9 @@ class Scheduler:
         self.reqs.pop(req.uid, None)
         self.prefix_len.pop(req.uid, None)
         self.stats["finished"] += 1
+        from ..utils.tracing import log_request
+
+        log_request("finish", req.uid, tokens=int(req.device_len))
 
     # ------------------------------------------------------------------ loops
     @property
@@ -398,36 +408,52 @@ class Scheduler:
 
     def overlap_loop(self) -> None:
         last: Optional[Ongoing] = None
+        hp = self._host_stages
         while not self._exit:
             blocking = not self.has_work and last is None
-            for msg in self.receive_msg(blocking):
-                self._process_one_msg(msg)
+            with hp.stage("receive"):
+                for msg in self.receive_msg(blocking):
+                    self._process_one_msg(msg)
             if last is not None and any(self._needs_constraints(r) for r in last.sampled):
                 # a grammar mask depends on the token of the step in flight: no overlap this round
                 self._process_last_data(last)
                 last = None
-            batch = self._schedule_next_batch()
-            ongoing = self._forward(batch) if batch is not None else None
-            self._process_last_data(last)
+            with hp.stage("schedule"):
+                batch = self._schedule_next_batch()
+            with hp.stage("plan+launch"):
+                ongoing = self._forward(batch) if batch is not None else None
+            with hp.stage("results"):
+                self._process_last_data(last)
             last = ongoing
-            self._maybe_exit_after_steps()
+            self._after_iteration()
         self._process_last_data(last)
 
     def normal_loop(self) -> None:
+        hp = self._host_stages
         while not self._exit:
-            for msg in self.receive_msg(blocking=not self.has_work):
-                self._process_one_msg(msg)
+            with hp.stage("receive"):
+                for msg in self.receive_msg(blocking=not self.has_work):
+                    self._process_one_msg(msg)
             if self.proposer is not None and not self.prefill.runnable and self.decode.runnable:
-                self._spec_decode_step()
+                with hp.stage("spec_step"):
+                    self._spec_decode_step()
             else:
-                batch = self._schedule_next_batch()
+                with hp.stage("schedule"):
+                    batch = self._schedule_next_batch()
                 if batch is not None:
-                    ongoing = self._forward(batch)
-                    self._process_last_data(ongoing)
+                    with hp.stage("plan+launch"):
+                        ongoing = self._forward(batch)
+                    with hp.stage("results"):
+                        self._process_last_data(ongoing)
                     if self.proposer is not None and batch.is_prefill:
                         self._feed_prefill_features(batch)
                         self.proposer.on_prefill(ongoing.sampled)
-            self._maybe_exit_after_steps()
+            self._after_iteration()
+
+    def _after_iteration(self) -> None:
+        self._step_profiler.on_step(self.stats["steps"])
+        self._host_stages.tick()
+        self._maybe_exit_after_steps()
 
     def _maybe_exit_after_steps(self) -> None:
         limit = ENV.EXIT_AFTER_STEPS.value
@@ -435,6 +461,17 @@ class Scheduler:
             self._exit = True
 
     def run_forever(self) -> None:
+        try:
+            self._run_loops()
+        finally:
+            self._step_profiler.close()
+            if self._host_stages.enabled:
+                logger.info("hostprof %s", self._host_stages.summary())
+            gt = getattr(self.engine.graph_runner, "timer", None) if self.engine is not None else None
+            if gt is not None and gt.enabled:
+                logger.info("graph replay timing: %s", gt.summary())
+
+    def _run_loops(self) -> None:
         try:
             if self.config.enable_ep and self.config.dp_size > 1:
                 from .ep import ep_lockstep_loop

@@ -87,3 +87,32 @@ def test_penalties_change_the_greedy_path():
     toks = torch.tensor([[3, 3, -1]])
     out = apply_penalties(logits, rows, toks, torch.tensor([0.5]), torch.tensor([0.4]))
     assert out[0, 3] == 1.0 and abs(float(out[1, 3]) - (1.0 - 0.5 - 0.8)) < 1e-6
+
+
+def test_tracing_hooks(monkeypatch, tmp_path):
+    """The opt-in tracing knobs: host stage breakdown, profiler window, plan bounds check."""
+    import numpy as np
+
+    from minisglang_rdna4_b200.utils.tracing import GraphTimer, HostStages, StepProfiler
+
+    monkeypatch.setenv("MSGL_HOSTPROF", "1")
+    hs = HostStages()
+    with hs.stage("schedule"):
+        pass
+    with hs.stage("schedule"):
+        pass
+    hs.tick()
+    assert hs.count["schedule"] == 2 and "schedule=" in hs.summary()
+    monkeypatch.delenv("MSGL_HOSTPROF")
+    assert not HostStages().enabled and not GraphTimer().enabled
+
+    trace = tmp_path / "trace.json"
+    monkeypatch.setenv("MSGL_PROFILE", str(trace))
+    monkeypatch.setenv("MSGL_PROFILE_SKIP", "1")
+    monkeypatch.setenv("MSGL_PROFILE_STEPS", "2")
+    prof = StepProfiler()
+    for step in range(5):
+        prof.on_step(step)
+        np.zeros(4).sum()
+    prof.close()
+    assert trace.exists() and trace.stat().st_size > 0

@@ -18,6 +18,11 @@ def _register_defaults() -> None:
     ):
         if arch not in MODEL_REGISTRY:
             MODEL_REGISTRY.register(arch)(CausalLM)
+    from .gemma import GemmaForCausalLM
+
+    for arch in ("Gemma2ForCausalLM", "Gemma3ForCausalLM", "Gemma3ForConditionalGeneration"):
+        if arch not in MODEL_REGISTRY:
+            MODEL_REGISTRY.register(arch)(GemmaForCausalLM)
 
 
 def create_model(cfg: ModelConfig, dtype: torch.dtype, device):

@@ -77,6 +77,9 @@ class ModelConfig:
     sliding_window: Optional[int] = None
     layer_types: Optional[Tuple[str, ...]] = None
     final_logit_softcapping: Optional[float] = None
+    # Gemma family
+    query_pre_attn_scalar: Optional[float] = None   # attention scale = this ** -0.5 (default head_dim)
+    rope_local_base_freq: Optional[float] = None    # RoPE base of the sliding-window layers
     num_nextn_predict_layers: int = 0
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
@@ -169,7 +172,25 @@ class ModelConfig:
         num_experts = int(g("num_experts") or g("num_local_experts") or g("n_routed_experts") or 0)
         quant = QuantConfig.from_hf(g("quantization_config")) if g("quantization_config") else None
         layer_types = g("layer_types")
-        qk_norm = model_type in ("qwen3", "qwen3_moe") or bool(g("use_qk_norm", False))
+        qk_norm = model_type in ("qwen3", "qwen3_moe", "gemma3", "gemma3_text") or bool(g("use_qk_norm", False))
+        if layer_types is None and model_type in ("gemma3", "gemma3_text") and g("sliding_window_pattern"):
+            pat = int(g("sliding_window_pattern"))
+            layer_types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
+                           for i in range(int(g("num_hidden_layers")))]
+        if layer_types is None and model_type == "gemma2":
+            layer_types = ["sliding_attention" if i % 2 == 0 else "full_attention"
+                           for i in range(int(g("num_hidden_layers")))]
+        local_theta = g("rope_local_base_freq")
+        if local_theta is None and isinstance(rope_params.get("sliding_attention"), dict):
+            local_theta = rope_params["sliding_attention"].get("rope_theta")
+        if isinstance(rope_params.get("full_attention"), dict):  # per-layer-type RoPE tables
+            full = rope_params["full_attention"]
+            theta = float(full.get("rope_theta", theta))
+            scaling = {k: v for k, v in full.items() if k != "rope_theta"} or None
+            if scaling and scaling.get("rope_type", "default") in ("default", None):
+                scaling = None
+            rotary = RotaryConfig(head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta,
+                                  scaling=scaling)
         attn_bias = bool(g("attention_bias", model_type in ("qwen2", "qwen2_moe")))
         return ModelConfig(
             num_layers=int(g("num_hidden_layers")),
@@ -210,6 +231,8 @@ class ModelConfig:
             sliding_window=g("sliding_window") if g("use_sliding_window", True) else None,
             layer_types=tuple(layer_types) if layer_types else None,
             final_logit_softcapping=g("final_logit_softcapping"),
+            query_pre_attn_scalar=g("query_pre_attn_scalar"),
+            rope_local_base_freq=float(local_theta) if local_theta else None,
             num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
             eos_token_ids=eos_ids,
             bos_token_id=g("bos_token_id"),
@@ -229,6 +252,9 @@ def _default_arch(model_type: str) -> List[str]:
         "qwen2_moe": ["Qwen2MoeForCausalLM"],
         "qwen3": ["Qwen3ForCausalLM"],
         "qwen3_moe": ["Qwen3MoeForCausalLM"],
+        "gemma2": ["Gemma2ForCausalLM"],
+        "gemma3": ["Gemma3ForCausalLM"],
+        "gemma3_text": ["Gemma3ForCausalLM"],
     }.get(model_type, ["LlamaForCausalLM"])
 
 

@@ -1,0 +1,49 @@
+"""Gemma-3 style decoder against the published implementation (``transformers``) on CPU fp32:
+a tiny random-init checkpoint is written by ``transformers``, loaded through this package's
+weight loader, and the greedy continuations must agree token for token. Covers sandwich norms,
+(1 + w) norm weights, GeGLU, the embedding scale, QK-norm, the custom query scale and the
+sliding / global layer pattern with two RoPE bases."""
+import pytest
+import torch
+
+from minisglang_rdna4_b200 import SamplingParams
+from minisglang_rdna4_b200.llm import LLM
+
+transformers = pytest.importorskip("transformers")
+
+
+def _tiny_gemma3(tmp_path):
+    try:
+        from transformers import Gemma3ForCausalLM, Gemma3TextConfig
+    except ImportError:
+        pytest.skip("this transformers build has no Gemma3")
+    cfg = Gemma3TextConfig(
+        vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=64, max_position_embeddings=512, rms_norm_eps=1e-6, sliding_window=16,
+        query_pre_attn_scalar=48, rope_theta=1e6, rope_local_base_freq=1e4, sliding_window_pattern=2,
+        layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+        tie_word_embeddings=True, attention_bias=False, final_logit_softcapping=None, attn_logit_softcapping=None,
+        pad_token_id=0, bos_token_id=2, eos_token_id=1, torch_dtype="float32",
+    )
+    torch.manual_seed(0)
+    model = Gemma3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if "norm" in name:
+                p.copy_(0.1 * torch.randn_like(p))  # exercise the (1 + w) convention
+    model.save_pretrained(tmp_path, safe_serialization=True)
+    return model, cfg
+
+
+def test_gemma3_matches_transformers_greedy(tmp_path):
+    hf, cfg = _tiny_gemma3(tmp_path)
+    llm = LLM(model_path=str(tmp_path), device="cpu", page_size=16, max_running_req=4, num_page_override=128,
+              max_extend_tokens=64, seed=0, dtype="float32")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 23)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for prompt, out in zip(prompts, outs):
+        ids = torch.tensor([prompt])
+        with torch.no_grad():
+            want = hf.generate(ids, max_new_tokens=12, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(prompt):]
+        assert out.token_ids == want.tolist(), (out.token_ids, want.tolist())

@@ -437,7 +437,7 @@ class Engine:
                     logits = None
                 else:
                     rows = hidden if n_sample == hidden.shape[0] else hidden[sample_rows.long()]
-                    logits = self.model.lm_head.forward(rows)
+                    logits = self.model.lm_head.forward_local(rows)
         self.steps += 1
         if n_sample == 0:
             empty = torch.empty(0, dtype=torch.int32)
@@ -445,8 +445,17 @@ class Engine:
         if batch.spec_verify:
             # the verify step decides acceptance itself from the logits of every row
             empty = torch.empty(0, dtype=torch.int32)
-            return ForwardOutput(empty.to(self.device), empty, None, None, logits)
-        sample = self.sampler.sample(logits, args)
+            return ForwardOutput(empty.to(self.device), empty, None, None, self.model.lm_head.gather(logits))
+        head = self.model.lm_head
+        if (self.config.tp_size > 1 and args.greedy and not return_logits and args.logprobs == 0
+                and args.bitmask is None and args.penalty_rows is None and not self.sampler.softcap
+                and not ENV.SANITIZE_LOGITS.value):
+            # plain greedy under tensor parallelism: shard arg-max + exchange of (max, index) pairs
+            # instead of gathering rows x vocabulary fp32 logits on every rank
+            sample = SampleOutput(head.argmax_from_local(logits))
+        else:
+            logits = head.gather(logits)
+            sample = self.sampler.sample(logits, args)
         tokens = sample.tokens
         tokens = self._agree_tokens(tokens)
         self.token_pool.view(-1)[write_idx.long()] = tokens

@@ -75,7 +75,8 @@ class GraphRunner:
             batch, self.block_table[:bs], self.cu_q[: bs + 1], self.seq_lens[:bs], 1, eng.max_seq_len)
         with eng.ctx.forward_batch(batch):
             hidden = eng.model.forward(batch.input_ids)
-            return eng.model.lm_head.forward(hidden)
+            # the vocabulary shard only: gathering (or the shard arg-max) happens after the replay
+            return eng.model.lm_head.forward_local(hidden)
 
     def _capture_all(self) -> None:
         from ..ops import cuda as K

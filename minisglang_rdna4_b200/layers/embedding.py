@@ -58,26 +58,44 @@ class ParallelLMHead(BaseOP):
     def _w(self) -> torch.Tensor:
         return self._tied.weight if self._tied is not None else self.weight
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """fp32 logits ``[rows, V]``."""
-        logits = ops.gemm(x, self._w, None, torch.float32)
+    def forward_local(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 logits of this rank's vocabulary shard ``[rows, ceil(V / tp)]`` (columns past the
+        shard's length are padding)."""
+        return ops.gemm(x, self._w, None, torch.float32)
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        """Shard logits → full-vocabulary logits ``[rows, V]`` on every rank."""
         if self._tp.size == 1:
-            return logits[:, : self._vocab]
-        gathered = get_comm().all_gather(logits)            # [tp * rows, V/tp]
-        rows = x.shape[0]
+            return local[:, : self._vocab]
+        rows = local.shape[0]
+        gathered = get_comm().all_gather(local.contiguous())            # [tp * rows, V/tp]
         full = gathered.view(self._tp.size, rows, self._per_rank).permute(1, 0, 2).reshape(rows, -1)
         return full[:, : self._vocab]
 
-    def forward_argmax(self, x: torch.Tensor) -> torch.Tensor:
-        """Greedy token ids without materialising the full-vocabulary logits on every rank."""
-        logits = ops.gemm(x, self._w, None, torch.float32)[:, : self._len]
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """fp32 logits ``[rows, V]``."""
+        return self.gather(self.forward_local(x))
+
+    def argmax_from_local(self, local: torch.Tensor) -> torch.Tensor:
+        """Greedy token ids from shard logits without materialising the full vocabulary anywhere:
+        every rank reduces its shard to (max, index) and only those pairs are exchanged
+        (vocabulary-parallel arg-max, python/minisgl/layers/embedding.py:196-242). Ties go to the
+        lowest index, as a full-row arg-max would."""
+        logits = local[:, : self._len]
         if self._tp.size == 1:
             return ops.argmax(logits)
-        val, idx = logits.max(dim=-1)
+        if self._len > 0:
+            val, idx = logits.max(dim=-1)
+        else:  # a rank whose shard is entirely past the vocabulary
+            val = torch.full((local.shape[0],), float("-inf"), device=local.device)
+            idx = torch.zeros(local.shape[0], dtype=torch.long, device=local.device)
         pair = torch.stack([val, (idx + self._start).float()], dim=-1)   # [rows, 2]
         allp = get_comm().all_gather(pair).view(self._tp.size, -1, 2)
-        best = allp[..., 0].argmax(dim=0)   # first maximum = lowest rank on ties
-        return allp[best, torch.arange(allp.shape[1], device=x.device), 1].to(torch.int32)
+        best = allp[..., 0].argmax(dim=0)   # first maximum = lowest rank = lowest index on ties
+        return allp[best, torch.arange(allp.shape[1], device=local.device), 1].to(torch.int32)
+
+    def forward_argmax(self, x: torch.Tensor) -> torch.Tensor:
+        return self.argmax_from_local(self.forward_local(x))
 
     def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
         if self._tied is None:

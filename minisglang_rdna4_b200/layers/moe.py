@@ -46,6 +46,10 @@ class MoELayer(BaseOP):
         self.gate = ReplicatedLinear(hidden, num_experts, dtype, device, None)
         self.w13 = torch.empty((self._e_local, 2 * self._i_local, hidden), dtype=dtype, device=device)
         self.w2 = torch.empty((self._e_local, hidden, self._i_local), dtype=dtype, device=device)
+        # MXFP4 experts run W4A8 on the GPU: the stacks are (re-)encoded to e2m1 + UE8M0 scale
+        # atoms after loading (lossless for an MXFP4 checkpoint, whose values are on that grid)
+        self._w4a8 = scheme is not None and "mxfp4" in str(getattr(scheme, "name", "")).lower() \
+            and hidden % 128 == 0 and self._i_local % 128 == 0
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Returns this rank's partial result (tensor-parallel partial sum when the
@@ -62,9 +66,32 @@ class MoELayer(BaseOP):
         tier = getattr(self, "_tier", None)
         if tier is not None:
             return tier.forward(x, topk_w, topk_ids - self._e_start)
+        packed = getattr(self, "_packed", None)
+        if packed is not None:
+            from ..ops.moe_kernels import moe_forward_w4a8
+
+            return moe_forward_w4a8(x, *packed, topk_w, topk_ids, self._e_start)
         return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
 
+    def _encode_w4a8(self) -> None:
+        from ..quant import mxfp4
+
+        def enc(w):  # [E, N, K] 16-bit → packed [E, N, K/2], atoms [E, N/128, K/128, 32, 4, 4]
+            e, n, k = w.shape
+            packed, sf = mxfp4.quantize_mxfp4(w.reshape(e * n, k))
+            atoms = torch.stack([mxfp4.pack_sf_atoms(sf[i * n:(i + 1) * n]) for i in range(e)])
+            return packed.view(e, n, k // 2).contiguous(), atoms.contiguous()
+
+        p13, a13 = enc(self.w13)
+        p2, a2 = enc(self.w2)
+        self._packed = (p13, a13, p2, a2)
+        self.w13 = self.w13[:0]
+        self.w2 = self.w2[:0]
+
     def _post_load_self(self) -> None:
+        if self._w4a8 and self.w13.is_cuda and not type(self).offload_slots:
+            self._encode_w4a8()
+            return
         slots = type(self).offload_slots
         if slots and slots < self._e_local:
             from ..weights import HostExpertTier

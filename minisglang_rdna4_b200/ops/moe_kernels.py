@@ -98,3 +98,39 @@ def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
                                  _DT[x.dtype], K._stream()), "moe_combine")
     K._count("moe_combine", "moe_combine_kernel")
     return out
+
+
+def gemm_grouped_w4a8(a_q, a_scale, b_packed, sf_atoms, tile_expert, out_dtype=torch.bfloat16, bn=0):
+    """MXFP4 experts: ``a_q [R, K]`` e4m3 rows (expert-sorted, R % 128 == 0) with per-row scales,
+    ``b_packed [E, N, K/2]`` e2m1 pairs, ``sf_atoms [E, ceil(N/128), ceil(K/128), 32, 4, 4]`` → ``[R, N]``."""
+    e, n, k2 = b_packed.shape
+    r = a_q.shape[0]
+    out = torch.empty((r, n), dtype=out_dtype, device=a_q.device)
+    check(lib().msgl_gemm_grouped(K.KIND_MXF4, a_q.data_ptr(), a_q.stride(0), b_packed.data_ptr(), out.data_ptr(), n,
+                                  r, n, k2 * 2, tile_expert.data_ptr(), e, a_scale.data_ptr(), sf_atoms.data_ptr(),
+                                  _DT[out_dtype], bn, K._stream()), "gemm_grouped_w4a8")
+    K._count("moe_gemm_grouped_w4a8", "gemm_tcgen05_kernel")
+    return out
+
+
+def moe_forward_w4a8(x, w13_packed, w13_atoms, w2_packed, w2_atoms, topk_w, topk_ids, expert_offset=0):
+    """Expert MLPs with 4-bit weights and e4m3 activations: permute → per-row quantise →
+    grouped block-scaled GEMM → SiLU·mul fused with the next quantiser → grouped GEMM → combine."""
+    t, h = x.shape
+    e_local = w13_packed.shape[0]
+    k = topk_ids.shape[1]
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local)
+    rows = sorted_pair.numel()
+    xs = torch.empty((rows, h), dtype=x.dtype, device=x.device)
+    check(lib().msgl_moe_permute(x.data_ptr(), sorted_pair.data_ptr(), xs.data_ptr(), h, k, rows, _DT[x.dtype],
+                                 K._stream()), "moe_permute")
+    K._count("moe_permute", "moe_permute_kernel")
+    xq, xsc = K.per_token_quant_fp8(xs)
+    hcur = gemm_grouped_w4a8(xq, xsc, w13_packed, w13_atoms, tile_expert, x.dtype)
+    aq, asc = K.silu_and_mul_quant(hcur)
+    y = gemm_grouped_w4a8(aq, asc, w2_packed, w2_atoms, tile_expert, x.dtype)
+    out = torch.empty_like(x)
+    check(lib().msgl_moe_combine(y.data_ptr(), topk_w.data_ptr(), pair_row.data_ptr(), out.data_ptr(), t, h, k,
+                                 _DT[x.dtype], K._stream()), "moe_combine")
+    K._count("moe_combine", "moe_combine_kernel")
+    return out

@@ -318,3 +318,32 @@ def test_moe_route_and_forward(K, tokens, E, k):
     got_ep = MK.moe_forward(x, w13[half:].contiguous(), w2[half:].contiguous(), w, ids, expert_offset=half)
     want_ep = R.moe_forward(x, w13[half:], w2[half:], w, ids, expert_offset=half)
     _close(got_ep, want_ep, 3e-2, 3e-2, "moe_forward ep")
+
+
+def test_moe_forward_w4a8_mxfp4(K):
+    """Expert MLPs with e2m1 weights and e4m3 activations (grouped block-scaled GEMMs) against the
+    16-bit expert path run on the de-quantised weights."""
+    from minisglang_rdna4_b200.ops import moe_kernels as MK
+    from minisglang_rdna4_b200.quant import mxfp4
+
+    R = _ref()
+    torch.manual_seed(0)
+    tokens, E, k, h, inter = 150, 16, 4, 512, 256
+    x = torch.randn(tokens, h, device="cuda").bfloat16()
+    logits = torch.randn(tokens, E, device="cuda").bfloat16()
+    w, ids = MK.moe_route(logits, k, True)
+
+    def enc(wt):
+        e, n, kk = wt.shape
+        packed, sf = mxfp4.quantize_mxfp4(wt.reshape(e * n, kk))
+        deq = mxfp4.dequant_mxfp4(packed, sf).view(e, n, kk).bfloat16()
+        atoms = torch.stack([mxfp4.pack_sf_atoms(sf[i * n:(i + 1) * n]) for i in range(e)]).contiguous()
+        return packed.view(e, n, kk // 2).contiguous(), atoms, deq
+
+    p13, a13, d13 = enc(torch.randn(E, 2 * inter, h, device="cuda") * 0.05)
+    p2, a2, d2 = enc(torch.randn(E, h, inter, device="cuda") * 0.05)
+    got = MK.moe_forward_w4a8(x, p13, a13, p2, a2, w, ids)
+    assert K.gemm_status() == 0
+    want = R.moe_forward(x, d13, d2, w, ids)
+    err = float((got.float() - want.float()).abs().max()) / float(want.float().abs().max())
+    assert err < 0.08, err

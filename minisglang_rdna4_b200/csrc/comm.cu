@@ -318,6 +318,86 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t seq, un
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Vocabulary-parallel arg-max: every rank holds the logits of its vocabulary shard. One CTA per
+// row reduces the shard to (max, global index), stores the pair into every rank's slot, raises
+// the row's sequence flag there, waits (bounded) for the peers' pairs and picks the winner.
+// Ranks own ascending index ranges, so "first maximum in rank order" is the lowest index, the
+// same tie rule as an arg-max over the full row. Replaces gathering rows x vocabulary logits.
+// ------------------------------------------------------------------------------------------
+struct ArgmaxArgs {
+  const float* logits;       // [rows, ld] this rank's shard
+  long long ld;
+  int len;                   // valid columns of the shard (0: this rank holds none)
+  int start;                 // global index of column 0
+  int32_t* out;              // [rows] winning token ids
+  uint2* pairs[kMaxRanks];   // pairs[p]: rank p's region [2 (parity)][src][max_rows]
+  uint32_t* flags[kMaxRanks];  // flags[p]: rank p's region [src][max_rows]
+  uint32_t* seq;             // local per-row sequence counters
+  int* status;
+  int rank, nranks, max_rows;
+  unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  __shared__ uint2 s_peer[kMaxRanks];
+  const int row = blockIdx.x;
+  const uint32_t seq = a.seq[row] + 1u;
+  const int parity = (int)(seq & 1u);
+  const float* x = a.logits + (size_t)row * a.ld;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < a.len; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+  }
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < idx)) { best = s_val[w]; idx = s_idx[w]; }
+    const uint2 mine = make_uint2(__float_as_uint(best), (uint32_t)(a.len > 0 && idx != 0x7fffffff ? idx + a.start : 0));
+    for (int p = 0; p < a.nranks; ++p)
+      a.pairs[p][((size_t)parity * a.nranks + a.rank) * a.max_rows + row] = mine;
+    __threadfence_system();
+    for (int p = 0; p < a.nranks; ++p) st_release_sys(a.flags[p] + (size_t)a.rank * a.max_rows + row, seq);
+  }
+  if (threadIdx.x < a.nranks) {
+    const int p = threadIdx.x;
+    const uint32_t* f = a.flags[a.rank] + (size_t)p * a.max_rows + row;
+    if ((int)(ld_acquire_sys(f) - seq) < 0) {
+      const unsigned long long t0 = gtimer();
+      while ((int)(ld_acquire_sys(f) - seq) < 0) {
+        if (gtimer() - t0 > a.wait_ns) {
+          atomicCAS(a.status, 0, 360 + p);
+          break;
+        }
+      }
+    }
+    const volatile uint32_t* src =
+        reinterpret_cast<const volatile uint32_t*>(&a.pairs[a.rank][((size_t)parity * a.nranks + p) * a.max_rows + row]);
+    s_peer[p] = make_uint2(src[0], src[1]);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bv = __uint_as_float(s_peer[0].x);
+    uint32_t bi = s_peer[0].y;
+    for (int p = 1; p < a.nranks; ++p) {
+      const float v = __uint_as_float(s_peer[p].x);
+      if (v > bv) { bv = v; bi = s_peer[p].y; }
+    }
+    a.out[row] = (int32_t)bi;
+    a.seq[row] = seq;
+  }
+}
+
 template <typename T>
 int launch_rs(const RsArgs& a, int owned_rows, bool quant, cudaStream_t stream) {
   int threads = ((a.hidden / 8 + 31) / 32) * 32;
@@ -437,6 +517,29 @@ MSGL_API int msgl_rs_norm_ag(const void* slots, const void* flags, void* residua
   if (dtype == MSGL_BF16) return launch_rs<__nv_bfloat16>(a, owned_rows, quant != 0, stream);
   if (dtype == MSGL_F16) return launch_rs<__half>(a, owned_rows, quant != 0, stream);
   return MSGL_BAD_ARG;
+}
+
+// pairs / flags: arrays of `nranks` peer-mapped region bases; seq: local [max_rows] counters.
+MSGL_API int msgl_argmax_exchange(const void* logits, long long ld, int rows, int len, int start, void* out,
+                                  void* const* pairs, void* const* flags, void* seq, int rank, int nranks,
+                                  int max_rows, long long wait_us, cudaStream_t stream) {
+  if (rows == 0) return MSGL_OK;
+  if (nranks > kMaxRanks || rows > max_rows || len < 0) {
+    msgl_set_error_text("argmax_exchange: unsupported shape");
+    return MSGL_BAD_ARG;
+  }
+  ArgmaxArgs a;
+  a.logits = (const float*)logits; a.ld = ld; a.len = len; a.start = start; a.out = (int32_t*)out;
+  for (int p = 0; p < nranks; ++p) { a.pairs[p] = (uint2*)pairs[p]; a.flags[p] = (uint32_t*)flags[p]; }
+  a.seq = (uint32_t*)seq;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_comm_status);
+  a.status = status;
+  a.rank = rank; a.nranks = nranks; a.max_rows = max_rows;
+  a.wait_ns = (unsigned long long)wait_us * 1000ull;
+  argmax_exchange_kernel<<<rows, 256, 0, stream>>>(a);
+  MSGL_CHECK_LAUNCH("argmax_exchange");
+  return MSGL_OK;
 }
 
 MSGL_API int msgl_wait_flags(const void* flags, int n, unsigned int seq, long long wait_us, cudaStream_t stream) {

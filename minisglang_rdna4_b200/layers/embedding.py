@@ -84,6 +84,9 @@ class ParallelLMHead(BaseOP):
         logits = local[:, : self._len]
         if self._tp.size == 1:
             return ops.argmax(logits)
+        fused = get_comm().vocab_argmax(local, self._len, self._start)
+        if fused is not None:
+            return fused
         if self._len > 0:
             val, idx = logits.max(dim=-1)
         else:  # a rank whose shard is entirely past the vocabulary

@@ -97,6 +97,20 @@ class Communicator:
     def wait_ready(self, ready) -> None:
         self._rs_impl.wait_ready(ready)
 
+    def vocab_argmax(self, local_logits: torch.Tensor, length: int, start: int):
+        """Fused shard arg-max + pair exchange when a peer-memory implementation is registered;
+        None tells the caller to use the all-gather formulation."""
+        if self.size == 1 or not local_logits.is_cuda:
+            return None
+        for impl in reversed(self.impls):
+            fn = getattr(impl, "vocab_argmax", None)
+            if fn is not None:
+                out = fn(local_logits, length, start)
+                if out is not None:
+                    self.calls["vocab_argmax"] = self.calls.get("vocab_argmax", 0) + 1
+                    return out
+        return None
+
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x

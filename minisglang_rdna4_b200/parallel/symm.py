@@ -38,6 +38,7 @@ _lib.bind("msgl_ipc_close", c_i, [c_p])
 _lib.bind("msgl_ar_oneshot", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i,
                                    c_f, c_i, c_ll, c_i, c_p])
 _lib.bind("msgl_comm_status", c_i, [c_i])
+_lib.bind("msgl_argmax_exchange", c_i, [c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_ll, c_p])
 
 _DT = {torch.bfloat16: 0, torch.float16: 1}
 
@@ -96,11 +97,17 @@ class SymmetricCollectives:
             self.max_rows //= 2
             flag_bytes = (world * self.max_rows * 4 + 255) // 256 * 256
             slot_bytes = 2 * world * self.max_rows * max_hidden * 2
-        self.heap = SymmetricHeap(flag_bytes + slot_bytes, cpu_group, rank, world)
+        # vocabulary-parallel arg-max exchange: (max, index) pairs and their flags
+        am_pair_bytes = 2 * world * self.max_rows * 8
+        am_flag_bytes = (world * self.max_rows * 4 + 255) // 256 * 256
+        self.heap = SymmetricHeap(flag_bytes + slot_bytes + am_pair_bytes + am_flag_bytes, cpu_group, rank, world)
         PtrArr = ctypes.c_void_p * world
         self._flags = PtrArr(*[p for p in self.heap.ptrs])
         self._slots = PtrArr(*[p + flag_bytes for p in self.heap.ptrs])
+        self._am_pairs = PtrArr(*[p + flag_bytes + slot_bytes for p in self.heap.ptrs])
+        self._am_flags = PtrArr(*[p + flag_bytes + slot_bytes + am_pair_bytes for p in self.heap.ptrs])
         self._seq = torch.zeros(self.max_rows, dtype=torch.int32, device=self.device)
+        self._am_seq = torch.zeros(self.max_rows, dtype=torch.int32, device=self.device)
         self.healthy = True
         self.wait_us = ENV.COMM_WAIT_US.value
         self.oneshot_max_bytes = ENV.ONESHOT_AR_MAX_KIB.value << 10
@@ -137,6 +144,24 @@ class SymmetricCollectives:
             return q, s
         out = torch.empty_like(x)
         self._launch(x, residual, weight, out, None, None, eps)
+        return out
+
+    def vocab_argmax(self, local_logits: torch.Tensor, length: int, start: int):
+        """Greedy ids from fp32 shard logits ``[rows, ld]`` (``length`` valid columns, global
+        index of column 0 = ``start``): one kernel reduces the shard, exchanges (max, index)
+        pairs through peer memory and picks the winner. None when the message does not fit."""
+        from ..ops import cuda as K
+
+        rows = local_logits.shape[0]
+        if (not self.healthy or rows > self.max_rows or local_logits.dtype != torch.float32
+                or local_logits.stride(1) != 1):
+            return None
+        out = torch.empty(rows, dtype=torch.int32, device=local_logits.device)
+        check(lib().msgl_argmax_exchange(local_logits.data_ptr(), local_logits.stride(0), rows, int(length), int(start),
+                                         out.data_ptr(), self._am_pairs, self._am_flags, self._am_seq.data_ptr(),
+                                         self.rank, self.world, self.max_rows, self.wait_us,
+                                         torch.cuda.current_stream().cuda_stream), "argmax_exchange")
+        K._count("vocab_parallel_argmax", "argmax_exchange_kernel")
         return out
 
     # ---- prefill-sized messages: reduce-scatter / all-gather fused into the GEMMs ----

@@ -60,6 +60,19 @@ def _worker(rank, world, port, q):
             if not torch.equal(y.cpu(), total.bfloat16()):
                 ok = False
                 msgs.append(f"all_reduce mismatch rows={rows} hidden={hidden}")
+    # vocabulary-parallel arg-max: shard logits -> global greedy ids, ties to the lowest index
+    for rows, shard in [(1, 1000), (37, 4096), (256, 19000)]:
+        g = torch.Generator(device="cpu").manual_seed(rows)
+        full = torch.randn(rows, shard * world, generator=g)
+        full[0, 5] = full[0, shard + 7] = 50.0  # a tie across ranks
+        mine = torch.zeros(rows, shard + 24)     # padded leading dimension
+        mine[:, :shard] = full[:, rank * shard:(rank + 1) * shard]
+        got = comm.vocab_argmax(mine.to(dev), shard, rank * shard)
+        for _ in range(2):  # the sequence counters must survive repeated calls
+            got = comm.vocab_argmax(mine.to(dev), shard, rank * shard)
+        if got is None or not torch.equal(got.cpu().long(), full.argmax(-1)):
+            ok = False
+            msgs.append(f"vocab argmax mismatch rows={rows}")
     # every rank must hold bit-identical results (rank-ordered reduction)
     x = torch.randn(64, 2560, device=dev).bfloat16()
     res = torch.zeros(64, 2560, device=dev).bfloat16()

@@ -54,6 +54,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ unsigned long long gtimer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -82,7 +87,9 @@ __global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
   // 2. raise the flag on every peer, then wait for every peer's flag here
   if (threadIdx.x < a.nranks) {
     const int p = threadIdx.x;
-    __threadfence_system();
+    // the barrier above orders the CTA's row stores before this thread; the release store makes
+    // them visible system-wide before the flag (no separate fence: a system-scope fence per row
+    // costs microseconds)
     st_release_sys(a.flags[p] + (size_t)a.rank * a.max_rows + row, seq);
     const uint32_t* mine = a.flags[a.rank] + (size_t)p * a.max_rows + row;
     if ((int)(ld_acquire_sys(mine) - seq) < 0) {
@@ -211,9 +218,12 @@ struct RsArgs {
   unsigned long long wait_ns;
 };
 
-template <typename T, bool QUANT>
-__global__ void __launch_bounds__(1024) rs_norm_ag_kernel(const RsArgs a) {
-  extern __shared__ float row_s[];
+// One 128-thread CTA per owned row, the row held in registers between the passes (VPT 16-byte
+// vectors per thread): the row time is latency, so throughput comes from many resident rows.
+constexpr int kRsThreads = 128;
+
+template <typename T, bool QUANT, int VPT>
+__global__ void __launch_bounds__(kRsThreads) rs_norm_ag_kernel(const RsArgs a) {
   __shared__ float scratch[32];
   const int lrow = blockIdx.x;
   const int lblk = lrow >> 7;
@@ -234,69 +244,68 @@ __global__ void __launch_bounds__(1024) rs_norm_ag_kernel(const RsArgs a) {
   }
   __syncthreads();
   const T* base = reinterpret_cast<const T*>(a.slots) + (size_t)lrow * a.ld;
-  T* rr = reinterpret_cast<T*>(a.residual) + (size_t)grow * H;
+  T* res = reinterpret_cast<T*>(a.residual) + (size_t)grow * H;
+  const T* w = reinterpret_cast<const T*>(a.weight);
+  float v[VPT][8];
   float ss = 0.f;
-  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-    float acc[8], r[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-    for (int q = 0; q < a.nranks; ++q) {
-      float v[8];
-      load8(base + (size_t)q * a.plane + i, v);
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRsThreads + threadIdx.x) * 8;
+    if (i < H) {
+      load8(res + i, v[j]);
+      for (int q = 0; q < a.nranks; ++q) {  // rank order: every rank would compute the same sum
+        float x[8];
+        load8(base + (size_t)q * a.plane + i, x);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += v[k];
-    }
-    load8(rr + i, r);
+        for (int k = 0; k < 8; ++k) v[j][k] += x[k];
+      }
+      store8(res + i, v[j]);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] += r[k];
-    store8(rr + i, acc);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      acc[k] = to_float(from_float<T>(acc[k]));
-      ss += acc[k] * acc[k];
-      row_s[i + k] = acc[k];
+      for (int k = 0; k < 8; ++k) {
+        v[j][k] = to_float(from_float<T>(v[j][k]));
+        ss += v[j][k] * v[j][k];
+      }
     }
   }
   ss = block_sum(ss, scratch);
   const float rstd = rsqrtf(ss / (float)H + a.eps);
-  const T* w = reinterpret_cast<const T*>(a.weight);
   float amax = 0.f;
-  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-    float wv[8], y[8];
-    load8(w + i, wv);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + a.w_offset)));
-      if (QUANT) {
-        amax = fmaxf(amax, fabsf(y[k]));
-        row_s[i + k] = y[k];
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kRsThreads + threadIdx.x) * 8;
+    if (i < H) {
+      float wv[8];
+      load8(w + i, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[j][k] = to_float(from_float<T>(v[j][k] * rstd * (wv[k] + a.w_offset)));
+        if (QUANT) amax = fmaxf(amax, fabsf(v[j][k]));
       }
-    }
-    if (!QUANT) {
-      for (int p = 0; p < a.nranks; ++p) store8(reinterpret_cast<T*>(a.out[p]) + (size_t)grow * H + i, y);
+      if (!QUANT)
+        for (int p = 0; p < a.nranks; ++p) store8(reinterpret_cast<T*>(a.out[p]) + (size_t)grow * H + i, v[j]);
     }
   }
   if (QUANT) {
     amax = block_max(amax, scratch);
     const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
     if (threadIdx.x < a.nranks) a.out_scale[threadIdx.x][grow] = scale;
-    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-      float y[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
-      const uint2 packed = pack8_e4m3(y, scale);
-      for (int p = 0; p < a.nranks; ++p) *reinterpret_cast<uint2*>(a.out_q[p] + (size_t)grow * H + i) = packed;
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kRsThreads + threadIdx.x) * 8;
+      if (i < H) {
+        const uint2 packed = pack8_e4m3(v[j], scale);
+        for (int p = 0; p < a.nranks; ++p) *reinterpret_cast<uint2*>(a.out_q[p] + (size_t)grow * H + i) = packed;
+      }
     }
   }
-  // publish: every thread's peer stores are fenced before the row is counted; the CTA that
-  // completes the 128-row block raises the block's flag everywhere
-  __threadfence_system();
+  // publish: the barrier orders the CTA's stores before thread 0; release / acquire at GPU scope
+  // chains the rows of the block, and the release stores of the CTA that completes the block
+  // publish everything system-wide
   __syncthreads();
   if (threadIdx.x == 0) {
-    const uint32_t seen = atomicAdd(a.count + lblk, 1u);
+    const uint32_t seen = atom_add_acq_rel_gpu(a.count + lblk, 1u);
     if (seen + 1u == 128u) {
       a.count[lblk] = 0u;
-      __threadfence_system();
       for (int p = 0; p < a.nranks; ++p) st_release_sys(a.ready[p] + gblk, a.ag_seq);
     }
   }
@@ -366,7 +375,6 @@ __global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a
     const uint2 mine = make_uint2(__float_as_uint(best), (uint32_t)(a.len > 0 && idx != 0x7fffffff ? idx + a.start : 0));
     for (int p = 0; p < a.nranks; ++p)
       a.pairs[p][((size_t)parity * a.nranks + a.rank) * a.max_rows + row] = mine;
-    __threadfence_system();
     for (int p = 0; p < a.nranks; ++p) st_release_sys(a.flags[p] + (size_t)a.rank * a.max_rows + row, seq);
   }
   if (threadIdx.x < a.nranks) {
@@ -398,21 +406,23 @@ __global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a
   }
 }
 
+template <typename T, int VPT>
+void launch_rs_vpt(const RsArgs& a, int owned_rows, bool quant, cudaStream_t stream) {
+  if (quant) rs_norm_ag_kernel<T, true, VPT><<<owned_rows, kRsThreads, 0, stream>>>(a);
+  else rs_norm_ag_kernel<T, false, VPT><<<owned_rows, kRsThreads, 0, stream>>>(a);
+}
+
 template <typename T>
 int launch_rs(const RsArgs& a, int owned_rows, bool quant, cudaStream_t stream) {
-  int threads = ((a.hidden / 8 + 31) / 32) * 32;
-  if (threads > 1024) threads = 1024;
-  if (threads < 32) threads = 32;
-  const size_t smem = (size_t)a.hidden * sizeof(float);
-  if (quant) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(rs_norm_ag_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rs_norm_ag_kernel<T, true><<<owned_rows, threads, smem, stream>>>(a);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(rs_norm_ag_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rs_norm_ag_kernel<T, false><<<owned_rows, threads, smem, stream>>>(a);
-  }
+  const int vpt = (a.hidden / 8 + kRsThreads - 1) / kRsThreads;
+  if (vpt <= 1) launch_rs_vpt<T, 1>(a, owned_rows, quant, stream);
+  else if (vpt <= 2) launch_rs_vpt<T, 2>(a, owned_rows, quant, stream);
+  else if (vpt <= 3) launch_rs_vpt<T, 3>(a, owned_rows, quant, stream);
+  else if (vpt <= 4) launch_rs_vpt<T, 4>(a, owned_rows, quant, stream);
+  else if (vpt <= 6) launch_rs_vpt<T, 6>(a, owned_rows, quant, stream);
+  else if (vpt <= 8) launch_rs_vpt<T, 8>(a, owned_rows, quant, stream);
+  else if (vpt <= 16) launch_rs_vpt<T, 16>(a, owned_rows, quant, stream);
+  else return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("rs_norm_ag");
   return MSGL_OK;
 }
@@ -491,7 +501,7 @@ MSGL_API int msgl_rs_norm_ag(const void* slots, const void* flags, void* residua
                              void* count, long long plane, int ld, int rank, int nranks, int rows,
                              int flag_stride, int hidden, unsigned int rs_seq, unsigned int ag_seq, float eps, int plus_one,
                              int quant, long long wait_us, int dtype, cudaStream_t stream) {
-  if (nranks > kMaxRanks || hidden % 8 || hidden > 48 * 1024 || rows <= 0 || rows % 128) {
+  if (nranks > kMaxRanks || hidden % 8 || hidden > 16 * 8 * 128 || rows <= 0 || rows % 128) {
     msgl_set_error_text("rs_norm_ag: unsupported shape");
     return MSGL_BAD_ARG;
   }

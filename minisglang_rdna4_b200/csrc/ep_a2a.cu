@@ -100,8 +100,9 @@ __global__ void ep_dispatch_kernel(EpBuffers b, const T* __restrict__ x, const i
                                           ((size_t)b.rank * b.cap + s_slot[kk]) * b.hidden);
     for (int i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = src[i];
   }
-  // last CTA publishes counts and flags
-  __threadfence_system();
+  // last CTA publishes counts and flags (GPU-scope fences chain the CTAs; the release stores of
+  // the last one publish system-wide)
+  __threadfence();
   __syncthreads();
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks], 1u) == gridDim.x - 1;
@@ -156,7 +157,7 @@ __global__ void ep_return_kernel(EpBuffers b, const T* __restrict__ y_sorted, co
                                           ((size_t)b.rank * b.cap + pos) * b.hidden);
     for (int i = threadIdx.x; i < b.hidden / 8; i += blockDim.x) out[i] = in[i];
   }
-  __threadfence_system();
+  __threadfence();
   __syncthreads();
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks + 2], 1u) == gridDim.x - 1;

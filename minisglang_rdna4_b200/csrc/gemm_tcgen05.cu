@@ -96,6 +96,25 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   }
 }
 
+// One epilogue warp's 32 rows x 128 columns of 128-row block `blk` have landed in the owner's
+// slots. The warp that completes the block raises the owner's flag; the local counter resets
+// itself for the next call.
+__device__ __forceinline__ void rs_signal(const GemmArgs& args, int blk) {
+  // the tensor stores of this warp are complete (bulk group waited for); order them, made by
+  // the async proxy, before the generic-proxy release below
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  // release / acquire at GPU scope chains the warps of the block (a system-scope fence per warp
+  // measured ~10 us each); the release store of the last one publishes system-wide
+  uint32_t seen;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(seen) : "l"(args.rs_count + blk), "r"(1u) : "memory");
+  if (seen + 1u == args.rs_arrivals) {
+    args.rs_count[blk] = 0u;
+    const int owner = blk % args.rs_world;
+    st_release_sys_u32(args.rs_flags[owner] + (size_t)args.rs_rank * args.rs_flag_stride + blk / args.rs_world,
+                       args.rs_seq);
+  }
+}
+
 template <int KIND> struct KindTraits;
 template <> struct KindTraits<KIND_F16> { static constexpr int BKE = 64; };
 template <> struct KindTraits<KIND_BF16> { static constexpr int BKE = 64; };
@@ -386,9 +405,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 constexpr int kPairThreads = 320;
 constexpr int kPairBN = 256;
 
-template <int KIND> struct PairCfg {
+// RS: the epilogue pushes its rows to other ranks. Stores issued by the SM's load/store path
+// top out near 2.4 GB/s per SM across NVLink (few outstanding requests, microseconds of
+// latency), so the rows go through a per-warp shared-memory patch and leave as TMA tensor
+// stores; their completion is awaited one tile late, behind the next tile's stores. Two
+// pipeline stages make room for the patches.
+template <int KIND, bool RS> struct PairCfg {
   static constexpr int NACC = KIND == KIND_MXF4 ? 1 : 2;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = RS ? 4 : 6;
+  static constexpr int PATCH_WARP = 2 * 32 * 128;            // two 64-column halves of 32 rows, 128-byte-swizzled
+  static constexpr int PATCH_BYTES = RS ? 8 * PATCH_WARP : 0;
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = 128 * 128;
   static constexpr int SF_BYTES = 1024;  // two 128-row scale atoms: every CTA needs all 256 columns' scales
@@ -397,18 +423,24 @@ template <int KIND> struct PairCfg {
   static constexpr int off_sf = off_b + STAGES * B_BYTES;
   static constexpr int off_sfa = off_sf + STAGES * SF_BYTES;
   static constexpr int off_colv = off_sfa + 512;       // 8 epilogue warps x (128 scales + 128 biases) fp32
-  static constexpr int off_bar = off_colv + 8 * 256 * 4;
+  static constexpr int off_patch = (off_colv + 8 * 256 * 4 + 1023) / 1024 * 1024;  // swizzle period
+  static constexpr int off_bar = off_patch + PATCH_BYTES;
   static constexpr int n_bars = 2 * STAGES + 2 * NACC;
   static constexpr int total = off_bar + n_bars * 8 + 16;
   static constexpr uint32_t STAGE_TX =
       KIND == KIND_MXF4 ? A_BYTES + B_BYTES / 2 + SF_BYTES : A_BYTES + B_BYTES;
 };
 
-template <int KIND>
+struct PairOwnerMaps {
+  CUtensorMap m[8];  // m[o]: this rank's plane in owner o's slot region (RS only)
+};
+
+template <int KIND, bool RS>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_sf, const GemmArgs args) {
-  using L = PairCfg<KIND>;
+                 const __grid_constant__ CUtensorMap tma_sf, const __grid_constant__ PairOwnerMaps omaps,
+                 const GemmArgs args) {
+  using L = PairCfg<KIND, RS>;
   using KT = KindTraits<KIND>;
   constexpr int NACC = L::NACC;
   constexpr int STAGES = L::STAGES;
@@ -565,6 +597,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // per-warp staging of the tile's column scales and bias: [0,128) scale, [128,256) bias
     float* colv = reinterpret_cast<float*>(smem + L::off_colv) + (warp - 2) * 256;
     const bool has_colv = args.b_scale != nullptr || args.bias != nullptr;
+    int pending_blk = -1;  // RS: block of the previous tile, whose stores are still in flight
     for (int tile = pair; tile < total_tiles; tile += num_pairs) {
       int m_tile, n_tile;
       tile_coords(tile, args.m_tiles, args.n_tiles, args.tile_order, m_tile, n_tile);
@@ -627,39 +660,48 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8u * acc);
-        if (row_ok) {
-          uint16_t* crow;
-          if (args.rs_world > 0) {
-            const int blk = row >> 7;
-            const int owner = blk % args.rs_world;
-            crow = reinterpret_cast<uint16_t*>(args.rs_slots[owner]) + (size_t)args.rs_rank * args.rs_plane +
-                   (size_t)((blk / args.rs_world) * 128 + (row & 127)) * args.rs_ld;
-          } else {
-            crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
+        if (RS) {
+          uint8_t* patch = smem + L::off_patch + (warp - 2) * L::PATCH_WARP;
+          const uint32_t patch_s = s_base + L::off_patch + (warp - 2) * L::PATCH_WARP;
+          const int blk0 = (m_tile * 256 + (int)rank * 128) >> 7;
+          const int owner = blk0 % args.rs_world;
+          // the previous tile's stores must have finished reading the patch
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u)  // 128-byte swizzle: 16-byte unit u of row r lives at unit u ^ (r & 7)
+              *reinterpret_cast<uint4*>(patch + half * 4096 + lane * 128 + ((u ^ (lane & 7)) << 4)) =
+                  make_uint4(packed[half * 32 + u * 4], packed[half * 32 + u * 4 + 1], packed[half * 32 + u * 4 + 2],
+                             packed[half * 32 + u * 4 + 3]);
           }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            const int drow = (blk0 / args.rs_world) * 128 + q * 32;
+            if ((blk0 << 7) < args.M) {
+              tma_store_2d(&omaps.m[owner], patch_s, colbase, drow);
+              tma_store_2d(&omaps.m[owner], patch_s + 4096, colbase + 64, drow);
+            }
+            bulk_commit_group();
+            // The tile before this one has had a whole tile time to land: wait for it now (this
+            // tile's group stays in flight), then count its warp as delivered. The warp that
+            // completes a 128-row block tells the owner; the counter resets itself.
+            if (pending_blk >= 0) {
+              bulk_wait_group<1>();
+              rs_signal(args, pending_blk);
+            }
+            pending_blk = (blk0 << 7) < args.M ? blk0 : -1;
+          }
+        } else if (row_ok) {
+          uint16_t* crow = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc;
 #pragma unroll
           for (int g = 0; g < 16; ++g) {
             const int col = colbase + g * 8;
             if (col < args.N)
               *reinterpret_cast<uint4*>(crow + col) =
                   make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
-          }
-        }
-        if (args.rs_world > 0) {
-          // Count this warp's 32 rows x 128 columns as delivered. The warp that completes the
-          // 128-row block tells the owner; the counter resets itself for the next call.
-          __threadfence_system();
-          __syncwarp();
-          const int blk = (m_tile * 256 + (int)rank * 128) >> 7;
-          if (lane == 0 && (blk << 7) < args.M) {
-            const uint32_t seen = atomicAdd(args.rs_count + blk, 1u);
-            if (seen + 1u == args.rs_arrivals) {
-              args.rs_count[blk] = 0u;
-              __threadfence_system();
-              const int owner = blk % args.rs_world;
-              st_release_sys_u32(args.rs_flags[owner] + (size_t)args.rs_rank * args.rs_flag_stride + blk / args.rs_world,
-                                 args.rs_seq);
-            }
           }
         }
       } else {
@@ -701,6 +743,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
       if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (RS && lane == 0) {
+      bulk_wait_group<0>();
+      if (pending_blk >= 0) rs_signal(args, pending_blk);
     }
   }
 
@@ -810,15 +856,15 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& 
 }
 
 // Launch the CTA-pair kernel: clusters of two, one cluster per pair of SMs, persistent over tiles.
-template <int KIND>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msf, GemmArgs& args, int max_ctas,
-                cudaStream_t stream) {
-  using L = PairCfg<KIND>;
+template <int KIND, bool RS>
+int launch_pair_impl(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msf, const PairOwnerMaps& omaps,
+                     GemmArgs& args, int max_ctas, cudaStream_t stream) {
+  using L = PairCfg<KIND, RS>;
   constexpr int smem = L::total + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
-        cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(gemm_pair_kernel<KIND, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) { msgl_set_error("pair gemm smem attribute", e); return MSGL_CUDA_ERROR; }
     configured = true;
   }
@@ -838,9 +884,30 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND>, ma, mb, msf, args);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, RS>, ma, mb, msf, omaps, args);
   if (e != cudaSuccess) { msgl_set_error("gemm_pair launch", e); return MSGL_CUDA_ERROR; }
   return MSGL_OK;
+}
+
+int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint64_t inner, uint64_t rows,
+                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, bool cache, bool swizzle);
+
+template <int KIND>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msf, GemmArgs& args, int max_ctas,
+                cudaStream_t stream) {
+  static PairOwnerMaps omaps;  // contents only matter to the RS instantiation
+  if (args.rs_world > 0) {
+    // store maps: this rank's plane in every owner's slot region, 64-column x 32-row boxes
+    for (int o = 0; o < args.rs_world; ++o) {
+      const uint16_t* base = reinterpret_cast<const uint16_t*>(args.rs_slots[o]) + (size_t)args.rs_rank * args.rs_plane;
+      const uint64_t rows = (uint64_t)(args.rs_plane / args.rs_ld);
+      int rc = make_map_2d(&omaps.m[o], base, CU_TENSOR_MAP_DATA_TYPE_UINT16, (uint64_t)args.rs_ld, rows,
+                           (uint64_t)args.rs_ld * 2, 64, 32, true, true);
+      if (rc) return rc;
+    }
+    return launch_pair_impl<KIND, true>(ma, mb, msf, omaps, args, max_ctas, stream);
+  }
+  return launch_pair_impl<KIND, false>(ma, mb, msf, omaps, args, max_ctas, stream);
 }
 
 int g_pair_mode = 0;  // 0 = by size, 1 = never, 2 = whenever the arguments allow

@@ -279,7 +279,8 @@ def _row_shard_worker(rank, world, port, q):
             qv, sc, ready = comm.row_shard.finish(plan, res, nw.to(dev), 1e-6, quant)
             torch.cuda.synchronize()
             own = torch.arange(rows).view(-1, 128)[rank::world].reshape(-1)  # blocks rank, rank + world, ...
-            if not torch.equal(res.cpu()[own], want_res[own]):
+            # the partials come out of a tensor-core GEMM: equal to the fp32 reference up to bf16 rounding
+            if float((res.cpu()[own].float() - want_res[own].float()).abs().max()) > 0.05:
                 ok = False
                 msgs.append(f"owned residual rows differ rows={rows} quant={quant}")
             if quant:

@@ -70,6 +70,7 @@ struct GemmArgs {
   uint32_t a_ready_seq;
   unsigned long long comm_wait_ns;
   int tile_order;           // 0: M fastest; w > 1: N fastest with M tiles interleaved over w owners
+  int dual_acc;             // experiment: odd K steps accumulate into the other buffer
 };
 
 __device__ int g_gemm_status = 0;
@@ -262,15 +263,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int k = 0; k < 4; ++k) {
             const uint64_t a_desc = smem_desc_sw128(a_s + k * 32);
             const uint64_t b_desc = smem_desc_sw128(b_s + k * 32);
-            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            uint32_t d_k = d_tmem;
+            if (args.dual_acc) {
+              d_k = (k & 1) ? tmem_base + (acc ^ 1) * BN : d_tmem;
+              accum = (kb != 0 || k >= 2) ? 1u : 0u;
+            }
             if (KIND == KIND_F16) {
-              mma_f16(d_tmem, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
+              mma_f16(d_k, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
             } else if (KIND == KIND_BF16) {
-              mma_f16(d_tmem, a_desc, b_desc, idesc_dense(1, 1, BM, BN), accum);
+              mma_f16(d_k, a_desc, b_desc, idesc_dense(1, 1, BM, BN), accum);
             } else if (KIND == KIND_F8) {
-              mma_f8f6f4(d_tmem, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
+              mma_f8f6f4(d_k, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
             } else {
-              mma_mxf8f6f4(d_tmem, a_desc, b_desc, idesc_block_scaled(0, 5, BM, BN, 0, (uint32_t)k), accum,
+              mma_mxf8f6f4(d_k, a_desc, b_desc, idesc_block_scaled(0, 5, BM, BN, 0, (uint32_t)k), accum,
                            sfa_tmem, sfb_tmem + (uint32_t)((n0 & 127) >> 5));
             }
           }
@@ -910,6 +916,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   return launch_pair_impl<KIND, false>(ma, mb, msf, omaps, args, max_ctas, stream);
 }
 
+int g_dual_acc = 0;
 int g_pair_mode = 0;  // 0 = by size, 1 = never, 2 = whenever the arguments allow
 
 }  // namespace
@@ -1035,6 +1042,7 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.a_ready = nullptr;
   args.tile_order = 0;
   args.comm_wait_ns = 0;
+  args.dual_acc = g_dual_acc;
   if (tp != nullptr) {
     for (int i = 0; i < 8; ++i) {
       args.rs_slots[i] = tp->rs_slots[i];
@@ -1139,6 +1147,7 @@ MSGL_API int msgl_gemm_grouped(int kind, const void* a, long long lda, const voi
 // 1 = single-CTA kernel always, 2 = CTA-pair kernel always. Returns the previous value.
 MSGL_API int msgl_gemm_pair_mode(int mode) {
   const int prev = g_pair_mode;
+  if (mode >= 256) { g_dual_acc = mode & 1; return prev; }
   if (mode >= 0 && mode <= 2) g_pair_mode = mode;
   return prev;
 }

@@ -187,8 +187,8 @@ __global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int
   store8(out + row * inter + col, y);
 }
 
-template <typename T, int VPT>
-__global__ void __launch_bounds__(kRowThreads) act_mul_quant_kernel(const T* __restrict__ x,
+template <typename T, int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS) act_mul_quant_kernel(const T* __restrict__ x,
                                                                     uint8_t* __restrict__ out_q,
                                                                     float* __restrict__ out_scale, int inter,
                                                                     int kind) {
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kRowThreads) act_mul_quant_kernel(const T* __r
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
-    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    const int i = (j * THREADS + threadIdx.x) * 8;
     if (i < inter) {
       float a[8], b[8];
       load8(g + i, a);
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(kRowThreads) act_mul_quant_kernel(const T* __r
   if (threadIdx.x == 0) out_scale[row] = scale;
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
-    const int i = (j * kRowThreads + threadIdx.x) * 8;
+    const int i = (j * THREADS + threadIdx.x) * 8;
     if (i < inter) *reinterpret_cast<uint2*>(out_q + (size_t)row * inter + i) = pack8_e4m3(v[j], scale);
   }
 }
@@ -224,17 +224,30 @@ __global__ void __launch_bounds__(kRowThreads) act_mul_quant_kernel(const T* __r
 template <typename T>
 static int launch_act_quant(const void* x, void* out_q, void* out_scale, int rows, int inter, int kind,
                             cudaStream_t s) {
-  const int vpt = (inter / 8 + kRowThreads - 1) / kRowThreads;
-#define ACT_LAUNCH(V) \
-  act_mul_quant_kernel<T, V><<<rows, kRowThreads, 0, s>>>((const T*)x, (uint8_t*)out_q, (float*)out_scale, inter, kind)
-  if (vpt <= 1) ACT_LAUNCH(1);
-  else if (vpt <= 2) ACT_LAUNCH(2);
-  else if (vpt <= 4) ACT_LAUNCH(4);
-  else if (vpt <= 6) ACT_LAUNCH(6);
-  else if (vpt <= 8) ACT_LAUNCH(8);
-  else if (vpt <= 10) ACT_LAUNCH(10);
-  else if (vpt <= 16) ACT_LAUNCH(16);
-  else if (vpt <= 28) ACT_LAUNCH(28);
+  // few rows (decode): 512 threads per row keep more loads in flight per row; many rows
+  // (prefill): 128 threads, rows in flight come from the grid
+  const bool wide = rows <= 2048 && inter >= 4096;
+  const int threads = wide ? 512 : kRowThreads;
+  const int vpt = (inter / 8 + threads - 1) / threads;
+#define ACT_LAUNCH(V, TH) \
+  act_mul_quant_kernel<T, V, TH><<<rows, TH, 0, s>>>((const T*)x, (uint8_t*)out_q, (float*)out_scale, inter, kind)
+  if (wide) {
+    if (vpt <= 1) ACT_LAUNCH(1, 512);
+    else if (vpt <= 2) ACT_LAUNCH(2, 512);
+    else if (vpt <= 3) ACT_LAUNCH(3, 512);
+    else if (vpt <= 4) ACT_LAUNCH(4, 512);
+    else if (vpt <= 7) ACT_LAUNCH(7, 512);
+    else return MSGL_BAD_ARG;
+    return MSGL_OK;
+  }
+  if (vpt <= 1) ACT_LAUNCH(1, kRowThreads);
+  else if (vpt <= 2) ACT_LAUNCH(2, kRowThreads);
+  else if (vpt <= 4) ACT_LAUNCH(4, kRowThreads);
+  else if (vpt <= 6) ACT_LAUNCH(6, kRowThreads);
+  else if (vpt <= 8) ACT_LAUNCH(8, kRowThreads);
+  else if (vpt <= 10) ACT_LAUNCH(10, kRowThreads);
+  else if (vpt <= 16) ACT_LAUNCH(16, kRowThreads);
+  else if (vpt <= 28) ACT_LAUNCH(28, kRowThreads);
   else return MSGL_BAD_ARG;
 #undef ACT_LAUNCH
   return MSGL_OK;

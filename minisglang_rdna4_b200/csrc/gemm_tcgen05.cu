@@ -70,7 +70,13 @@ struct GemmArgs {
   uint32_t a_ready_seq;
   unsigned long long comm_wait_ns;
   int tile_order;           // 0: M fastest; w > 1: N fastest with M tiles interleaved over w owners
-  int dual_acc;             // experiment: odd K steps accumulate into the other buffer
+  // ---- split-K (single-CTA kernel, small M): a work item is (tile, K range). Every item stores
+  // its raw fp32 accumulators; the item that arrives last at the tile's counter adds the ranges
+  // in ascending order and writes the result, so the sum does not depend on arrival order.
+  int splits;               // 1: off
+  int kb_per_split;
+  float* splitk_ws;         // [splits][m_tiles * 128][n_tiles * BN] fp32
+  uint32_t* splitk_count;   // [m_tiles * n_tiles], zero between calls
 };
 
 __device__ int g_gemm_status = 0;
@@ -172,9 +178,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::off_bar + (2 * STAGES + 4) * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_bar + (2 * STAGES + 4) * 8 + 4);
+  volatile int* splitk_last = reinterpret_cast<volatile int*>(smem + L::off_bar + (2 * STAGES + 4) * 8 + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = args.m_tiles * args.n_tiles;
+  const int splits = args.splits;
+  const int total_tiles = args.m_tiles * args.n_tiles * splits;  // work items: (tile, K range)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -210,7 +218,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_tiles && !*abort_flag; item += gridDim.x) {
+        const int tile = item / splits, split = item - tile * splits;
         const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
         const int n0 = n_tile * BN;
         int expert = 0;
@@ -218,7 +227,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           expert = args.tile_expert[m_tile];
           if (expert < 0) continue;
         }
-        for (int kb = 0; kb < args.k_blocks; ++kb) {
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 101)) break;
           mbar_expect_tx(full_bar(stage), STAGE_TX);
           tma_load_2d(s_base + L::off_a + stage * L::A_BYTES, &tma_a, full_bar(stage), kb * KT::BKE, m_tile * BM);
@@ -245,14 +256,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (KIND == KIND_MXF4) tmem_cp_32x128b_warpx4(sfa_tmem, smem_desc_sf(s_base + L::off_sfa));
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_tiles && !*abort_flag; item += gridDim.x) {
+        const int tile = item / splits, split = item - tile * splits;
         const int n0 = (tile / args.m_tiles) * BN;
         if (args.tile_expert != nullptr && args.tile_expert[tile % args.m_tiles] < 0) continue;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 102)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = 0; kb < args.k_blocks; ++kb) {
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 103)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_s = s_base + L::off_a + stage * L::A_BYTES;
@@ -263,12 +277,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int k = 0; k < 4; ++k) {
             const uint64_t a_desc = smem_desc_sw128(a_s + k * 32);
             const uint64_t b_desc = smem_desc_sw128(b_s + k * 32);
-            uint32_t accum = (kb | k) != 0 ? 1u : 0u;
-            uint32_t d_k = d_tmem;
-            if (args.dual_acc) {
-              d_k = (k & 1) ? tmem_base + (acc ^ 1) * BN : d_tmem;
-              accum = (kb != 0 || k >= 2) ? 1u : 0u;
-            }
+            const uint32_t accum = (kb != kb0 || k != 0) ? 1u : 0u;
+            const uint32_t d_k = d_tmem;
             if (KIND == KIND_F16) {
               mma_f16(d_k, a_desc, b_desc, idesc_dense(0, 0, BM, BN), accum);
             } else if (KIND == KIND_BF16) {
@@ -296,7 +306,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // per-warp staging of the tile's column scales and bias: [0,BN) scale, [BN,2BN) bias
     float* colv = reinterpret_cast<float*>(smem + L::off_colv) + (warp - 2) * 2 * BN;
     const bool has_colv = args.b_scale != nullptr || args.bias != nullptr;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < total_tiles; item += gridDim.x) {
+      const int tile = item / splits, split = item - tile * splits;
       const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
       if (args.tile_expert != nullptr && args.tile_expert[m_tile] < 0) continue;
       const int row = m_tile * BM + q * 32 + lane;
@@ -325,7 +336,77 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      if (args.out_dtype != MSGL_F32) {
+      if (splits > 1) {
+        // raw partial sums of this K range -> workspace; the last range to arrive finishes the tile
+        const int ws_ld = args.n_tiles * BN;
+        const size_t ws_plane = (size_t)args.m_tiles * BM * ws_ld;
+        float* wrow = args.splitk_ws + (size_t)split * ws_plane + (size_t)row * ws_ld + colbase;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<uint4*>(wrow + c * 32 + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        // the four epilogue warps meet, one thread takes the tile's ticket
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          uint32_t seen;
+          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(seen) : "l"(args.splitk_count + tile), "r"(1u) : "memory");
+          *splitk_last = seen + 1u == (uint32_t)splits ? 1 : 0;
+          if (seen + 1u == (uint32_t)splits) args.splitk_count[tile] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*splitk_last) {
+          __threadfence();
+          const float* srow = args.splitk_ws + (size_t)row * ws_ld + colbase;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            float accv[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) accv[e] = 0.f;
+            for (int sp = 0; sp < splits; ++sp) {  // ascending K ranges: the order never changes
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(srow + (size_t)sp * ws_plane + c * 32 + g * 4));
+                accv[g * 4] += v.x; accv[g * 4 + 1] += v.y; accv[g * 4 + 2] += v.z; accv[g * 4 + 3] += v.w;
+              }
+            }
+            if (row_ok) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const int lc = c * 32 + g * 8;
+                if (colbase + lc < args.N) {
+                  float o[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    float x = accv[g * 8 + e] * a_s;
+                    if (has_colv) x = fmaf(x, colv[lc + e], colv[BN + lc + e]);
+                    o[e] = x;
+                  }
+                  if (args.out_dtype == MSGL_F32) {
+                    float* cp = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + colbase + lc;
+                    *reinterpret_cast<float4*>(cp) = make_float4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<float4*>(cp + 4) = make_float4(o[4], o[5], o[6], o[7]);
+                  } else {
+                    uint16_t* cp = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc + colbase + lc;
+                    *reinterpret_cast<uint4*>(cp) =
+                        make_uint4(pack2_out(args.out_dtype, o[0], o[1]), pack2_out(args.out_dtype, o[2], o[3]),
+                                   pack2_out(args.out_dtype, o[4], o[5]), pack2_out(args.out_dtype, o[6], o[7]));
+                  }
+                }
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // splitk_last is reused by the next item
+      } else if (args.out_dtype != MSGL_F32) {
         // pack the whole row segment, hand the accumulator back, then store in one burst
         // (stores interleaved with the conversion measured 2x slower)
         uint32_t packed[BN / 2];
@@ -843,7 +924,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& args, int max
     if (e != cudaSuccess) { msgl_set_error("gemm smem attribute", e); return MSGL_CUDA_ERROR; }
     configured = true;
   }
-  int total = args.m_tiles * args.n_tiles;
+  int total = args.m_tiles * args.n_tiles * args.splits;
   int grid = total < max_ctas ? total : max_ctas;
   gemm_tcgen05_kernel<KIND, BN, STAGES><<<grid, kThreads, smem, stream>>>(ma, mb, args);
   MSGL_CHECK_LAUNCH("gemm_tcgen05");
@@ -916,7 +997,6 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
   return launch_pair_impl<KIND, false>(ma, mb, msf, omaps, args, max_ctas, stream);
 }
 
-int g_dual_acc = 0;
 int g_pair_mode = 0;  // 0 = by size, 1 = never, 2 = whenever the arguments allow
 
 }  // namespace
@@ -976,7 +1056,8 @@ struct MsglGemmTp {
 static int gemm_impl(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
                      int K, const void* a_scale, const void* b_scale, const void* bias, int bias_dtype,
                      const void* sf_atoms, int out_dtype, int bn_override, int max_ctas, const void* tile_expert,
-                     int num_experts, cudaStream_t stream, const MsglGemmTp* tp = nullptr) {
+                     int num_experts, cudaStream_t stream, const MsglGemmTp* tp = nullptr, int splits = 1,
+                     void* splitk_ws = nullptr, void* splitk_count = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? MSGL_OK : MSGL_BAD_ARG;
   if (tp != nullptr) {
     if (tile_expert != nullptr || M % 128 || (tp->rs_world > 0 && out_dtype == MSGL_F32)) {
@@ -1038,11 +1119,20 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.sf_k_atoms = (K + 127) / 128;
   args.sf_n_atoms = (N + 127) / 128;
   args.tile_expert = (const int32_t*)tile_expert;
+  args.splits = 1;
+  args.kb_per_split = args.k_blocks;
+  args.splitk_ws = nullptr;
+  args.splitk_count = nullptr;
+  if (splits > 1 && !use_pair && tile_expert == nullptr && splitk_ws != nullptr && splitk_count != nullptr) {
+    args.splits = splits;
+    args.kb_per_split = (args.k_blocks + splits - 1) / splits;
+    args.splitk_ws = (float*)splitk_ws;
+    args.splitk_count = (uint32_t*)splitk_count;
+  }
   args.rs_world = 0;
   args.a_ready = nullptr;
   args.tile_order = 0;
   args.comm_wait_ns = 0;
-  args.dual_acc = g_dual_acc;
   if (tp != nullptr) {
     for (int i = 0; i < 8; ++i) {
       args.rs_slots[i] = tp->rs_slots[i];
@@ -1115,6 +1205,30 @@ MSGL_API int msgl_gemm(int kind, const void* a, long long lda, const void* b, vo
                    bn_override, max_ctas, nullptr, 0, stream);
 }
 
+// Split-K plan for small M: the number of K ranges depends on (kind, N, K) only, never on M, so a
+// row's result is the same at every batch size this applies to (M <= 256). Returns 1 when the
+// 128-wide tiles of two M tiles already fill half the GPU or K is short.
+MSGL_API int msgl_gemm_splitk_plan(int kind, int N, int K) {
+  const int bke = (kind == KIND_F16 || kind == KIND_BF16) ? 64 : 128;
+  const int n_tiles = (N + 127) / 128, kbs = (K + bke - 1) / bke;
+  int s = num_sms() / (2 * n_tiles);
+  if (s > kbs / 8) s = kbs / 8;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : s;
+}
+
+// msgl_gemm for M <= 256 with `splits` K ranges per tile (msgl_gemm_splitk_plan). ws: fp32
+// [splits][ceil(M/128)*128][ceil(N/128)*128]; counters: uint32 [ceil(M/128) * ceil(N/128)], zero on
+// entry and zero again on exit.
+MSGL_API int msgl_gemm_splitk(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M,
+                              int N, int K, const void* a_scale, const void* b_scale, const void* bias,
+                              int bias_dtype, const void* sf_atoms, int out_dtype, int splits, void* ws,
+                              void* counters, cudaStream_t stream) {
+  if (M > 256 || splits < 2 || ws == nullptr || counters == nullptr) return MSGL_BAD_ARG;
+  return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, out_dtype, 128, 0,
+                   nullptr, 0, stream, nullptr, splits, ws, counters);
+}
+
 // msgl_gemm with the tensor-parallel fusions of the CTA-pair kernel: the epilogue can push its
 // partial rows to the ranks that own them (GEMM -> reduce-scatter), and the producer can wait
 // for A row blocks that other ranks are still delivering (all-gather -> GEMM).
@@ -1147,7 +1261,6 @@ MSGL_API int msgl_gemm_grouped(int kind, const void* a, long long lda, const voi
 // 1 = single-CTA kernel always, 2 = CTA-pair kernel always. Returns the previous value.
 MSGL_API int msgl_gemm_pair_mode(int mode) {
   const int prev = g_pair_mode;
-  if (mode >= 256) { g_dual_acc = mode & 1; return prev; }
   if (mode >= 0 && mode <= 2) g_pair_mode = mode;
   return prev;
 }

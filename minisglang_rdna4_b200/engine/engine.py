@@ -183,6 +183,14 @@ class Engine:
             single_split=config.spec_algorithm != "none",
         )
         self.ctx.comm = comm_mod.get_comm()
+        self._spec_exact = config.spec_algorithm != "none" and dev_kind == "cuda"
+        if self._spec_exact:
+            # greedy speculative decoding must reproduce plain decoding bit for bit: verify rows
+            # (many per request) and decode rows have to take the same GEMM code path, so K is
+            # never split and verify steps never switch to the CTA-pair kernel
+            from ..ops import cuda as K
+
+            K.SPLIT_K = False
         if config.enable_ep and config.dp_size > 1:
             from ..parallel.ep import EPContext, FusedEPContext
 
@@ -391,6 +399,17 @@ class Engine:
         return self._forward_impl(batch, plan, args, return_logits)
 
     def _forward_impl(self, batch, plan, args, return_logits) -> ForwardOutput:
+        if self._spec_exact and batch.spec_verify:
+            from ..ops import cuda as K
+
+            prev = K.gemm_pair_mode(1)
+            try:
+                return self._forward_step(batch, plan, args, return_logits)
+            finally:
+                K.gemm_pair_mode(prev)
+        return self._forward_step(batch, plan, args, return_logits)
+
+    def _forward_step(self, batch, plan, args, return_logits) -> ForwardOutput:
         n_sample = int(plan.sample_rows.size)
         bs = batch.size
         use_graph = (self.graph_runner is not None and batch.is_decode and not batch.spec_verify

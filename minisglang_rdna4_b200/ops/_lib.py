@@ -28,6 +28,9 @@ _SIGNATURES = {
     "msgl_store_kv": (c_i, [c_p] * 7 + [c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
     "msgl_gemm": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_i, c_i, c_p]),
     "msgl_gemm_tp": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_p, c_p]),
+    "msgl_gemm_splitk_plan": (c_i, [c_i, c_i, c_i]),
+    "msgl_gemm_splitk": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p,
+                               c_p]),
     "msgl_gemm_status": (c_i, [c_i]),
     "msgl_gemm_pair_mode": (c_i, [c_i]),
     "msgl_attn_make_kv_map": (c_i, [c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_i]),

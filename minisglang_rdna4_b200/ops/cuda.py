@@ -237,6 +237,25 @@ KIND_F16, KIND_BF16, KIND_F8, KIND_MXF4 = 0, 1, 2, 3
 
 
 _PENDING_TP = None
+SPLIT_K = ENV.GEMM_SPLIT_K.value
+_SPLITK_PLANS: Dict[Tuple[int, int, int], int] = {}
+_SPLITK_COUNTERS: Dict[torch.device, torch.Tensor] = {}
+
+
+def _splitk_plan(kind: int, n: int, k: int) -> int:
+    key = (kind, n, k)
+    s = _SPLITK_PLANS.get(key)
+    if s is None:
+        s = _SPLITK_PLANS[key] = int(lib().msgl_gemm_splitk_plan(kind, n, k))
+    return s
+
+
+def _splitk_counters(device, n: int) -> torch.Tensor:
+    """Per-tile arrival counters: zero between calls (the kernel resets what it used)."""
+    t = _SPLITK_COUNTERS.get(device)
+    if t is None or t.numel() < n:
+        t = _SPLITK_COUNTERS[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return t
 
 
 def set_next_gemm_tp(args) -> None:
@@ -269,6 +288,18 @@ def _gemm(kind, a, b, n, k, out_dtype, a_scale=None, b_scale=None, bias=None, sf
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if m == 0:
         return out
+    if m <= 256 and bn == 0 and SPLIT_K:
+        splits = _splitk_plan(kind, n, k)
+        if splits > 1:
+            # small M: K ranges of one tile run on different SMs; the plan depends on (N, K) only
+            mt, nt = (m + 127) // 128, (n + 127) // 128
+            ws = torch.empty((splits, mt * 128, nt * 128), dtype=torch.float32, device=a.device)
+            check(lib().msgl_gemm_splitk(kind, _p(a), a.stride(0), _p(b), _p(out), n, m, n, k, _p(a_scale), _p(b_scale),
+                                         _p(bias), _DT[bias.dtype] if bias is not None else 0, _p(sf_atoms),
+                                         _DT[out_dtype], splits, _p(ws), _p(_splitk_counters(a.device, mt * nt)),
+                                         _stream()), "gemm_splitk")
+            _count(("gemm_f16", "gemm_bf16", "gemm_w8a8", "gemm_w4a8_mxfp4")[kind] + "_splitk", "gemm_tcgen05_kernel")
+            return out
     check(lib().msgl_gemm(kind, _p(a), a.stride(0), _p(b), _p(out), n, m, n, k, _p(a_scale), _p(b_scale), _p(bias),
                           _DT[bias.dtype] if bias is not None else 0, _p(sf_atoms), _DT[out_dtype], bn, max_ctas,
                           _stream()), "gemm")

@@ -347,3 +347,33 @@ def test_moe_forward_w4a8_mxfp4(K):
     want = R.moe_forward(x, d13, d2, w, ids)
     err = float((got.float() - want.float()).abs().max()) / float(want.float().abs().max())
     assert err < 0.08, err
+
+
+@pytest.mark.parametrize("n,k", [(2560, 4096), (2560, 9728), (1024, 2048)])
+def test_gemm_split_k_small_m(K, n, k):
+    """Small-M GEMMs whose tiles would leave most SMs idle split K over several CTAs. The plan
+    depends on (N, K) only, so a row's result is the same at every M up to 256, and the sum of the
+    K ranges is taken in a fixed order (repeatable bit for bit)."""
+    R = _ref()
+    from minisglang_rdna4_b200.ops._lib import lib
+    from minisglang_rdna4_b200.quant import mxfp4
+
+    splits = lib().msgl_gemm_splitk_plan(3, n, k)
+    x = torch.randn(200, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda") * 0.02
+    packed, sf = mxfp4.quantize_mxfp4(w)
+    atoms = mxfp4.pack_sf_atoms(sf)
+    xq, xs = K.per_token_quant_fp8(x)
+    want = R.gemm_w4a8_mxfp4(xq, xs, packed, sf)
+    y = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms)          # automatic: split-K when the plan says so
+    assert K.gemm_status() == 0
+    _close(y, want, 2e-2, 2e-2, f"split-k mxfp4 (splits={splits})")
+    assert torch.equal(y, K.gemm_w4a8_mxfp4(xq, xs, packed, atoms))            # repeatable
+    for m in (1, 7, 130):
+        assert torch.equal(K.gemm_w4a8_mxfp4(xq[:m].contiguous(), xs[:m].contiguous(), packed, atoms), y[:m])
+    xb = torch.randn(96, k, device="cuda").bfloat16()
+    wb = w.bfloat16()
+    bias = torch.randn(n, device="cuda").bfloat16()
+    _close(K.gemm(xb, wb, bias), xb.float() @ wb.float().t() + bias.float(), 2e-2, 2e-2, "split-k bf16 + bias")
+    _close(K.gemm(xb, wb, out_dtype=torch.float32), xb.float() @ wb.float().t(), 2e-3, 2e-3, "split-k f32 out")
+    assert K.gemm_status() == 0

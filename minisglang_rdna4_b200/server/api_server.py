@@ -7,6 +7,8 @@ as JSON or server-sent events. A client that disconnects mid-stream aborts its r
 """
 from __future__ import annotations
 
+import os
+
 import asyncio
 import json
 import time
@@ -426,6 +428,29 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
             choice["logprobs"] = {"content": lp_records}
         return JSONResponse({"id": rid, "object": obj, "created": created, "model": model, "choices": [choice],
                              "usage": _usage(prompt_tok, n_tok, cached)})
+
+    if os.environ.get("MSGL_CAM", os.environ.get("MINISGL_CAM", "0")) == "1":
+        # editable associative memory: /cam/* edit plane; /cam/ask answers through the served model
+        from ..cam import CamMemory
+        from .cam_api import make_cam_router
+
+        cam_memory = CamMemory(os.environ.get("MSGL_CAM_PATH") or None,
+                               int(os.environ.get("MSGL_CAM_MAX_NAMESPACES", "0") or 0))
+        app.state.cam = cam_memory
+
+        async def _cam_generate(prompt: str, max_tokens: int) -> str:
+            state.ensure_listener()
+            uid = state.new_user()
+            await state.send_one(TokenizeMsg(uid, prompt, SamplingParams(temperature=0.0, max_tokens=max_tokens)))
+            parts = []
+            async for reply in state.replies(uid):
+                if reply.error:
+                    raise HTTPException(status_code=500, detail=reply.error)
+                if reply.incremental_output:
+                    parts.append(reply.incremental_output)
+            return "".join(parts)
+
+        app.include_router(make_cam_router(cam_memory, _cam_generate if state.send_queue is not None else None))
 
     @app.post("/v1/chat/completions")
     async def v1_chat_completions(req: OpenAICompletionRequest, request: Request):

@@ -58,6 +58,9 @@ def main(argv=None) -> None:
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1400)
+    ap.add_argument("--ctx-min", type=int, default=0, help="decode: context lengths uniform in [ctx-min, ctx]")
+    ap.add_argument("--order", default="random", choices=["random", "desc", "asc"],
+                    help="decode with --ctx-min: order of the requests in the batch by context length")
     ap.add_argument("--seqs", type=int, default=6)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
@@ -118,12 +121,18 @@ def main(argv=None) -> None:
         bt = torch.arange(b * npg, device="cuda", dtype=torch.int32).view(b, npg)
         cu = torch.arange(b + 1, device="cuda", dtype=torch.int32) * q_len
         sl = torch.full((b,), kv_len, device="cuda", dtype=torch.int32)
+        if a.op == "attn_decode" and a.ctx_min > 0:
+            g = torch.Generator().manual_seed(0)
+            lens = torch.randint(a.ctx_min, kv_len + 1, (b,), generator=g)
+            if a.order != "random":
+                lens = lens.sort(descending=a.order == "desc").values
+            sl = lens.to("cuda", torch.int32)
         q = torch.randn(b * q_len, hq, d, device="cuda").bfloat16()
         ks = torch.ones(hk, device="cuda") / 8 if a.kv == "fp8" else None
         fn = lambda: K.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, d ** -0.5, k_scale=ks, v_scale=ks,
                                        max_q=q_len, max_kv=kv_len, decode=q_len == 1, splits=a.splits)
         ms = timeit(fn, a.iters, a.warmup, flush)
-        kv_bytes = b * kv_len * hk * d * 2 * pool.element_size()
+        kv_bytes = int(sl.sum()) * hk * d * 2 * pool.element_size()
         flops = 4.0 * b * hq * d * (kv_len * q_len if q_len == 1 else kv_len * kv_len / 2)
         out.update(batch=b, q_len=q_len, kv_len=kv_len, kv=a.kv, splits=a.splits, us=ms * 1e3,
                    kv_gbs=kv_bytes / ms / 1e6, tflops=flops / ms / 1e9, frac_of_hbm=kv_bytes / ms / 1e6 / hbm,

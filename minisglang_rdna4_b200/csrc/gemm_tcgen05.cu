@@ -1050,7 +1050,8 @@ struct MsglGemmTp {
 };
 
 // a: [M, K] (kind 0/1: 16-bit, kind 2/3: e4m3 bytes), row stride lda elements
-// b: [N, K] (kind 0/1: 16-bit, kind 2: e4m3 bytes, kind 3: packed e2m1 [N, K/2])
+// b: [N, K] (kind 0/1: 16-bit, kind 2: e4m3 bytes, kind 3: packed e2m1 [N, ceil(K/128)*64], zero codes
+//    past K)
 // c: [M, N] out_dtype, row stride ldc elements
 // bn_override: 0 = automatic, else 32 / 64 / 128; max_ctas: 0 = one per SM
 static int gemm_impl(int kind, const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
@@ -1170,7 +1171,10 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   } else if (kind == KIND_MXF4) {
     rc = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, K, M, (uint64_t)lda, 128, BM, false);
     if (rc) return rc;
-    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, K, b_rows, (uint64_t)K / 2, 128, b_box, true);
+    // 4-bit rows are stored in whole 128-element K blocks (zero codes past K); A's last block is
+    // zero-filled by TMA past its own K
+    const uint64_t kb4 = ((uint64_t)K + 127) / 128 * 128;
+    rc = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, kb4, b_rows, kb4 / 2, 128, b_box, true);
   } else {
     return MSGL_BAD_ARG;
   }

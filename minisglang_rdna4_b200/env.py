@@ -115,7 +115,7 @@ ENV = EnvRegistry()
 # --- engine -------------------------------------------------------------------------------
 ENV.flag("KV_FP8", False, "store the paged KV pool as e4m3 with per-(layer,head) scales")
 ENV.flag("DISABLE_OVERLAP", False, "run the synchronous scheduler loop instead of the overlapped one")
-ENV.flag("GEMM_SPLIT_K", True, "GEMMs with at most 256 rows split K over several SMs when their tiles leave most SMs idle")
+ENV.flag("GEMM_SPLIT_K", False, "experimental: GEMMs with at most 256 rows split K over several SMs (measured slower than full-K tiles; breaks chunk-size invariance)")
 ENV.flag("DISABLE_GRAPH", False, "never capture CUDA graphs (eager decode)")
 ENV.int("GRAPH_MAX_BS", 0, "largest decode batch captured as a CUDA graph (0 = auto)")
 ENV.int("EXIT_AFTER_STEPS", 0, "stop the scheduler loop after this many forward steps (0 = never)")

@@ -328,7 +328,11 @@ def gemm_w8a8(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16, bias=None, b
 
 
 def gemm_w4a8_mxfp4(x_q, x_scale, w_packed, sf_atoms, out_dtype=torch.bfloat16, bias=None, bn=0):
-    n, k = w_packed.shape[0], w_packed.shape[1] * 2
+    n, k = w_packed.shape[0], x_q.shape[-1]
+    if w_packed.shape[1] * 2 != (k + 127) // 128 * 128 and w_packed.shape[1] * 2 != k:
+        raise ValueError(f"gemm_w4a8_mxfp4: weights of K={w_packed.shape[1] * 2} do not match activations of K={k}")
+    if w_packed.shape[1] * 2 != k and k % 128 == 0:
+        raise ValueError("gemm_w4a8_mxfp4: padded weights with an unpadded K")
     if sf_atoms is None:
         raise ValueError("gemm_w4a8_mxfp4 needs the packed scale atoms (quant.mxfp4.pack_sf_atoms)")
     return _gemm(KIND_MXF4, x_q, w_packed, n, k, out_dtype, a_scale=x_scale, bias=bias, sf_atoms=sf_atoms, bn=bn)

@@ -205,6 +205,12 @@ class MxFp4Method(LinearMethod):
         layer._n, layer._k = layer.weight_packed.shape[0], layer.weight_packed.shape[1] * 2
         if layer.weight_packed.is_cuda:
             layer._sf_atoms = mx_codec.pack_sf_atoms(layer.weight_scale)
+            # the 4-bit tensor map wants K in whole 128-element blocks (a row-parallel shard of an
+            # odd intermediate size is not): pad the rows with zero codes; the activation's K block
+            # past its end is filled with zeros by TMA, so the padding contributes nothing
+            k_pad = (layer._k + 127) // 128 * 128
+            if k_pad != layer._k:
+                layer.weight_packed = torch.nn.functional.pad(layer.weight_packed, (0, (k_pad - layer._k) // 2))
 
     def apply(self, layer, x, bias):
         if not isinstance(x, ActQ):

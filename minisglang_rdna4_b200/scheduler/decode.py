@@ -35,5 +35,10 @@ class DecodeManager:
     def schedule_next_batch(self) -> Optional[Batch]:
         if not self.running:
             return None
-        reqs = sorted(self.running.values(), key=lambda r: r.uid)
+        # Longest context first (uid breaks ties, so the order is deterministic): the decode
+        # attention kernel runs one CTA per (request, KV head) in batch order, and starting the long
+        # ones first leaves the short ones to fill the tail. Measured on 256 requests with contexts
+        # in [600, 2300]: 162 us against 197 us in arrival order. The reference orders by uid
+        # (python/minisgl/scheduler/decode.py:62-71); nothing depends on the order of a batch.
+        reqs = sorted(self.running.values(), key=lambda r: (-r.device_len, r.uid))
         return Batch(reqs=reqs, phase="decode")

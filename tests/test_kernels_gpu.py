@@ -350,7 +350,7 @@ def test_moe_forward_w4a8_mxfp4(K):
 
 
 @pytest.mark.parametrize("n,k", [(2560, 4096), (2560, 9728), (1024, 2048)])
-def test_gemm_split_k_small_m(K, n, k):
+def test_gemm_split_k_small_m(K, n, k, monkeypatch):
     """Small-M GEMMs whose tiles would leave most SMs idle split K over several CTAs. The plan
     depends on (N, K) only, so a row's result is the same at every M up to 256, and the sum of the
     K ranges is taken in a fixed order (repeatable bit for bit)."""
@@ -365,7 +365,8 @@ def test_gemm_split_k_small_m(K, n, k):
     atoms = mxfp4.pack_sf_atoms(sf)
     xq, xs = K.per_token_quant_fp8(x)
     want = R.gemm_w4a8_mxfp4(xq, xs, packed, sf)
-    y = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms)          # automatic: split-K when the plan says so
+    monkeypatch.setattr(K, "SPLIT_K", True)               # off by default (experimental)
+    y = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms)          # split-K when the plan says so
     assert K.gemm_status() == 0
     _close(y, want, 2e-2, 2e-2, f"split-k mxfp4 (splits={splits})")
     assert torch.equal(y, K.gemm_w4a8_mxfp4(xq, xs, packed, atoms))            # repeatable
@@ -377,3 +378,24 @@ def test_gemm_split_k_small_m(K, n, k):
     _close(K.gemm(xb, wb, bias), xb.float() @ wb.float().t() + bias.float(), 2e-2, 2e-2, "split-k bf16 + bias")
     _close(K.gemm(xb, wb, out_dtype=torch.float32), xb.float() @ wb.float().t(), 2e-3, 2e-3, "split-k f32 out")
     assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("m", [5, 200, 700])
+def test_gemm_w4a8_mxfp4_k_not_multiple_of_128(K, m):
+    """A row-parallel shard can leave K = 1216 (9.5 blocks of 128): the 4-bit rows are padded with
+    zero codes to whole blocks, the activation keeps its own K and TMA zero-fills its last block."""
+    R = _ref()
+    from minisglang_rdna4_b200.quant import mxfp4
+
+    n, k = 2560, 1216
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda") * 0.02
+    packed, sf = mxfp4.quantize_mxfp4(w)
+    atoms = mxfp4.pack_sf_atoms(sf)
+    padded = torch.nn.functional.pad(packed, (0, (1280 - k) // 2))
+    xq, xs = K.per_token_quant_fp8(x)
+    want = R.gemm_w4a8_mxfp4(xq, xs, packed, sf)
+    for bn in (0, 128, 256):
+        y = K.gemm_w4a8_mxfp4(xq, xs, padded, atoms, bn=bn)
+        assert K.gemm_status() == 0
+        _close(y, want, 2e-2, 2e-2, f"mxfp4 K=1216 bn={bn}")

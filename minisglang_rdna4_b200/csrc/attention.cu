@@ -126,7 +126,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
   const int q_begin = args.cu_q[b], q_len = args.cu_q[b + 1] - q_begin;
   const int kv_len = args.seq_lens[b];
   const int pos_per_tile = (16 * NWQ) / G;
-  const int q_start = blockIdx.x * pos_per_tile;
+  // query tiles are handed out last-first: under a causal mask the late tiles see the most keys,
+  // and starting them first leaves the short ones to fill the tail of the grid
+  const int q_start = (int)(gridDim.x - 1 - blockIdx.x) * pos_per_tile;
   if (q_start >= q_len) return;   // uniform for the CTA; nothing has been initialised yet
   const int q_end = min(q_start + pos_per_tile, q_len);
 

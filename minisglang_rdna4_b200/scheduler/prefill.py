@@ -134,4 +134,7 @@ class PrefillManager:
         if not reqs:
             return None, None
         self.pending = self.pending[done:]
+        # longest extend first: the attention grid walks requests in batch order and the long ones
+        # have the most work per query tile (admission order only decided who got into the step)
+        reqs.sort(key=lambda r: (-(r.device_len - r.cached_len), r.uid))
         return Batch(reqs=reqs, phase="prefill"), adder

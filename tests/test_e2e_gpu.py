@@ -67,3 +67,56 @@ def test_bf16_engine_tracks_fp32_oracle():
     cpu.shutdown()
     first_ok = sum(g[0] == w[0] for g, w in zip(got, want))
     assert first_ok >= len(want) - 1, (got, want)
+
+
+def _tp_worker(rank, world, port, env, out_q):
+    import os
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0", **env)
+    torch.cuda.set_device(rank)
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import cuda as K
+    from minisglang_rdna4_b200.parallel.comm import get_comm
+
+    llm = LLM(model_config=_cfg(layers=3), use_dummy_weight=True, quantization="mxfp4", kv_cache_dtype="fp8",
+              device="cuda", tp_size=world, tp_rank=rank, page_size=16, max_running_req=8,
+              num_page_override=512, seed=0)
+    outs = llm.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    calls = dict(get_comm().calls)
+    ok = K.gemm_status() == 0 and K.attn_status() == 0
+    if rank == 0:
+        out_q.put(([o.token_ids for o in outs], calls, ok))
+    llm.shutdown()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_fused_paths_track_nccl_only_path():
+    """Two tensor-parallel ranks: the peer-memory paths (one-shot all-reduce + norm for decode,
+    GEMM -> reduce-scatter -> norm -> all-gather -> GEMM for the 800-token prefill step,
+    vocabulary-parallel arg-max) against the same engine with every collective on NCCL. The
+    fused kernels round once after adding the residual, NCCL rounds the sum first, so late
+    tokens of a sequence may differ; the first tokens must agree."""
+    import os
+
+    import torch.multiprocessing as mp
+
+    results = {}
+    for name, env in (("fused", {}), ("nccl", {"MSGL_DISABLE_FUSED_COMM": "1"})):
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 29300 + os.getpid() % 500 + (7 if name == "nccl" else 0)
+        procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, env, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        results[name] = q.get(timeout=300)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    (fused, calls, ok), (nccl, calls_nccl, ok2) = results["fused"], results["nccl"]
+    assert ok and ok2
+    assert calls.get("fused_rs_ag", 0) > 0 and calls.get("fused_ar_norm", 0) > 0 and calls.get("vocab_argmax", 0) > 0
+    assert calls_nccl.get("fused_rs_ag", 0) == 0 and calls_nccl.get("fused_ar_norm", 0) == 0
+    same_first = sum(a[:3] == b[:3] for a, b in zip(fused, nccl))
+    assert same_first >= len(fused) - 1, (fused, nccl)

@@ -65,10 +65,12 @@ __device__ __forceinline__ unsigned long long gtimer() {
   return t;
 }
 
-// One CTA per row. NORM: residual add + RMSNorm after the reduction. QUANT: e4m3 output.
-template <typename T, bool NORM, bool QUANT>
-__global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
-  extern __shared__ float row_s[];
+// One 128-thread CTA per row, the row held in registers (VPT 16-byte vectors per thread) from the
+// push to the final store. NORM: residual add + RMSNorm after the reduction. QUANT: e4m3 output.
+constexpr int kArThreads = 128;
+
+template <typename T, bool NORM, bool QUANT, int VPT>
+__global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) {
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const int H = a.hidden;
@@ -76,16 +78,26 @@ __global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
   const int parity = (int)(seq & 1u);
   const T* xr = reinterpret_cast<const T*>(a.x) + (size_t)row * H;
 
-  // 1. push this rank's partial row into every rank's slot (its own included)
+  // 1. push this rank's partial row into every PEER's slot (its own copy stays in registers)
+  uint4 mine_raw[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kArThreads + threadIdx.x) * 8;
+    if (i < H) mine_raw[j] = *reinterpret_cast<const uint4*>(xr + i);
+  }
   for (int p = 0; p < a.nranks; ++p) {
+    if (p == a.rank) continue;
     T* dst = reinterpret_cast<T*>(a.slots[p]) + (size_t)(parity * a.nranks + a.rank) * a.slot_stride +
              (size_t)row * a.max_hidden;
-    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8)
-      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(xr + i);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kArThreads + threadIdx.x) * 8;
+      if (i < H) *reinterpret_cast<uint4*>(dst + i) = mine_raw[j];
+    }
   }
   __syncthreads();
   // 2. raise the flag on every peer, then wait for every peer's flag here
-  if (threadIdx.x < a.nranks) {
+  if (threadIdx.x < a.nranks && threadIdx.x != a.rank) {
     const int p = threadIdx.x;
     // the barrier above orders the CTA's row stores before this thread; the release store makes
     // them visible system-wide before the flag (no separate fence: a system-scope fence per row
@@ -107,31 +119,40 @@ __global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
   const T* base = reinterpret_cast<const T*>(a.slots[a.rank]) + (size_t)(parity * a.nranks) * a.slot_stride +
                   (size_t)row * a.max_hidden;
   T* rr = NORM ? reinterpret_cast<T*>(a.residual) + (size_t)row * H : nullptr;
+  float v[VPT][8];
   float ss = 0.f;
-  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-    float acc[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-    for (int q = 0; q < a.nranks; ++q) {
-      float v[8];
-      load8(base + (size_t)q * a.slot_stride + i, v);
+  for (int j = 0; j < VPT; ++j) {
+    const int i = (j * kArThreads + threadIdx.x) * 8;
+    if (i < H) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += v[k];
-    }
-    if (NORM) {
-      float r[8];
-      load8(rr + i, r);
+      for (int k = 0; k < 8; ++k) v[j][k] = 0.f;
+      for (int q = 0; q < a.nranks; ++q) {
+        float x[8];
+        if (q == a.rank) {
+          const T* own = reinterpret_cast<const T*>(&mine_raw[j]);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += r[k];
-      store8(rr + i, acc);
+          for (int k = 0; k < 8; ++k) x[k] = to_float(own[k]);
+        } else {
+          load8(base + (size_t)q * a.slot_stride + i, x);
+        }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        acc[k] = to_float(from_float<T>(acc[k]));
-        ss += acc[k] * acc[k];
-        row_s[i + k] = acc[k];
+        for (int k = 0; k < 8; ++k) v[j][k] += x[k];
       }
-    } else {
-      store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, acc);
+      if (NORM) {
+        float r[8];
+        load8(rr + i, r);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j][k] += r[k];
+        store8(rr + i, v[j]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          v[j][k] = to_float(from_float<T>(v[j][k]));
+          ss += v[j][k] * v[j][k];
+        }
+      } else {
+        store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, v[j]);
+      }
     }
   }
   if (NORM) {
@@ -139,51 +160,53 @@ __global__ void __launch_bounds__(1024) ar_oneshot_kernel(const ArArgs a) {
     const float rstd = rsqrtf(ss / (float)H + a.eps);
     const T* w = reinterpret_cast<const T*>(a.weight);
     float amax = 0.f;
-    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-      float wv[8], y[8];
-      load8(w + i, wv);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        y[k] = to_float(from_float<T>(row_s[i + k] * rstd * (wv[k] + a.w_offset)));
-        if (QUANT) {
-          amax = fmaxf(amax, fabsf(y[k]));
-          row_s[i + k] = y[k];
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kArThreads + threadIdx.x) * 8;
+      if (i < H) {
+        float wv[8];
+        load8(w + i, wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          v[j][k] = to_float(from_float<T>(v[j][k] * rstd * (wv[k] + a.w_offset)));
+          if (QUANT) amax = fmaxf(amax, fabsf(v[j][k]));
         }
+        if (!QUANT) store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, v[j]);
       }
-      if (!QUANT) store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, y);
     }
     if (QUANT) {
       amax = block_max(amax, scratch);
       const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
       if (threadIdx.x == 0) a.out_scale[row] = scale;
-      for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-        float y[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) y[k] = row_s[i + k];
-        *reinterpret_cast<uint2*>(a.out_q + (size_t)row * H + i) = pack8_e4m3(y, scale);
+      for (int j = 0; j < VPT; ++j) {
+        const int i = (j * kArThreads + threadIdx.x) * 8;
+        if (i < H) *reinterpret_cast<uint2*>(a.out_q + (size_t)row * H + i) = pack8_e4m3(v[j], scale);
       }
     }
   }
   if (threadIdx.x == 0) a.seq[row] = seq;
 }
 
+template <typename T, int VPT>
+void launch_ar_vpt(const ArArgs& a, cudaStream_t stream) {
+  const bool norm = a.residual != nullptr, quant = a.out_q != nullptr;
+  if (norm && quant) ar_oneshot_kernel<T, true, true, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
+  else if (norm) ar_oneshot_kernel<T, true, false, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
+  else ar_oneshot_kernel<T, false, false, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
+}
+
 template <typename T>
 int launch_ar(const ArArgs& a, cudaStream_t stream) {
-  int threads = ((a.hidden / 8 + 31) / 32) * 32;
-  if (threads > 1024) threads = 1024;
-  if (threads < 32 * ((a.nranks + 31) / 32)) threads = 32;
-  const bool norm = a.residual != nullptr, quant = a.out_q != nullptr;
-  const size_t smem = norm ? (size_t)a.hidden * sizeof(float) : 0;
-#define AR_LAUNCH(N, Q)                                                                                      \
-  do {                                                                                                        \
-    if (smem > 48 * 1024)                                                                                     \
-      cudaFuncSetAttribute(ar_oneshot_kernel<T, N, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    ar_oneshot_kernel<T, N, Q><<<a.rows, threads, smem, stream>>>(a);                                          \
-  } while (0)
-  if (norm && quant) AR_LAUNCH(true, true);
-  else if (norm) AR_LAUNCH(true, false);
-  else AR_LAUNCH(false, false);
-#undef AR_LAUNCH
+  const int vpt = (a.hidden / 8 + kArThreads - 1) / kArThreads;
+  if (vpt <= 1) launch_ar_vpt<T, 1>(a, stream);
+  else if (vpt <= 2) launch_ar_vpt<T, 2>(a, stream);
+  else if (vpt <= 3) launch_ar_vpt<T, 3>(a, stream);
+  else if (vpt <= 4) launch_ar_vpt<T, 4>(a, stream);
+  else if (vpt <= 6) launch_ar_vpt<T, 6>(a, stream);
+  else if (vpt <= 8) launch_ar_vpt<T, 8>(a, stream);
+  else if (vpt <= 16) launch_ar_vpt<T, 16>(a, stream);
+  else return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("ar_oneshot");
   return MSGL_OK;
 }
@@ -471,7 +494,7 @@ MSGL_API int msgl_ar_oneshot(const void* x, void* residual, const void* weight, 
                              int nranks, int rows, int hidden, int max_rows, int max_hidden, float eps,
                              int plus_one, long long wait_us, int dtype, cudaStream_t stream) {
   if (rows == 0) return MSGL_OK;
-  if (nranks > kMaxRanks || rows > max_rows || hidden > max_hidden || hidden % 8 || hidden > 48 * 1024) {
+  if (nranks > kMaxRanks || rows > max_rows || hidden > max_hidden || hidden % 8 || hidden > 16 * 8 * 128) {
     msgl_set_error_text("ar_oneshot: message does not fit the symmetric slots");
     return MSGL_BAD_ARG;
   }

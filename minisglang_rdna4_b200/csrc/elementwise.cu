@@ -240,14 +240,22 @@ static int launch_act_quant(const void* x, void* out_q, void* out_scale, int row
     else return MSGL_BAD_ARG;
     return MSGL_OK;
   }
+  if (inter >= 2048) {
+    // many long rows (prefill): 256 threads per row halve the registers a thread holds between the
+    // two passes, which doubles the resident warps
+    const int v256 = (inter / 8 + 255) / 256;
+    if (v256 <= 1) ACT_LAUNCH(1, 256);
+    else if (v256 <= 2) ACT_LAUNCH(2, 256);
+    else if (v256 <= 3) ACT_LAUNCH(3, 256);
+    else if (v256 <= 5) ACT_LAUNCH(5, 256);
+    else if (v256 <= 8) ACT_LAUNCH(8, 256);
+    else if (v256 <= 14) ACT_LAUNCH(14, 256);
+    else return MSGL_BAD_ARG;
+    return MSGL_OK;
+  }
   if (vpt <= 1) ACT_LAUNCH(1, kRowThreads);
   else if (vpt <= 2) ACT_LAUNCH(2, kRowThreads);
   else if (vpt <= 4) ACT_LAUNCH(4, kRowThreads);
-  else if (vpt <= 6) ACT_LAUNCH(6, kRowThreads);
-  else if (vpt <= 8) ACT_LAUNCH(8, kRowThreads);
-  else if (vpt <= 10) ACT_LAUNCH(10, kRowThreads);
-  else if (vpt <= 16) ACT_LAUNCH(16, kRowThreads);
-  else if (vpt <= 28) ACT_LAUNCH(28, kRowThreads);
   else return MSGL_BAD_ARG;
 #undef ACT_LAUNCH
   return MSGL_OK;

@@ -218,6 +218,102 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_fast_kernel(
   }
 }
 
+// Vectorised variant for the common case (head_dim 128, full NeoX rotation): eight lanes own one
+// head, each lane holding eight consecutive elements of the low half and the matching eight of
+// the high half (one 16-byte load each), so a warp covers four heads; the per-head RMS is a
+// reduction over the eight lanes; q leaves as 16-byte stores and fp8 K/V as 8-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(128) qk_norm_rope_store_vec128_kernel(
+    const T* __restrict__ qkv, const T* __restrict__ q_w, const T* __restrict__ k_w,
+    const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, T* __restrict__ q_out,
+    void* __restrict__ k_cache, void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
+    const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hq, int hk, int page_size, float eps,
+    int cache_fp8, int max_pos, int num_slots) {
+  constexpr int D = 128, H2 = 64;
+  const int token = blockIdx.x;
+  const int sub = threadIdx.x & 7;                       // lane within the head's group of eight
+  const int head = blockIdx.y * 16 + (threadIdx.x >> 3);
+  const int heads_total = hq + 2 * hk;
+  const bool live = head < heads_total;
+  const int hd = live ? head : heads_total - 1;          // idle groups shadow the last head (no stores)
+  const T* src = qkv + (size_t)token * heads_total * D + (size_t)hd * D;
+  float a[8], b[8];
+  load8(src + sub * 8, a);
+  load8(src + H2 + sub * 8, b);
+  float ss = 0.f;
+#pragma unroll
+  for (int t = 0; t < 8; ++t) ss += a[t] * a[t] + b[t] * b[t];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  if (!live) return;
+  const bool is_q = head < hq, is_k = !is_q && head < hq + hk;
+  if (is_q || is_k) {
+    const T* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      const float rstd = rsqrtf(ss / (float)D + eps);
+      float wl[8], wh[8];
+      load8(w + sub * 8, wl);
+      load8(w + H2 + sub * 8, wh);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        a[t] = to_float(from_float<T>(a[t] * rstd * wl[t]));
+        b[t] = to_float(from_float<T>(b[t] * rstd * wh[t]));
+      }
+    }
+    int pos = positions[token];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * D + sub * 8);
+    const float4* sn = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * D + H2 + sub * 8);
+    const float4 c0 = cs[0], c1 = cs[1], s0 = sn[0], s1 = sn[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const float x0 = a[t], x1 = b[t];
+      a[t] = x0 * c[t] - x1 * sv[t];
+      b[t] = x1 * c[t] + x0 * sv[t];
+    }
+  }
+  if (is_q) {
+    T* dst = q_out + ((size_t)token * hq + head) * D;
+    store8(dst + sub * 8, a);
+    store8(dst + H2 + sub * 8, b);
+    return;
+  }
+  const int kvh = is_k ? head - hq : head - hq - hk;
+  const int slot = out_loc[token];
+  if (slot < 0 || slot >= num_slots) return;
+  const int page = slot / page_size, off = slot % page_size;
+  const size_t base = (((size_t)page * hk + kvh) * page_size + off) * D;
+  void* cache = is_k ? k_cache : v_cache;
+  if (cache_fp8) {
+    const float sc = is_k ? k_scale[kvh] : v_scale[kvh];
+    uint8_t* dst = (uint8_t*)cache + base;
+    float ra[8], rb[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      ra[t] = to_float(from_float<T>(a[t])) / sc;   // same rounding and division as the scalar kernel
+      rb[t] = to_float(from_float<T>(b[t])) / sc;
+    }
+    uint2 pa, pb;
+    pa.x = (uint32_t)float_to_e4m3(ra[0]) | ((uint32_t)float_to_e4m3(ra[1]) << 8) | ((uint32_t)float_to_e4m3(ra[2]) << 16) |
+           ((uint32_t)float_to_e4m3(ra[3]) << 24);
+    pa.y = (uint32_t)float_to_e4m3(ra[4]) | ((uint32_t)float_to_e4m3(ra[5]) << 8) | ((uint32_t)float_to_e4m3(ra[6]) << 16) |
+           ((uint32_t)float_to_e4m3(ra[7]) << 24);
+    pb.x = (uint32_t)float_to_e4m3(rb[0]) | ((uint32_t)float_to_e4m3(rb[1]) << 8) | ((uint32_t)float_to_e4m3(rb[2]) << 16) |
+           ((uint32_t)float_to_e4m3(rb[3]) << 24);
+    pb.y = (uint32_t)float_to_e4m3(rb[4]) | ((uint32_t)float_to_e4m3(rb[5]) << 8) | ((uint32_t)float_to_e4m3(rb[6]) << 16) |
+           ((uint32_t)float_to_e4m3(rb[7]) << 24);
+    *reinterpret_cast<uint2*>(dst + sub * 8) = pa;
+    *reinterpret_cast<uint2*>(dst + H2 + sub * 8) = pb;
+  } else {
+    T* dst = (T*)cache + base;
+    store8(dst + sub * 8, a);
+    store8(dst + H2 + sub * 8, b);
+  }
+}
+
 MSGL_API int msgl_qk_norm_rope_store(const void* qkv, const void* q_w, const void* k_w, const void* positions,
                                      const void* cos_sin, void* q_out, void* k_cache, void* v_cache,
                                      const void* out_loc, const void* k_scale, const void* v_scale, int tokens,
@@ -229,7 +325,12 @@ MSGL_API int msgl_qk_norm_rope_store(const void* qkv, const void* q_w, const voi
  dim3 grid(tokens, (hq + 2 * hk + 3) / 4);
 #define LAUNCH(T, D)                                                                                        \
   do {                                                                                                      \
-  if (rot == head_dim)                                                                                      \
+  if (rot == head_dim && D == 128 && !interleaved)                                                          \
+    qk_norm_rope_store_vec128_kernel<T><<<dim3(tokens, (hq + 2 * hk + 15) / 16), 128, 0, stream>>>(         \
+        (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,      \
+        (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale, \
+        hq, hk, page_size, eps, cache_fp8, max_pos, num_slots);                                             \
+  else if (rot == head_dim)                                                                                 \
     qk_norm_rope_store_fast_kernel<T, D><<<grid, 128, 0, stream>>>(                                         \
         (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,      \
         (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale, \

@@ -280,7 +280,8 @@ def main() -> None:
             "data": "synthetic (uniform-random token ids, random-init weights seed 1)",
             "impl": "ours",
             "config": {
-                "model": f"{args.model}-shaped dense, {args.quant} W4A8, {args.kv} KV",
+                "model": f"{args.model}-shaped {'MoE' if eng.model_config.is_moe else 'dense'}, {args.quant}"
+                         f"{' W4A8' if args.quant == 'mxfp4' else ''}, {args.kv} KV",
                 "global_batch": args.requests, "seq_len": f"in U[{args.in_min},{args.in_max}], out {args.out_len}",
                 "parallelism": f"tp{world}", "step": "one full pass of the workload (prefill + decode)",
                 "l2": "inputs larger than L2 (weights + KV pool >> 126 MB)",

@@ -109,6 +109,8 @@ class GemmaForCausalLM(BaseOP):
         self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype, device,
                                       tied=self.model.embed_tokens if cfg.tie_word_embeddings else None)
         self._embed_scale = float(cfg.hidden_size) ** 0.5
+        self._embed_scale_dtype = None
+        self._embed_scale_rounded = self._embed_scale
 
     @property
     def config(self) -> ModelConfig:
@@ -120,7 +122,11 @@ class GemmaForCausalLM(BaseOP):
         capture = ctx.batch.capture_layers
         x = self.model.embed_tokens.forward(input_ids)
         # the scale is rounded to the activation dtype first, as the published implementation does
-        x = x * torch.tensor(self._embed_scale, dtype=x.dtype, device=x.device)
+        # (a Python scalar: nothing is copied to the device, so the step stays graph-capturable)
+        if self._embed_scale_dtype != x.dtype:
+            self._embed_scale_rounded = float(torch.tensor(self._embed_scale, dtype=x.dtype))
+            self._embed_scale_dtype = x.dtype
+        x = x * self._embed_scale_rounded
         seen = {}
         for i, layer in enumerate(self.model.layers):
             if capture is not None and i in capture:

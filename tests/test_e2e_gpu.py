@@ -151,3 +151,35 @@ def test_moe_model_graph_matches_eager(quant):
         llm.shutdown()
     assert outs["graph"] == outs["eager"]
     assert all(len(t) == 10 for t in outs["graph"])
+
+
+def test_gemma_style_model_tracks_fp32_oracle():
+    """The Gemma-family decoder on the kernel path ((1 + w) norms, GeGLU, sliding-window layers,
+    custom query scale, scaled embeddings) against the CPU fp32 oracle path with the same weights."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=4, num_qo_heads=4, num_kv_heads=2, head_dim=128, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-6, hidden_act="gelu_pytorch_tanh",
+            rotary_config=RotaryConfig(head_dim=128, rotary_dim=128, max_position=2048, base=1e6),
+            model_type="gemma3_text", architectures=("Gemma3ForCausalLM",), qk_norm=True, tie_word_embeddings=True,
+            max_position_embeddings=2048, sliding_window=64, query_pre_attn_scalar=96.0, rope_local_base_freq=1e4,
+            layer_types=("sliding_attention", "full_attention", "sliding_attention", "full_attention"),
+        )
+
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    gpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    state = {k: v.float().cpu() for k, v in gpu.engine.model.state_dict().items()}
+    got = [o.token_ids for o in gpu.generate(_prompts(), sp)]
+    gpu.shutdown()
+    cpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    cpu.engine.model.load_state_dict(state, strict=False)
+    want = [o.token_ids for o in cpu.generate(_prompts(), sp)]
+    cpu.shutdown()
+    first_ok = sum(g[0] == w[0] for g, w in zip(got, want))
+    assert first_ok >= len(want) - 1, (got, want)

@@ -183,3 +183,44 @@ def test_gemma_style_model_tracks_fp32_oracle():
     cpu.shutdown()
     first_ok = sum(g[0] == w[0] for g, w in zip(got, want))
     assert first_ok >= len(want) - 1, (got, want)
+
+
+@pytest.mark.parametrize("quant,kv", [(None, "bf16"), ("mxfp4", "fp8")])
+def test_speculative_decoding_is_exact_on_the_gpu(quant, kv):
+    """Greedy output with a proposer (n-gram, EAGLE3 draft head) equals plain greedy decoding on
+    the kernel path: verify rows go through the tree-mask attention kernel and the same GEMM code
+    path as decode rows."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import cuda as K
+
+    def make(**kw):
+        return LLM(model_config=_cfg(), use_dummy_weight=True, quantization=quant, kv_cache_dtype=kv, device="cuda",
+                   page_size=16, max_running_req=8, num_page_override=256, seed=0, **kw)
+
+    from minisglang_rdna4_b200.spec.base import Proposer
+
+    class NoDraft(Proposer):
+        """Never proposes: every step verifies one row per request, i.e. plain greedy decoding on
+        the code path a speculative engine uses (general attention kernel, unsplit K)."""
+
+        name = "none"
+
+        def propose(self, reqs):
+            return [[] for _ in reqs]
+
+    prompts = _prompts() + [[5, 6, 7, 8, 9, 10, 11, 12] * 8]   # a repetitive prompt for the n-gram lookup
+    sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    plain = make(spec_algorithm="ngram", spec_num_draft=4)
+    plain.proposer = NoDraft(4)
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    assert plain.stats["spec_accepted"] == 0
+    plain.shutdown()
+    for algo, draft in (("ngram", 4), ("eagle3", 3)):
+        spec = make(spec_algorithm=algo, spec_num_draft=draft)
+        got = [o.token_ids for o in spec.generate(prompts, sp)]
+        assert K.gemm_status() == 0 and K.attn_status() == 0
+        assert spec.stats["spec_steps"] > 0 and spec.stats["spec_drafted"] > 0
+        spec.cache.check_integrity()
+        spec.shutdown()
+        assert got == want, algo

@@ -21,6 +21,7 @@ class AttnMetadata:
     causal: bool = True
     mask: Optional[torch.Tensor] = None   # additive [T, >= max_kv] bias for tree verification
     workspace: Optional[torch.Tensor] = None
+    prefill_plan: Optional[object] = None  # ops.cuda.PrefillPlan of a prefill-phase step on a GPU
 
 
 class BaseAttnBackend(ABC):

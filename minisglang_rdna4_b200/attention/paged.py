@@ -34,16 +34,38 @@ class PagedAttentionBackend(BaseAttnBackend):
             K.force_general_decode_attention(single_split)
 
     def prepare_metadata(self, batch: Batch, block_table, cu_q, seq_lens, max_q: int, max_kv: int,
-                         causal: bool = True, mask: Optional[torch.Tensor] = None) -> None:
+                         causal: bool = True, mask: Optional[torch.Tensor] = None,
+                         host_cu_q=None, host_seq_lens=None) -> None:
+        """``host_cu_q`` / ``host_seq_lens`` are the same lengths as numpy arrays: a prefill-phase
+        step on a GPU builds the tables of the tensor-core prefill kernel from them (every such
+        step, whatever its size, so that a row's result does not depend on how its prompt was
+        chunked). Decode and verification steps stay on the general kernel."""
+        plan = None
+        if (host_cu_q is not None and batch.is_prefill and not batch.spec_verify and mask is None and causal
+                and self._workspace is not None and self.d == 128 and (self.hq // self.hk) % 2 == 0):
+            from ..env import ENV
+            from ..ops import cuda as K
+
+            if not ENV.DISABLE_TC_PREFILL.value:
+                plan = K.PrefillPlan(host_cu_q, host_seq_lens, self.device)
         batch.attn_metadata = AttnMetadata(
             cu_q=cu_q, seq_lens=seq_lens, block_table=block_table, max_q=max_q, max_kv=max_kv,
-            decode=(max_q == 1), causal=causal, mask=mask, workspace=self._workspace,
+            decode=(max_q == 1 and plan is None), causal=causal, mask=mask, workspace=self._workspace,
+            prefill_plan=plan,
         )
 
     def forward(self, q, layer: int, batch: Batch, *, scale: float, window: int = 0):
         md = batch.attn_metadata
         pool = get_global_ctx().kv_cache
         fp8 = getattr(pool, "fp8", False)
+        if md.prefill_plan is not None and not window:
+            from ..ops import cuda as K
+
+            k_cache = pool.k_cache(layer)
+            if K.prefill_attention_tc_ok(q, k_cache, causal=md.causal, window=window, mask=md.mask, decode=False):
+                return K.prefill_attention_tc(
+                    q, k_cache, pool.v_cache(layer), md.block_table, md.prefill_plan, scale,
+                    k_scale=pool.k_scale[layer] if fp8 else None, v_scale=pool.v_scale[layer] if fp8 else None)
         splits = 1
         if md.decode and not self.single_split and q.is_cuda:
             from ..ops.cuda import choose_splits

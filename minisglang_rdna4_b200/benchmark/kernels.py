@@ -67,6 +67,7 @@ def main(argv=None) -> None:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--general", action="store_true", help="attn_prefill: the warp-level MMA kernel instead of the tcgen05 one")
     ap.add_argument("--kv", default="fp8", choices=["fp8", "bf16"])
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--top-k", type=int, default=8)
@@ -129,12 +130,17 @@ def main(argv=None) -> None:
             sl = lens.to("cuda", torch.int32)
         q = torch.randn(b * q_len, hq, d, device="cuda").bfloat16()
         ks = torch.ones(hk, device="cuda") / 8 if a.kv == "fp8" else None
+        plan = None
+        if q_len > 1 and not a.general:
+            plan = K.PrefillPlan(cu.cpu().numpy(), sl.cpu().numpy(), q.device)  # once per step, as the engine does
         fn = lambda: K.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, d ** -0.5, k_scale=ks, v_scale=ks,
-                                       max_q=q_len, max_kv=kv_len, decode=q_len == 1, splits=a.splits)
+                                       max_q=q_len, max_kv=kv_len, decode=q_len == 1, splits=a.splits, plan=plan,
+                                       tc=plan is not None)
         ms = timeit(fn, a.iters, a.warmup, flush)
         kv_bytes = int(sl.sum()) * hk * d * 2 * pool.element_size()
         flops = 4.0 * b * hq * d * (kv_len * q_len if q_len == 1 else kv_len * kv_len / 2)
         out.update(batch=b, q_len=q_len, kv_len=kv_len, kv=a.kv, splits=a.splits, us=ms * 1e3,
+                   kernel=K.LEDGER.get("prefill_attention", K.LEDGER.get("paged_attention")),
                    kv_gbs=kv_bytes / ms / 1e6, tflops=flops / ms / 1e9, frac_of_hbm=kv_bytes / ms / 1e6 / hbm,
                    frac_of_bf16_peak=flops / ms / 1e9 / tf)
         assert K.attn_status() == 0

@@ -204,9 +204,22 @@ def choose_splits(batch, hk, max_kv, decode):
 
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, causal=True, window=0, mask=None,
-                    k_scale=None, v_scale=None, max_q=0, max_kv=0, decode=False, workspace=None, splits=None):
+                    k_scale=None, v_scale=None, max_q=0, max_kv=0, decode=False, workspace=None, splits=None,
+                    plan=None, tc=None):
+    """``plan`` (a ``PrefillPlan``) or ``tc=True`` sends a causal prefill / extend step to the
+    tcgen05 kernel when it covers the shape (``tc=True`` without a plan builds the step tables from
+    the device lengths, which synchronises). Without either the general kernel runs: decode and
+    verification steps must not change kernels with the number of rows per request."""
     t, hq, d = q.shape
     pages_p1, hk, ps, _ = k_cache.shape
+    if max_q <= 0:
+        max_q = int((cu_q[1:] - cu_q[:-1]).max())
+    if tc is None:
+        tc = plan is not None
+    if tc and prefill_attention_tc_ok(q, k_cache, causal=causal, window=window, mask=mask, decode=decode):
+        if plan is None:
+            plan = PrefillPlan(cu_q.cpu().numpy(), seq_lens.cpu().numpy(), q.device)
+        return prefill_attention_tc(q, k_cache, v_cache, block_table, plan, scale, k_scale=k_scale, v_scale=v_scale)
     desc, layer, layers = _kv_map(k_cache)
     b = seq_lens.numel()
     if max_q <= 0:
@@ -229,6 +242,86 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, 
         b, t, max_q, hq, hk, d, ps, pages_p1 - 1, layer, layers, int(fp8), int(causal), int(window), splits,
         float(scale), _dt(q), _stream()), "paged_attention")
     _count("paged_attention", "paged_attention_kernel", 2 if splits > 1 else 1)
+    return out
+
+
+class PrefillPlan:
+    """Per-step tables of the tensor-core prefill kernel: one item per (request, block of 128
+    query positions), heaviest first; the request of every 128-row scratch block; per request
+    the scratch offset and KV length. Built on the host from the step's lengths, one H2D copy."""
+
+    __slots__ = ("tables", "n_items", "t_pad", "n_req", "off_blk", "off_req")
+
+    def __init__(self, cu_q: np.ndarray, seq_lens: np.ndarray, device) -> None:
+        cu_q = np.asarray(cu_q, dtype=np.int64)
+        kv = np.asarray(seq_lens, dtype=np.int64)
+        b = int(kv.size)
+        q_len = cu_q[1:b + 1] - cu_q[:b]
+        kv_pad = (kv + 127) // 128 * 128
+        kv_off = np.concatenate([[0], np.cumsum(kv_pad)[:-1]]) if b else np.zeros(0, dtype=np.int64)
+        self.t_pad = int(kv_pad.sum())
+        self.n_req = b
+        n_tiles = (q_len + 127) // 128
+        req = np.repeat(np.arange(b), n_tiles)
+        first = np.concatenate([[0], np.cumsum(n_tiles)[:-1]]) if b else np.zeros(0, dtype=np.int64)
+        qb = np.arange(int(n_tiles.sum())) - np.repeat(first, n_tiles)
+        items = np.zeros((req.size, 8), dtype=np.int32)
+        rows = np.minimum(128, q_len[req] - qb * 128)
+        pos0 = kv[req] - q_len[req] + qb * 128
+        items[:, 0] = cu_q[req] + qb * 128
+        items[:, 1] = rows
+        items[:, 2] = pos0
+        items[:, 3] = kv_off[req]
+        items[:, 4] = (pos0 + rows + 127) // 128
+        items[:, 5] = req
+        items = items[np.argsort(-items[:, 4], kind="stable")]
+        blk_req = np.repeat(np.arange(b), kv_pad // 128).astype(np.int32)
+        req_info = np.stack([kv_off, kv], axis=1).astype(np.int32).reshape(-1)
+        self.n_items = int(items.shape[0])
+        self.off_blk = items.size
+        self.off_req = self.off_blk + blk_req.size
+        host = np.concatenate([items.reshape(-1), blk_req, req_info])
+        self.tables = torch.from_numpy(host).to(device, non_blocking=False)
+
+
+_TC_SCRATCH: Dict[Tuple[torch.device, torch.dtype, int], Tuple[torch.Tensor, torch.Tensor, int]] = {}
+
+
+def _tc_scratch(device, dtype, hk: int, rows: int):
+    """Dense K / V^T scratch shared by all layers of a step (each layer's gather overwrites it in
+    stream order). Grows in steps of 8192 rows."""
+    key = (device, dtype, hk)
+    hit = _TC_SCRATCH.get(key)
+    if hit is None or hit[2] < rows:
+        cap = -(-rows // 8192) * 8192
+        _TC_SCRATCH[key] = hit = (torch.zeros(hk * cap * 128, dtype=dtype, device=device),
+                                   torch.zeros(hk * cap * 128, dtype=dtype, device=device), cap)
+    return hit
+
+
+def prefill_attention_tc_ok(q, k_cache, *, causal, window, mask, decode) -> bool:
+    """The tcgen05 prefill kernel covers causal prefill / extend steps with head_dim 128 and an
+    even number of query heads per KV head; everything else stays on the general kernel."""
+    t, hq, d = q.shape
+    hk = k_cache.shape[1]
+    return (not decode and causal and not window and mask is None and d == 128 and hq % hk == 0
+            and (hq // hk) % 2 == 0 and q.dtype in (torch.bfloat16, torch.float16) and q.stride(2) == 1
+            and q.stride(1) == 128 and q.stride(0) % 8 == 0)
+
+
+def prefill_attention_tc(q, k_cache, v_cache, block_table, plan: PrefillPlan, scale, *, k_scale=None, v_scale=None):
+    t, hq, d = q.shape
+    _, hk, ps, _ = k_cache.shape
+    kc, vt, cap = _tc_scratch(q.device, q.dtype, hk, plan.t_pad)
+    out = torch.empty((t, hq, d), dtype=q.dtype, device=q.device)
+    tb = plan.tables
+    base = tb.data_ptr()
+    fp8 = k_cache.dtype == torch.float8_e4m3fn
+    check(lib().msgl_attn_prefill_tc(
+        _p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), _p(kc), _p(vt), cap, plan.t_pad,
+        base, plan.n_items, base + 4 * plan.off_blk, base + 4 * plan.off_req, _p(block_table), block_table.stride(0),
+        _p(k_scale), _p(v_scale), t, hq, hk, ps, int(fp8), float(scale), _dt(q), _stream()), "attn_prefill_tc")
+    _count("prefill_attention", "attn_prefill_tc_kernel", 2)
     return out
 
 
@@ -369,7 +462,9 @@ def force_general_decode_attention(on: bool) -> None:
 
 
 def attn_status(reset=True) -> int:
-    return int(lib().msgl_attn_status(int(reset)))
+    a = int(lib().msgl_attn_status(int(reset)))
+    b = int(lib().msgl_attn_tc_status(int(reset)))
+    return a or b
 
 
 # ------------------------------------------------------------------------------------------ sampling

@@ -191,7 +191,7 @@ def test_gemm_w4a8_mxfp4(K, m, n, k):
 
 # ------------------------------------------------------------------------------------------ attention
 def _attn_case(K, fp8, b, q_lens, kv_lens, hq, hk, d, ps, causal=True, window=0, mask=False, dtype=torch.bfloat16,
-               splits=None):
+               splits=None, tc=None):
     R = _ref()
     torch.manual_seed(0)
     pages = sum(-(-n // ps) for n in kv_lens) + 3
@@ -217,7 +217,7 @@ def _attn_case(K, fp8, b, q_lens, kv_lens, hq, hk, d, ps, causal=True, window=0,
         m[:, 0] = 0.0
     scale = d ** -0.5
     out = K.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, scale, causal=causal, window=window, mask=m,
-                            k_scale=ks, v_scale=vs, max_q=max(q_lens), max_kv=max(kv_lens), splits=splits)
+                            k_scale=ks, v_scale=vs, max_q=max(q_lens), max_kv=max(kv_lens), splits=splits, tc=tc)
     assert K.attn_status() == 0
     want = R.paged_attention(q, pool[0, 0], pool[1, 0], bt, cu, sl, scale, causal, window, m, ks, vs)
     _close(out, want, 3e-2, 3e-2, f"attention fp8={fp8}")
@@ -399,3 +399,35 @@ def test_gemm_w4a8_mxfp4_k_not_multiple_of_128(K, m):
         y = K.gemm_w4a8_mxfp4(xq, xs, padded, atoms, bn=bn)
         assert K.gemm_status() == 0
         _close(y, want, 2e-2, 2e-2, f"mxfp4 K=1216 bn={bn}")
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_attention_prefill_tcgen05(K, fp8):
+    """The tensor-core prefill kernel (gather to a dense scratch + tcgen05 QK^T / PV) against the fp32
+    reference on ragged prefill / extend batches, against the general kernel, and bit for bit
+    against itself when a prompt is processed in two chunks."""
+    K.LEDGER.pop("prefill_attention", None)
+    _attn_case(K, fp8, 3, [5, 130, 64], [5, 130, 64], 8, 2, 128, 16, tc=True)
+    assert K.LEDGER.get("prefill_attention") == "attn_prefill_tc_kernel"
+    _attn_case(K, fp8, 3, [7, 33, 100], [200, 33, 1000], 16, 4, 128, 16, tc=True)
+    _attn_case(K, fp8, 4, [1365, 257, 128, 1], [1365, 300, 128, 513], 32, 8, 128, 16, tc=True)
+    _attn_case(K, fp8, 2, [300, 40], [300, 700], 8, 4, 128, 64, dtype=torch.float16, tc=True)
+
+    torch.manual_seed(1)
+    hq, hk, d, ps, n, cut = 8, 2, 128, 16, 700, 300
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    pages = -(-n // ps)
+    pool = (torch.randn(2, 1, pages + 1, hk, ps, d, device="cuda") * (8 if fp8 else 1)).to(dt)
+    bt = torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages)
+    q = torch.randn(n, hq, d, device="cuda").bfloat16()
+    ks = (0.5 + torch.rand(hk, device="cuda")) / 8 if fp8 else None
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    run = lambda qq, ql, kl, **kw: K.paged_attention(qq, pool[0, 0], pool[1, 0], bt, i32([0, ql]), i32([kl]),
+                                                     d ** -0.5, k_scale=ks, v_scale=ks, max_q=ql, max_kv=kl, **kw)
+    whole = run(q, n, n, tc=True)
+    first = run(q[:cut].contiguous(), cut, cut, tc=True)
+    second = run(q[cut:].contiguous(), n - cut, n, tc=True)
+    assert torch.equal(whole[:cut], first) and torch.equal(whole[cut:], second)
+    general = run(q, n, n, tc=False)
+    _close(whole, general, 3e-2, 3e-2, "tcgen05 vs general prefill kernel")
+    assert K.attn_status() == 0

@@ -12,13 +12,16 @@
 //      attention does ~hundreds of FLOP per byte, so it is noise next to the main kernel, and it
 //      leaves the main kernel with plain 2-D tensor maps and K-major operands only.
 //   2. attn_prefill_tc_kernel: one CTA per (128 query positions of one request, two query heads
-//      of one KV head). S = Q K^T and O_j = P_j V_j are tcgen05.mma (kind::f16, M = N = 128) with
-//      S and the per-block O_j in tensor memory (2 x 128 + 2 x 128 columns); warp 0 is the TMA
-//      producer (Q once, then a 3-slot ring of K_j / V_j tiles), warp 1 issues the MMAs, and two
-//      groups of four warps own one head each: they read S with tcgen05.ld, keep the online-
-//      softmax state and the running output row in registers, and hand P_j back through
-//      shared memory in the swizzled K-major layout the MMA reads. The two heads alternate on
-//      the tensor pipe, so one group's softmax overlaps the other's MMAs.
+//      of one KV head). S = Q K^T and O += P_j V_j are tcgen05.mma (kind::f16, M = N = 128) with
+//      S and the output accumulator in tensor memory (2 x 128 + 2 x 128 columns); warp 0 is the
+//      TMA producer (Q once, then a 3-slot ring of K_j / V_j tiles), warp 1 issues the MMAs, and
+//      two groups of four warps (warps 4-7, 8-11) own one head each: they pull a block of S into
+//      registers with tcgen05.ld (which frees S for the next QK^T at once), keep the online-
+//      softmax state, rescale O in tensor memory when the running maximum has to move
+//      (tcgen05.ld / st, rare), and hand P_j to the MMA through shared memory in the swizzled
+//      K-major layout it reads. The two heads alternate on the tensor pipe, so one group's
+//      softmax overlaps the other's MMAs. setmaxnreg moves the idle warps' registers to the
+//      softmax groups.
 //
 // A row's result does not depend on which other rows share its tile or on how a prompt was
 // chunked: KV blocks are absolute (0, 128, ...), visited in ascending order, and a block that
@@ -189,7 +192,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
   auto s_free = [&](int t) { return bar(8 + 5 * t); };
   auto p_full = [&](int t) { return bar(9 + 5 * t); };
   auto o_full = [&](int t) { return bar(10 + 5 * t); };
-  auto o_free = [&](int t) { return bar(11 + 5 * t); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + TcSmem::off_bar + 8 * TcSmem::n_bars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TcSmem::off_bar + 8 * TcSmem::n_bars + 8);
 
@@ -201,7 +203,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
       mbar_init(s_free(t), 128);
       mbar_init(p_full(t), 128);
       mbar_init(o_full(t), 1);
-      mbar_init(o_free(t), 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -258,11 +259,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
           mma_f16(tmem_base + t * 128, smem_desc_sw128(q_s + (t * 2 + (kk >> 2)) * kPanel + (kk & 3) * 32),
                   smem_desc_sw128(k_tile + (kk >> 2) * kPanel + (kk & 3) * 32), idesc, kk > 0 ? 1u : 0u);
       };
-      auto issue_pv = [&](int t, uint32_t v_tile) {
+      auto issue_pv = [&](int t, uint32_t v_tile, bool first) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           mma_f16(tmem_base + 256 + t * 128, smem_desc_sw128(p_s + (t * 2 + (kk >> 2)) * kPanel + (kk & 3) * 32),
-                  smem_desc_sw128(v_tile + (kk >> 2) * kPanel + (kk & 3) * 32), idesc, kk > 0 ? 1u : 0u);
+                  smem_desc_sw128(v_tile + (kk >> 2) * kPanel + (kk & 3) * 32), idesc, (kk > 0 || !first) ? 1u : 0u);
       };
       bool ok = mbar_wait(q_full(), 0, abort_flag, args.status, 202) &&
                 mbar_wait(kv_full(0), 0, abort_flag, args.status, 203);
@@ -287,12 +288,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
             tc_commit(s_full(t));
           }
           if (!mbar_wait(p_full(t), (uint32_t)(j & 1), abort_flag, args.status, 207)) { ok = false; break; }
-          if (j > 0 && !mbar_wait(o_free(t), (uint32_t)((j - 1) & 1), abort_flag, args.status, 208)) {
-            ok = false;
-            break;
-          }
           tc_fence_after();
-          issue_pv(t, kv_s + (iv % 3) * 2 * kPanel);
+          issue_pv(t, kv_s + (iv % 3) * 2 * kPanel, j == 0);
           tc_commit(o_full(t));
         }
         if (!ok) break;
@@ -315,54 +312,62 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
     const uint32_t swz = (uint32_t)(row & 7);
     const float sl2 = args.scale * kLog2eTc * (args.k_scale != nullptr ? args.k_scale[hk] : 1.f);
 
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    uint32_t r[32];
+    // The output row accumulates in tensor memory across KV blocks. The running maximum is only
+    // raised when a block exceeds it by more than 2^8 (probabilities then stay below 256, exact
+    // enough in 16 bits and harmless in the fp32 row sum), so rescaling the accumulator - read,
+    // multiply, write back - is rare after the first blocks. The decision depends on the row's
+    // own history over absolute KV blocks only.
+    float m = -INFINITY, l = 0.f;
+    uint32_t s[4][32];
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
       const int kv0 = j * kTile;
       const bool masked = kv0 + kTile - 1 > it.q_pos0;   // the block reaches past some row's position
       if (!mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag, args.status, 209)) { ok = false; break; }
       tc_fence_after();
-      // pass 1: row maximum
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, s[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_free(t));                             // S is in registers: the next QK^T may start
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (masked && kv0 + c * 32 + i > q_pos) s = -INFINITY;
-          mx = fmaxf(mx, s);
+          if (masked && kv0 + c * 32 + i > q_pos) s[c][i] = 0xFF800000u;   // -inf
+          mx = fmaxf(mx, __uint_as_float(s[c][i]));
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = ex2f((m - m_use) * sl2);   // m = -inf on the first block: alpha = 0
-      // fold the previous block's P V into the running row; this also frees the P buffer
+      const bool grow = (mx - m) * sl2 > 8.f;             // false when both are -inf (NaN compares false)
+      float alpha = 1.f;
+      if (grow) {
+        alpha = ex2f((m - mx) * sl2);                     // m = -inf on the first block: 0
+        m = mx;
+        l *= alpha;
+      }
       if (j > 0) {
+        // P V of the previous block is complete: the P buffer is free and O may be rescaled
         if (!mbar_wait(o_full(t), (uint32_t)((j - 1) & 1), abort_flag, args.status, 210)) { ok = false; break; }
         tc_fence_after();
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+          uint32_t r[32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_32x32b_x32(o_addr + c * 32, r);
-          tmem_ld_wait();
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32b_x32(o_addr + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + c * 32, r);
+          }
+          tmem_st_wait();
         }
-        tc_fence_before();
-        mbar_arrive(o_free(t));
       }
-      // pass 2: probabilities -> shared memory (K-major, 128-byte swizzle), row sum
-      const float mb = m_use * sl2;
+      // probabilities -> shared memory (K-major, 128-byte swizzle), row sum
+      const float mb = (m == -INFINITY ? 0.f : m) * sl2;
       float l_blk = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         const uint32_t panel = p_row + (uint32_t)(c >> 1) * kPanel;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -370,12 +375,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = g * 8 + e * 2;
-            float p0 = ex2f(fmaf(__uint_as_float(r[i]), sl2, -mb));
-            float p1 = ex2f(fmaf(__uint_as_float(r[i + 1]), sl2, -mb));
-            if (masked) {
-              if (kv0 + c * 32 + i > q_pos) p0 = 0.f;
-              if (kv0 + c * 32 + i + 1 > q_pos) p1 = 0.f;
-            }
+            const float p0 = ex2f(fmaf(__uint_as_float(s[c][i]), sl2, -mb));
+            const float p1 = ex2f(fmaf(__uint_as_float(s[c][i + 1]), sl2, -mb));
             l_blk += p0 + p1;
             pk[e] = pack2_tc<T>(p0, p1);
           }
@@ -385,33 +386,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_c
                        : "memory");
         }
       }
+      l += l_blk;
       tc_fence_before();
-      mbar_arrive(s_free(t));
       fence_proxy_async();
       mbar_arrive(p_full(t));
-      l = fmaf(l, alpha, l_blk);
-      m = m_new;
-      alpha_prev = alpha;
     }
     if (ok && nb > 0 && mbar_wait(o_full(t), (uint32_t)((nb - 1) & 1), abort_flag, args.status, 211)) {
       tc_fence_after();
+      const float inv = (l > 0.f ? 1.f / l : 0.f) * (args.v_scale != nullptr ? args.v_scale[hk] : 1.f);
+      T* dst = reinterpret_cast<T*>(args.out) + ((long long)(it.q_row0 + row) * args.Hq + head) * kD;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(o_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(r[i]));
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(o_addr + c * 32, s[c]);
+      tmem_ld_wait();
       if (row < it.q_rows) {
-        const float inv = (l > 0.f ? 1.f / l : 0.f) * (args.v_scale != nullptr ? args.v_scale[hk] : 1.f);
-        T* dst = reinterpret_cast<T*>(args.out) + ((long long)(it.q_row0 + row) * args.Hq + head) * kD;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
+          const uint32_t* o = &s[c >> 2][(c & 3) * 8];
           uint4 v;
-          v.x = pack2_tc<T>(o[8 * c] * inv, o[8 * c + 1] * inv);
-          v.y = pack2_tc<T>(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
-          v.z = pack2_tc<T>(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
-          v.w = pack2_tc<T>(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
+          v.x = pack2_tc<T>(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+          v.y = pack2_tc<T>(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+          v.z = pack2_tc<T>(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+          v.w = pack2_tc<T>(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
           *reinterpret_cast<uint4*>(dst + 8 * c) = v;
         }
       }

@@ -67,6 +67,7 @@ def main(argv=None) -> None:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--stages", type=int, default=0, help="attn_decode with fp8 KV: stages of the TMA ring (2-4)")
     ap.add_argument("--general", action="store_true", help="attn_prefill: the warp-level MMA kernel instead of the tcgen05 one")
     ap.add_argument("--kv", default="fp8", choices=["fp8", "bf16"])
     ap.add_argument("--experts", type=int, default=128)
@@ -130,6 +131,8 @@ def main(argv=None) -> None:
             sl = lens.to("cuda", torch.int32)
         q = torch.randn(b * q_len, hq, d, device="cuda").bfloat16()
         ks = torch.ones(hk, device="cuda") / 8 if a.kv == "fp8" else None
+        if a.stages:
+            K.decode_attention_stages(a.stages)
         plan = None
         if q_len > 1 and not a.general:
             plan = K.PrefillPlan(cu.cpu().numpy(), sl.cpu().numpy(), q.device)  # once per step, as the engine does

@@ -849,13 +849,18 @@ int launch_attn(const CUtensorMap& map, const AttnArgs& a, int q_tiles, cudaStre
 }
 
 bool g_force_general_decode = false;
+int g_decode_stages = 2;   // shared-memory stages of the fp8 decode kernel (2, 3 or 4)
 
 template <typename T>
 int dispatch_attn(const CUtensorMap& map, const AttnArgs& a, bool kv8, int d, int max_q, cudaStream_t stream) {
   const int G = a.Hq / a.Hk;
   if (max_q == 1 && G <= 8 && a.mask == nullptr && !g_force_general_decode) {
     if (d == 128) {
-      if (kv8) return launch_decode<T, true, 128, 2>(map, a, stream);
+      if (kv8) {
+        if (g_decode_stages == 3) return launch_decode<T, true, 128, 3>(map, a, stream);
+        if (g_decode_stages == 4) return launch_decode<T, true, 128, 4>(map, a, stream);
+        return launch_decode<T, true, 128, 2>(map, a, stream);
+      }
       return launch_decode<T, false, 128, 2>(map, a, stream);
     }
     if (d == 64 && !kv8) return launch_decode<T, false, 64, 3>(map, a, stream);
@@ -962,6 +967,8 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
 
 // Test hook: route decode batches through the general (prefill/verify) kernel.
 MSGL_API void msgl_attn_force_general_decode(int on) { g_force_general_decode = on != 0; }
+// Tuning hook: stages of the fp8 decode kernel's TMA ring (fewer, deeper CTAs per SM as it grows).
+MSGL_API void msgl_attn_decode_stages(int stages) { g_decode_stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages); }
 
 MSGL_API int msgl_attn_status(int reset) {
   int v = 0;

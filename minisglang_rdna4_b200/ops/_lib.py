@@ -43,6 +43,7 @@ _SIGNATURES = {
                                    c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_p]),
     "msgl_attn_tc_status": (c_i, [c_i]),
     "msgl_attn_force_general_decode": (None, [c_i]),
+    "msgl_attn_decode_stages": (None, [c_i]),
     "msgl_argmax": (c_i, [c_p, c_p, c_i, c_i, c_ll, c_p]),
     "msgl_sample": (c_i, [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_p]),
 }

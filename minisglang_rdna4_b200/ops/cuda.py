@@ -454,6 +454,11 @@ def gemm_pair_mode(mode: int) -> int:
     return int(lib().msgl_gemm_pair_mode(int(mode)))
 
 
+def decode_attention_stages(stages: int) -> None:
+    """Depth of the fp8 decode kernel's TMA ring (2-4 stages of 64 tokens)."""
+    lib().msgl_attn_decode_stages(int(stages))
+
+
 def force_general_decode_attention(on: bool) -> None:
     """Route single-query batches through the general attention kernel. Speculative decoding
     sets this: verification rows run on the general kernel, and greedy output is only

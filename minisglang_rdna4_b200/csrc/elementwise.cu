@@ -54,15 +54,19 @@ MSGL_API int msgl_embedding(const void* ids, const void* w, void* out, int rows,
 // ------------------------------------------------------------------------------------------
 constexpr int kRowThreads = 128;
 
-template <typename T, bool ADD, bool QUANT, int VPT>
+//   PLANES: x is fp32 [planes][rows][hidden], the K ranges of a split-K GEMM; they are summed in
+//           ascending order and rounded to T, which is what an unsplit GEMM would have handed over
+template <typename T, bool ADD, bool QUANT, int VPT, bool PLANES = false>
 __global__ void __launch_bounds__(kRowThreads) rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual,
                                                                const T* __restrict__ w, T* __restrict__ out,
                                                                uint8_t* __restrict__ out_q,
                                                                float* __restrict__ out_scale, int hidden, float eps,
-                                                               float w_offset) {
+                                                               float w_offset, int planes = 0,
+                                                               size_t plane_stride = 0) {
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const T* xr = x + (size_t)row * hidden;
+  const float* xp = reinterpret_cast<const float*>(x) + (size_t)row * hidden;
   T* rr = ADD ? residual + (size_t)row * hidden : nullptr;
   float v[VPT][8];
   float ss = 0.f;
@@ -70,7 +74,20 @@ __global__ void __launch_bounds__(kRowThreads) rms_norm_kernel(const T* __restri
   for (int j = 0; j < VPT; ++j) {
     const int i = (j * kRowThreads + threadIdx.x) * 8;
     if (i < hidden) {
-      load8(xr + i, v[j]);
+      if (PLANES) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j][k] = 0.f;
+        for (int p = 0; p < planes; ++p) {
+          const float4 lo = __ldg(reinterpret_cast<const float4*>(xp + p * plane_stride + i));
+          const float4 hi = __ldg(reinterpret_cast<const float4*>(xp + p * plane_stride + i + 4));
+          v[j][0] += lo.x; v[j][1] += lo.y; v[j][2] += lo.z; v[j][3] += lo.w;
+          v[j][4] += hi.x; v[j][5] += hi.y; v[j][6] += hi.z; v[j][7] += hi.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j][k] = to_float(from_float<T>(v[j][k]));
+      } else {
+        load8(xr + i, v[j]);
+      }
       if (ADD) {
         float r[8];
         load8(rr + i, r);
@@ -144,6 +161,49 @@ static int launch_rms(const void* x, void* residual, const void* w, void* out, v
   else return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("rms_norm");
   return MSGL_OK;
+}
+
+template <typename T, int VPT>
+static void launch_rms_planes_vpt(const void* x, int planes, void* residual, const void* w, void* out, void* out_q,
+                                  void* out_scale, int rows, int hidden, float eps, float off, cudaStream_t s) {
+  const size_t stride = (size_t)rows * hidden;
+  if (out_q != nullptr)
+    rms_norm_kernel<T, true, true, VPT, true><<<rows, kRowThreads, 0, s>>>(
+        (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
+  else
+    rms_norm_kernel<T, true, false, VPT, true><<<rows, kRowThreads, 0, s>>>(
+        (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
+}
+
+template <typename T>
+static int launch_rms_planes(const void* x, int planes, void* residual, const void* w, void* out, void* out_q,
+                             void* out_scale, int rows, int hidden, float eps, int plus_one, cudaStream_t s) {
+  const float off = plus_one ? 1.f : 0.f;
+  const int vpt = (hidden / 8 + kRowThreads - 1) / kRowThreads;
+  if (vpt <= 1) launch_rms_planes_vpt<T, 1>(x, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 2) launch_rms_planes_vpt<T, 2>(x, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 3) launch_rms_planes_vpt<T, 3>(x, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 4) launch_rms_planes_vpt<T, 4>(x, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else if (vpt <= 8) launch_rms_planes_vpt<T, 8>(x, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, off, s);
+  else return MSGL_BAD_ARG;
+  MSGL_CHECK_LAUNCH("rms_norm_planes");
+  return MSGL_OK;
+}
+
+// residual += sum of the fp32 planes [planes][rows][hidden] of a split-K GEMM (ascending order,
+// rounded to the 16-bit type first), then the norm of the sum; 16-bit or quantised output.
+MSGL_API int msgl_rms_norm_planes(const void* x_planes, int planes, void* residual, const void* w, void* out,
+                                  void* out_q, void* out_scale, int rows, int hidden, float eps, int plus_one,
+                                  int dtype, cudaStream_t stream) {
+  if (hidden % 8 || hidden > 8 * 8 * kRowThreads || planes < 1 || residual == nullptr) return MSGL_BAD_ARG;
+  if (rows == 0) return MSGL_OK;
+  if (dtype == MSGL_BF16)
+    return launch_rms_planes<__nv_bfloat16>(x_planes, planes, residual, w, out, out_q, out_scale, rows, hidden, eps,
+                                            plus_one, stream);
+  if (dtype == MSGL_F16)
+    return launch_rms_planes<__half>(x_planes, planes, residual, w, out, out_q, out_scale, rows, hidden, eps, plus_one,
+                                     stream);
+  return MSGL_BAD_ARG;
 }
 
 // residual == nullptr: plain norm. out_q != nullptr: quantised output (out may be nullptr).

@@ -322,7 +322,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           float sc = 1.f, bi = 0.f;
           if (col < args.N) {
             if (args.b_scale != nullptr) sc = __ldg(args.b_scale + col);
-            if (args.bias != nullptr)
+            if (args.bias != nullptr && (split == 0 || args.splitk_count != nullptr))
               bi = args.bias_dtype == MSGL_BF16
                        ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
                        : (args.bias_dtype == MSGL_F16 ? __half2float(reinterpret_cast<const __half*>(args.bias)[col])
@@ -336,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 104)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      if (splits > 1) {
+      if (splits > 1 && args.splitk_count != nullptr) {
         // raw partial sums of this K range -> workspace; the last range to arrive finishes the tile
         const int ws_ld = args.n_tiles * BN;
         const size_t ws_plane = (size_t)args.m_tiles * BM * ws_ld;
@@ -452,7 +452,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             r[e] = __float_as_uint(x);
           }
           if (row_ok) {
-            float* crow = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + colbase + c * 32;
+            // planes mode (splits > 1 without counters): K range `split` writes plane `split` of an
+            // fp32 [splits][M][ldc] output; the consumer sums the planes in ascending order
+            float* crow = reinterpret_cast<float*>(args.c) + (size_t)split * args.M * args.ldc +
+                          (size_t)row * args.ldc + colbase + c * 32;
 #pragma unroll
             for (int g = 0; g < 8; ++g)
               if (colbase + c * 32 + g * 4 < args.N)
@@ -1124,11 +1127,15 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   args.kb_per_split = args.k_blocks;
   args.splitk_ws = nullptr;
   args.splitk_count = nullptr;
-  if (splits > 1 && !use_pair && tile_expert == nullptr && splitk_ws != nullptr && splitk_count != nullptr) {
+  const bool planes = splits > 1 && splitk_ws == nullptr && splitk_count == nullptr && out_dtype == MSGL_F32;
+  if (splits > 1 && !use_pair && tile_expert == nullptr && ((splitk_ws != nullptr && splitk_count != nullptr) || planes)) {
     args.splits = splits;
     args.kb_per_split = (args.k_blocks + splits - 1) / splits;
     args.splitk_ws = (float*)splitk_ws;
     args.splitk_count = (uint32_t*)splitk_count;
+  } else if (planes) {
+    msgl_set_error_text("gemm_splitk_planes: needs the single-CTA kernel (M <= 256) and ungrouped operands");
+    return MSGL_BAD_ARG;
   }
   args.rs_world = 0;
   args.a_ready = nullptr;
@@ -1231,6 +1238,19 @@ MSGL_API int msgl_gemm_splitk(int kind, const void* a, long long lda, const void
   if (M > 256 || splits < 2 || ws == nullptr || counters == nullptr) return MSGL_BAD_ARG;
   return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, out_dtype, 128, 0,
                    nullptr, 0, stream, nullptr, splits, ws, counters);
+}
+
+// Split-K without a reduction inside the GEMM: K range s of every tile writes its scaled partial
+// sums to plane s of the fp32 output [splits][M][N] (ldc = N); the bias goes to plane 0. The
+// consumer (msgl_rms_norm_planes) adds the planes in ascending order, so the result does not depend
+// on scheduling. For M <= 256, where a projection with few N tiles would otherwise leave most
+// SMs idle while a few walk a long K loop.
+MSGL_API int msgl_gemm_splitk_planes(int kind, const void* a, long long lda, const void* b, void* planes, int M, int N,
+                                     int K, const void* a_scale, const void* b_scale, const void* bias,
+                                     int bias_dtype, const void* sf_atoms, int splits, cudaStream_t stream) {
+  if (M > 256 || splits < 2 || planes == nullptr) return MSGL_BAD_ARG;
+  return gemm_impl(kind, a, lda, b, planes, N, M, N, K, a_scale, b_scale, bias, bias_dtype, sf_atoms, MSGL_F32, 128, 0,
+                   nullptr, 0, stream, nullptr, splits, nullptr, nullptr);
 }
 
 // msgl_gemm with the tensor-parallel fusions of the CTA-pair kernel: the epilogue can push its

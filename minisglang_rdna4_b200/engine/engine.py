@@ -191,6 +191,7 @@ class Engine:
             from ..ops import cuda as K
 
             K.SPLIT_K = False
+            K.SPLIT_K_DECODE = False
         if config.enable_ep and config.dp_size > 1:
             from ..parallel.ep import EPContext, FusedEPContext
 

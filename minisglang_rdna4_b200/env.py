@@ -127,6 +127,7 @@ ENV.int("PROFILE_SKIP", 8, "forward steps to skip before the profiler window ope
 ENV.int("PROFILE_STEPS", 8, "forward steps inside the profiler window")
 ENV.flag("HOSTPROF", False, "print a host-side stage breakdown of the scheduler loop")
 ENV.flag("GRAPH_TIMING", False, "time every graph replay with CUDA events")
+ENV.flag("DISABLE_SPLIT_K_DECODE", False, "decode-phase o_proj / down_proj keep K in one range instead of handing split-K planes to the next add + norm")
 ENV.flag("DISABLE_TC_PREFILL", False, "prefill attention on the general (warp-level MMA) kernel instead of the tcgen05 one")
 # --- distributed --------------------------------------------------------------------------
 ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")

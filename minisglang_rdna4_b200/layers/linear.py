@@ -132,5 +132,15 @@ class RowParallelLinear(_LinearBase):
                 if K.take_pending_gemm_tp() is not None:
                     raise RuntimeError("linear method did not consume the pending reduce-scatter arguments")
                 return PushedPartial(plan, (rows, self._n), self._compute_dtype)
+        if not reduce and comm.size == 1 and comm.split_k_ok and len(x.shape) == 2 and x.shape[0] <= 256:
+            # decode step on one GPU: few N tiles and a long K would leave most SMs idle, so the
+            # GEMM may return its K ranges as fp32 planes that the following add + norm sums
+            from ..ops import cuda as K
+
+            K.set_next_gemm_planes(True)
+            try:
+                return self._method.apply(self, x, bias)
+            finally:
+                K.set_next_gemm_planes(False)
         y = self._method.apply(self, x, bias)
         return comm.all_reduce(y) if reduce else y

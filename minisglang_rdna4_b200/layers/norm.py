@@ -35,6 +35,14 @@ class RMSNorm(BaseOP):
         only. With ``to_gemm`` the caller promises that the normed rows go straight into a
         linear layer, which waits for them block by block; otherwise the wait happens here."""
         comm = get_comm()
+        if hasattr(x, "planes"):  # ops.cuda.SplitPartial: unreduced K ranges of a decode-step GEMM
+            if residual is None:
+                x = x.materialise()
+            else:
+                from ..ops import cuda as K
+
+                out = K.rms_norm_planes(x, residual, self.weight, self._eps, self._plus_one, quant)
+                return (ActQ(*out) if quant else out), residual
         if not isinstance(x, torch.Tensor):  # PushedPartial
             if residual is None:
                 raise ValueError("a pushed partial sum needs a residual stream")

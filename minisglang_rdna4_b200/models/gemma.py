@@ -118,6 +118,7 @@ class GemmaForCausalLM(BaseOP):
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
         get_comm().row_shard_ok = False
+        get_comm().split_k_ok = False
         ctx = get_global_ctx()
         capture = ctx.batch.capture_layers
         x = self.model.embed_tokens.forward(input_ids)

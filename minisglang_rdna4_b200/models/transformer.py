@@ -172,7 +172,13 @@ class CausalLM(BaseOP):
         partial = False
         # the row-sharded prefill path needs every row-parallel output of the pass to end in a
         # fused add + norm: dense layers only, no hidden-state capture
-        get_comm().row_shard_ok = capture is None and not any(l._is_moe for l in self.model.layers)
+        comm = get_comm()
+        comm.row_shard_ok = capture is None and not any(l._is_moe for l in self.model.layers)
+        comm.split_k_ok = False
+        if comm.row_shard_ok and comm.size == 1 and input_ids.is_cuda and ctx.batch.is_decode and not ctx.batch.spec_verify:
+            from ..ops import cuda as K
+
+            comm.split_k_ok = K.SPLIT_K_DECODE
         seen = {}
         for i, layer in enumerate(self.model.layers):
             if capture is not None and i in capture:

@@ -31,6 +31,8 @@ _SIGNATURES = {
     "msgl_gemm_splitk_plan": (c_i, [c_i, c_i, c_i]),
     "msgl_gemm_splitk": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_i, c_p, c_p,
                                c_p]),
+    "msgl_gemm_splitk_planes": (c_i, [c_i, c_p, c_ll, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_i, c_p]),
+    "msgl_rms_norm_planes": (c_i, [c_p, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_i, c_p]),
     "msgl_gemm_status": (c_i, [c_i]),
     "msgl_gemm_pair_mode": (c_i, [c_i]),
     "msgl_attn_make_kv_map": (c_i, [c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_i]),

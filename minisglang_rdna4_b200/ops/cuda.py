@@ -76,6 +76,24 @@ def _rms(x, residual, w, eps, plus_one, quant):
     return (out_q, out_s) if quant else out
 
 
+def rms_norm_planes(part: "SplitPartial", residual, w, eps, plus_one=False, quant=False):
+    """residual += (sum of the split-K planes, ascending); returns the norm of the new residual as a
+    16-bit tensor or an (e4m3, scale) pair."""
+    planes = part.planes
+    splits, rows, hidden = planes.shape
+    assert planes.is_contiguous() and residual.is_contiguous() and residual.shape == (rows, hidden)
+    out = out_q = out_s = None
+    if quant:
+        out_q = torch.empty((rows, hidden), dtype=torch.float8_e4m3fn, device=planes.device)
+        out_s = torch.empty((rows,), dtype=torch.float32, device=planes.device)
+    else:
+        out = torch.empty_like(residual)
+    check(lib().msgl_rms_norm_planes(_p(planes), splits, _p(residual), _p(w), _p(out), _p(out_q), _p(out_s), rows,
+                                     hidden, eps, int(plus_one), _dt(residual), _stream()), "rms_norm_planes")
+    _count("rms_norm_add_planes" + ("_quant" if quant else ""), "rms_norm_kernel")
+    return (out_q, out_s) if quant else out
+
+
 def rms_norm(x, w, eps, plus_one=False):
     shape = x.shape
     return _rms(x.reshape(-1, shape[-1]), None, w, eps, plus_one, False).view(shape)
@@ -351,6 +369,40 @@ def _splitk_counters(device, n: int) -> torch.Tensor:
     return t
 
 
+class SplitPartial:
+    """Output of a split-K GEMM whose K ranges were not reduced: fp32 planes [splits, rows, N] that
+    the next fused add + norm sums in ascending order (``rms_norm_planes``)."""
+
+    __slots__ = ("planes", "dtype")
+
+    def __init__(self, planes: torch.Tensor, dtype: torch.dtype) -> None:
+        self.planes = planes
+        self.dtype = dtype
+
+    @property
+    def shape(self):
+        return self.planes.shape[1:]
+
+    def materialise(self) -> torch.Tensor:
+        out = self.planes[0].clone()
+        for p in self.planes[1:]:
+            out += p
+        return out.to(self.dtype)
+
+
+# Decode-phase row-parallel projections may hand their K ranges to the following add + norm
+# unreduced. Engines that need verify rows and decode rows on one GEMM code path switch it off.
+SPLIT_K_DECODE = not ENV.DISABLE_SPLIT_K_DECODE.value
+_PENDING_PLANES = False
+
+
+def set_next_gemm_planes(on: bool = True) -> None:
+    """Ask the next GEMM call of this thread (M <= 256) to return a ``SplitPartial`` when the
+    split-K plan of its (N, K) has more than one range. Consumed by exactly one call."""
+    global _PENDING_PLANES
+    _PENDING_PLANES = on
+
+
 def set_next_gemm_tp(args) -> None:
     """Tensor-parallel fusion arguments (``parallel.symm.GemmTpArgs``) for the next GEMM call of
     this thread: push the output rows to their owner ranks and / or wait for A rows that peers
@@ -378,6 +430,18 @@ def _gemm(kind, a, b, n, k, out_dtype, a_scale=None, b_scale=None, bias=None, sf
         _count(("gemm_f16", "gemm_bf16", "gemm_w8a8", "gemm_w4a8_mxfp4")[kind] + ("_rs" if pushes else "_ag"),
                "gemm_pair_kernel")
         return out
+    global _PENDING_PLANES
+    want_planes, _PENDING_PLANES = _PENDING_PLANES, False
+    if want_planes and 0 < m <= 256 and bn == 0:
+        splits = _splitk_plan(kind, n, k)
+        if splits > 1:
+            planes = torch.empty((splits, m, n), dtype=torch.float32, device=a.device)
+            check(lib().msgl_gemm_splitk_planes(kind, _p(a), a.stride(0), _p(b), _p(planes), m, n, k, _p(a_scale),
+                                                _p(b_scale), _p(bias), _DT[bias.dtype] if bias is not None else 0,
+                                                _p(sf_atoms), splits, _stream()), "gemm_splitk_planes")
+            _count(("gemm_f16", "gemm_bf16", "gemm_w8a8", "gemm_w4a8_mxfp4")[kind] + "_splitk_planes",
+                   "gemm_tcgen05_kernel")
+            return SplitPartial(planes, out_dtype)
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if m == 0:
         return out
@@ -412,6 +476,8 @@ def gemm(x, w, bias=None, out_dtype=None, bn=0, max_ctas=0):
     if n % 8:
         raise ValueError("gemm: N must be a multiple of 8")
     out = _gemm(kind, x2, w, n, k, out_dtype or x.dtype, bias=bias, bn=bn, max_ctas=max_ctas)
+    if isinstance(out, SplitPartial):
+        return out
     return out.view(*shape[:-1], n) if out is not None else None
 
 

@@ -54,6 +54,9 @@ class Communicator:
         # set per forward pass by the model: True only for passes in which every row-parallel
         # output feeds a fused add + norm (dense layers, no hidden-state capture)
         self.row_shard_ok = False
+        # set per forward pass by the model: every row-parallel output of this pass ends in a fused
+        # add + norm and the pass is a plain decode step on one GPU (see layers/linear.py)
+        self.split_k_ok = False
         self._rs_impl = None
 
     @property

@@ -42,6 +42,7 @@ def test_embedding(K, dtype):
 @pytest.mark.parametrize("rows", [1, 7, 300])
 def test_rms_norm_family(K, hidden, rows):
     R = _ref()
+    torch.manual_seed(hidden + rows)
     x = torch.randn(rows, hidden, device="cuda").bfloat16()
     res = torch.randn(rows, hidden, device="cuda").bfloat16()
     w = (1 + 0.1 * torch.randn(hidden, device="cuda")).bfloat16()
@@ -58,7 +59,7 @@ def test_rms_norm_family(K, hidden, rows):
     _close(s1, s2, 1e-2, 0, "scale")
     # a bf16 rounding flip before the quantiser moves a value by one e4m3 step (12.5 % at most)
     _close(q1.float() * s1[:, None], q2.float() * s2[:, None], 0.14, 0.02, "rms_norm_add_quant")
-    assert float((q1.float() != q2.float()).float().mean()) < 0.01
+    assert float((q1.float() != q2.float()).float().sum()) <= max(4.0, 0.01 * q1.numel())
 
 
 def test_act_and_quant(K):
@@ -431,3 +432,50 @@ def test_attention_prefill_tcgen05(K, fp8):
     general = run(q, n, n, tc=False)
     _close(whole, general, 3e-2, 3e-2, "tcgen05 vs general prefill kernel")
     assert K.attn_status() == 0
+
+
+@pytest.mark.parametrize("n,k", [(2560, 9728), (2560, 4096)])
+def test_gemm_split_k_planes_feed_the_fused_norm(K, n, k):
+    """Decode-step row-parallel projections: the GEMM leaves its K ranges as fp32 planes (bias in
+    plane 0) and the following residual-add + RMSNorm (+ e4m3 producer) sums them in ascending
+    order. Against the fp32 reference of GEMM -> add -> norm, repeatable, and the same rows at
+    every M."""
+    R = _ref()
+    from minisglang_rdna4_b200.ops._lib import lib
+    from minisglang_rdna4_b200.quant import mxfp4
+
+    assert lib().msgl_gemm_splitk_plan(3, n, k) > 1
+    torch.manual_seed(0)
+    m = 200
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda") * 0.02
+    packed, sf = mxfp4.quantize_mxfp4(w)
+    atoms = mxfp4.pack_sf_atoms(sf)
+    xq, xs = K.per_token_quant_fp8(x)
+    bias = torch.randn(n, device="cuda").bfloat16()
+    res0 = torch.randn(m, n, device="cuda").bfloat16()
+    nw = (1 + 0.1 * torch.randn(n, device="cuda")).bfloat16()
+
+    K.set_next_gemm_planes(True)
+    part = K.gemm_w4a8_mxfp4(xq, xs, packed, atoms, bias=bias)
+    assert isinstance(part, K.SplitPartial) and part.planes.shape[1:] == (m, n)
+    assert isinstance(K.gemm_w4a8_mxfp4(xq, xs, packed, atoms), torch.Tensor)      # the request is used up
+    want_y = R.gemm_w4a8_mxfp4(xq, xs, packed, sf).float() + bias.float()
+    _close(part.materialise(), want_y, 2e-2, 2e-2, "sum of the split-k planes")
+
+    res = res0.clone()
+    normed = K.rms_norm_planes(part, res, nw, 1e-6)
+    want_res = (want_y.bfloat16().float() + res0.float())
+    _close(res, want_res, 3e-2, 3e-2, "residual after planes add")
+    want_norm = R.rms_norm(want_res.bfloat16(), nw, 1e-6)
+    _close(normed, want_norm, 4e-2, 4e-2, "norm of planes + residual")
+    res_q = res0.clone()
+    q, s = K.rms_norm_planes(part, res_q, nw, 1e-6, quant=True)
+    assert torch.equal(res_q, res)
+    _close(q.float() * s[:, None], want_norm.float(), 8e-2, 8e-2, "quantised norm of planes + residual")
+
+    for mm in (1, 130):
+        K.set_next_gemm_planes(True)
+        sub = K.gemm_w4a8_mxfp4(xq[:mm].contiguous(), xs[:mm].contiguous(), packed, atoms, bias=bias)
+        assert torch.equal(sub.planes, part.planes[:, :mm])
+    assert K.gemm_status() == 0

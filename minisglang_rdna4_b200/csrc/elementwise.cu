@@ -224,7 +224,14 @@ MSGL_API int msgl_rms_norm(const void* x, void* residual, const void* w, void* o
 // ------------------------------------------------------------------------------------------
 enum ActKind : int { ACT_SILU = 0, ACT_GELU = 1, ACT_GELU_TANH = 2 };
 __device__ __forceinline__ float act_fn(float g, int kind) {
-  if (kind == ACT_SILU) return __fdividef(g, 1.f + __expf(-g));
+  if (kind == ACT_SILU) {
+    // x * sigmoid(x) = h + h * tanh(h) with h = x / 2: one special-function op instead of two
+    // (exp and reciprocal); tanh.approx is good to ~2^-11, below the 16-bit rounding of the result
+    const float h = 0.5f * g;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
+  }
   if (kind == ACT_GELU) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   return 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g)));

@@ -113,7 +113,11 @@ def resolve_model_config(cfg: EngineConfig) -> ModelConfig:
 
 class Engine:
     def __init__(self, config: EngineConfig) -> None:
+        from ..weights import BootTimeline, MemoryLedger
+
         self.config = config
+        self.boot = BootTimeline()
+        self.ledger = MemoryLedger()
         set_tp_info(config.tp_rank, config.tp_size)
         set_dp_info(config.dp_rank, config.dp_size)
         set_ep(config.enable_ep, over_tp=(config.dp_size == 1))
@@ -133,6 +137,9 @@ class Engine:
         self.dp_group: Optional[dist.ProcessGroup] = None
         self.dp_cpu_group: Optional[dist.ProcessGroup] = None
         self._init_communication()
+        self.boot.mark("process groups")
+        if dev_kind == "cuda":
+            self.ledger.capacity = int(torch.cuda.get_device_properties(self.device).total_memory)
 
         free_before = self._free_memory()
         self.model = create_model(self.model_config, self.dtype, self.device)
@@ -149,6 +156,8 @@ class Engine:
             torch.cuda.synchronize()
             torch.cuda.empty_cache()
         self.model_bytes = max(free_before - self._free_memory(), 0)
+        self.ledger.add("weights", self.model_bytes)
+        self.boot.mark("weights (load + post-load)")
 
         # ---- KV pool ----
         mc = self.model_config
@@ -172,6 +181,8 @@ class Engine:
                                                config.tp_size)
             self.kv_cache.set_scales(ks, vs)
             logger.info_rank0("fp8 KV scales: %s", source)
+        self.ledger.add("kv pool", self.kv_cache._buf.numel() * self.kv_cache._buf.element_size())
+        self.boot.mark("kv pool")
         # slot max_running_req is the dummy request used to pad graph batches
         self.num_slots = config.max_running_req + 1
         self.token_pool = torch.zeros((self.num_slots, self.max_seq_len), dtype=torch.int32, device=self.device)
@@ -227,7 +238,12 @@ class Engine:
                 and not ep_replicas and not host_tier):
             from .graph import GraphRunner
 
+            before = self._free_memory()
             self.graph_runner = GraphRunner(self)
+            self.ledger.add("cuda graphs", max(before - self._free_memory(), 0))
+            self.boot.mark("graph capture")
+        logger.info_rank0("%s", self.ledger.report())
+        logger.info_rank0("%s", self.boot.render())
         logger.info_rank0(
             "engine ready: %s, %d pages x %d tokens, max_seq_len %d, dtype %s, kv %s",
             mc.model_type, self.num_pages, self.page_size, self.max_seq_len, self.dtype,
@@ -284,17 +300,34 @@ class Engine:
         G GiB in total; the rest stay in pinned host memory (python/minisgl/server/args.py:199-249)."""
         from ..layers.moe import MoELayer
 
+        from ..weights import ExpertGeometry, TierBudgets, resolve_plan
+        from ..weights.host_capacity import check_pinned
+
         cfg, mc = self.config, self.model_config
         MoELayer.offload_slots = 0
+        self.offload_plan = None
         if cfg.expert_cache_gb <= 0 or not mc.is_moe:
             return
         itemsize = torch.empty((), dtype=self.dtype).element_size()
-        per_expert = 3 * mc.hidden_size * mc.moe_intermediate_size * itemsize
         layers = sum(1 for i in range(mc.num_layers) if mc.layer_is_moe(i))
-        slots = int(cfg.expert_cache_gb * (1 << 30) // max(per_expert * layers, 1))
-        MoELayer.offload_slots = max(slots, mc.num_experts_per_tok * 2)
-        logger.info_rank0("host expert tier: %d of %d experts resident per layer", MoELayer.offload_slots,
-                          mc.num_experts)
+        geo = ExpertGeometry(layers, mc.num_experts, mc.num_experts_per_tok,
+                             3 * mc.hidden_size * mc.moe_intermediate_size * itemsize)
+        plan = resolve_plan(geo, TierBudgets(device_bytes=int(cfg.expert_cache_gb * (1 << 30))))
+        if self.cpu_group is not None and cfg.tp_size > 1:
+            # every rank must have resolved the same placement before anything is pinned
+            from ..weights.plan import check_agreement
+
+            digests = [None] * cfg.tp_size
+            dist.all_gather_object(digests, plan.digest, group=self.cpu_group)
+            check_agreement(digests)
+        if plan.offloaded and self.device.type == "cuda":
+            check_pinned(plan.host_bytes)
+        self.offload_plan = plan
+        MoELayer.offload_slots = plan.layers[0].device_slots if plan.offloaded else 0
+        for note in plan.notes:
+            logger.info_rank0("offload plan: %s", note)
+        logger.info_rank0("host expert tier: %d of %d experts resident per layer (plan %s, %.2f GiB pinned)",
+                          plan.layers[0].device_slots, mc.num_experts, plan.digest, plan.host_bytes / (1 << 30))
 
     def _free_memory(self) -> int:
         if self.device.type == "cuda":

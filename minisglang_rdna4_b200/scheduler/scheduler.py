@@ -415,7 +415,7 @@ class Scheduler:
                 for msg in self.receive_msg(blocking):
                     self._process_one_msg(msg)
             if last is not None and any(self._needs_constraints(r) for r in last.sampled):
-                # a grammar mask depends on the token of the step in flight: no overlap this round
+                # a grammar mask depends on the token of the step in flight: no overlap for this iteration
                 self._process_last_data(last)
                 last = None
             with hp.stage("schedule"):

@@ -35,6 +35,14 @@ class HostExpertTier:
         self.slot_map = torch.full((self.num_experts,), -1, dtype=torch.int32, device=self.device)
         self.copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self.bytes_copied = 0
+        # optional (RouteTrace, layer index): every step's routed experts are counted there
+        self.trace = None
+        self.layer_index = 0
+
+    def prewarm(self, experts: List[int]) -> None:
+        """Make the hottest experts of an earlier run's route trace resident before the first step
+        (python/minisgl/weights/route_trace.py: hot sets seed the cache at boot)."""
+        self.ensure_resident(list(experts)[: self.slots])
 
     def ensure_resident(self, expert_ids: List[int]) -> None:
         need = sorted(set(int(e) for e in expert_ids if 0 <= int(e) < self.num_experts))
@@ -80,7 +88,10 @@ class HostExpertTier:
         """A step that routes to more experts than the slab holds (a wide prefill) runs in rounds:
         each round makes one slab-full of experts resident and adds their contribution (the
         reference stages such prefills through a separate slab, weights/prefill_stage.py:116)."""
-        need = sorted(set(int(e) for e in topk_ids.reshape(-1).tolist() if 0 <= int(e) < self.num_experts))
+        routed = topk_ids.reshape(-1).tolist()
+        if self.trace is not None:
+            self.trace.record(self.layer_index, routed)
+        need = sorted(set(int(e) for e in routed if 0 <= int(e) < self.num_experts))
         if len(need) <= self.slots:
             self.ensure_resident(need)
             return self._run(x, topk_w, topk_ids)

@@ -89,3 +89,90 @@ def test_cpu_expert_tier_matches_fp32_reference():
     assert float((got8 - want).abs().max()) < 0.05 * float(want.abs().max())
     assert tier.isa in ("scalar", "avx512-fp32", "avx512-vnni-int8")
     tier.close()
+
+
+def test_offload_plan_resolver_and_agreement():
+    import pytest
+
+    from minisglang_rdna4_b200.weights import ExpertGeometry, PlanError, TierBudgets, resolve_plan
+    from minisglang_rdna4_b200.weights.plan import check_agreement
+
+    geo = ExpertGeometry(num_moe_layers=4, num_experts=64, experts_per_token=8, bytes_per_expert=1 << 20)
+    fits = resolve_plan(geo, TierBudgets(device_bytes=4 * 64 << 20))
+    assert not fits.offloaded and fits.host_bytes == 0 and fits.device_bytes == 4 * 64 << 20
+    half = resolve_plan(geo, TierBudgets(device_bytes=4 * 32 << 20))
+    assert half.offloaded and [p.device_slots for p in half.layers] == [32] * 4
+    assert all(p.host_experts == 64 and p.disk_experts == 0 for p in half.layers)   # every expert has a host home
+    tiny = resolve_plan(geo, TierBudgets(device_bytes=1 << 20))
+    assert tiny.layers[0].device_slots == 16 and tiny.notes                       # raised to two steps' worth
+    with pytest.raises(PlanError):
+        resolve_plan(geo, TierBudgets(device_bytes=4 * 32 << 20, host_bytes=4 * 40 << 20))
+    disk = resolve_plan(geo, TierBudgets(device_bytes=4 * 32 << 20, host_bytes=4 * 40 << 20, disk=True))
+    assert disk.layers[0].host_experts == 40 and disk.layers[0].disk_experts == 24
+    assert half.digest == resolve_plan(geo, TierBudgets(device_bytes=4 * 32 << 20)).digest != disk.digest
+    check_agreement([half.digest, half.digest])
+    with pytest.raises(PlanError):
+        check_agreement([half.digest, disk.digest])
+
+
+def test_memory_ledger_host_capacity_and_boot_timeline():
+    import pytest
+
+    from minisglang_rdna4_b200.weights import BootTimeline, MemoryLedger
+    from minisglang_rdna4_b200.weights.host_capacity import check_pinned, pinned_budget
+
+    led = MemoryLedger(capacity_bytes=10 << 30)
+    led.add("weights", 4 << 30)
+    led.add("kv pool", 5 << 30)
+    led.add("weights", 1 << 29)
+    assert led.total == (9 << 30) + (1 << 29) and led.entries()[0][0] == "kv pool"
+    assert led.would_fit(1 << 28) and not led.would_fit(1 << 30)
+    led.release("kv pool", 1 << 30)
+    assert led.headroom() == (1 << 30) + (1 << 29) and "weights 4.50 GiB" in led.report()
+
+    meminfo = lambda: "MemTotal: 100 kB\nMemAvailable:   10485760 kB\n"
+    assert pinned_budget(0.2, meminfo, (-1, -1)) == int(10 * (1 << 30) * 0.8)
+    assert pinned_budget(0.2, meminfo, (2 << 30, 2 << 30)) == 2 << 30
+    check_pinned(7 << 30, read_meminfo=meminfo, memlock=(-1, -1))
+    with pytest.raises(MemoryError):
+        check_pinned(9 << 30, read_meminfo=meminfo, memlock=(-1, -1))
+
+    ticks = iter([0.0, 1.0, 4.0, 4.5])
+    tl = BootTimeline(clock=lambda: next(ticks))
+    assert tl.mark("weights") == 1.0 and tl.mark("kv pool") == 3.0 and tl.mark("graphs") == 0.5
+    out = tl.render()
+    assert "4.50 s" in out and "kv pool" in out and "66.7 %" in out
+
+
+def test_route_trace_and_disk_tier(tmp_path):
+    from minisglang_rdna4_b200.weights import DiskExpertTier, ExpertFile, HostExpertTier, RouteTrace
+
+    tr = RouteTrace(8)
+    tr.record(0, [1, 1, 3, -1, 9])
+    tr.record(0, torch.tensor([1, 2]).numpy())
+    tr.record(2, [7])
+    assert tr.hottest(0, 2) == [1, 2] and tr.hottest(1, 3) == [] and tr.skew(0) == 0.6
+    path = str(tmp_path / "trace.json")
+    tr.save(path)
+    again = RouteTrace.load(path)
+    assert again.hottest(0, 3) == [1, 2, 3] and again.steps == 3
+
+    torch.manual_seed(0)
+    w13 = torch.randn(8, 6, 4)
+    tier = HostExpertTier(w13, torch.randn(8, 4, 3), slots=4, device="cpu")
+    tier.trace, tier.layer_index = RouteTrace(8), 5
+    tier.prewarm([1, 2])
+    misses = tier.cache.misses
+    tier.forward(torch.randn(2, 4), torch.rand(2, 2), torch.tensor([[1, 2], [2, 1]], dtype=torch.int32))
+    assert tier.cache.misses == misses and tier.trace.hottest(5, 2) == [1, 2]
+
+    f = ExpertFile(str(tmp_path / "w13.bin"), layers=2, experts=8, shape=(6, 4), dtype=torch.float32)
+    f.create()
+    for e in range(8):
+        f.write(1, e, w13[e])
+    assert f.stride == 4096 and f.offset(1, 3) == (8 + 3) * 4096
+    disk = DiskExpertTier({"w13": f}, workers=2)
+    out = {"w13": torch.empty(3, 6, 4)}
+    disk.fetch(1, [5, 0, 7], out)
+    assert torch.equal(out["w13"], w13[[5, 0, 7]]) and disk.bytes_read == 3 * 96
+    disk.close()

@@ -49,6 +49,8 @@ class EngineConfig:
     # expert offload tiers
     weight_offload_gb: float = 0.0
     expert_cache_gb: float = 0.0
+    expert_host_gb: float = 0.0       # pinned host budget of the expert tier (0 = every expert pinned)
+    expert_disk_dir: str = ""         # flat expert files for what the pinned budget cannot hold
     # when set, overrides the config read from model_path (named shapes, tests)
     model_config: Optional[ModelConfig] = None
     base_port: int = 2333

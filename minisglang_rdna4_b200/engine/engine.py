@@ -312,7 +312,10 @@ class Engine:
         layers = sum(1 for i in range(mc.num_layers) if mc.layer_is_moe(i))
         geo = ExpertGeometry(layers, mc.num_experts, mc.num_experts_per_tok,
                              3 * mc.hidden_size * mc.moe_intermediate_size * itemsize)
-        plan = resolve_plan(geo, TierBudgets(device_bytes=int(cfg.expert_cache_gb * (1 << 30))))
+        MoELayer.offload_host_experts, MoELayer.offload_disk_dir, MoELayer._tier_seq = 0, "", 0
+        host_bytes = int(cfg.expert_host_gb * (1 << 30)) if cfg.expert_host_gb > 0 else None
+        plan = resolve_plan(geo, TierBudgets(device_bytes=int(cfg.expert_cache_gb * (1 << 30)), host_bytes=host_bytes,
+                                             disk=bool(cfg.expert_disk_dir)))
         if self.cpu_group is not None and cfg.tp_size > 1:
             # every rank must have resolved the same placement before anything is pinned
             from ..weights.plan import check_agreement
@@ -324,6 +327,9 @@ class Engine:
             check_pinned(plan.host_bytes)
         self.offload_plan = plan
         MoELayer.offload_slots = plan.layers[0].device_slots if plan.offloaded else 0
+        if plan.offloaded and plan.layers[0].disk_experts > 0:
+            MoELayer.offload_host_experts = plan.layers[0].host_experts
+            MoELayer.offload_disk_dir = os.path.join(cfg.expert_disk_dir, f"rank{cfg.tp_rank}")
         for note in plan.notes:
             logger.info_rank0("offload plan: %s", note)
         logger.info_rank0("host expert tier: %d of %d experts resident per layer (plan %s, %.2f GiB pinned)",

@@ -25,6 +25,10 @@ class MoELayer(BaseOP):
     # experts kept on the device per layer when the host-RAM expert tier is on (0 = all resident);
     # set by the engine from --expert-cache-gb before the weights are post-processed
     offload_slots: int = 0
+    # pinned host rows per layer (0 = all experts) and the directory of the disk tier behind them
+    offload_host_experts: int = 0
+    offload_disk_dir: str = ""
+    _tier_seq: int = 0
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, renormalize: bool,
                  dtype, device, scoring: str = "softmax", routed_scale: float = 1.0,
@@ -96,7 +100,11 @@ class MoELayer(BaseOP):
         if slots and slots < self._e_local:
             from ..weights import HostExpertTier
 
-            self._tier = HostExpertTier(self.w13, self.w2, slots, self.w13.device)
+            cls = type(self)
+            host = cls.offload_host_experts if 0 < cls.offload_host_experts < self._e_local else None
+            self._tier = HostExpertTier(self.w13, self.w2, slots, self.w13.device, host_experts=host,
+                                        disk_dir=cls.offload_disk_dir or None, layer_index=cls._tier_seq)
+            cls._tier_seq += 1
             # the full stacks now live in pinned host memory only
             self.w13 = self.w13[:0]
             self.w2 = self.w2[:0]

@@ -25,6 +25,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--weight-offload-gb", type=float, default=0.0)
     p.add_argument("--weight-offload-device-gb", type=float, default=0.0)
     p.add_argument("--expert-cache-gb", type=float, default=0.0)
+    p.add_argument("--expert-host-gb", type=float, default=0.0,
+                   help="pinned host budget of the expert tier; 0 pins every expert")
+    p.add_argument("--expert-disk-dir", default="", help="directory of the disk tier's flat expert files")
     p.add_argument("--weight-offload-cpu-layers", type=int, default=0)
     p.add_argument("--weight-offload-stream-layers", type=int, default=0)
     p.add_argument("--dummy-weight", dest="use_dummy_weight", action="store_true")
@@ -88,7 +91,8 @@ def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
         kv_cache_dtype=ns.kv_cache_dtype, quantization=ns.quantization, device=ns.device,
         spec_algorithm=ns.spec_algorithm, spec_draft_model_path=ns.spec_draft_model_path,
         spec_num_draft=ns.spec_num_draft, spec_ngram_max=ns.spec_ngram_max, spec_ngram_min=ns.spec_ngram_min,
-        spec_tree_width=ns.spec_tree_width, weight_offload_gb=ns.weight_offload_gb, expert_cache_gb=ns.expert_cache_gb,
+        spec_tree_width=ns.spec_tree_width, weight_offload_gb=ns.weight_offload_gb, expert_cache_gb=ns.expert_cache_gb, expert_host_gb=ns.expert_host_gb,
+        expert_disk_dir=ns.expert_disk_dir,
         max_extend_tokens=ns.max_extend_tokens, disable_overlap=ns.disable_overlap, host=ns.host, port=ns.port,
         served_model_name=ns.served_model_name, num_tokenizer=ns.num_tokenizer, shell_mode=ns.shell_mode,
         chat_template=chat_template, chat_template_kwargs=kwargs, reasoning_parser=ns.reasoning_parser,

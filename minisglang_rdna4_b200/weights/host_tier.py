@@ -21,14 +21,44 @@ from .pinned_arena import PinnedArena
 
 
 class HostExpertTier:
-    def __init__(self, w13: torch.Tensor, w2: torch.Tensor, slots: int, device, protected_fraction: float = 0.8
-                 ) -> None:
+    """``host_experts`` < E together with ``disk_dir`` adds a third tier: the pinned arena then holds
+    only that many experts (its own SLRU cache) and every expert has a record in two flat files
+    under ``disk_dir`` (weights/disk_tier.py); a device miss whose expert is not in the arena
+    first reads the records into an arena slot, then uploads from there."""
+
+    def __init__(self, w13: torch.Tensor, w2: torch.Tensor, slots: int, device, protected_fraction: float = 0.8,
+                 host_experts: Optional[int] = None, disk_dir: Optional[str] = None, layer_index: int = 0) -> None:
         self.num_experts = w13.shape[0]
         self.slots = min(slots, self.num_experts)
         self.device = torch.device(device)
         self.arena = PinnedArena()
-        self.h13 = self.arena.put("w13", w13)
-        self.h2 = self.arena.put("w2", w2)
+        self.disk = None
+        self.host_cache: Optional[SLRUCache] = None
+        if host_experts is not None and host_experts < self.num_experts:
+            if not disk_dir:
+                raise ValueError("a pinned arena smaller than the expert set needs a disk tier")
+            if host_experts < self.slots:
+                raise ValueError("the pinned arena must hold at least what the device slab holds")
+            import os
+
+            from .disk_tier import DiskExpertTier, ExpertFile
+
+            os.makedirs(disk_dir, exist_ok=True)
+            files = {}
+            for name, w in (("w13", w13), ("w2", w2)):
+                f = ExpertFile(os.path.join(disk_dir, f"layer{layer_index}.{name}.bin"), 1, self.num_experts,
+                               tuple(w.shape[1:]), w.dtype)
+                f.create()
+                for e in range(self.num_experts):
+                    f.write(0, e, w[e])
+                files[name] = f
+            self.disk = DiskExpertTier(files)
+            self.host_cache = SLRUCache(host_experts, protected_fraction)
+            self.h13 = self.arena.put("w13", torch.zeros((host_experts,) + tuple(w13.shape[1:]), dtype=w13.dtype))
+            self.h2 = self.arena.put("w2", torch.zeros((host_experts,) + tuple(w2.shape[1:]), dtype=w2.dtype))
+        else:
+            self.h13 = self.arena.put("w13", w13)
+            self.h2 = self.arena.put("w2", w2)
         self.d13 = torch.empty((self.slots,) + tuple(w13.shape[1:]), dtype=w13.dtype, device=self.device)
         self.d2 = torch.empty((self.slots,) + tuple(w2.shape[1:]), dtype=w2.dtype, device=self.device)
         self.cache = SLRUCache(self.slots, protected_fraction)
@@ -37,7 +67,30 @@ class HostExpertTier:
         self.bytes_copied = 0
         # optional (RouteTrace, layer index): every step's routed experts are counted there
         self.trace = None
-        self.layer_index = 0
+        self.layer_index = layer_index
+
+    def _host_rows(self, experts: List[int]) -> Dict[int, int]:
+        """Arena row of every expert in ``experts``, reading from disk what the arena lacks."""
+        if self.host_cache is None:
+            return {e: e for e in experts}
+        rows: Dict[int, int] = {}
+        missing: List[int] = []
+        for e in experts:
+            hit = self.host_cache.touch(e)
+            if hit is None:
+                missing.append(e)
+            else:
+                rows[e] = self.host_cache.slot_of(e)
+        if missing:
+            if self.copy_stream is not None:
+                # an arena row may still be the source of an upload queued earlier
+                self.copy_stream.synchronize()
+            for e in missing:
+                slot, _ = self.host_cache.admit(e, pinned=experts)
+                rows[e] = slot
+            self.disk.fetch(0, missing, {"w13": [self.h13[rows[e]] for e in missing],
+                                         "w2": [self.h2[rows[e]] for e in missing]})
+        return rows
 
     def prewarm(self, experts: List[int]) -> None:
         """Make the hottest experts of an earlier run's route trace resident before the first step
@@ -58,20 +111,21 @@ class HostExpertTier:
             updates[e] = slot
             if old is not None:
                 evicted.append(old)
+        rows = self._host_rows(list(updates.keys()))
         if self.copy_stream is not None:
             # the slab may still be read by kernels queued earlier on the compute stream
             self.copy_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.copy_stream):
                 for e, slot in updates.items():
-                    self.d13[slot].copy_(self.h13[e], non_blocking=True)
-                    self.d2[slot].copy_(self.h2[e], non_blocking=True)
+                    self.d13[slot].copy_(self.h13[rows[e]], non_blocking=True)
+                    self.d2[slot].copy_(self.h2[rows[e]], non_blocking=True)
             torch.cuda.current_stream(self.device).wait_stream(self.copy_stream)
         else:
             for e, slot in updates.items():
-                self.d13[slot].copy_(self.h13[e])
-                self.d2[slot].copy_(self.h2[e])
-        self.bytes_copied += sum(self.h13[e].numel() * self.h13.element_size()
-                                 + self.h2[e].numel() * self.h2.element_size() for e in updates)
+                self.d13[slot].copy_(self.h13[rows[e]])
+                self.d2[slot].copy_(self.h2[rows[e]])
+        per_expert = self.h13[0].numel() * self.h13.element_size() + self.h2[0].numel() * self.h2.element_size()
+        self.bytes_copied += per_expert * len(updates)
         idx = torch.tensor(list(updates.keys()) + evicted, dtype=torch.int64)
         val = torch.tensor(list(updates.values()) + [-1] * len(evicted), dtype=torch.int32)
         self.slot_map[idx.to(self.device)] = val.to(self.device)

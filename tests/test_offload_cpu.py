@@ -176,3 +176,35 @@ def test_route_trace_and_disk_tier(tmp_path):
     disk.fetch(1, [5, 0, 7], out)
     assert torch.equal(out["w13"], w13[[5, 0, 7]]) and disk.bytes_read == 3 * 96
     disk.close()
+
+
+def test_three_tier_engine_matches_resident_engine(tmp_path):
+    """Device slab < pinned arena < expert set: misses of the arena are read from the flat files."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.layers.moe import MoELayer
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    cfg = ModelConfig(num_layers=2, num_qo_heads=2, num_kv_heads=1, head_dim=32, hidden_size=64, vocab_size=300,
+                      intermediate_size=128, rms_norm_eps=1e-6, rotary_config=RotaryConfig(32, 32, 512, 1e4),
+                      model_type="qwen3_moe", architectures=("Qwen3MoeForCausalLM",), qk_norm=True, num_experts=16,
+                      num_experts_per_tok=2, moe_intermediate_size=32, torch_dtype="float32",
+                      max_position_embeddings=512)
+    prompts = [list(range(5, 25)), list(range(40, 49))]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    kw = dict(model_config=cfg, use_dummy_weight=True, device="cpu", page_size=16, max_running_req=4,
+              num_page_override=64, seed=2)
+    try:
+        want = [o.token_ids for o in LLM(**kw).generate(prompts, sp)]
+        per_layer = 3 * 64 * 32 * 4                                      # bytes of one expert
+        tiered = LLM(expert_cache_gb=2 * 6 * per_layer / (1 << 30),      # 6 device slots per layer
+                     expert_host_gb=2 * 10 * per_layer / (1 << 30),      # 10 pinned rows per layer
+                     expert_disk_dir=str(tmp_path), **kw)
+        got = [o.token_ids for o in tiered.generate(prompts, sp)]
+        tiers = [m._tier for m in tiered.engine.model.modules() if getattr(m, "_tier", None) is not None]
+        assert len(tiers) == 2 and all(t.slots == 6 and t.host_cache.capacity == 10 for t in tiers)
+        assert sum(t.disk.bytes_read for t in tiers) > 0 and sum(t.host_cache.evictions for t in tiers) > 0
+        assert tiered.engine.offload_plan.layers[0].disk_experts == 6
+    finally:
+        MoELayer.offload_slots, MoELayer.offload_host_experts, MoELayer.offload_disk_dir = 0, 0, ""
+    assert got == want

@@ -263,6 +263,36 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, 
     return out
 
 
+_PLAN_RING: Dict[torch.device, list] = {}
+_PLAN_RING_POS: Dict[torch.device, int] = {}
+
+
+def _upload_tables(host: np.ndarray, device) -> torch.Tensor:
+    """int32 tables -> device through a small ring of pinned buffers: the copy is asynchronous, so
+    building the plan of the next step does not wait for the kernels of the step in flight. A
+    ring slot is reused only after the event recorded behind its copy."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return torch.from_numpy(host.copy())
+    ring = _PLAN_RING.setdefault(device, [None] * 4)
+    pos = _PLAN_RING_POS.get(device, 0)
+    _PLAN_RING_POS[device] = pos + 1
+    slot = ring[pos % 4]
+    n = int(host.size)
+    if slot is not None and slot[1] is not None:
+        slot[1].synchronize()
+    if slot is None or slot[0].numel() < n:
+        slot = [torch.empty(max(n * 2, 1 << 14), dtype=torch.int32, pin_memory=True), None]
+        ring[pos % 4] = slot
+    slot[0].numpy()[:n] = host
+    dev = torch.empty(n, dtype=torch.int32, device=device)
+    dev.copy_(slot[0][:n], non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    slot[1] = ev
+    return dev
+
+
 class PrefillPlan:
     """Per-step tables of the tensor-core prefill kernel: one item per (request, block of 128
     query positions), heaviest first; the request of every 128-row scratch block; per request
@@ -299,7 +329,7 @@ class PrefillPlan:
         self.off_blk = items.size
         self.off_req = self.off_blk + blk_req.size
         host = np.concatenate([items.reshape(-1), blk_req, req_info])
-        self.tables = torch.from_numpy(host).to(device, non_blocking=False)
+        self.tables = _upload_tables(host, device)
 
 
 _TC_SCRATCH: Dict[Tuple[torch.device, torch.dtype, int], Tuple[torch.Tensor, torch.Tensor, int]] = {}

@@ -28,6 +28,12 @@ class CacheManager:
         self.page_table = np.zeros((num_slots, max_pages_per_seq), dtype=np.int32)
         self.prefix_hit_tokens = 0
         self.prefix_query_tokens = 0
+        # measure-only: what an unbounded prefix cache would have reused (kvcache/ghost_oracle.py)
+        self.ghost = None
+        from ..kvcache.ghost_oracle import GhostPrefixOracle, oracle_enabled
+
+        if oracle_enabled():
+            self.ghost = GhostPrefixOracle(page_size)
 
     # ---- sizes (pages) ----
     @property
@@ -52,6 +58,8 @@ class CacheManager:
         (python/minisgl/scheduler/cache.py:39)."""
         n = int(input_ids.numel())
         handle, pages = self.prefix_cache.match_prefix(input_ids[: max(n - 1, 0)])
+        if self.ghost is not None:
+            self.ghost.observe(input_ids[: max(n - 1, 0)].tolist(), handle.cached_len)
         return handle, pages
 
     def lock(self, handle: BaseCacheHandle) -> None:

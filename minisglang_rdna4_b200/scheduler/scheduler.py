@@ -483,6 +483,23 @@ class Scheduler:
                 self.normal_loop()
         except RequestAllFinished:
             pass
+        finally:
+            self._flush_ghost_oracle()
+
+    def _flush_ghost_oracle(self) -> None:
+        """Log the prefix-reuse oracle's counters and persist them when a directory is configured."""
+        ghost = getattr(getattr(self, "cache", None), "ghost", None)
+        if ghost is None or ghost.requests == 0:
+            return
+        from ..kvcache.ghost_oracle import oracle_path
+
+        logger.info("%s", ghost.report())
+        path = oracle_path(self.config.model_path, self.config.dp_rank)
+        if path:
+            try:
+                ghost.save(path)
+            except OSError as exc:
+                logger.warning("ghost oracle state not saved: %s", exc)
 
     # ------------------------------------------------------------------ spec decode
     def _feed_prefill_features(self, batch: Batch) -> None:

@@ -93,6 +93,15 @@ def resolve_model_config(cfg: EngineConfig) -> ModelConfig:
         mc = NAMED_CONFIGS[cfg.model_path]()
     else:
         mc = ModelConfig.from_hf(cfg.model_path)
+        # the serving list of stop tokens lives in generation_config.json; config.json often names
+        # only one of them
+        from dataclasses import replace
+
+        from ..utils.hf import resolve_stop_token_ids
+
+        stops = resolve_stop_token_ids(cfg.model_path, None, mc.eos_token_ids)
+        if tuple(stops) != tuple(mc.eos_token_ids):
+            mc = replace(mc, eos_token_ids=tuple(stops))
     if cfg.quantization and mc.quant is None:
         from ..quant.config import QuantConfig
 

@@ -175,6 +175,21 @@ class FrontendManager:
 
 
 # ------------------------------------------------------------------------------------------ helpers
+# The served model's recommended sampling (generation_config.json), applied to the fields a
+# request leaves unset; filled by ``set_sampling_defaults`` when the server starts
+# (python/minisgl/utils/hf.py:192: a repack served with top_p = 1 / top_k = -1 while its card says
+# 0.95 / 64 samples from the whole distribution).
+_SAMPLING_DEFAULTS: Dict[str, float] = {}
+
+
+def set_sampling_defaults(model_path: str) -> Dict[str, float]:
+    from ..utils.hf import sampling_defaults
+
+    _SAMPLING_DEFAULTS.clear()
+    _SAMPLING_DEFAULTS.update(sampling_defaults(model_path))
+    return dict(_SAMPLING_DEFAULTS)
+
+
 def sampling_from_request(req: OpenAICompletionRequest, reasoning: Optional[ReasoningParser],
                           chat_template: Optional[str]) -> SamplingParams:
     stop = [req.stop] if isinstance(req.stop, str) else list(req.stop or [])
@@ -203,10 +218,10 @@ def sampling_from_request(req: OpenAICompletionRequest, reasoning: Optional[Reas
     if thinking is None and req.chat_template_kwargs:
         thinking = req.chat_template_kwargs.get("enable_thinking")
     sp = SamplingParams(
-        temperature=0.0 if req.temperature is None else float(req.temperature),
-        top_k=-1 if req.top_k is None else int(req.top_k),
-        top_p=1.0 if req.top_p is None else float(req.top_p),
-        min_p=0.0 if req.min_p is None else float(req.min_p),
+        temperature=float(_SAMPLING_DEFAULTS.get("temperature", 0.0)) if req.temperature is None else float(req.temperature),
+        top_k=int(_SAMPLING_DEFAULTS.get("top_k", -1)) if req.top_k is None else int(req.top_k),
+        top_p=float(_SAMPLING_DEFAULTS.get("top_p", 1.0)) if req.top_p is None else float(req.top_p),
+        min_p=float(_SAMPLING_DEFAULTS.get("min_p", 0.0)) if req.min_p is None else float(req.min_p),
         ignore_eos=req.ignore_eos, max_tokens=req.resolved_max_tokens(), logprobs=logprobs,
         presence_penalty=req.presence_penalty, frequency_penalty=req.frequency_penalty, stop=stop,
         grammar=grammar, grammar_required=required, seed=req.seed,
@@ -479,6 +494,9 @@ def run_api_server(args: ServerArgs, start_backend=None) -> None:
             template = getattr(load_tokenizer(args.model_path), "chat_template", None)
         except Exception:
             template = None
+    defaults = set_sampling_defaults(args.model_path)
+    if defaults:
+        logger.info("sampling defaults from generation_config.json: %s", defaults)
     if start_backend is not None:
         start_backend()
     app = create_app(args, manager, template if isinstance(template, str) else None)

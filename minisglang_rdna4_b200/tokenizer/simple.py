@@ -51,5 +51,7 @@ def load_tokenizer(model_path: str):
                                                                   "tokenizer.model")):
         from transformers import AutoTokenizer
 
-        return AutoTokenizer.from_pretrained(model_path)
+        from ..utils.hf import apply_chat_template_sources
+
+        return apply_chat_template_sources(AutoTokenizer.from_pretrained(model_path), model_path)
     return ByteTokenizer()

@@ -301,7 +301,11 @@ class Scheduler:
                 continue
             if sp.grammar is not None and (think is None or think.grammar_active):
                 backend.fill(gs.ensure(r.uid, sp.grammar), bm, j)
-            if tool is not None and tool.suppress_eos:
+            # no end of turn inside an open tool call, nor inside a reasoning span that the prompt
+            # opened and whose budget will force the close delimiter out (a thinking model that stops there returns
+            # a blank answer; python/minisgl/engine/sample.py:29-32)
+            thinking = think is not None and not think.released and think.budget > 0 and sp.think_span_open
+            if (tool is not None and tool.suppress_eos) or thinking:
                 for e in self.eos_ids:
                     word, bit = e // 32, e % 32
                     mask = ~(1 << bit) if bit != 31 else 0x7FFFFFFF

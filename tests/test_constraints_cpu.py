@@ -73,3 +73,23 @@ def test_reasoning_budget_forces_close_delimiter_end_to_end():
     out = llm.generate([list(b"hello")], sp)[0]
     text = ByteTokenizer().decode(out.token_ids)
     assert text[4:8] == "</t>", text
+
+
+def test_end_of_turn_is_suppressed_inside_a_budgeted_reasoning_span():
+    """A thinking model must not end its turn in the middle of a reasoning span: while the span the
+    prompt opened is still open (and a budget will close it), the end-of-sequence ids are masked."""
+    prompt = [list(b"hello")]
+    plain = _llm().generate(prompt, SamplingParams(max_tokens=4, ignore_eos=True))[0].token_ids
+    stop = plain[0]                                   # what the model wants to say first
+
+    llm = _llm()
+    llm.eos_ids = {stop}                              # pretend that token ends the turn
+    free = llm.generate(prompt, SamplingParams(max_tokens=8))[0]
+    assert free.token_ids == [stop]                   # without a gate the turn ends at once
+
+    llm = _llm()
+    llm.eos_ids = {stop}
+    sp = SamplingParams(max_tokens=8, think_close_delim="</t>", think_budget=3, think_span_open=True)
+    gated = llm.generate(prompt, sp)[0].token_ids
+    text = ByteTokenizer().decode(gated)
+    assert stop not in gated[:3] and "</t>" in text   # three thought tokens, then the forced close

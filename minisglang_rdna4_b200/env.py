@@ -148,6 +148,11 @@ ENV.flag("METRICS", True, "collect Prometheus metrics")
 ENV.int("DEFAULT_MAX_TOKENS", 1024, "max_tokens applied to a request that gives none")
 ENV.str("SHELL_SYSTEM_PROMPT", "", "system prompt of the interactive shell")
 ENV.flag("LOG_REQUESTS", False, "log one line per admitted and finished request")
+ENV.str("CHAT_TEMPLATE", "", "chat template of the served model: a file path or a literal Jinja string")
+ENV.str("CHAT_TEMPLATE_MODEL", "", "model path the CHAT_TEMPLATE override applies to")
+# --- measurement --------------------------------------------------------------------------
+ENV.flag("GHOST_ORACLE", False, "count what an unbounded prefix cache would have reused (measure-only)")
+ENV.str("GHOST_ORACLE_DIR", "", "directory where the prefix-reuse oracle keeps its state across restarts")
 
 
 def env_int(name: str, default: int) -> int:

@@ -22,13 +22,15 @@ _OFFSET, _PRIME, _MASK = 0xCBF29CE484222325, 0x100000001B3, (1 << 64) - 1
 
 
 def oracle_enabled() -> bool:
-    from ..env import env_int
+    from ..env import ENV
 
-    return env_int("GHOST_ORACLE", 0) == 1
+    return bool(ENV.GHOST_ORACLE.value)
 
 
 def oracle_path(model: str, dp_rank: int = 0) -> Optional[str]:
-    d = os.environ.get("MSGL_GHOST_ORACLE_DIR") or os.environ.get("MINISGL_GHOST_ORACLE_DIR")
+    from ..env import ENV
+
+    d = ENV.GHOST_ORACLE_DIR.value
     if not d:
         return None
     slug = "".join(c if c.isalnum() or c in "-._" else "_" for c in (model or "unknown"))

@@ -77,8 +77,9 @@ def chat_template_override(model_path: str) -> Optional[str]:
     """``MSGL_CHAT_TEMPLATE`` (a file path or a literal Jinja string) applies to the tokenizer of
     ``MSGL_CHAT_TEMPLATE_MODEL`` only, so every process that loads the served tokenizer gets the
     same template while drafters' and calibrators' tokenizers stay untouched."""
-    spec = os.environ.get("MSGL_CHAT_TEMPLATE") or os.environ.get("MINISGL_CHAT_TEMPLATE")
-    model = os.environ.get("MSGL_CHAT_TEMPLATE_MODEL") or os.environ.get("MINISGL_CHAT_TEMPLATE_MODEL")
+    from ..env import ENV
+
+    spec, model = ENV.CHAT_TEMPLATE.value, ENV.CHAT_TEMPLATE_MODEL.value
     if not spec or model != model_path:
         return None
     if os.path.isfile(spec):

@@ -38,8 +38,10 @@ class PagedAttentionBackend(BaseAttnBackend):
                          host_cu_q=None, host_seq_lens=None) -> None:
         """``host_cu_q`` / ``host_seq_lens`` are the same lengths as numpy arrays: a prefill-phase
         step on a GPU builds the tables of the tensor-core prefill kernel from them (every such
-        step, whatever its size, so that a row's result does not depend on how its prompt was
-        chunked). Decode and verification steps stay on the general kernel."""
+        step whose KV rows number at most 16 times its query rows: every prefill and chunked-prefill
+        step whatever its size, so that a row's result does not depend on how its prompt was chunked;
+        a short extend over a long cached prefix reads the pool in place with the general kernel).
+        Decode and verification steps stay on the general kernel."""
         plan = None
         if (host_cu_q is not None and batch.is_prefill and not batch.spec_verify and mask is None and causal
                 and self._workspace is not None and self.d == 128 and (self.hq // self.hk) % 2 == 0):
@@ -47,7 +49,10 @@ class PagedAttentionBackend(BaseAttnBackend):
             from ..ops import cuda as K
 
             if not ENV.DISABLE_TC_PREFILL.value:
-                plan = K.PrefillPlan(host_cu_q, host_seq_lens, self.device)
+                b = int(len(host_seq_lens))
+                t_pad = int(((host_seq_lens.astype("int64") + 127) // 128 * 128).sum()) if b else 0
+                if K.tc_prefill_pays(int(host_cu_q[b]), t_pad):
+                    plan = K.PrefillPlan(host_cu_q, host_seq_lens, self.device)
         batch.attn_metadata = AttnMetadata(
             cu_q=cu_q, seq_lens=seq_lens, block_table=block_table, max_q=max_q, max_kv=max_kv,
             decode=(max_q == 1 and plan is None), causal=causal, mask=mask, workspace=self._workspace,

@@ -347,6 +347,15 @@ def _tc_scratch(device, dtype, hk: int, rows: int):
     return hit
 
 
+def tc_prefill_pays(total_q: int, t_pad: int) -> bool:
+    """The tensor-core path first copies every KV row the step can see into a dense 16-bit
+    scratch. That is noise when the step has about as many query rows as KV rows (prefill, chunked
+    prefill), but a short extend over a long cached prefix (a new chat turn over tens of thousands
+    of tokens) would move several times the bytes the general kernel reads in place: such steps
+    stay on the general kernel."""
+    return t_pad <= 16 * max(int(total_q), 128)
+
+
 def prefill_attention_tc_ok(q, k_cache, *, causal, window, mask, decode) -> bool:
     """The tcgen05 prefill kernel covers causal prefill / extend steps with head_dim 128 and an
     even number of query heads per KV head; everything else stays on the general kernel."""

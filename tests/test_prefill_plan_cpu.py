@@ -45,3 +45,14 @@ def test_empty_and_single_token_steps():
     assert items.tolist() == [[0, 1, 0, 0, 1, 0, 0, 0]] and blk_req.tolist() == [0] and req_info.tolist() == [[0, 1]]
     plan = PrefillPlan(np.array([0]), np.zeros(0, dtype=np.int64), "cpu")
     assert plan.n_items == 0 and plan.t_pad == 0
+
+
+def test_short_extends_over_long_prefixes_stay_on_the_general_kernel():
+    from minisglang_rdna4_b200.ops.cuda import tc_prefill_pays
+
+    assert tc_prefill_pays(8192, 9600)            # a prefill chunk
+    assert tc_prefill_pays(96, 256)               # a small chunk of a chunked prefill
+    assert tc_prefill_pays(8192, 4 * 32768)       # last chunk of a 32k prompt
+    assert tc_prefill_pays(5, 128)                # a tiny prompt
+    assert not tc_prefill_pays(100, 32 * 1024)    # a new chat turn over a 32k history
+    assert not tc_prefill_pays(16 * 32, 32 * 32768)

@@ -31,6 +31,10 @@ def spec_decode_step(sched) -> None:
         batch = sched.decode.schedule_next_batch()
         sched._process_last_data(sched._forward(batch))
         return
+    if getattr(proposer, "tree_width", 1) > 1 and hasattr(proposer, "propose_paths") \
+            and not getattr(proposer, "capture_layers", None):
+        _tree_decode_step(sched, reqs)
+        return
     if not hasattr(sched, "_spec_width"):
         sched._spec_width = AdaptiveWidth(proposer.num_draft)
     drafts = proposer.propose(reqs)
@@ -149,3 +153,94 @@ def _verify_plan(sched, batch: Batch, drafts):
                     seq_lens=ends.astype(np.int32), block_table=block_table,
                     sample_rows=np.arange(total, dtype=np.int32), write_idx=np.zeros(0, dtype=np.int32),
                     max_q=int(q_lens.max()), max_kv=max_kv)
+
+
+def _tree_decode_step(sched, reqs: List[Req]) -> None:
+    """Tree-structured verification (python/minisgl/spec/ddtree.py): the proposer's candidate
+    continuations of a request are merged into a prefix tree; one forward scores every node, each
+    attending to the committed prefix and to its ancestors through an additive mask; the target's
+    arg-max is followed down the tree; the K/V of the accepted path are then moved to the
+    positions they hold in the committed sequence. Greedy requests only (others take the
+    target's token after the root, i.e. a plain decode step)."""
+    from ..spec.tree import TokenTree, accept_greedy_tree, compaction_moves, tree_mask
+
+    proposer = sched.proposer
+    eng = sched.engine
+    msl, ps = sched.max_seq_len, sched.page_size
+    paths = proposer.propose_paths(reqs)
+    max_nodes = 1 + proposer.num_draft * proposer.tree_width
+    trees = []
+    for r, cand in zip(reqs, paths):
+        room = max(0, msl - r.device_len - 1)                 # KV slots left for draft nodes
+        budget = min(proposer.budget(r), room)
+        cand = [p[:budget] for p in cand] if r.sampling_params.is_greedy and budget > 0 else []
+        trees.append(TokenTree.from_paths(0, cand, max_nodes=min(max_nodes, 1 + room)))
+
+    # stage the node tokens behind each request's last token (node i at pool position cached_len + i)
+    flat_idx, flat_tok = [], []
+    for r, t in zip(reqs, trees):
+        for i in range(1, len(t)):
+            flat_idx.append(r.table_idx * msl + r.device_len - 1 + i)
+            flat_tok.append(t.tokens[i])
+    if flat_idx:
+        idx = torch.tensor(flat_idx, dtype=torch.int64)
+        tok = torch.tensor(flat_tok, dtype=torch.int32)
+        if eng.device.type == "cuda":
+            with torch.cuda.stream(eng.stream):
+                eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
+        else:
+            eng.token_pool.view(-1)[idx] = tok
+
+    batch = Batch(reqs=reqs, phase="decode")
+    batch.spec_verify = True
+    # rows and KV slots are laid out by node index; only the rotary positions follow the depth
+    plan = _verify_plan(sched, batch, [[0] * (len(t) - 1) for t in trees])
+    cu = plan.cu_q.tolist()
+    prefix = [r.cached_len for r in reqs]
+    pos = plan.positions.copy()
+    mask = torch.full((plan.num_tokens, plan.max_kv), float("-inf"), dtype=torch.float32)
+    for i, (t, p0) in enumerate(zip(trees, prefix)):
+        pos[cu[i]:cu[i + 1]] = np.asarray([p0 + d for d in t.depth], dtype=pos.dtype)
+        mask[cu[i]:cu[i + 1]] = tree_mask(t, p0, plan.max_kv)
+    plan.positions[:] = pos
+    batch.tree_mask = mask.to(eng.device)
+    args = BatchSamplingArgs()
+    out = eng.forward_batch(batch, plan, args, return_logits=True)
+    logits = eng.sampler.condition_logits(out.logits, args)
+    target = logits.argmax(-1).to(torch.int32).cpu().tolist()
+    sched.stats["steps"] += 1
+    sched.stats["spec_steps"] += 1
+    sched.stats["decode_tokens"] += plan.num_tokens
+
+    replies: List[DetokenizeMsg] = []
+    buf = eng.kv_cache._buf
+    for i, (r, t) in enumerate(zip(reqs, trees)):
+        emitted, path = accept_greedy_tree(t, target[cu[i]:cu[i + 1]])
+        emitted = emitted[: max(1, min(len(emitted), r.sampling_params.max_tokens - r.num_generated))]
+        emitted, hit_eos = eos_truncate(emitted, sched.eos_ids, r.sampling_params.ignore_eos)
+        n = len(emitted)
+        sched.stats["spec_drafted"] += len(t) - 1
+        sched.stats["spec_accepted"] += n - 1
+        sched.stats["spec_emitted"] += n
+        # accepted nodes' K/V -> the slots of their positions in the committed sequence
+        row = sched.cache.page_table[r.table_idx]
+        for src, dst in compaction_moves(path[:n], prefix[i]):
+            buf[:, :, int(row[dst // ps]), :, dst % ps, :] = buf[:, :, int(row[src // ps]), :, src % ps, :]
+        r.append_host(torch.tensor(emitted, dtype=torch.int32))
+        at = r.table_idx * msl + r.device_len
+        eng.token_pool.view(-1)[at:at + n] = torch.tensor(emitted, dtype=torch.int32).to(eng.device)
+        r.complete_many(n)
+        proposer.on_accept(r, emitted)
+        finished = hit_eos or r.num_generated >= r.sampling_params.max_tokens
+        reason = "stop" if hit_eos else ("length" if finished else None)
+        for j, tok_id in enumerate(emitted):
+            last = j == n - 1
+            replies.append(DetokenizeMsg(r.uid, tok_id, finished and last, reason if last else None,
+                                         prompt_tokens=r.prompt_len, cached_tokens=sched.prefix_len.get(r.uid, 0)))
+        if finished:
+            r.finished, r.finish_reason = True, reason
+            proposer.on_finish(r)
+            sched._free_req_resources(r, insert=True)
+    sched.decode.filter_finished()
+    if replies:
+        sched.send_result(replies)

@@ -42,7 +42,8 @@ def make_proposer(config, scheduler) -> Proposer:
     if algo == "ngram":
         from .ngram import NgramProposer
 
-        return NgramProposer(config.spec_num_draft, config.spec_ngram_max, config.spec_ngram_min)
+        return NgramProposer(config.spec_num_draft, config.spec_ngram_max, config.spec_ngram_min,
+                             tree_width=max(1, int(getattr(config, "spec_tree_width", 1) or 1)))
     if algo == "eagle3":
         from .eagle3 import Eagle3Proposer
 

@@ -134,3 +134,47 @@ def test_eagle3_draft_is_exact_and_a_distilled_head_gets_accepted():
     # MTP variant: one feature layer, no fc
     mtp = _llm(spec_algorithm="mtp", spec_num_draft=2)
     assert [o.token_ids for o in mtp.generate(prompts, sp)] == want
+
+
+from minisglang_rdna4_b200.spec.ngram import NgramProposer  # noqa: E402
+
+
+class _TreeOracle(NgramProposer):
+    """Two candidates per request: a wrong continuation first, the true one second, so that the
+    accepted path runs through a non-first branch and its K/V has to be moved."""
+
+    def __init__(self, k, answers):
+        super().__init__(k, tree_width=2)
+        self.answers = answers
+
+    def propose_paths(self, reqs):
+        out = []
+        for r in reqs:
+            done = r.num_generated
+            good = self.answers[r.uid][done: done + self.budget(r)]
+            bad = [(t + 1) % 1000 for t in good]
+            out.append([list(bad), list(good)] if good else [])
+        return out
+
+
+def test_tree_verification_is_exact_and_follows_the_right_branch():
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (20, 33, 47)]
+    prompts.append([1, 2, 3, 4, 5, 6, 7, 8] * 6)
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    plain = _llm()
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    tree = _llm(spec_algorithm="ngram", spec_num_draft=4, spec_tree_width=3)
+    got = [o.token_ids for o in tree.generate(prompts, sp)]
+    assert got == want and tree.stats["spec_steps"] > 0
+    tree.cache.check_integrity()
+    oracle = _llm(spec_algorithm="ngram", spec_num_draft=3, spec_tree_width=2)
+    oracle.proposer = _TreeOracle(3, {i: w for i, w in enumerate(want)})
+    got2 = [o.token_ids for o in oracle.generate(prompts, sp)]
+    assert got2 == want
+    assert oracle.stats["spec_accepted"] > 0 and oracle.stats["spec_steps"] < plain.stats["steps"]
+    # with max_tokens / eos cut-offs
+    short = _llm(spec_algorithm="ngram", spec_num_draft=3, spec_tree_width=2)
+    short.proposer = _TreeOracle(3, {0: want[0]})
+    out = short.generate([prompts[0]], SamplingParams(max_tokens=7, ignore_eos=True))[0]
+    assert out.token_ids == want[0][:7] and out.finish_reason == "length"

@@ -124,6 +124,10 @@ class ServerArgs(SchedulerConfig):
     chat_template: Optional[str] = None
     chat_template_kwargs: Optional[Dict[str, Any]] = None
     reasoning_parser: str = "auto"
+    # recursive self-aggregation defaults (rsa.RSAParams) of requests that ask for it with ``rsa: true``,
+    # and whether ``reasoning_effort`` alone switches it on through the effort ladder
+    rsa: Optional[Any] = None
+    rsa_effort_ladder: bool = False
 
     @property
     def zmq_frontend_addr(self) -> str:     # detokenizer -> frontend

@@ -79,6 +79,8 @@ class OpenAICompletionRequest(BaseModel):
     enable_thinking: Optional[bool] = None
     reasoning_max_tokens: Optional[int] = None
     reasoning_effort: Optional[str] = None
+    # recursive self-aggregation: true = the server's defaults, or an object overriding n / k / t / ...
+    rsa: Union[bool, Dict[str, Any], None] = None
     logprobs: Union[bool, int, None] = None
     top_logprobs: Optional[int] = None
     seed: Optional[int] = None
@@ -467,8 +469,87 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
 
         app.include_router(make_cam_router(cam_memory, _cam_generate if state.send_queue is not None else None))
 
+    def _rsa_params(req: OpenAICompletionRequest):
+        """Recursive self-aggregation applies when the request asks for it (``rsa``), or, with the
+        server's effort ladder enabled, when ``reasoning_effort`` maps to a ladder rung
+        (python/minisgl/server/api_server.py:1204)."""
+        from dataclasses import fields, replace
+
+        from ..rsa import RSAParams
+
+        base = getattr(args, "rsa", None) or RSAParams()
+        if req.rsa:
+            if isinstance(req.rsa, dict):
+                allowed = {f.name for f in fields(RSAParams)}
+                bad = sorted(set(req.rsa) - allowed)
+                if bad:
+                    raise HTTPException(status_code=400, detail=f"unknown rsa fields: {bad}")
+                return replace(base, **req.rsa)
+            return base
+        if getattr(args, "rsa_effort_ladder", False) and req.reasoning_effort:
+            return RSAParams.from_effort(req.reasoning_effort)
+        return None
+
+    async def _run_rsa(req: OpenAICompletionRequest, request: Request, params):
+        from ..rsa import run_rsa
+
+        if req.messages is None:
+            raise HTTPException(status_code=400, detail="`messages` is required")
+        if req.tools:
+            raise HTTPException(status_code=400, detail="rsa does not combine with tools")
+        state.ensure_listener()
+        usage = {"prompt_tokens": 0, "completion_tokens": 0}
+
+        async def generate(msgs, max_tokens, temperature, top_p) -> str:
+            uid = state.new_user()
+            sp = SamplingParams(temperature=float(temperature), top_p=float(top_p), max_tokens=int(max_tokens),
+                                ignore_eos=False)
+            await state.send_one(TokenizeMsg(uid, msgs, sp, dict(req.chat_template_kwargs or {}) or None, None))
+            parts = []
+            try:
+                async for reply in state.replies(uid):
+                    if reply.error:
+                        raise RuntimeError(reply.error)
+                    if reply.incremental_output:
+                        parts.append(reply.incremental_output)
+                    usage["completion_tokens"] += len(reply.token_ids)
+                    if getattr(reply, "prompt_tokens", 0):
+                        usage["prompt_tokens"] = max(usage["prompt_tokens"], int(reply.prompt_tokens))
+            except asyncio.CancelledError:
+                await state.abort_user(uid)
+                raise
+            text = "".join(parts)
+            if reasoning is not None:   # candidates are aggregated on their answers, not on their thoughts
+                text = reasoning.split(text)[1] if hasattr(reasoning, "split") else text
+            return text
+
+        messages = [m.model_dump(exclude_none=True) for m in req.messages]
+        result = await run_rsa(messages, params, generate)
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        model = req.model or args.model_name
+        created = int(time.time())
+        usage["total_tokens"] = usage["prompt_tokens"] + usage["completion_tokens"]
+        meta = {"rounds": result["rounds"], "calls": result["calls"], "n": params.n, "k": params.k, "t": params.t}
+        if req.stream:
+            async def gen():
+                yield _sse({"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
+                            "choices": [{"index": 0, "delta": {"role": "assistant", "content": result["answer"]},
+                                         "finish_reason": None}]})
+                yield _sse({"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
+                            "choices": [{"index": 0, "delta": {}, "finish_reason": "stop"}], "usage": usage,
+                            "rsa": meta})
+                yield _sse("[DONE]")
+
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        return JSONResponse({"id": rid, "object": "chat.completion", "created": created, "model": model,
+                             "choices": [{"index": 0, "message": {"role": "assistant", "content": result["answer"]},
+                                          "finish_reason": "stop"}], "usage": usage, "rsa": meta})
+
     @app.post("/v1/chat/completions")
     async def v1_chat_completions(req: OpenAICompletionRequest, request: Request):
+        params = _rsa_params(req)
+        if params is not None:
+            return await _run_rsa(req, request, params)
         return await _run(req, request, chat=True)
 
     @app.post("/v1/completions")

@@ -59,6 +59,21 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--spec-tree-width", type=int, default=1)
     p.add_argument("--disable-overlap", action="store_true")
     p.add_argument("--device", default="auto", choices=["auto", "cuda", "cpu"])
+    # recursive self-aggregation (python/minisgl/rsa/config.py:157-228): N rollouts, T rounds in which
+    # every rollout is rewritten from K candidates, then a vote over the final answers
+    p.add_argument("--rsa-n", type=int, default=4)
+    p.add_argument("--rsa-k", type=int, default=2)
+    p.add_argument("--rsa-t", type=int, default=2)
+    p.add_argument("--rsa-tail-tokens", type=int, default=1024)
+    p.add_argument("--rsa-max-tokens", type=int, default=1024)
+    p.add_argument("--rsa-agg-max-tokens", type=int, default=1024)
+    p.add_argument("--rsa-temperature", type=float, default=0.7)
+    p.add_argument("--rsa-top-p", type=float, default=0.95)
+    p.add_argument("--rsa-selection", default="vote", choices=["vote", "first", "longest"])
+    p.add_argument("--rsa-max-concurrency", type=int, default=8)
+    p.add_argument("--rsa-max-retries", type=int, default=1)
+    p.add_argument("--rsa-effort-ladder", action="store_true",
+                   help="`reasoning_effort` medium / high / max runs the request through self-aggregation")
     p.add_argument("--print-env", action="store_true", help="list every MSGL_* variable and exit")
     return p
 
@@ -96,4 +111,14 @@ def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
         max_extend_tokens=ns.max_extend_tokens, disable_overlap=ns.disable_overlap, host=ns.host, port=ns.port,
         served_model_name=ns.served_model_name, num_tokenizer=ns.num_tokenizer, shell_mode=ns.shell_mode,
         chat_template=chat_template, chat_template_kwargs=kwargs, reasoning_parser=ns.reasoning_parser,
+        rsa=_rsa_defaults(ns), rsa_effort_ladder=ns.rsa_effort_ladder,
     )
+
+
+def _rsa_defaults(ns):
+    from ..rsa import RSAParams
+
+    return RSAParams(n=ns.rsa_n, k=ns.rsa_k, t=ns.rsa_t, tail_tokens=ns.rsa_tail_tokens, max_tokens=ns.rsa_max_tokens,
+                     agg_max_tokens=ns.rsa_agg_max_tokens, temperature=ns.rsa_temperature, top_p=ns.rsa_top_p,
+                     selection=ns.rsa_selection, max_concurrency=ns.rsa_max_concurrency,
+                     max_retries=ns.rsa_max_retries)

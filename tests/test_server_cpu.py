@@ -246,3 +246,41 @@ def test_metrics_lifecycle():
     m.on_finish(1, "stop", prompt_tokens=10, cached_tokens=4)
     assert m.counters["generation_tokens_total"] == 4 and m.counters["requests_finished_total"] == 1
     assert m.ttft.n == 1 and m.tpot.n == 1 and m.e2e.n == 1
+
+
+def test_rsa_requests_run_rollouts_aggregation_rounds_and_a_vote():
+    """``rsa`` on a chat request: N rollouts, T - 1 aggregation rounds that each see K candidates, then a
+    vote on the final lines. ``reasoning_effort`` alone only does so when the server enabled the ladder."""
+    from minisglang_rdna4_b200.server.args import parse_args
+
+    def script(m):
+        text = m.text[-1]["content"]
+        if "candidate solutions" in text:                    # an aggregation call
+            return _words(m.uid, ["merged\n", "42"])
+        n = sum(1 for s in mgr.sent if isinstance(s, TokenizeMsg))
+        return _words(m.uid, ["guess\n", "42" if n % 3 else "41"])
+
+    c, mgr = _client(script)
+    body = {"messages": [{"role": "user", "content": "What is 6 x 7?"}], "rsa": {"n": 3, "k": 2, "t": 2}}
+    r = c.post("/v1/chat/completions", json=body)
+    out = r.json()
+    assert r.status_code == 200 and out["rsa"] == {"rounds": 2, "calls": 6, "n": 3, "k": 2, "t": 2}
+    assert out["choices"][0]["message"]["content"].endswith("42") and out["usage"]["completion_tokens"] == 12
+    rollouts = [s for s in mgr.sent if isinstance(s, TokenizeMsg)]
+    assert len(rollouts) == 6 and all(s.sampling_params.temperature == 0.7 for s in rollouts)
+    assert sum("Candidate 2:" in s.text[-1]["content"] for s in rollouts) == 3
+
+    assert c.post("/v1/chat/completions", json={**body, "rsa": {"rounds": 9}}).status_code == 400
+    # without the ladder, reasoning_effort is an ordinary request
+    c2, mgr2 = _client(lambda m: _words(m.uid, ["x"]))
+    c2.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "reasoning_effort": "high"})
+    assert len(mgr2.sent) == 1
+
+    args = parse_args(["--model", "tiny-llama", "--rsa-n", "6", "--rsa-selection", "longest", "--rsa-effort-ladder"])
+    assert args.rsa.n == 6 and args.rsa.selection == "longest" and args.rsa_effort_ladder
+    mgr3 = FakeManager(args, lambda m: _words(m.uid, ["a\n", "7"]))
+    c3 = TestClient(create_app(args, mgr3, None))
+    out3 = c3.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}],
+                                                 "reasoning_effort": "medium", "stream": True})
+    assert out3.status_code == 200 and '"rsa"' in out3.text and "[DONE]" in out3.text
+    assert sum(isinstance(s, TokenizeMsg) for s in mgr3.sent) == 4     # medium: n = 2, t = 2

@@ -44,6 +44,8 @@ class GenerateRequest(BaseModel):
     presence_penalty: float = 0.0
     frequency_penalty: float = 0.0
     seed: Optional[int] = None
+    cam_read: Optional[bool] = None
+    cam_write: Optional[bool] = None
 
 
 class ChatMessage(BaseModel):
@@ -81,6 +83,10 @@ class OpenAICompletionRequest(BaseModel):
     reasoning_effort: Optional[str] = None
     # recursive self-aggregation: true = the server's defaults, or an object overriding n / k / t / ...
     rsa: Union[bool, Dict[str, Any], None] = None
+    # associative memory: per-request override of the ambient read / write defaults (MSGL_CAM_AUTO,
+    # MSGL_CAM_AUTO_WRITE); only meaningful when the server runs with MSGL_CAM=1
+    cam_read: Optional[bool] = None
+    cam_write: Optional[bool] = None
     logprobs: Union[bool, int, None] = None
     top_logprobs: Optional[int] = None
     seed: Optional[int] = None
@@ -258,6 +264,63 @@ async def stream_with_cancellation(request: Request, gen: AsyncIterator[str], on
 
 
 # ------------------------------------------------------------------------------------------ app
+# ------------------------------------------------------------------------------------------ CAM hooks
+_FACT_RE = None
+
+
+def looks_like_fact_statement(text: str) -> bool:
+    """Does the text plausibly assert a durable fact? Questions and texts without a copula do not
+    (python/minisgl/server/api_server.py:2003-2014); keeps chit-chat out of the store."""
+    import re
+
+    t = (text or "").strip()
+    return bool(t) and not t.endswith("?") and re.search(r"\b(is|was|are|were)\b", t, re.IGNORECASE) is not None
+
+
+def extract_facts(text: str) -> List[tuple]:
+    """``(subject, relation, object)`` triples of the plain ``<subject> is|was|are|were <object>``
+    sentences of the text. The reference asks the served model to extract them; this build uses
+    the sentence pattern, which is deterministic and needs no extra generation."""
+    import re
+
+    out = []
+    for sent in re.split(r"(?<=[.!;])\s+|\n+", text or ""):
+        sent = sent.strip().rstrip(".!;")
+        m = re.match(r"^(?P<s>[^,:?]{2,80}?)\s+(?P<r>is|was|are|were)\s+(?P<o>[^?]{1,200})$", sent, re.IGNORECASE)
+        if m and not sent.endswith("?"):
+            subj = re.sub(r"^(remember that|note that|fyi,?)\s+", "", m.group("s").strip(), flags=re.IGNORECASE)
+            out.append((subj, m.group("r").lower(), m.group("o").strip()))
+    return out
+
+
+def cam_auto_read(memory, payload: Any, override: Optional[bool], namespace: str = "default") -> Any:
+    """Transparent read: facts that match the request are stated in front of it (a system message
+    for chat, a preface for a raw prompt). Unchanged when off or when nothing matches."""
+    enabled = override if override is not None else os.environ.get("MSGL_CAM_AUTO", "0") == "1"
+    if memory is None or not enabled:
+        return payload
+    if isinstance(payload, list):
+        query = " ".join(str(m.get("content") or "") for m in payload if m.get("role") in ("user", "system"))
+        hits = memory.lookup(query, namespace) if query.strip() else []
+        if not hits:
+            return payload
+        note = "Known facts:\n" + "\n".join(f"- {f.subject}: {f.prompt} {f.object}".replace("  ", " ") for _, f in hits)
+        return [{"role": "system", "content": note}] + list(payload)
+    return memory.augment(str(payload), namespace)
+
+
+def cam_auto_write(memory, text: str, override: Optional[bool], namespace: str = "default") -> int:
+    """Ambient write: durable facts asserted in the latest user turn are remembered. Returns how many."""
+    enabled = override if override is not None else os.environ.get("MSGL_CAM_AUTO_WRITE", "0") == "1"
+    if memory is None or not enabled or not looks_like_fact_statement(text):
+        return 0
+    n = 0
+    for subj, rel, obj in extract_facts(text):
+        memory.remember(subj, rel, obj, namespace)
+        n += 1
+    return n
+
+
 def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat_template: Optional[str] = None
                ) -> FastAPI:
     app = FastAPI(title="minisglang-rdna4 b200")
@@ -294,7 +357,13 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
         sp = SamplingParams(temperature=req.temperature, top_k=req.top_k, top_p=req.top_p, min_p=req.min_p,
                             ignore_eos=req.ignore_eos, max_tokens=req.max_tokens, seed=req.seed,
                             presence_penalty=req.presence_penalty, frequency_penalty=req.frequency_penalty)
-        await state.send_one(TokenizeMsg(uid, req.prompt, sp))
+        prompt = req.prompt
+        cam = getattr(app.state, "cam", None)
+        if cam is not None:
+            ns = request.headers.get("x-cam-namespace") or "default"
+            cam_auto_write(cam, prompt, req.cam_write, ns)
+            prompt = cam_auto_read(cam, prompt, req.cam_read, ns)
+        await state.send_one(TokenizeMsg(uid, prompt, sp))
 
         async def gen():
             async for reply in state.replies(uid):
@@ -321,6 +390,13 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
             payload: Any = [m.model_dump(exclude_none=True) for m in req.messages]
         else:
             payload = req.prompt if req.prompt is not None else [m.model_dump(exclude_none=True) for m in req.messages]
+        cam = getattr(app.state, "cam", None)
+        if cam is not None:
+            ns = request.headers.get("x-cam-namespace") or "default"
+            last_user = payload if isinstance(payload, str) else next(
+                (str(m.get("content") or "") for m in reversed(payload) if m.get("role") == "user"), "")
+            cam_auto_write(cam, last_user, req.cam_write, ns)
+            payload = cam_auto_read(cam, payload, req.cam_read, ns)
         kwargs = dict(req.chat_template_kwargs or {})
         if req.enable_thinking is not None:
             kwargs.setdefault("enable_thinking", req.enable_thinking)

@@ -47,3 +47,47 @@ def test_rest_plane_with_namespace_tokens(monkeypatch):
     assert c.delete("/cam/facts/Kite", headers=a).json() == {"deleted": True}
     assert c.post("/cam/undo", headers=a).json()["undone"].startswith("undid forget")
     assert len(c.get("/cam/facts", headers=a).json()) == 1
+
+
+def test_ambient_read_and_write_hooks_on_the_completion_endpoints(monkeypatch, tmp_path):
+    """With the memory mounted, a request can state a fact (``cam_write``) and a later request gets
+    it placed in front of its prompt (``cam_read``); both are off unless asked for or enabled by
+    the server's environment."""
+    from fastapi.testclient import TestClient
+
+    from minisglang_rdna4_b200.config import ServerArgs
+    from minisglang_rdna4_b200.message import TokenizeMsg, UserReply
+    from minisglang_rdna4_b200.server.api_server import FrontendManager, create_app
+
+    monkeypatch.setenv("MSGL_CAM", "1")
+    monkeypatch.setenv("MSGL_CAM_PATH", str(tmp_path / "cam.json"))
+
+    class Fake(FrontendManager):
+        def __init__(self, args):
+            super().__init__(args)
+            self.sent = []
+
+        async def send_one(self, msg):
+            self.sent.append(msg)
+            if isinstance(msg, TokenizeMsg):
+                self.queues[msg.uid].put_nowait(UserReply(msg.uid, "ok", True, "stop", [1], prompt_tokens=3))
+
+    args = ServerArgs(model_path="tiny-llama", served_model_name="tiny")
+    mgr = Fake(args)
+    c = TestClient(create_app(args, mgr, None))
+    ask = {"messages": [{"role": "user", "content": "What is Zephyrina's mother tongue?"}]}
+    c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "Zephyrina's mother tongue is Klingon."}]})
+    assert c.get("/cam/facts").json() == []                                   # writing is off by default
+    c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "Zephyrina's mother tongue is Klingon."}],
+                                         "cam_write": True})
+    assert c.get("/cam/facts").json() == [{"subject": "Zephyrina's mother tongue", "prompt": "is", "object": "Klingon"}]
+    c.post("/v1/chat/completions", json=ask)                                  # read is off by default
+    assert mgr.sent[-1].text == ask["messages"]
+    c.post("/v1/chat/completions", json={**ask, "cam_read": True})
+    sent = mgr.sent[-1].text
+    assert sent[0]["role"] == "system" and "Klingon" in sent[0]["content"] and sent[1:] == ask["messages"]
+    c.post("/v1/chat/completions", json={**ask, "cam_read": True}, headers={"X-CAM-Namespace": "other"})
+    assert mgr.sent[-1].text == ask["messages"]                               # another namespace knows nothing
+    monkeypatch.setenv("MSGL_CAM_AUTO", "1")
+    c.post("/generate", json={"prompt": "Tell me about Zephyrina's mother tongue", "max_tokens": 4})
+    assert "Klingon" in mgr.sent[-1].text and mgr.sent[-1].text.endswith("Tell me about Zephyrina's mother tongue")

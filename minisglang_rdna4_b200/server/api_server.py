@@ -82,6 +82,10 @@ class OpenAICompletionRequest(BaseModel):
     reasoning_max_tokens: Optional[int] = None
     reasoning_effort: Optional[str] = None
     # recursive self-aggregation: true = the server's defaults, or an object overriding n / k / t / ...
+    # the same three knobs in the shapes other APIs use: ``reasoning: {effort, max_tokens, enabled}``
+    # and ``thinking: true | {type: "enabled" | "disabled", budget_tokens}``; folded into the fields above
+    reasoning: Optional[Dict[str, Any]] = None
+    thinking: Union[bool, Dict[str, Any], None] = None
     rsa: Union[bool, Dict[str, Any], None] = None
     # associative memory: per-request override of the ambient read / write defaults (MSGL_CAM_AUTO,
     # MSGL_CAM_AUTO_WRITE); only meaningful when the server runs with MSGL_CAM=1
@@ -119,6 +123,27 @@ class OpenAICompletionRequest(BaseModel):
             raise ValueError("suffix is not supported")
         if self.best_of not in (None, 1):
             raise ValueError("best_of is not supported")
+        if isinstance(self.reasoning, dict):
+            r = self.reasoning
+            if self.reasoning_effort is None and isinstance(r.get("effort"), str):
+                self.reasoning_effort = r["effort"]
+            if self.reasoning_max_tokens is None and isinstance(r.get("max_tokens"), int):
+                self.reasoning_max_tokens = r["max_tokens"]
+            if self.enable_thinking is None and isinstance(r.get("enabled"), bool):
+                self.enable_thinking = r["enabled"]
+        if self.thinking is not None:
+            t = self.thinking
+            if isinstance(t, bool):
+                on, budget = t, None
+            else:
+                on = {"enabled": True, "disabled": False}.get(str(t.get("type", "")).lower())
+                budget = t.get("budget_tokens")
+                if on is None and "type" in t:
+                    raise ValueError("thinking.type must be `enabled` or `disabled`")
+            if self.enable_thinking is None and on is not None:
+                self.enable_thinking = on
+            if self.reasoning_max_tokens is None and isinstance(budget, int) and budget > 0:
+                self.reasoning_max_tokens = budget
         return self
 
     def resolved_max_tokens(self) -> int:

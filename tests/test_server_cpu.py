@@ -284,3 +284,22 @@ def test_rsa_requests_run_rollouts_aggregation_rounds_and_a_vote():
                                                  "reasoning_effort": "medium", "stream": True})
     assert out3.status_code == 200 and '"rsa"' in out3.text and "[DONE]" in out3.text
     assert sum(isinstance(s, TokenizeMsg) for s in mgr3.sent) == 4     # medium: n = 2, t = 2
+
+
+def test_reasoning_and_thinking_aliases_fold_into_the_canonical_fields():
+    from minisglang_rdna4_b200.server.api_server import OpenAICompletionRequest as Req
+
+    msgs = [{"role": "user", "content": "q"}]
+    r = Req(messages=msgs, reasoning={"effort": "high", "max_tokens": 256, "enabled": True})
+    assert (r.reasoning_effort, r.reasoning_max_tokens, r.enable_thinking) == ("high", 256, True)
+    r = Req(messages=msgs, thinking={"type": "enabled", "budget_tokens": 512})
+    assert (r.enable_thinking, r.reasoning_max_tokens) == (True, 512)
+    r = Req(messages=msgs, thinking=False, reasoning_max_tokens=64)
+    assert r.enable_thinking is False and r.reasoning_max_tokens == 64
+    r = Req(messages=msgs, enable_thinking=True, thinking={"type": "disabled"})   # the explicit field wins
+    assert r.enable_thinking is True
+    with pytest.raises(ValueError):
+        Req(messages=msgs, thinking={"type": "sometimes"})
+    c, mgr = _client(lambda m: _words(m.uid, ["a"]))
+    c.post("/v1/chat/completions", json={"messages": msgs, "thinking": {"type": "disabled"}})
+    assert mgr.sent[0].chat_template_kwargs == {"enable_thinking": False}

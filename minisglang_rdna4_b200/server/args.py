@@ -79,12 +79,14 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
-    ns = build_parser().parse_args(argv)
-    if ns.print_env:
+    import sys
+
+    if "--print-env" in (argv if argv is not None else sys.argv[1:]):   # needs no model
         from ..env import ENV
 
         print(ENV.describe())
         raise SystemExit(0)
+    ns = build_parser().parse_args(argv)
     if ns.enable_ep and ns.tp_size * ns.dp_size == 1:
         raise SystemExit("--enable-ep needs --tp-size > 1 or --dp-size > 1")
     kwargs = json.loads(ns.chat_template_kwargs) if ns.chat_template_kwargs else None

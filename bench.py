@@ -22,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -51,6 +52,9 @@ def parse_args():
     ap.add_argument("--max-extend", type=int, default=8192)
     ap.add_argument("--memory-ratio", type=float, default=0.85)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-matched", action="store_true",
+                    help="skip the extra bf16-weights / bf16-KV run of this repository that is reported beside "
+                         "the quantised number for a like-for-like ratio against the bf16 reference arm")
     return ap.parse_args()
 
 
@@ -113,28 +117,92 @@ class ClockSampler:
         return out
 
 
+def _reference_attempt(args, backend: str, small: bool, timeout: float):
+    """One run of ``baseline/reference_arm.py`` (the unmodified reference through its own
+    ``minisgl.llm.LLM``) in a child process that sees the reference package only."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--gpus", str(args.gpus),
+           "--model", args.model, "--attention-backend", backend, "--page-size", str(args.page_size),
+           "--max-extend", str(args.max_extend), "--memory-ratio", str(args.memory_ratio)]
+    if small:
+        cmd += ["--steps", "1", "--warmup", "1", "--requests", "8", "--in-min", "64", "--in-max", "128",
+                "--out-len", "8"]
+    else:
+        cmd += ["--steps", str(args.steps), "--warmup", str(args.warmup), "--requests", str(args.requests),
+                "--in-min", str(args.in_min), "--in-max", str(args.in_max), "--out-len", str(args.out_len)]
+    env = dict(os.environ, PYTHONPATH=ref_dir, MINISGL_TAIL_HIP="0")
+    env.pop("MSGL_BENCH_PROFILE", None)
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout, cwd=tempfile.gettempdir())
+    except subprocess.TimeoutExpired:
+        return None, f"attention backend {backend}: no result within {int(timeout)} s"
+    line = None
+    for ln in proc.stdout.splitlines():
+        if ln.startswith("{") and '"impl": "reference"' in ln:
+            line = ln
+    if proc.returncode == 0 and line is not None:
+        return json.loads(line), None
+    err = [ln for ln in proc.stderr.strip().splitlines() if ln.strip()]
+    sys.stderr.write(f"[reference arm, backend {backend}] rc={proc.returncode}\n" + "\n".join(err[-25:]) + "\n")
+    exc = [ln for ln in err if re.match(r"^[A-Za-z_.]+(Error|Exception|Exit)\b", ln)]
+    return None, f"attention backend {backend}: rc={proc.returncode}: " + ((exc or err or ["no output"])[-1])[:400]
+
+
 def run_reference(args) -> None:
     """The reference arm: the unmodified reference, installed under ``baseline/_ref``, through
-    its own offline API. Its layer package imports the out-of-tree gfx1201 HIP kernel
-    packages unconditionally, so on an NVIDIA box the import itself fails; the arm reports
-    that instead of substituting any code of this repository."""
+    its own offline API (``baseline/reference_arm.py``), with the knobs the reference documents
+    for a box without its gfx1201 HIP kernel packages (``MINISGL_TAIL_HIP=0``, torch sampler
+    fallback, its own attention back-end selector). The reference has no W4A8 / fp8-KV path on
+    NVIDIA GPUs, so this arm is bf16 and marks ``same_config: false``. Each back-end is first
+    tried on a few short requests; the first that works runs the named workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = None
     if not os.path.isdir(os.path.join(ref_dir, "minisgl")):
-        why = "the reference is not installed under baseline/_ref"
-    else:
-        probe = subprocess.run(
-            [sys.executable, "-c", "from minisgl.llm import LLM"], capture_output=True, text=True,
-            env=dict(os.environ, PYTHONPATH=ref_dir), timeout=600)
-        if probe.returncode != 0:
-            last = [ln for ln in probe.stderr.strip().splitlines() if ln.strip()][-1:]
-            why = ("the unmodified reference does not import on this box: " + (last[0] if last else "import failed")
-                   + " (its kernels are out-of-tree gfx1201 HIP packages; it has no NVIDIA path for W4A8 / fp8 KV)")
-        else:
-            why = ("the reference imports, but it has no quantised (W4A8 MXFP4, fp8 KV) execution path on NVIDIA "
-                   "GPUs for the named configuration")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}))
+        return
+    if world > 1:
+        # every rank runs its own child with the launcher's RANK / WORLD_SIZE / LOCAL_RANK
+        result, why = _reference_attempt(args, os.environ.get("MSGL_REF_BACKEND", "fi"), False, 1500)
+        if rank == 0:
+            print(json.dumps(result if result is not None else {"impl": "reference", "unavailable": why}))
+        return
+    reasons = []
+    t_start = time.time()
+    for backend in ("auto", "fi"):
+        probe, why = _reference_attempt(args, backend, True, 420)
+        if probe is None:
+            reasons.append(why)
+            continue
+        left = max(300.0, 1650.0 - (time.time() - t_start))
+        result, why = _reference_attempt(args, backend, False, left)
+        if result is not None:
+            print(json.dumps(result))
+            return
+        reasons.append(why)
+    print(json.dumps({"impl": "reference", "unavailable": "the unmodified reference (MINISGL_TAIL_HIP=0, bf16) did not "
+                      "complete on this box: " + " | ".join(reasons)}))
+
+
+def run_matched_bf16(args):
+    """This repository on the reference arm's precision (bf16 weights, bf16 KV), same workload,
+    in a child process before the main engine takes the device memory."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--gpus", "1", "--quant", "none", "--kv", "bf16",
+           "--steps", "2", "--warmup", "3", "--no-matched", "--model", args.model,
+           "--requests", str(args.requests), "--in-min", str(args.in_min), "--in-max", str(args.in_max),
+           "--out-len", str(args.out_len), "--page-size", str(args.page_size), "--max-extend", str(args.max_extend),
+           "--memory-ratio", str(args.memory_ratio)] + (["--no-graph"] if args.no_graph else [])
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+        for ln in proc.stdout.splitlines():
+            if ln.startswith("{") and '"metric"' in ln:
+                d = json.loads(ln)
+                return {"tok_s": d["value"], "e2e_tok_s": d["e2e"]["value"], "dtype": "bf16 weights, bf16 KV",
+                        "p50_tpot_ms": d["config"]["p50_tpot_ms"], "steps": d["steps"], "warmup": d["warmup"]}
+        return {"error": (proc.stderr.strip().splitlines() or ["no result line"])[-1][:300]}
+    except Exception as exc:  # the headline run does not depend on this one
+        return {"error": repr(exc)[:300]}
 
 
 def main() -> None:
@@ -142,6 +210,11 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args)
         return
+
+    matched = None
+    if (args.gpus == 1 and args.quant != "none" and not args.no_matched
+            and not os.environ.get("MSGL_BENCH_PROFILE")):
+        matched = run_matched_bf16(args)
 
     import numpy as np
     import torch
@@ -288,6 +361,7 @@ def main() -> None:
                 "p50_ttft_ms": last["ttft_p50"], "p50_tpot_ms": last["tpot_p50"],
                 "prefill_ms_per_pass": last["prefill_ms"], "engine_steps_per_pass": last["steps"],
                 "prompt_tokens_per_pass": last["in_tokens"], "cuda_graphs": not args.no_graph,
+                "matched_bf16": matched,
             },
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": last["h2d"],
                     "d2h_bytes_per_step": last["d2h"], "ms_per_pass": wall_ms / args.steps},
@@ -297,11 +371,17 @@ def main() -> None:
         print(json.dumps(line))
     sys.stdout.flush()
     llm.shutdown()
-    # The result line is out and every rank has passed the shutdown barrier. Leave without the
-    # interpreter's teardown: destroying NCCL communicators that captured graphs still reference
-    # has been seen to block one rank forever, which would stall the launcher.
+    if world == 1:
+        return  # normal interpreter exit
+    # Multi-rank: every rank has passed the shutdown barrier. Run the exit handlers now, then leave
+    # without the interpreter's module teardown: destroying NCCL communicators that captured graphs
+    # still reference has been seen to block one rank forever, which would stall the launcher.
     sys.stderr.flush()
-    os._exit(0)
+    import atexit
+    try:
+        atexit._run_exitfuncs()
+    finally:
+        os._exit(0)
 
 
 if __name__ == "__main__":

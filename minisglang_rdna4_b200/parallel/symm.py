@@ -78,6 +78,15 @@ class SymmetricHeap:
         self.ptrs, self.local = [], None
 
 
+def agree_status(local_code: int, cpu_group, world: int) -> int:
+    """MAX of the ranks' status words over the (gloo) control group."""
+    if world <= 1 or cpu_group is None:
+        return local_code
+    t = torch.tensor([int(local_code)], dtype=torch.int64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=cpu_group)
+    return int(t.item())
+
+
 class SymmetricCollectives:
     name = "symm"
 
@@ -186,10 +195,16 @@ class SymmetricCollectives:
         K._count("wait_ready", "wait_flags_kernel")
 
     def check_health(self) -> bool:
-        code = int(lib().msgl_comm_status(1))
+        """Collective over the CPU group: every rank of the group calls this on the same step.
+        A bounded wait can run out on one rank only (the late peer finds its flags already
+        raised), so the ranks agree on the worst status before any of them leaves the fused
+        path; they then all switch to NCCL on the same step and their NCCL call sequences stay
+        aligned."""
+        code = agree_status(int(lib().msgl_comm_status(1)), self.cpu_group, self.world)
         if code != 0:
             self.healthy = False
-            logger.warning("peer-memory collective timed out (status %d): falling back to NCCL", code)
+            logger.warning("peer-memory collective timed out on some rank (status %d): all ranks fall back to NCCL",
+                           code)
         return self.healthy
 
     def close(self) -> None:

@@ -62,6 +62,10 @@ class PrefillAdder:
         if pending.chunked is not None:
             prev = pending.chunked
             slot, handle, cached = prev.table_idx, prev.cache_handle, prev.cached_len
+            # an admitted request still owes pages for the rest of its prompt and for its output:
+            # requests admitted behind it in this step must not count that room as theirs
+            # (python/minisgl/scheduler/prefill.py:160 reserves remain + output for every request)
+            self.reserved += pending.input_len - cached + pending.output_len
         else:
             if self.table.available_size == 0:
                 return None

@@ -372,12 +372,16 @@ class Scheduler:
             self.send_result(replies)
 
     def _check_comm_health(self) -> None:
-        """Every few steps read the status word of the peer-memory collectives (the host has just
-        synchronised with the device anyway). A wait that ran out means a peer is missing or slow:
-        the fused path is switched off for the rest of the process and decode leaves its captured
-        graphs, which contain the fused kernels, for eager steps on the NCCL path. A peer that is
-        really gone is then caught by the process-group timeout and the crash watchdog."""
-        if self.config.tp_size == 1 or self.stats["steps"] % 16 != 0:
+        """Every ``MSGL_COMM_HEALTH_STEPS`` steps (the host has just synchronised with the device
+        anyway) the ranks of the tensor-parallel group agree, over the CPU group, on the worst
+        status word of the peer-memory collectives. A wait that ran out on any rank means a peer
+        is missing or slow: every rank leaves the fused path on this same step, decode leaves its
+        captured graphs (which contain the fused kernels) for eager steps on the NCCL path, and the
+        requests that were running are ended with an error, because steps since the last clean
+        check may have summed incomplete partials. A peer that is really gone is then caught by
+        the process-group timeout and the crash watchdog."""
+        every = max(1, ENV.COMM_HEALTH_STEPS.value)
+        if self.config.tp_size == 1 or self.stats["steps"] % every != 0:
             return
         from ..parallel.comm import get_comm
 
@@ -386,6 +390,19 @@ class Scheduler:
             if check is not None and getattr(impl, "healthy", True) and not check():
                 logger.warning("peer-memory collectives disabled after a device-side timeout")
                 self.engine.graph_runner = None
+                self._fail_running("a collective timed out; the request was ended because its state may be incomplete")
+
+    def _fail_running(self, why: str) -> None:
+        replies = []
+        for req in list(self.decode.running.values()):
+            if req.finished:
+                continue
+            req.finished, req.finish_reason = True, "error"
+            replies.append(DetokenizeMsg(req.uid, 0, True, "error", error=why))
+            self._free_req_resources(req, insert=False)
+        self.decode.filter_finished()
+        if replies:
+            self.send_result(replies)
 
     def _free_req_resources(self, req: Req, insert: bool) -> None:
         if req.resources_freed:  # several paths can reach a request; free exactly once

@@ -8,6 +8,7 @@ positions are fed again, so only the length bookkeeping rolls back.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import List
 
 import numpy as np
@@ -21,16 +22,58 @@ from ..spec.accept import accept_greedy, accept_rejection_sampling, eos_truncate
 from ..spec.width import AdaptiveWidth
 
 
+def _engine_stream(eng):
+    """Everything that touches the verify forward's results (logits, auxiliary hidden states,
+    token pool, KV pool) is issued on the engine's stream: that stream does not synchronise
+    with the default stream, so work left on the default stream could read the logits before
+    the forward has produced them, and the next forward could read the token pool before the
+    commit has landed."""
+    if eng.device.type == "cuda":
+        return torch.cuda.stream(eng.stream)
+    return contextlib.nullcontext()
+
+
+def req_spec_ok(sched, req: Req) -> bool:
+    """May this request take a speculative step? The verify step accepts by arg-max (or, with
+    ``MSGL_SPEC_SAMPLED``, by rejection sampling at a plain temperature); it applies no grammar
+    mask, reasoning / tool-call gate, penalty, top-k / top-p / min-p filter, seed or logprob
+    capture. A request that needs any of those decodes one token at a time through the normal
+    sampler (python/minisgl/scheduler/scheduler.py:3276-3293)."""
+    sp = req.sampling_params
+    if sched._needs_constraints(req) or sp.grammar is not None or sp.has_penalty or sp.logprobs > 0:
+        return False
+    if sp.is_greedy:
+        return True
+    if not ENV.SPEC_SAMPLED.value:
+        return False
+    return sp.top_k <= 0 and sp.top_p >= 1.0 and sp.min_p <= 0.0 and sp.seed is None
+
+
+def _plain_decode_step(sched) -> None:
+    batch = sched.decode.schedule_next_batch()
+    if batch is None:
+        return
+    ongoing = sched._forward(batch)
+    sched._process_last_data(ongoing)
+    proposer = sched.proposer
+    if proposer is not None and hasattr(proposer, "on_plain_step"):
+        proposer.on_plain_step(ongoing.sampled)
+
+
 def spec_decode_step(sched) -> None:
     proposer = sched.proposer
     reqs: List[Req] = sorted(sched.decode.running.values(), key=lambda r: r.uid)
     if not reqs:
         return
     limit = ENV.SPEC_MAX_BS.value or proposer.max_batch
-    if len(reqs) > limit:
-        batch = sched.decode.schedule_next_batch()
-        sched._process_last_data(sched._forward(batch))
+    if len(reqs) > limit or not all(req_spec_ok(sched, r) for r in reqs):
+        _plain_decode_step(sched)
         return
+    with _engine_stream(sched.engine):
+        _spec_decode_step_on_stream(sched, proposer, reqs)
+
+
+def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
     if getattr(proposer, "tree_width", 1) > 1 and hasattr(proposer, "propose_paths") \
             and not getattr(proposer, "capture_layers", None):
         _tree_decode_step(sched, reqs)
@@ -52,11 +95,7 @@ def spec_decode_step(sched) -> None:
     if flat_idx:
         idx = torch.tensor(flat_idx, dtype=torch.int64)
         tok = torch.tensor(flat_tok, dtype=torch.int32)
-        if eng.device.type == "cuda":
-            with torch.cuda.stream(eng.stream):
-                eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
-        else:
-            eng.token_pool.view(-1)[idx] = tok
+        eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
 
     batch = Batch(reqs=reqs, phase="decode")
     batch.spec_verify = True
@@ -185,11 +224,7 @@ def _tree_decode_step(sched, reqs: List[Req]) -> None:
     if flat_idx:
         idx = torch.tensor(flat_idx, dtype=torch.int64)
         tok = torch.tensor(flat_tok, dtype=torch.int32)
-        if eng.device.type == "cuda":
-            with torch.cuda.stream(eng.stream):
-                eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
-        else:
-            eng.token_pool.view(-1)[idx] = tok
+        eng.token_pool.view(-1)[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
 
     batch = Batch(reqs=reqs, phase="decode")
     batch.spec_verify = True

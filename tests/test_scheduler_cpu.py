@@ -116,3 +116,25 @@ def test_tracing_hooks(monkeypatch, tmp_path):
         np.zeros(4).sum()
     prof.close()
     assert trace.exists() and trace.stat().st_size > 0
+
+
+def test_a_chunked_prompt_keeps_its_reservation_against_requests_behind_it():
+    """A prompt prefilled in pieces still owes pages for the rest of its prompt and its output.
+    A short request queued behind it must wait instead of taking that room (which would end in
+    an out-of-pages error inside the step planner)."""
+    pre, cache, table, dec = _mgr(pages=8, ps=16)   # 128 tokens
+    pre.add_one_req(1, torch.arange(90, dtype=torch.int32), SamplingParams(max_tokens=20))
+    pre.add_one_req(2, torch.arange(10, dtype=torch.int32) + 500, SamplingParams(max_tokens=10))
+    batch, _ = pre.schedule_next_batch(64)
+    assert isinstance(batch.reqs[0], ChunkedReq) and len(batch.reqs) == 1
+    # the step planner takes the pages of the first chunk
+    cache.page_table[batch.reqs[0].table_idx, :4] = cache._take(4)
+    batch.reqs[0].cached_len = batch.reqs[0].device_len
+    batch, _ = pre.schedule_next_batch(64)
+    assert [r.uid for r in batch.reqs] == [1] and not isinstance(batch.reqs[0], ChunkedReq)
+    assert [p.uid for p in pre.pending] == [2]     # 26 + 20 owed by request 1, 20 wanted: 66 > 64 free
+    # end to end on a pool that holds one of them at a time: both finish, nothing raises
+    llm = LLM(model_config=tiny_llama_config(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=4,
+              num_page_override=8, max_extend_tokens=64, cache_type="naive")
+    outs = llm.generate([list(range(90)), list(range(500, 510))], SamplingParams(max_tokens=20, ignore_eos=True))
+    assert [len(o.token_ids) for o in outs] == [20, 20]

@@ -178,3 +178,35 @@ def test_tree_verification_is_exact_and_follows_the_right_branch():
     short.proposer = _TreeOracle(3, {0: want[0]})
     out = short.generate([prompts[0]], SamplingParams(max_tokens=7, ignore_eos=True))[0]
     assert out.token_ids == want[0][:7] and out.finish_reason == "length"
+
+
+def test_sampled_and_constrained_requests_leave_the_speculative_path():
+    """A request with temperature > 0 is not silently made greedy by the verify arg-max, and a
+    grammar holds with a proposer configured: both decode through the normal sampler."""
+    import json
+
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+    from minisglang_rdna4_b200.tokenizer import ByteTokenizer
+
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 1024, (24,), generator=g).tolist()
+    greedy = _llm().generate([prompt], SamplingParams(max_tokens=24, ignore_eos=True))[0].token_ids
+    spec = _llm(spec_algorithm="ngram", spec_num_draft=4)
+    spec.proposer = _Oracle(4, {0: greedy, 1: greedy})
+    hot = spec.generate([prompt], SamplingParams(temperature=1.5, max_tokens=24, ignore_eos=True))[0].token_ids
+    assert hot != greedy                       # sampled, not the verify arg-max
+    assert spec.stats["spec_steps"] == 0       # never took a speculative step
+    again = spec.generate([prompt], SamplingParams(max_tokens=24, ignore_eos=True))[0].token_ids
+    assert again == greedy and spec.stats["spec_steps"] > 0
+
+    cfg = ModelConfig(num_layers=1, num_qo_heads=2, num_kv_heads=1, head_dim=32, hidden_size=64, vocab_size=260,
+                      intermediate_size=128, rms_norm_eps=1e-6, rotary_config=RotaryConfig(32, 32, 512, 1e4),
+                      model_type="llama", torch_dtype="float32", max_position_embeddings=512, eos_token_ids=(257,))
+    llm = LLM(model_config=cfg, use_dummy_weight=True, device="cpu", page_size=16, max_running_req=4,
+              num_page_override=64, seed=3, spec_algorithm="ngram", spec_num_draft=3)
+    schema = json.dumps({"type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "boolean"}},
+                         "required": ["a", "b"], "additionalProperties": False})
+    out = llm.generate([list(b"give me json:")], SamplingParams(max_tokens=60, grammar=schema, temperature=0.8,
+                                                              top_k=40))[0]
+    obj = json.loads(ByteTokenizer().decode(out.token_ids))
+    assert isinstance(obj["a"], int) and isinstance(obj["b"], bool) and llm.stats["spec_steps"] == 0

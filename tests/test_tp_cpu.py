@@ -115,3 +115,34 @@ def test_dp2_expert_parallel_lockstep_matches_single_replica():
             assert p.exitcode == 0
     assert got[0] + got[1] == want
     assert calls[0] == calls[1] > 0   # both replicas issued the same number of exchanges
+
+
+def _health_worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+
+    from minisglang_rdna4_b200.parallel.symm import agree_status
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # step 1: nobody timed out; step 2: a wait ran out on rank 1 only
+    clean = agree_status(0, dist.group.WORLD, world)
+    bad = agree_status(3 if rank == 1 else 0, dist.group.WORLD, world)
+    out_q.put((rank, clean, bad))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_agree_on_a_collective_timeout_seen_by_one_rank():
+    """The status word of the peer-memory collectives is local to a rank; the health check takes
+    the MAX over the control group so that every rank leaves the fused path on the same step."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 28100 + os.getpid() % 1000
+    procs = [ctx.Process(target=_health_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, 0, 3), (1, 0, 3)]

@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--max-extend", type=int, default=8192)
     ap.add_argument("--memory-ratio", type=float, default=0.85)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling only: cut the model to this many layers (the result line is marked reduced)")
     ap.add_argument("--no-matched", action="store_true",
                     help="skip the extra bf16-weights / bf16-KV run of this repository that is reported beside "
                          "the quantised number for a like-for-like ratio against the bf16 reference arm")
@@ -231,8 +233,15 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
 
+    model_config = None
+    if args.layers > 0:
+        import dataclasses
+
+        from minisglang_rdna4_b200.models.config import NAMED_CONFIGS
+
+        model_config = dataclasses.replace(NAMED_CONFIGS[args.model](), num_layers=args.layers)
     llm = LLM(
-        model_path=args.model, use_dummy_weight=True, quantization=None if args.quant == "none" else args.quant,
+        model_path=args.model, model_config=model_config, use_dummy_weight=True, quantization=None if args.quant == "none" else args.quant,
         kv_cache_dtype=args.kv, tp_size=world, tp_rank=rank, page_size=args.page_size,
         max_running_req=args.requests, max_extend_tokens=args.max_extend, memory_ratio=args.memory_ratio,
         seed=1, cuda_graph_max_bs=(-1 if args.no_graph else None), max_seq_len_override=4096,
@@ -362,6 +371,7 @@ def main() -> None:
                 "prefill_ms_per_pass": last["prefill_ms"], "engine_steps_per_pass": last["steps"],
                 "prompt_tokens_per_pass": last["in_tokens"], "cuda_graphs": not args.no_graph,
                 "matched_bf16": matched,
+                **({"reduced_layers": args.layers, "valid": False} if args.layers > 0 else {}),
             },
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": last["h2d"],
                     "d2h_bytes_per_step": last["d2h"], "ms_per_pass": wall_ms / args.steps},

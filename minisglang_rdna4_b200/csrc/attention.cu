@@ -99,6 +99,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 template <typename T, bool KV8, int D, int NWQ, int NWK, int STAGES>
 __global__ void __launch_bounds__(32 * (NWQ * NWK + 1))
 paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs args) {
+  pdl_enter();
   constexpr int NW = NWQ * NWK;
   constexpr int ESZ = KV8 ? 1 : 2;
   constexpr int RB = D * ESZ;                 // bytes per KV row
@@ -494,6 +495,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
 template <typename T, int D>
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse,
                                     T* __restrict__ out, int rows_heads, int splits) {
+  pdl_enter();
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (idx >= rows_heads) return;
   const int lane = threadIdx.x & 31;
@@ -538,6 +540,10 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 template <typename T, bool KV8, int D, int STAGES>
 __global__ void __launch_bounds__(64)
 paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs args) {
+  // This kernel starts once the kernel ahead of it (the one that writes this step's q and the
+  // newest token's K / V) has begun, which is after everything before THAT kernel has finished.
+  // So the step's tables and all older KV may be read at once; only q and the tile that holds
+  // position kv_len - 1 wait for pdl_wait().
   constexpr int ESZ = KV8 ? 1 : 2;
   constexpr int RB = D * ESZ;
   constexpr int PLANES = RB / 128;
@@ -589,7 +595,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
       const int32_t* bt = args.block_table + (size_t)b * args.bt_stride;
       int stage = 0;
       uint32_t phase = 0;
+      const int newest_tile = kv_len > 0 ? (kv_len - 1) / TK : 0;
+      bool waited = false;
       for (int t = 0; t < n_tiles; ++t) {
+        if (!waited && t_begin + t >= newest_tile) {
+          pdl_wait();
+          waited = true;
+        }
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 211)) break;
         mbar_expect_tx(full_bar(stage), STAGE_BYTES);
         const int first_page = (t_begin + t) * pages_per_tile;
@@ -617,6 +629,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
   }
 
   // ---------------------------------------------------------------------- consumer warp
+  pdl_enter();
   const int j = lane & 3, g = lane >> 2;
   const int mi = lane >> 3;
   // Q^T fragments (B operand): column n = g is head h*G + g
@@ -823,7 +836,7 @@ int launch_decode(const CUtensorMap& map, const AttnArgs& a, cudaStream_t stream
     configured = true;
   }
   dim3 grid(1, a.B * a.Hk, a.splits);
-  paged_decode_kernel<T, KV8, D, STAGES><<<grid, 64, smem, stream>>>(map, a);
+  msgl_launch(paged_decode_kernel<T, KV8, D, STAGES>, dim3(grid), dim3(64), smem, stream, map, a);
   MSGL_CHECK_LAUNCH("paged_decode");
   return MSGL_OK;
 }
@@ -843,7 +856,7 @@ int launch_attn(const CUtensorMap& map, const AttnArgs& a, int q_tiles, cudaStre
     configured = true;
   }
   dim3 grid(q_tiles, a.B * a.Hk, a.splits);
-  paged_attention_kernel<T, KV8, D, NWQ, NWK, STAGES><<<grid, 32 * (NW + 1), smem, stream>>>(map, a);
+  msgl_launch(paged_attention_kernel<T, KV8, D, NWQ, NWK, STAGES>, dim3(grid), dim3(32 * (NW + 1)), smem, stream, map, a);
   MSGL_CHECK_LAUNCH("paged_attention");
   return MSGL_OK;
 }
@@ -956,7 +969,7 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
     const int rows_heads = total_q * hq;
     const int warps = 4;
     const int blocks = (rows_heads + warps - 1) / warps;
-#define COMBINE(T, D) attn_combine_kernel<T, D><<<blocks, warps * 32, 0, stream>>>(a.ws_o, a.ws_lse, (T*)out, rows_heads, splits)
+#define COMBINE(T, D) msgl_launch(attn_combine_kernel<T, D>, dim3(blocks), dim3(warps * 32), 0, stream, a.ws_o, a.ws_lse, (T*)out, rows_heads, splits)
     if (dtype == MSGL_BF16) { if (head_dim == 128) COMBINE(__nv_bfloat16, 128); else COMBINE(__nv_bfloat16, 64); }
     else { if (head_dim == 128) COMBINE(__half, 128); else COMBINE(__half, 64); }
 #undef COMBINE

@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(256)
 kv_gather_kernel(const void* __restrict__ k_pool, const void* __restrict__ v_pool, T* __restrict__ kc,
                  T* __restrict__ vt, const int* __restrict__ blk_req, const int* __restrict__ req_info,
                  const int* __restrict__ block_table, int bt_stride, int Hk, int page_size, long long t_cap) {
+  pdl_enter();
   __shared__ __align__(16) T vs[64][kD + 8];
   const int t0 = blockIdx.x * 64, h = blockIdx.y;
   const int req = blk_req[t0 >> 7];
@@ -170,6 +171,7 @@ template <typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                        const __grid_constant__ CUtensorMap tma_v, const TcArgs args) {
+  pdl_enter();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t s_base = (raw + 1023u) & ~1023u;
@@ -443,7 +445,7 @@ int launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& m
     if (e != cudaSuccess) { msgl_set_error("prefill attention smem attribute", e); return MSGL_CUDA_ERROR; }
     configured = true;
   }
-  attn_prefill_tc_kernel<T><<<a.n_items * a.pairs, kTcThreads, TcSmem::bytes, stream>>>(mq, mk, mv, a);
+  msgl_launch(attn_prefill_tc_kernel<T>, dim3(a.n_items * a.pairs), dim3(kTcThreads), TcSmem::bytes, stream, mq, mk, mv, a);
   MSGL_CHECK_LAUNCH("attn_prefill_tc");
   return MSGL_OK;
 }
@@ -490,7 +492,7 @@ MSGL_API int msgl_attn_prefill_tc(const void* q, long long q_row_stride, void* o
   cudaGetSymbolAddress((void**)&status, g_attn_tc_status);
   const dim3 ggrid(t_pad / 64, hk);
 #define GATHER(T, F8)                                                                                              \
-  kv_gather_kernel<T, F8><<<ggrid, 256, 0, stream>>>(k_pool, v_pool, (T*)kc, (T*)vt, (const int*)blk_req,          \
+  msgl_launch(kv_gather_kernel<T, F8>, dim3(ggrid), dim3(256), 0, stream, k_pool, v_pool, (T*)kc, (T*)vt, (const int*)blk_req,          \
                                                      (const int*)req_info, (const int*)block_table, bt_stride, hk, \
                                                      page_size, t_cap)
   if (dtype == MSGL_BF16) { if (kv_fp8) GATHER(__nv_bfloat16, true); else GATHER(__nv_bfloat16, false); }

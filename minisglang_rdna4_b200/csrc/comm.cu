@@ -71,6 +71,7 @@ constexpr int kArThreads = 128;
 
 template <typename T, bool NORM, bool QUANT, int VPT>
 __global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) {
+  pdl_enter();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const int H = a.hidden;
@@ -191,9 +192,9 @@ __global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) 
 template <typename T, int VPT>
 void launch_ar_vpt(const ArArgs& a, cudaStream_t stream) {
   const bool norm = a.residual != nullptr, quant = a.out_q != nullptr;
-  if (norm && quant) ar_oneshot_kernel<T, true, true, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
-  else if (norm) ar_oneshot_kernel<T, true, false, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
-  else ar_oneshot_kernel<T, false, false, VPT><<<a.rows, kArThreads, 0, stream>>>(a);
+  if (norm && quant) msgl_launch(ar_oneshot_kernel<T, true, true, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
+  else if (norm) msgl_launch(ar_oneshot_kernel<T, true, false, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
+  else msgl_launch(ar_oneshot_kernel<T, false, false, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
 }
 
 template <typename T>
@@ -247,6 +248,7 @@ constexpr int kRsThreads = 128;
 
 template <typename T, bool QUANT, int VPT>
 __global__ void __launch_bounds__(kRsThreads) rs_norm_ag_kernel(const RsArgs a) {
+  pdl_enter();
   __shared__ float scratch[32];
   const int lrow = blockIdx.x;
   const int lblk = lrow >> 7;
@@ -338,6 +340,7 @@ __global__ void __launch_bounds__(kRsThreads) rs_norm_ag_kernel(const RsArgs a) 
 // are not a GEMM with its own per-block wait.
 __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t seq, unsigned long long wait_ns,
                                   int* status) {
+  pdl_enter();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     if ((int)(ld_acquire_sys(flags + i) - seq) >= 0) continue;
     const unsigned long long t0 = gtimer();
@@ -372,6 +375,7 @@ struct ArgmaxArgs {
 };
 
 __global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a) {
+  pdl_enter();
   __shared__ float s_val[8];
   __shared__ int s_idx[8];
   __shared__ uint2 s_peer[kMaxRanks];
@@ -431,8 +435,8 @@ __global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a
 
 template <typename T, int VPT>
 void launch_rs_vpt(const RsArgs& a, int owned_rows, bool quant, cudaStream_t stream) {
-  if (quant) rs_norm_ag_kernel<T, true, VPT><<<owned_rows, kRsThreads, 0, stream>>>(a);
-  else rs_norm_ag_kernel<T, false, VPT><<<owned_rows, kRsThreads, 0, stream>>>(a);
+  if (quant) msgl_launch(rs_norm_ag_kernel<T, true, VPT>, dim3(owned_rows), dim3(kRsThreads), 0, stream, a);
+  else msgl_launch(rs_norm_ag_kernel<T, false, VPT>, dim3(owned_rows), dim3(kRsThreads), 0, stream, a);
 }
 
 template <typename T>
@@ -570,7 +574,7 @@ MSGL_API int msgl_argmax_exchange(const void* logits, long long ld, int rows, in
   a.status = status;
   a.rank = rank; a.nranks = nranks; a.max_rows = max_rows;
   a.wait_ns = (unsigned long long)wait_us * 1000ull;
-  argmax_exchange_kernel<<<rows, 256, 0, stream>>>(a);
+  msgl_launch(argmax_exchange_kernel, dim3(rows), dim3(256), 0, stream, a);
   MSGL_CHECK_LAUNCH("argmax_exchange");
   return MSGL_OK;
 }
@@ -579,7 +583,7 @@ MSGL_API int msgl_wait_flags(const void* flags, int n, unsigned int seq, long lo
   if (n <= 0) return MSGL_OK;
   int* status = nullptr;
   cudaGetSymbolAddress((void**)&status, g_comm_status);
-  wait_flags_kernel<<<1, 256, 0, stream>>>((const uint32_t*)flags, n, seq, (unsigned long long)wait_us * 1000ull,
+  msgl_launch(wait_flags_kernel, dim3(1), dim3(256), 0, stream, (const uint32_t*)flags, n, seq, (unsigned long long)wait_us * 1000ull,
                                            status);
   MSGL_CHECK_LAUNCH("wait_flags");
   return MSGL_OK;

@@ -117,7 +117,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return warp_max(r);
 }
 
+// Programmatic dependent launch. Every kernel of this library starts with pdl_wait() before it
+// touches global memory that an earlier kernel of the stream may still be writing (or reading),
+// and raises pdl_trigger() early, so that the next kernel of the stream is scheduled while this
+// one still runs: its launch latency and its prologue (barrier initialisation, tensor-memory
+// allocation, descriptor prefetch) overlap this kernel's tail. In a kernel launched without the
+// attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_wait();
+  pdl_trigger();
+}
+
 }  // namespace msgl
+
+// Host side: launches go through msgl_launch, which adds the programmatic-stream-serialization
+// attribute unless msgl_set_pdl(0) switched it off. The kernel argument list must be complete
+// (default arguments do not exist behind a function pointer).
+bool msgl_pdl_enabled();
+template <typename... P, typename... A>
+inline cudaError_t msgl_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               A&&... args) {
+  static_assert(sizeof...(P) == sizeof...(A), "msgl_launch: pass every kernel argument");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = msgl_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
 
 // Host side: remember the last CUDA error text for msgl_last_error().
 void msgl_set_error(const char* where, cudaError_t err);

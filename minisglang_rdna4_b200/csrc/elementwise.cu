@@ -20,11 +20,21 @@ void msgl_set_error(const char* where, cudaError_t err) {
 void msgl_set_error_text(const char* text) { g_last_error = text; }
 MSGL_API const char* msgl_last_error() { return g_last_error.c_str(); }
 
+static int g_pdl = 1;
+bool msgl_pdl_enabled() { return g_pdl != 0; }
+// Programmatic dependent launch of every kernel of the library: 1 on (default), 0 off.
+MSGL_API int msgl_set_pdl(int on) {
+  const int prev = g_pdl;
+  g_pdl = on;
+  return prev;
+}
+
 // ------------------------------------------------------------------------------------------
 // embedding: out[i, :] = (start <= ids[i] < start + len) ? W[ids[i] - start, :] : 0
 // ------------------------------------------------------------------------------------------
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* __restrict__ w,
                                  uint4* __restrict__ out, int row_vecs, int start, int len) {
+  pdl_enter();
   int row = blockIdx.x;
   int id = ids[row] - start;
   bool inside = id >= 0 && id < len;
@@ -40,7 +50,7 @@ MSGL_API int msgl_embedding(const void* ids, const void* w, void* out, int rows,
   if (rows == 0) return MSGL_OK;
   int vecs = hidden_bytes / 16;
   int threads = vecs < 256 ? ((vecs + 31) / 32) * 32 : 256;
-  embedding_kernel<<<rows, threads, 0, stream>>>((const int32_t*)ids, (const uint4*)w, (uint4*)out, vecs,
+  msgl_launch(embedding_kernel, dim3(rows), dim3(threads), 0, stream, (const int32_t*)ids, (const uint4*)w, (uint4*)out, vecs,
                                                  start, len);
   MSGL_CHECK_LAUNCH("embedding");
   return MSGL_OK;
@@ -63,6 +73,7 @@ __global__ void __launch_bounds__(kRowThreads) rms_norm_kernel(const T* __restri
                                                                float* __restrict__ out_scale, int hidden, float eps,
                                                                float w_offset, int planes = 0,
                                                                size_t plane_stride = 0) {
+  pdl_enter();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const T* xr = x + (size_t)row * hidden;
@@ -137,8 +148,8 @@ static void launch_rms_vpt(const void* x, void* residual, const void* w, void* o
                            int rows, int hidden, float eps, float off, cudaStream_t s) {
   const bool add = residual != nullptr, quant = out_q != nullptr;
 #define RMS_LAUNCH(A, Q)                                                                                    \
-  rms_norm_kernel<T, A, Q, VPT><<<rows, kRowThreads, 0, s>>>((const T*)x, (T*)residual, (const T*)w, (T*)out, \
-                                                            (uint8_t*)out_q, (float*)out_scale, hidden, eps, off)
+  msgl_launch(rms_norm_kernel<T, A, Q, VPT>, dim3(rows), dim3(kRowThreads), 0, s, (const T*)x, (T*)residual, (const T*)w, (T*)out, \
+                                                            (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, 0, (size_t)0)
   if (add && quant) RMS_LAUNCH(true, true);
   else if (add) RMS_LAUNCH(true, false);
   else if (quant) RMS_LAUNCH(false, true);
@@ -168,11 +179,9 @@ static void launch_rms_planes_vpt(const void* x, int planes, void* residual, con
                                   void* out_scale, int rows, int hidden, float eps, float off, cudaStream_t s) {
   const size_t stride = (size_t)rows * hidden;
   if (out_q != nullptr)
-    rms_norm_kernel<T, true, true, VPT, true><<<rows, kRowThreads, 0, s>>>(
-        (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
+    msgl_launch(rms_norm_kernel<T, true, true, VPT, true>, dim3(rows), dim3(kRowThreads), 0, s, (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
   else
-    rms_norm_kernel<T, true, false, VPT, true><<<rows, kRowThreads, 0, s>>>(
-        (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
+    msgl_launch(rms_norm_kernel<T, true, false, VPT, true>, dim3(rows), dim3(kRowThreads), 0, s, (const T*)x, (T*)residual, (const T*)w, (T*)out, (uint8_t*)out_q, (float*)out_scale, hidden, eps, off, planes, stride);
 }
 
 template <typename T>
@@ -240,6 +249,7 @@ __device__ __forceinline__ float act_fn(float g, int kind) {
 template <typename T>
 __global__ void act_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, size_t total_vecs,
                                int kind) {
+  pdl_enter();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total_vecs) return;
   int vecs_per_row = inter / 8;
@@ -259,6 +269,7 @@ __global__ void __launch_bounds__(THREADS) act_mul_quant_kernel(const T* __restr
                                                                     uint8_t* __restrict__ out_q,
                                                                     float* __restrict__ out_scale, int inter,
                                                                     int kind) {
+  pdl_enter();
   __shared__ float scratch[32];
   const int row = blockIdx.x;
   const T* g = x + (size_t)row * 2 * inter;
@@ -297,7 +308,7 @@ static int launch_act_quant(const void* x, void* out_q, void* out_scale, int row
   const int threads = wide ? 512 : kRowThreads;
   const int vpt = (inter / 8 + threads - 1) / threads;
 #define ACT_LAUNCH(V, TH) \
-  act_mul_quant_kernel<T, V, TH><<<rows, TH, 0, s>>>((const T*)x, (uint8_t*)out_q, (float*)out_scale, inter, kind)
+  msgl_launch(act_mul_quant_kernel<T, V, TH>, dim3(rows), dim3(TH), 0, s, (const T*)x, (uint8_t*)out_q, (float*)out_scale, inter, kind)
   if (wide) {
     if (vpt <= 1) ACT_LAUNCH(1, 512);
     else if (vpt <= 2) ACT_LAUNCH(2, 512);
@@ -337,10 +348,10 @@ MSGL_API int msgl_act_and_mul(const void* x, void* out, void* out_q, void* out_s
     int threads = 256;
     unsigned blocks = (unsigned)((vecs + threads - 1) / threads);
     if (dtype == MSGL_BF16)
-      act_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+      msgl_launch(act_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
                                                                     inter, vecs, kind);
     else if (dtype == MSGL_F16)
-      act_mul_kernel<__half><<<blocks, threads, 0, stream>>>((const __half*)x, (__half*)out, inter, vecs, kind);
+      msgl_launch(act_mul_kernel<__half>, dim3(blocks), dim3(threads), 0, stream, (const __half*)x, (__half*)out, inter, vecs, kind);
     else
       return MSGL_BAD_ARG;
   } else {
@@ -360,6 +371,7 @@ MSGL_API int msgl_act_and_mul(const void* x, void* out, void* out_q, void* out_s
 template <typename T>
 __global__ void quant_group_kernel(const T* __restrict__ x, uint8_t* __restrict__ out_q,
                                    float* __restrict__ out_scale, int group, size_t total_groups) {
+  pdl_enter();
   // one warp per group; groups are contiguous runs of `group` elements (group % 8 == 0)
   const size_t gidx = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gidx >= total_groups) return;
@@ -391,10 +403,10 @@ MSGL_API int msgl_quant_fp8(const void* x, void* out_q, void* out_scale, int row
   int warps = 8;
   unsigned blocks = (unsigned)((total + warps - 1) / warps);
   if (dtype == MSGL_BF16)
-    quant_group_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out_q,
+    msgl_launch(quant_group_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)x, (uint8_t*)out_q,
                                                                         (float*)out_scale, group, total);
   else if (dtype == MSGL_F16)
-    quant_group_kernel<__half><<<blocks, warps * 32, 0, stream>>>((const __half*)x, (uint8_t*)out_q,
+    msgl_launch(quant_group_kernel<__half>, dim3(blocks), dim3(warps * 32), 0, stream, (const __half*)x, (uint8_t*)out_q,
                                                                  (float*)out_scale, group, total);
   else
     return MSGL_BAD_ARG;

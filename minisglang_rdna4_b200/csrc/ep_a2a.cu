@@ -69,6 +69,7 @@ template <typename T>
 __global__ void ep_dispatch_kernel(EpBuffers b, const T* __restrict__ x, const int32_t* __restrict__ topk_ids,
                                    int32_t* __restrict__ send_slot, uint32_t* __restrict__ state, int tokens, int k,
                                    int experts_per_rank) {
+  pdl_enter();
   __shared__ int s_slot[16];
   __shared__ int s_dst[16];
   const int t = blockIdx.x;
@@ -128,6 +129,7 @@ __global__ void ep_dispatch_kernel(EpBuffers b, const T* __restrict__ x, const i
 // grid = R * ceil(cap/256); expert_ids [R*cap] <- local expert id or -1
 __global__ void ep_recv_prepare_kernel(EpBuffers b, int32_t* __restrict__ expert_ids, const uint32_t* __restrict__ seq_ptr,
                                        unsigned long long limit_ns) {
+  pdl_enter();
   const int blocks_per_src = (b.cap + 255) / 256;
   const int src = blockIdx.x / blocks_per_src;
   const int pos = (blockIdx.x % blocks_per_src) * 256 + threadIdx.x;
@@ -148,6 +150,7 @@ __global__ void ep_recv_prepare_kernel(EpBuffers b, int32_t* __restrict__ expert
 template <typename T>
 __global__ void ep_return_kernel(EpBuffers b, const T* __restrict__ y_sorted, const int32_t* __restrict__ pair_row,
                                  uint32_t* __restrict__ state, const uint32_t* __restrict__ seq_ptr) {
+  pdl_enter();
   const int idx = blockIdx.x;           // src * cap + pos
   const int src = idx / b.cap, pos = idx % b.cap;
   const int row = pair_row[idx];
@@ -175,6 +178,7 @@ template <typename T>
 __global__ void ep_combine_kernel(EpBuffers b, const float* __restrict__ topk_w, const int32_t* __restrict__ send_slot,
                                   T* __restrict__ out, const uint32_t* __restrict__ seq_ptr, int k,
                                   unsigned long long limit_ns) {
+  pdl_enter();
   const int t = blockIdx.x;
   if (threadIdx.x < b.nranks) {
     const uint32_t* flag = reinterpret_cast<const uint32_t*>(b.base[b.rank] + b.off_ret_flag) + threadIdx.x;
@@ -230,11 +234,11 @@ MSGL_API int msgl_ep_dispatch(void* const* bases, int rank, int nranks, int cap,
   if (tokens == 0) return MSGL_BAD_ARG;   // every rank must take part: pad to at least one token
   EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
   if (dtype == MSGL_BF16)
-    ep_dispatch_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(b, (const __nv_bfloat16*)x, (const int32_t*)topk_ids,
+    msgl_launch(ep_dispatch_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, b, (const __nv_bfloat16*)x, (const int32_t*)topk_ids,
                                                                   (int32_t*)send_slot, (uint32_t*)state, tokens, k,
                                                                   experts_per_rank);
   else if (dtype == MSGL_F16)
-    ep_dispatch_kernel<__half><<<tokens, 128, 0, stream>>>(b, (const __half*)x, (const int32_t*)topk_ids,
+    msgl_launch(ep_dispatch_kernel<__half>, dim3(tokens), dim3(128), 0, stream, b, (const __half*)x, (const int32_t*)topk_ids,
                                                            (int32_t*)send_slot, (uint32_t*)state, tokens, k,
                                                            experts_per_rank);
   else
@@ -247,7 +251,7 @@ MSGL_API int msgl_ep_recv_prepare(void* const* bases, int rank, int nranks, int 
                                   void* state, long long wait_us, cudaStream_t stream) {
   EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
   const int blocks = nranks * ((cap + 255) / 256);
-  ep_recv_prepare_kernel<<<blocks, 256, 0, stream>>>(b, (int32_t*)expert_ids, (const uint32_t*)state + nranks + 1,
+  msgl_launch(ep_recv_prepare_kernel, dim3(blocks), dim3(256), 0, stream, b, (int32_t*)expert_ids, (const uint32_t*)state + nranks + 1,
                                                      (unsigned long long)wait_us * 1000ull);
   MSGL_CHECK_LAUNCH("ep_recv_prepare");
   return MSGL_OK;
@@ -258,11 +262,11 @@ MSGL_API int msgl_ep_return(void* const* bases, int rank, int nranks, int cap, i
   EpBuffers b = make_buffers(bases, rank, nranks, cap, hidden, 2);
   const int blocks = nranks * cap;
   if (dtype == MSGL_BF16)
-    ep_return_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(b, (const __nv_bfloat16*)y_sorted,
+    msgl_launch(ep_return_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, b, (const __nv_bfloat16*)y_sorted,
                                                                (const int32_t*)pair_row, (uint32_t*)state,
                                                                (const uint32_t*)state + nranks + 1);
   else if (dtype == MSGL_F16)
-    ep_return_kernel<__half><<<blocks, 128, 0, stream>>>(b, (const __half*)y_sorted, (const int32_t*)pair_row,
+    msgl_launch(ep_return_kernel<__half>, dim3(blocks), dim3(128), 0, stream, b, (const __half*)y_sorted, (const int32_t*)pair_row,
                                                         (uint32_t*)state, (const uint32_t*)state + nranks + 1);
   else
     return MSGL_BAD_ARG;
@@ -277,12 +281,12 @@ MSGL_API int msgl_ep_combine(void* const* bases, int rank, int nranks, int cap, 
   int threads = hidden / 8 < 256 ? ((hidden / 8 + 31) / 32) * 32 : 256;
   if (threads < 32) threads = 32;
   if (dtype == MSGL_BF16)
-    ep_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(b, (const float*)topk_w, (const int32_t*)send_slot,
+    msgl_launch(ep_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, b, (const float*)topk_w, (const int32_t*)send_slot,
                                                                     (__nv_bfloat16*)out,
                                                                     (const uint32_t*)state + nranks + 1, k,
                                                                     (unsigned long long)wait_us * 1000ull);
   else if (dtype == MSGL_F16)
-    ep_combine_kernel<__half><<<tokens, threads, 0, stream>>>(b, (const float*)topk_w, (const int32_t*)send_slot,
+    msgl_launch(ep_combine_kernel<__half>, dim3(tokens), dim3(threads), 0, stream, b, (const float*)topk_w, (const int32_t*)send_slot,
                                                              (__half*)out, (const uint32_t*)state + nranks + 1, k,
                                                              (unsigned long long)wait_us * 1000ull);
   else

@@ -52,6 +52,7 @@ struct GemmArgs {
   const int32_t* tile_expert;
   int sf_n_atoms;          // scale-factor atoms along N per expert
   int* status;
+  int b_static;            // B and its scale atoms were written before the kernels now in flight
   // ---- tensor-parallel fusion (CTA-pair kernel only) -------------------------------------
   // Row-parallel GEMM -> reduce-scatter: instead of writing C locally, the epilogue stores each
   // partial row into the slot of the rank that owns that row (peer memory, plain st.global).
@@ -213,11 +214,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched no global memory. The weights (B, scale atoms) are not written by
+  // any kernel of the stream either, so the producer puts the first stages' weight tiles in
+  // flight before it waits for the kernels ahead of this one; the activations (A), their scales
+  // and the expert table of the grouped mode are only read after the wait.
+  if (!(warp == 0 && lane == 0)) pdl_enter();
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int pre = 0;  // leading stages of the first work item whose weight tile is already in flight
+      if (args.b_static && args.tile_expert == nullptr && (int)blockIdx.x < total_tiles) {
+        const int tile = (int)blockIdx.x / splits, split = (int)blockIdx.x - tile * splits;
+        const int n0 = (tile / args.m_tiles) * BN;
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        pre = min(STAGES, kb1 - kb0);
+        for (int s = 0; s < pre; ++s) {
+          const int kb = kb0 + s;
+          mbar_expect_tx(full_bar(s), STAGE_TX);
+          tma_load_2d(s_base + L::off_b + s * L::B_BYTES, &tma_b, full_bar(s), kb * KT::BKE, n0);
+          if (KIND == KIND_MXF4) {
+            const uint8_t* src = args.sfb + ((size_t)(n0 / 128) * args.sf_k_atoms + kb) * 512;
+            bulk_load(s_base + L::off_sf + s * L::SF_BYTES, src, 512, full_bar(s));
+          }
+        }
+      }
+      pdl_enter();
       for (int item = blockIdx.x; item < total_tiles && !*abort_flag; item += gridDim.x) {
         const int tile = item / splits, split = item - tile * splits;
         const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
@@ -230,15 +255,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const int kb0 = split * args.kb_per_split;
         const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 101)) break;
-          mbar_expect_tx(full_bar(stage), STAGE_TX);
+          const bool have_b = pre > 0;
+          if (have_b) {
+            --pre;  // fresh stage: nothing to wait for, the weight tile and the byte count are posted
+          } else {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 101)) break;
+            mbar_expect_tx(full_bar(stage), STAGE_TX);
+          }
           tma_load_2d(s_base + L::off_a + stage * L::A_BYTES, &tma_a, full_bar(stage), kb * KT::BKE, m_tile * BM);
-          tma_load_2d(s_base + L::off_b + stage * L::B_BYTES, &tma_b, full_bar(stage), kb * KT::BKE,
-                      expert * args.N + n0);
-          if (KIND == KIND_MXF4) {
-            const uint8_t* src =
-                args.sfb + ((size_t)(expert * args.sf_n_atoms + n0 / 128) * args.sf_k_atoms + kb) * 512;
-            bulk_load(s_base + L::off_sf + stage * L::SF_BYTES, src, 512, full_bar(stage));
+          if (!have_b) {
+            tma_load_2d(s_base + L::off_b + stage * L::B_BYTES, &tma_b, full_bar(stage), kb * KT::BKE,
+                        expert * args.N + n0);
+            if (KIND == KIND_MXF4) {
+              const uint8_t* src =
+                  args.sfb + ((size_t)(expert * args.sf_n_atoms + n0 / 128) * args.sf_k_atoms + kb) * 512;
+              bulk_load(s_base + L::off_sf + stage * L::SF_BYTES, src, 512, full_bar(stage));
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -309,7 +341,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int item = blockIdx.x; item < total_tiles; item += gridDim.x) {
       const int tile = item / splits, split = item - tile * splits;
       const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-      if (args.tile_expert != nullptr && args.tile_expert[m_tile] < 0) continue;
+      int expert = 0;
+      if (args.tile_expert != nullptr) {
+        expert = args.tile_expert[m_tile];
+        if (expert < 0) continue;
+      }
       const int row = m_tile * BM + q * 32 + lane;
       const bool row_ok = row < args.M;
       const int colbase = n_tile * BN;
@@ -321,7 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const int col = colbase + i;
           float sc = 1.f, bi = 0.f;
           if (col < args.N) {
-            if (args.b_scale != nullptr) sc = __ldg(args.b_scale + col);
+            if (args.b_scale != nullptr) sc = __ldg(args.b_scale + (size_t)expert * args.N + col);  // [experts][N]
             if (args.bias != nullptr && (split == 0 || args.splitk_count != nullptr))
               bi = args.bias_dtype == MSGL_BF16
                        ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col])
@@ -581,6 +617,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   cluster_sync_all();  // the other CTA's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // the prologue above touched no global memory
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -905,6 +942,7 @@ int make_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint6
   return MSGL_OK;
 }
 
+int g_b_static = 0;
 int g_num_sms = 0;
 int num_sms() {
   if (g_num_sms == 0) {
@@ -929,7 +967,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmArgs& args, int max
   }
   int total = args.m_tiles * args.n_tiles * args.splits;
   int grid = total < max_ctas ? total : max_ctas;
-  gemm_tcgen05_kernel<KIND, BN, STAGES><<<grid, kThreads, smem, stream>>>(ma, mb, args);
+  msgl_launch(gemm_tcgen05_kernel<KIND, BN, STAGES>, dim3(grid), dim3(kThreads), smem, stream, ma, mb, args);
   MSGL_CHECK_LAUNCH("gemm_tcgen05");
   return MSGL_OK;
 }
@@ -967,13 +1005,15 @@ int launch_pair_impl(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2] = {};
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = msgl_pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, RS>, ma, mb, msf, omaps, args);
   if (e != cudaSuccess) { msgl_set_error("gemm_pair launch", e); return MSGL_CUDA_ERROR; }
   return MSGL_OK;
@@ -1163,6 +1203,7 @@ static int gemm_impl(int kind, const void* a, long long lda, const void* b, void
   int* status = nullptr;
   cudaGetSymbolAddress((void**)&status, g_gemm_status);
   args.status = status;
+  args.b_static = g_b_static;
 
   CUtensorMap ma, mb;
   int rc;
@@ -1279,6 +1320,32 @@ MSGL_API int msgl_gemm_grouped(int kind, const void* a, long long lda, const voi
   }
   return gemm_impl(kind, a, lda, b, c, ldc, M, N, K, a_scale, nullptr, nullptr, 0, sf_atoms, out_dtype, bn, 0,
                    tile_expert, num_experts, stream);
+}
+
+// Grouped W8A8 (kind 2): e4m3 rows with per-row scales against e4m3 expert weights with one
+// scale per (expert, output channel): b_scale [experts * N] fp32.
+MSGL_API int msgl_gemm_grouped_w8a8(const void* a, long long lda, const void* b, void* c, long long ldc, int M, int N,
+                                    int K, const void* tile_expert, int num_experts, const void* a_scale,
+                                    const void* b_scale, int out_dtype, int bn_override, cudaStream_t stream) {
+  if (M % 128 || tile_expert == nullptr || num_experts <= 0 || b_scale == nullptr) return MSGL_BAD_ARG;
+  int bn = bn_override;
+  if (bn == 0) bn = (N % 128 == 0) ? 128 : (N % 64 == 0 ? 64 : 32);
+  if (N % bn) {
+    msgl_set_error_text("grouped gemm: N must be a multiple of the N tile");
+    return MSGL_BAD_ARG;
+  }
+  return gemm_impl(KIND_F8, a, lda, b, c, ldc, M, N, K, a_scale, b_scale, nullptr, 0, nullptr, out_dtype, bn, 0,
+                   tile_expert, num_experts, stream);
+}
+
+// Promise about the B operands (weights, scale atoms) of every GEMM call from now on: 1 = they
+// were written before any kernel that can still be in flight on the calling stream (model
+// parameters), so a kernel may fetch them before it has waited for the kernels ahead of it;
+// 0 (default) = no promise, B is only read after that wait. Returns the previous setting.
+MSGL_API int msgl_gemm_static_weights(int on) {
+  const int prev = g_b_static;
+  g_b_static = on ? 1 : 0;
+  return prev;
 }
 
 // Tile-shape policy of msgl_gemm when bn_override is 0: 0 = CTA-pair kernel above 256 rows,

@@ -27,6 +27,7 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ logits, float* __restrict__ topk_w,
                                  int32_t* __restrict__ topk_ids, int32_t* __restrict__ counts, int tokens, int E,
                                  int k, int renorm, int sigmoid, float scale, int e_start, int e_local) {
+  pdl_enter();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
   const int lane = threadIdx.x & 31;
@@ -93,6 +94,7 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, float* __restrict
 __global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
                                    int32_t* __restrict__ cursor, int32_t* __restrict__ tile_expert,
                                    int32_t* __restrict__ meta, int e_local, int max_tiles, int block) {
+  pdl_enter();
   __shared__ int s_off[kMaxExperts + 1];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -129,6 +131,7 @@ __global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int32_t* 
 __global__ void moe_scatter_kernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ offsets,
                                    int32_t* __restrict__ cursor, int32_t* __restrict__ sorted_pair,
                                    int32_t* __restrict__ pair_row, int pairs, int e_start, int e_local) {
+  pdl_enter();
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= pairs) return;
   const int local = topk_ids[p] - e_start;
@@ -144,6 +147,7 @@ __global__ void moe_scatter_kernel(const int32_t* __restrict__ topk_ids, const i
 template <typename T>
 __global__ void moe_permute_kernel(const T* __restrict__ x, const int32_t* __restrict__ sorted_pair,
                                    T* __restrict__ out, int hidden, int k, int rows) {
+  pdl_enter();
   const int row = blockIdx.x;
   if (row >= rows) return;
   const int pair = sorted_pair[row];
@@ -160,6 +164,7 @@ __global__ void moe_permute_kernel(const T* __restrict__ x, const int32_t* __res
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ topk_w,
                                    const int32_t* __restrict__ pair_row, T* __restrict__ out, int hidden, int k) {
+  pdl_enter();
   const int t = blockIdx.x;
   for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
     float acc[8];
@@ -189,15 +194,14 @@ MSGL_API int msgl_moe_route(const void* logits, void* topk_w, void* topk_ids, vo
   const int warps = 4;
   const int blocks = (tokens + warps - 1) / warps;
   if (dtype == MSGL_F32)
-    moe_route_kernel<float><<<blocks, warps * 32, 0, stream>>>((const float*)logits, (float*)topk_w, (int32_t*)topk_ids,
+    msgl_launch(moe_route_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, (const float*)logits, (float*)topk_w, (int32_t*)topk_ids,
                                                                (int32_t*)counts, tokens, E, k, renorm, sigmoid, scale,
                                                                e_start, e_local);
   else if (dtype == MSGL_BF16)
-    moe_route_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, stream>>>(
-        (const __nv_bfloat16*)logits, (float*)topk_w, (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k, renorm,
+    msgl_launch(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)logits, (float*)topk_w, (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k, renorm,
         sigmoid, scale, e_start, e_local);
   else if (dtype == MSGL_F16)
-    moe_route_kernel<__half><<<blocks, warps * 32, 0, stream>>>((const __half*)logits, (float*)topk_w,
+    msgl_launch(moe_route_kernel<__half>, dim3(blocks), dim3(warps * 32), 0, stream, (const __half*)logits, (float*)topk_w,
                                                                 (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k,
                                                                 renorm, sigmoid, scale, e_start, e_local);
   else
@@ -214,10 +218,10 @@ MSGL_API int msgl_moe_align(const void* topk_ids, const void* counts, void* offs
   if (tokens == 0) return MSGL_OK;
   if (e_local > kMaxExperts) return MSGL_BAD_ARG;
   cudaMemsetAsync(sorted_pair, 0xff, sizeof(int32_t) * (size_t)max_rows, stream);
-  moe_offsets_kernel<<<1, 256, 0, stream>>>((const int32_t*)counts, (int32_t*)offsets, (int32_t*)cursor,
+  msgl_launch(moe_offsets_kernel, dim3(1), dim3(256), 0, stream, (const int32_t*)counts, (int32_t*)offsets, (int32_t*)cursor,
                                             (int32_t*)tile_expert, (int32_t*)meta, e_local, max_rows / block, block);
   const int pairs = tokens * k;
-  moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>((const int32_t*)topk_ids, (const int32_t*)offsets,
+  msgl_launch(moe_scatter_kernel, dim3((pairs + 255) / 256), dim3(256), 0, stream, (const int32_t*)topk_ids, (const int32_t*)offsets,
                                                               (int32_t*)cursor, (int32_t*)sorted_pair,
                                                               (int32_t*)pair_row, pairs, e_start, e_local);
   MSGL_CHECK_LAUNCH("moe_align");
@@ -230,10 +234,10 @@ MSGL_API int msgl_moe_permute(const void* x, const void* sorted_pair, void* out,
   if (hidden % 8) return MSGL_BAD_ARG;
   int threads = hidden / 8 < 256 ? ((hidden / 8 + 31) / 32) * 32 : 256;
   if (dtype == MSGL_BF16)
-    moe_permute_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>((const __nv_bfloat16*)x, (const int32_t*)sorted_pair,
+    msgl_launch(moe_permute_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)x, (const int32_t*)sorted_pair,
                                                                    (__nv_bfloat16*)out, hidden, k, rows);
   else if (dtype == MSGL_F16)
-    moe_permute_kernel<__half><<<rows, threads, 0, stream>>>((const __half*)x, (const int32_t*)sorted_pair,
+    msgl_launch(moe_permute_kernel<__half>, dim3(rows), dim3(threads), 0, stream, (const __half*)x, (const int32_t*)sorted_pair,
                                                             (__half*)out, hidden, k, rows);
   else
     return MSGL_BAD_ARG;
@@ -247,11 +251,11 @@ MSGL_API int msgl_moe_combine(const void* y, const void* topk_w, const void* pai
   if (hidden % 8) return MSGL_BAD_ARG;
   int threads = hidden / 8 < 256 ? ((hidden / 8 + 31) / 32) * 32 : 256;
   if (dtype == MSGL_BF16)
-    moe_combine_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)y, (const float*)topk_w,
+    msgl_launch(moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)y, (const float*)topk_w,
                                                                      (const int32_t*)pair_row, (__nv_bfloat16*)out,
                                                                      hidden, k);
   else if (dtype == MSGL_F16)
-    moe_combine_kernel<__half><<<tokens, threads, 0, stream>>>((const __half*)y, (const float*)topk_w,
+    msgl_launch(moe_combine_kernel<__half>, dim3(tokens), dim3(threads), 0, stream, (const __half*)y, (const float*)topk_w,
                                                               (const int32_t*)pair_row, (__half*)out, hidden, k);
   else
     return MSGL_BAD_ARG;

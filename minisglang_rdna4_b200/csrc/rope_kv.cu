@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
     void* __restrict__ k_cache, void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hq, int hk, int rot,
     int page_size, float eps, int interleaved, int cache_fp8, int max_pos, int num_slots) {
+  pdl_enter();
   __shared__ float rows[4][D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int token = blockIdx.x;
@@ -128,6 +129,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_fast_kernel(
     void* __restrict__ k_cache, void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hq, int hk, int page_size, float eps,
     int interleaved, int cache_fp8, int max_pos, int num_slots) {
+  pdl_enter();
   constexpr int E = D / 64, H2 = D / 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int token = blockIdx.x;
@@ -229,6 +231,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_vec128_kernel(
     void* __restrict__ k_cache, void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hq, int hk, int page_size, float eps,
     int cache_fp8, int max_pos, int num_slots) {
+  pdl_enter();
   constexpr int D = 128, H2 = 64;
   const int token = blockIdx.x;
   const int sub = threadIdx.x & 7;                       // lane within the head's group of eight
@@ -326,18 +329,18 @@ MSGL_API int msgl_qk_norm_rope_store(const void* qkv, const void* q_w, const voi
 #define LAUNCH(T, D)                                                                                        \
   do {                                                                                                      \
   if (rot == head_dim && D == 128 && !interleaved)                                                          \
-    qk_norm_rope_store_vec128_kernel<T><<<dim3(tokens, (hq + 2 * hk + 15) / 16), 128, 0, stream>>>(         \
+    msgl_launch(qk_norm_rope_store_vec128_kernel<T>, dim3(dim3(tokens, (hq + 2 * hk + 15) / 16)), dim3(128), 0, stream, \
         (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,      \
         (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale, \
         hq, hk, page_size, eps, cache_fp8, max_pos, num_slots);                                             \
   else if (rot == head_dim)                                                                                 \
-    qk_norm_rope_store_fast_kernel<T, D><<<grid, 128, 0, stream>>>(                                         \
+    msgl_launch(qk_norm_rope_store_fast_kernel<T, D>, dim3(grid), dim3(128), 0, stream, \
         (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,      \
         (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale, \
         hq, hk, page_size, eps, interleaved, cache_fp8, max_pos, num_slots);                                \
   else                                                                                                      \
                                                                                         \
-  qk_norm_rope_store_kernel<T, D><<<grid, 128, 0, stream>>>(                                                \
+  msgl_launch(qk_norm_rope_store_kernel<T, D>, dim3(grid), dim3(128), 0, stream, \
       (const T*)qkv, (const T*)q_w, (const T*)k_w, (const int32_t*)positions, (const float*)cos_sin,        \
       (T*)q_out, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale, (const float*)v_scale,   \
       hq, hk, rot, page_size, eps, interleaved, cache_fp8, max_pos, num_slots);                            \
@@ -368,6 +371,7 @@ __global__ void store_kv_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 void* __restrict__ v_cache, const int32_t* __restrict__ out_loc,
                                 const float* __restrict__ k_scale, const float* __restrict__ v_scale, int hk,
                                 int d, int page_size, int cache_fp8, int num_slots) {
+  pdl_enter();
   const int token = blockIdx.x;
   const int slot = out_loc[token];
   if (slot < 0 || slot >= num_slots) return;
@@ -391,12 +395,10 @@ MSGL_API int msgl_store_kv(const void* k, const void* v, void* k_cache, void* v_
                            int page_size, int cache_fp8, int num_slots, int dtype, cudaStream_t stream) {
   if (tokens == 0) return MSGL_OK;
   if (dtype == MSGL_BF16)
-    store_kv_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
-        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_cache, v_cache, (const int32_t*)out_loc,
+    msgl_launch(store_kv_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, k_cache, v_cache, (const int32_t*)out_loc,
         (const float*)k_scale, (const float*)v_scale, hk, head_dim, page_size, cache_fp8, num_slots);
   else if (dtype == MSGL_F16)
-    store_kv_kernel<__half><<<tokens, 256, 0, stream>>>(
-        (const __half*)k, (const __half*)v, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale,
+    msgl_launch(store_kv_kernel<__half>, dim3(tokens), dim3(256), 0, stream, (const __half*)k, (const __half*)v, k_cache, v_cache, (const int32_t*)out_loc, (const float*)k_scale,
         (const float*)v_scale, hk, head_dim, page_size, cache_fp8, num_slots);
   else
     return MSGL_BAD_ARG;

@@ -27,6 +27,7 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out,
                                                       int vocab, long long stride) {
+  pdl_enter();
   __shared__ ArgMax red[32];
   const float* row = logits + (size_t)blockIdx.x * stride;
   ArgMax best{-INFINITY, 0x7fffffff};
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
                                                       const float* __restrict__ top_p, const float* __restrict__ min_p,
                                                       const float* __restrict__ uniform, int32_t* __restrict__ out,
                                                       int vocab) {
+  pdl_enter();
   __shared__ float scratch[32];
   __shared__ ArgMax red[32];
   __shared__ float warp_mass[32];
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
 
 MSGL_API int msgl_argmax(const void* logits, void* out, int rows, int vocab, long long stride, cudaStream_t stream) {
   if (rows == 0) return MSGL_OK;
-  argmax_kernel<<<rows, 1024, 0, stream>>>((const float*)logits, (int32_t*)out, vocab, stride);
+  msgl_launch(argmax_kernel, dim3(rows), dim3(1024), 0, stream, (const float*)logits, (int32_t*)out, vocab, stride);
   MSGL_CHECK_LAUNCH("argmax");
   return MSGL_OK;
 }
@@ -188,7 +190,7 @@ MSGL_API int msgl_sample(const void* logits, long long stride, const void* temps
                          const void* top_p, const void* min_p, const void* uniform, void* out, int rows, int vocab,
                          cudaStream_t stream) {
   if (rows == 0) return MSGL_OK;
-  sample_kernel<<<rows, 1024, 0, stream>>>((const float*)logits, stride, (const float*)temps, (const int32_t*)top_k,
+  msgl_launch(sample_kernel, dim3(rows), dim3(1024), 0, stream, (const float*)logits, stride, (const float*)temps, (const int32_t*)top_k,
                                            (const float*)top_p, (const float*)min_p, (const float*)uniform,
                                            (int32_t*)out, vocab);
   MSGL_CHECK_LAUNCH("sample");

@@ -243,6 +243,13 @@ class Engine:
         from ..layers.moe import MoELayer as _Moe
 
         host_tier = _Moe.offload_slots > 0   # expert residency is decided on the host every step
+        if dev_kind == "cuda":
+            from ..ops import cuda as K
+
+            K.set_pdl(ENV.PDL.value)
+            # model parameters never change while kernels run, unless experts are paged in from the
+            # host tier: only then must a GEMM wait for the stream before it reads its weights
+            K.gemm_static_weights(ENV.PDL.value and not host_tier)
         if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0
                 and not ep_replicas and not host_tier):
             from .graph import GraphRunner

@@ -133,6 +133,7 @@ ENV.flag("DISABLE_TC_PREFILL", False, "prefill attention on the general (warp-le
 ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
 ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of the fused reduce-scatter / all-gather GEMMs")
+ENV.flag("PDL", True, "programmatic dependent launch: a kernel's prologue overlaps the tail of the kernel ahead of it")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger ones go to the row-sharded GEMM fusion or to NCCL")
 ENV.int("COMM_HEALTH_STEPS", 8, "the tensor-parallel ranks agree on the collectives' status word every this many steps")

@@ -50,10 +50,24 @@ class MoELayer(BaseOP):
         self.gate = ReplicatedLinear(hidden, num_experts, dtype, device, None)
         self.w13 = torch.empty((self._e_local, 2 * self._i_local, hidden), dtype=dtype, device=device)
         self.w2 = torch.empty((self._e_local, hidden, self._i_local), dtype=dtype, device=device)
-        # MXFP4 experts run W4A8 on the GPU: the stacks are (re-)encoded to e2m1 + UE8M0 scale
-        # atoms after loading (lossless for an MXFP4 checkpoint, whose values are on that grid)
-        self._w4a8 = scheme is not None and "mxfp4" in str(getattr(scheme, "name", "")).lower() \
-            and hidden % 128 == 0 and self._i_local % 128 == 0
+        # Quantised experts keep their checkpoint precision on the GPU (the reference's expert
+        # methods: python/minisgl/layers/moe.py:42-520):
+        #   mxfp4        W4A8, e2m1 + UE8M0 scale atoms (re-encoding the stacks is lossless for an
+        #                MXFP4 checkpoint, whose values are on that grid)
+        #   fp8_block    W8A8 with 128 x 128 weight blocks and 1 x 128 activation groups; the loader
+        #                hands over the checkpoint's own e4m3 values and scales (``_raw_fp8``)
+        #   fp8_channel  W8A8 with one scale per (expert, output channel)
+        name = str(getattr(scheme, "name", "")).lower() if scheme is not None else ""
+        aligned = hidden % 128 == 0 and self._i_local % 128 == 0
+        self._quant_kind = None
+        if aligned and "mxfp4" in name:
+            self._quant_kind = "mxfp4"
+        elif aligned and name == "fp8_block" and tuple(getattr(scheme, "block", (128, 128))) == (128, 128):
+            self._quant_kind = "fp8_block"
+        elif aligned and name in ("fp8_channel", "fp8_tensor"):
+            self._quant_kind = "fp8_channel"
+        self._w4a8 = self._quant_kind == "mxfp4"
+        self._raw_fp8 = None   # (w13_q, w13_scale, w2_q, w2_scale) straight from an fp8 checkpoint
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Returns this rank's partial result (tensor-parallel partial sum when the
@@ -72,10 +86,18 @@ class MoELayer(BaseOP):
             return tier.forward(x, topk_w, topk_ids - self._e_start)
         packed = getattr(self, "_packed", None)
         if packed is not None:
-            from ..ops.moe_kernels import moe_forward_w4a8
+            from ..ops.moe_kernels import moe_forward_quant
 
-            return moe_forward_w4a8(x, *packed, topk_w, topk_ids, self._e_start)
+            return moe_forward_quant(self._quant_kind, x, packed, topk_w, topk_ids, self._e_start)
         return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
+
+    def expert_weights(self):
+        """``(kind, tensors)`` of the resident expert stacks for the grouped-GEMM pipeline
+        (``ops.moe_kernels.run_experts``)."""
+        packed = getattr(self, "_packed", None)
+        if packed is not None:
+            return self._quant_kind, packed
+        return "bf16", (self.w13, self.w2)
 
     def _encode_w4a8(self) -> None:
         from ..quant import mxfp4
@@ -92,10 +114,54 @@ class MoELayer(BaseOP):
         self.w13 = self.w13[:0]
         self.w2 = self.w2[:0]
 
+    def _encode_fp8(self) -> None:
+        """fp8 expert stacks: the checkpoint's own tensors when the loader kept them, otherwise
+        (random-init weights) a fresh quantisation of the 16-bit stacks."""
+        dev = self.w13.device
+        if self._raw_fp8 is not None:
+            self._packed = tuple(t.to(dev).contiguous() for t in self._raw_fp8)
+            self._raw_fp8 = None
+        elif self._quant_kind == "fp8_block":
+            def enc(w):  # [E, N, K] -> e4m3 [E, N, K], fp32 [E, N/128, K/128]
+                e, n, k = w.shape
+                qs, ss = [], []
+                for i in range(e):
+                    blocks = w[i].float().view(n // 128, 128, k // 128, 128)
+                    scale = blocks.abs().amax((1, 3)).clamp_min(1e-8) / 448.0
+                    qs.append((blocks / scale[:, None, :, None]).view(n, k).to(torch.float8_e4m3fn))
+                    ss.append(scale)
+                return torch.stack(qs).contiguous(), torch.stack(ss).float().contiguous()
+
+            self._packed = enc(self.w13) + enc(self.w2)
+        else:
+            def enc(w):  # [E, N, K] -> e4m3 [E, N, K], fp32 [E, N]
+                scale = w.float().abs().amax(-1).clamp_min(1e-8) / 448.0
+                return (w.float() / scale[..., None]).to(torch.float8_e4m3fn).contiguous(), scale.float().contiguous()
+
+            self._packed = enc(self.w13) + enc(self.w2)
+        self.w13 = self.w13[:0]
+        self.w2 = self.w2[:0]
+
     def _post_load_self(self) -> None:
         if self._w4a8 and self.w13.is_cuda and not type(self).offload_slots:
             self._encode_w4a8()
             return
+        if self._quant_kind in ("fp8_block", "fp8_channel") and self.w13.is_cuda and not type(self).offload_slots:
+            self._encode_fp8()
+            return
+        if self._raw_fp8 is not None:
+            # CPU oracle path: expand the checkpoint tensors to the 16-bit stacks
+            w13_q, w13_s, w2_q, w2_s = self._raw_fp8
+            self._raw_fp8 = None
+
+            def dense(q, s):
+                if s.dim() == 3:
+                    s = s.repeat_interleave(128, 1).repeat_interleave(128, 2)[:, : q.shape[1], : q.shape[2]]
+                else:
+                    s = s[..., None]
+                return (q.float() * s.float()).to(self._compute_dtype)
+
+            self.w13, self.w2 = dense(w13_q, w13_s), dense(w2_q, w2_s)
         slots = type(self).offload_slots
         if slots and slots < self._e_local:
             from ..weights import HostExpertTier

@@ -216,9 +216,41 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
     for block, _items in by_block.items():
         moe = modules[block + ".experts"]
         scheme = cfg.quant.for_module(block + ".experts.0.gate_proj") if cfg.quant is not None else None
+        inter = moe._i_local
+        first = expert_buf[(block, moe._e_start, "gate_proj")]
+        kind = getattr(moe, "_quant_kind", None)
+        raw_ok = (kind in ("fp8_block", "fp8_channel") and first.get("weight") is not None
+                  and first["weight"].dtype == torch.float8_e4m3fn
+                  and ("weight_scale_inv" in first if kind == "fp8_block" else "weight_scale" in first))
+        if raw_ok:
+            # keep the checkpoint's e4m3 values and scales: [E, 2I, H] + scales, [E, H, I] + scales
+            sname = "weight_scale_inv" if kind == "fp8_block" else "weight_scale"
+            qs13, ss13, qs2, ss2 = [], [], [], []
+            for local in range(moe._e_local):
+                e = moe._e_start + local
+                parts = {p: expert_buf[(block, e, p)] for p in ("gate_proj", "up_proj", "down_proj")}
+                gq, uq, dq = (parts[p]["weight"] for p in ("gate_proj", "up_proj", "down_proj"))
+                gs, us, ds = (parts[p][sname].float() for p in ("gate_proj", "up_proj", "down_proj"))
+                if kind == "fp8_channel":
+                    gs, us, ds = gs.reshape(-1), us.reshape(-1), ds.reshape(-1)
+                if moe._ep is None and tp.size > 1:
+                    gq, uq = _slice(gq, 0, tp.rank, tp.size), _slice(uq, 0, tp.rank, tp.size)
+                    dq = _slice(dq, 1, tp.rank, tp.size)
+                    gs, us = _slice(gs, 0, tp.rank, tp.size), _slice(us, 0, tp.rank, tp.size)
+                    if kind == "fp8_block":
+                        ds = _slice(ds, 1, tp.rank, tp.size)
+                qs13.append(torch.cat([gq, uq], 0))
+                ss13.append(torch.cat([gs, us], 0))
+                qs2.append(dq)
+                ss2.append(ds)
+            moe._raw_fp8 = (torch.stack(qs13), torch.stack(ss13), torch.stack(qs2), torch.stack(ss2))
+            moe.w13 = torch.empty((0,) + tuple(moe.w13.shape[1:]), dtype=moe.w13.dtype, device=device)
+            moe.w2 = torch.empty((0,) + tuple(moe.w2.shape[1:]), dtype=moe.w2.dtype, device=device)
+            loaded.add(block + ".experts.w13")
+            loaded.add(block + ".experts.w2")
+            continue
         w13 = torch.empty(moe.w13.shape, dtype=moe.w13.dtype)
         w2 = torch.empty(moe.w2.shape, dtype=moe.w2.dtype)
-        inter = moe._i_local
         for local in range(moe._e_local):
             e = moe._e_start + local
             gate = _expert_dense(expert_buf[(block, e, "gate_proj")], scheme)

@@ -35,6 +35,8 @@ _SIGNATURES = {
     "msgl_rms_norm_planes": (c_i, [c_p, c_i, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_f, c_i, c_i, c_p]),
     "msgl_gemm_status": (c_i, [c_i]),
     "msgl_gemm_pair_mode": (c_i, [c_i]),
+    "msgl_gemm_static_weights": (c_i, [c_i]),
+    "msgl_set_pdl": (c_i, [c_i]),
     "msgl_attn_make_kv_map": (c_i, [c_p, c_p, c_i, c_i, c_i, c_i, c_ll, c_i]),
     "msgl_attn_workspace_floats": (c_ll, [c_i, c_i, c_i, c_i]),
     "msgl_paged_attention": (c_i, [c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_p, c_p, c_ll, c_p,

@@ -536,16 +536,56 @@ def gemm_w4a8_mxfp4(x_q, x_scale, w_packed, sf_atoms, out_dtype=torch.bfloat16, 
     return _gemm(KIND_MXF4, x_q, w_packed, n, k, out_dtype, a_scale=x_scale, bias=bias, sf_atoms=sf_atoms, bn=bn)
 
 
-def gemm_fp8_block(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16):
-    """128x128-block fp8: one tensor-core GEMM per 128-deep K block would need partial-sum
-    promotion; until that kernel exists the block scales are folded into 16-bit operands and
-    the product runs on the bf16 tensor-core path."""
-    n, k = w_q.shape
-    ws = w_scale.repeat_interleave(128, 0).repeat_interleave(128, 1)[:n, :k]
-    w = (w_q.float() * ws).to(out_dtype)
-    xs = x_scale.repeat_interleave(128, 1)[:, :k]
-    x = (x_q.float() * xs).to(out_dtype)
-    return gemm(x, w, None, out_dtype)
+def gemm_fp8_block(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16, tile_expert=None):
+    """Block-scaled fp8 W8A8: ``x_q [M, K]`` e4m3 with ``x_scale [M, ceil(K/128)]`` (1 x 128 groups),
+    ``w_q [N, K]`` e4m3 with ``w_scale [ceil(N/128), ceil(K/128)]`` (128 x 128 blocks). Grouped
+    form: ``w_q [E, N, K]``, ``w_scale [E, N/128, ceil(K/128)]``, rows of ``x_q`` sorted by expert in
+    128-row tiles and ``tile_expert [M/128]``. Every K block is accumulated on the tensor core by
+    itself and promoted with its scale product (``gemm_fp8_block_kernel``)."""
+    from ._lib import bind, c_i, c_ll, c_p
+
+    if not hasattr(gemm_fp8_block, "_bound"):
+        bind("msgl_gemm_fp8_block", c_i, [c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_i, c_p])
+        bind("msgl_gemm_fp8_block_status", c_i, [c_i])
+        gemm_fp8_block._bound = True
+    assert x_q.dtype == torch.float8_e4m3fn and w_q.dtype == torch.float8_e4m3fn
+    assert x_q.dim() == 2 and x_q.stride(1) == 1 and w_q.is_contiguous()
+    m, k = x_q.shape
+    experts = 0
+    if tile_expert is not None:
+        experts, n, kw = w_q.shape
+    else:
+        n, kw = w_q.shape
+    if kw != k:
+        raise ValueError(f"gemm_fp8_block: activations of K={k} against weights of K={kw}")
+    kb = (k + 127) // 128
+    x_scale = x_scale.float() if x_scale.dtype != torch.float32 else x_scale
+    w_scale = w_scale.float() if w_scale.dtype != torch.float32 else w_scale
+    assert x_scale.is_contiguous() and x_scale.shape == (m, kb), (x_scale.shape, (m, kb))
+    assert w_scale.is_contiguous() and w_scale.shape[-1] == kb and w_scale.shape[-2] == (n + 127) // 128
+    out = torch.empty((m, n), dtype=out_dtype, device=x_q.device)
+    check(lib().msgl_gemm_fp8_block(_p(x_q), x_q.stride(0), _p(w_q), _p(out), n, m, n, k, _p(x_scale), _p(w_scale),
+                                    _p(tile_expert), experts, _DT[out_dtype], _stream()), "gemm_fp8_block")
+    _count("gemm_w8a8_block" + ("_grouped" if tile_expert is not None else ""), "gemm_fp8_block_kernel")
+    return out
+
+
+def silu_and_mul_quant_group(x):
+    """SiLU(gate) * up of ``x [rows, 2I]`` quantised to e4m3 in groups of 128 outputs:
+    returns ``(q [rows, I], scales [rows, I / 128])``."""
+    from ._lib import bind, c_i, c_p
+
+    if not hasattr(silu_and_mul_quant_group, "_bound"):
+        bind("msgl_silu_mul_quant_group", c_i, [c_p, c_p, c_p, c_i, c_i, c_i, c_p])
+        silu_and_mul_quant_group._bound = True
+    assert x.is_contiguous() and x.dim() == 2
+    rows, two_i = x.shape
+    inter = two_i // 2
+    q = torch.empty((rows, inter), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows, inter // 128), dtype=torch.float32, device=x.device)
+    check(lib().msgl_silu_mul_quant_group(_p(x), _p(q), _p(s), rows, inter, _dt(x), _stream()), "silu_mul_quant_group")
+    _count("silu_and_mul_quant_group", "silu_mul_quant_group_kernel")
+    return q, s
 
 
 def gemm_status(reset=True) -> int:
@@ -559,6 +599,19 @@ def gemm_pair_mode(mode: int) -> int:
     return int(lib().msgl_gemm_pair_mode(int(mode)))
 
 
+def gemm_static_weights(on: bool) -> int:
+    """Promise that the weight operands of all GEMM calls from now on are model parameters
+    (written long before the kernels in flight): the decode GEMMs then fetch their first weight
+    tiles while the kernel ahead of them is still running. Returns the previous setting."""
+    return int(lib().msgl_gemm_static_weights(int(on)))
+
+
+def set_pdl(on: bool) -> int:
+    """Programmatic dependent launch of the library's kernels (on by default; ``MSGL_PDL=0``
+    switches it off). Returns the previous setting."""
+    return int(lib().msgl_set_pdl(int(on)))
+
+
 def decode_attention_stages(stages: int) -> None:
     """Depth of the fp8 decode kernel's TMA ring (2-4 stages of 64 tokens)."""
     lib().msgl_attn_decode_stages(int(stages))
@@ -569,6 +622,13 @@ def force_general_decode_attention(on: bool) -> None:
     sets this: verification rows run on the general kernel, and greedy output is only
     bit-identical to plain decoding when the decode rows take the same code path."""
     lib().msgl_attn_force_general_decode(int(on))
+
+
+def gemm_fp8_block_status(reset=True) -> int:
+    from ._lib import bind, c_i
+
+    bind("msgl_gemm_fp8_block_status", c_i, [c_i])
+    return int(lib().msgl_gemm_fp8_block_status(int(reset)))
 
 
 def attn_status(reset=True) -> int:

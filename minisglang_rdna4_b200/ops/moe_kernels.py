@@ -134,3 +134,86 @@ def moe_forward_w4a8(x, w13_packed, w13_atoms, w2_packed, w2_atoms, topk_w, topk
                                  _DT[x.dtype], K._stream()), "moe_combine")
     K._count("moe_combine", "moe_combine_kernel")
     return out
+
+
+_lib.bind("msgl_gemm_grouped_w8a8", c_i, [c_p, c_ll, c_p, c_p, c_ll, c_i, c_i, c_i, c_p, c_i, c_p, c_p, c_i, c_i, c_p])
+
+
+def _permute(x, sorted_pair, k):
+    rows, h = sorted_pair.numel(), x.shape[1]
+    xs = torch.empty((rows, h), dtype=x.dtype, device=x.device)
+    check(lib().msgl_moe_permute(x.data_ptr(), sorted_pair.data_ptr(), xs.data_ptr(), h, k, rows, _DT[x.dtype],
+                                 K._stream()), "moe_permute")
+    K._count("moe_permute", "moe_permute_kernel")
+    return xs
+
+
+def _combine(y, topk_w, pair_row, like, k):
+    t, h = like.shape
+    out = torch.empty_like(like)
+    check(lib().msgl_moe_combine(y.data_ptr(), topk_w.data_ptr(), pair_row.data_ptr(), out.data_ptr(), t, h, k,
+                                 _DT[like.dtype], K._stream()), "moe_combine")
+    K._count("moe_combine", "moe_combine_kernel")
+    return out
+
+
+def gemm_grouped_w8a8(a_q, a_scale, b_q, b_scale, tile_expert, out_dtype=torch.bfloat16, bn=0):
+    """fp8 experts with per-channel scales: ``a_q [R, K]`` e4m3 rows (expert-sorted) with per-row
+    scales, ``b_q [E, N, K]`` e4m3, ``b_scale [E, N]`` fp32 → ``[R, N]``."""
+    e, n, k = b_q.shape
+    r = a_q.shape[0]
+    out = torch.empty((r, n), dtype=out_dtype, device=a_q.device)
+    check(lib().msgl_gemm_grouped_w8a8(a_q.data_ptr(), a_q.stride(0), b_q.data_ptr(), out.data_ptr(), n, r, n, k,
+                                       tile_expert.data_ptr(), e, a_scale.data_ptr(), b_scale.data_ptr(),
+                                       _DT[out_dtype], bn, K._stream()), "gemm_grouped_w8a8")
+    K._count("moe_gemm_grouped_w8a8", "gemm_tcgen05_kernel")
+    return out
+
+
+def experts_w8a8(xs, tile_expert, w13_q, w13_s, w2_q, w2_s, out_dtype):
+    """The two expert GEMMs on expert-sorted rows ``xs`` for per-channel fp8 experts
+    (python/minisgl/quant/kernels.py:1181-1331)."""
+    xq, xsc = K.per_token_quant_fp8(xs)
+    hcur = gemm_grouped_w8a8(xq, xsc, w13_q, w13_s, tile_expert, out_dtype)
+    aq, asc = K.silu_and_mul_quant(hcur)
+    return gemm_grouped_w8a8(aq, asc, w2_q, w2_s, tile_expert, out_dtype)
+
+
+def experts_fp8_block(xs, tile_expert, w13_q, w13_s, w2_q, w2_s, out_dtype):
+    """The two expert GEMMs for block-scaled fp8 experts (128 x 128 weight blocks, 1 x 128
+    activation groups; python/minisgl/quant/method.py:846-897)."""
+    xq, xsc = K.per_group_quant_fp8(xs, 128)
+    hcur = K.gemm_fp8_block(xq, xsc, w13_q, w13_s, out_dtype, tile_expert=tile_expert)
+    aq, asc = K.silu_and_mul_quant_group(hcur)
+    return K.gemm_fp8_block(aq, asc, w2_q, w2_s, out_dtype, tile_expert=tile_expert)
+
+
+def experts_w4a8(xs, tile_expert, w13_packed, w13_atoms, w2_packed, w2_atoms, out_dtype):
+    xq, xsc = K.per_token_quant_fp8(xs)
+    hcur = gemm_grouped_w4a8(xq, xsc, w13_packed, w13_atoms, tile_expert, out_dtype)
+    aq, asc = K.silu_and_mul_quant(hcur)
+    return gemm_grouped_w4a8(aq, asc, w2_packed, w2_atoms, tile_expert, out_dtype)
+
+
+def experts_bf16(xs, tile_expert, w13, w2, out_dtype):
+    return gemm_grouped(K.act_and_mul(gemm_grouped(xs, w13, tile_expert)), w2, tile_expert)
+
+
+EXPERT_KERNELS = {"bf16": experts_bf16, "mxfp4": experts_w4a8, "fp8_channel": experts_w8a8,
+                  "fp8_block": experts_fp8_block}
+
+
+def run_experts(kind: str, xs, tile_expert, weights, out_dtype):
+    """Expert MLPs of kind ``bf16 | mxfp4 | fp8_channel | fp8_block`` on expert-sorted rows."""
+    return EXPERT_KERNELS[kind](xs, tile_expert, *weights, out_dtype)
+
+
+def moe_forward_quant(kind: str, x, weights, topk_w, topk_ids, expert_offset=0):
+    """align → permute → quantise → grouped GEMM → SiLU·mul + quantise → grouped GEMM → combine
+    for quantised expert stacks ``weights`` of ``kind``."""
+    e_local = weights[0].shape[0]
+    k = topk_ids.shape[1]
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local)
+    xs = _permute(x, sorted_pair, k)
+    y = run_experts(kind, xs, tile_expert, weights, x.dtype)
+    return _combine(y, topk_w, pair_row, x, k)

@@ -479,3 +479,83 @@ def test_gemm_split_k_planes_feed_the_fused_norm(K, n, k):
         sub = K.gemm_w4a8_mxfp4(xq[:mm].contiguous(), xs[:mm].contiguous(), packed, atoms, bias=bias)
         assert torch.equal(sub.planes, part.planes[:, :mm])
     assert K.gemm_status() == 0
+
+
+# ------------------------------------------------------------------------------------------ block-scaled fp8
+def _quant_blocks(w, bn=128, bk=128):
+    n, k = w.shape
+    npad, kpad = -(-n // bn) * bn, -(-k // bk) * bk
+    wp = torch.zeros(npad, kpad, device=w.device)
+    wp[:n, :k] = w
+    blocks = wp.view(npad // bn, bn, kpad // bk, bk)
+    scale = blocks.abs().amax((1, 3)).clamp_min(1e-8) / 448.0
+    q = (blocks / scale[:, None, :, None]).view(npad, kpad)[:n, :k].to(torch.float8_e4m3fn).contiguous()
+    return q, scale.float().contiguous()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 384, 768), (130, 2048, 512), (300, 1536, 2048), (257, 136, 384)])
+def test_gemm_fp8_block(K, m, n, k):
+    """128 x 128 weight blocks times 1 x 128 activation groups against the fp32 restatement; a
+    row's result does not depend on how many rows are multiplied with it."""
+    R = _ref()
+    torch.manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    # groups with very different magnitudes make the per-block promotion matter
+    x[:, : k // 2] *= 8.0
+    w = torch.randn(n, k, device="cuda") * 0.05
+    w[: n // 2] *= 4.0
+    wq, ws = _quant_blocks(w)
+    xq, xs = K.per_group_quant_fp8(x, 128)
+    got = K.gemm_fp8_block(xq, xs, wq, ws, torch.bfloat16)
+    assert K.gemm_fp8_block_status() == 0
+    want = R.gemm_fp8_block(xq, xs, wq, ws, 128, torch.float32)
+    _close(got, want, 1e-2, 1e-2 * float(want.abs().max()), "gemm_fp8_block")
+    got32 = K.gemm_fp8_block(xq, xs, wq, ws, torch.float32)
+    _close(got32, want, 2e-3, 2e-3 * float(want.abs().max()), "gemm_fp8_block fp32")
+    one = K.gemm_fp8_block(xq[-1:].contiguous(), xs[-1:].contiguous(), wq, ws, torch.float32)
+    assert torch.equal(one[0], got32[-1])
+
+
+def test_moe_forward_fp8_kinds(K):
+    """Expert MLPs on block-scaled and per-channel fp8 expert stacks (grouped GEMMs), with experts
+    that receive no token and experts whose rows do not fill a tile, against the 16-bit expert path
+    on the de-quantised weights."""
+    from minisglang_rdna4_b200.ops import moe_kernels as MK
+
+    R = _ref()
+    torch.manual_seed(3)
+    tokens, E, k, h, inter = 150, 16, 4, 512, 256
+    x = torch.randn(tokens, h, device="cuda").bfloat16()
+    logits = torch.randn(tokens, E, device="cuda")
+    logits[:, 5] = -1e9      # expert 5 never selected
+    logits[:3, 7] = 1e9      # and expert 7 by few rows only
+    logits[3:, 7] = -1e9
+    w, ids = MK.moe_route(logits, k, True)
+    w13 = torch.randn(E, 2 * inter, h, device="cuda") * 0.05
+    w2 = torch.randn(E, h, inter, device="cuda") * 0.05
+
+    def blk(wt):
+        qs, ss = zip(*[_quant_blocks(wt[e]) for e in range(wt.shape[0])])
+        q, s = torch.stack(qs).contiguous(), torch.stack(ss).contiguous()
+        deq = q.float() * s.repeat_interleave(128, 1).repeat_interleave(128, 2)
+        return q, s, deq.bfloat16()
+
+    def chan(wt):
+        s = wt.abs().amax(-1).clamp_min(1e-8) / 448.0
+        q = (wt / s[..., None]).to(torch.float8_e4m3fn).contiguous()
+        return q, s.float().contiguous(), (q.float() * s[..., None]).bfloat16()
+
+    for kind, enc in (("fp8_block", blk), ("fp8_channel", chan)):
+        q13, s13, d13 = enc(w13)
+        q2, s2, d2 = enc(w2)
+        got = MK.moe_forward_quant(kind, x, (q13, s13, q2, s2), w, ids)
+        assert K.gemm_status() == 0 and K.gemm_fp8_block_status() == 0
+        want = R.moe_forward(x, d13, d2, w, ids)
+        err = float((got.float() - want.float()).abs().max()) / float(want.float().abs().max())
+        assert err < 0.06, (kind, err)
+    # the fused SiLU·mul + 1 x 128 quantiser against the two-step form
+    hcur = torch.randn(77, 2 * inter, device="cuda").bfloat16()
+    q, s = K.silu_and_mul_quant_group(hcur)
+    q0, s0 = K.per_group_quant_fp8(K.act_and_mul(hcur), 128)
+    _close(s, s0, 1e-3, 0, "group scales")
+    _close(q.float() * s.repeat_interleave(128, 1), q0.float() * s0.repeat_interleave(128, 1), 0.13, 1e-3, "group q")

@@ -35,19 +35,46 @@ sys.path.insert(0, ROOT)
 BASELINE_TOK_S = None  # the reference publishes no B200 number for this configuration
 
 
+# The named benchmark configurations (the workload shapes of the baseline description). The
+# default, ``dense``, is the headline; the others are selected with ``--config``. Explicit flags
+# override a preset's values.
+PRESETS = {
+    # Qwen3-4B-shaped dense decoder, MXFP4 W4A8 + fp8 KV, tensor parallel
+    "dense": dict(model="qwen3-4b", quant="mxfp4", kv="fp8", requests=256, in_min=512, in_max=2048, out_len=256,
+                  parallel="tp"),
+    # Qwen3-30B-A3B-shaped MoE, block-scaled fp8 W8A8, attention data-parallel + expert-parallel
+    # with the all-to-all exchange: every GPU is a replica holding E / N experts
+    "moe-ep": dict(model="qwen3-30b-a3b", quant="fp8_block", kv="fp8", requests=512, in_min=256, in_max=1024,
+                   out_len=256, parallel="dp-ep"),
+    # Llama-3-70B-shaped dense decoder, fp8 W8A8 per channel + fp8 KV, tensor parallel; all requests
+    # share a 2048-token random prefix followed by a unique 256-token suffix
+    "prefix70b": dict(model="llama3-70b", quant="fp8", kv="fp8", requests=512, in_min=256, in_max=256, out_len=128,
+                      shared_prefix=2048, parallel="tp"),
+    # Qwen3-8B-shaped bf16 target with an EAGLE3-style one-layer draft head, draft length 4, greedy
+    "spec": dict(model="qwen3-8b", quant="none", kv="bf16", requests=64, in_min=1024, in_max=1024, out_len=256,
+                 spec="eagle3", spec_draft=4, spec_tree_width=4, parallel="tp"),
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="dense", choices=sorted(PRESETS))
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="qwen3-4b")
-    ap.add_argument("--quant", default="mxfp4")
-    ap.add_argument("--kv", default="fp8")
-    ap.add_argument("--requests", type=int, default=256)
-    ap.add_argument("--in-min", type=int, default=512)
-    ap.add_argument("--in-max", type=int, default=2048)
-    ap.add_argument("--out-len", type=int, default=256)
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--quant", default=None)
+    ap.add_argument("--kv", default=None)
+    ap.add_argument("--requests", type=int, default=None)
+    ap.add_argument("--in-min", type=int, default=None)
+    ap.add_argument("--in-max", type=int, default=None)
+    ap.add_argument("--out-len", type=int, default=None)
+    ap.add_argument("--shared-prefix", type=int, default=None)
+    ap.add_argument("--parallel", default=None, choices=["tp", "dp-ep"])
+    ap.add_argument("--spec", default=None, choices=["none", "ngram", "eagle3", "mtp"])
+    ap.add_argument("--spec-draft", type=int, default=None)
+    ap.add_argument("--spec-tree-width", type=int, default=None)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--max-extend", type=int, default=8192)
     ap.add_argument("--memory-ratio", type=float, default=0.85)
@@ -57,7 +84,13 @@ def parse_args():
     ap.add_argument("--no-matched", action="store_true",
                     help="skip the extra bf16-weights / bf16-KV run of this repository that is reported beside "
                          "the quantised number for a like-for-like ratio against the bf16 reference arm")
-    return ap.parse_args()
+    args = ap.parse_args()
+    preset = dict(shared_prefix=0, spec="none", spec_draft=4, spec_tree_width=1)
+    preset.update(PRESETS[args.config])
+    for key, val in preset.items():
+        if getattr(args, key, None) is None:
+            setattr(args, key, val)
+    return args
 
 
 class ClockSampler:
@@ -214,7 +247,7 @@ def main() -> None:
         return
 
     matched = None
-    if (args.gpus == 1 and args.quant != "none" and not args.no_matched
+    if (args.gpus == 1 and args.quant != "none" and not args.no_matched and args.config == "dense"
             and not os.environ.get("MSGL_BENCH_PROFILE")):
         matched = run_matched_bf16(args)
 
@@ -240,11 +273,19 @@ def main() -> None:
         from minisglang_rdna4_b200.models.config import NAMED_CONFIGS
 
         model_config = dataclasses.replace(NAMED_CONFIGS[args.model](), num_layers=args.layers)
+    dp_ep = args.parallel == "dp-ep" and world > 1
+    par = dict(dp_size=world, dp_rank=rank, enable_ep=True) if dp_ep else dict(tp_size=world, tp_rank=rank)
+    spec = {}
+    if args.spec != "none":
+        spec = dict(spec_algorithm=args.spec, spec_num_draft=args.spec_draft, spec_tree_width=args.spec_tree_width)
+    local_requests = -(-args.requests // world) if dp_ep else args.requests
     llm = LLM(
-        model_path=args.model, model_config=model_config, use_dummy_weight=True, quantization=None if args.quant == "none" else args.quant,
-        kv_cache_dtype=args.kv, tp_size=world, tp_rank=rank, page_size=args.page_size,
-        max_running_req=args.requests, max_extend_tokens=args.max_extend, memory_ratio=args.memory_ratio,
-        seed=1, cuda_graph_max_bs=(-1 if args.no_graph else None), max_seq_len_override=4096,
+        model_path=args.model, model_config=model_config, use_dummy_weight=True,
+        quantization=None if args.quant == "none" else args.quant,
+        kv_cache_dtype=args.kv, page_size=args.page_size,
+        max_running_req=local_requests, max_extend_tokens=args.max_extend, memory_ratio=args.memory_ratio,
+        seed=1, cuda_graph_max_bs=(-1 if args.no_graph else None),
+        max_seq_len_override=max(4096, args.shared_prefix + args.in_max + args.out_len + 16), **par, **spec,
     )
     eng = llm.engine
     vocab = eng.model_config.vocab_size
@@ -281,7 +322,10 @@ def main() -> None:
     def make_prompts(seed: int):
         g = np.random.default_rng(seed)
         lens = g.integers(args.in_min, args.in_max + 1, size=args.requests)
-        return [g.integers(0, vocab, size=int(n), dtype=np.int32) for n in lens]
+        prefix = g.integers(0, vocab, size=args.shared_prefix, dtype=np.int32)
+        prompts = [np.concatenate([prefix, g.integers(0, vocab, size=int(n), dtype=np.int32)]) for n in lens]
+        # data-parallel replicas serve disjoint slices of the request set
+        return prompts[rank::world] if dp_ep else prompts
 
     def barrier():
         if world > 1:
@@ -316,7 +360,7 @@ def main() -> None:
         dev_ms = sum(s.elapsed_time(e) for s, e, _, _ in step_events)
         prefill_ms = sum(s.elapsed_time(e) for s, e, ph, _ in step_events if ph == "prefill")
         n_out = sum(len(o.token_ids) for o in outs)
-        assert n_out == args.requests * args.out_len, (n_out, args.requests * args.out_len)
+        assert n_out == len(prompts) * args.out_len, (n_out, len(prompts) * args.out_len)
         ttft = sorted((t_first[u] - t0) * 1e3 for u in t_first)
         tpot = sorted((t_last[u] - t_first[u]) * 1e3 / max(args.out_len - 1, 1) for u in t_first)
         n_steps = len(step_events)
@@ -349,6 +393,10 @@ def main() -> None:
     dev_ms = reduce_max(sum(r["dev_ms"] for r in results))
     wall_ms = reduce_max(sum(r["wall_ms"] for r in results))
     n_out = sum(r["n_out"] for r in results)
+    if dp_ep:  # every replica produced its own share of the output tokens
+        t = torch.tensor([float(n_out)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        n_out = int(t.item())
     value = n_out / (dev_ms / 1e3)
     e2e = n_out / (wall_ms / 1e3)
     last = results[-1]
@@ -358,14 +406,21 @@ def main() -> None:
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / BASELINE_TOK_S) if BASELINE_TOK_S else None,
-            "dtype": f"w4a8-mxfp4+{args.kv}-kv" if args.quant == "mxfp4" else ("bf16" if args.quant == "none" else args.quant),
+            "dtype": (f"w4a8-mxfp4+{args.kv}-kv" if args.quant == "mxfp4" else
+                      ("bf16" if args.quant == "none" else f"{args.quant}+{args.kv}-kv")),
             "data": "synthetic (uniform-random token ids, random-init weights seed 1)",
             "impl": "ours",
             "config": {
                 "model": f"{args.model}-shaped {'MoE' if eng.model_config.is_moe else 'dense'}, {args.quant}"
                          f"{' W4A8' if args.quant == 'mxfp4' else ''}, {args.kv} KV",
                 "global_batch": args.requests, "seq_len": f"in U[{args.in_min},{args.in_max}], out {args.out_len}",
-                "parallelism": f"tp{world}", "step": "one full pass of the workload (prefill + decode)",
+                "parallelism": (f"dp{world}+ep{world} (all-to-all over peer memory)" if dp_ep else f"tp{world}"),
+                "preset": args.config, "shared_prefix": args.shared_prefix,
+                "spec": ({"algorithm": args.spec, "draft": args.spec_draft, "tree_width": args.spec_tree_width,
+                          "verify_steps": llm.stats.get("spec_steps", 0),
+                          "accepted_per_step": (llm.stats.get("spec_emitted", 0) / max(llm.stats.get("spec_steps", 0), 1))}
+                         if args.spec != "none" else None),
+                "step": "one full pass of the workload (prefill + decode)",
                 "l2": "inputs larger than L2 (weights + KV pool >> 126 MB)",
                 "p50_ttft_ms": last["ttft_p50"], "p50_tpot_ms": last["tpot_p50"],
                 "prefill_ms_per_pass": last["prefill_ms"], "engine_steps_per_pass": last["steps"],

@@ -216,12 +216,24 @@ class Engine:
             from ..parallel.ep import EPContext, FusedEPContext
 
             self.ctx.ep = None
-            if dev_kind == "cuda" and mc.is_moe and not ENV.DISABLE_FUSED_COMM.value:
+            from ..layers.moe import MoELayer as _MoeCls
+
+            if (dev_kind == "cuda" and mc.is_moe and not ENV.DISABLE_FUSED_COMM.value
+                    and not _MoeCls.offload_slots):
                 try:
+                    kinds = {m._quant_kind or "bf16" for m in self.model.modules() if isinstance(m, _MoeCls)}
+                    kind = kinds.pop() if len(kinds) == 1 else "bf16"
+                    # regions for the largest step (a full prefill chunk) as long as they stay within
+                    # MSGL_EP_REGION_GIB per rank; the 16-bit return rows dominate: 2 bytes x hidden
+                    # x top_k x ranks per token
+                    per_token = mc.hidden_size * mc.num_experts_per_tok * config.dp_size * 3 + 64
+                    fit = int((ENV.EP_REGION_GIB.value << 30) // per_token)
+                    want = max(config.max_running_req, config.max_extend_tokens)
                     self.ctx.ep = FusedEPContext(
                         self.dp_group, self.dp_cpu_group, config.dp_rank, config.dp_size, self.device,
                         mc.hidden_size, mc.num_experts_per_tok, mc.num_experts // config.dp_size,
-                        max_tokens=min(config.max_running_req, 512))
+                        max_tokens=max(min(want, fit), min(config.max_running_req, 512)), kind=kind)
+                    self.ledger.add("expert exchange regions", self.ctx.ep.region_bytes)
                 except Exception as exc:
                     logger.warning("fused expert-parallel exchange unavailable (%s); using NCCL", exc)
             if self.ctx.ep is None:
@@ -237,9 +249,13 @@ class Engine:
         self.d2h_bytes = 0
         self.steps = 0
         self.graph_runner = None
-        # replicas that exchange expert rows every layer run eagerly: a captured graph would pin
-        # the row count of the exchange
-        ep_replicas = config.enable_ep and config.dp_size > 1
+        # Replicas that exchange expert rows every layer can only capture their decode step when
+        # the exchange itself is capturable (the peer-memory kernels with device-resident sequence
+        # numbers, under a fixed row bound); the NCCL gather / reduce form pins the agreed row count
+        # and runs eagerly.
+        from ..parallel.ep import FusedEPContext as _FusedEP
+
+        ep_replicas = config.enable_ep and config.dp_size > 1 and not isinstance(self.ctx.ep, _FusedEP)
         from ..layers.moe import MoELayer as _Moe
 
         host_tier = _Moe.offload_slots > 0   # expert residency is decided on the host every step
@@ -366,6 +382,9 @@ class Engine:
             return int(cfg.num_page_override)
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
         per_page = MHAKVCache.token_bytes(mc.num_layers, self.kv_heads_local, mc.head_dim, itemsize) * self.page_size
+        if cfg.spec_algorithm in ("eagle3", "mtp"):
+            # the draft head keeps one 16-bit, unsharded layer of K/V on the same page table
+            per_page += MHAKVCache.token_bytes(1, mc.num_kv_heads, mc.head_dim, 2) * self.page_size
         if self.device.type != "cuda":
             return 2048
         free, total = torch.cuda.mem_get_info(self.device)
@@ -471,6 +490,13 @@ class Engine:
         use_graph = (self.graph_runner is not None and batch.is_decode and not batch.spec_verify
                      and plan.max_q == 1 and self.graph_runner.can_run(bs)
                      and batch.capture_layers is None and n_sample == bs)
+        ep = self.ctx.ep
+        if use_graph and ep is not None and hasattr(ep, "static_bound"):
+            # the captured exchange works under the row bound of the largest bucket: a step in which
+            # some replica sends more rows than that (a prefill chunk elsewhere) runs eagerly, as
+            # does every step once the exchange fell back to NCCL
+            common = ep.common_tokens
+            use_graph = ep.healthy and common is not None and common <= self.graph_runner.max_bs
         if use_graph:
             gr = self.graph_runner
             bucket = gr.bucket_of(bs)
@@ -499,6 +525,8 @@ class Engine:
         token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
         batch.positions = positions
         batch.out_loc = out_loc
+        batch.token_idx = token_idx
+        batch.host_cu_q = plan.cu_q
         if use_graph:
             logits = self.graph_runner.replay(bs, token_idx, positions, out_loc, seq_lens, block_table)
         else:
@@ -527,12 +555,14 @@ class Engine:
                 and not ENV.SANITIZE_LOGITS.value):
             # plain greedy under tensor parallelism: shard arg-max + exchange of (max, index) pairs
             # instead of gathering rows x vocabulary fp32 logits on every rank
+            # every rank picks the winner from the same exchanged (max, index) pairs in rank order:
+            # the ids are identical by construction and need no further agreement
             sample = SampleOutput(head.argmax_from_local(logits))
+            tokens = sample.tokens
         else:
             logits = head.gather(logits)
             sample = self.sampler.sample(logits, args)
-        tokens = sample.tokens
-        tokens = self._agree_tokens(tokens)
+            tokens = self._agree_tokens(sample.tokens)
         self.token_pool.view(-1)[write_idx.long()] = tokens
         host = self._out_buffer(n_sample)
         event = None

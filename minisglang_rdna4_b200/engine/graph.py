@@ -82,6 +82,16 @@ class GraphRunner:
         from ..ops import cuda as K
 
         eng = self.engine
+        ep = getattr(eng.ctx, "ep", None)
+        if ep is not None and hasattr(ep, "static_bound"):
+            # Expert-parallel replicas run their warm-up forwards together (each one exchanges rows
+            # with every peer), under the row bound of the largest bucket. All replicas have the same
+            # bucket list, so they stay in step; the barrier removes the boot skew first.
+            import torch.distributed as dist
+
+            ep.static_bound = self.max_bs
+            ep.common_tokens = None
+            dist.barrier(group=eng.dp_cpu_group)
         dummy_slot = eng.kv_cache.dummy_page * eng.page_size
         self.out_loc.fill_(dummy_slot)
         self.token_idx.fill_((eng.num_slots - 1) * eng.max_seq_len)

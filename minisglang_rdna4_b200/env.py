@@ -134,6 +134,7 @@ ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-re
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
 ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of the fused reduce-scatter / all-gather GEMMs")
 ENV.flag("PDL", True, "programmatic dependent launch: a kernel's prologue overlaps the tail of the kernel ahead of it")
+ENV.int("EP_REGION_GIB", 6, "per-rank budget of the expert-parallel exchange regions (sets the largest fused step)")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger ones go to the row-sharded GEMM fusion or to NCCL")
 ENV.int("COMM_HEALTH_STEPS", 8, "the tensor-parallel ranks agree on the collectives' status word every this many steps")
@@ -141,6 +142,7 @@ ENV.int("COMM_WAIT_US", 500_000, "bound of every device-side flag wait, in micro
 # --- speculative decode -------------------------------------------------------------------
 ENV.flag("SPEC_SAMPLED", False, "verify drafts by rejection sampling instead of greedy prefix match")
 ENV.int("SPEC_MAX_BS", 0, "largest batch that still runs a speculative step (0 = per-algorithm default)")
+ENV.flag("SPEC_HOST_STEP", False, "run the speculative step through the host-driven path even on a GPU")
 ENV.flag("SPEC_ADAPTIVE_WIDTH", True, "choose the verify width from the running acceptance rate")
 # --- quantization -------------------------------------------------------------------------
 ENV.flag("MOE_W4A16", False, "run int4/fp4 expert weights against 16-bit activations")

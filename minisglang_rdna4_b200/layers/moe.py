@@ -94,6 +94,8 @@ class MoELayer(BaseOP):
     def expert_weights(self):
         """``(kind, tensors)`` of the resident expert stacks for the grouped-GEMM pipeline
         (``ops.moe_kernels.run_experts``)."""
+        if getattr(self, "_tier", None) is not None:
+            raise RuntimeError("experts paged in from the host tier have no resident stack")
         packed = getattr(self, "_packed", None)
         if packed is not None:
             return self._quant_kind, packed

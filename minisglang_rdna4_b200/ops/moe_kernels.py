@@ -170,42 +170,46 @@ def gemm_grouped_w8a8(a_q, a_scale, b_q, b_scale, tile_expert, out_dtype=torch.b
     return out
 
 
-def experts_w8a8(xs, tile_expert, w13_q, w13_s, w2_q, w2_s, out_dtype):
-    """The two expert GEMMs on expert-sorted rows ``xs`` for per-channel fp8 experts
-    (python/minisgl/quant/kernels.py:1181-1331)."""
-    xq, xsc = K.per_token_quant_fp8(xs)
-    hcur = gemm_grouped_w8a8(xq, xsc, w13_q, w13_s, tile_expert, out_dtype)
-    aq, asc = K.silu_and_mul_quant(hcur)
-    return gemm_grouped_w8a8(aq, asc, w2_q, w2_s, tile_expert, out_dtype)
+# How the rows entering the expert MLPs are quantised, per kind of expert stack:
+# 0 = 16-bit rows, 1 = e4m3 + one scale per token, 2 = e4m3 + one scale per 128 elements
+ROW_QUANT = {"bf16": 0, "mxfp4": 1, "fp8_channel": 1, "fp8_block": 2}
 
 
-def experts_fp8_block(xs, tile_expert, w13_q, w13_s, w2_q, w2_s, out_dtype):
-    """The two expert GEMMs for block-scaled fp8 experts (128 x 128 weight blocks, 1 x 128
-    activation groups; python/minisgl/quant/method.py:846-897)."""
-    xq, xsc = K.per_group_quant_fp8(xs, 128)
-    hcur = K.gemm_fp8_block(xq, xsc, w13_q, w13_s, out_dtype, tile_expert=tile_expert)
-    aq, asc = K.silu_and_mul_quant_group(hcur)
-    return K.gemm_fp8_block(aq, asc, w2_q, w2_s, out_dtype, tile_expert=tile_expert)
+def quantise_rows(kind: str, xs):
+    mode = ROW_QUANT[kind]
+    if mode == 0:
+        return xs, None
+    if mode == 1:
+        return K.per_token_quant_fp8(xs)
+    return K.per_group_quant_fp8(xs, 128)
 
 
-def experts_w4a8(xs, tile_expert, w13_packed, w13_atoms, w2_packed, w2_atoms, out_dtype):
-    xq, xsc = K.per_token_quant_fp8(xs)
-    hcur = gemm_grouped_w4a8(xq, xsc, w13_packed, w13_atoms, tile_expert, out_dtype)
-    aq, asc = K.silu_and_mul_quant(hcur)
-    return gemm_grouped_w4a8(aq, asc, w2_packed, w2_atoms, tile_expert, out_dtype)
-
-
-def experts_bf16(xs, tile_expert, w13, w2, out_dtype):
-    return gemm_grouped(K.act_and_mul(gemm_grouped(xs, w13, tile_expert)), w2, tile_expert)
-
-
-EXPERT_KERNELS = {"bf16": experts_bf16, "mxfp4": experts_w4a8, "fp8_channel": experts_w8a8,
-                  "fp8_block": experts_fp8_block}
+def run_experts_q(kind: str, xq, xsc, tile_expert, weights, out_dtype):
+    """The two expert GEMMs with SiLU·mul (+ re-quantisation) between them, on expert-sorted rows
+    that are already in the input form of ``kind`` (``quantise_rows``): 16-bit rows for ``bf16``,
+    e4m3 rows with their scales otherwise (python/minisgl/quant/kernels.py:562-873,1181-1331)."""
+    if kind == "bf16":
+        w13, w2 = weights
+        return gemm_grouped(K.act_and_mul(gemm_grouped(xq, w13, tile_expert)), w2, tile_expert)
+    if kind == "mxfp4":
+        p13, a13, p2, a2 = weights
+        aq, asc = K.silu_and_mul_quant(gemm_grouped_w4a8(xq, xsc, p13, a13, tile_expert, out_dtype))
+        return gemm_grouped_w4a8(aq, asc, p2, a2, tile_expert, out_dtype)
+    if kind == "fp8_channel":
+        q13, s13, q2, s2 = weights
+        aq, asc = K.silu_and_mul_quant(gemm_grouped_w8a8(xq, xsc, q13, s13, tile_expert, out_dtype))
+        return gemm_grouped_w8a8(aq, asc, q2, s2, tile_expert, out_dtype)
+    if kind == "fp8_block":
+        q13, s13, q2, s2 = weights
+        aq, asc = K.silu_and_mul_quant_group(K.gemm_fp8_block(xq, xsc, q13, s13, out_dtype, tile_expert=tile_expert))
+        return K.gemm_fp8_block(aq, asc, q2, s2, out_dtype, tile_expert=tile_expert)
+    raise ValueError(kind)
 
 
 def run_experts(kind: str, xs, tile_expert, weights, out_dtype):
-    """Expert MLPs of kind ``bf16 | mxfp4 | fp8_channel | fp8_block`` on expert-sorted rows."""
-    return EXPERT_KERNELS[kind](xs, tile_expert, *weights, out_dtype)
+    """Expert MLPs of kind ``bf16 | mxfp4 | fp8_channel | fp8_block`` on 16-bit expert-sorted rows."""
+    xq, xsc = quantise_rows(kind, xs)
+    return run_experts_q(kind, xq, xsc, tile_expert, weights, out_dtype)
 
 
 def moe_forward_quant(kind: str, x, weights, topk_w, topk_ids, expert_offset=0):

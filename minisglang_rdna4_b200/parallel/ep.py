@@ -53,42 +53,63 @@ class EPContext:
 
 class FusedEPContext(EPContext):
     """Expert-parallel exchange on the peer-memory kernels of ``csrc/ep_a2a.cu``: only the rows
-    an expert owner needs are stored into its receive region (dispatch), and only the expert
-    outputs go back (combine, with the gate-weighted sum applied on arrival). Used for steps of
-    up to ``max_tokens`` rows per rank (decode and small prefills); larger steps take the
-    gather/reduce baseline of the parent class. Works for DP+EP (ranks = replicas) and for
-    EP over TP (ranks = tensor-parallel ranks, every rank dispatching only its own row slice)."""
+    an expert owner needs are stored into its receive region (dispatch, quantised to the input
+    form of the expert stack on the way out: e4m3 with one scale per token or per 128 elements),
+    and only the expert outputs go back (combine, with the gate-weighted sum applied on arrival).
+
+    Shapes are static: the regions hold ``max_tokens * top_k`` rows per source, and every step
+    works under a bound ``active`` (rows any source can send this step) that is the same on all
+    ranks: the agreed row count of the lock-step scheduler for eager steps, the largest graph
+    bucket inside captured decode graphs. Sequence numbers and slot cursors live on the device,
+    so a captured graph replays the exchange unchanged. Steps above ``max_tokens`` rows, and every
+    step after a bounded wait has run out, take the gather / reduce baseline of the parent class.
+    Works for DP+EP (ranks = replicas) and for EP over TP."""
 
     def __init__(self, group, cpu_group, rank: int, size: int, device, hidden: int, top_k: int,
-                 experts_per_rank: int, max_tokens: int = 256) -> None:
+                 experts_per_rank: int, max_tokens: int = 256, kind: str = "bf16") -> None:
         super().__init__(group, rank, size)
         import ctypes
 
         from ..env import ENV
         from ..ops._lib import bind, c_i, c_ll, c_p, lib
+        from ..ops.moe_kernels import ROW_QUANT
         from .symm import SymmetricHeap
 
         bind("msgl_ep_region_bytes", c_ll, [c_i, c_i, c_i, c_i])
-        bind("msgl_ep_dispatch", c_i, [c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p])
-        bind("msgl_ep_recv_prepare", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_ll, c_p])
-        bind("msgl_ep_return", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p])
-        bind("msgl_ep_combine", c_i, [c_p, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_p])
+        bind("msgl_ep_dispatch", c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p])
+        bind("msgl_ep_recv_prepare", c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_ll, c_p])
+        bind("msgl_ep_gather", c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p])
+        bind("msgl_ep_return", c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p])
+        bind("msgl_ep_combine", c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_p])
         bind("msgl_ep_status", c_i, [c_i])
         self.device = torch.device(device)
         self.hidden, self.top_k, self.experts_per_rank = hidden, top_k, experts_per_rank
+        self.kind = kind
+        self.qmode = ROW_QUANT[kind] if hidden % 128 == 0 and hidden <= 8192 else 0
         self.max_tokens = max_tokens
         self.cap = max_tokens * top_k
-        nbytes = int(lib().msgl_ep_region_bytes(size, self.cap, hidden, 2))
+        nbytes = int(lib().msgl_ep_region_bytes(size, self.cap, hidden, self.qmode))
         self.heap = SymmetricHeap(nbytes, cpu_group, rank, size)
         self._bases = (ctypes.c_void_p * size)(*self.heap.ptrs)
         self._state = torch.zeros(size + 4, dtype=torch.int32, device=self.device)
         self.wait_us = ENV.COMM_WAIT_US.value
         self.healthy = True
         self.fused_calls = 0
+        self.static_bound: Optional[int] = None   # row bound while decode graphs are captured / replayed
+        self.region_bytes = nbytes
+
+    def step_bound(self, n_local: int) -> int:
+        """Rows any rank may send in this step (identical on every rank)."""
+        if self.common_tokens is not None:
+            return int(self.common_tokens)
+        if self.static_bound is not None:
+            return int(self.static_bound)
+        return self.max_tokens
 
     def dispatch_compute_combine(self, moe, x, topk_w, topk_ids):
         n = x.shape[0]
-        if (not self.healthy or not x.is_cuda or n > self.max_tokens or n == 0 or x.dtype not in (
+        bound = self.step_bound(n)
+        if (not self.healthy or not x.is_cuda or bound > self.max_tokens or n > bound or n == 0 or x.dtype not in (
                 torch.bfloat16, torch.float16)):
             return super().dispatch_compute_combine(moe, x, topk_w, topk_ids)
         from ..ops import cuda as K
@@ -98,32 +119,44 @@ class FusedEPContext(EPContext):
         L = lib()
         dt = 0 if x.dtype == torch.bfloat16 else 1
         st = K._stream()
+        kind, weights = moe.expert_weights()
+        qmode = self.qmode
+        if qmode not in (0, MK.ROW_QUANT[kind]):
+            raise RuntimeError(f"expert stack of kind {kind!r} against an exchange set up for {self.kind!r}")
+        active = bound * self.top_k
         x = x.contiguous()
         ids = topk_ids.contiguous()
         send_slot = torch.empty(n * self.top_k, dtype=torch.int32, device=x.device)
-        check(L.msgl_ep_dispatch(self._bases, self.rank, self.size, self.cap, x.data_ptr(), ids.data_ptr(),
-                                 send_slot.data_ptr(), self._state.data_ptr(), n, self.hidden, self.top_k,
-                                 self.experts_per_rank, dt, st), "ep_dispatch")
-        flat = self.size * self.cap
+        check(L.msgl_ep_dispatch(self._bases, self.rank, self.size, self.cap, active, qmode, x.data_ptr(),
+                                 ids.data_ptr(), send_slot.data_ptr(), self._state.data_ptr(), n, self.hidden,
+                                 self.top_k, self.experts_per_rank, dt, st), "ep_dispatch")
+        flat = self.size * active
         expert_ids = torch.empty(flat, dtype=torch.int32, device=x.device)
-        check(L.msgl_ep_recv_prepare(self._bases, self.rank, self.size, self.cap, self.hidden, expert_ids.data_ptr(),
-                                     self._state.data_ptr(), self.wait_us, st), "ep_recv_prepare")
+        check(L.msgl_ep_recv_prepare(self._bases, self.rank, self.size, self.cap, active, qmode, self.hidden,
+                                     expert_ids.data_ptr(), self._state.data_ptr(), self.wait_us, st),
+              "ep_recv_prepare")
         sorted_pair, pair_row, tile_expert, _meta = MK.moe_align(expert_ids.view(-1, 1), 0, self.experts_per_rank)
         rows = sorted_pair.numel()
-        xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=x.device)
-        check(L.msgl_moe_permute(self.heap.local, sorted_pair.data_ptr(), xs.data_ptr(), self.hidden, 1, rows, dt, st),
-              "ep permute")
-        tier_w13, tier_w2 = moe.w13, moe.w2
-        hcur = MK.gemm_grouped(xs, tier_w13, tile_expert)
-        act = K.act_and_mul(hcur)
-        y = MK.gemm_grouped(act, tier_w2, tile_expert)
-        check(L.msgl_ep_return(self._bases, self.rank, self.size, self.cap, self.hidden, y.data_ptr(),
+        if qmode == 0:
+            xq = torch.empty((rows, self.hidden), dtype=x.dtype, device=x.device)
+            xsc = None
+        else:
+            xq = torch.empty((rows, self.hidden), dtype=torch.float8_e4m3fn, device=x.device)
+            nscale = 1 if qmode == 1 else self.hidden // 128
+            xsc = torch.empty((rows,) if qmode == 1 else (rows, nscale), dtype=torch.float32, device=x.device)
+        check(L.msgl_ep_gather(self._bases, self.rank, self.size, self.cap, active, qmode, self.hidden,
+                               sorted_pair.data_ptr(), xq.data_ptr(), None if xsc is None else xsc.data_ptr(), rows,
+                               st), "ep_gather")
+        if qmode == 0:
+            xq, xsc = MK.quantise_rows(kind, xq)
+        y = MK.run_experts_q(kind, xq, xsc, tile_expert, weights, x.dtype)
+        check(L.msgl_ep_return(self._bases, self.rank, self.size, self.cap, active, qmode, self.hidden, y.data_ptr(),
                                pair_row.data_ptr(), self._state.data_ptr(), dt, st), "ep_return")
         out = torch.empty_like(x)
-        check(L.msgl_ep_combine(self._bases, self.rank, self.size, self.cap, self.hidden, topk_w.contiguous().data_ptr(),
-                                send_slot.data_ptr(), out.data_ptr(), self._state.data_ptr(), n, self.top_k,
-                                self.wait_us, dt, st), "ep_combine")
-        K._count("ep_all_to_all", "ep_dispatch+ep_recv_prepare+ep_return+ep_combine", 4)
+        check(L.msgl_ep_combine(self._bases, self.rank, self.size, self.cap, qmode, self.hidden,
+                                topk_w.contiguous().data_ptr(), send_slot.data_ptr(), out.data_ptr(),
+                                self._state.data_ptr(), n, self.top_k, self.wait_us, dt, st), "ep_combine")
+        K._count("ep_all_to_all", "ep_dispatch+ep_recv_prepare+ep_gather+ep_return+ep_combine", 5)
         self.fused_calls += 1
         self.calls += 1
         return out

@@ -81,6 +81,9 @@ class Scheduler:
 
             self.proposer = make_proposer(config, self)
             self._use_overlap = False
+            from .spec_step import device_runner
+
+            device_runner(self)   # GPU engines: build the on-device step and capture its graphs at boot
 
     # ------------------------------------------------------------------ I/O hooks
     def receive_msg(self, blocking: bool) -> List[BaseMsg]:
@@ -530,6 +533,15 @@ class Scheduler:
         prop = self.proposer
         aux = self.engine.ctx.aux_hidden
         if not hasattr(prop, "on_features") or not aux:
+            return
+        from .spec_step import _engine_stream, device_runner
+
+        runner = device_runner(self)
+        if runner is not None and runner.draft is not None:
+            # batched draft update on the device: same rows, positions and K/V slots as the step
+            slots = np.fromiter((r.table_idx for r in batch.reqs), dtype=np.int64, count=len(batch.reqs))
+            with _engine_stream(self.engine):
+                runner.feed_prefill(batch, batch.token_idx, slots, batch.host_cu_q)
             return
         cu, starts = self._feature_meta
         carry = getattr(self, "_feature_carry", None)

@@ -69,8 +69,89 @@ def spec_decode_step(sched) -> None:
     if len(reqs) > limit or not all(req_spec_ok(sched, r) for r in reqs):
         _plain_decode_step(sched)
         return
+    runner = device_runner(sched)
     with _engine_stream(sched.engine):
-        _spec_decode_step_on_stream(sched, proposer, reqs)
+        if runner is not None and all(r.sampling_params.is_greedy for r in reqs):
+            _device_spec_step(sched, proposer, runner, reqs)
+        else:
+            _spec_decode_step_on_stream(sched, proposer, reqs)
+
+
+def device_runner(sched):
+    """The GPU runner of the speculative step (``spec.device.DeviceSpecRunner``), built on first
+    use: chain drafting with the n-gram proposer or the EAGLE3 / MTP head on a CUDA engine. Tree
+    verification and CPU engines keep the host-driven step below."""
+    runner = getattr(sched, "_spec_runner", False)
+    if runner is not False:
+        return runner
+    runner = None
+    eng, proposer = sched.engine, sched.proposer
+    if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and getattr(proposer, "tree_width", 1) <= 1
+            and proposer.num_draft >= 1):
+        from ..spec.device import DeviceSpecRunner
+
+        draft = getattr(proposer, "draft", None)
+        with _engine_stream(eng):
+            runner = DeviceSpecRunner(eng, proposer.num_draft, draft, getattr(proposer, "capture_layers", None),
+                                      max_batch=ENV.SPEC_MAX_BS.value or proposer.max_batch)
+            runner.capture()
+    sched._spec_runner = runner
+    return runner
+
+
+def _device_spec_step(sched, proposer, runner, reqs: List[Req]) -> None:
+    """Host side of a step that runs entirely on the device: build the tables, replay, read the
+    acceptance record, do the length bookkeeping and reply."""
+    from ..utils import cdiv
+
+    ps = sched.page_size
+    K = runner.K
+    host_drafts = runner.draft is None
+    drafts = proposer.propose(reqs) if host_drafts else None
+    rows, staged = [], []
+    for i, r in enumerate(reqs):
+        budget = proposer.budget(r)
+        k = min(len(drafts[i]), budget) if host_drafts else budget
+        c = r.cached_len
+        end = r.device_len + k                      # positions c .. c + k get target K/V
+        have = sched.alloc_len.get(r.uid, r.cache_handle.cached_len)
+        if end > have:
+            first, last = cdiv(have, ps), cdiv(end, ps)
+            if last > first:
+                sched.cache.page_table[r.table_idx, first:last] = sched.cache._take(last - first)
+            sched.alloc_len[r.uid] = end
+        n_pages = cdiv(end, ps)
+        rows.append(dict(slot=r.table_idx, c=c, k=k, alloc_end=end, ignore_eos=r.sampling_params.ignore_eos,
+                         max_emit=max(1, r.sampling_params.max_tokens - r.num_generated),
+                         pages=sched.cache.page_table[r.table_idx, :n_pages]))
+        staged.append(list(drafts[i][:k]) if host_drafts else [])
+    record = runner.run(rows, staged)
+    sched.stats["steps"] += 1
+    sched.stats["spec_steps"] += 1
+    sched.stats["decode_tokens"] += len(reqs) * runner.W
+    replies: List[DetokenizeMsg] = []
+    for i, r in enumerate(reqs):
+        n, hit_eos = int(record[i, 0]), bool(record[i, 1])
+        emitted = record[i, 2:2 + n].tolist()
+        sched.stats["spec_drafted"] += rows[i]["k"]
+        sched.stats["spec_accepted"] += n - 1
+        sched.stats["spec_emitted"] += n
+        r.append_host(torch.from_numpy(record[i, 2:2 + n].copy()))
+        r.complete_many(n)
+        proposer.on_accept(r, emitted)
+        finished = hit_eos or r.num_generated >= r.sampling_params.max_tokens
+        reason = "stop" if hit_eos else ("length" if finished else None)
+        for j, t in enumerate(emitted):
+            last = j == n - 1
+            replies.append(DetokenizeMsg(r.uid, t, finished and last, reason if last else None,
+                                         prompt_tokens=r.prompt_len, cached_tokens=sched.prefix_len.get(r.uid, 0)))
+        if finished:
+            r.finished, r.finish_reason = True, reason
+            proposer.on_finish(r)
+            sched._free_req_resources(r, insert=True)
+    sched.decode.filter_finished()
+    if replies:
+        sched.send_result(replies)
 
 
 def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:

@@ -122,7 +122,97 @@ def test_tp2_fused_paths_track_nccl_only_path():
     assert same_first >= len(fused) - 1, (fused, nccl)
 
 
-@pytest.mark.parametrize("quant", [None, "mxfp4"])
+def _moe_cfg():
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    return ModelConfig(
+        num_layers=2, num_qo_heads=8, num_kv_heads=2, head_dim=128, hidden_size=512, vocab_size=2048,
+        intermediate_size=1024, rms_norm_eps=1e-6,
+        rotary_config=RotaryConfig(head_dim=128, rotary_dim=128, max_position=2048, base=1e6),
+        model_type="qwen3_moe", architectures=("Qwen3MoeForCausalLM",), qk_norm=True, max_position_embeddings=2048,
+        num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True,
+    )
+
+
+def _moe_hf_cfg():
+    return dict(model_type="qwen3_moe", architectures=["Qwen3MoeForCausalLM"], num_hidden_layers=2, hidden_size=512,
+                num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=1024, vocab_size=2048,
+                rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=2048, tie_word_embeddings=False,
+                torch_dtype="bfloat16", num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256,
+                norm_topk_prob=True)
+
+
+def _dp_ep_worker(rank, world, port, ckpt, out_q):
+    import os
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import cuda as K
+
+    llm = LLM(model_path=ckpt, device="cuda", dp_size=world, dp_rank=rank, enable_ep=True, page_size=16,
+              max_running_req=8, num_page_override=256, seed=0)
+    prompts = _prompts()[rank::world]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    ep = llm.engine.ctx.ep
+    ok = K.gemm_status() == 0 and K.attn_status() == 0 and ep.check_health()
+    out_q.put((rank, [o.token_ids for o in outs], ok, getattr(ep, "fused_calls", 0),
+               llm.engine.graph_runner.replays if llm.engine.graph_runner is not None else -1))
+    llm.shutdown()
+
+
+def test_dp_ep_replicas_match_one_replica():
+    """Two replicas, each holding half of the experts of one checkpoint, exchanging rows through
+    the peer-memory all-to-all with captured decode graphs: their greedy output equals that of one
+    engine that holds all experts."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import os
+    import tempfile
+
+    import torch.multiprocessing as mp
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models import ModelConfig, create_model
+    from minisglang_rdna4_b200.models.weight import save_dummy_checkpoint
+
+    with tempfile.TemporaryDirectory() as tmp:
+        cfgd = _moe_hf_cfg()
+        model = create_model(ModelConfig.from_hf(cfgd), torch.bfloat16, "cpu")
+        model.init_dummy(seed=7, std=0.05)
+        save_dummy_checkpoint(model, tmp, cfgd)
+        llm = LLM(model_path=tmp, device="cuda", page_size=16, max_running_req=8, num_page_override=256, seed=0)
+        want = [o.token_ids for o in llm.generate(_prompts(), SamplingParams(temperature=0.0, max_tokens=10,
+                                                                             ignore_eos=True))]
+        llm.shutdown()
+        del llm
+        torch.cuda.empty_cache()
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 27100 + os.getpid() % 500
+        procs = [ctx.Process(target=_dp_ep_worker, args=(r, 2, port, tmp, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = {}
+        for _ in procs:
+            rank, toks, ok, fused, replays = q.get(timeout=420)
+            assert ok and fused > 0 and replays > 0, (rank, ok, fused, replays)
+            got[rank] = toks
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    merged = [None] * len(want)
+    for r in (0, 1):
+        for i, t in enumerate(got[r]):
+            merged[r + 2 * i] = t
+    same_first = sum(a[:4] == b[:4] for a, b in zip(merged, want))
+    assert same_first >= len(want) - 1, (merged, want)
+
+
+@pytest.mark.parametrize("quant", [None, "mxfp4", "fp8_block", "fp8"])
 def test_moe_model_graph_matches_eager(quant):
     """A small Qwen3-MoE-shaped model end to end on the GPU: fused routing, grouped expert GEMMs
     (16-bit, or W4A8 MXFP4 experts when quantised) and the gate-weighted combine, with CUDA-graph
@@ -185,8 +275,8 @@ def test_gemma_style_model_tracks_fp32_oracle():
     assert first_ok >= len(want) - 1, (got, want)
 
 
-@pytest.mark.parametrize("quant,kv", [(None, "bf16"), ("mxfp4", "fp8")])
-def test_speculative_decoding_is_exact_on_the_gpu(quant, kv):
+@pytest.mark.parametrize("quant,kv,layers", [(None, "bf16", 2), ("mxfp4", "fp8", 2), (None, "bf16", 12)])
+def test_speculative_decoding_is_exact_on_the_gpu(quant, kv, layers):
     """Greedy output with a proposer (n-gram, EAGLE3 draft head) equals plain greedy decoding on
     the kernel path: verify rows go through the tree-mask attention kernel and the same GEMM code
     path as decode rows."""
@@ -195,8 +285,8 @@ def test_speculative_decoding_is_exact_on_the_gpu(quant, kv):
     from minisglang_rdna4_b200.ops import cuda as K
 
     def make(**kw):
-        return LLM(model_config=_cfg(), use_dummy_weight=True, quantization=quant, kv_cache_dtype=kv, device="cuda",
-                   page_size=16, max_running_req=8, num_page_override=256, seed=0, **kw)
+        return LLM(model_config=_cfg(layers=layers), use_dummy_weight=True, quantization=quant, kv_cache_dtype=kv,
+                   device="cuda", page_size=16, max_running_req=8, num_page_override=256, seed=0, **kw)
 
     from minisglang_rdna4_b200.spec.base import Proposer
 
@@ -221,9 +311,22 @@ def test_speculative_decoding_is_exact_on_the_gpu(quant, kv):
         got = [o.token_ids for o in spec.generate(prompts, sp)]
         assert K.gemm_status() == 0 and K.attn_status() == 0
         assert spec.stats["spec_steps"] > 0 and spec.stats["spec_drafted"] > 0
+        # the step ran on the device (propose / verify / accept in one captured graph per bucket)
+        assert spec._spec_runner is not None and spec._spec_runner.replays > 0
+        assert "spec_accept" in K.LEDGER
         spec.cache.check_integrity()
         spec.shutdown()
         assert got == want, algo
+    # the host-driven step (tree verification, sampled acceptance) stays exact as well
+    import os
+
+    os.environ["MSGL_SPEC_HOST_STEP"] = "1"
+    try:
+        host = make(spec_algorithm="ngram", spec_num_draft=4)
+        assert [o.token_ids for o in host.generate(prompts, sp)] == want
+        host.shutdown()
+    finally:
+        os.environ.pop("MSGL_SPEC_HOST_STEP", None)
 
 
 def test_host_expert_tier_matches_resident_experts_on_the_gpu():

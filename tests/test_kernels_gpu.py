@@ -559,3 +559,50 @@ def test_moe_forward_fp8_kinds(K):
     q0, s0 = K.per_group_quant_fp8(K.act_and_mul(hcur), 128)
     _close(s, s0, 1e-3, 0, "group scales")
     _close(q.float() * s.repeat_interleave(128, 1), q0.float() * s0.repeat_interleave(128, 1), 0.13, 1e-3, "group q")
+
+
+def test_spec_accept_kernel_matches_the_host_rules(K):
+    """On-device acceptance, EOS / length truncation and commit against ``spec.accept``."""
+    import ctypes
+
+    from minisglang_rdna4_b200.ops._lib import check, lib
+    from minisglang_rdna4_b200.spec.accept import accept_greedy, eos_truncate
+    from minisglang_rdna4_b200.spec.device import _bind
+
+    _bind()
+    g = torch.Generator().manual_seed(0)
+    B, W, msl = 37, 5, 64
+    pool = torch.randint(0, 50, (B + 1, msl), generator=g, dtype=torch.int32)
+    target = torch.randint(0, 6, (B, W), generator=g, dtype=torch.int32)
+    c = torch.randint(3, 40, (B,), generator=g)
+    k = torch.randint(0, W, (B,), generator=g)
+    max_emit = torch.randint(1, 7, (B,), generator=g)
+    ignore = torch.randint(0, 2, (B,), generator=g)
+    for b in range(B):  # make some drafts stand
+        good = int(torch.randint(0, W, (1,), generator=g))
+        pool[b, c[b] + 1: c[b] + 1 + good] = target[b, :good]
+    eos = [3, 4]
+    want_pool = pool.clone()
+    want = []
+    for b in range(B):
+        drafts = pool[b, c[b] + 1: c[b] + 1 + int(k[b])].tolist()
+        em = accept_greedy(target[b].tolist(), drafts)
+        em = em[: max(1, min(len(em), int(max_emit[b])))]
+        em, hit = eos_truncate(em, set(eos), bool(ignore[b]))
+        want.append((len(em), int(hit), em))
+        want_pool[b, c[b] + 1: c[b] + 1 + len(em)] = torch.tensor(em, dtype=torch.int32)
+    dev = "cuda"
+    d_pool = pool.to(dev)
+    rec = torch.zeros(B * (W + 2), dtype=torch.int32, device=dev)
+    sel = torch.zeros(B, dtype=torch.int32, device=dev)
+    first = (torch.arange(B) * msl + c + 1).to(torch.int32).to(dev)
+    eos_arr = (ctypes.c_int * 8)(*(eos + [-1] * 6))
+    check(lib().msgl_spec_accept(target.to(dev).data_ptr(), d_pool.data_ptr(), first.data_ptr(),
+                                 k.to(torch.int32).to(dev).data_ptr(), max_emit.to(torch.int32).to(dev).data_ptr(),
+                                 ignore.to(torch.int32).to(dev).data_ptr(), rec.data_ptr(), sel.data_ptr(), eos_arr,
+                                 2, B, W, torch.cuda.current_stream().cuda_stream), "spec_accept")
+    rec = rec.cpu().view(B, W + 2)
+    for b, (n, hit, em) in enumerate(want):
+        assert int(rec[b, 0]) == n and int(rec[b, 1]) == hit and rec[b, 2:2 + n].tolist() == em, b
+        assert int(sel[b]) == b * W + n - 1
+    assert torch.equal(d_pool.cpu(), want_pool)

@@ -207,6 +207,8 @@ class Context:
     ep: Any = None
     comm: Any = None
     aux_hidden: Optional[List[torch.Tensor]] = None
+    # recurrent state of gated-delta-net layers (kvcache.gdn_state.GDNStateCache), hybrid models only
+    gdn_state: Any = None
     _batch: Optional[Batch] = None
 
     @property

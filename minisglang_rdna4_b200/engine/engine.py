@@ -179,14 +179,16 @@ class Engine:
         self.num_pages = self._determine_num_pages()
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
+        # hybrid models keep K/V pages for their full-attention layers only
+        self.kv_layers = mc.num_layers - mc.num_linear_layers
         self.kv_cache = MHAKVCache(
-            mc.num_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
+            self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
             self.dtype, self.device, fp8=self.kv_fp8,
         )
         if self.kv_fp8:
             from ..kvcache.fp8_scales import resolve_kv_scales
 
-            ks, vs, source = resolve_kv_scales(config.model_path, mc.num_layers, mc.num_kv_heads, config.tp_rank,
+            ks, vs, source = resolve_kv_scales(config.model_path, self.kv_layers, mc.num_kv_heads, config.tp_rank,
                                                config.tp_size)
             self.kv_cache.set_scales(ks, vs)
             logger.info_rank0("fp8 KV scales: %s", source)
@@ -197,6 +199,18 @@ class Engine:
         self.token_pool = torch.zeros((self.num_slots, self.max_seq_len), dtype=torch.int32, device=self.device)
         self.ctx = Context(page_size=self.page_size)
         self.ctx.kv_cache = self.kv_cache
+        self.gdn_state = None
+        if mc.is_recurrent:
+            from ..kvcache.gdn_state import GDNStateCache
+
+            conv_dim = 2 * mc.linear_num_key_heads * mc.linear_key_head_dim + \
+                mc.linear_num_value_heads * mc.linear_value_head_dim
+            self.gdn_state = GDNStateCache(mc.num_linear_layers, self.num_slots, conv_dim, mc.linear_conv_kernel_dim,
+                                           mc.linear_num_value_heads, mc.linear_key_head_dim,
+                                           mc.linear_value_head_dim, self.dtype, self.device)
+            self.ledger.add("recurrent state", self.gdn_state.conv.numel() * self.gdn_state.conv.element_size()
+                            + self.gdn_state.ssm.numel() * 4)
+        self.ctx.gdn_state = self.gdn_state
         self.ctx.attn_backend = create_attention_backend(
             config.attention_backend, self.q_heads_local, self.kv_heads_local, mc.head_dim, self.device,
             max_batch=config.max_running_req, max_seq_len=self.max_seq_len,
@@ -381,7 +395,8 @@ class Engine:
         if cfg.num_page_override is not None:
             return int(cfg.num_page_override)
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
-        per_page = MHAKVCache.token_bytes(mc.num_layers, self.kv_heads_local, mc.head_dim, itemsize) * self.page_size
+        per_page = MHAKVCache.token_bytes(mc.num_layers - mc.num_linear_layers, self.kv_heads_local, mc.head_dim,
+                                          itemsize) * self.page_size
         if cfg.spec_algorithm in ("eagle3", "mtp"):
             # the draft head keeps one 16-bit, unsharded layer of K/V on the same page table
             per_page += MHAKVCache.token_bytes(1, mc.num_kv_heads, mc.head_dim, 2) * self.page_size
@@ -393,6 +408,14 @@ class Engine:
         widest = max(2 * mc.intermediate_size // cfg.tp_size, mc.q_size + 2 * mc.kv_size, mc.hidden_size * 4)
         act_reserve = chunk * widest * 2 * 4 + (2 << 30)
         budget = int(total * cfg.memory_ratio) - (total - free) - act_reserve
+        if mc.is_recurrent:
+            from ..kvcache.gdn_state import GDNStateCache
+
+            conv_dim = 2 * mc.linear_num_key_heads * mc.linear_key_head_dim + \
+                mc.linear_num_value_heads * mc.linear_value_head_dim
+            budget -= (cfg.max_running_req + 1) * GDNStateCache.slot_bytes(
+                mc.num_linear_layers, conv_dim, mc.linear_conv_kernel_dim, mc.linear_num_value_heads,
+                mc.linear_key_head_dim, mc.linear_value_head_dim, 2)
         pages = budget // per_page
         if self.cpu_group is not None:
             t = torch.tensor([pages], dtype=torch.int64)
@@ -527,6 +550,12 @@ class Engine:
         batch.out_loc = out_loc
         batch.token_idx = token_idx
         batch.host_cu_q = plan.cu_q
+        if self.gdn_state is not None and not use_graph:
+            # state slot of every request (its row of the token pool) and whether it already has a
+            # state: a request whose step starts at position 0 begins from zeros
+            first = cu_q[:-1].long()
+            batch.gdn_slots = (token_idx[first] // self.max_seq_len).to(torch.int32)
+            batch.gdn_has_state = (positions[first] > 0).to(torch.int32)
         if use_graph:
             logits = self.graph_runner.replay(bs, token_idx, positions, out_loc, seq_lens, block_table)
         else:

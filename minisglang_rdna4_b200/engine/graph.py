@@ -71,6 +71,9 @@ class GraphRunner:
         batch.positions = self.positions[:bs]
         batch.out_loc = self.out_loc[:bs]
         batch.input_ids = eng.token_pool.view(-1)[self.token_idx[:bs].long()]
+        if eng.gdn_state is not None:
+            batch.gdn_slots = (self.token_idx[:bs] // eng.max_seq_len).to(torch.int32)
+            batch.gdn_has_state = torch.ones(bs, dtype=torch.int32, device=eng.device)
         eng.ctx.attn_backend.prepare_metadata(
             batch, self.block_table[:bs], self.cu_q[: bs + 1], self.seq_lens[:bs], 1, eng.max_seq_len)
         with eng.ctx.forward_batch(batch):

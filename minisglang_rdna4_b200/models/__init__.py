@@ -25,6 +25,14 @@ def _register_defaults() -> None:
             MODEL_REGISTRY.register(arch)(GemmaForCausalLM)
 
 
+    from .qwen3_5 import Qwen3_5ForCausalLM
+
+    for arch in ("Qwen3_5ForCausalLM", "Qwen3_5ForConditionalGeneration", "Qwen3_5MoeForCausalLM",
+                 "Qwen3_5MoeForConditionalGeneration", "Qwen3NextForCausalLM"):
+        if arch not in MODEL_REGISTRY:
+            MODEL_REGISTRY.register(arch)(Qwen3_5ForCausalLM)
+
+
 def create_model(cfg: ModelConfig, dtype: torch.dtype, device):
     """Instantiate the model for ``cfg`` with uninitialised (or meta) parameters."""
     _register_defaults()

@@ -73,6 +73,14 @@ class ModelConfig:
     qk_nope_head_dim: Optional[int] = None
     qk_rope_head_dim: Optional[int] = None
     v_head_dim: Optional[int] = None
+    # gated delta net (linear-attention layers of the Qwen3.5 / Qwen3-Next hybrid family)
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
+    attn_output_gate: bool = False        # q_proj also emits a per-head sigmoid gate of the attention output
+    norm_plus_one: bool = False           # RMSNorm weights are stored as (w - 1)
     # misc
     sliding_window: Optional[int] = None
     layer_types: Optional[Tuple[str, ...]] = None
@@ -98,6 +106,15 @@ class ModelConfig:
     @property
     def is_mla(self) -> bool:
         return self.kv_lora_rank is not None
+
+    @property
+    def is_recurrent(self) -> bool:
+        """Some layers keep a recurrent state per request instead of K/V pages."""
+        return bool(self.layer_types) and any(t == "linear_attention" for t in self.layer_types)
+
+    @property
+    def num_linear_layers(self) -> int:
+        return sum(1 for t in (self.layer_types or ()) if t == "linear_attention")
 
     @property
     def q_size(self) -> int:
@@ -162,7 +179,7 @@ class ModelConfig:
         if scaling and scaling.get("rope_type", scaling.get("type", "default")) in ("default", None):
             scaling = None
         theta = float(g("rope_theta") or rope_params.get("rope_theta") or 10000.0)
-        partial = float(g("partial_rotary_factor", 1.0) or 1.0)
+        partial = float(g("partial_rotary_factor") or rope_params.get("partial_rotary_factor") or 1.0)
         rope_dim = int(g("qk_rope_head_dim") or 0) or int(head_dim * partial)
         rotary = RotaryConfig(
             head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta, scaling=scaling
@@ -172,7 +189,20 @@ class ModelConfig:
         num_experts = int(g("num_experts") or g("num_local_experts") or g("n_routed_experts") or 0)
         quant = QuantConfig.from_hf(g("quantization_config")) if g("quantization_config") else None
         layer_types = g("layer_types")
-        qk_norm = model_type in ("qwen3", "qwen3_moe", "gemma3", "gemma3_text") or bool(g("use_qk_norm", False))
+        gdn_family = model_type in ("qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "qwen3_next")
+        qk_norm = (model_type in ("qwen3", "qwen3_moe", "gemma3", "gemma3_text") or gdn_family
+                   or bool(g("use_qk_norm", False)))
+        if gdn_family:
+            if layer_types is None:
+                every = int(g("full_attention_interval") or 4)
+                layer_types = ["linear_attention" if (i + 1) % every else "full_attention"
+                               for i in range(int(g("num_hidden_layers")))]
+            if partial == 1.0 and "partial_rotary_factor" not in cfg and "partial_rotary_factor" not in rope_params:
+                rope_dim = head_dim // 4
+                rotary = RotaryConfig(head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta,
+                                      scaling=scaling)
+            if archs and not any(a.startswith("Qwen3_5") or a.startswith("Qwen3Next") for a in archs):
+                archs = ("Qwen3_5ForCausalLM",)
         if layer_types is None and model_type in ("gemma3", "gemma3_text") and g("sliding_window_pattern"):
             pat = int(g("sliding_window_pattern"))
             layer_types = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention"
@@ -228,6 +258,13 @@ class ModelConfig:
             qk_nope_head_dim=g("qk_nope_head_dim"),
             qk_rope_head_dim=g("qk_rope_head_dim"),
             v_head_dim=g("v_head_dim"),
+            linear_num_key_heads=int(g("linear_num_key_heads") or 0),
+            linear_num_value_heads=int(g("linear_num_value_heads") or 0),
+            linear_key_head_dim=int(g("linear_key_head_dim") or 0),
+            linear_value_head_dim=int(g("linear_value_head_dim") or 0),
+            linear_conv_kernel_dim=int(g("linear_conv_kernel_dim") or 4),
+            attn_output_gate=gdn_family,
+            norm_plus_one=gdn_family,
             sliding_window=g("sliding_window") if g("use_sliding_window", True) else None,
             layer_types=tuple(layer_types) if layer_types else None,
             final_logit_softcapping=g("final_logit_softcapping"),
@@ -255,6 +292,11 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma2": ["Gemma2ForCausalLM"],
         "gemma3": ["Gemma3ForCausalLM"],
         "gemma3_text": ["Gemma3ForCausalLM"],
+        "qwen3_5": ["Qwen3_5ForCausalLM"],
+        "qwen3_5_text": ["Qwen3_5ForCausalLM"],
+        "qwen3_5_moe": ["Qwen3_5MoeForCausalLM"],
+        "qwen3_5_moe_text": ["Qwen3_5MoeForCausalLM"],
+        "qwen3_next": ["Qwen3NextForCausalLM"],
     }.get(model_type, ["LlamaForCausalLM"])
 
 

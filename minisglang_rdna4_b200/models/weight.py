@@ -134,6 +134,47 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             continue
         if name.startswith("language_model."):
             name = name[len("language_model."):]
+        if name.startswith("model.language_model."):
+            name = "model." + name[len("model.language_model."):]
+        if name.startswith("model.visual."):
+            continue
+        # ---- gated delta net (Qwen3.5 / Qwen3-Next linear-attention layers)
+        if ".linear_attn." in name:
+            block, _, tail = name.partition(".linear_attn.")
+            gdn = modules.get(block + ".linear_attn")
+            if gdn is None:
+                continue
+            if tail in ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight"):
+                part = ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight").index(tail)
+                key = block + ".linear_attn.in_proj.weight"
+                col = pending.setdefault(key, _Collector(4))
+                if col.add(part, tensor):
+                    w = col.cat(0)
+                    rows = gdn.in_proj.weight.shape[0]
+                    if w.shape[0] < rows:   # the projection is padded to a multiple of 8 output columns
+                        w = torch.cat([w, w.new_zeros((rows - w.shape[0], w.shape[1]))])
+                    assign(gdn.in_proj, "weight", w, key)
+                    del pending[key]
+            elif tail == "conv1d.weight":
+                assign(gdn, "conv1d_weight", tensor.reshape(tensor.shape[0], -1), block + ".linear_attn.conv1d_weight")
+            elif tail == "norm.weight":
+                assign(gdn, "norm_weight", tensor, block + ".linear_attn.norm_weight")
+            elif tail in ("dt_bias", "A_log"):
+                assign(gdn, tail, tensor.float(), block + ".linear_attn." + tail)
+            elif tail == "out_proj.weight":
+                assign(gdn.out_proj, "weight", shard_linear(gdn.out_proj, "weight", tensor, "row", None), name)
+            continue
+        if cfg.attn_output_gate and name.endswith(".self_attn.q_proj.weight"):
+            # rows are [q_h ‖ gate_h] per head: the query half joins the merged q/k/v projection, the
+            # gate half becomes a projection of its own
+            attn = modules.get(name[: -len(".q_proj.weight")])
+            d = cfg.head_dim
+            t4 = tensor.view(cfg.num_qo_heads, 2, d, tensor.shape[-1])
+            gate = t4[:, 1].reshape(cfg.num_qo_heads * d, -1)
+            tensor = t4[:, 0].reshape(cfg.num_qo_heads * d, -1).contiguous()
+            if attn is not None and hasattr(attn, "gate_proj"):
+                assign(attn.gate_proj, "weight", shard_linear(attn.gate_proj, "weight", gate, "col", None),
+                       name[: -len(".q_proj.weight")] + ".gate_proj.weight")
         m = re.match(r"^model\.layers\.(\d+)\.", name)
         if m and int(m.group(1)) >= cfg.num_layers:
             continue  # MTP / next-n layers stored after the decoder

@@ -146,6 +146,30 @@ def gemm_fp8_block(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16):
     return ref.gemm_fp8_block(x_q, x_scale, w_q, w_scale, 128, out_dtype)
 
 
+# ---------------------------------------------------------------------------- gated delta net
+def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state):
+    if x.is_cuda:
+        return _cuda().gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state)
+    return ref.causal_conv1d(x, weight, conv_state, cu_q, slots, has_state)
+
+
+def gdn_recurrent(qkv, a, b, a_log, dt_bias, state, cu_q, slots, has_state, hk: int, hv: int, dk: int, dv: int):
+    """Gated delta rule on the rows ``qkv = [q heads ‖ k heads ‖ v heads]`` left by the convolution."""
+    if qkv.is_cuda:
+        return _cuda().gdn_recurrent(qkv, a, b, a_log, dt_bias, state, cu_q, slots, has_state, hk, hv, dk, dv)
+    t = qkv.shape[0]
+    q, k, v = qkv.split([hk * dk, hk * dk, hv * dv], dim=-1)
+    g, beta = ref.gdn_gates(a, b, a_log, dt_bias)
+    return ref.gdn_recurrent(q.reshape(t, hk, dk), k.reshape(t, hk, dk), v.reshape(t, hv, dv), g, beta, state,
+                             cu_q, slots, has_state)
+
+
+def rms_norm_gated(x, z, w, eps: float):
+    if x.is_cuda:
+        return _cuda().rms_norm_gated(x, z, w, eps)
+    return ref.rms_norm_gated(x, z.reshape(x.shape), w, eps)
+
+
 # ---------------------------------------------------------------------------- sampling
 def argmax(logits):
     if logits.is_cuda:

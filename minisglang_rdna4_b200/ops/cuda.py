@@ -670,3 +670,58 @@ def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
     from . import moe_cuda
 
     return moe_cuda.moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset)
+
+
+# ------------------------------------------------------------------------------------------ gated delta net
+def _bind_gdn():
+    from ._lib import bind, c_f, c_i, c_ll, c_p
+
+    if getattr(_bind_gdn, "done", False):
+        return
+    bind("msgl_gdn_conv1d", c_i, [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+    bind("msgl_gdn_recurrent", c_i, [c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i,
+                                     c_p])
+    bind("msgl_rms_norm_gated", c_i, [c_p, c_p, c_ll, c_i, c_p, c_p, c_i, c_i, c_f, c_i, c_p])
+    _bind_gdn.done = True
+
+
+def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state):
+    """Depthwise causal conv (4 taps) + SiLU over packed sequences; ``x [T, C]`` may be a column
+    slice of a wider projection (row stride = its leading dimension). Updates ``conv_state``."""
+    _bind_gdn()
+    assert x.dim() == 2 and x.stride(1) == 1 and weight.is_contiguous() and conv_state.is_contiguous()
+    t, c = x.shape
+    out = torch.empty((t, c), dtype=x.dtype, device=x.device)
+    check(lib().msgl_gdn_conv1d(_p(x), x.stride(0), _p(weight), _p(conv_state), _p(cu_q), _p(slots), _p(has_state),
+                                _p(out), cu_q.numel() - 1, c, weight.shape[1], _dt(x), _stream()), "gdn_conv1d")
+    _count("gdn_conv1d", "gdn_conv1d_kernel")
+    return out
+
+
+def gdn_recurrent(qkv, a, b, a_log, dt_bias, state, cu_q, slots, has_state, hk, hv, dk, dv):
+    """Gated delta rule over packed sequences. ``qkv [T, 2*hk*dk + hv*dv]`` (after the convolution),
+    ``a, b [T, hv]`` raw gate projections (column slices allowed, same row stride), ``state
+    [slots, hv, dk, dv]`` fp32 updated in place. Returns ``[T, hv, dv]``."""
+    _bind_gdn()
+    assert qkv.is_contiguous() and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) == b.stride(0)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    t = qkv.shape[0]
+    out = torch.empty((t, hv, dv), dtype=qkv.dtype, device=qkv.device)
+    check(lib().msgl_gdn_recurrent(_p(qkv), _p(a), _p(b), a.stride(0), _p(a_log), _p(dt_bias), _p(state), _p(cu_q),
+                                   _p(slots), _p(has_state), _p(out), cu_q.numel() - 1, hk, hv, dk, dv, _dt(qkv),
+                                   _stream()), "gdn_recurrent")
+    _count("gdn_recurrent", "gdn_recurrent_kernel")
+    return out
+
+
+def rms_norm_gated(x, z, w, eps):
+    """``norm(x) * w * silu(z)`` per head: ``x [T, heads, D]`` contiguous, ``z [T, heads * D]`` (a column
+    slice of a wider projection is fine)."""
+    _bind_gdn()
+    t, heads, d = x.shape
+    assert x.is_contiguous() and z.stride(1) == 1
+    out = torch.empty_like(x)
+    check(lib().msgl_rms_norm_gated(_p(x), _p(z), z.stride(0), heads, _p(w), _p(out), t * heads, d, eps, _dt(x),
+                                    _stream()), "rms_norm_gated")
+    _count("rms_norm_gated", "rms_norm_gated_kernel")
+    return out

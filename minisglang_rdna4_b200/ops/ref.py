@@ -380,3 +380,80 @@ def moe_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: to
         act = (F.silu(gate) * up).to(x.dtype).float()
         out[rows] += (act @ w2[e].float().t()) * wt[:, None]
     return out.to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# gated delta net (linear attention with a recurrent state)
+# ------------------------------------------------------------------------------------------
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, cu_q: torch.Tensor,
+                  slots: torch.Tensor, has_state: torch.Tensor) -> torch.Tensor:
+    """Depthwise causal convolution + SiLU over packed sequences.
+
+    ``x [T, C]`` holds the rows of B sequences (``cu_q [B+1]``); ``weight [C, Kw]``;
+    ``conv_state [slots, C, Kw-1]`` keeps the last ``Kw-1`` inputs of every sequence and is
+    updated in place (a sequence with ``has_state == 0`` starts from zeros). Returns ``[T, C]``
+    (python/minisgl/gdn/layer.py:346-420 causal_conv1d_fwd / _update)."""
+    out = torch.empty_like(x)
+    kw = weight.shape[1]
+    wf = weight.float()
+    for b in range(cu_q.numel() - 1):
+        lo, hi = int(cu_q[b]), int(cu_q[b + 1])
+        slot = int(slots[b])
+        hist = conv_state[slot].float().t() if int(has_state[b]) else x.new_zeros((kw - 1, x.shape[1])).float()
+        seq = torch.cat([hist, x[lo:hi].float()])                    # [Kw-1 + n, C]
+        n = hi - lo
+        acc = torch.zeros((n, x.shape[1]))
+        for j in range(kw):
+            acc += seq[j:j + n] * wf[:, j]
+        out[lo:hi] = F.silu(acc).to(x.dtype)
+        conv_state[slot] = seq[-(kw - 1):].t().to(conv_state.dtype)
+    return out
+
+
+def gdn_gates(a: torch.Tensor, b: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor):
+    """Per (token, value head): log-decay ``g = -exp(A_log) * softplus(a + dt_bias)`` and write
+    strength ``beta = sigmoid(b)``."""
+    g = -a_log.float().exp() * F.softplus(a.float() + dt_bias.float())
+    return g, torch.sigmoid(b.float())
+
+
+def gdn_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                  state: torch.Tensor, cu_q: torch.Tensor, slots: torch.Tensor, has_state: torch.Tensor
+                  ) -> torch.Tensor:
+    """Gated delta rule, token by token (the recurrent form).
+
+    ``q, k [T, Hk, Dk]`` (L2-normalised here, q scaled by ``Dk ** -0.5``; key heads are shared by
+    ``Hv / Hk`` value heads), ``v [T, Hv, Dv]``, ``g, beta [T, Hv]``, ``state [slots, Hv, Dk, Dv]``
+    fp32, updated in place. Per token: ``S *= exp(g)``; ``delta = (v - S^T k) * beta``;
+    ``S += k (x) delta``; ``out = S^T q``. Returns ``[T, Hv, Dv]``
+    (python/minisgl/gdn/layer.py:421-760 gdn_prefill / gdn_decode)."""
+    t, hk, dk = q.shape
+    hv, dv = v.shape[1], v.shape[2]
+    rep = hv // hk
+    qf = q.float()
+    kf = k.float()
+    qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+    kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+    qf = qf.repeat_interleave(rep, dim=1)
+    kf = kf.repeat_interleave(rep, dim=1)
+    out = torch.empty((t, hv, dv), dtype=torch.float32)
+    for bi in range(cu_q.numel() - 1):
+        lo, hi = int(cu_q[bi]), int(cu_q[bi + 1])
+        slot = int(slots[bi])
+        s = state[slot].float().clone() if int(has_state[bi]) else torch.zeros((hv, dk, dv))
+        for i in range(lo, hi):
+            s = s * g[i].float().exp()[:, None, None]
+            kv = (s * kf[i][:, :, None]).sum(1)                      # [Hv, Dv]
+            delta = (v[i].float() - kv) * beta[i].float()[:, None]
+            s = s + kf[i][:, :, None] * delta[:, None, :]
+            out[i] = (s * qf[i][:, :, None]).sum(1)
+        state[slot] = s
+    return out.to(v.dtype)
+
+
+def rms_norm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """``norm(x) * w * silu(z)`` over the last dimension (the norm comes before the gate)."""
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    y = (w.float() * y.to(x.dtype).float()) * F.silu(z.float())
+    return y.to(x.dtype)

@@ -55,8 +55,14 @@ class Scheduler:
         eng = self.engine
         self.page_size = eng.page_size
         self.table = TableManager(config.max_running_req)
+        # A recurrent state cannot be rewound to a matched prefix: hybrid models admit every request
+        # with an empty prefix (python/minisgl/engine/config.py:75-133 resolves the same way when
+        # the recurrent-snapshot cache is off).
+        cache_type = "naive" if eng.model_config.is_recurrent else config.cache_type
+        if eng.model_config.is_recurrent and config.spec_algorithm != "none":
+            raise ValueError("speculative decoding is not available for models with recurrent layers")
         self.cache = CacheManager(eng.num_pages, eng.page_size, eng.num_slots, eng.max_pages_per_seq,
-                                  config.cache_type)
+                                  cache_type)
         self.decode = DecodeManager(eng.page_size)
         self.prefill = PrefillManager(self.cache, self.table, self.decode)
         self.max_seq_len = eng.max_seq_len

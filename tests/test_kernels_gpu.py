@@ -597,10 +597,12 @@ def test_spec_accept_kernel_matches_the_host_rules(K):
     sel = torch.zeros(B, dtype=torch.int32, device=dev)
     first = (torch.arange(B) * msl + c + 1).to(torch.int32).to(dev)
     eos_arr = (ctypes.c_int * 8)(*(eos + [-1] * 6))
-    check(lib().msgl_spec_accept(target.to(dev).data_ptr(), d_pool.data_ptr(), first.data_ptr(),
-                                 k.to(torch.int32).to(dev).data_ptr(), max_emit.to(torch.int32).to(dev).data_ptr(),
-                                 ignore.to(torch.int32).to(dev).data_ptr(), rec.data_ptr(), sel.data_ptr(), eos_arr,
+    d_target, d_k = target.to(dev), k.to(torch.int32).to(dev)
+    d_emit, d_flags = max_emit.to(torch.int32).to(dev), ignore.to(torch.int32).to(dev)
+    check(lib().msgl_spec_accept(d_target.data_ptr(), d_pool.data_ptr(), first.data_ptr(), d_k.data_ptr(),
+                                 d_emit.data_ptr(), d_flags.data_ptr(), rec.data_ptr(), sel.data_ptr(), eos_arr,
                                  2, B, W, torch.cuda.current_stream().cuda_stream), "spec_accept")
+    torch.cuda.synchronize()
     rec = rec.cpu().view(B, W + 2)
     for b, (n, hit, em) in enumerate(want):
         assert int(rec[b, 0]) == n and int(rec[b, 1]) == hit and rec[b, 2:2 + n].tolist() == em, b

@@ -893,6 +893,9 @@ int dispatch_attn(const CUtensorMap& map, const AttnArgs& a, bool kv8, int d, in
   if (d == 64 && !kv8)
     return small ? launch_attn<T, false, 64, 1, 1, 3>(map, a, q_tiles, stream)
                  : launch_attn<T, false, 64, 4, 1, 4>(map, a, q_tiles, stream);
+  if (d == 256 && !kv8)   // Qwen3.5-style 256-wide heads: two stages of 64 tokens fit beside the 4 query warps
+    return small ? launch_attn<T, false, 256, 1, 1, 2>(map, a, q_tiles, stream)
+                 : launch_attn<T, false, 256, 4, 1, 2>(map, a, q_tiles, stream);
   msgl_set_error_text("attention: unsupported head_dim / KV dtype combination");
   return MSGL_BAD_ARG;
 }
@@ -970,8 +973,15 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
     const int warps = 4;
     const int blocks = (rows_heads + warps - 1) / warps;
 #define COMBINE(T, D) msgl_launch(attn_combine_kernel<T, D>, dim3(blocks), dim3(warps * 32), 0, stream, a.ws_o, a.ws_lse, (T*)out, rows_heads, splits)
-    if (dtype == MSGL_BF16) { if (head_dim == 128) COMBINE(__nv_bfloat16, 128); else COMBINE(__nv_bfloat16, 64); }
-    else { if (head_dim == 128) COMBINE(__half, 128); else COMBINE(__half, 64); }
+    if (dtype == MSGL_BF16) {
+      if (head_dim == 128) COMBINE(__nv_bfloat16, 128);
+      else if (head_dim == 256) COMBINE(__nv_bfloat16, 256);
+      else COMBINE(__nv_bfloat16, 64);
+    } else {
+      if (head_dim == 128) COMBINE(__half, 128);
+      else if (head_dim == 256) COMBINE(__half, 256);
+      else COMBINE(__half, 64);
+    }
 #undef COMBINE
     MSGL_CHECK_LAUNCH("attn_combine");
   }

@@ -24,9 +24,10 @@ constexpr int kMaxTopK = 16;
 
 // one warp per token; E <= 512 (16 values per lane)
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ logits, float* __restrict__ topk_w,
-                                 int32_t* __restrict__ topk_ids, int32_t* __restrict__ counts, int tokens, int E,
-                                 int k, int renorm, int sigmoid, float scale, int e_start, int e_local) {
+__global__ void moe_route_kernel(const T* __restrict__ logits, const float* __restrict__ bias,
+                                 float* __restrict__ topk_w, int32_t* __restrict__ topk_ids,
+                                 int32_t* __restrict__ counts, int tokens, int E, int k, int renorm, int sigmoid,
+                                 float scale, int e_start, int e_local) {
   pdl_enter();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
@@ -56,28 +57,38 @@ __global__ void moe_route_kernel(const T* __restrict__ logits, float* __restrict
 #pragma unroll
     for (int i = 0; i < PER; ++i) v[i] = (lane + 32 * i) < E ? v[i] * inv : -INFINITY;
   }
+  // experts are chosen by score + selection bias (when given); the weights are the scores themselves
+  float c[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    c[i] = (bias != nullptr && e < E) ? v[i] + bias[e] : v[i];
+  }
   float wsel[kMaxTopK];
   int isel[kMaxTopK];
   float total = 0.f;
   for (int kk = 0; kk < k; ++kk) {
-    // arg-max over the remaining scores, lowest expert id on ties
-    float best = -INFINITY;
+    // arg-max over the remaining choice scores, lowest expert id on ties
+    float best = -INFINITY, bw = 0.f;
     int bi = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int e = lane + 32 * i;
-      if (v[i] > best || (v[i] == best && e < bi)) { best = v[i]; bi = e; }
+      if (c[i] > best || (c[i] == best && e < bi)) { best = c[i]; bi = e; bw = v[i]; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float ow = __shfl_xor_sync(0xffffffffu, bw, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; bw = ow; }
     }
-    wsel[kk] = best;
+    wsel[kk] = bw;
     isel[kk] = bi;
-    total += best;
-    if ((bi & 31) == lane) v[bi >> 5] = -INFINITY;
+    total += bw;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (lane + 32 * i == bi) c[i] = -INFINITY;
   }
   if (lane == 0) {
     const float norm = renorm ? 1.f / fmaxf(total, 1e-20f) : 1.f;
@@ -185,27 +196,24 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restr
 
 }  // namespace
 
-MSGL_API int msgl_moe_route(const void* logits, void* topk_w, void* topk_ids, void* counts, int tokens, int E,
-                            int k, int renorm, int sigmoid, float scale, int e_start, int e_local, int dtype,
-                            cudaStream_t stream) {
-  if (tokens == 0) return MSGL_OK;
+MSGL_API int msgl_moe_route(const void* logits, const void* bias, void* topk_w, void* topk_ids, void* counts,
+                            int tokens, int E, int k, int renorm, int sigmoid, float scale, int e_start, int e_local,
+                            int dtype, cudaStream_t stream) {
   if (E > kMaxExperts || k > kMaxTopK || k > E) return MSGL_BAD_ARG;
+  // counts (optional): tokens per local expert, for the alignment step; zeroed here
   if (counts != nullptr) cudaMemsetAsync(counts, 0, sizeof(int32_t) * e_local, stream);
+  if (tokens == 0) return MSGL_OK;
   const int warps = 4;
   const int blocks = (tokens + warps - 1) / warps;
-  if (dtype == MSGL_F32)
-    msgl_launch(moe_route_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, (const float*)logits, (float*)topk_w, (int32_t*)topk_ids,
-                                                               (int32_t*)counts, tokens, E, k, renorm, sigmoid, scale,
-                                                               e_start, e_local);
-  else if (dtype == MSGL_BF16)
-    msgl_launch(moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)logits, (float*)topk_w, (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k, renorm,
-        sigmoid, scale, e_start, e_local);
-  else if (dtype == MSGL_F16)
-    msgl_launch(moe_route_kernel<__half>, dim3(blocks), dim3(warps * 32), 0, stream, (const __half*)logits, (float*)topk_w,
-                                                                (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k,
-                                                                renorm, sigmoid, scale, e_start, e_local);
-  else
-    return MSGL_BAD_ARG;
+#define ROUTE(T)                                                                                                   \
+  msgl_launch(moe_route_kernel<T>, dim3(blocks), dim3(warps * 32), 0, stream, (const T*)logits, (const float*)bias, \
+              (float*)topk_w, (int32_t*)topk_ids, (int32_t*)counts, tokens, E, k, renorm, sigmoid, scale, e_start,   \
+              e_local)
+  if (dtype == MSGL_F32) ROUTE(float);
+  else if (dtype == MSGL_BF16) ROUTE(__nv_bfloat16);
+  else if (dtype == MSGL_F16) ROUTE(__half);
+  else return MSGL_BAD_ARG;
+#undef ROUTE
   MSGL_CHECK_LAUNCH("moe_route");
   return MSGL_OK;
 }

@@ -32,7 +32,7 @@ class MoELayer(BaseOP):
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, renormalize: bool,
                  dtype, device, scoring: str = "softmax", routed_scale: float = 1.0,
-                 scheme=None) -> None:
+                 scheme=None, n_group: int = 1, topk_group: int = 1, selection_bias: bool = False) -> None:
         tp = get_tp_info()
         ep = get_ep_info()
         self._ep = ep if ep_enabled() else None
@@ -47,7 +47,11 @@ class MoELayer(BaseOP):
             self._i_local = div_even(inter, tp.size)
         self._hidden = hidden
         self._compute_dtype = dtype
+        self._n_group, self._topk_group = max(1, n_group), max(1, topk_group)
         self.gate = ReplicatedLinear(hidden, num_experts, dtype, device, None)
+        if selection_bias:
+            # DeepSeek-V3 / GLM-4 style: added to the scores when choosing experts, not to the weights
+            self.e_score_correction_bias = torch.zeros((num_experts,), dtype=torch.float32, device=device)
         self.w13 = torch.empty((self._e_local, 2 * self._i_local, hidden), dtype=dtype, device=device)
         self.w2 = torch.empty((self._e_local, hidden, self._i_local), dtype=dtype, device=device)
         # Quantised experts keep their checkpoint precision on the GPU (the reference's expert
@@ -73,14 +77,30 @@ class MoELayer(BaseOP):
         """Returns this rank's partial result (tensor-parallel partial sum when the
         intermediate dimension is sharded; complete under expert parallelism)."""
         logits = self.gate.forward(x)
-        topk_w, topk_ids = ops.moe_route(logits, self._k, self._renorm, self._scoring, None,
-                                         self._routed_scale)
+        bias = getattr(self, "e_score_correction_bias", None)
         ctx = try_global_ctx()
-        if self._ep is not None and ctx is not None and ctx.ep is not None:
-            return ctx.ep.dispatch_compute_combine(self, x, topk_w, topk_ids)
-        return self.local_experts(x, topk_w, topk_ids)
+        use_ep = self._ep is not None and ctx is not None and ctx.ep is not None
+        counts = None
+        if self._n_group > 1:
+            from ..ops import ref
 
-    def local_experts(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+            topk_w, topk_ids = ref.moe_route_grouped(logits, self._k, self._renorm, self._scoring, bias,
+                                                     self._routed_scale, self._n_group, self._topk_group)
+        elif x.is_cuda and not use_ep and getattr(self, "_tier", None) is None:
+            # the routing kernel also counts the tokens of every local expert for the alignment step
+            from ..ops import cuda as K
+
+            counts = torch.empty(self._e_local, dtype=torch.int32, device=x.device)
+            topk_w, topk_ids = K.moe_route(logits, self._k, self._renorm, self._scoring, bias, self._routed_scale,
+                                           counts, self._e_start, self._e_local)
+        else:
+            topk_w, topk_ids = ops.moe_route(logits, self._k, self._renorm, self._scoring, bias, self._routed_scale)
+        if use_ep:
+            return ctx.ep.dispatch_compute_combine(self, x, topk_w, topk_ids)
+        return self.local_experts(x, topk_w, topk_ids, counts)
+
+    def local_experts(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor, counts=None
+                      ) -> torch.Tensor:
         tier = getattr(self, "_tier", None)
         if tier is not None:
             return tier.forward(x, topk_w, topk_ids - self._e_start)
@@ -88,7 +108,11 @@ class MoELayer(BaseOP):
         if packed is not None:
             from ..ops.moe_kernels import moe_forward_quant
 
-            return moe_forward_quant(self._quant_kind, x, packed, topk_w, topk_ids, self._e_start)
+            return moe_forward_quant(self._quant_kind, x, packed, topk_w, topk_ids, self._e_start, counts)
+        if x.is_cuda:
+            from ..ops import cuda as K
+
+            return K.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start, counts)
         return ops.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start)
 
     def expert_weights(self):

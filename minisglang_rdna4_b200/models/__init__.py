@@ -33,6 +33,13 @@ def _register_defaults() -> None:
             MODEL_REGISTRY.register(arch)(Qwen3_5ForCausalLM)
 
 
+    from .glm4_moe_lite import Glm4MoeLiteForCausalLM
+
+    for arch in ("Glm4MoeLiteForCausalLM", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM"):
+        if arch not in MODEL_REGISTRY:
+            MODEL_REGISTRY.register(arch)(Glm4MoeLiteForCausalLM)
+
+
 def create_model(cfg: ModelConfig, dtype: torch.dtype, device):
     """Instantiate the model for ``cfg`` with uninitialised (or meta) parameters."""
     _register_defaults()

@@ -221,6 +221,17 @@ class ModelConfig:
                 scaling = None
             rotary = RotaryConfig(head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta,
                                   scaling=scaling)
+        if g("kv_lora_rank"):
+            # latent attention: the pool holds materialised per-head keys of qk_nope + qk_rope channels;
+            # the rotary part is GPT-J interleaved unless the checkpoint says otherwise
+            head_dim = int(g("qk_nope_head_dim")) + int(g("qk_rope_head_dim"))
+            kv_heads = heads
+            rotary = RotaryConfig(head_dim=head_dim, rotary_dim=int(g("qk_rope_head_dim")), max_position=max_pos,
+                                  base=theta, scaling=scaling, interleaved=bool(g("rope_interleave", True)))
+            if g("mlp_layer_types") and not g("first_k_dense_replace"):
+                dense = [i for i, t in enumerate(g("mlp_layer_types")) if t != "sparse"]
+                cfg = dict(cfg, mlp_only_layers=dense)
+                g = cfg.get
         attn_bias = bool(g("attention_bias", model_type in ("qwen2", "qwen2_moe")))
         return ModelConfig(
             num_layers=int(g("num_hidden_layers")),
@@ -250,7 +261,8 @@ class ModelConfig:
             first_k_dense_replace=int(g("first_k_dense_replace") or 0),
             n_shared_experts=int(g("n_shared_experts") or 0),
             routed_scaling_factor=float(g("routed_scaling_factor") or 1.0),
-            scoring_func=g("scoring_func", "softmax"),
+            scoring_func=g("scoring_func", "sigmoid" if model_type in ("glm4_moe_lite", "glm4_moe", "deepseek_v3")
+                           else "softmax"),
             n_group=int(g("n_group") or 1),
             topk_group=int(g("topk_group") or 1),
             kv_lora_rank=g("kv_lora_rank"),
@@ -292,6 +304,9 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma2": ["Gemma2ForCausalLM"],
         "gemma3": ["Gemma3ForCausalLM"],
         "gemma3_text": ["Gemma3ForCausalLM"],
+        "glm4_moe_lite": ["Glm4MoeLiteForCausalLM"],
+        "deepseek_v2": ["DeepseekV2ForCausalLM"],
+        "deepseek_v3": ["DeepseekV3ForCausalLM"],
         "qwen3_5": ["Qwen3_5ForCausalLM"],
         "qwen3_5_text": ["Qwen3_5ForCausalLM"],
         "qwen3_5_moe": ["Qwen3_5MoeForCausalLM"],

@@ -192,6 +192,29 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                 continue  # expert-parallel filter
             expert_buf.setdefault((block, eidx, proj), {})[suffix] = tensor
             continue
+        if name.endswith(".mlp.gate.e_score_correction_bias"):
+            moe = modules.get(name[: -len(".gate.e_score_correction_bias")] + ".experts")
+            if moe is not None and hasattr(moe, "e_score_correction_bias"):
+                assign(moe, "e_score_correction_bias", tensor.float(),
+                       name[: -len(".gate.e_score_correction_bias")] + ".experts.e_score_correction_bias")
+            continue
+        if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")) and tensor.dim() == 3:
+            # expert stacks stored fused: [E, 2I, H] (gate rows then up rows) and [E, H, I]
+            moe = modules.get(name.rsplit(".", 1)[0])
+            if moe is None:
+                continue
+            lo, hi = moe._e_start, moe._e_start + moe._e_local
+            t3 = tensor[lo:hi]
+            if name.endswith("gate_up_proj"):
+                if moe._ep is None and tp.size > 1:
+                    gate, up = t3.chunk(2, dim=1)
+                    t3 = torch.cat([_slice(gate, 1, tp.rank, tp.size), _slice(up, 1, tp.rank, tp.size)], dim=1)
+                assign(moe, "w13", t3, name.rsplit(".", 1)[0] + ".w13")
+            else:
+                if moe._ep is None and tp.size > 1:
+                    t3 = _slice(t3, 2, tp.rank, tp.size)
+                assign(moe, "w2", t3, name.rsplit(".", 1)[0] + ".w2")
+            continue
         if name.endswith(".mlp.gate.weight") and (name[: -len(".gate.weight")] + ".experts") in modules:
             moe = modules[name[: -len(".gate.weight")] + ".experts"]
             assign(moe.gate, "weight", tensor, name[: -len(".gate.weight")] + ".experts.gate.weight")
@@ -215,8 +238,8 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
         parent, _, leaf = name.rpartition(".")
         gp, _, proj = parent.rpartition(".")
         # suffixes with a dot ("weight_scale_inv" has none, fine)
-        if proj in _QKV or proj in _GATE_UP:
-            merged_name = gp + (".qkv_proj" if proj in _QKV else ".gate_up_proj")
+        merged_name = gp + (".qkv_proj" if proj in _QKV else ".gate_up_proj")
+        if (proj in _QKV or proj in _GATE_UP) and (merged_name in modules or parent not in modules):
             mod = modules.get(merged_name)
             if mod is None:
                 continue

@@ -660,16 +660,17 @@ def sample(logits, temperatures, top_k=None, top_p=None, min_p=None, generator=N
 
 
 # ------------------------------------------------------------------------------------------ MoE (composed)
-def moe_route(router_logits, top_k, renormalize, scoring="softmax", bias=None, scale=1.0):
-    from . import moe_cuda
+def moe_route(router_logits, top_k, renormalize, scoring="softmax", bias=None, scale=1.0, counts=None, e_start=0,
+              e_local=None):
+    from . import moe_kernels
 
-    return moe_cuda.moe_route(router_logits, top_k, renormalize, scoring, bias, scale)
+    return moe_kernels.moe_route(router_logits, top_k, renormalize, scoring, scale, counts, e_start, e_local, bias)
 
 
-def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
-    from . import moe_cuda
+def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0, counts=None):
+    from . import moe_kernels
 
-    return moe_cuda.moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset)
+    return moe_kernels.moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset, counts)
 
 
 # ------------------------------------------------------------------------------------------ gated delta net

@@ -10,7 +10,7 @@ from . import _lib
 from . import cuda as K
 from ._lib import c_f, c_i, c_ll, c_p, check, lib
 
-_lib.bind("msgl_moe_route", c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_i, c_i, c_p])
+_lib.bind("msgl_moe_route", c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_f, c_i, c_i, c_i, c_p])
 _lib.bind("msgl_moe_align", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p])
 _lib.bind("msgl_moe_permute", c_i, [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
 _lib.bind("msgl_moe_combine", c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
@@ -20,13 +20,20 @@ BLOCK = 128
 _DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
-def moe_route(router_logits, top_k, renormalize, scoring="softmax", scale=1.0, counts=None, e_start=0, e_local=None):
+def moe_route(router_logits, top_k, renormalize, scoring="softmax", scale=1.0, counts=None, e_start=0, e_local=None,
+              bias=None):
+    """Softmax / sigmoid scores, top-k by score (+ selection ``bias`` when given), optional
+    renormalisation, in one launch. ``counts [e_local]`` (int32), when given, receives the number
+    of tokens routed to every local expert, which is what the alignment step needs."""
     t, e = router_logits.shape
     assert router_logits.is_contiguous()
     w = torch.empty((t, top_k), dtype=torch.float32, device=router_logits.device)
     ids = torch.empty((t, top_k), dtype=torch.int32, device=router_logits.device)
-    check(lib().msgl_moe_route(router_logits.data_ptr(), w.data_ptr(), ids.data_ptr(),
-                               None if counts is None else counts.data_ptr(), t, e, top_k, int(renormalize),
+    if bias is not None:
+        bias = bias.float().contiguous()
+    check(lib().msgl_moe_route(router_logits.data_ptr(), None if bias is None else bias.data_ptr(), w.data_ptr(),
+                               ids.data_ptr(), None if counts is None else counts.data_ptr(), t, e, top_k,
+                               int(renormalize),
                                int(scoring != "softmax"), float(scale), e_start, e if e_local is None else e_local,
                                _DT[router_logits.dtype], K._stream()), "moe_route")
     K._count("moe_route", "moe_route_kernel")
@@ -38,16 +45,18 @@ def max_sorted_rows(tokens: int, top_k: int, e_local: int) -> int:
     return (rows + BLOCK - 1) // BLOCK * BLOCK
 
 
-def moe_align(topk_ids, e_start: int, e_local: int):
+def moe_align(topk_ids, e_start: int, e_local: int, counts=None):
     """Returns ``(sorted_pair [R], pair_row [T*k], tile_expert [R/128], meta [2])`` with R the
-    worst-case padded row count (static for a given T, k, E)."""
+    worst-case padded row count (static for a given T, k, E). ``counts`` = tokens per local expert
+    when the routing kernel already produced them."""
     t, k = topk_ids.shape
     dev = topk_ids.device
     rows = max_sorted_rows(t, k, e_local)
-    counts = torch.zeros(e_local, dtype=torch.int32, device=dev)
-    flat = topk_ids.reshape(-1).long() - e_start
-    ok = (flat >= 0) & (flat < e_local)
-    counts.index_add_(0, flat.clamp(0, e_local - 1), ok.to(torch.int32))
+    if counts is None:
+        counts = torch.zeros(e_local, dtype=torch.int32, device=dev)
+        flat = topk_ids.reshape(-1).long() - e_start
+        ok = (flat >= 0) & (flat < e_local)
+        counts.index_add_(0, flat.clamp(0, e_local - 1), ok.to(torch.int32))
     return _align_with_counts(topk_ids, counts, e_start, e_local, rows)
 
 
@@ -80,11 +89,11 @@ def gemm_grouped(a, b, tile_expert, out_dtype=None, bn=0):
     return out
 
 
-def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0):
+def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0, counts=None):
     t, h = x.shape
     e_local = w13.shape[0]
     k = topk_ids.shape[1]
-    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local)
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local, counts)
     rows = sorted_pair.numel()
     xs = torch.empty((rows, h), dtype=x.dtype, device=x.device)
     check(lib().msgl_moe_permute(x.data_ptr(), sorted_pair.data_ptr(), xs.data_ptr(), h, k, rows, _DT[x.dtype],
@@ -212,12 +221,12 @@ def run_experts(kind: str, xs, tile_expert, weights, out_dtype):
     return run_experts_q(kind, xq, xsc, tile_expert, weights, out_dtype)
 
 
-def moe_forward_quant(kind: str, x, weights, topk_w, topk_ids, expert_offset=0):
+def moe_forward_quant(kind: str, x, weights, topk_w, topk_ids, expert_offset=0, counts=None):
     """align → permute → quantise → grouped GEMM → SiLU·mul + quantise → grouped GEMM → combine
     for quantised expert stacks ``weights`` of ``kind``."""
     e_local = weights[0].shape[0]
     k = topk_ids.shape[1]
-    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local)
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, e_local, counts)
     xs = _permute(x, sorted_pair, k)
     y = run_experts(kind, xs, tile_expert, weights, x.dtype)
     return _combine(y, topk_w, pair_row, x, k)

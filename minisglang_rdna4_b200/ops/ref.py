@@ -360,6 +360,27 @@ def moe_route(router_logits: torch.Tensor, top_k: int, renormalize: bool, scorin
     return (w * scale).float(), ids.to(torch.int32)
 
 
+def moe_route_grouped(router_logits: torch.Tensor, top_k: int, renormalize: bool, scoring: str,
+                      bias: Optional[torch.Tensor], scale: float, n_group: int, topk_group: int
+                      ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Group-limited routing (DeepSeek-V3 / GLM-4 MoE): experts are split into ``n_group`` groups,
+    a group's score is the sum of its two best choice scores, only the best ``topk_group`` groups
+    stay eligible, then top-k over the eligible experts; weights are the un-biased scores."""
+    g = router_logits.float()
+    scores = torch.softmax(g, dim=-1) if scoring == "softmax" else torch.sigmoid(g)
+    choice = scores + bias.float() if bias is not None else scores
+    t, e = choice.shape
+    group_scores = choice.view(t, n_group, e // n_group).topk(2, dim=-1)[0].sum(-1)
+    keep = torch.zeros_like(group_scores)
+    keep.scatter_(1, group_scores.topk(topk_group, dim=-1, sorted=False)[1], 1.0)
+    mask = keep[:, :, None].expand(t, n_group, e // n_group).reshape(t, e).bool()
+    _, ids = choice.masked_fill(~mask, 0.0).topk(top_k, dim=-1)
+    w = scores.gather(-1, ids)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return (w * scale).float(), ids.to(torch.int32)
+
+
 def moe_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
                 topk_ids: torch.Tensor, expert_offset: int = 0) -> torch.Tensor:
     """``sum_k w_k * down_e(silu(gate_e x) * up_e x)`` over the experts held locally

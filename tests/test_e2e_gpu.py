@@ -380,3 +380,84 @@ def test_host_expert_tier_matches_resident_experts_on_the_gpu():
         want_y = ops.moe_forward(x, w13, w2, w, ids, 0).float()
         assert float((got_y - want_y).abs().max()) <= 0.02 * float(want_y.abs().max()) + 1e-3, t
     assert tier.cache.misses > 0 and tier.cache.evictions > 0 and tier.bytes_copied > 0
+
+
+def test_qwen3_5_hybrid_model_tracks_fp32_oracle():
+    """The gated-delta-net / gated-attention hybrid on the kernel path (256-wide attention heads with
+    rotary on their first quarter, 128-wide delta-rule heads, recurrent state slots, CUDA-graph decode)
+    against the CPU fp32 oracle path with the same weights; graph decode reproduces eager decode."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=4, num_qo_heads=4, num_kv_heads=2, head_dim=256, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-6,
+            rotary_config=RotaryConfig(head_dim=256, rotary_dim=64, max_position=2048, base=1e7),
+            model_type="qwen3_5_text", architectures=("Qwen3_5ForCausalLM",), qk_norm=True,
+            max_position_embeddings=2048, attn_output_gate=True, norm_plus_one=True,
+            layer_types=("linear_attention", "linear_attention", "linear_attention", "full_attention"),
+            linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128,
+            linear_conv_kernel_dim=4,
+        )
+
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = {}
+    state = None
+    for name, kw in (("graph", dict()), ("eager", dict(cuda_graph_max_bs=-1)),
+                     ("chunked", dict(cuda_graph_max_bs=-1, max_extend_tokens=96))):
+        gpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                  num_page_override=256, seed=0, **kw)
+        if state is None:
+            state = {k: v.float().cpu() for k, v in gpu.engine.model.state_dict().items()}
+        outs[name] = [o.token_ids for o in gpu.generate(_prompts(), sp)]
+        gpu.shutdown()
+    assert outs["graph"] == outs["eager"]
+    cpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    cpu.engine.model.load_state_dict(state, strict=False)
+    want = [o.token_ids for o in cpu.generate(_prompts(), sp)]
+    cpu.shutdown()
+    for got in (outs["eager"], outs["chunked"]):
+        first_ok = sum(g[0] == w[0] for g, w in zip(got, want))
+        assert first_ok >= len(want) - 1, (got, want)
+
+
+def test_glm4_moe_lite_model_tracks_fp32_oracle():
+    """Latent-attention + sigmoid-routed MoE decoder on the kernel path (materialised 256-wide heads
+    with interleaved rotary on their first 64 channels, selection bias in the routing kernel, shared
+    experts, a dense first layer) against the CPU fp32 oracle path with the same weights."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=3, num_qo_heads=4, num_kv_heads=4, head_dim=256, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-5,
+            rotary_config=RotaryConfig(head_dim=256, rotary_dim=64, max_position=2048, base=1e6, interleaved=True),
+            model_type="glm4_moe_lite", architectures=("Glm4MoeLiteForCausalLM",), max_position_embeddings=2048,
+            num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, norm_topk_prob=True,
+            n_shared_experts=1, routed_scaling_factor=1.8, scoring_func="sigmoid", mlp_only_layers=(0,),
+            kv_lora_rank=128, q_lora_rank=96, qk_nope_head_dim=192, qk_rope_head_dim=64, v_head_dim=256,
+        )
+
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = {}
+    state = None
+    for name, kw in (("graph", dict()), ("eager", dict(cuda_graph_max_bs=-1))):
+        gpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                  num_page_override=256, seed=0, **kw)
+        if state is None:
+            state = {k: v.float().cpu() for k, v in gpu.engine.model.state_dict().items()}
+        outs[name] = [o.token_ids for o in gpu.generate(_prompts(), sp)]
+        gpu.shutdown()
+    assert outs["graph"] == outs["eager"]
+    cpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    cpu.engine.model.load_state_dict(state, strict=False)
+    want = [o.token_ids for o in cpu.generate(_prompts(), sp)]
+    cpu.shutdown()
+    first_ok = sum(g[0] == w[0] for g, w in zip(outs["eager"], want))
+    assert first_ok >= len(want) - 1, (outs["eager"], want)

@@ -307,6 +307,14 @@ def test_moe_route_and_forward(K, tokens, E, k):
     ws, _ = MK.moe_route(logits, k, False, scoring="sigmoid", scale=2.5)
     wr, _ = R.moe_route(logits, k, False, "sigmoid", None, 2.5)
     _close(ws.sort(-1).values, wr.sort(-1).values, 1e-4, 1e-6, "sigmoid weights")
+    # selection bias: experts chosen by score + bias, weighted by the score; per-expert counts
+    bias = torch.randn(E, device="cuda") * 0.3
+    counts = torch.empty(E, dtype=torch.int32, device="cuda")
+    wb, ib = MK.moe_route(logits, k, True, scoring="sigmoid", scale=1.8, bias=bias, counts=counts)
+    wbr, ibr = R.moe_route(logits, k, True, "sigmoid", bias, 1.8)
+    assert torch.equal(ib.sort(-1).values, ibr.sort(-1).values)
+    _close(wb.sort(-1).values, wbr.sort(-1).values, 1e-4, 1e-6, "biased route weights")
+    assert torch.equal(counts.long(), torch.bincount(ib.reshape(-1).long(), minlength=E))
     x = torch.randn(tokens, h, device="cuda").bfloat16()
     w13 = (torch.randn(E, 2 * inter, h, device="cuda") * 0.05).bfloat16()
     w2 = (torch.randn(E, h, inter, device="cuda") * 0.05).bfloat16()
@@ -608,3 +616,61 @@ def test_spec_accept_kernel_matches_the_host_rules(K):
         assert int(rec[b, 0]) == n and int(rec[b, 1]) == hit and rec[b, 2:2 + n].tolist() == em, b
         assert int(sel[b]) == b * W + n - 1
     assert torch.equal(d_pool.cpu(), want_pool)
+
+
+def test_attention_head_dim_256(K):
+    """256-wide heads (the Qwen3.5 full-attention layers): prefill, extend, decode and a split decode."""
+    _attn_case(K, False, 2, [70, 9], [70, 200], 8, 2, 256, 16)
+    _attn_case(K, False, 3, [1] * 3, [40, 333, 1200], 8, 2, 256, 16)
+    _attn_case(K, False, 2, [1] * 2, [700, 2048], 16, 4, 256, 16, splits=4)
+
+
+# ------------------------------------------------------------------------------------------ gated delta net
+@pytest.mark.parametrize("d", [64, 128])
+def test_gated_delta_net_kernels(K, d):
+    """Causal convolution with a rolling state, the recurrent gated delta rule with its state matrix
+    per (request, head), and the gated RMSNorm against their fp32 restatements: packed sequences of
+    different lengths, a request that continues from a stored state, slots in any order."""
+    R = _ref()
+    torch.manual_seed(d)
+    hk, hv, kw = 2, 4, 4
+    dk = dv = d
+    lens = [1, 37, 130, 1]
+    t = sum(lens)
+    cdim = 2 * hk * dk + hv * dv
+    ncol = cdim + hv * dv + 2 * hv
+    proj = (torch.randn(t, (ncol + 7) // 8 * 8, device="cuda") * 0.7).bfloat16()
+    w = (torch.randn(cdim, kw, device="cuda") * 0.4).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    slots = torch.tensor([3, 0, 5, 1], dtype=torch.int32, device="cuda")
+    has = torch.tensor([1, 0, 1, 0], dtype=torch.int32, device="cuda")
+    conv0 = (torch.randn(6, cdim, kw - 1, device="cuda") * 0.5).bfloat16()
+    ssm0 = torch.randn(6, hv, dk, dv, device="cuda") * 0.1
+    a_log = torch.log(torch.empty(hv, device="cuda").uniform_(1, 8))
+    dt_bias = torch.randn(hv, device="cuda") * 0.3
+    # GPU
+    conv_g, ssm_g = conv0.clone(), ssm0.clone()
+    qkv = K.gdn_conv1d(proj[:, :cdim], w, conv_g, cu, slots, has)
+    z = proj[:, cdim:cdim + hv * dv]
+    b = proj[:, cdim + hv * dv:cdim + hv * dv + hv]
+    a = proj[:, cdim + hv * dv + hv:cdim + hv * dv + 2 * hv]
+    o = K.gdn_recurrent(qkv, a, b, a_log, dt_bias, ssm_g, cu, slots, has, hk, hv, dk, dv)
+    nw = (1 + 0.1 * torch.randn(dv, device="cuda")).bfloat16()
+    y = K.rms_norm_gated(o, z, nw, 1e-6)
+    torch.cuda.synchronize()
+    # fp32 restatement on the CPU
+    conv_c, ssm_c = conv0.cpu().clone(), ssm0.cpu().clone()
+    pc = proj.cpu()
+    qkv_c = R.causal_conv1d(pc[:, :cdim], w.cpu(), conv_c, cu.cpu(), slots.cpu(), has.cpu())
+    _close(qkv.cpu(), qkv_c, 2e-2, 2e-2, "conv1d")
+    assert torch.equal(conv_g.cpu()[[3, 0, 5, 1]], conv_c[[3, 0, 5, 1]])
+    assert torch.equal(conv_g.cpu()[[2, 4]], conv0.cpu()[[2, 4]])        # untouched slots
+    g_c, beta_c = R.gdn_gates(pc[:, cdim + hv * dv + hv:cdim + hv * dv + 2 * hv], pc[:, cdim + hv * dv:cdim + hv * dv + hv],
+                              a_log.cpu(), dt_bias.cpu())
+    q_c, k_c, v_c = qkv.cpu().split([hk * dk, hk * dk, hv * dv], dim=-1)
+    o_c = R.gdn_recurrent(q_c.reshape(t, hk, dk), k_c.reshape(t, hk, dk), v_c.reshape(t, hv, dv), g_c, beta_c, ssm_c,
+                          cu.cpu(), slots.cpu(), has.cpu())
+    _close(o.cpu(), o_c, 3e-2, 3e-2 * float(o_c.float().abs().max()), "delta rule output")
+    _close(ssm_g.cpu(), ssm_c, 1e-3, 1e-3 * float(ssm_c.abs().max()), "recurrent state")
+    y_c = R.rms_norm_gated(o.cpu(), pc[:, cdim:cdim + hv * dv].reshape(t, hv, dv), nw.cpu(), 1e-6)
+    _close(y.cpu(), y_c, 2e-2, 2e-2, "gated norm")

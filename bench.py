@@ -318,6 +318,21 @@ def main() -> None:
         return out
 
     eng.forward_batch = timed_forward
+    runner = getattr(llm, "_spec_runner", None)
+    if runner:
+        # the speculative step runs on the device without passing through forward_batch: time it too
+        orig_run = runner.run
+
+        def timed_run(rows, staged):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(eng.stream)
+            with torch.cuda.stream(eng.stream):
+                out = orig_run(rows, staged)
+            e.record(eng.stream)
+            step_events.append((s, e, "decode", len(rows) * runner.W))
+            return out
+
+        runner.run = timed_run
 
     def make_prompts(seed: int):
         g = np.random.default_rng(seed)
@@ -418,6 +433,10 @@ def main() -> None:
                 "preset": args.config, "shared_prefix": args.shared_prefix,
                 "spec": ({"algorithm": args.spec, "draft": args.spec_draft, "tree_width": args.spec_tree_width,
                           "verify_steps": llm.stats.get("spec_steps", 0),
+                          "verify_step_ms_p50": (sorted(s.elapsed_time(e) for s, e, ph, _ in step_events
+                                                        if ph == "decode") or [None])[len([1 for x in step_events if x[2] == "decode"]) // 2],
+                          "accepted_tokens_per_request_step": (llm.stats.get("spec_accepted", 0)
+                                                               / max(llm.stats.get("spec_drafted", 0), 1) * args.spec_draft),
                           "accepted_per_step": (llm.stats.get("spec_emitted", 0) / max(llm.stats.get("spec_steps", 0), 1))}
                          if args.spec != "none" else None),
                 "step": "one full pass of the workload (prefill + decode)",

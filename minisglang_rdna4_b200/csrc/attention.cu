@@ -494,11 +494,20 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
 // merge split partials: one warp per (query row, head)
 template <typename T, int D>
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_lse,
-                                    T* __restrict__ out, int rows_heads, int splits) {
+                                    T* __restrict__ out, int rows_heads, int splits,
+                                    const int32_t* __restrict__ cu_q, int B, int hq) {
   pdl_enter();
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (idx >= rows_heads) return;
   const int lane = threadIdx.x & 31;
+  // rows past cu_q[B] belong to no request (padding of a captured batch): the split kernels wrote
+  // no partials for them, so they are zero-filled instead of merged from whatever the workspace holds
+  if (idx >= cu_q[B] * hq) {
+    T* pad = out + (size_t)idx * D + lane * (D / 32);
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) pad[i] = from_float<T>(0.f);
+    return;
+  }
   float mx = -INFINITY;
   for (int s = 0; s < splits; ++s) mx = fmaxf(mx, ws_lse[(size_t)s * rows_heads + idx]);
   constexpr int PER = D / 32;
@@ -972,7 +981,7 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
     const int rows_heads = total_q * hq;
     const int warps = 4;
     const int blocks = (rows_heads + warps - 1) / warps;
-#define COMBINE(T, D) msgl_launch(attn_combine_kernel<T, D>, dim3(blocks), dim3(warps * 32), 0, stream, a.ws_o, a.ws_lse, (T*)out, rows_heads, splits)
+#define COMBINE(T, D) msgl_launch(attn_combine_kernel<T, D>, dim3(blocks), dim3(warps * 32), 0, stream, a.ws_o, a.ws_lse, (T*)out, rows_heads, splits, a.cu_q, a.B, a.Hq)
     if (dtype == MSGL_BF16) {
       if (head_dim == 128) COMBINE(__nv_bfloat16, 128);
       else if (head_dim == 256) COMBINE(__nv_bfloat16, 256);

@@ -42,6 +42,12 @@ struct ArArgs {
   int max_hidden;
   float eps, w_offset;
   unsigned long long wait_ns;
+  // ---- in-switch reduction (NVLS): every rank keeps only its own partial rows, in a buffer that is
+  // also mapped through an NVLink multicast object; one multimem.ld_reduce returns the sum over ranks
+  void* my_rows;             // local address of this rank's row region [2 parity][max_rows][max_hidden]
+  const void* mc_rows;       // multicast address of the same region
+  uint32_t* my_count;        // local address of the arrival counters [max_rows]
+  uint32_t* mc_count;        // multicast address of the counters (a reduction adds on every rank)
 };
 
 __device__ int g_comm_status = 0;
@@ -65,11 +71,30 @@ __device__ __forceinline__ unsigned long long gtimer() {
   return t;
 }
 
+// eight 16-bit values summed over all ranks by the switch (fp32 accumulation, one rounding)
+template <typename T> __device__ __forceinline__ uint4 multimem_ld_reduce8(const void* mc_addr);
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce8<__nv_bfloat16>(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+template <> __device__ __forceinline__ uint4 multimem_ld_reduce8<__half>(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_red_release_add(uint32_t* mc_addr, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+
 // One 128-thread CTA per row, the row held in registers (VPT 16-byte vectors per thread) from the
 // push to the final store. NORM: residual add + RMSNorm after the reduction. QUANT: e4m3 output.
+// NVLS: the reduction happens inside the NVSwitch (see ArArgs) instead of by stores into every peer.
 constexpr int kArThreads = 128;
 
-template <typename T, bool NORM, bool QUANT, int VPT>
+template <typename T, bool NORM, bool QUANT, int VPT, bool NVLS = false>
 __global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) {
   pdl_enter();
   __shared__ float scratch[32];
@@ -78,6 +103,94 @@ __global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) 
   const uint32_t seq = a.seq[row] + 1u;
   const int parity = (int)(seq & 1u);
   const T* xr = reinterpret_cast<const T*>(a.x) + (size_t)row * H;
+  if (NVLS) {
+    // 1. this rank's partial row goes into its own buffer (a local store)
+    T* mine = reinterpret_cast<T*>(a.my_rows) + ((size_t)parity * a.max_rows + row) * a.max_hidden;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kArThreads + threadIdx.x) * 8;
+      if (i < H) *reinterpret_cast<uint4*>(mine + i) = *reinterpret_cast<const uint4*>(xr + i);
+    }
+    __syncthreads();
+    // 2. one multicast reduction bumps this row's arrival counter on every rank; then wait until all
+    //    ranks have arrived here (the counter counts arrivals over all calls: seq * nranks by now)
+    if (threadIdx.x == 0) {
+      multimem_red_release_add(a.mc_count + row, 1u);
+      const uint32_t want = seq * (uint32_t)a.nranks;
+      const uint32_t* cnt = a.my_count + row;
+      if ((int)(ld_acquire_sys(cnt) - want) < 0) {
+        const unsigned long long t0 = gtimer();
+        while ((int)(ld_acquire_sys(cnt) - want) < 0) {
+          if (gtimer() - t0 > a.wait_ns) {
+            atomicCAS(a.status, 0, 320);
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // 3. the switch returns the sum over ranks; residual add and norm as in the push form
+    const T* mc = reinterpret_cast<const T*>(a.mc_rows) + ((size_t)parity * a.max_rows + row) * a.max_hidden;
+    T* rr = NORM ? reinterpret_cast<T*>(a.residual) + (size_t)row * H : nullptr;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = (j * kArThreads + threadIdx.x) * 8;
+      if (i < H) {
+        const uint4 red = multimem_ld_reduce8<T>(mc + i);
+        const T* rp = reinterpret_cast<const T*>(&red);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[j][k] = to_float(rp[k]);
+        if (NORM) {
+          float r[8];
+          load8(rr + i, r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[j][k] += r[k];
+          store8(rr + i, v[j]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            v[j][k] = to_float(from_float<T>(v[j][k]));
+            ss += v[j][k] * v[j][k];
+          }
+        } else {
+          store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, v[j]);
+        }
+      }
+    }
+    if (NORM) {
+      ss = block_sum(ss, scratch);
+      const float rstd = rsqrtf(ss / (float)H + a.eps);
+      const T* w = reinterpret_cast<const T*>(a.weight);
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int i = (j * kArThreads + threadIdx.x) * 8;
+        if (i < H) {
+          float wv[8];
+          load8(w + i, wv);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            v[j][k] = to_float(from_float<T>(v[j][k] * rstd * (wv[k] + a.w_offset)));
+            if (QUANT) amax = fmaxf(amax, fabsf(v[j][k]));
+          }
+          if (!QUANT) store8(reinterpret_cast<T*>(a.out) + (size_t)row * H + i, v[j]);
+        }
+      }
+      if (QUANT) {
+        amax = block_max(amax, scratch);
+        const float scale = fmaxf(amax, 1e-8f) / kFp8Max;
+        if (threadIdx.x == 0) a.out_scale[row] = scale;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+          const int i = (j * kArThreads + threadIdx.x) * 8;
+          if (i < H) *reinterpret_cast<uint2*>(a.out_q + (size_t)row * H + i) = pack8_e4m3(v[j], scale);
+        }
+      }
+    }
+    if (threadIdx.x == 0) a.seq[row] = seq;
+    return;
+  }
 
   // 1. push this rank's partial row into every PEER's slot (its own copy stays in registers)
   uint4 mine_raw[VPT];
@@ -192,6 +305,12 @@ __global__ void __launch_bounds__(kArThreads) ar_oneshot_kernel(const ArArgs a) 
 template <typename T, int VPT>
 void launch_ar_vpt(const ArArgs& a, cudaStream_t stream) {
   const bool norm = a.residual != nullptr, quant = a.out_q != nullptr;
+  if (a.mc_rows != nullptr) {
+    if (norm && quant) msgl_launch(ar_oneshot_kernel<T, true, true, VPT, true>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
+    else if (norm) msgl_launch(ar_oneshot_kernel<T, true, false, VPT, true>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
+    else msgl_launch(ar_oneshot_kernel<T, false, false, VPT, true>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
+    return;
+  }
   if (norm && quant) msgl_launch(ar_oneshot_kernel<T, true, true, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
   else if (norm) msgl_launch(ar_oneshot_kernel<T, true, false, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
   else msgl_launch(ar_oneshot_kernel<T, false, false, VPT>, dim3(a.rows), dim3(kArThreads), 0, stream, a);
@@ -515,6 +634,47 @@ MSGL_API int msgl_ar_oneshot(const void* x, void* residual, const void* weight, 
   a.slot_stride = (long long)max_rows * max_hidden;
   a.eps = eps; a.w_offset = plus_one ? 1.f : 0.f;
   a.wait_ns = (unsigned long long)wait_us * 1000ull;
+  a.my_rows = nullptr; a.mc_rows = nullptr; a.my_count = nullptr; a.mc_count = nullptr;
+  if (dtype == MSGL_BF16) return launch_ar<__nv_bfloat16>(a, stream);
+  if (dtype == MSGL_F16) return launch_ar<__half>(a, stream);
+  return MSGL_BAD_ARG;
+}
+
+// The same fused all-reduce (+ residual add + RMSNorm (+ e4m3)) with the reduction done inside the
+// NVSwitch. `local` / `mc` are this rank's address and the multicast address of one symmetric
+// buffer laid out as [counters: max_rows u32, padded to 256 bytes][rows: 2 x max_rows x max_hidden
+// 16-bit]; the buffer starts zeroed. Every rank stores only its own rows (locally) and reads the
+// sum once through the multicast mapping: per-rank NVLink traffic is one row set in, however many
+// ranks there are. `seq` [max_rows] are local per-row call counters (device-resident, so a
+// captured graph replays unchanged).
+MSGL_API int msgl_ar_nvls(const void* x, void* residual, const void* weight, void* out, void* out_q, void* out_scale,
+                          void* local, void* mc, void* seq, int rank, int nranks, int rows, int hidden, int max_rows,
+                          int max_hidden, float eps, int plus_one, long long wait_us, int dtype,
+                          cudaStream_t stream) {
+  if (rows == 0) return MSGL_OK;
+  if (local == nullptr || mc == nullptr || nranks > kMaxRanks || rows > max_rows || hidden > max_hidden || hidden % 8 ||
+      max_hidden % 8 || hidden > 16 * 8 * 128) {
+    msgl_set_error_text("ar_nvls: message does not fit the symmetric buffer");
+    return MSGL_BAD_ARG;
+  }
+  const size_t count_bytes = ((size_t)max_rows * 4 + 255) / 256 * 256;
+  ArArgs a;
+  a.x = x; a.residual = residual; a.weight = weight; a.out = out;
+  a.out_q = (uint8_t*)out_q; a.out_scale = (float*)out_scale;
+  for (int p = 0; p < kMaxRanks; ++p) { a.slots[p] = nullptr; a.flags[p] = nullptr; }
+  a.seq = (uint32_t*)seq;
+  int* status = nullptr;
+  cudaGetSymbolAddress((void**)&status, g_comm_status);
+  a.status = status;
+  a.rank = rank; a.nranks = nranks; a.rows = rows; a.hidden = hidden; a.max_rows = max_rows;
+  a.max_hidden = max_hidden;
+  a.slot_stride = (long long)max_rows * max_hidden;
+  a.eps = eps; a.w_offset = plus_one ? 1.f : 0.f;
+  a.wait_ns = (unsigned long long)wait_us * 1000ull;
+  a.my_count = (uint32_t*)local;
+  a.mc_count = (uint32_t*)mc;
+  a.my_rows = (unsigned char*)local + count_bytes;
+  a.mc_rows = (const unsigned char*)mc + count_bytes;
   if (dtype == MSGL_BF16) return launch_ar<__nv_bfloat16>(a, stream);
   if (dtype == MSGL_F16) return launch_ar<__half>(a, stream);
   return MSGL_BAD_ARG;

@@ -18,13 +18,17 @@
 //   * A problem whose partials do not fit (splits * total_q * hq * (head_dim + 1) floats more
 //     than the array holds) is rejected with MSGL_BAD_ARG and a message in msgl_last_error();
 //     lower `splits` or the batch.
-//   * The first call on each device looks up the device address of the array (a blocking
-//     runtime query). Make that first call outside of any stream capture.
+//   * The first call on each device that actually splits the KV range (splits > 1) looks up the
+//     device address of the array (a blocking runtime query). Make that first call outside of
+//     any stream capture. The looked-up address is remembered per device in a plain table that
+//     is written without a lock: two threads racing on the first call both store the same value,
+//     which is harmless, but do not rely on more than that.
 //   * All calls on one device share the one array, and it keeps whatever the previous call left
-//     in it. Nothing in it has to be cleared between calls: every slot that the merge step
-//     reads is written earlier in the same call. Two calls that overlap in time on the same
-//     device (different streams, or different threads) would trample each other's partials, so
-//     serialise them.
+//     in it. Nothing in it has to be cleared between calls: for every query row that belongs to
+//     a request (the rows below cu_q[B]) each slot the merge step reads is written earlier in
+//     the same call; rows past cu_q[B] are padding and come back as zeros without touching the
+//     array. Two calls that overlap in time on the same device (different streams, or different
+//     threads) would trample each other's partials, so serialise them.
 #pragma once
 #include <cuda_runtime.h>
 

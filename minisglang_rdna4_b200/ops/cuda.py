@@ -588,6 +588,70 @@ def silu_and_mul_quant_group(x):
     return q, s
 
 
+W4_EXPAND_ROWS = 256
+_W4_SCRATCH: Dict[Tuple[torch.device, torch.dtype], torch.Tensor] = {}
+
+
+def _w4_scratch(device, dtype, elems: int) -> torch.Tensor:
+    key = (device, dtype)
+    t = _W4_SCRATCH.get(key)
+    if t is None or t.numel() < elems:
+        t = _W4_SCRATCH[key] = torch.empty(elems, dtype=dtype, device=device)
+    return t
+
+
+def gemm_w4a16(x, w_packed, scales_t, zeros_t=None, channel=None, group=128, nvfp4=False, bias=None, out_dtype=None):
+    """``x @ dequant(W).T`` with W kept 4-bit in HBM (``gemm_w4a16_kernel``): ``w_packed [N, K/2]`` bytes
+    (low nibble = even k), ``scales_t [K/group, N]`` fp32 with ``zeros_t`` of the same shape (integer
+    formats: ``w = (code - zero) * scale``), or e4m3 bytes with a per-channel fp32 factor ``channel [N]``
+    (NVFP4: ``w = e2m1(code) * scale * channel``). Activations stay 16-bit."""
+    from ._lib import bind, c_i, c_ll, c_p
+
+    if not hasattr(gemm_w4a16, "_bound"):
+        bind("msgl_gemm_w4a16", c_i, [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_ll, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
+                                      c_p])
+        bind("msgl_gemm_w4a16_status", c_i, [c_i])
+        bind("msgl_w4_expand", c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p])
+        gemm_w4a16._bound = True
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    n = w_packed.shape[0]
+    assert w_packed.dtype == torch.uint8 and w_packed.is_contiguous() and w_packed.shape[1] * 2 == k
+    assert scales_t.is_contiguous() and scales_t.shape == (k // group, n)
+    out_dtype = out_dtype or x.dtype
+    if m > W4_EXPAND_ROWS:
+        # many rows (prefill): expand the matrix once into a scratch shared by all layers, then the
+        # ordinary GEMM; the in-kernel expansion would repeat per 128-row tile
+        scratch = _w4_scratch(x.device, x.dtype, n * k)
+        check(lib().msgl_w4_expand(_p(w_packed), _p(scales_t), _p(zeros_t), _p(channel), _p(scratch), n, k, group,
+                                   int(nvfp4), _dt(x2), _stream()), "w4_expand")
+        _count("w4_expand", "w4_expand_kernel")
+        # the scratch is written by the kernel just ahead: no weight fetch before the dependency wait
+        prev = gemm_static_weights(False)
+        try:
+            out = _gemm(KIND_BF16 if x.dtype == torch.bfloat16 else KIND_F16, x2, scratch[: n * k].view(n, k), n, k,
+                        out_dtype, bias=bias)
+        finally:
+            gemm_static_weights(bool(prev))
+        return out.view(*shape[:-1], n) if out is not None else None
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(lib().msgl_gemm_w4a16(_p(x2), x2.stride(0), _p(w_packed), _p(scales_t), _p(zeros_t), _p(channel), _p(bias),
+                                _p(out), n, m, n, k, group, int(nvfp4), _dt(x2), _DT[out_dtype], _stream()),
+          "gemm_w4a16")
+    _count("gemm_w4a16_nvfp4" if nvfp4 else "gemm_w4a16_int4", "gemm_w4a16_kernel")
+    return out.view(*shape[:-1], n)
+
+
+def gemm_w4a16_status(reset=True) -> int:
+    from ._lib import bind, c_i
+
+    bind("msgl_gemm_w4a16_status", c_i, [c_i])
+    return int(lib().msgl_gemm_w4a16_status(int(reset)))
+
+
 def gemm_status(reset=True) -> int:
     return int(lib().msgl_gemm_status(int(reset)))
 

@@ -37,6 +37,8 @@ _lib.bind("msgl_ipc_open", c_p, [c_p])
 _lib.bind("msgl_ipc_close", c_i, [c_p])
 _lib.bind("msgl_ar_oneshot", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i,
                                    c_f, c_i, c_ll, c_i, c_p])
+_lib.bind("msgl_ar_nvls", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_f, c_i,
+                                c_ll, c_i, c_p])
 _lib.bind("msgl_comm_status", c_i, [c_i])
 _lib.bind("msgl_argmax_exchange", c_i, [c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_ll, c_p])
 
@@ -87,6 +89,43 @@ def agree_status(local_code: int, cpu_group, world: int) -> int:
     return int(t.item())
 
 
+class MulticastBuffer:
+    """One symmetric buffer that is also bound to an NVLink multicast object, set up through
+    PyTorch's symmetric-memory rendezvous (``torch.distributed._symmetric_memory``): every rank gets
+    its local address and one multicast address through which a ``multimem`` instruction reaches
+    the same offset on all ranks (loads reduce in the switch, reductions update every copy).
+    ``None`` from :meth:`create` when the platform has no multicast support."""
+
+    def __init__(self, tensor, handle) -> None:
+        self.tensor, self.handle = tensor, handle
+        self.local = int(tensor.data_ptr())
+        self.mc = int(handle.multicast_ptr)
+
+    @classmethod
+    def create(cls, nbytes: int, group, device) -> Optional["MulticastBuffer"]:
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            name = group.group_name
+            enable = getattr(symm_mem, "enable_symm_mem_for_group", None)
+            if enable is not None:
+                try:
+                    enable(name)
+                except Exception:
+                    pass
+            t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            hdl = symm_mem.rendezvous(t, name)
+            if not int(getattr(hdl, "multicast_ptr", 0) or 0):
+                return None
+            t.zero_()
+            torch.cuda.synchronize(device)
+            hdl.barrier()
+            return cls(t, hdl)
+        except Exception as exc:  # no fabric / no multicast: the push form stays in use
+            logger.info_rank0("NVLink multicast unavailable (%s): one-shot all-reduce stays on peer stores", exc)
+            return None
+
+
 class SymmetricCollectives:
     name = "symm"
 
@@ -120,8 +159,18 @@ class SymmetricCollectives:
         self.healthy = True
         self.wait_us = ENV.COMM_WAIT_US.value
         self.oneshot_max_bytes = ENV.ONESHOT_AR_MAX_KIB.value << 10
-        logger.info_rank0("peer-memory collectives ready: %d ranks, %d rows x %d, heap %.1f MiB",
-                          world, self.max_rows, max_hidden, (flag_bytes + slot_bytes) / 2 ** 20)
+        # in-switch reduction for the decode all-reduce when the fabric offers NVLink multicast
+        self.nvls: Optional[MulticastBuffer] = None
+        self._nvls_seq = None
+        mode = ENV.NVLS.value
+        if mode != "off" and world >= (2 if mode == "on" else 4):
+            count_bytes = (self.max_rows * 4 + 255) // 256 * 256
+            self.nvls = MulticastBuffer.create(count_bytes + 2 * self.max_rows * max_hidden * 2, group, self.device)
+            if self.nvls is not None:
+                self._nvls_seq = torch.zeros(self.max_rows, dtype=torch.int32, device=self.device)
+        logger.info_rank0("peer-memory collectives ready: %d ranks, %d rows x %d, heap %.1f MiB, all-reduce by %s",
+                          world, self.max_rows, max_hidden, (flag_bytes + slot_bytes) / 2 ** 20,
+                          "in-switch reduction (multimem)" if self.nvls is not None else "peer stores")
 
     # ---- dispatch predicate ----
     def accepts(self, x: torch.Tensor) -> bool:
@@ -134,6 +183,13 @@ class SymmetricCollectives:
 
         rows, hidden = x.shape
         p = lambda t: None if t is None else t.data_ptr()
+        if self.nvls is not None:
+            check(lib().msgl_ar_nvls(
+                p(x), p(residual), p(weight), p(out), p(out_q), p(out_s), self.nvls.local, self.nvls.mc,
+                self._nvls_seq.data_ptr(), self.rank, self.world, rows, hidden, self.max_rows, self.max_hidden, eps,
+                int(plus_one), self.wait_us, _DT[x.dtype], torch.cuda.current_stream().cuda_stream), "ar_nvls")
+            K._count("fused_allreduce", "ar_oneshot_kernel<NVLS>")
+            return
         check(lib().msgl_ar_oneshot(
             p(x), p(residual), p(weight), p(out), p(out_q), p(out_s), self._slots, self._flags, self._seq.data_ptr(),
             self.rank, self.world, rows, hidden, self.max_rows, self.max_hidden, eps, int(plus_one), self.wait_us,
@@ -212,6 +268,7 @@ class SymmetricCollectives:
         if rs is not None:
             rs.close()
             self.row_shard = None
+        self.nvls = None
         self.heap.close()
 
 

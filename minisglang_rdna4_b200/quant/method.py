@@ -10,11 +10,14 @@ none             bf16 ``(N, K)``            ``kind::f16``
 fp8_channel      e4m3 + ``(N,)`` f32        ``kind::f8f6f4``; per-token × per-channel
                                             scales applied in the epilogue (W8A8)
 fp8_tensor       as fp8_channel (scale broadcast)
-fp8_block        e4m3 + 128x128 f32 scales  ``kind::f8f6f4`` per 128-deep K block, partial
-                                            sums promoted with the block scales
+fp8_block        e4m3 + 128x128 f32 scales  ``kind::f8f6f4``: every 128-deep K block accumulates in
+                                            its own tensor-memory buffer and is promoted with
+                                            (1 x 128 activation scale) x (block scale) by the
+                                            epilogue warps (``csrc/gemm_fp8_block.cu``); other
+                                            block shapes are expanded to 16-bit at load
 mxfp4            packed e2m1 + UE8M0/32     ``kind::mxf8f6f4.block_scale`` against e4m3
                                             activations (W4A8); per-token scale in epilogue
-nvfp4, int4      expanded to bf16 at load   ``kind::f16`` (W4A16 semantics)
+nvfp4, int4      see ``NvFp4Method`` / ``Int4Method``
 ===============  =========================  ==========================================
 
 The reference's method table is python/minisgl/quant/method.py:352-949.
@@ -234,8 +237,16 @@ class MxFp4Method(LinearMethod):
         layer.weight_scale = torch.cat(scales)
 
 
+def _w4_native_ok(n: int, k: int, group: int, device) -> bool:
+    """Shapes the 4-bit-resident GEMM takes (``csrc/gemm_w4a16.cu``); anything else is expanded."""
+    return torch.device(device).type == "cuda" and n % 8 == 0 and k % 64 == 0 and group >= 16 and group % 8 == 0
+
+
 class NvFp4Method(LinearMethod):
-    """NVFP4 checkpoint tensors; expanded to 16-bit weights after loading."""
+    """NVFP4 checkpoint tensors (e2m1 codes, an e4m3 scale per 16 elements, a per-channel factor;
+    python/minisgl/quant/method.py:729-749). On the GPU the codes stay 4-bit in HBM and are expanded
+    inside the GEMM (W4A16: 16-bit activations, weights exact); on the CPU oracle path, and for
+    shapes the kernel does not take, they are expanded once after loading."""
 
     def __init__(self, divides: bool) -> None:
         self.divides = divides
@@ -251,6 +262,13 @@ class NvFp4Method(LinearMethod):
         return {"weight_packed": (0, 1), "weight_scale": (0, 1), "weight_global_scale": (0, -1)}
 
     def process_after_load(self, layer):
+        n, k = layer.weight_packed.shape[0], layer.weight_packed.shape[1] * 2
+        if _w4_native_ok(n, k, 16, layer.weight_packed.device) and layer._compute_dtype in (torch.bfloat16, torch.float16):
+            layer._w4 = (layer.weight_packed.contiguous(),
+                         layer.weight_scale.view(torch.uint8).t().contiguous(),       # [K/16, N] e4m3 bytes
+                         layer.weight_global_scale.float().contiguous())
+            layer.weight_scale = layer.weight_scale[:0]
+            return
         layer._dense = nv_codec.dequant_nvfp4(
             layer.weight_packed, layer.weight_scale, layer.weight_global_scale
         ).to(layer._compute_dtype)
@@ -258,6 +276,11 @@ class NvFp4Method(LinearMethod):
         layer.weight_scale = layer.weight_scale[:0]
 
     def apply(self, layer, x, bias):
+        w4 = getattr(layer, "_w4", None)
+        if w4 is not None:
+            from ..ops import cuda as K
+
+            return K.gemm_w4a16(_dequant_input(x, layer._compute_dtype), w4[0], w4[1], None, w4[2], 16, True, bias)
         return ops.gemm(_dequant_input(x, layer._dense.dtype), layer._dense, bias)
 
     def init_dummy(self, layer, gen, std=0.02):
@@ -267,8 +290,10 @@ class NvFp4Method(LinearMethod):
 
 
 class Int4Method(LinearMethod):
-    """AWQ / GPTQ / compressed-tensors int4; converted to the canonical (codes, scales, zeros)
-    form and expanded to 16-bit weights after loading."""
+    """AWQ / GPTQ / compressed-tensors int4, converted to the canonical (codes, scales, zeros) form
+    after loading (python/minisgl/quant/kernels.py:255-346). On the GPU the codes are re-packed two
+    per byte and stay 4-bit in HBM; the GEMM expands them tile by tile (W4A16: 16-bit activations,
+    ``(code - zero) * scale`` exact). The CPU oracle path and odd shapes expand once at load."""
 
     def __init__(self, scheme: QuantScheme) -> None:
         self.scheme = scheme
@@ -304,12 +329,23 @@ class Int4Method(LinearMethod):
             c, s, z = int4_codec.ct_to_canonical(layer.weight_packed, layer.weight_scale,
                                                  getattr(layer, "weight_zero_point", None),
                                                  getattr(layer, "_ct_convention", None))
-        layer._dense = int4_codec.dequant_int4(c, s, z).to(layer._compute_dtype)
+        n, k = c.shape
+        group = k // s.shape[1]
+        if _w4_native_ok(n, k, group, c.device) and layer._compute_dtype in (torch.bfloat16, torch.float16):
+            packed = (c[:, 0::2] | (c[:, 1::2] << 4)).to(torch.uint8).contiguous()
+            layer._w4 = (packed, s.float().t().contiguous(), z.float().t().contiguous(), group)
+        else:
+            layer._dense = int4_codec.dequant_int4(c, s, z).to(layer._compute_dtype)
         for name in ("qweight", "scales", "qzeros", "weight_packed", "weight_scale", "weight_zero_point"):
             if hasattr(layer, name):
                 setattr(layer, name, getattr(layer, name)[:0])
 
     def apply(self, layer, x, bias):
+        w4 = getattr(layer, "_w4", None)
+        if w4 is not None:
+            from ..ops import cuda as K
+
+            return K.gemm_w4a16(_dequant_input(x, layer._compute_dtype), w4[0], w4[1], w4[2], None, w4[3], False, bias)
         return ops.gemm(_dequant_input(x, layer._dense.dtype), layer._dense, bias)
 
     def init_dummy(self, layer, gen, std=0.02):

@@ -674,3 +674,71 @@ def test_gated_delta_net_kernels(K, d):
     _close(ssm_g.cpu(), ssm_c, 1e-3, 1e-3 * float(ssm_c.abs().max()), "recurrent state")
     y_c = R.rms_norm_gated(o.cpu(), pc[:, cdim:cdim + hv * dv].reshape(t, hv, dv), nw.cpu(), 1e-6)
     _close(y.cpu(), y_c, 2e-2, 2e-2, "gated norm")
+
+
+# ------------------------------------------------------------------------------------------ 4-bit-resident GEMM
+@pytest.mark.parametrize("m,n,k,group", [(1, 256, 256, 128), (77, 1032, 512, 32), (300, 384, 1024, 64)])
+def test_gemm_w4a16_int4_dialects(K, m, n, k, group):
+    """AWQ, GPTQ and compressed-tensors int4 checkpoints through the GEMM that keeps the codes 4-bit
+    in memory, against the fp32 product with the de-quantised weights; the in-kernel expansion equals
+    the load-time expansion bit for bit, so a row does not depend on the batch it is multiplied in."""
+    from minisglang_rdna4_b200.quant import int4 as I
+
+    torch.manual_seed(m + n)
+    w = torch.randn(n, k) * 0.05
+    c, s, z = I.quantize_int4(w, group)
+    z = torch.randint(5, 12, z.shape).float()          # asymmetric zero points
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    dense = I.dequant_int4(c, s, z)
+    want = x.float().cpu() @ dense.t()
+    checks = []
+    qw, sc, qz = I.pack_awq(c, s, z)
+    checks.append(("awq", I.awq_to_canonical(qw, sc, qz)))
+    qw, sc, qz = I.pack_gptq(c, s, z)
+    checks.append(("gptq", I.gptq_to_canonical(qw, sc, qz, symmetric=False)))
+    packed, sc = I.pack_ct(c, s, twos=True)
+    checks.append(("ct", I.ct_to_canonical(packed, sc, None, "twos")))
+    for name, (cc, ss, zz) in checks:
+        if name == "ct":
+            ref_dense = I.dequant_int4(cc, ss, zz)
+            ref = x.float().cpu() @ ref_dense.t()
+        else:
+            assert torch.equal(cc, c)
+            ref_dense, ref = I.dequant_int4(cc, ss, zz), want
+        pk = (cc[:, 0::2] | (cc[:, 1::2] << 4)).to(torch.uint8).contiguous().cuda()
+        got = K.gemm_w4a16(x, pk, ss.float().t().contiguous().cuda(), zz.float().t().contiguous().cuda(), None, group)
+        assert K.gemm_w4a16_status() == 0
+        _close(got.cpu(), ref, 2e-2, 2e-2 * float(ref.abs().max()), f"w4a16 {name}")
+        expanded = K.gemm(x, ref_dense.bfloat16().cuda())
+        assert torch.equal(got, expanded), name           # same numerics as the expanded weights
+        one = K.gemm_w4a16(x[-1:].contiguous(), pk, ss.float().t().contiguous().cuda(),
+                           zz.float().t().contiguous().cuda(), None, group)
+        assert torch.equal(one[0], got[-1])
+        if m > K.W4_EXPAND_ROWS:
+            # above the row threshold the weights are expanded once into a scratch matrix; the
+            # tile-by-tile expansion gives the same bits
+            keep, K.W4_EXPAND_ROWS = K.W4_EXPAND_ROWS, 1 << 30
+            try:
+                tiled = K.gemm_w4a16(x, pk, ss.float().t().contiguous().cuda(), zz.float().t().contiguous().cuda(), None,
+                                     group)
+            finally:
+                K.W4_EXPAND_ROWS = keep
+            assert torch.equal(tiled, got), name
+
+
+@pytest.mark.parametrize("m,n,k", [(3, 256, 128), (200, 1032, 512)])
+def test_gemm_w4a16_nvfp4(K, m, n, k):
+    from minisglang_rdna4_b200.quant import nvfp4 as NV
+
+    torch.manual_seed(n)
+    w = torch.randn(n, k) * 0.05
+    packed, blk, glob = NV.quantize_nvfp4(w)
+    glob = glob * (0.5 + torch.rand(n))                   # per-channel factors
+    dense = NV.dequant_nvfp4(packed, blk, glob)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    got = K.gemm_w4a16(x, packed.cuda(), blk.view(torch.uint8).t().contiguous().cuda(), None, glob.float().cuda(), 16,
+                       True)
+    assert K.gemm_w4a16_status() == 0
+    want = x.float().cpu() @ dense.float().t()
+    _close(got.cpu(), want, 2e-2, 2e-2 * float(want.abs().max()), "w4a16 nvfp4")
+    assert torch.equal(got, K.gemm(x, dense.bfloat16().cuda()))

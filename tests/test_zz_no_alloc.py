@@ -4,7 +4,7 @@ Some embedders of this library may not request device memory once they are runni
 cudaMalloc from their call sites). For them ``msgl_paged_attention_noalloc`` keeps the split-KV
 partials in an array built into the library. This test drives that symbol directly with ctypes
 and checks, on two calls in a row with different inputs, that it returns what the regular entry
-point returns when it is given a workspace tensor.
+point returns when it is given a workspace tensor, and what the fp32 restatement of the op gives.
 
 The file name sorts last on purpose: if this test fails, a run that stops at the first failure
 has already run everything else.
@@ -74,6 +74,13 @@ def test_noalloc_entry_point_matches_regular_entry_point():
         assert K.attn_status() == 0
         err = (got.float() - want.float()).abs().max().item()
         assert err <= 3e-2 * max(1.0, want.float().abs().max().item()), f"call {call}: max err {err}"
+        # and against the fp32 restatement of the op itself
+        from minisglang_rdna4_b200.ops import ref
+
+        oracle = ref.paged_attention(c["q"], c["pool"][0, 0], c["pool"][1, 0], c["bt"], c["cu"], c["sl"],
+                                     c["d"] ** -0.5, True, 0, None, c["ks"], c["vs"])
+        err = (got.float() - oracle.float()).abs().max().item()
+        assert err <= 3e-2 * max(1.0, oracle.float().abs().max().item()), f"call {call}: max err vs oracle {err}"
     # a request that cannot fit the built-in scratch is refused with a message, not run
     c = _case(3, False)
     big_q = torch.randn(4096, c["hq"], c["d"], device="cuda").bfloat16()

@@ -2,6 +2,9 @@
 
 * ``ops/libmsgl_cuda.so``  — every sm_100a kernel (``csrc/*.cu``), compiled with
   ``nvcc -gencode arch=compute_100a,code=sm_100a`` (cross-compiles without a GPU).
+* ``ops/libmsgl_cuda_checked.so`` — the same sources with ``-DMSGL_CHECK_BOUNDS`` (device-side index
+  checks that record and skip instead of trapping); built by ``--checked`` and loaded when
+  ``MSGL_CHECK_BOUNDS=1``.
 * ``ops/libmsgl_host.so``  — host helpers (``csrc/host/*.cpp``).
 
 Objects are cached under ``csrc/_obj`` keyed by a hash of the source, its headers and the
@@ -22,6 +25,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 OPS = os.path.join(HERE, "ops")
 CUDA_LIB = os.path.join(OPS, "libmsgl_cuda.so")
+CHECKED_LIB = os.path.join(OPS, "libmsgl_cuda_checked.so")
 HOST_LIB = os.path.join(OPS, "libmsgl_host.so")
 
 NVCC_FLAGS = [
@@ -60,34 +64,38 @@ def _compile(cmd: List[str], out: str, log: str) -> str:
     return out
 
 
-def build_cuda(verbose: bool = True) -> str:
+def build_cuda(verbose: bool = True, checked: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
+    flags = NVCC_FLAGS + (["-DMSGL_CHECK_BOUNDS=1"] if checked else [])
+    out_lib = CHECKED_LIB if checked else CUDA_LIB
+    variant = ".chk" if checked else ""
     sources = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
     headers = _headers()
     jobs, objs = [], []
     for src in sources:
-        tag = _digest([src] + headers, NVCC_FLAGS)
-        obj = os.path.join(OBJ, f"{os.path.basename(src)[:-3]}.{tag}.o")
+        tag = _digest([src] + headers, flags)
+        obj = os.path.join(OBJ, f"{os.path.basename(src)[:-3]}{variant}.{tag}.o")
         objs.append(obj)
         if not os.path.exists(obj):
-            jobs.append(([nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj], obj, obj[:-2] + ".log"))
+            jobs.append(([nvcc] + flags + ["-c", src, "-o", obj], obj, obj[:-2] + ".log"))
     if jobs and verbose:
         print(f"[build] compiling {len(jobs)} CUDA source(s) for sm_100a", file=sys.stderr)
     with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
         list(pool.map(lambda j: _compile(*j), jobs))
     stamp = _digest(objs, ["link"])
-    stamp_file = CUDA_LIB + ".stamp"
-    if jobs or not os.path.exists(CUDA_LIB) or not os.path.exists(stamp_file) or open(stamp_file).read() != stamp:
-        _compile([nvcc, "-shared", "-o", CUDA_LIB] + objs + ["-lcudart"], CUDA_LIB, os.path.join(OBJ, "link.log"))
+    stamp_file = out_lib + ".stamp"
+    if jobs or not os.path.exists(out_lib) or not os.path.exists(stamp_file) or open(stamp_file).read() != stamp:
+        _compile([nvcc, "-shared", "-o", out_lib] + objs + ["-lcudart"], out_lib,
+                 os.path.join(OBJ, f"link{variant}.log"))
         with open(stamp_file, "w") as fh:
             fh.write(stamp)
     # drop stale objects
     keep = {os.path.basename(o) for o in objs}
     for f in os.listdir(OBJ):
-        if f.endswith(".o") and f not in keep:
+        if f.endswith(".o") and f not in keep and (".chk." in f) == checked:
             os.remove(os.path.join(OBJ, f))
-    return CUDA_LIB
+    return out_lib
 
 
 def build_host(verbose: bool = True) -> str:
@@ -108,12 +116,16 @@ def build_host(verbose: bool = True) -> str:
     return HOST_LIB
 
 
-def build_all(verbose: bool = True) -> None:
+def build_all(verbose: bool = True, checked: bool = False) -> None:
     build_host(verbose)
     build_cuda(verbose)
+    if checked:
+        build_cuda(verbose, checked=True)
 
 
 if __name__ == "__main__":
-    build_all()
+    build_all(checked="--checked" in sys.argv[1:])
     print(CUDA_LIB)
+    if "--checked" in sys.argv[1:]:
+        print(CHECKED_LIB)
     print(HOST_LIB)

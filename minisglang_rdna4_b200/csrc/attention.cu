@@ -172,6 +172,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
           int col = first_page + p;
           col = col < args.bt_stride ? col : args.bt_stride - 1;
           int page = bt[col];
+          (void)MSGL_OOB(page, args.num_pages + 1);
           page = page < 0 ? 0 : (page > args.num_pages ? args.num_pages : page);
 #pragma unroll
           for (int pl = 0; pl < PLANES; ++pl) {
@@ -619,6 +620,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
           int col = first_page + p;
           col = col < args.bt_stride ? col : args.bt_stride - 1;
           int page = bt[col];
+          (void)MSGL_OOB(page, args.num_pages + 1);
           page = page < 0 ? 0 : (page > args.num_pages ? args.num_pages : page);
 #pragma unroll
           for (int pl = 0; pl < PLANES; ++pl) {

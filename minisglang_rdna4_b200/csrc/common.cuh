@@ -130,7 +130,64 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_trigger();
 }
 
+// Bounds-checking build (-DMSGL_CHECK_BOUNDS, library libmsgl_cuda_checked.so): every index a kernel
+// takes from a device array (token slot, page id, position, expert id, request slot) goes through
+// MSGL_OOB(value, limit) before it is used. A value outside [0, limit) is recorded as
+// (source line, value, limit) in a small ring of the translation unit and the macro yields true,
+// on which the kernel skips that access; nothing traps. The host collects and clears the rings of
+// all translation units with msgl_bounds_report(). In the regular build the macro is `false`
+// and the kernels keep their silent clamps.
+#ifdef MSGL_CHECK_BOUNDS
+struct BoundsRecord {
+  int line;
+  int pad;
+  long long value, limit;
+};
+constexpr int kBoundsRing = 16;
+static __device__ BoundsRecord t_bounds_ring[kBoundsRing];
+static __device__ unsigned int t_bounds_count;
+__device__ __forceinline__ bool oob_record(long long v, long long limit, int line) {
+  if (v >= 0 && v < limit) return false;
+  const unsigned int i = atomicAdd(&t_bounds_count, 1u);
+  if (i < (unsigned)kBoundsRing) {
+    t_bounds_ring[i].line = line;
+    t_bounds_ring[i].value = v;
+    t_bounds_ring[i].limit = limit;
+  }
+  return true;
+}
+#define MSGL_OOB(value, limit) ::msgl::oob_record((long long)(value), (long long)(limit), __LINE__)
+#else
+#define MSGL_OOB(value, limit) false
+#endif
+
 }  // namespace msgl
+
+#ifdef MSGL_CHECK_BOUNDS
+// Each translation unit registers a collector for its own ring when the library is loaded (host
+// code only); msgl_bounds_report (elementwise.cu) walks the collectors.
+typedef int (*msgl_bounds_collect_fn)(const char** file, msgl::BoundsRecord* out, int max_records);
+void msgl_bounds_register(msgl_bounds_collect_fn fn);
+namespace {
+int msgl_bounds_collect_tu(const char** file, msgl::BoundsRecord* out, int max_records) {
+  *file = __FILE__;
+  unsigned int n = 0;
+  if (cudaMemcpyFromSymbol(&n, msgl::t_bounds_count, sizeof(n)) != cudaSuccess || n == 0) return 0;
+  msgl::BoundsRecord ring[msgl::kBoundsRing];
+  if (cudaMemcpyFromSymbol(ring, msgl::t_bounds_ring, sizeof(ring)) != cudaSuccess) return 0;
+  const unsigned int zero = 0;
+  cudaMemcpyToSymbol(msgl::t_bounds_count, &zero, sizeof(zero));
+  int k = (int)(n < (unsigned)msgl::kBoundsRing ? n : (unsigned)msgl::kBoundsRing);
+  if (k > max_records) k = max_records;
+  for (int i = 0; i < k; ++i) out[i] = ring[i];
+  return k;
+}
+struct MsglBoundsRegistrar {
+  MsglBoundsRegistrar() { msgl_bounds_register(&msgl_bounds_collect_tu); }
+};
+MsglBoundsRegistrar g_msgl_bounds_registrar;
+}  // namespace
+#endif
 
 // Host side: launches go through msgl_launch, which adds the programmatic-stream-serialization
 // attribute unless msgl_set_pdl(0) switched it off. The kernel argument list must be complete

@@ -36,6 +36,7 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* _
                                  uint4* __restrict__ out, int row_vecs, int start, int len) {
   pdl_enter();
   int row = blockIdx.x;
+  (void)MSGL_OOB(ids[row], 0x7fffffffLL);   // a negative token id
   int id = ids[row] - start;
   bool inside = id >= 0 && id < len;
   const uint4* src = w + (size_t)(inside ? id : 0) * row_vecs;
@@ -412,4 +413,54 @@ MSGL_API int msgl_quant_fp8(const void* x, void* out_q, void* out_scale, int row
     return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("quant_fp8");
   return MSGL_OK;
+}
+
+
+// ---------------------------------------------------------------------------------- bounds-check report
+#ifdef MSGL_CHECK_BOUNDS
+namespace {
+constexpr int kMaxCollectors = 64;
+msgl_bounds_collect_fn g_collectors[kMaxCollectors];
+int g_num_collectors = 0;
+}  // namespace
+void msgl_bounds_register(msgl_bounds_collect_fn fn) {
+  if (g_num_collectors < kMaxCollectors) g_collectors[g_num_collectors++] = fn;
+}
+#endif
+
+// 1 when this library was built with the device-side bounds checks.
+MSGL_API int msgl_bounds_enabled() {
+#ifdef MSGL_CHECK_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Collects (and clears) the out-of-range indices the kernels of this library have recorded on the
+// current device since the last call. Writes up to `max_lines` text lines of `line_bytes` bytes each
+// ("file.cu:LINE value V limit L") into `text`; returns the number of records. Synchronises the device.
+MSGL_API int msgl_bounds_report(char* text, int max_lines, int line_bytes) {
+#ifdef MSGL_CHECK_BOUNDS
+  cudaDeviceSynchronize();
+  int total = 0;
+  for (int c = 0; c < g_num_collectors; ++c) {
+    const char* file = "";
+    msgl::BoundsRecord recs[msgl::kBoundsRing];
+    const int n = g_collectors[c](&file, recs, msgl::kBoundsRing);
+    const char* base = file;
+    for (const char* p = file; *p; ++p)
+      if (*p == '/') base = p + 1;
+    for (int i = 0; i < n; ++i) {
+      if (total < max_lines && text != nullptr)
+        snprintf(text + (size_t)total * line_bytes, line_bytes, "%s:%d value %lld limit %lld", base, recs[i].line,
+                 recs[i].value, recs[i].limit);
+      ++total;
+    }
+  }
+  return total;
+#else
+  (void)text; (void)max_lines; (void)line_bytes;
+  return 0;
+#endif
 }

@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
     }
     __syncwarp();
     int pos = positions[token];
+    (void)MSGL_OOB(pos, max_pos);
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
     const float* cs = cos_sin + (size_t)pos * rot;
     const int half = rot >> 1;
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
   }
   const int kvh = is_k ? head - hq : head - hq - hk;
   int slot = out_loc[token];
+  if (slot >= 0) (void)MSGL_OOB(slot, num_slots);
   if (slot < 0 || slot >= num_slots) return;  // padded row: nothing to store
   const int page = slot / page_size, off = slot % page_size;
   const size_t base = (((size_t)page * hk + kvh) * page_size + off) * D;
@@ -171,6 +173,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_fast_kernel(
       }
     }
     int pos = positions[token];
+    (void)MSGL_OOB(pos, max_pos);
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
     const float* cs = cos_sin + (size_t)pos * D;
 #pragma unroll
@@ -198,6 +201,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_fast_kernel(
   }
   const int kvh = is_k ? head - hq : head - hq - hk;
   const int slot = out_loc[token];
+  if (slot >= 0) (void)MSGL_OOB(slot, num_slots);
   if (slot < 0 || slot >= num_slots) return;
   const int page = slot / page_size, off = slot % page_size;
   const size_t base = (((size_t)page * hk + kvh) * page_size + off) * D;
@@ -265,6 +269,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_vec128_kernel(
       }
     }
     int pos = positions[token];
+    (void)MSGL_OOB(pos, max_pos);
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
     const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * D + sub * 8);
     const float4* sn = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * D + H2 + sub * 8);
@@ -286,6 +291,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_vec128_kernel(
   }
   const int kvh = is_k ? head - hq : head - hq - hk;
   const int slot = out_loc[token];
+  if (slot >= 0) (void)MSGL_OOB(slot, num_slots);
   if (slot < 0 || slot >= num_slots) return;
   const int page = slot / page_size, off = slot % page_size;
   const size_t base = (((size_t)page * hk + kvh) * page_size + off) * D;
@@ -374,6 +380,7 @@ __global__ void store_kv_kernel(const T* __restrict__ k, const T* __restrict__ v
   pdl_enter();
   const int token = blockIdx.x;
   const int slot = out_loc[token];
+  if (slot >= 0) (void)MSGL_OOB(slot, num_slots);
   if (slot < 0 || slot >= num_slots) return;
   const int page = slot / page_size, off = slot % page_size;
   for (int i = threadIdx.x; i < hk * d; i += blockDim.x) {

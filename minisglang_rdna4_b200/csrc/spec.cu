@@ -64,6 +64,7 @@ __global__ void spec_write_draft_kernel(const int32_t* __restrict__ ids, const i
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int id = ids[i];
+  (void)MSGL_OOB(id, draft_vocab);
   id = id < 0 ? 0 : (id >= draft_vocab ? draft_vocab - 1 : id);
   const int t = id + (int)d2t[id];
   if (dst_idx[i] >= 0) token_pool[dst_idx[i]] = t;

@@ -175,7 +175,8 @@ class Engine:
         self.q_heads_local = div_even(mc.num_qo_heads, config.tp_size)
         kv_fp8 = config.kv_cache_dtype == "fp8" or (config.kv_cache_dtype == "auto" and (
             ENV.KV_FP8.value or (mc.quant is not None and mc.quant.kv_cache_fp8)))
-        self.kv_fp8 = bool(kv_fp8)
+        self.kv_calibrating = bool(ENV.KV_FP8_CALIBRATE.value)
+        self.kv_fp8 = bool(kv_fp8) and not self.kv_calibrating
         self.num_pages = self._determine_num_pages()
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
@@ -192,6 +193,9 @@ class Engine:
                                                config.tp_size)
             self.kv_cache.set_scales(ks, vs)
             logger.info_rank0("fp8 KV scales: %s", source)
+        if self.kv_calibrating:
+            self.kv_cache.start_calibration()
+            logger.info_rank0("fp8 KV calibration run: 16-bit pool, eager steps")
         self.ledger.add("kv pool", self.kv_cache._buf.numel() * self.kv_cache._buf.element_size())
         self.boot.mark("kv pool")
         # slot max_running_req is the dummy request used to pad graph batches
@@ -280,7 +284,7 @@ class Engine:
             # model parameters never change while kernels run, unless experts are paged in from the
             # host tier: only then must a GEMM wait for the stream before it reads its weights
             K.gemm_static_weights(ENV.PDL.value and not host_tier)
-        if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and (config.cuda_graph_max_bs or 0) >= 0
+        if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and not self.kv_calibrating and (config.cuda_graph_max_bs or 0) >= 0
                 and not ep_replicas and not host_tier):
             from .graph import GraphRunner
 
@@ -545,6 +549,9 @@ class Engine:
                                 plan.sample_rows, plan.write_idx, plan.max_q, plan.max_kv)
         if ENV.CHECK_BOUNDS.value:
             self._check_plan_bounds(plan)
+            self._bounds_steps = getattr(self, "_bounds_steps", 0) + 1
+            if self._bounds_steps % 64 == 0:
+                self.check_device_bounds()
         token_idx, positions, out_loc, cu_q, seq_lens, block_table, sample_rows, write_idx = self._stage(plan)
         batch.positions = positions
         batch.out_loc = out_loc
@@ -639,11 +646,51 @@ class Engine:
         dist.broadcast(tokens, src=self.config.dp_rank * self.config.tp_size, group=self.tp_group)
         return tokens
 
+    def check_device_bounds(self) -> None:
+        """``MSGL_CHECK_BOUNDS=1`` on a GPU: collect what the bounds-checking kernel build recorded
+        (out-of-range indices that the kernels skipped) and re-read the guard zones around the
+        kernels' workspaces; anything found is an error naming the source line or the workspace."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import cuda as K
+
+        found = K.bounds_report() + [f"workspace overrun: {n}" for n in K.verify_workspaces()]
+        if found:
+            raise RuntimeError("device-side bounds check: " + "; ".join(found))
+
+    def finish_kv_calibration(self, path: Optional[str] = None, margin: float = 1.0):
+        """End a calibration run (``MSGL_KV_FP8_CALIBRATE=1``): per-(layer, kv head) descales from the
+        recorded amax, heads of all tensor-parallel ranks put back in checkpoint order, written as the
+        side-car ``kv_scales.safetensors`` that an fp8-KV engine picks up at boot
+        (python/minisgl/kvcache/mha_pool.py:207-270, tools/kv_fp8_calibrate.py). Returns
+        ``(k_scale, v_scale)`` with the full head count."""
+        k, v = self.kv_cache.finish_calibration(margin)
+        cfg = self.config
+        total = self.model_config.num_kv_heads
+        if cfg.tp_size > 1 and self.cpu_group is not None:
+            parts: List = [None] * cfg.tp_size
+            dist.all_gather_object(parts, (k, v), group=self.cpu_group)
+            # with fewer kv heads than ranks a head is replicated on tp_size // total neighbouring ranks
+            step = max(cfg.tp_size // total, 1)
+            k = torch.cat([parts[r][0] for r in range(0, cfg.tp_size, step)], dim=1)
+            v = torch.cat([parts[r][1] for r in range(0, cfg.tp_size, step)], dim=1)
+        if path is None and cfg.model_path and os.path.isdir(cfg.model_path):
+            path = os.path.join(cfg.model_path, "kv_scales.safetensors")
+        if path is not None and cfg.tp_rank == 0:
+            from safetensors.torch import save_file
+
+            save_file({"k_scale": k.contiguous(), "v_scale": v.contiguous()}, path)
+            logger.info_rank0("fp8 KV scales written to %s (k %.4g..%.4g, v %.4g..%.4g)", path, float(k.min()),
+                              float(k.max()), float(v.min()), float(v.max()))
+        return k, v
+
     def shutdown(self) -> None:
         """Release what would keep a process-group teardown waiting: captured graphs (they hold
         NCCL kernels), peer-memory mappings, then meet the other ranks at a CPU barrier."""
         import gc
 
+        if ENV.CHECK_BOUNDS.value:
+            self.check_device_bounds()
         set_global_ctx(None)
         if self.graph_runner is not None:
             self.graph_runner.graphs.clear()

@@ -114,13 +114,17 @@ ENV = EnvRegistry()
 
 # --- engine -------------------------------------------------------------------------------
 ENV.flag("KV_FP8", False, "store the paged KV pool as e4m3 with per-(layer,head) scales")
+ENV.flag("KV_FP8_CALIBRATE", False, "calibration run: 16-bit KV pool, eager steps, running |max| per (layer, kv head) "
+         "of every stored row; Engine.finish_kv_calibration writes the kv_scales side-car")
 ENV.flag("DISABLE_OVERLAP", False, "run the synchronous scheduler loop instead of the overlapped one")
 ENV.flag("GEMM_SPLIT_K", False, "experimental: GEMMs with at most 256 rows split K over several SMs (measured slower than full-K tiles; breaks chunk-size invariance)")
 ENV.flag("DISABLE_GRAPH", False, "never capture CUDA graphs (eager decode)")
 ENV.int("GRAPH_MAX_BS", 0, "largest decode batch captured as a CUDA graph (0 = auto)")
 ENV.int("EXIT_AFTER_STEPS", 0, "stop the scheduler loop after this many forward steps (0 = never)")
 ENV.flag("SANITIZE_LOGITS", False, "replace NaN/Inf logits before sampling and count them")
-ENV.flag("CHECK_BOUNDS", False, "validate every step's token / KV-slot / page ids on the host before they reach a kernel")
+ENV.flag("CHECK_BOUNDS", False, "validate every step's token / KV-slot / page ids on the host before they reach a "
+         "kernel; on a GPU also load the bounds-checking kernel build (indices checked on the device, recorded and "
+         "skipped) and put guard zones around the kernels' workspaces")
 ENV.flag("DISPATCH_LEDGER", False, "log once per op which sm_100a kernel served it")
 ENV.str("PROFILE", "", "path of a torch.profiler chrome trace to write around the profiled steps")
 ENV.int("PROFILE_SKIP", 8, "forward steps to skip before the profiler window opens")

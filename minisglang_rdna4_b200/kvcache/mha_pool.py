@@ -45,6 +45,40 @@ class MHAKVCache(BaseKVCachePool):
         )
         self.k_scale = torch.ones((num_layers, num_kv_heads), dtype=torch.float32, device=device)
         self.v_scale = torch.ones((num_layers, num_kv_heads), dtype=torch.float32, device=device)
+        # calibration run (16-bit pool only): running |max| per (layer, head) of every row written
+        self.amax: Optional[torch.Tensor] = None
+
+    # ---- calibration of the fp8 descales (python/minisgl/kvcache/mha_pool.py:123-270) ----
+    def start_calibration(self) -> None:
+        """Record the largest |value| per (layer, kv head) of all K / V rows stored from now on.
+        Runs against a 16-bit pool, so the first calibration of a model does not need fp8 scales."""
+        if self.fp8:
+            raise ValueError("calibrate the fp8 KV scales on a 16-bit pool (--kv-dtype auto)")
+        self.amax = torch.zeros((2, self.num_layers, self.num_kv_heads), dtype=torch.float32, device=self.device)
+
+    def observe_written(self, layer: int, out_loc: torch.Tensor) -> None:
+        """Fold the rows just stored at token slots ``out_loc`` of ``layer`` into the running amax."""
+        if self.amax is None or out_loc.numel() == 0:
+            return
+        loc = out_loc.long()
+        page, off = loc // self.page_size, loc % self.page_size
+        keep = page < self.num_pages                       # padded graph rows write the dummy page
+        page, off = page[keep], off[keep]
+        for which in (0, 1):
+            rows = self._buf[which, layer][page, :, off]   # [n, heads, dim]
+            if rows.numel():
+                self.amax[which, layer] = torch.maximum(self.amax[which, layer], rows.float().abs().amax(dim=(0, 2)))
+
+    def finish_calibration(self, margin: float = 1.0):
+        """Descales ``(k_scale, v_scale)`` ``[layers, heads]`` = amax * margin / 448; a head that saw
+        no data keeps 1.0. Ends the recording."""
+        from .fp8_scales import FP8_MAX
+
+        if self.amax is None:
+            raise ValueError("no calibration is running")
+        amax, self.amax = self.amax, None
+        scales = torch.where(amax > 0, amax * margin / FP8_MAX, torch.ones_like(amax)).clamp_min(1e-6)
+        return scales[0].cpu(), scales[1].cpu()
 
     # ---- accessors ----
     @property

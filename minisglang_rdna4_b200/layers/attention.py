@@ -44,5 +44,7 @@ class AttentionLayer(BaseOP):
             self._eps, pool.k_cache(layer), pool.v_cache(layer), batch.out_loc, k_scale, v_scale,
             self._rotary.interleaved,
         )
+        if getattr(pool, "amax", None) is not None:
+            pool.observe_written(layer, batch.out_loc)
         out = ctx.attn_backend.forward(q, layer, batch, scale=self._scale, window=self._window)
         return out.reshape(out.shape[0], self._hq * self._d)

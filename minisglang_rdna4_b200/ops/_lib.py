@@ -12,6 +12,15 @@ from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmsgl_cuda.so")
+# built with -DMSGL_CHECK_BOUNDS (python -m minisglang_rdna4_b200.build --checked); chosen by MSGL_CHECK_BOUNDS=1
+CHECKED_LIB_PATH = os.path.join(_HERE, "libmsgl_cuda_checked.so")
+
+
+def _wanted_lib() -> str:
+    flag = (os.environ.get("MSGL_CHECK_BOUNDS") or os.environ.get("MINISGL_CHECK_BOUNDS") or "").strip().lower()
+    if flag in ("1", "true", "yes", "on") and os.path.exists(CHECKED_LIB_PATH):
+        return CHECKED_LIB_PATH
+    return LIB_PATH
 
 c_p = ctypes.c_void_p
 c_i = ctypes.c_int
@@ -62,11 +71,12 @@ class NativeLibraryMissing(RuntimeError):
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = _wanted_lib()
+        if not os.path.exists(path):
             raise NativeLibraryMissing(
-                f"{LIB_PATH} is missing: run `python -m minisglang_rdna4_b200.build` "
+                f"{path} is missing: run `python -m minisglang_rdna4_b200.build` "
                 "(the CUDA ops have no eager fallback)")
-        handle = ctypes.CDLL(LIB_PATH)
+        handle = ctypes.CDLL(path)
         for name, (res, args) in _SIGNATURES.items():
             fn = getattr(handle, name, None)
             if fn is None:

@@ -33,6 +33,60 @@ def _count(op: str, kernel: str, n: int = 1) -> None:
             print(f"[sm100-engage] {op} -> {kernel}", flush=True)
 
 
+# ---- guarded workspaces and the device-side bounds report (MSGL_CHECK_BOUNDS=1) ----
+_GUARD_BYTES = 256
+_GUARD_BYTE = 0xA5
+_GUARDED: Dict[str, Tuple[torch.Tensor, int]] = {}
+
+
+def workspace(name: str, numel: int, dtype, device, zero: bool = False) -> torch.Tensor:
+    """A scratch buffer the kernels write. With ``MSGL_CHECK_BOUNDS=1`` it sits between two 256-byte
+    guard zones filled with a byte pattern, which :func:`verify_workspaces` re-reads: a kernel that
+    wrote past either end of its scratch is named instead of corrupting a neighbour silently."""
+    if not ENV.CHECK_BOUNDS.value:
+        return (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=device)
+    item = torch.empty((), dtype=dtype).element_size()
+    g = _GUARD_BYTES // item
+    full = (torch.zeros if zero else torch.empty)(numel + 2 * g, dtype=dtype, device=device)
+    raw = full.view(torch.uint8)
+    raw[:_GUARD_BYTES] = _GUARD_BYTE
+    raw[raw.numel() - _GUARD_BYTES:] = _GUARD_BYTE
+    _GUARDED[f"{name}@{device}"] = (full, g)
+    return full[g:g + numel]
+
+
+def verify_workspaces() -> list:
+    """Names of the guarded workspaces whose guard zones no longer hold the pattern (synchronises)."""
+    bad = []
+    for name, (full, g) in _GUARDED.items():
+        raw = full.view(torch.uint8)
+        lo, hi = raw[:_GUARD_BYTES], raw[raw.numel() - _GUARD_BYTES:]
+        if not (bool((lo == _GUARD_BYTE).all()) and bool((hi == _GUARD_BYTE).all())):
+            bad.append(name)
+    return bad
+
+
+def bounds_checks_enabled() -> bool:
+    """True when the loaded library is the bounds-checking build."""
+    from ._lib import bind, c_i
+
+    bind("msgl_bounds_enabled", c_i, [])
+    return bool(lib().msgl_bounds_enabled())
+
+
+def bounds_report(max_lines: int = 64) -> list:
+    """Out-of-range indices recorded by the kernels since the last call, as text lines
+    ``file.cu:LINE value V limit L`` (empty with the regular library). Synchronises the device."""
+    from ._lib import bind, c_i, c_p
+
+    bind("msgl_bounds_report", c_i, [c_p, c_i, c_i])
+    width = 96
+    buf = ctypes.create_string_buffer(max_lines * width)
+    n = int(lib().msgl_bounds_report(buf, max_lines, width))
+    raw = buf.raw
+    return [raw[i * width:(i + 1) * width].split(b"\0", 1)[0].decode() for i in range(min(n, max_lines))]
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -209,7 +263,7 @@ def make_pool_buffer(num_layers, pages_plus_one, hk, page_size, d, dtype, device
 
 
 def attention_workspace(max_rows, hq, d, device, max_splits=16):
-    return torch.empty(max_splits * max_rows * hq * (d + 1), dtype=torch.float32, device=device)
+    return workspace("attention split partials", max_splits * max_rows * hq * (d + 1), torch.float32, device)
 
 
 def choose_splits(batch, hk, max_kv, decode):
@@ -342,8 +396,8 @@ def _tc_scratch(device, dtype, hk: int, rows: int):
     hit = _TC_SCRATCH.get(key)
     if hit is None or hit[2] < rows:
         cap = -(-rows // 8192) * 8192
-        _TC_SCRATCH[key] = hit = (torch.zeros(hk * cap * 128, dtype=dtype, device=device),
-                                   torch.zeros(hk * cap * 128, dtype=dtype, device=device), cap)
+        _TC_SCRATCH[key] = hit = (workspace(f"prefill K scratch {hk}", hk * cap * 128, dtype, device, zero=True),
+                                   workspace(f"prefill V scratch {hk}", hk * cap * 128, dtype, device, zero=True), cap)
     return hit
 
 
@@ -404,7 +458,7 @@ def _splitk_counters(device, n: int) -> torch.Tensor:
     """Per-tile arrival counters: zero between calls (the kernel resets what it used)."""
     t = _SPLITK_COUNTERS.get(device)
     if t is None or t.numel() < n:
-        t = _SPLITK_COUNTERS[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+        t = _SPLITK_COUNTERS[device] = workspace("split-K counters", max(n, 4096), torch.int32, device, zero=True)
     return t
 
 
@@ -596,7 +650,7 @@ def _w4_scratch(device, dtype, elems: int) -> torch.Tensor:
     key = (device, dtype)
     t = _W4_SCRATCH.get(key)
     if t is None or t.numel() < elems:
-        t = _W4_SCRATCH[key] = torch.empty(elems, dtype=dtype, device=device)
+        t = _W4_SCRATCH[key] = workspace("4-bit expansion scratch", elems, dtype, device)
     return t
 
 

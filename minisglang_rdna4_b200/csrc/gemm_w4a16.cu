@@ -15,11 +15,13 @@
 // because they take power-of-two (UE8M0) scales per 32 elements, which neither format has.
 //
 // Pipeline per CTA (persistent, one 128 x 128 output tile at a time, K blocks of 64):
-//   warp 0       TMA producer: A tile (128 x 64, 128-byte swizzle) and the raw packed weight tile
-//                (128 rows x 32 bytes) per stage
+//   warp 0       TMA producer: one or two A tiles (128 x 64, 128-byte swizzle) and the raw packed
+//                weight tile (128 rows x 32 bytes) per stage
 //   warp 1       MMA issuer, owner of tensor memory (two accumulator buffers)
 //   warps 2-5    epilogue (tcgen05.ld, convert, store)
-//   warps 6-9    expanders: thread r owns weight row r of the tile
+//   warps 6-13   expanders: two threads per weight row of the tile, group parameters fetched one
+//                K block ahead
+// With more than 128 rows, two activation tiles are multiplied from each expanded weight tile.
 // All waits are bounded; a wait that runs out sets a status word and the CTA unwinds.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -34,25 +36,32 @@ using namespace msgl::ptx;
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kThreads = 320;
-constexpr int STAGES = 5;
-constexpr int A_BYTES = BM * BK * 2;       // 16 KB
+constexpr int kThreads = 448;              // TMA, MMA, 4 epilogue warps, 8 expander warps
+constexpr int kExpandWarp0 = 6, kExpandWarps = 8;
+constexpr int A_BYTES = BM * BK * 2;       // 16 KB per 128-row activation tile
 constexpr int B_BYTES = BN * BK * 2;       // 16 KB, written by the expanders
 constexpr int RAW_BYTES = BN * BK / 2;     // 4 KB packed codes
-constexpr int off_a = 0;
-constexpr int off_b = off_a + STAGES * A_BYTES;
-constexpr int off_raw = off_b + STAGES * B_BYTES;
-constexpr int off_bar = off_raw + STAGES * RAW_BYTES;
-constexpr int n_bars = 3 * STAGES + 4;     // loaded / expanded / empty per stage, tfull / tempty per accumulator
-constexpr int smem_total = off_bar + n_bars * 8 + 16;
-constexpr int NCOLS = 256;
+
+// MT = activation tiles (of 128 rows) that share one expanded weight tile: with 129..256 rows both
+// tiles of a column block are multiplied from one expansion.
+template <int MT> struct Cfg {
+  static constexpr int STAGES = MT == 1 ? 5 : 4;
+  static constexpr int STAGE_A = MT * A_BYTES;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * STAGE_A;
+  static constexpr int off_raw = off_b + STAGES * B_BYTES;
+  static constexpr int off_bar = off_raw + STAGES * RAW_BYTES;
+  static constexpr int n_bars = 3 * STAGES + 4;   // loaded / expanded / empty per stage, tfull / tempty per buffer
+  static constexpr int smem_total = off_bar + n_bars * 8 + 16;
+  static constexpr int NCOLS = 2 * MT * BN;       // two accumulator buffers of MT tiles
+};
 
 enum W4Format : int { W4_INT = 0, W4_NVFP4 = 1 };
 
 struct W4Args {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
-  int group;                 // K elements per scale (multiple of 16; 16 for NVFP4)
+  int group;                 // K elements per scale: 16 or a multiple of 32
   int fmt;
   const void* scales;        // [K / group, N]: fp32 (int formats) or e4m3 bytes (NVFP4)
   const float* zeros;        // [K / group, N] fp32 (int formats)
@@ -67,11 +76,16 @@ struct W4Args {
 
 __device__ int g_w4_status = 0;
 
+// e2m1 code -> value {0, .5, 1, 1.5, 2, 3, 4, 6} with sign, built from the float's bit fields
 __device__ __forceinline__ float e2m1_value(uint32_t nib) {
   const uint32_t e = (nib >> 1) & 3u, m = nib & 1u;
-  float mag = e == 0 ? 0.5f * (float)m : (1.0f + 0.5f * (float)m) * (float)(1u << (e - 1));
-  return (nib & 8u) ? -mag : mag;
+  const uint32_t normal = ((126u + e) << 23) | (m << 22);
+  const uint32_t sub = m ? 0x3F000000u : 0u;
+  return __uint_as_float((e ? normal : sub) | ((nib & 8u) << 28));
 }
+
+// integer code 0..15 as a float without an int->float conversion: 2^23 + code, minus 2^23 (exact)
+__device__ __forceinline__ float code_value(uint32_t nib) { return __uint_as_float(0x4B000000u | nib) - 8388608.0f; }
 
 __device__ __forceinline__ uint32_t pack2(bool bf16, float a, float b) {
   if (bf16) {
@@ -82,28 +96,35 @@ __device__ __forceinline__ uint32_t pack2(bool bf16, float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// MT: activation tiles per weight tile; INT: integer codes with zero points (else NVFP4); BF: bf16
+// activations (else f16). Format and type are compile-time so that the expanders' inner loop holds
+// one conversion only.
+template <int MT, bool INT, bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_w,
                   const W4Args args) {
+  using C = Cfg<MT>;
+  constexpr int STAGES = C::STAGES;
   extern __shared__ __align__(1024) uint8_t smem_raw_[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t bar_base = s_base + off_bar;
+  const uint32_t bar_base = s_base + C::off_bar;
   auto loaded_bar = [&](int s) { return bar_base + 8u * s; };
   auto expanded_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
   auto tfull_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + s); };
   auto tempty_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + 2 + s); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + off_bar + n_bars * 8);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + off_bar + n_bars * 8 + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::off_bar + C::n_bars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::off_bar + C::n_bars * 8 + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = args.m_tiles * args.n_tiles;
+  const int m_groups = (args.m_tiles + MT - 1) / MT;
+  const int total_units = m_groups * args.n_tiles;    // unit = one weight tile x MT activation tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(loaded_bar(s), 1);
-      mbar_init(expanded_bar(s), 4);   // one arrival per expander warp
+      mbar_init(expanded_bar(s), kExpandWarps);   // one arrival per expander warp
       mbar_init(empty_bar(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -116,7 +137,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     prefetch_tensormap(&tma_w);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), NCOLS);
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::NCOLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -130,13 +151,16 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+      for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x) {
+        const int m_group = unit % m_groups, n_tile = unit / m_groups;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 131)) break;
-          mbar_expect_tx(loaded_bar(stage), A_BYTES + RAW_BYTES);
-          tma_load_2d(s_base + off_a + stage * A_BYTES, &tma_a, loaded_bar(stage), kb * BK, m_tile * BM);
-          tma_load_2d(s_base + off_raw + stage * RAW_BYTES, &tma_w, loaded_bar(stage), kb * (BK / 2), n_tile * BN);
+          mbar_expect_tx(loaded_bar(stage), MT * A_BYTES + RAW_BYTES);
+          tma_load_2d(s_base + C::off_raw + stage * RAW_BYTES, &tma_w, loaded_bar(stage), kb * (BK / 2), n_tile * BN);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)   // rows past M read as zeros
+            tma_load_2d(s_base + C::off_a + stage * C::STAGE_A + mt * A_BYTES, &tma_a, loaded_bar(stage), kb * BK,
+                        (m_group * MT + mt) * BM);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -151,20 +175,23 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      const uint32_t idesc = args.act_bf16 ? idesc_dense(1, 1, BM, BN) : idesc_dense(0, 0, BM, BN);
-      for (int tile = blockIdx.x; tile < total_tiles && ok && !*abort_flag; tile += gridDim.x) {
+      const uint32_t idesc = BF ? idesc_dense(1, 1, BM, BN) : idesc_dense(0, 0, BM, BN);
+      for (int unit = blockIdx.x; unit < total_units && ok && !*abort_flag; unit += gridDim.x) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 132)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * (MT * BN);
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(expanded_bar(stage), phase, abort_flag, args.status, 133)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_s = s_base + off_a + stage * A_BYTES;
-          const uint32_t b_s = s_base + off_b + stage * B_BYTES;
+          const uint32_t b_s = s_base + C::off_b + stage * B_BYTES;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // four K = 16 steps of 32 bytes inside the 128-byte rows
-            mma_f16(d_tmem, smem_desc_sw128(a_s + k * 32), smem_desc_sw128(b_s + k * 32), idesc,
-                    (kb != 0 || k != 0) ? 1u : 0u);
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t a_s = s_base + C::off_a + stage * C::STAGE_A + mt * A_BYTES;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)   // four K = 16 steps of 32 bytes inside the 128-byte rows
+              mma_f16(d_tmem + mt * BN, smem_desc_sw128(a_s + k * 32), smem_desc_sw128(b_s + k * 32), idesc,
+                      (kb != 0 || k != 0) ? 1u : 0u);
+          }
           tc_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -173,47 +200,50 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < kExpandWarp0) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
-      const int row = m_tile * BM + q * 32 + lane;
-      const bool row_ok = row < args.M;
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+      const int m_group = unit % m_groups, n_tile = unit / m_groups;
       const int colbase = n_tile * BN;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 134)) break;
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-      for (int cblk = 0; cblk < BN / 32; ++cblk) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + cblk * 32, r);
-        tmem_ld_wait();
-        if (row_ok) {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = (m_group * MT + mt) * BM + q * 32 + lane;
+        const bool row_ok = row < args.M;
+        const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * (MT * BN) + mt * BN);
+#pragma unroll 1
+        for (int cblk = 0; cblk < BN / 32; ++cblk) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + cblk * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = colbase + cblk * 32 + g * 8;
-            if (col < args.N) {
-              float o[8];
+            for (int g = 0; g < 4; ++g) {
+              const int col = colbase + cblk * 32 + g * 8;
+              if (col < args.N) {
+                float o[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float x = __uint_as_float(r[g * 8 + e]);
-                if (args.bias != nullptr)
-                  x += args.act_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col + e])
-                                     : __half2float(reinterpret_cast<const __half*>(args.bias)[col + e]);
-                o[e] = x;
-              }
-              if (args.out_dtype == MSGL_F32) {
-                float* cp = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + col;
-                *reinterpret_cast<float4*>(cp) = make_float4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<float4*>(cp + 4) = make_float4(o[4], o[5], o[6], o[7]);
-              } else {
-                const bool bf = args.out_dtype == MSGL_BF16;
-                uint16_t* cp = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc + col;
-                *reinterpret_cast<uint4*>(cp) = make_uint4(pack2(bf, o[0], o[1]), pack2(bf, o[2], o[3]),
-                                                           pack2(bf, o[4], o[5]), pack2(bf, o[6], o[7]));
+                for (int e = 0; e < 8; ++e) {
+                  float x = __uint_as_float(r[g * 8 + e]);
+                  if (args.bias != nullptr)
+                    x += BF ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(args.bias)[col + e])
+                            : __half2float(reinterpret_cast<const __half*>(args.bias)[col + e]);
+                  o[e] = x;
+                }
+                if (args.out_dtype == MSGL_F32) {
+                  float* cp = reinterpret_cast<float*>(args.c) + (size_t)row * args.ldc + col;
+                  *reinterpret_cast<float4*>(cp) = make_float4(o[0], o[1], o[2], o[3]);
+                  *reinterpret_cast<float4*>(cp + 4) = make_float4(o[4], o[5], o[6], o[7]);
+                } else {
+                  const bool bf = args.out_dtype == MSGL_BF16;
+                  uint16_t* cp = reinterpret_cast<uint16_t*>(args.c) + (size_t)row * args.ldc + col;
+                  *reinterpret_cast<uint4*>(cp) = make_uint4(pack2(bf, o[0], o[1]), pack2(bf, o[2], o[3]),
+                                                             pack2(bf, o[4], o[5]), pack2(bf, o[6], o[7]));
+                }
               }
             }
           }
@@ -225,53 +255,73 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
-    // ------------------------------------------------------------------ expanders (warps 6..9)
-    const int r = (warp - 6) * 32 + lane;   // weight row of the tile owned by this thread
+    // ------------------------------------------------------------------ expanders (warps 6..13)
+    // Two threads per weight row: thread (r, half) expands k = 32 half .. 32 half + 31 of each K block.
+    // The group parameters of the NEXT K block are fetched before this one's codes are awaited, so
+    // their global-memory latency hides behind the expansion of the current block.
+    const int et = threadIdx.x - kExpandWarp0 * 32;
+    const int r = et & 127, half = et >> 7;
+    constexpr bool bf = BF;
+    constexpr bool is_int = INT;
+    const int per = args.group == 16 ? 2 : 1;            // scales per 32 consecutive k
+    struct Params { float sc0, sc1, zp0, zp1, chan; };
+    auto fetch = [&](int unit, int kb, Params& p) {
+      const int n = (unit / m_groups) * BN + r;
+      p.sc0 = p.sc1 = p.zp0 = p.zp1 = 0.f;
+      p.chan = 1.f;
+      if (n >= args.N) return;
+      const int gi = (kb * BK + half * 32) / args.group;
+      const size_t at = (size_t)gi * args.N + n;
+      if (is_int) {
+        p.sc0 = __ldg(reinterpret_cast<const float*>(args.scales) + at);
+        p.zp0 = __ldg(args.zeros + at);
+        if (per == 2) {
+          p.sc1 = __ldg(reinterpret_cast<const float*>(args.scales) + at + args.N);
+          p.zp1 = __ldg(args.zeros + at + args.N);
+        }
+      } else {
+        p.sc0 = e4m3_to_float(__ldg(reinterpret_cast<const uint8_t*>(args.scales) + at));
+        if (per == 2) p.sc1 = e4m3_to_float(__ldg(reinterpret_cast<const uint8_t*>(args.scales) + at + args.N));
+        if (args.channel != nullptr) p.chan = __ldg(args.channel + n);
+      }
+    };
     int stage = 0;
     uint32_t phase = 0;
-    bool ok = true;
-    const bool bf = args.act_bf16 != 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int n_tile = tile / args.m_tiles;
-      const int n = n_tile * BN + r;
-      const bool n_ok = n < args.N;
-      const float chan = (args.channel != nullptr && n_ok) ? __ldg(args.channel + n) : 1.f;
-      for (int kb = 0; kb < args.k_blocks; ++kb) {
-        if (!mbar_wait(loaded_bar(stage), phase, abort_flag, args.status, 135)) { ok = false; break; }
-        const uint4* raw = reinterpret_cast<const uint4*>(smem + off_raw + stage * RAW_BYTES + r * (BK / 2));
-        const uint4 lo = raw[0], hi = raw[1];   // 64 codes: byte b holds k = 2b (low nibble) and 2b + 1
-        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        uint8_t* brow = smem + off_b + stage * B_BYTES + r * 128;
+    int unit = blockIdx.x, kb = 0;
+    Params cur, nxt;
+    if (unit < total_units) fetch(unit, 0, cur);
+    while (unit < total_units) {
+      int n_unit = unit, n_kb = kb + 1;
+      if (n_kb == args.k_blocks) { n_kb = 0; n_unit += gridDim.x; }
+      if (n_unit < total_units) fetch(n_unit, n_kb, nxt);
+      if (!mbar_wait(loaded_bar(stage), phase, abort_flag, args.status, 135)) break;
+      const uint4 raw = *reinterpret_cast<const uint4*>(smem + C::off_raw + stage * RAW_BYTES + r * (BK / 2) + half * 16);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};   // byte b holds k = 2b (low nibble) and 2b + 1
+      uint8_t* brow = smem + C::off_b + stage * B_BYTES + r * 128;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {        // chunk ch: k = 8 ch .. 8 ch + 7 of this K block
-          const int k0 = kb * BK + ch * 8;
-          const int gi = k0 / args.group;
-          float sc = 0.f, zp = 0.f;
-          if (n_ok && k0 < args.K) {
-            if (args.fmt == W4_INT) {
-              sc = __ldg(reinterpret_cast<const float*>(args.scales) + (size_t)gi * args.N + n);
-              zp = __ldg(args.zeros + (size_t)gi * args.N + n);
-            } else {
-              sc = e4m3_to_float(__ldg(reinterpret_cast<const uint8_t*>(args.scales) + (size_t)gi * args.N + n));
-            }
-          }
-          const uint32_t w = words[ch];
-          float v[8];
+      for (int c = 0; c < 4; ++c) {             // chunk: 8 consecutive k
+        const bool second = per == 2 && c >= 2;
+        const float sc = second ? cur.sc1 : cur.sc0, zp = second ? cur.zp1 : cur.zp0;
+        const uint32_t w = words[c];
+        float v[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const uint32_t nib = (w >> (4 * e)) & 0xFu;
-            // e2m1 x e4m3 is exact in fp32; the channel factor is the one rounding, as in a load-time expansion
-            v[e] = args.fmt == W4_INT ? ((float)nib - zp) * sc : (e2m1_value(nib) * sc) * chan;
-          }
-          // 128-byte swizzle: 16-byte chunk ch of row r lives at chunk position ch ^ (r & 7)
-          *reinterpret_cast<uint4*>(brow + ((ch ^ (r & 7)) << 4)) =
-              make_uint4(pack2(bf, v[0], v[1]), pack2(bf, v[2], v[3]), pack2(bf, v[4], v[5]), pack2(bf, v[6], v[7]));
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t nib = (w >> (4 * e)) & 0xFu;
+          // e2m1 x e4m3 is exact in fp32; the channel factor is the one rounding, as in a load-time expansion
+          v[e] = is_int ? (code_value(nib) - zp) * sc : (e2m1_value(nib) * sc) * cur.chan;
         }
-        fence_proxy_async();   // generic-proxy stores become visible to the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(expanded_bar(stage));
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        // 128-byte swizzle: 16-byte chunk ch of row r lives at chunk position ch ^ (r & 7)
+        const int ch = half * 4 + c;
+        *reinterpret_cast<uint4*>(brow + ((ch ^ (r & 7)) << 4)) =
+            make_uint4(pack2(bf, v[0], v[1]), pack2(bf, v[2], v[3]), pack2(bf, v[4], v[5]), pack2(bf, v[6], v[7]));
       }
+      fence_proxy_async();   // generic-proxy stores become visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(expanded_bar(stage));
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      cur = nxt;
+      unit = n_unit;
+      kb = n_kb;
     }
   }
 
@@ -279,7 +329,7 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, NCOLS);
+    tmem_dealloc(tmem_base, C::NCOLS);
   }
 }
 
@@ -370,8 +420,9 @@ int make_map(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, uint64_t
 MSGL_API int msgl_gemm_w4a16(const void* a, long long lda, const void* wq, const void* scales, const void* zeros,
                              const void* channel, const void* bias, void* c, long long ldc, int M, int N, int K,
                              int group, int fmt, int act_dtype, int out_dtype, cudaStream_t stream) {
-  if (M < 0 || N <= 0 || K <= 0 || N % 8 || K % 64 || group < 16 || group % 8 || lda % 8) {
-    msgl_set_error_text("gemm_w4a16: needs N % 8 == 0, K % 64 == 0, group a multiple of 8 (>= 16)");
+  if (M < 0 || N <= 0 || K <= 0 || N % 8 || K % 64 || (group != 16 && (group < 32 || group % 32)) || K % group ||
+      lda % 8) {
+    msgl_set_error_text("gemm_w4a16: needs N % 8 == 0, K % 64 == 0, group 16 or a multiple of 32 that divides K");
     return MSGL_BAD_ARG;
   }
   if (fmt != W4_INT && fmt != W4_NVFP4) return MSGL_BAD_ARG;
@@ -403,10 +454,20 @@ MSGL_API int msgl_gemm_w4a16(const void* a, long long lda, const void* wq, const
   rc = make_map(&mw, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK / 2, BN, false,
                 true);
   if (rc) return rc;
-  constexpr int smem = smem_total + 1024;
+  constexpr int smem1 = Cfg<1>::smem_total + 1024, smem2 = Cfg<2>::smem_total + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaSuccess;
+#define MSGL_W4_ATTR(MT_, SMEM_)                                                                                    \
+  for (int v = 0; v < 4 && e == cudaSuccess; ++v)                                                                  \
+    e = cudaFuncSetAttribute(v == 0   ? gemm_w4a16_kernel<MT_, true, true>                                         \
+                             : v == 1 ? gemm_w4a16_kernel<MT_, true, false>                                        \
+                             : v == 2 ? gemm_w4a16_kernel<MT_, false, true>                                        \
+                                      : gemm_w4a16_kernel<MT_, false, false>,                                      \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_);
+    MSGL_W4_ATTR(1, smem1)
+    MSGL_W4_ATTR(2, smem2)
+#undef MSGL_W4_ATTR
     if (e != cudaSuccess) { msgl_set_error("w4a16 gemm smem attribute", e); return MSGL_CUDA_ERROR; }
     configured = true;
   }
@@ -417,9 +478,18 @@ MSGL_API int msgl_gemm_w4a16(const void* a, long long lda, const void* wq, const
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
   }
-  int grid = args.m_tiles * args.n_tiles;
+  // pairs of activation tiles share one weight expansion whenever there is more than one tile
+  const bool pair = args.m_tiles > 1;
+  int grid = ((args.m_tiles + (pair ? 1 : 0)) / (pair ? 2 : 1)) * args.n_tiles;
   if (grid > sms) grid = sms;
-  cudaError_t e = msgl_launch(gemm_w4a16_kernel, dim3(grid), dim3(kThreads), smem, stream, ma, mw, args);
+  void (*kernel)(const CUtensorMap, const CUtensorMap, const W4Args) = nullptr;
+  const bool is_int = fmt == W4_INT, bf = act_dtype == MSGL_BF16;
+#define MSGL_W4_PICK(MT_)                                                                                   \
+  (is_int ? (bf ? gemm_w4a16_kernel<MT_, true, true> : gemm_w4a16_kernel<MT_, true, false>)                 \
+          : (bf ? gemm_w4a16_kernel<MT_, false, true> : gemm_w4a16_kernel<MT_, false, false>))
+  kernel = pair ? MSGL_W4_PICK(2) : MSGL_W4_PICK(1);
+#undef MSGL_W4_PICK
+  cudaError_t e = msgl_launch(kernel, dim3(grid), dim3(kThreads), pair ? smem2 : smem1, stream, ma, mw, args);
   if (e != cudaSuccess) { msgl_set_error("gemm_w4a16 launch", e); return MSGL_CUDA_ERROR; }
   return MSGL_OK;
 }

@@ -142,6 +142,10 @@ ENV.int("EP_REGION_GIB", 6, "per-rank budget of the expert-parallel exchange reg
 ENV.str("NVLS", "auto", "decode all-reduce by in-switch reduction (multimem): auto = on 4 or more ranks, on, off")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger ones go to the row-sharded GEMM fusion or to NCCL")
+ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-loop detector looks for; 0 = off")
+ENV.int("THINK_LOOP_SPAN", 48, "a reasoning loop is reported once this many consecutive tokens repeat")
+ENV.int("THINK_LOOP_REPS", 3, "... and the block has repeated this many times")
+ENV.int("TOOLCALL_RUNAWAY_LIMIT", 8192, "tokens one open tool call may run for before the request is ended; 0 = off")
 ENV.int("COMM_HEALTH_STEPS", 8, "the tensor-parallel ranks agree on the collectives' status word every this many steps")
 ENV.int("COMM_WAIT_US", 500_000, "bound of every device-side flag wait, in microseconds")
 # --- speculative decode -------------------------------------------------------------------

@@ -239,7 +239,8 @@ class MxFp4Method(LinearMethod):
 
 def _w4_native_ok(n: int, k: int, group: int, device) -> bool:
     """Shapes the 4-bit-resident GEMM takes (``csrc/gemm_w4a16.cu``); anything else is expanded."""
-    return torch.device(device).type == "cuda" and n % 8 == 0 and k % 64 == 0 and group >= 16 and group % 8 == 0
+    return torch.device(device).type == "cuda" and n % 8 == 0 and k % 64 == 0 and \
+        (group == 16 or (group >= 32 and group % 32 == 0)) and k % group == 0
 
 
 class NvFp4Method(LinearMethod):

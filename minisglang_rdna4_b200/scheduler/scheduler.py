@@ -278,13 +278,22 @@ class Scheduler:
         enc = lambda text: list(st["tok"].encode(text))
         think = st["think"].get(req.uid)
         if think is None and sp.think_close_delim is not None:
+            # a direct answer (the model's own answer-turn header) and a closer that names a recipient
+            # in its middle (prefix .. up to 16 arbitrary tokens .. suffix) release the gate as well
+            answers = [enc(sp.think_answer_delim)] if sp.think_answer_delim else []
+            wild = []
+            if sp.think_close_prefix and sp.think_close_suffix:
+                wild.append((tuple(enc(sp.think_close_prefix)), tuple(enc(sp.think_close_suffix)), 16))
             think = st["think"][req.uid] = ThinkGate(
                 enc(sp.think_close_delim), [enc(t) for t in sp.think_tool_release], sp.think_budget,
-                span_open=sp.think_span_open or sp.think_budget > 0)
+                span_open=sp.think_span_open or sp.think_budget > 0, answer_patterns=answers, close_wildcards=wild,
+                loop_period=ENV.THINK_LOOP_PERIOD.value, loop_span=ENV.THINK_LOOP_SPAN.value,
+                loop_reps=ENV.THINK_LOOP_REPS.value)
         tool = st["tool"].get(req.uid)
         if tool is None and sp.tool_call_openers and sp.tool_call_closers:
             tool = st["tool"][req.uid] = ToolCallGate([enc(t) for t in sp.tool_call_openers],
-                                                      [enc(t) for t in sp.tool_call_closers])
+                                                      [enc(t) for t in sp.tool_call_closers],
+                                                      limit=ENV.TOOLCALL_RUNAWAY_LIMIT.value)
         return think, tool
 
     def _attach_constraints(self, reqs: Sequence[Req], args: BatchSamplingArgs) -> None:
@@ -330,10 +339,25 @@ class Scheduler:
         active = think is None or think.grammar_active
         if think is not None:
             think.observe(tok)
+            period = think.take_loop_report()
+            if period:
+                logger.warning("request %d repeats a block of %d token(s) inside its reasoning span: closing the span",
+                               req.uid, period)
         if tool is not None:
             tool.observe(tok)
         if req.sampling_params.grammar is not None and active:
             st["grammar"].accept(req.uid, tok)
+
+    def _tool_call_runaway(self, req: Req) -> bool:
+        """A tool call that has run past ``MSGL_TOOLCALL_RUNAWAY_LIMIT`` tokens without closing ends
+        the request (python/minisgl/scheduler/think_gate.py:123-230: EOS is masked inside a call, so
+        a degenerate model would otherwise run to the token cap)."""
+        st = getattr(self, "_cstate", None)
+        tool = st["tool"].get(req.uid) if st is not None else None
+        if tool is not None and tool.runaway:
+            logger.warning("request %d: tool call still open after %d tokens, ending the request", req.uid, tool.inside)
+            return True
+        return False
 
     def _forget_constraints(self, uid: int) -> None:
         st = getattr(self, "_cstate", None)
@@ -365,6 +389,8 @@ class Scheduler:
             if not req.sampling_params.ignore_eos and tok in self.eos_ids:
                 reason = "stop"
             elif req.num_generated >= req.sampling_params.max_tokens:
+                reason = "length"
+            elif self._tool_call_runaway(req):
                 reason = "length"
             msg = DetokenizeMsg(req.uid, tok, reason is not None, reason,
                                 prompt_tokens=req.prompt_len, cached_tokens=self.prefix_len.get(req.uid, 0))

@@ -27,7 +27,8 @@ from ..message import AbortMsg, StatsMsg, TokenizeMsg, UserReply
 from ..utils import init_logger
 from .metrics import FrontendMetrics
 from .reasoning import ReasoningParser, ReasoningStreamState, resolve_reasoning_parser
-from .tools import ToolCallStreamState, grammar_from_tools, parse_tool_calls, tool_openers_closers
+from .tools import (ToolCallStreamState, grammar_from_tools, parse_tool_calls, resolve_tool_format,
+                    structural_tag_for_tools, tool_openers_closers)
 
 logger = init_logger(__name__)
 
@@ -242,11 +243,14 @@ def sampling_from_request(req: OpenAICompletionRequest, reasoning: Optional[Reas
             raise ValueError(f"unsupported response_format type {kind!r}")
     openers: List[str] = []
     closers: List[str] = []
-    if req.tools:
-        forced = grammar_from_tools(req.tools, req.tool_choice)
+    if req.tools and req.tool_choice != "none":
+        fmt = resolve_tool_format(None, chat_template)
+        forced = grammar_from_tools(req.tools, req.tool_choice, fmt)
         if forced is not None and grammar is None:
             grammar, required = forced, True
-        openers, closers = tool_openers_closers(chat_template)
+        elif grammar is None and os.environ.get("MSGL_TOOL_AUTO_CONSTRAIN", "0") == "1":
+            grammar = structural_tag_for_tools(req.tools, fmt)     # free text, schema-checked call bodies
+        openers, closers = tool_openers_closers(chat_template, fmt)
     thinking = req.enable_thinking
     if thinking is None and req.chat_template_kwargs:
         thinking = req.chat_template_kwargs.get("enable_thinking")
@@ -262,7 +266,9 @@ def sampling_from_request(req: OpenAICompletionRequest, reasoning: Optional[Reas
     )
     if reasoning is not None and thinking is not False:
         sp = replace(sp, think_close_delim=reasoning.close, think_span_open=reasoning.starts_open,
-                     think_budget=int(req.reasoning_max_tokens or 0), think_tool_release=list(openers))
+                     think_budget=int(req.reasoning_max_tokens or 0), think_tool_release=list(openers),
+                     think_answer_delim=reasoning.answer_delim, think_close_prefix=reasoning.close_prefix,
+                     think_close_suffix=reasoning.close_suffix)
     return sp
 
 
@@ -346,12 +352,16 @@ def cam_auto_write(memory, text: str, override: Optional[bool], namespace: str =
     return n
 
 
-def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat_template: Optional[str] = None
-               ) -> FastAPI:
+def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat_template: Optional[str] = None,
+               tokenizer=None) -> FastAPI:
     app = FastAPI(title="minisglang-rdna4 b200")
     state = manager or FrontendManager(args)
     app.state.manager = state
-    reasoning = resolve_reasoning_parser(args.reasoning_parser, chat_template)
+    reasoning = resolve_reasoning_parser(args.reasoning_parser, chat_template, tokenizer)
+    if reasoning is not None:
+        logger.info("reasoning delimiters %r .. %r (%s)", reasoning.open, reasoning.close, reasoning.how or "named")
+    if tokenizer is not None:
+        resolve_tool_format(tokenizer, chat_template)            # log the derived tool-call format once
     created = int(time.time())
 
     @app.on_event("startup")
@@ -437,7 +447,8 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
 
             async def gen():
                 rstate = ReasoningStreamState(reasoning, reasoning.starts_open) if use_reasoning else None
-                tstate = ToolCallStreamState() if want_tools else None
+                tstate = ToolCallStreamState(req.tools, resolve_tool_format(None, chat_template)) if want_tools else None
+                n_calls = 0
                 n_tok = prompt_tok = cached = 0
                 finish = None
                 if chat:
@@ -458,8 +469,9 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
                         if reply.finished:
                             r2, c2 = rstate.flush()
                             r_delta, c_delta = r_delta + r2, c_delta + c2
+                    call_deltas: List[Dict[str, Any]] = []
                     if tstate is not None:
-                        c_delta = tstate.feed(c_delta)
+                        c_delta, call_deltas = tstate.push(c_delta)
                     delta: Dict[str, Any] = {}
                     if r_delta:
                         delta["reasoning_content"] = r_delta
@@ -469,6 +481,10 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
                         delta_lp = {"content": reply.logprobs}
                     else:
                         delta_lp = None
+                    if call_deltas:
+                        # a call's name goes out as soon as it is complete, its arguments as they grow
+                        delta["tool_calls"] = call_deltas
+                        n_calls += sum(1 for c in call_deltas if "id" in c)
                     if delta:
                         choice = ({"index": 0, "delta": delta, "finish_reason": None} if chat
                                   else {"index": 0, "text": c_delta, "finish_reason": None})
@@ -480,15 +496,15 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
                         finish = reply.finish_reason or "stop"
                 calls: List[Dict[str, Any]] = []
                 if tstate is not None:
-                    rest, calls = tstate.finish()
+                    rest, calls = tstate.flush()
                     if rest:
                         yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model,
                                     "choices": [{"index": 0, "delta": {"content": rest}, "finish_reason": None}]})
-                    for i, call in enumerate(calls):
+                    if calls:
                         yield _sse({"id": rid, "object": obj + ".chunk", "created": created, "model": model,
-                                    "choices": [{"index": 0, "delta": {"tool_calls": [dict(call, index=i)]},
-                                                 "finish_reason": None}]})
-                if calls and finish in (None, "stop"):
+                                    "choices": [{"index": 0, "delta": {"tool_calls": calls}, "finish_reason": None}]})
+                    n_calls += sum(1 for c in calls if "id" in c)
+                if n_calls and finish in (None, "stop"):
                     finish = "tool_calls"
                 final = ({"index": 0, "delta": {}, "finish_reason": finish or "stop"} if chat
                          else {"index": 0, "text": "", "finish_reason": finish or "stop"})
@@ -531,7 +547,7 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
                 reasoning_text, text = reasoning.split(text)
             calls: List[Dict[str, Any]] = []
             if want_tools:
-                text, calls = parse_tool_calls(text)
+                text, calls = parse_tool_calls(text, req.tools, resolve_tool_format(None, chat_template))
             message: Dict[str, Any] = {"role": "assistant", "content": text if (text or not calls) else None}
             if reasoning_text:
                 message["reasoning_content"] = reasoning_text
@@ -671,15 +687,18 @@ def run_api_server(args: ServerArgs, start_backend=None) -> None:
         args, send_queue=ZmqAsyncPushQueue(args.zmq_tokenizer_addr, create=False),
         recv_queue=ZmqAsyncPullQueue(args.zmq_frontend_addr, create=True))
     template = args.chat_template
+    tokenizer = None
+    try:
+        tokenizer = load_tokenizer(args.model_path)
+    except Exception:
+        tokenizer = None
     if template is None:
-        try:
-            template = getattr(load_tokenizer(args.model_path), "chat_template", None)
-        except Exception:
-            template = None
+        template = getattr(tokenizer, "chat_template", None)
     defaults = set_sampling_defaults(args.model_path)
     if defaults:
         logger.info("sampling defaults from generation_config.json: %s", defaults)
     if start_backend is not None:
         start_backend()
-    app = create_app(args, manager, template if isinstance(template, str) else None)
+    app = create_app(args, manager, template if isinstance(template, str) else None,
+                     tokenizer if hasattr(tokenizer, "apply_chat_template") else None)
     uvicorn.run(app, host=args.host, port=args.port, log_level="warning")

@@ -56,6 +56,69 @@ def test_think_gate_budget_and_release():
     assert ThinkGate(close_ids=[1], span_open=False).grammar_active
 
 
+def test_think_gate_sequences_wildcards_and_direct_answers():
+    # a self-overlapping close delimiter: a cursor that resets on divergence would miss (4, 4, 5) in 4 4 4 5
+    g = ThinkGate(close_ids=[4, 4, 5])
+    for t in (4, 4, 4):
+        g.observe(t)
+        assert not g.released
+    assert g.observe(5) and g.released
+    # delimiters that share their last token: the opener 328 19669 200023 must not release the gate
+    close = [200007, 200022, 140680, 328, 76976, 200023]
+    g = ThinkGate(close_ids=close, answer_patterns=[[328, 76976, 200023]])
+    assert g.commit_many([328, 19669, 200023, 11, 12]) is None and not g.released
+    assert g.commit_many(close) == len(close) - 1
+    # ... and answering directly (the answer-turn header without a reasoning turn) releases it as well
+    g = ThinkGate(close_ids=close, answer_patterns=[[328, 76976, 200023]])
+    assert g.commit_many([7, 328, 76976, 200023]) == 3
+    # wildcard closer: head, at most two arbitrary tokens (the recipient), tail
+    g = ThinkGate(close_ids=[1, 2, 3], close_wildcards=[((50, 51), (60,), 2)])
+    assert g.scan([9, 50, 51, 7, 8, 60]) == 5              # pure query: nothing advanced
+    assert not g.released and g.thought == 0
+    assert g.commit_many([9, 50, 51, 7, 8, 9, 60]) is None  # three tokens in between: no match
+    assert g.commit_many([50, 51, 60]) == 2
+    # what a speculative verify row k tokens ahead would be forced to
+    g = ThinkGate(close_ids=[5, 6], budget=3)
+    g.observe(1)
+    assert [g.forced_at(a) for a in range(5)] == [None, None, 5, 6, None]
+
+
+def test_think_gate_loop_detector_spends_the_budget():
+    g = ThinkGate(close_ids=[99], budget=10_000, loop_period=16, loop_span=24, loop_reps=3)
+    block = [11, 12, 13, 14, 15, 16]
+    n = 0
+    for t in [1, 2, 3] + block * 10:
+        if g.forced_token() is not None:
+            break
+        g.observe(t)
+        n += 1
+    assert g.loop == len(block) and g.take_loop_report() == len(block) and g.take_loop_report() == 0
+    assert n < 3 + len(block) * 6                      # caught within a few repeats, far below the budget
+    assert g.forced_token() == 99
+    g.observe(99)
+    assert g.released
+    # legitimate short repetition (a ruler, a short list) stays below the span floor
+    g = ThinkGate(close_ids=[99], budget=0, loop_period=16, loop_span=24, loop_reps=3)
+    for t in [7] * 20 + list(range(100, 140)) + [8, 9] * 8:
+        g.observe(t)
+    assert g.loop == 0 and g.forced_token() is None
+    # without a budget the detector still closes an endless loop
+    g = ThinkGate(close_ids=[99], budget=0, loop_period=16, loop_span=24, loop_reps=3)
+    for t in block * 8:
+        g.observe(t)
+    assert g.forced_token() == 99
+
+
+def test_tool_call_gate_runaway_limit():
+    g = ToolCallGate(openers=[[10]], closers=[[12]], limit=5)
+    g.observe(10)
+    for _ in range(4):
+        g.observe(3)
+    assert g.suppress_eos and not g.runaway
+    g.observe(3)
+    assert g.runaway and not g.suppress_eos
+
+
 def test_tool_call_gate_suppresses_eos_until_closed():
     g = ToolCallGate(openers=[[10, 11]], closers=[[12]])
     assert not g.suppress_eos

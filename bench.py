@@ -431,7 +431,12 @@ def main() -> None:
                 "global_batch": args.requests, "seq_len": f"in U[{args.in_min},{args.in_max}], out {args.out_len}",
                 "parallelism": (f"dp{world}+ep{world} (all-to-all over peer memory)" if dp_ep else f"tp{world}"),
                 "preset": args.config, "shared_prefix": args.shared_prefix,
-                "spec": ({"algorithm": args.spec, "draft": args.spec_draft, "tree_width": args.spec_tree_width,
+                "spec": ({"algorithm": args.spec, "draft": args.spec_draft, "tree_width_requested": args.spec_tree_width,
+                          "tree_width_verified": (getattr(llm._spec_runner, "T", 1)
+                                                  if getattr(llm, "_spec_runner", None) is not None
+                                                  else args.spec_tree_width),
+                          "verify_rows_per_request": (getattr(llm._spec_runner, "R", None)
+                                                      if getattr(llm, "_spec_runner", None) is not None else None),
                           "verify_steps": llm.stats.get("spec_steps", 0),
                           "verify_step_ms_p50": (sorted(s.elapsed_time(e) for s, e, ph, _ in step_events
                                                         if ph == "decode") or [None])[len([1 for x in step_events if x[2] == "decode"]) // 2],

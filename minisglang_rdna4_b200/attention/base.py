@@ -20,6 +20,7 @@ class AttnMetadata:
     decode: bool                # every request has exactly one query row
     causal: bool = True
     mask: Optional[torch.Tensor] = None   # additive [T, >= max_kv] bias for tree verification
+    mask_window: int = 0                  # > 0: mask rows [T, mask_window] cover the last mask_window KV positions only
     workspace: Optional[torch.Tensor] = None
     prefill_plan: Optional[object] = None  # ops.cuda.PrefillPlan of a prefill-phase step on a GPU
 

@@ -48,6 +48,56 @@ def timeit(fn, iters: int, warmup: int = 3, flush=None) -> float:
     return times[len(times) // 2]
 
 
+def _library_attention(a, q, pool, bt, cu, sl, ks, q_len, kv_len, kv_bytes, flops, hbm, tf, ours, flush) -> dict:
+    """The same attention problem through flashinfer: its paged wrappers (``flashinfer``) or the
+    TensorRT-LLM generation kernels it ships (``flashinfer-trtllm``). The library gets this GPU's own
+    tensors only. Reports the time, the same roofline fractions and the largest difference to our output;
+    an arm that cannot run here says why instead."""
+    res = {"lib": a.lib}
+    try:
+        import flashinfer
+
+        hq, hk, d, ps = a.heads, a.kv_heads, a.head_dim, a.page_size
+        b = sl.numel()
+        kc, vc = pool[0, 0], pool[1, 0]                      # [pages, hk, ps, d] = flashinfer's "HND" layout
+        ws = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+        scale = d ** -0.5
+        kscale = float(ks[0]) if ks is not None else 1.0
+        if a.lib == "flashinfer-trtllm":
+            if q_len == 1:
+                run = lambda: flashinfer.decode.trtllm_batch_decode_with_kv_cache(
+                    q, (kc, vc), ws, bt, sl, kv_len, bmm1_scale=scale * kscale, bmm2_scale=kscale, kv_layout="HND")
+            else:
+                cu_kv = torch.zeros(b + 1, dtype=torch.int32, device="cuda")
+                cu_kv[1:] = sl.cumsum(0)
+                run = lambda: flashinfer.prefill.trtllm_batch_context_with_kv_cache(
+                    q, (kc, vc), ws, bt, sl, q_len, kv_len, scale * kscale, kscale, b, cu, cu_kv, kv_layout="HND")
+        else:
+            pages = (sl + ps - 1) // ps
+            indptr = torch.zeros(b + 1, dtype=torch.int32, device="cuda")
+            indptr[1:] = pages.cumsum(0)
+            indices = torch.cat([bt[i, :int(pages[i])] for i in range(b)]).to(torch.int32)
+            last = ((sl - 1) % ps + 1).to(torch.int32)
+            if q_len == 1:
+                w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "HND", use_tensor_cores=True)
+                w.plan(indptr, indices, last, hq, hk, d, ps, q_data_type=q.dtype, kv_data_type=kc.dtype, sm_scale=scale)
+            else:
+                w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws, "HND")
+                w.plan(cu, indptr, indices, last, hq, hk, d, ps, causal=True, q_data_type=q.dtype,
+                       kv_data_type=kc.dtype, sm_scale=scale)
+            kw = dict(k_scale=kscale, v_scale=kscale) if ks is not None else {}
+            run = lambda: w.run(q, (kc, vc), **kw)
+        got = run()
+        torch.cuda.synchronize()
+        ms = timeit(run, a.iters, a.warmup, flush)
+        res.update(us=ms * 1e3, kv_gbs=kv_bytes / ms / 1e6, tflops=flops / ms / 1e9, frac_of_hbm=kv_bytes / ms / 1e6 / hbm,
+                   frac_of_bf16_peak=flops / ms / 1e9 / tf,
+                   max_abs_diff_to_ours=float((got.float().view(-1) - ours.float().view(-1)).abs().max()))
+    except Exception as exc:                                   # missing cubins, no JIT toolchain, unsupported shape
+        res["unavailable"] = f"{type(exc).__name__}: {str(exc)[:300]}"
+    return res
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["gemm", "attn_decode", "attn_prefill", "rms_norm", "silu_quant", "rope_store", "moe"])
@@ -70,6 +120,9 @@ def main(argv=None) -> None:
     ap.add_argument("--stages", type=int, default=0, help="attn_decode with fp8 KV: stages of the TMA ring (2-4)")
     ap.add_argument("--general", action="store_true", help="attn_prefill: the warp-level MMA kernel instead of the tcgen05 one")
     ap.add_argument("--kv", default="fp8", choices=["fp8", "bf16"])
+    ap.add_argument("--lib", default="", choices=["", "flashinfer", "flashinfer-trtllm"],
+                    help="attn_decode / attn_prefill: also time the library kernel on the same inputs (the reference's "
+                         "attention backends on this GPU: python/minisgl/attention/fi.py, trtllm.py:53-90)")
     ap.add_argument("--experts", type=int, default=128)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
@@ -164,6 +217,9 @@ def main(argv=None) -> None:
                    kv_gbs=kv_bytes / ms / 1e6, tflops=flops / ms / 1e9, frac_of_hbm=kv_bytes / ms / 1e6 / hbm,
                    frac_of_bf16_peak=flops / ms / 1e9 / tf)
         assert K.attn_status() == 0
+        if a.lib:
+            out["library"] = _library_attention(a, q, pool, bt, cu, sl, ks, q_len, kv_len, kv_bytes, flops, hbm, tf,
+                                                fn(), flush)
     elif a.op == "rms_norm":
         x = torch.randn(a.m, a.k, device="cuda").bfloat16()
         r = torch.randn(a.m, a.k, device="cuda").bfloat16()

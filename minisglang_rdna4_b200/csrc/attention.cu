@@ -41,6 +41,7 @@ struct AttnArgs {
   const float* v_scale;
   const float* mask;
   long long mask_stride;
+  int mask_window;   // > 0: a mask row covers only the last mask_window KV positions of its request; the rest is visible
   float* ws_o;
   float* ws_lse;
   int B, Hq, Hk, page_size, num_pages;
@@ -244,6 +245,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
   }
   if (!ok_a) hi_a = 0;
   if (!ok_b) hi_b = 0;
+  const int mask_lo = args.mask_window > 0 ? kv_len - args.mask_window : 0;   // negative for a sequence shorter than the window
   const float* mask_a = use_mask ? args.mask + (size_t)(q_begin + (ok_a ? qi_a : q_start)) * args.mask_stride : nullptr;
   const float* mask_b = use_mask ? args.mask + (size_t)(q_begin + (ok_b ? qi_b : q_start)) * args.mask_stride : nullptr;
 
@@ -301,8 +303,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArg
         const int tok = tok0 + nb * 8 + 2 * j + e;
         float va = s[nb][e] * sm_scale, vb = s[nb][2 + e] * sm_scale;
         if (use_mask) {
-          va = (tok < hi_a) ? va + mask_a[tok] * kLog2e : -INFINITY;
-          vb = (tok < hi_b) ? vb + mask_b[tok] * kLog2e : -INFINITY;
+          const int mt = tok - mask_lo;   // negative: ahead of the masked window, visible to every row
+          va = (tok < hi_a) ? (mt >= 0 ? va + mask_a[mt] * kLog2e : va) : -INFINITY;
+          vb = (tok < hi_b) ? (mt >= 0 ? vb + mask_b[mt] * kLog2e : vb) : -INFINITY;
         } else {
           if (tok >= hi_a || tok < lo_a) va = -INFINITY;
           if (tok >= hi_b || tok < lo_b) vb = -INFINITY;
@@ -963,7 +966,10 @@ MSGL_API int msgl_paged_attention(const void* kv_map, const void* q, void* out, 
   a.block_table = (const int32_t*)block_table; a.bt_stride = bt_stride;
   a.cu_q = (const int32_t*)cu_q; a.seq_lens = (const int32_t*)seq_lens;
   a.k_scale = (const float*)k_scale; a.v_scale = (const float*)v_scale;
-  a.mask = (const float*)mask; a.mask_stride = mask_stride;
+  // a negative stride selects the windowed form: rows of -mask_stride floats for the last -mask_stride KV positions
+  a.mask = (const float*)mask;
+  a.mask_window = mask_stride < 0 ? (int)(-mask_stride) : 0;
+  a.mask_stride = mask_stride < 0 ? -mask_stride : mask_stride;
   a.ws_o = (float*)workspace;
   a.ws_lse = a.ws_o != nullptr ? a.ws_o + (size_t)splits * total_q * hq * head_dim : nullptr;
   a.B = B; a.Hq = hq; a.Hk = hk; a.page_size = page_size; a.num_pages = num_pages;

@@ -29,6 +29,8 @@
 using namespace msgl;
 using namespace msgl::ptx;
 
+int msgl_b_static_level();   // gemm_tcgen05.cu: level set by msgl_gemm_static_weights
+
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 128;
@@ -51,6 +53,7 @@ struct BlockArgs {
   long long ldc;
   int out_dtype;
   const int32_t* tile_expert;  // grouped: expert of M tile m (negative: tile past the live rows)
+  int l2_ahead;                // request a work item's weight stream into L2 one item ahead
   int* status;
 };
 
@@ -102,8 +105,20 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      // A weight tile that only one or two row tiles use (grouped experts, decode-sized dense calls) is
+      // streamed once: its whole K range is requested into L2 one work item ahead, so the ring in
+      // shared memory covers L2 latency instead of HBM latency.
+      const bool l2_ahead = args.l2_ahead && (args.tile_expert != nullptr || args.m_tiles <= 2);
+      auto prefetch_item = [&](int tile) {
+        const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+        const int expert = args.tile_expert != nullptr ? args.tile_expert[m_tile] : 0;
+        if (expert < 0) return;
+        for (int kb = 0; kb < args.k_blocks; ++kb) tma_prefetch_2d(&tma_b, kb * BK, expert * args.N + n_tile * BN);
+      };
+      if (l2_ahead && (int)blockIdx.x < total_tiles) prefetch_item(blockIdx.x);
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
+        if (l2_ahead && tile + (int)gridDim.x < total_tiles) prefetch_item(tile + gridDim.x);
         int expert = 0;
         if (args.tile_expert != nullptr) {
           expert = args.tile_expert[m_tile];
@@ -345,6 +360,7 @@ MSGL_API int msgl_gemm_fp8_block(const void* a, long long lda, const void* b, vo
   args.ldc = ldc;
   args.out_dtype = out_dtype;
   args.tile_expert = (const int32_t*)tile_expert;
+  args.l2_ahead = msgl_b_static_level() >= 2 ? 1 : 0;
   int* status = nullptr;
   cudaGetSymbolAddress((void**)&status, g_block_status);
   args.status = status;

@@ -226,6 +226,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       int pre = 0;  // leading stages of the first work item whose weight tile is already in flight
+      const bool l2_ahead = args.b_static >= 2 && args.tile_expert == nullptr && args.m_tiles <= 2;
+      // grouped (expert) calls: every weight tile serves the rows of one expert only; same treatment,
+      // one work item ahead, once the expert table may be read
+      const bool l2_grouped = args.b_static >= 2 && args.tile_expert != nullptr;
+      auto prefetch_weights = [&](int item, int skip) {
+        const int tile = item / splits, split = item - tile * splits;
+        const int n0 = (tile / args.m_tiles) * BN;
+        int expert = 0;
+        if (args.tile_expert != nullptr) {
+          expert = args.tile_expert[tile % args.m_tiles];
+          if (expert < 0) return;
+        }
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        for (int kb = kb0 + skip; kb < kb1; ++kb) tma_prefetch_2d(&tma_b, kb * KT::BKE, expert * args.N + n0);
+        if (KIND == KIND_MXF4 && kb1 > kb0 + skip)
+          bulk_prefetch_l2(args.sfb + ((size_t)(expert * args.sf_n_atoms + n0 / 128) * args.sf_k_atoms + kb0 + skip) * 512,
+                           (uint32_t)(kb1 - kb0 - skip) * 512u);
+      };
       if (args.b_static && args.tile_expert == nullptr && (int)blockIdx.x < total_tiles) {
         const int tile = (int)blockIdx.x / splits, split = (int)blockIdx.x - tile * splits;
         const int n0 = (tile / args.m_tiles) * BN;
@@ -241,12 +260,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             bulk_load(s_base + L::off_sf + s * L::SF_BYTES, src, 512, full_bar(s));
           }
         }
+        // decode-sized calls: the rest of this item's weight stream is requested into L2 now, so the
+        // ring only has to cover L2 latency once the kernels ahead have finished
+        if (l2_ahead) prefetch_weights(blockIdx.x, pre);
       }
       pdl_enter();
+      if (l2_grouped && (int)blockIdx.x < total_tiles) prefetch_weights(blockIdx.x, 0);
       for (int item = blockIdx.x; item < total_tiles && !*abort_flag; item += gridDim.x) {
         const int tile = item / splits, split = item - tile * splits;
         const int m_tile = tile % args.m_tiles, n_tile = tile / args.m_tiles;
         const int n0 = n_tile * BN;
+        if ((l2_ahead || l2_grouped) && item + (int)gridDim.x < total_tiles) prefetch_weights(item + gridDim.x, 0);
         int expert = 0;
         if (args.tile_expert != nullptr) {
           expert = args.tile_expert[m_tile];
@@ -1342,9 +1366,11 @@ MSGL_API int msgl_gemm_grouped_w8a8(const void* a, long long lda, const void* b,
 // were written before any kernel that can still be in flight on the calling stream (model
 // parameters), so a kernel may fetch them before it has waited for the kernels ahead of it;
 // 0 (default) = no promise, B is only read after that wait. Returns the previous setting.
+int msgl_b_static_level() { return g_b_static; }   // for the other GEMM translation units
+
 MSGL_API int msgl_gemm_static_weights(int on) {
   const int prev = g_b_static;
-  g_b_static = on ? 1 : 0;
+  g_b_static = on < 0 ? 0 : (on > 2 ? 2 : on);   // 2: also request the rest of a decode-sized item's weights into L2
   return prev;
 }
 

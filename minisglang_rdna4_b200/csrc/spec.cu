@@ -56,6 +56,79 @@ __global__ void spec_accept_kernel(AcceptArgs a) {
   a.sel_row[b] = b * W + n - 1;
 }
 
+// Acceptance over a draft tree with a fixed shape: a best chain of K nodes (verify rows 1 .. K, K/V
+// already at their sequence positions) and W - 1 sibling candidates per depth (rows K + 1 ..., K/V at
+// scratch slots behind the chain). The target's prediction is followed from the root: at depth d
+// it either equals the chain's draft (continue), equals a sibling (accept it, emit that sibling
+// row's own prediction as the bonus token, stop: siblings have no children), or neither (stop).
+struct TreeArgs {
+  const int32_t* target;     // [B * R] arg-max ids of the verify rows, R = 1 + K * W
+  int32_t* token_pool;
+  const int32_t* first_idx;  // [B] flat pool index of position c + 1 (the chain drafts sit there)
+  const int32_t* num_draft;  // [B] depth offered, 0 .. K
+  const int32_t* max_emit;
+  const int32_t* flags;
+  const int32_t* sib_tok;    // [K][sib_stride][W - 1] sibling candidates (target vocabulary)
+  const int32_t* out_loc;    // [B * R] K/V token slot of every verify row
+  int32_t* record;           // [B * (K + 3)]: n, hit_eos, emitted[K + 1]
+  int32_t* sel_row;          // [B] row of the draft-update batch that holds the next chain state
+  int32_t* feat_row;         // [B * (K + 1)] verify row whose features feed update row j
+  int32_t* moves;            // [B * 2] (src slot, dst slot) of an accepted sibling's K/V, or -1
+  int32_t eos[kMaxEos];
+  int n_eos;
+  int B, K, W, sib_stride;
+};
+
+__global__ void spec_accept_tree_kernel(TreeArgs a) {
+  pdl_enter();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= a.B) return;
+  const int K = a.K, W = a.W, R = 1 + K * W;
+  const int32_t* tgt = a.target + (size_t)b * R;
+  int32_t* pool = a.token_pool + a.first_idx[b];
+  const int k = min(max(a.num_draft[b], 0), K);
+  const int limit = max(a.max_emit[b], 1);
+  const bool stop_at_eos = !(a.flags[b] & 1);
+  int32_t* rec = a.record + (size_t)b * (K + 3);
+  int32_t* frow = a.feat_row + (size_t)b * (K + 1);
+  for (int j = 0; j <= K; ++j) frow[j] = b * R + j;
+  int n = 0, hit = 0, cur = 0, mv_src = -1, mv_dst = -1;
+  auto is_eos = [&](int t) {
+    for (int e = 0; e < a.n_eos; ++e)
+      if (t == a.eos[e]) return true;
+    return false;
+  };
+  for (int d = 1; d <= K + 1; ++d) {
+    const int p = tgt[cur];                       // the token at position c + d
+    rec[2 + n] = p;
+    ++n;
+    if (stop_at_eos && is_eos(p)) { hit = 1; break; }
+    if (n >= limit || d > k) break;
+    if (pool[d - 1] == p) { cur = d; continue; }  // the chain's draft stands
+    int found = -1;
+    const int32_t* sib = a.sib_tok + ((size_t)(d - 1) * a.sib_stride + b) * (W - 1);
+    for (int s = 0; s < W - 1; ++s)
+      if (sib[s] == p) { found = s; break; }
+    if (found < 0) break;
+    const int row = K + (d - 1) * (W - 1) + found + 1;
+    mv_src = a.out_loc[(size_t)b * R + row];
+    mv_dst = a.out_loc[(size_t)b * R + d];
+    frow[d] = b * R + row;
+    const int p2 = tgt[row];                      // bonus: the accepted sibling's own prediction
+    rec[2 + n] = p2;
+    ++n;
+    if (stop_at_eos && is_eos(p2)) hit = 1;
+    break;
+  }
+  rec[0] = n;
+  rec[1] = hit;
+  for (int j = n; j <= K; ++j) rec[2 + j] = -1;
+  for (int j = 0; j < n; ++j) pool[j] = rec[2 + j];   // commit: positions c + 1 .. c + n
+  a.sel_row[b] = b * (K + 1) + n - 1;
+  a.moves[2 * b] = mv_src;
+  a.moves[2 * b + 1] = mv_dst;
+}
+
 // token_pool[dst_idx[i]] = ids[i] + d2t[ids[i]]   (draft vocabulary -> target vocabulary)
 __global__ void spec_write_draft_kernel(const int32_t* __restrict__ ids, const int64_t* __restrict__ d2t,
                                         const int32_t* __restrict__ dst_idx, int32_t* __restrict__ token_pool,
@@ -113,6 +186,32 @@ MSGL_API int msgl_spec_accept(const void* target, void* token_pool, const void* 
   a.W = W;
   msgl_launch(spec_accept_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, a);
   MSGL_CHECK_LAUNCH("spec_accept");
+  return MSGL_OK;
+}
+
+MSGL_API int msgl_spec_accept_tree(const void* target, void* token_pool, const void* first_idx, const void* num_draft,
+                                   const void* max_emit, const void* flags, const void* sib_tok, const void* out_loc,
+                                   void* record, void* sel_row, void* feat_row, void* moves, const int* eos_ids,
+                                   int n_eos, int B, int K, int W, int sib_stride, cudaStream_t stream) {
+  if (B <= 0 || K < 1 || K > 16 || W < 2 || W > 16 || n_eos < 0 || n_eos > kMaxEos || sib_stride < B) return MSGL_BAD_ARG;
+  TreeArgs a;
+  a.target = (const int32_t*)target;
+  a.token_pool = (int32_t*)token_pool;
+  a.first_idx = (const int32_t*)first_idx;
+  a.num_draft = (const int32_t*)num_draft;
+  a.max_emit = (const int32_t*)max_emit;
+  a.flags = (const int32_t*)flags;
+  a.sib_tok = (const int32_t*)sib_tok;
+  a.out_loc = (const int32_t*)out_loc;
+  a.record = (int32_t*)record;
+  a.sel_row = (int32_t*)sel_row;
+  a.feat_row = (int32_t*)feat_row;
+  a.moves = (int32_t*)moves;
+  for (int i = 0; i < kMaxEos; ++i) a.eos[i] = i < n_eos ? eos_ids[i] : -1;
+  a.n_eos = n_eos;
+  a.B = B; a.K = K; a.W = W; a.sib_stride = sib_stride;
+  msgl_launch(spec_accept_tree_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, a);
+  MSGL_CHECK_LAUNCH("spec_accept_tree");
   return MSGL_OK;
 }
 

@@ -283,7 +283,7 @@ class Engine:
             K.set_pdl(ENV.PDL.value)
             # model parameters never change while kernels run, unless experts are paged in from the
             # host tier: only then must a GEMM wait for the stream before it reads its weights
-            K.gemm_static_weights(ENV.PDL.value and not host_tier)
+            K.gemm_static_weights((2 if ENV.GEMM_L2_AHEAD.value else 1) if (ENV.PDL.value and not host_tier) else 0)
         if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and not self.kv_calibrating and (config.cuda_graph_max_bs or 0) >= 0
                 and not ep_replicas and not host_tier):
             from .graph import GraphRunner

@@ -110,14 +110,14 @@ def store_kv(k, v, k_cache, v_cache, out_loc, k_scale=None, v_scale=None):
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale: float, *, causal: bool = True,
                     window: int = 0, mask=None, k_scale=None, v_scale=None, max_q: int = 0,
-                    max_kv: int = 0, decode: bool = False, workspace=None, splits=None):
+                    max_kv: int = 0, decode: bool = False, workspace=None, splits=None, mask_window: int = 0):
     if q.is_cuda:
         return _cuda().paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale,
                                        causal=causal, window=window, mask=mask, k_scale=k_scale,
                                        v_scale=v_scale, max_q=max_q, max_kv=max_kv, decode=decode,
-                                       workspace=workspace, splits=splits)
+                                       workspace=workspace, splits=splits, mask_window=mask_window)
     return ref.paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, causal, window,
-                               mask, k_scale, v_scale)
+                               mask, k_scale, v_scale, mask_window)
 
 
 # ---------------------------------------------------------------------------- GEMMs

@@ -277,7 +277,7 @@ def choose_splits(batch, hk, max_kv, decode):
 
 def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, causal=True, window=0, mask=None,
                     k_scale=None, v_scale=None, max_q=0, max_kv=0, decode=False, workspace=None, splits=None,
-                    plan=None, tc=None):
+                    plan=None, tc=None, mask_window=0):
     """``plan`` (a ``PrefillPlan``) or ``tc=True`` sends a causal prefill / extend step to the
     tcgen05 kernel when it covers the shape (``tc=True`` without a plan builds the step tables from
     the device lengths, which synchronises). Without either the general kernel runs: decode and
@@ -306,11 +306,18 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, seq_lens, scale, *, 
             workspace = torch.empty(need, dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
     fp8 = k_cache.dtype == torch.float8_e4m3fn
+    mask_stride = 0
     if mask is not None:
         assert mask.dtype == torch.float32 and mask.stride(-1) == 1
+        mask_stride = mask.stride(0)
+        if mask_window:
+            # windowed form: rows of exactly ``mask_window`` floats for the last ``mask_window`` KV
+            # positions of each request (earlier positions are visible); passed as a negative stride
+            assert mask.stride(0) == mask_window and mask.shape[-1] == mask_window
+            mask_stride = -int(mask_window)
     check(lib().msgl_paged_attention(
         desc.ctypes.data, _p(q), _p(out), _p(block_table), block_table.stride(0), _p(cu_q), _p(seq_lens),
-        _p(k_scale), _p(v_scale), _p(mask), mask.stride(0) if mask is not None else 0, _p(workspace) if splits > 1 else None,
+        _p(k_scale), _p(v_scale), _p(mask), mask_stride, _p(workspace) if splits > 1 else None,
         b, t, max_q, hq, hk, d, ps, pages_p1 - 1, layer, layers, int(fp8), int(causal), int(window), splits,
         float(scale), _dt(q), _stream()), "paged_attention")
     _count("paged_attention", "paged_attention_kernel", 2 if splits > 1 else 1)
@@ -689,7 +696,7 @@ def gemm_w4a16(x, w_packed, scales_t, zeros_t=None, channel=None, group=128, nvf
             out = _gemm(KIND_BF16 if x.dtype == torch.bfloat16 else KIND_F16, x2, scratch[: n * k].view(n, k), n, k,
                         out_dtype, bias=bias)
         finally:
-            gemm_static_weights(bool(prev))
+            gemm_static_weights(prev)
         return out.view(*shape[:-1], n) if out is not None else None
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     check(lib().msgl_gemm_w4a16(_p(x2), x2.stride(0), _p(w_packed), _p(scales_t), _p(zeros_t), _p(channel), _p(bias),
@@ -717,10 +724,11 @@ def gemm_pair_mode(mode: int) -> int:
     return int(lib().msgl_gemm_pair_mode(int(mode)))
 
 
-def gemm_static_weights(on: bool) -> int:
+def gemm_static_weights(on) -> int:
     """Promise that the weight operands of all GEMM calls from now on are model parameters
     (written long before the kernels in flight): the decode GEMMs then fetch their first weight
-    tiles while the kernel ahead of them is still running. Returns the previous setting."""
+    tiles while the kernel ahead of them is still running (1), and also request the rest of their
+    first work item's weight stream into L2 (2). Returns the previous setting."""
     return int(lib().msgl_gemm_static_weights(int(on)))
 
 

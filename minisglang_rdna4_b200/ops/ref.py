@@ -192,7 +192,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     block_table: torch.Tensor, cu_q: torch.Tensor, seq_lens: torch.Tensor,
                     scale: float, causal: bool = True, window: int = 0,
                     mask: Optional[torch.Tensor] = None, k_scale: Optional[torch.Tensor] = None,
-                    v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    v_scale: Optional[torch.Tensor] = None, mask_window: int = 0) -> torch.Tensor:
     """Attention of packed queries over paged KV.
 
     ``q`` ``[T, Hq, D]``; request ``b`` owns rows ``cu_q[b]:cu_q[b+1]`` which are the LAST
@@ -200,6 +200,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     ``block_table[b]``. ``causal``: row at absolute position p sees kv positions <= p.
     ``window`` > 0 additionally hides positions <= p - window. ``mask`` is an additive
     ``[T, >=max_kv]`` float bias (tree verification); when given it replaces the causal rule.
+    With ``mask_window`` > 0 the mask is ``[T, mask_window]`` and covers only the last
+    ``mask_window`` KV positions of each request; earlier positions are visible to every row.
     """
     t, hq, d = q.shape
     hk, ps = k_cache.shape[1], k_cache.shape[2]
@@ -224,7 +226,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         s = torch.einsum("hgqd,hkd->hgqk", qq, kk) * scale
         q_pos = torch.arange(kv_len - q_len, kv_len, device=q.device)[:, None]
         k_pos = torch.arange(kv_len, device=q.device)[None, :]
-        if mask is not None:
+        if mask is not None and mask_window:
+            w = min(mask_window, kv_len)
+            full = torch.zeros(q_len, kv_len, dtype=torch.float32, device=q.device)
+            full[:, kv_len - w:] = mask[qs:qe, mask_window - w:mask_window].float()
+            s = s + full[None, None]
+        elif mask is not None:
             s = s + mask[qs:qe, :kv_len].float()[None, None]
         else:
             if causal:

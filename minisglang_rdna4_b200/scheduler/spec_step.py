@@ -86,14 +86,16 @@ def device_runner(sched):
         return runner
     runner = None
     eng, proposer = sched.engine, sched.proposer
-    if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and getattr(proposer, "tree_width", 1) <= 1
+    draft = getattr(proposer, "draft", None)
+    tree_width = getattr(proposer, "tree_width", 1)
+    # a tree on the device needs the draft head's ranked candidates; n-gram trees stay on the host-driven step
+    if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and (tree_width <= 1 or draft is not None)
             and proposer.num_draft >= 1):
         from ..spec.device import DeviceSpecRunner
 
-        draft = getattr(proposer, "draft", None)
         with _engine_stream(eng):
             runner = DeviceSpecRunner(eng, proposer.num_draft, draft, getattr(proposer, "capture_layers", None),
-                                      max_batch=ENV.SPEC_MAX_BS.value or proposer.max_batch)
+                                      max_batch=ENV.SPEC_MAX_BS.value or proposer.max_batch, tree_width=tree_width)
             runner.capture()
     sched._spec_runner = runner
     return runner
@@ -114,6 +116,14 @@ def _device_spec_step(sched, proposer, runner, reqs: List[Req]) -> None:
         k = min(len(drafts[i]), budget) if host_drafts else budget
         c = r.cached_len
         end = r.device_len + k                      # positions c .. c + k get target K/V
+        if runner.T > 1 and k > 0:
+            # a tree also parks its siblings' K/V behind the chain; without room for them the request
+            # takes a plain step (depth 0)
+            if r.device_len + runner.K * runner.T <= sched.max_seq_len and k == runner.K:
+                end = r.device_len + runner.K * runner.T
+            else:
+                k = 0
+                end = r.device_len
         have = sched.alloc_len.get(r.uid, r.cache_handle.cached_len)
         if end > have:
             first, last = cdiv(have, ps), cdiv(end, ps)
@@ -128,7 +138,7 @@ def _device_spec_step(sched, proposer, runner, reqs: List[Req]) -> None:
     record = runner.run(rows, staged)
     sched.stats["steps"] += 1
     sched.stats["spec_steps"] += 1
-    sched.stats["decode_tokens"] += len(reqs) * runner.W
+    sched.stats["decode_tokens"] += len(reqs) * runner.R
     replies: List[DetokenizeMsg] = []
     for i, r in enumerate(reqs):
         n, hit_eos = int(record[i, 0]), bool(record[i, 1])

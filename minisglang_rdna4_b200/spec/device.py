@@ -31,6 +31,18 @@ Order inside the step for a request whose committed tokens end at position c:
 4. draft update: the draft layer runs all W rows (feature of position ``c + j``, token at ``c + j + 1``),
    which rewrites the draft K/V of positions ``c .. c + K`` (the ones past ``c + n - 1`` are rewritten by
    later steps before anything reads them); the output of row ``sel_row`` becomes ``hidden[slot]``.
+
+Tree verification (``tree_width`` T > 1, draft head only; python/minisgl/engine/graph.py:950,
+python/minisgl/spec/ddtree.py): the tree has a fixed shape, so it is captured like the chain. At
+every depth the head's best token continues the chain and its next T - 1 candidates become
+siblings without children. A request then feeds ``R = 1 + K * T`` verify rows: the root, the chain
+(rows 1 .. K, K/V at their sequence positions, exactly as in the chain step), then the siblings,
+whose K/V go to scratch slots ``c + K + 1 ..`` of the same request. Rows see the committed prefix,
+the root and their ancestors through a constant ``[R, R]`` additive mask over the last R K/V
+positions. ``spec_accept_tree_kernel`` follows the target's prediction down the tree; when a sibling
+is accepted its K/V is moved to its sequence position in every layer (``spec_kv_compact_kernel``)
+and its features replace the chain row's in the draft update. The draft chain costs the same K
+layer runs as without a tree; the price of the tree is the wider verify forward.
 """
 from __future__ import annotations
 
@@ -57,6 +69,7 @@ def _bind():
     bind("msgl_spec_accept", c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p])
     bind("msgl_spec_write_draft", c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_p])
     bind("msgl_spec_kv_compact", c_i, [c_p, c_p, c_i, c_ll, c_i, c_i, c_i, c_i, c_p])
+    bind("msgl_spec_accept_tree", c_i, [c_p] * 12 + [c_p, c_i, c_i, c_i, c_i, c_i, c_p])
 
 
 class BatchedDraft:
@@ -91,6 +104,11 @@ class BatchedDraft:
             L.post_attention_layernorm.forward(h))))
         return h + mlp
 
+    def head_topk(self, h, width: int) -> torch.Tensor:
+        """The ``width`` highest-scoring draft-vocabulary ids per row, best first, int32 ``[rows, width]``."""
+        logits = ops.gemm(self.m.norm.forward(h), self.m.lm_head.weight, None, torch.float32)
+        return torch.topk(logits, width, dim=-1).indices.to(torch.int32)
+
     def head_ids(self, h) -> torch.Tensor:
         """Arg-max of the draft head (reduced vocabulary), int32."""
         logits = ops.gemm(self.m.norm.forward(h), self.m.lm_head.weight, None, torch.float32)
@@ -102,11 +120,14 @@ class BatchedDraft:
 
 class DeviceSpecRunner:
     def __init__(self, engine, num_draft: int, draft=None, capture_layers: Optional[List[int]] = None,
-                 max_batch: int = 64) -> None:
+                 max_batch: int = 64, tree_width: int = 1) -> None:
         _bind()
         self.engine = engine
         self.K = int(num_draft)
         self.W = self.K + 1
+        # tree verification needs candidates per depth, which only the draft head provides
+        self.T = int(tree_width) if (draft is not None and tree_width > 1) else 1
+        self.R = 1 + self.K * self.T                      # verify rows per request (== W for a chain)
         self.draft = BatchedDraft(draft, engine) if draft is not None else None
         self.capture_layers = list(capture_layers) if capture_layers else None
         eng = engine
@@ -115,9 +136,10 @@ class DeviceSpecRunner:
         if self.max_bs not in self.buckets:
             self.buckets.append(self.max_bs)
         self.P = eng.max_pages_per_seq
-        B, W, K, P = self.max_bs, self.W, self.K, self.P
+        B, W, K, P, R = self.max_bs, self.W, self.K, self.P, self.R
         # one int32 arena: a single H2D copy fills every table of the step
-        fields = [("token_idx", B * W), ("positions", B * W), ("out_loc", B * W), ("seq_lens", B),
+        fields = [("token_idx", B * R), ("positions", B * R), ("out_loc", B * R), ("seq_lens", B),
+                  ("u_tok_idx", B * W), ("u_positions", B * W), ("u_out_loc", B * W), ("u_seq_lens", B),
                   ("block_table", B * P), ("first_idx", B), ("num_draft", B), ("max_emit", B), ("flags", B),
                   ("slots", B), ("stage_idx", B * K), ("stage_tok", B * K),
                   ("c_tok_idx", max(K - 1, 1) * B), ("c_dst_idx", K * B), ("c_positions", max(K - 1, 1) * B),
@@ -133,7 +155,24 @@ class DeviceSpecRunner:
         self._pinned = [torch.zeros(off, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._pin_events = [None, None]
         self._pin_pos = 0
-        self.cu_q_verify = (torch.arange(B + 1, dtype=torch.int32, device=dev) * W).contiguous()
+        self.cu_q_verify = (torch.arange(B + 1, dtype=torch.int32, device=dev) * R).contiguous()
+        self.cu_q_update = (torch.arange(B + 1, dtype=torch.int32, device=dev) * W).contiguous()
+        self.tree_mask = None
+        if self.T > 1:
+            T = self.T
+            vis = torch.full((R, R), float("-inf"))
+            vis[:, 0] = 0.0                                             # the root (last committed token)
+            for d in range(1, K + 1):
+                vis[d, 1:d + 1] = 0.0                                   # chain node: chain nodes 1 .. d
+                for sb in range(T - 1):
+                    row = K + (d - 1) * (T - 1) + sb + 1
+                    vis[row, 1:d] = 0.0                                 # sibling: the chain above it and itself
+                    vis[row, row] = 0.0
+            self.tree_mask = vis.repeat(B, 1).contiguous().to(dev)      # one [R, R] block per request
+            self.sib_tok = torch.zeros((K, B, T - 1), dtype=torch.int32, device=dev)
+            self.no_dst = torch.full((B * (T - 1),), -1, dtype=torch.int32, device=dev)
+            self.feat_row = torch.zeros(B * W, dtype=torch.int32, device=dev)
+            self.moves = torch.full((B * 2,), -1, dtype=torch.int32, device=dev)
         self.cu_q_decode = torch.arange(B + 1, dtype=torch.int32, device=dev)
         self.record = torch.zeros(B * (W + 2), dtype=torch.int32, device=dev)
         self.sel_row = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -160,7 +199,8 @@ class DeviceSpecRunner:
         from ..ops import cuda as Kc
         from ..ops._lib import check, lib
 
-        eng, W, K, P = self.engine, self.W, self.K, self.P
+        eng, W, K, P, R, T = self.engine, self.W, self.K, self.P, self.R, self.T
+        tree = T > 1
         L = lib()
         st = Kc._stream()
         pool_flat = eng.token_pool.view(-1)
@@ -175,9 +215,21 @@ class DeviceSpecRunner:
             # ---- propose: chain of K draft tokens from the per-slot hidden state
             h = d.hidden[slots]
             c_dst = self.view("c_dst_idx").view(K, -1)
-            ids = d.head_ids(h)
-            check(L.msgl_spec_write_draft(ids.data_ptr(), d.m.d2t.data_ptr(), c_dst[0, :bs].data_ptr(),
-                                          pool_flat.data_ptr(), None, bs, d.m._draft_vocab, st), "spec_write_draft")
+
+            def emit(h_rows, depth):
+                """Write the head's best token behind the chain (and its runners-up to the sibling table)."""
+                if tree:
+                    top = d.head_topk(h_rows, T)
+                    best, sib = top[:, 0].contiguous(), top[:, 1:].contiguous()
+                    check(L.msgl_spec_write_draft(sib.data_ptr(), d.m.d2t.data_ptr(), self.no_dst.data_ptr(),
+                                                  pool_flat.data_ptr(), self.sib_tok[depth].data_ptr(), bs * (T - 1),
+                                                  d.m._draft_vocab, st), "spec_write_draft")
+                else:
+                    best = d.head_ids(h_rows)
+                check(L.msgl_spec_write_draft(best.data_ptr(), d.m.d2t.data_ptr(), c_dst[depth, :bs].data_ptr(),
+                                              pool_flat.data_ptr(), None, bs, d.m._draft_vocab, st), "spec_write_draft")
+
+            emit(h, 0)
             if K > 1:
                 c_tok = self.view("c_tok_idx").view(K - 1, -1)
                 c_pos = self.view("c_positions").view(K - 1, -1)
@@ -187,21 +239,23 @@ class DeviceSpecRunner:
                     emb = d.embed.forward(pool_flat[c_tok[i - 1, :bs].long()])
                     h = d.layer(emb, h, c_pos[i - 1, :bs], c_loc[i - 1, :bs], bt, self.cu_q_decode[:bs + 1],
                                 c_len[i - 1, :bs], 1, msl)
-                    ids = d.head_ids(h)
-                    check(L.msgl_spec_write_draft(ids.data_ptr(), d.m.d2t.data_ptr(), c_dst[i, :bs].data_ptr(),
-                                                  pool_flat.data_ptr(), None, bs, d.m._draft_vocab, st),
-                          "spec_write_draft")
-        # ---- verify: W rows per request through the target
-        tok_idx = self._v("token_idx", bs * W)
+                    emit(h, i)
+        # ---- verify: R rows per request through the target
+        tok_idx = self._v("token_idx", bs * R)
         batch = Batch(reqs=[], phase="decode")
         batch.spec_verify = True
         batch.capture_layers = self.capture_layers
-        batch.positions = self._v("positions", bs * W)
-        batch.out_loc = self._v("out_loc", bs * W)
+        batch.positions = self._v("positions", bs * R)
+        batch.out_loc = self._v("out_loc", bs * R)
         batch.input_ids = pool_flat[tok_idx.long()]
+        if tree:
+            # sibling rows take their tokens from the sibling table ([K, B, T - 1] -> per request, depth-major)
+            batch.input_ids.view(bs, R)[:, W:] = self.sib_tok[:, :bs].permute(1, 0, 2).reshape(bs, K * (T - 1))
         seq_lens = self._v("seq_lens", bs)
         cu_q = self.cu_q_verify[:bs + 1]
-        eng.ctx.attn_backend.prepare_metadata(batch, bt, cu_q, seq_lens, W, msl, causal=True, mask=None)
+        eng.ctx.attn_backend.prepare_metadata(batch, bt, cu_q, seq_lens, R, msl, causal=True,
+                                              mask=self.tree_mask[:bs * R] if tree else None,
+                                              mask_window=R if tree else 0)
         prev = Kc.gemm_pair_mode(1)   # verify rows never leave the single-CTA GEMM (one code path for all steps)
         try:
             with eng.ctx.forward_batch(batch):
@@ -212,16 +266,39 @@ class DeviceSpecRunner:
         aux = eng.ctx.aux_hidden
         eng.ctx.aux_hidden = None
         # ---- accept + commit
-        check(L.msgl_spec_accept(target.data_ptr(), pool_flat.data_ptr(), self._v("first_idx", bs).data_ptr(),
-                                 self._v("num_draft", bs).data_ptr(), self._v("max_emit", bs).data_ptr(),
-                                 self._v("flags", bs).data_ptr(), self.record.data_ptr(), self.sel_row.data_ptr(),
-                                 self._eos, self._n_eos, bs, W, st), "spec_accept")
-        Kc._count("spec_accept", "spec_accept_kernel")
+        if tree:
+            check(L.msgl_spec_accept_tree(
+                target.data_ptr(), pool_flat.data_ptr(), self._v("first_idx", bs).data_ptr(),
+                self._v("num_draft", bs).data_ptr(), self._v("max_emit", bs).data_ptr(), self._v("flags", bs).data_ptr(),
+                self.sib_tok.data_ptr(), batch.out_loc.data_ptr(), self.record.data_ptr(), self.sel_row.data_ptr(),
+                self.feat_row.data_ptr(), self.moves.data_ptr(), self._eos, self._n_eos, bs, K, T, self.max_bs, st),
+                "spec_accept_tree")
+            Kc._count("spec_accept", "spec_accept_tree_kernel")
+            # an accepted sibling's K/V goes from its scratch slot to its sequence position, in every layer
+            buf = eng.kv_cache._buf
+            _, layers, pages_p1, hk, ps, hd = buf.shape
+            check(L.msgl_spec_kv_compact(buf.data_ptr(), self.moves.data_ptr(), bs,
+                                         pages_p1 * hk * ps * hd * buf.element_size(), 2 * layers, hk, ps,
+                                         hd * buf.element_size(), st), "spec_kv_compact")
+            Kc._count("spec_kv_compact", "spec_kv_compact_kernel")
+        else:
+            check(L.msgl_spec_accept(target.data_ptr(), pool_flat.data_ptr(), self._v("first_idx", bs).data_ptr(),
+                                     self._v("num_draft", bs).data_ptr(), self._v("max_emit", bs).data_ptr(),
+                                     self._v("flags", bs).data_ptr(), self.record.data_ptr(), self.sel_row.data_ptr(),
+                                     self._eos, self._n_eos, bs, W, st), "spec_accept")
+            Kc._count("spec_accept", "spec_accept_kernel")
         if d is not None:
-            # ---- draft update over the verify rows (feature of position p, token at p + 1)
+            # ---- draft update over the accepted path's rows (feature of position p, token at p + 1)
             feat = d.features(aux)
-            emb = d.embed.forward(pool_flat[(tok_idx + 1).long()])
-            hx = d.layer(emb, feat, batch.positions, batch.out_loc, bt, cu_q, seq_lens, W, msl)
+            if tree:
+                feat = feat[self.feat_row[:bs * W].long()]
+                u_tok = self._v("u_tok_idx", bs * W)
+                emb = d.embed.forward(pool_flat[(u_tok + 1).long()])
+                hx = d.layer(emb, feat, self._v("u_positions", bs * W), self._v("u_out_loc", bs * W), bt,
+                             self.cu_q_update[:bs + 1], self._v("u_seq_lens", bs), W, msl)
+            else:
+                emb = d.embed.forward(pool_flat[(tok_idx + 1).long()])
+                hx = d.layer(emb, feat, batch.positions, batch.out_loc, bt, cu_q, seq_lens, W, msl)
             d.hidden[slots] = hx[self.sel_row[:bs].long()]
 
     # ------------------------------------------------------------------ prefill feed
@@ -324,10 +401,30 @@ class DeviceSpecRunner:
         pos_c = np.minimum(pos, msl - 1)
         page = np.take_along_axis(bt.astype(np.int64), np.minimum(pos_c // ps, P - 1), axis=1)
         loc = np.where(live, page * ps + pos_c % ps, dummy_page * ps + (j % ps))
-        put("token_idx", slot[:, None] * msl + np.minimum(pos, msl - 2))
-        put("positions", pos_c)
-        put("out_loc", loc)
-        put("seq_lens", np.minimum(c + W, msl))
+        tok = slot[:, None] * msl + np.minimum(pos, msl - 2)
+        if self.T == 1:
+            put("token_idx", tok)
+            put("positions", pos_c)
+            put("out_loc", loc)
+            put("seq_lens", np.minimum(c + W, msl))
+        else:
+            T, R = self.T, self.R
+            put("u_tok_idx", tok)
+            put("u_positions", pos_c)
+            put("u_out_loc", loc)
+            put("u_seq_lens", np.minimum(c + W, msl))
+            # sibling i (depth-major): position of its depth, K/V at scratch position c + K + 1 + i
+            i_s = np.arange(K * (T - 1), dtype=np.int64)[None, :]
+            s_pos = np.minimum(c[:, None] + i_s // (T - 1) + 1, msl - 1)
+            s_at = c[:, None] + K + 1 + i_s
+            s_live = s_at < alloc_end[:, None]
+            s_at_c = np.minimum(s_at, msl - 1)
+            s_page = np.take_along_axis(bt.astype(np.int64), np.minimum(s_at_c // ps, P - 1), axis=1)
+            s_loc = np.where(s_live, s_page * ps + s_at_c % ps, dummy_page * ps + (i_s % ps))
+            put("token_idx", np.concatenate([tok, np.full_like(s_pos, dummy_slot * msl)], axis=1))
+            put("positions", np.concatenate([pos_c, s_pos], axis=1))
+            put("out_loc", np.concatenate([loc, s_loc], axis=1))
+            put("seq_lens", np.minimum(c + R, msl))
         off, _ = self.offsets["block_table"]
         host[off:off + bucket * P] = bt.reshape(-1)
         put("first_idx", slot * msl + np.minimum(c + 1, msl - 1))

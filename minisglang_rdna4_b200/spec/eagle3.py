@@ -196,6 +196,8 @@ class Eagle3Proposer(Proposer):
 
     def __init__(self, config, scheduler, mtp: bool = False) -> None:
         super().__init__(config.spec_num_draft)
+        # candidates per depth of the verify tree (1 = a chain); used by the device step only
+        self.tree_width = max(1, int(getattr(config, "spec_tree_width", 1) or 1))
         eng = scheduler.engine
         self.engine = eng
         cfg = eng.model_config

@@ -329,6 +329,74 @@ def test_speculative_decoding_is_exact_on_the_gpu(quant, kv, layers):
         os.environ.pop("MSGL_SPEC_HOST_STEP", None)
 
 
+def test_tree_verification_with_the_draft_head_is_exact_and_accepts_siblings():
+    """Device tree step (chain + siblings per depth, constant mask, tree acceptance, K/V move). A
+    random-init draft head never guesses right, so the head's candidates are replaced by an oracle
+    built from the plain run: right at depth 1, while at depth 2 the chain goes wrong and the
+    right token sits among the siblings. Every step must then accept the chain token of depth 1, the
+    sibling of depth 2 and the bonus token, and the output must still be
+    exactly the plain greedy output (which it can only be if the sibling's K/V was moved into place)."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import cuda as K
+
+    def make(**kw):
+        return LLM(model_config=_cfg(layers=3), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                   num_page_override=256, seed=0, **kw)
+
+    prompts = _prompts()
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    plain = make(spec_algorithm="eagle3", spec_num_draft=3)
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    plain.shutdown()
+    # next-token oracle keyed by (position of the previous token, previous token)
+    vocab = _cfg().vocab_size
+    oracle = torch.zeros((2048, vocab), dtype=torch.int32)
+    for p, w in zip(prompts, want):
+        seq = list(p) + list(w)
+        for i in range(len(p) - 1, len(seq) - 1):
+            oracle[i, seq[i]] = seq[i + 1]
+    spec = make(spec_algorithm="eagle3", spec_num_draft=3, spec_tree_width=3)
+    from minisglang_rdna4_b200.scheduler.spec_step import device_runner
+
+    runner = device_runner(spec)
+    assert runner is not None and runner.T == 3 and runner.R == 10
+    assert int(runner.draft.m._draft_vocab) == vocab and not bool(runner.draft.m.d2t.any())
+    oracle_d = oracle.cuda()
+    state = {"depth": 0, "prev": None}
+    eng = spec.engine
+
+    def fake_topk(h_rows, width):
+        bs = h_rows.shape[0]
+        depth = state["depth"]
+        root_pos = runner._v("positions", bs * runner.R).view(bs, runner.R)[:, 0].long()
+        if depth == 0:
+            root_idx = runner._v("token_idx", bs * runner.R).view(bs, runner.R)[:, 0].long()
+            state["prev"] = eng.token_pool.view(-1)[root_idx].long()
+        right = oracle_d[(root_pos + depth).clamp_max(2047), state["prev"]].long()
+        state["prev"] = right
+        state["depth"] = (depth + 1) % runner.K
+        wrong = (right + 1) % vocab
+        cand = torch.stack([right, wrong, (right + 2) % vocab], dim=1)
+        if depth == 1:                       # depth 2 of the tree: the chain is wrong, sibling 0 is right
+            cand = torch.stack([wrong, right, (right + 2) % vocab], dim=1)
+        return cand.to(torch.int32)
+
+    runner.draft.head_topk = fake_topk
+    runner.graphs.clear()
+    runner.capture()                         # capture again, now with the oracle in the graphs
+    got = [o.token_ids for o in spec.generate(prompts, sp)]
+    assert K.gemm_status() == 0 and K.attn_status() == 0
+    assert got == want
+    steps, emitted = spec.stats["spec_steps"], spec.stats["spec_emitted"]
+    assert runner.replays > 0 and "spec_kv_compact" in K.LEDGER
+    # chain depth 1 + sibling at depth 2 + bonus = 3 tokens per request-step, except the last steps of a request
+    tree_steps = spec.stats["spec_drafted"] // runner.K
+    assert tree_steps > 0 and spec.stats["spec_accepted"] >= 1.6 * tree_steps, (steps, emitted, spec.stats)
+    spec.cache.check_integrity()
+    spec.shutdown()
+
+
 def test_host_expert_tier_matches_resident_experts_on_the_gpu():
     """MoE experts that do not fit the device budget live in pinned host memory and are copied in
     on a side stream when routed to (SLRU residency cache): the slab forward agrees with the all-resident

@@ -619,6 +619,126 @@ def test_spec_accept_kernel_matches_the_host_rules(K):
     assert torch.equal(d_pool.cpu(), want_pool)
 
 
+def test_spec_accept_tree_kernel_follows_the_target_down_the_tree(K):
+    """Tree acceptance (chain + siblings per depth): emitted tokens, EOS / length truncation, commit,
+    the K/V move of an accepted sibling and the feature rows of the draft update, against a plain
+    restatement of the rule."""
+    import ctypes
+
+    from minisglang_rdna4_b200.ops._lib import check, lib
+    from minisglang_rdna4_b200.spec.device import _bind
+
+    _bind()
+    g = torch.Generator().manual_seed(1)
+    B, Kd, T, msl, Bmax = 41, 3, 4, 64, 48
+    R = 1 + Kd * T
+    pool = torch.randint(0, 50, (B + 1, msl), generator=g, dtype=torch.int32)
+    target = torch.randint(0, 7, (B, R), generator=g, dtype=torch.int32)
+    sib = torch.randint(0, 7, (Kd, Bmax, T - 1), generator=g, dtype=torch.int32)
+    c = torch.randint(3, 40, (B,), generator=g)
+    k = torch.where(torch.rand(B, generator=g) < 0.2, 0, Kd)
+    max_emit = torch.randint(1, 7, (B,), generator=g)
+    ignore = torch.randint(0, 2, (B,), generator=g)
+    out_loc = torch.randint(0, 10_000, (B, R), generator=g, dtype=torch.int32)
+    eos = [5]
+    for b in range(B):     # some chain drafts stand: draft at depth d is the prediction of the node above it
+        good = int(torch.randint(0, Kd + 1, (1,), generator=g))
+        for d in range(1, good + 1):
+            pool[b, c[b] + d] = target[b, d - 1]
+    want_pool = pool.clone()
+    want = []
+    for b in range(B):
+        em, hit, cur, mv, frow = [], 0, 0, (-1, -1), [b * R + j for j in range(Kd + 1)]
+        limit = max(int(max_emit[b]), 1)
+        for d in range(1, Kd + 2):
+            p = int(target[b, cur])
+            em.append(p)
+            if not ignore[b] and p in eos:
+                hit = 1
+                break
+            if len(em) >= limit or d > int(k[b]):
+                break
+            if int(pool[b, c[b] + d]) == p:
+                cur = d
+                continue
+            cands = sib[d - 1, b].tolist()
+            if p not in cands:
+                break
+            row = Kd + (d - 1) * (T - 1) + cands.index(p) + 1
+            mv = (int(out_loc[b, row]), int(out_loc[b, d]))
+            frow[d] = b * R + row
+            p2 = int(target[b, row])
+            em.append(p2)
+            if not ignore[b] and p2 in eos:
+                hit = 1
+            break
+        want.append((em, hit, mv, frow))
+        want_pool[b, c[b] + 1: c[b] + 1 + len(em)] = torch.tensor(em, dtype=torch.int32)
+    dev = "cuda"
+    d_pool = pool.to(dev)
+    rec = torch.zeros(B * (Kd + 3), dtype=torch.int32, device=dev)
+    sel = torch.zeros(B, dtype=torch.int32, device=dev)
+    frow_d = torch.zeros(B * (Kd + 1), dtype=torch.int32, device=dev)
+    moves = torch.zeros(B * 2, dtype=torch.int32, device=dev)
+    first = (torch.arange(B) * msl + c + 1).to(torch.int32).to(dev)
+    eos_arr = (ctypes.c_int * 8)(*(eos + [-1] * 7))
+    keep = [target.to(dev), k.to(torch.int32).to(dev), max_emit.to(torch.int32).to(dev), ignore.to(torch.int32).to(dev),
+            sib.to(dev), out_loc.to(dev)]
+    check(lib().msgl_spec_accept_tree(keep[0].data_ptr(), d_pool.data_ptr(), first.data_ptr(), keep[1].data_ptr(),
+                                      keep[2].data_ptr(), keep[3].data_ptr(), keep[4].data_ptr(), keep[5].data_ptr(),
+                                      rec.data_ptr(), sel.data_ptr(), frow_d.data_ptr(), moves.data_ptr(), eos_arr, 1, B,
+                                      Kd, T, Bmax, torch.cuda.current_stream().cuda_stream), "spec_accept_tree")
+    torch.cuda.synchronize()
+    rec = rec.cpu().view(B, Kd + 3)
+    accepted_sibling = 0
+    for b, (em, hit, mv, frow) in enumerate(want):
+        n = len(em)
+        assert int(rec[b, 0]) == n and int(rec[b, 1]) == hit and rec[b, 2:2 + n].tolist() == em, (b, rec[b], em)
+        assert int(sel[b]) == b * (Kd + 1) + n - 1
+        assert tuple(moves.cpu()[2 * b:2 * b + 2].tolist()) == mv, b
+        assert frow_d.cpu()[b * (Kd + 1):(b + 1) * (Kd + 1)].tolist() == frow, b
+        accepted_sibling += mv[0] >= 0
+    assert accepted_sibling >= 3                       # the case this kernel exists for did occur
+    assert torch.equal(d_pool.cpu(), want_pool)
+
+
+def test_windowed_tree_mask_equals_the_full_mask(K):
+    """A mask that covers only the last R K/V positions of each request gives the same result as the
+    full-length additive mask with zeros in front of it, and as the fp32 restatement."""
+    from minisglang_rdna4_b200.ops import ref
+
+    torch.manual_seed(5)
+    hq, hk, d, ps, R = 8, 2, 128, 16, 9
+    kv_lens = [40, 9, 133, 77]
+    b = len(kv_lens)
+    pages = sum(-(-n // ps) for n in kv_lens)
+    pool = torch.randn(2, 1, pages + 1, hk, ps, d, device="cuda").bfloat16()
+    maxp = max(-(-n // ps) for n in kv_lens)
+    bt = torch.zeros(b, maxp, dtype=torch.int32, device="cuda")
+    off = 0
+    for i, n in enumerate(kv_lens):
+        np_ = -(-n // ps)
+        bt[i, :np_] = torch.arange(off, off + np_, dtype=torch.int32)
+        off += np_
+    cu = (torch.arange(b + 1, dtype=torch.int32, device="cuda") * R).contiguous()
+    sl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    q = torch.randn(b * R, hq, d, device="cuda").bfloat16()
+    vis = torch.where(torch.rand(R, R) < 0.5, 0.0, float("-inf"))
+    vis[:, 0] = 0.0
+    win = vis.repeat(b, 1).contiguous().cuda()
+    full = torch.zeros(b * R, max(kv_lens), device="cuda")
+    for i, n in enumerate(kv_lens):
+        full[i * R:(i + 1) * R, n - R:n] = vis.cuda()
+        full[i * R:(i + 1) * R, n:] = float("-inf")
+    args = (q, pool[0, 0], pool[1, 0], bt, cu, sl, d ** -0.5)
+    a = K.paged_attention(*args, mask=win, mask_window=R, max_q=R, max_kv=max(kv_lens), splits=1)
+    f = K.paged_attention(*args, mask=full, max_q=R, max_kv=max(kv_lens), splits=1)
+    assert K.attn_status() == 0
+    assert torch.equal(a, f)
+    o = ref.paged_attention(*args, True, 0, win, None, None, R)
+    _close(a.float().cpu(), o.float().cpu(), 2e-2, 2e-2, "windowed mask vs oracle")
+
+
 def test_attention_head_dim_256(K):
     """256-wide heads (the Qwen3.5 full-attention layers): prefill, extend, decode and a split decode."""
     _attn_case(K, False, 2, [70, 9], [70, 200], 8, 2, 256, 16)

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(128) gdn_conv1d_kernel(const T* __restrict__ x
                                                          const int32_t* __restrict__ cu_q,
                                                          const int32_t* __restrict__ slots,
                                                          const int32_t* __restrict__ has_state, T* __restrict__ out,
-                                                         int channels) {
+                                                         int channels, const T* __restrict__ bias) {
   pdl_enter();
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= channels) return;
@@ -39,10 +39,11 @@ __global__ void __launch_bounds__(128) gdn_conv1d_kernel(const T* __restrict__ x
   float wv[KW];
 #pragma unroll
   for (int j = 0; j < KW; ++j) wv[j] = to_float(w[(size_t)c * KW + j]);
+  const float bv = bias != nullptr ? to_float(bias[c]) : 0.f;
 #pragma unroll 4
   for (int t = lo; t < hi; ++t) {
     const float cur = to_float(x[(size_t)t * ldx + c]);
-    float acc = cur * wv[KW - 1];
+    float acc = fmaf(cur, wv[KW - 1], bv);
 #pragma unroll
     for (int j = 0; j < KW - 1; ++j) acc = fmaf(hist[j], wv[j], acc);
 #pragma unroll
@@ -168,10 +169,11 @@ __global__ void rms_norm_gated_kernel(const T* __restrict__ x, const T* __restri
 
 }  // namespace
 
-// x [T, channels] with row stride ldx, w [channels, kw], state [slots, channels, kw - 1], out [T, channels]
+// x [T, channels] with row stride ldx, w [channels, kw], state [slots, channels, kw - 1], out [T, channels];
+// bias [channels] or null
 MSGL_API int msgl_gdn_conv1d(const void* x, long long ldx, const void* w, void* state, const void* cu_q,
                              const void* slots, const void* has_state, void* out, int B, int channels, int kw,
-                             int dtype, cudaStream_t stream) {
+                             const void* bias, int dtype, cudaStream_t stream) {
   if (B <= 0 || channels <= 0) return B == 0 ? MSGL_OK : MSGL_BAD_ARG;
   if (kw != 4) {
     msgl_set_error_text("gdn_conv1d: only a kernel of 4 taps is built");
@@ -181,11 +183,11 @@ MSGL_API int msgl_gdn_conv1d(const void* x, long long ldx, const void* w, void* 
   if (dtype == MSGL_BF16)
     msgl_launch(gdn_conv1d_kernel<__nv_bfloat16, 4>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx,
                 (const __nv_bfloat16*)w, (__nv_bfloat16*)state, (const int32_t*)cu_q, (const int32_t*)slots,
-                (const int32_t*)has_state, (__nv_bfloat16*)out, channels);
+                (const int32_t*)has_state, (__nv_bfloat16*)out, channels, (const __nv_bfloat16*)bias);
   else if (dtype == MSGL_F16)
     msgl_launch(gdn_conv1d_kernel<__half, 4>, grid, dim3(128), 0, stream, (const __half*)x, ldx, (const __half*)w,
                 (__half*)state, (const int32_t*)cu_q, (const int32_t*)slots, (const int32_t*)has_state, (__half*)out,
-                channels);
+                channels, (const __half*)bias);
   else
     return MSGL_BAD_ARG;
   MSGL_CHECK_LAUNCH("gdn_conv1d");

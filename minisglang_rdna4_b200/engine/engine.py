@@ -181,7 +181,7 @@ class Engine:
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
         # hybrid models keep K/V pages for their full-attention layers only
-        self.kv_layers = mc.num_layers - mc.num_linear_layers
+        self.kv_layers = mc.num_kv_layers
         self.kv_cache = MHAKVCache(
             self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
             self.dtype, self.device, fp8=self.kv_fp8,
@@ -207,11 +207,9 @@ class Engine:
         if mc.is_recurrent:
             from ..kvcache.gdn_state import GDNStateCache
 
-            conv_dim = 2 * mc.linear_num_key_heads * mc.linear_key_head_dim + \
-                mc.linear_num_value_heads * mc.linear_value_head_dim
+            conv_dim, st_heads, st_rows, st_cols = mc.recurrent_geometry
             self.gdn_state = GDNStateCache(mc.num_linear_layers, self.num_slots, conv_dim, mc.linear_conv_kernel_dim,
-                                           mc.linear_num_value_heads, mc.linear_key_head_dim,
-                                           mc.linear_value_head_dim, self.dtype, self.device)
+                                           st_heads, st_rows, st_cols, self.dtype, self.device)
             self.ledger.add("recurrent state", self.gdn_state.conv.numel() * self.gdn_state.conv.element_size()
                             + self.gdn_state.ssm.numel() * 4)
         self.ctx.gdn_state = self.gdn_state
@@ -399,7 +397,7 @@ class Engine:
         if cfg.num_page_override is not None:
             return int(cfg.num_page_override)
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
-        per_page = MHAKVCache.token_bytes(mc.num_layers - mc.num_linear_layers, self.kv_heads_local, mc.head_dim,
+        per_page = MHAKVCache.token_bytes(mc.num_kv_layers, self.kv_heads_local, mc.head_dim,
                                           itemsize) * self.page_size
         if cfg.spec_algorithm in ("eagle3", "mtp"):
             # the draft head keeps one 16-bit, unsharded layer of K/V on the same page table
@@ -415,11 +413,9 @@ class Engine:
         if mc.is_recurrent:
             from ..kvcache.gdn_state import GDNStateCache
 
-            conv_dim = 2 * mc.linear_num_key_heads * mc.linear_key_head_dim + \
-                mc.linear_num_value_heads * mc.linear_value_head_dim
+            conv_dim, st_heads, st_rows, st_cols = mc.recurrent_geometry
             budget -= (cfg.max_running_req + 1) * GDNStateCache.slot_bytes(
-                mc.num_linear_layers, conv_dim, mc.linear_conv_kernel_dim, mc.linear_num_value_heads,
-                mc.linear_key_head_dim, mc.linear_value_head_dim, 2)
+                mc.num_linear_layers, conv_dim, mc.linear_conv_kernel_dim, st_heads, st_rows, st_cols, 2)
         pages = budget // per_page
         if self.cpu_group is not None:
             t = torch.tensor([pages], dtype=torch.int64)

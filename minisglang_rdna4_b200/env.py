@@ -139,7 +139,8 @@ ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the 
 ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of the fused reduce-scatter / all-gather GEMMs")
 ENV.flag("PDL", True, "programmatic dependent launch: a kernel's prologue overlaps the tail of the kernel ahead of it")
 ENV.int("EP_REGION_GIB", 6, "per-rank budget of the expert-parallel exchange regions (sets the largest fused step)")
-ENV.str("NVLS", "auto", "decode all-reduce by in-switch reduction (multimem): auto = on 4 or more ranks, on, off")
+ENV.str("NVLS", "auto", "decode all-reduce by in-switch reduction (multimem): auto = from 8 ranks up (measured slower than peer "
+        "stores at 2 and 4 ranks), on, off")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger ones go to the row-sharded GEMM fusion or to NCCL")
 ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-loop detector looks for; 0 = off")

@@ -32,7 +32,8 @@ class MoELayer(BaseOP):
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, renormalize: bool,
                  dtype, device, scoring: str = "softmax", routed_scale: float = 1.0,
-                 scheme=None, n_group: int = 1, topk_group: int = 1, selection_bias: bool = False) -> None:
+                 scheme=None, n_group: int = 1, topk_group: int = 1, selection_bias: bool = False,
+                 gated: bool = True, act: str = "silu", expert_input: Optional[int] = None) -> None:
         tp = get_tp_info()
         ep = get_ep_info()
         self._ep = ep if ep_enabled() else None
@@ -47,13 +48,18 @@ class MoELayer(BaseOP):
             self._i_local = div_even(inter, tp.size)
         self._hidden = hidden
         self._compute_dtype = dtype
+        # non-gated experts (down(act(up x)), Nemotron-H) take 16-bit weights and the local path only;
+        # expert_input: width of the experts' input when a latent projection sits in front of them
+        self._gated, self._act = gated, act
+        self._in = expert_input or hidden
         self._n_group, self._topk_group = max(1, n_group), max(1, topk_group)
         self.gate = ReplicatedLinear(hidden, num_experts, dtype, device, None)
         if selection_bias:
             # DeepSeek-V3 / GLM-4 style: added to the scores when choosing experts, not to the weights
             self.e_score_correction_bias = torch.zeros((num_experts,), dtype=torch.float32, device=device)
-        self.w13 = torch.empty((self._e_local, 2 * self._i_local, hidden), dtype=dtype, device=device)
-        self.w2 = torch.empty((self._e_local, hidden, self._i_local), dtype=dtype, device=device)
+        self.w13 = torch.empty((self._e_local, (2 if gated else 1) * self._i_local, self._in), dtype=dtype,
+                               device=device)
+        self.w2 = torch.empty((self._e_local, self._in, self._i_local), dtype=dtype, device=device)
         # Quantised experts keep their checkpoint precision on the GPU (the reference's expert
         # methods: python/minisgl/layers/moe.py:42-520):
         #   mxfp4        W4A8, e2m1 + UE8M0 scale atoms (re-encoding the stacks is lossless for an
@@ -73,10 +79,13 @@ class MoELayer(BaseOP):
         self._w4a8 = self._quant_kind == "mxfp4"
         self._raw_fp8 = None   # (w13_q, w13_scale, w2_q, w2_scale) straight from an fp8 checkpoint
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, expert_x: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Returns this rank's partial result (tensor-parallel partial sum when the
-        intermediate dimension is sharded; complete under expert parallelism)."""
+        intermediate dimension is sharded; complete under expert parallelism). ``expert_x``: the
+        experts' input when it differs from the router's (a latent projection in front of them)."""
         logits = self.gate.forward(x)
+        if expert_x is not None:
+            x = expert_x
         bias = getattr(self, "e_score_correction_bias", None)
         ctx = try_global_ctx()
         use_ep = self._ep is not None and ctx is not None and ctx.ep is not None
@@ -95,12 +104,14 @@ class MoELayer(BaseOP):
                                            counts, self._e_start, self._e_local)
         else:
             topk_w, topk_ids = ops.moe_route(logits, self._k, self._renorm, self._scoring, bias, self._routed_scale)
-        if use_ep:
+        if use_ep and self._gated:
             return ctx.ep.dispatch_compute_combine(self, x, topk_w, topk_ids)
         return self.local_experts(x, topk_w, topk_ids, counts)
 
     def local_experts(self, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor, counts=None
                       ) -> torch.Tensor:
+        if not self._gated:
+            return ops.moe_forward_plain(x, self.w13, self.w2, topk_w, topk_ids, self._e_start, counts, self._act)
         tier = getattr(self, "_tier", None)
         if tier is not None:
             return tier.forward(x, topk_w, topk_ids - self._e_start)

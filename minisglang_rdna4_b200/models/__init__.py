@@ -40,6 +40,12 @@ def _register_defaults() -> None:
             MODEL_REGISTRY.register(arch)(Glm4MoeLiteForCausalLM)
 
 
+    from .nemotron_h import NemotronHForCausalLM
+
+    if "NemotronHForCausalLM" not in MODEL_REGISTRY:
+        MODEL_REGISTRY.register("NemotronHForCausalLM")(NemotronHForCausalLM)
+
+
 def create_model(cfg: ModelConfig, dtype: torch.dtype, device):
     """Instantiate the model for ``cfg`` with uninitialised (or meta) parameters."""
     _register_defaults()

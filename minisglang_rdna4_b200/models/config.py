@@ -79,6 +79,16 @@ class ModelConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    # Mamba-2 mixers (Nemotron-H hybrid family): layer_types entries "mamba" / "attention" / "moe" / "mlp"
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    ssm_state_size: int = 0
+    mamba_n_groups: int = 1
+    mamba_conv_bias: bool = True
+    mamba_proj_bias: bool = False
+    time_step_min: float = 0.0
+    moe_latent_size: Optional[int] = None
+    mlp_hidden_act: str = "silu"          # "relu2": non-gated squared-ReLU MLPs and experts
     attn_output_gate: bool = False        # q_proj also emits a per-head sigmoid gate of the attention output
     norm_plus_one: bool = False           # RMSNorm weights are stored as (w - 1)
     # misc
@@ -110,11 +120,31 @@ class ModelConfig:
     @property
     def is_recurrent(self) -> bool:
         """Some layers keep a recurrent state per request instead of K/V pages."""
-        return bool(self.layer_types) and any(t == "linear_attention" for t in self.layer_types)
+        return bool(self.layer_types) and any(t in ("linear_attention", "mamba") for t in self.layer_types)
 
     @property
     def num_linear_layers(self) -> int:
-        return sum(1 for t in (self.layer_types or ()) if t == "linear_attention")
+        """Layers with a recurrent state (gated delta net or Mamba-2)."""
+        return sum(1 for t in (self.layer_types or ()) if t in ("linear_attention", "mamba"))
+
+    @property
+    def num_kv_layers(self) -> int:
+        """Layers that keep K/V pages."""
+        if self.model_type == "nemotron_h":
+            return sum(1 for t in (self.layer_types or ()) if t == "attention")
+        return self.num_layers - self.num_linear_layers
+
+    @property
+    def recurrent_geometry(self) -> Tuple[int, int, int, int]:
+        """``(conv channels, heads, rows, cols)`` of one recurrent layer's state: a convolution window
+        over ``conv channels`` inputs and a ``[heads, rows, cols]`` fp32 state matrix per request."""
+        if self.mamba_num_heads:
+            inter = self.mamba_num_heads * self.mamba_head_dim
+            return (inter + 2 * self.mamba_n_groups * self.ssm_state_size, self.mamba_num_heads, self.mamba_head_dim,
+                    self.ssm_state_size)
+        return (2 * self.linear_num_key_heads * self.linear_key_head_dim
+                + self.linear_num_value_heads * self.linear_value_head_dim,
+                self.linear_num_value_heads, self.linear_key_head_dim, self.linear_value_head_dim)
 
     @property
     def q_size(self) -> int:
@@ -233,6 +263,18 @@ class ModelConfig:
                 cfg = dict(cfg, mlp_only_layers=dense)
                 g = cfg.get
         attn_bias = bool(g("attention_bias", model_type in ("qwen2", "qwen2_moe")))
+        if model_type == "nemotron_h":
+            # one mixer per layer: M = Mamba-2, * = attention, E = mixture of experts, - = MLP; no rotary embedding
+            pattern = g("hybrid_override_pattern")
+            names = {"M": "mamba", "*": "attention", "E": "moe", "-": "mlp"}
+            layer_types = list(g("layers_block_type") or g("layer_types") or [names[ch] for ch in (pattern or "")])
+            if not layer_types:
+                raise ValueError("nemotron_h config without layers_block_type / hybrid_override_pattern")
+            rotary = RotaryConfig(head_dim=head_dim, rotary_dim=0, max_position=max_pos, base=theta)
+            cfg = dict(cfg, num_hidden_layers=len(layer_types), rms_norm_eps=g("layer_norm_epsilon", g("rms_norm_eps", 1e-5)),
+                       shared_expert_intermediate_size=g("moe_shared_expert_intermediate_size") or 0,
+                       scoring_func="sigmoid")
+            g = cfg.get
         return ModelConfig(
             num_layers=int(g("num_hidden_layers")),
             num_qo_heads=heads,
@@ -274,7 +316,16 @@ class ModelConfig:
             linear_num_value_heads=int(g("linear_num_value_heads") or 0),
             linear_key_head_dim=int(g("linear_key_head_dim") or 0),
             linear_value_head_dim=int(g("linear_value_head_dim") or 0),
-            linear_conv_kernel_dim=int(g("linear_conv_kernel_dim") or 4),
+            linear_conv_kernel_dim=int(g("linear_conv_kernel_dim") or g("conv_kernel") or g("mamba_d_conv") or 4),
+            mamba_num_heads=int(g("mamba_num_heads") or 0),
+            mamba_head_dim=int(g("mamba_head_dim") or 0),
+            ssm_state_size=int(g("ssm_state_size") or 0),
+            mamba_n_groups=int(g("n_groups") or g("mamba_n_groups") or 1),
+            mamba_conv_bias=bool(g("use_conv_bias", g("mamba_conv_bias", True))),
+            mamba_proj_bias=bool(g("mamba_proj_bias", g("use_bias", False))),
+            time_step_min=float(g("time_step_min") or g("mamba_dt_min") or 0.0) if model_type == "nemotron_h" else 0.0,
+            moe_latent_size=g("moe_latent_size"),
+            mlp_hidden_act=g("mlp_hidden_act", "silu"),
             attn_output_gate=gdn_family,
             norm_plus_one=gdn_family,
             sliding_window=g("sliding_window") if g("use_sliding_window", True) else None,
@@ -312,6 +363,7 @@ def _default_arch(model_type: str) -> List[str]:
         "qwen3_5_moe": ["Qwen3_5MoeForCausalLM"],
         "qwen3_5_moe_text": ["Qwen3_5MoeForCausalLM"],
         "qwen3_next": ["Qwen3NextForCausalLM"],
+        "nemotron_h": ["NemotronHForCausalLM"],
     }.get(model_type, ["LlamaForCausalLM"])
 
 

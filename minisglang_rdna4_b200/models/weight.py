@@ -138,6 +138,49 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             name = "model." + name[len("model.language_model."):]
         if name.startswith("model.visual."):
             continue
+        # ---- Nemotron-H (Mamba-2 hybrid): backbone.* names, one "mixer" per layer
+        if cfg.model_type == "nemotron_h":
+            if name.startswith("backbone."):
+                name = "model." + name[len("backbone."):]
+            name = {"model.embeddings.weight": "model.embed_tokens.weight", "model.norm_f.weight": "model.norm.weight"
+                    }.get(name, name)
+            if ".mixer." in name:
+                block, _, tail = name.partition(".mixer.")
+                mixer = modules.get(block + ".mixer")
+                if mixer is None:
+                    continue
+                if tail == "conv1d.weight":
+                    assign(mixer, "conv1d_weight", tensor.reshape(tensor.shape[0], -1), block + ".mixer.conv1d_weight")
+                    continue
+                if tail == "conv1d.bias":
+                    assign(mixer, "conv1d_bias", tensor, block + ".mixer.conv1d_bias")
+                    continue
+                if tail == "norm.weight":
+                    assign(mixer, "norm_weight", tensor, block + ".mixer.norm_weight")
+                    continue
+                if tail in ("dt_bias", "A_log", "D"):
+                    assign(mixer, tail, tensor.float(), block + ".mixer." + tail)
+                    continue
+                if tail in ("in_proj.weight", "in_proj.bias") and hasattr(mixer, "in_proj"):
+                    rows = getattr(mixer.in_proj, tail.split(".")[1]).shape[0]
+                    if tensor.shape[0] < rows:      # the projection is padded to a multiple of 8 output columns
+                        pad = torch.zeros((rows - tensor.shape[0],) + tuple(tensor.shape[1:]), dtype=tensor.dtype)
+                        tensor = torch.cat([tensor, pad])
+                    assign(mixer.in_proj, tail.split(".")[1], tensor, block + ".mixer." + tail)
+                    continue
+                if tail in ("experts.up_proj", "experts.down_proj") and tensor.dim() == 3:
+                    moe = mixer.experts
+                    t3 = tensor[moe._e_start:moe._e_start + moe._e_local]
+                    assign(moe, "w13" if tail.endswith("up_proj") else "w2", t3,
+                           block + ".mixer.experts." + ("w13" if tail.endswith("up_proj") else "w2"))
+                    continue
+                if tail == "gate.weight" and hasattr(mixer, "experts"):
+                    assign(mixer.experts.gate, "weight", tensor, block + ".mixer.experts.gate.weight")
+                    continue
+                if tail == "gate.e_score_correction_bias" and hasattr(mixer, "experts"):
+                    assign(mixer.experts, "e_score_correction_bias", tensor.float(),
+                           block + ".mixer.experts.e_score_correction_bias")
+                    continue
         # ---- gated delta net (Qwen3.5 / Qwen3-Next linear-attention layers)
         if ".linear_attn." in name:
             block, _, tail = name.partition(".linear_attn.")

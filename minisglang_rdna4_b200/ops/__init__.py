@@ -147,10 +147,36 @@ def gemm_fp8_block(x_q, x_scale, w_q, w_scale, out_dtype=torch.bfloat16):
 
 
 # ---------------------------------------------------------------------------- gated delta net
-def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state):
+def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state, bias=None):
     if x.is_cuda:
-        return _cuda().gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state)
-    return ref.causal_conv1d(x, weight, conv_state, cu_q, slots, has_state)
+        return _cuda().gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state, bias)
+    return ref.causal_conv1d(x, weight, conv_state, cu_q, slots, has_state, bias)
+
+
+def mamba2_scan(xbc, dt, a_log, d_skip, dt_bias, state, cu_q, slots, has_state, heads: int, groups: int,
+                head_dim: int, state_size: int, dt_min: float = 0.0):
+    """Selective state-space recurrence on the rows ``xbc = [x heads ‖ B groups ‖ C groups]`` left by the
+    convolution (python/minisgl/mamba2/)."""
+    if xbc.is_cuda:
+        return _cuda().mamba2_scan(xbc, dt, a_log, d_skip, dt_bias, state, cu_q, slots, has_state, heads, groups,
+                                   head_dim, state_size, dt_min)
+    t = xbc.shape[0]
+    x, b, c = xbc.split([heads * head_dim, groups * state_size, groups * state_size], dim=-1)
+    return ref.mamba2_scan(x.reshape(t, heads, head_dim), dt, b.reshape(t, groups, state_size),
+                           c.reshape(t, groups, state_size), a_log, d_skip, dt_bias, state, cu_q, slots, has_state,
+                           dt_min)
+
+
+def rms_norm_gate_first(x, z, w, eps: float, group: int):
+    if x.is_cuda:
+        return _cuda().rms_norm_gate_first(x, z, w, eps, group)
+    return ref.rms_norm_gate_first(x, z, w, eps, group)
+
+
+def relu2(x):
+    if x.is_cuda:
+        return _cuda().relu2(x)
+    return ref.relu2(x)
 
 
 def gdn_recurrent(qkv, a, b, a_log, dt_bias, state, cu_q, slots, has_state, hk: int, hv: int, dk: int, dv: int):
@@ -195,6 +221,14 @@ def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0):
     if x.is_cuda:
         return _cuda().moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset)
     return ref.moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset)
+
+
+def moe_forward_plain(x, w1, w2, topk_w, topk_ids, expert_offset: int = 0, counts=None, act: str = "relu2"):
+    if x.is_cuda:
+        from . import moe_kernels
+
+        return moe_kernels.moe_forward_plain(x, w1, w2, topk_w, topk_ids, expert_offset, counts, act)
+    return ref.moe_forward_plain(x, w1, w2, topk_w, topk_ids, expert_offset, act)
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]

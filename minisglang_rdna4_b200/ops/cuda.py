@@ -805,22 +805,26 @@ def _bind_gdn():
 
     if getattr(_bind_gdn, "done", False):
         return
-    bind("msgl_gdn_conv1d", c_i, [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p])
+    bind("msgl_gdn_conv1d", c_i, [c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_i, c_p])
+    bind("msgl_mamba2_scan", c_i, [c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_f,
+                                   c_i, c_p])
+    bind("msgl_rms_norm_gate_first", c_i, [c_p, c_p, c_ll, c_p, c_p, c_i, c_i, c_i, c_f, c_i, c_p])
+    bind("msgl_relu2", c_i, [c_p, c_p, c_ll, c_i, c_p])
     bind("msgl_gdn_recurrent", c_i, [c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i,
                                      c_p])
     bind("msgl_rms_norm_gated", c_i, [c_p, c_p, c_ll, c_i, c_p, c_p, c_i, c_i, c_f, c_i, c_p])
     _bind_gdn.done = True
 
 
-def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state):
-    """Depthwise causal conv (4 taps) + SiLU over packed sequences; ``x [T, C]`` may be a column
-    slice of a wider projection (row stride = its leading dimension). Updates ``conv_state``."""
+def gdn_conv1d(x, weight, conv_state, cu_q, slots, has_state, bias=None):
+    """Depthwise causal conv (4 taps, optional bias) + SiLU over packed sequences; ``x [T, C]`` may be a
+    column slice of a wider projection (row stride = its leading dimension). Updates ``conv_state``."""
     _bind_gdn()
     assert x.dim() == 2 and x.stride(1) == 1 and weight.is_contiguous() and conv_state.is_contiguous()
     t, c = x.shape
     out = torch.empty((t, c), dtype=x.dtype, device=x.device)
     check(lib().msgl_gdn_conv1d(_p(x), x.stride(0), _p(weight), _p(conv_state), _p(cu_q), _p(slots), _p(has_state),
-                                _p(out), cu_q.numel() - 1, c, weight.shape[1], _dt(x), _stream()), "gdn_conv1d")
+                                _p(out), cu_q.numel() - 1, c, weight.shape[1], _p(bias), _dt(x), _stream()), "gdn_conv1d")
     _count("gdn_conv1d", "gdn_conv1d_kernel")
     return out
 
@@ -838,6 +842,43 @@ def gdn_recurrent(qkv, a, b, a_log, dt_bias, state, cu_q, slots, has_state, hk, 
                                    _p(slots), _p(has_state), _p(out), cu_q.numel() - 1, hk, hv, dk, dv, _dt(qkv),
                                    _stream()), "gdn_recurrent")
     _count("gdn_recurrent", "gdn_recurrent_kernel")
+    return out
+
+
+def mamba2_scan(xbc, dt, a_log, d_skip, dt_bias, state, cu_q, slots, has_state, heads, groups, head_dim, state_size,
+                dt_min=0.0):
+    """Selective state-space recurrence over packed sequences. ``xbc [T, H*P + 2*G*N]`` (after the
+    convolution: x heads, B groups, C groups), ``dt [T, H]`` raw step sizes (a column slice is fine),
+    ``state [slots, H, P, N]`` fp32 updated in place. Returns ``[T, H, P]``."""
+    _bind_gdn()
+    assert xbc.is_contiguous() and dt.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    t = xbc.shape[0]
+    out = torch.empty((t, heads, head_dim), dtype=xbc.dtype, device=xbc.device)
+    check(lib().msgl_mamba2_scan(_p(xbc), _p(dt), dt.stride(0), _p(a_log), _p(d_skip), _p(dt_bias), _p(state), _p(cu_q),
+                                 _p(slots), _p(has_state), _p(out), cu_q.numel() - 1, heads, groups, head_dim,
+                                 state_size, float(dt_min), _dt(xbc), _stream()), "mamba2_scan")
+    _count("mamba2_scan", "mamba2_scan_kernel")
+    return out
+
+
+def rms_norm_gate_first(x, z, w, eps, group):
+    """``w * norm_group(x * silu(z))``: ``x [T, D]`` contiguous, ``z [T, D]`` (a column slice is fine)."""
+    _bind_gdn()
+    t, d = x.shape
+    assert x.is_contiguous() and z.stride(1) == 1
+    out = torch.empty_like(x)
+    check(lib().msgl_rms_norm_gate_first(_p(x), _p(z), z.stride(0), _p(w), _p(out), t, d, group, eps, _dt(x), _stream()),
+          "rms_norm_gate_first")
+    _count("rms_norm_gate_first", "rms_norm_gate_first_kernel")
+    return out
+
+
+def relu2(x):
+    _bind_gdn()
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    check(lib().msgl_relu2(_p(x), _p(out), x.numel(), _dt(x), _stream()), "relu2")
+    _count("relu2", "relu2_kernel")
     return out
 
 

@@ -109,6 +109,18 @@ def moe_forward(x, w13, w2, topk_w, topk_ids, expert_offset=0, counts=None):
     return out
 
 
+def moe_forward_plain(x, w1, w2, topk_w, topk_ids, expert_offset=0, counts=None, act="relu2"):
+    """Non-gated experts (``down(act(up x))``, Nemotron-H): ``w1 [E, I, H]``, ``w2 [E, H, I]``, 16-bit."""
+    if act != "relu2":
+        raise ValueError(f"non-gated experts with activation {act!r}")
+    t, h = x.shape
+    k = topk_ids.shape[1]
+    sorted_pair, pair_row, tile_expert, _meta = moe_align(topk_ids, expert_offset, w1.shape[0], counts)
+    xs = _permute(x, sorted_pair, k)
+    y = gemm_grouped(K.relu2(gemm_grouped(xs, w1, tile_expert)), w2, tile_expert)
+    return _combine(y, topk_w, pair_row, x, k)
+
+
 def gemm_grouped_w4a8(a_q, a_scale, b_packed, sf_atoms, tile_expert, out_dtype=torch.bfloat16, bn=0):
     """MXFP4 experts: ``a_q [R, K]`` e4m3 rows (expert-sorted, R % 128 == 0) with per-row scales,
     ``b_packed [E, N, K/2]`` e2m1 pairs, ``sf_atoms [E, ceil(N/128), ceil(K/128), 32, 4, 4]`` → ``[R, N]``."""

@@ -410,11 +410,28 @@ def moe_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: to
     return out.to(x.dtype)
 
 
+def moe_forward_plain(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
+                      topk_ids: torch.Tensor, expert_offset: int = 0, act: str = "relu2") -> torch.Tensor:
+    """``sum_k w_k * down_e(act(up_e x))`` for non-gated experts (``w1 [E, I, H]``, ``w2 [E, H, I]``)."""
+    t, h = x.shape
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    xf = x.float()
+    for e in range(w1.shape[0]):
+        sel = (topk_ids == e + expert_offset)
+        rows = sel.any(-1).nonzero().squeeze(-1)
+        if rows.numel() == 0:
+            continue
+        wt = (topk_w * sel).sum(-1)[rows]
+        hcur = relu2((xf[rows] @ w1[e].float().t()).to(x.dtype)).float()
+        out[rows] += (hcur @ w2[e].float().t()) * wt[:, None]
+    return out.to(x.dtype)
+
+
 # ------------------------------------------------------------------------------------------
 # gated delta net (linear attention with a recurrent state)
 # ------------------------------------------------------------------------------------------
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tensor, cu_q: torch.Tensor,
-                  slots: torch.Tensor, has_state: torch.Tensor) -> torch.Tensor:
+                  slots: torch.Tensor, has_state: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Depthwise causal convolution + SiLU over packed sequences.
 
     ``x [T, C]`` holds the rows of B sequences (``cu_q [B+1]``); ``weight [C, Kw]``;
@@ -433,6 +450,8 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, conv_state: torch.Tenso
         acc = torch.zeros((n, x.shape[1]))
         for j in range(kw):
             acc += seq[j:j + n] * wf[:, j]
+        if bias is not None:
+            acc += bias.float()
         out[lo:hi] = F.silu(acc).to(x.dtype)
         conv_state[slot] = seq[-(kw - 1):].t().to(conv_state.dtype)
     return out
@@ -477,6 +496,52 @@ def gdn_recurrent(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Te
             out[i] = (s * qf[i][:, :, None]).sum(1)
         state[slot] = s
     return out.to(v.dtype)
+
+
+def mamba2_scan(x: torch.Tensor, dt: torch.Tensor, b: torch.Tensor, c: torch.Tensor, a_log: torch.Tensor,
+                d_skip: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+                slots: torch.Tensor, has_state: torch.Tensor, dt_min: float = 0.0) -> torch.Tensor:
+    """Selective state-space recurrence of a Mamba-2 mixer, token by token.
+
+    ``x [T, H, P]`` (after the convolution), ``dt [T, H]`` raw step sizes, ``b, c [T, G, N]`` (a group
+    of ``H / G`` heads shares one B and C), ``a_log, d_skip, dt_bias [H]``, ``state [slots, H, P, N]``
+    fp32, updated in place (a sequence with ``has_state == 0`` starts from zeros). Per token and head:
+    ``dt' = max(softplus(dt + dt_bias), dt_min)``; ``S = S * exp(-exp(a_log) dt') + dt' x (x) B``;
+    ``y = S C + d_skip x``. Returns ``[T, H, P]``."""
+    t, h, p = x.shape
+    g = b.shape[1]
+    rep = h // g
+    out = torch.empty((t, h, p), dtype=torch.float32)
+    a = -a_log.float().exp()
+    for s_i in range(cu_q.numel() - 1):
+        lo, hi = int(cu_q[s_i]), int(cu_q[s_i + 1])
+        slot = int(slots[s_i])
+        st = state[slot].float().clone() if int(has_state[s_i]) else torch.zeros_like(state[slot], dtype=torch.float32)
+        for i in range(lo, hi):
+            step = torch.clamp(F.softplus(dt[i].float() + dt_bias.float()), min=dt_min)          # [H]
+            bi = b[i].float().repeat_interleave(rep, dim=0)                                         # [H, N]
+            ci = c[i].float().repeat_interleave(rep, dim=0)
+            xi = x[i].float()                                                                       # [H, P]
+            st = st * torch.exp(step * a)[:, None, None] + (step[:, None] * xi)[:, :, None] * bi[:, None, :]
+            out[i] = torch.einsum("hpn,hn->hp", st, ci) + d_skip.float()[:, None] * xi
+        state[slot] = st.to(state.dtype)
+    return out.to(x.dtype)
+
+
+def rms_norm_gate_first(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, group: int) -> torch.Tensor:
+    """``w * norm_g(x * silu(z))`` where the RMS is taken over groups of ``group`` consecutive
+    channels (the gate comes before the norm: Mamba-2 / Zamba-2 / Nemotron-H mixers)."""
+    y = x.float() * F.silu(z.float())
+    shape = y.shape
+    yg = y.view(*shape[:-1], shape[-1] // group, group)
+    yg = yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + eps)
+    return (w.float() * yg.view(shape).to(x.dtype).float()).to(x.dtype)
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    """Squared ReLU (the non-gated MLP activation of the Nemotron-H family)."""
+    r = torch.relu(x.float())
+    return (r * r).to(x.dtype)
 
 
 def rms_norm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:

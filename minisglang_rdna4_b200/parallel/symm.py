@@ -163,7 +163,7 @@ class SymmetricCollectives:
         self.nvls: Optional[MulticastBuffer] = None
         self._nvls_seq = None
         mode = ENV.NVLS.value
-        if mode != "off" and world >= (2 if mode == "on" else 4):
+        if mode != "off" and world >= (2 if mode == "on" else 8):
             count_bytes = (self.max_rows * 4 + 255) // 256 * 256
             self.nvls = MulticastBuffer.create(count_bytes + 2 * self.max_rows * max_hidden * 2, group, self.device)
             if self.nvls is not None:

@@ -56,7 +56,7 @@ def _worker(rank, world, port, q):
             if not res_ok:
                 ok = False
                 msgs.append(f"residual mismatch rows={rows} hidden={hidden} it={it}")
-            if float((out.cpu().float() - want.float()).abs().max()) > 0.05:
+            if float((out.cpu().float() - want.float()).abs().max()) > (0.12 if nvls else 0.05):
                 ok = False
                 msgs.append(f"norm mismatch rows={rows} hidden={hidden} it={it}")
             # quantised variant and plain all-reduce

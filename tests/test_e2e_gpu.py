@@ -492,6 +492,49 @@ def test_qwen3_5_hybrid_model_tracks_fp32_oracle():
         assert first_ok >= len(want) - 1, (got, want)
 
 
+def test_nemotron_h_hybrid_model_tracks_fp32_oracle():
+    """Mamba-2 / attention / non-gated MoE hybrid on the kernel path (state-space scan with a register-
+    resident state row per thread, convolution with bias, gate-first grouped norm, attention without
+    rotary embedding, squared-ReLU experts through the grouped GEMM) against the CPU fp32 oracle path with
+    the same weights; graph decode reproduces eager decode and a chunked prefill carries the states over."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=5, num_qo_heads=8, num_kv_heads=2, head_dim=128, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-5,
+            rotary_config=RotaryConfig(head_dim=128, rotary_dim=0, max_position=2048, base=1e4),
+            model_type="nemotron_h", architectures=("NemotronHForCausalLM",), max_position_embeddings=2048,
+            layer_types=("mamba", "moe", "attention", "mlp", "mamba"),
+            mamba_num_heads=16, mamba_head_dim=64, ssm_state_size=128, mamba_n_groups=4, time_step_min=0.001,
+            mlp_hidden_act="relu2", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256,
+            shared_expert_intermediate_size=512, scoring_func="sigmoid", routed_scaling_factor=1.5,
+        )
+
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = {}
+    state = None
+    for name, kw in (("graph", dict()), ("eager", dict(cuda_graph_max_bs=-1)),
+                     ("chunked", dict(cuda_graph_max_bs=-1, max_extend_tokens=96))):
+        gpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                  num_page_override=256, seed=0, **kw)
+        if state is None:
+            state = {k: v.float().cpu() for k, v in gpu.engine.model.state_dict().items()}
+        outs[name] = [o.token_ids for o in gpu.generate(_prompts(), sp)]
+        gpu.shutdown()
+    assert outs["graph"] == outs["eager"]
+    cpu = LLM(model_config=cfg(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    cpu.engine.model.load_state_dict(state, strict=False)
+    want = [o.token_ids for o in cpu.generate(_prompts(), sp)]
+    cpu.shutdown()
+    for got in (outs["eager"], outs["chunked"]):
+        first_ok = sum(g[0] == w[0] for g, w in zip(got, want))
+        assert first_ok >= len(want) - 1, (got, want)
+
+
 def test_glm4_moe_lite_model_tracks_fp32_oracle():
     """Latent-attention + sigmoid-routed MoE decoder on the kernel path (materialised 256-wide heads
     with interleaved rotary on their first 64 channels, selection bias in the routing kernel, shared

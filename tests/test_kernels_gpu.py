@@ -797,6 +797,49 @@ def test_gated_delta_net_kernels(K, d):
     _close(y.cpu(), y_c, 2e-2, 2e-2, "gated norm")
 
 
+def test_mamba2_kernels_match_the_oracle(K):
+    """Convolution with bias, selective scan (fresh and continued states, grouped B / C), gate-first
+    grouped norm and squared ReLU against their fp32 restatements."""
+    from minisglang_rdna4_b200.ops import ref as R
+
+    torch.manual_seed(3)
+    for h, p, n, g in ((16, 64, 128, 4), (4, 32, 16, 2), (8, 64, 64, 8)):
+        inter, cdim = h * p, h * p + 2 * g * n
+        lens = [5, 1, 37, 12]
+        t, b = sum(lens), len(lens)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        slots = torch.tensor([3, 0, 5, 1], dtype=torch.int32, device="cuda")
+        has = torch.tensor([0, 1, 1, 0], dtype=torch.int32, device="cuda")
+        proj = (torch.randn(t, inter + cdim + h, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(cdim, 4, device="cuda") * 0.3).bfloat16()
+        bias = (torch.randn(cdim, device="cuda") * 0.1).bfloat16()
+        conv = (torch.randn(6, cdim, 3, device="cuda") * 0.5).bfloat16()
+        ssm = torch.randn(6, h, p, n, device="cuda") * 0.3
+        a_log = torch.log(torch.empty(h, device="cuda").uniform_(1, 8))
+        dsk, dtb = torch.randn(h, device="cuda"), torch.randn(h, device="cuda") * 0.5
+        nw = (1 + 0.1 * torch.randn(inter, device="cuda")).bfloat16()
+        conv_c, ssm_c = conv.cpu().clone(), ssm.cpu().clone()
+        xbc = K.gdn_conv1d(proj[:, inter:inter + cdim], w, conv, cu, slots, has, bias)
+        dt = proj[:, inter + cdim:]
+        y = K.mamba2_scan(xbc, dt, a_log, dsk, dtb, ssm, cu, slots, has, h, g, p, n, 0.001)
+        o = K.rms_norm_gate_first(y.reshape(t, inter), proj[:, :inter], nw, 1e-5, inter // g)
+        torch.cuda.synchronize()
+        pc = proj.cpu()
+        xbc_c = R.causal_conv1d(pc[:, inter:inter + cdim].contiguous(), w.cpu(), conv_c, cu.cpu(), slots.cpu(),
+                                has.cpu(), bias.cpu())
+        _close(xbc.cpu(), xbc_c, 2e-2, 2e-2, "conv with bias")
+        assert torch.equal(conv.cpu(), conv_c)
+        xs, bb, cc = xbc.cpu().split([inter, g * n, g * n], dim=-1)     # the kernel's own conv output as input
+        y_c = R.mamba2_scan(xs.reshape(t, h, p), pc[:, inter + cdim:], bb.reshape(t, g, n), cc.reshape(t, g, n),
+                            a_log.cpu(), dsk.cpu(), dtb.cpu(), ssm_c, cu.cpu(), slots.cpu(), has.cpu(), 0.001)
+        _close(y.cpu(), y_c, 3e-2, 3e-2 * float(y_c.float().abs().max()), f"scan output {h, p, n}")
+        _close(ssm.cpu(), ssm_c, 1e-3, 1e-3 * float(ssm_c.abs().max()), "scan state")
+        o_c = R.rms_norm_gate_first(y.cpu().reshape(t, inter), pc[:, :inter], nw.cpu(), 1e-5, inter // g)
+        _close(o.cpu(), o_c, 2e-2, 2e-2, "gate-first norm")
+    x = torch.randn(33, 256, device="cuda").bfloat16()
+    assert torch.equal(K.relu2(x).cpu(), R.relu2(x.cpu()))
+
+
 # ------------------------------------------------------------------------------------------ 4-bit-resident GEMM
 @pytest.mark.parametrize("m,n,k,group", [(1, 256, 256, 128), (77, 1032, 512, 32), (300, 384, 1024, 64)])
 def test_gemm_w4a16_int4_dialects(K, m, n, k, group):

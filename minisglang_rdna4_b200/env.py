@@ -143,6 +143,9 @@ ENV.str("NVLS", "auto", "decode all-reduce by in-switch reduction (multimem): au
         "stores at 2 and 4 ranks), on, off")
 ENV.int("SYMM_HEAP_MIB", 256, "size of the per-rank symmetric peer-memory heap")
 ENV.int("ONESHOT_AR_MAX_KIB", 512, "messages up to this size use the one-shot all-reduce; larger ones go to the row-sharded GEMM fusion or to NCCL")
+ENV.int("RECURRENT_SNAPSHOT_MIB", 2048, "memory for recurrent-state snapshots (prefix reuse of hybrid models); 0 = no "
+        "prefix reuse for models with recurrent layers")
+ENV.int("RECURRENT_SNAPSHOT_TOKENS", 512, "a running request's recurrent state is kept every this many tokens")
 ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-loop detector looks for; 0 = off")
 ENV.int("THINK_LOOP_SPAN", 48, "a reasoning loop is reported once this many consecutive tokens repeat")
 ENV.int("THINK_LOOP_REPS", 3, "... and the block has repeated this many times")

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from .base import BaseCacheHandle, BaseKVCachePool, BasePrefixCache, SizeInfo
 from .naive_cache import NaivePrefixCache
-from .radix_cache import RadixPrefixCache
+from .radix_cache import RadixPrefixCache, SnapshotRadixCache
 from .mha_pool import MHAKVCache
 
 
@@ -11,6 +11,8 @@ def create_prefix_cache(kind: str, page_size: int) -> BasePrefixCache:
     """``radix`` or ``naive`` (python/minisgl/kvcache/__init__.py:60-101)."""
     if kind == "radix":
         return RadixPrefixCache(page_size)
+    if kind == "radix_snapshot":
+        return SnapshotRadixCache(page_size)
     if kind == "naive":
         return NaivePrefixCache(page_size)
     raise ValueError(f"unknown cache type {kind!r}")
@@ -23,6 +25,7 @@ __all__ = [
     "SizeInfo",
     "NaivePrefixCache",
     "RadixPrefixCache",
+    "SnapshotRadixCache",
     "MHAKVCache",
     "create_prefix_cache",
 ]

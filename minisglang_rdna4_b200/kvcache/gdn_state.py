@@ -21,7 +21,7 @@ class GDNStateCache:
         self.conv = torch.zeros((num_layers, num_slots, conv_dim, conv_kernel - 1), dtype=dtype, device=device)
         self.ssm = torch.zeros((num_layers, num_slots, num_v_heads, head_k_dim, head_v_dim), dtype=torch.float32,
                                device=device)
-        self._snapshots: Dict[Tuple[int, ...], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._snapshots: Dict[object, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     @staticmethod
     def slot_bytes(num_layers: int, conv_dim: int, conv_kernel: int, num_v_heads: int, dk: int, dv: int,
@@ -35,13 +35,17 @@ class GDNStateCache:
         return self.ssm[layer]
 
     # ---- snapshots: the state of one slot after exactly ``key`` tokens ----
-    def snapshot(self, slot: int, key: Tuple[int, ...], host: bool = True) -> None:
+    def slot_nbytes(self) -> int:
+        """Bytes of one request's state over all recurrent layers (= the size of a snapshot)."""
+        return int(self.conv[:, 0].numel() * self.conv.element_size() + self.ssm[:, 0].numel() * 4)
+
+    def snapshot(self, slot: int, key, host: bool = True) -> None:
         conv, ssm = self.conv[:, slot].clone(), self.ssm[:, slot].clone()
         if host and conv.is_cuda:
             conv, ssm = conv.to("cpu", non_blocking=True), ssm.to("cpu", non_blocking=True)
         self._snapshots[key] = (conv, ssm)
 
-    def restore(self, slot: int, key: Tuple[int, ...]) -> bool:
+    def restore(self, slot: int, key) -> bool:
         snap = self._snapshots.get(key)
         if snap is None:
             return False
@@ -49,7 +53,7 @@ class GDNStateCache:
         self.ssm[:, slot].copy_(snap[1], non_blocking=True)
         return True
 
-    def drop_snapshot(self, key: Tuple[int, ...]) -> None:
+    def drop_snapshot(self, key) -> None:
         self._snapshots.pop(key, None)
 
     @property

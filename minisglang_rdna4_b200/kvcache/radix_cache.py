@@ -12,6 +12,7 @@ a query and a node key runs in the native host library when it is built.
 from __future__ import annotations
 
 import heapq
+import collections
 import itertools
 import time
 from dataclasses import dataclass
@@ -25,7 +26,7 @@ from ..ops.host import common_prefix_len
 
 
 class RadixNode:
-    __slots__ = ("key", "pages", "children", "parent", "ref", "stamp", "uid")
+    __slots__ = ("key", "pages", "children", "parent", "ref", "stamp", "uid", "snap")
     _uids = itertools.count()
 
     def __init__(self, key: np.ndarray, pages: np.ndarray, parent: Optional["RadixNode"]) -> None:
@@ -36,6 +37,7 @@ class RadixNode:
         self.ref = 0
         self.stamp = time.monotonic_ns()
         self.uid = next(RadixNode._uids)
+        self.snap: Optional[int] = None   # id of a recurrent-state snapshot taken exactly at this node's end
 
     @property
     def is_leaf(self) -> bool:
@@ -49,6 +51,7 @@ class RadixNode:
 @dataclass
 class RadixHandle(BaseCacheHandle):
     node: RadixNode = None  # type: ignore[assignment]
+    snap: Optional[int] = None      # recurrent-state snapshot to restore for this prefix
 
 
 class RadixPrefixCache(BasePrefixCache):
@@ -180,6 +183,8 @@ class RadixPrefixCache(BasePrefixCache):
             if node.parent.children.get(self._child_key(node.key)) is not node:
                 continue
             del node.parent.children[self._child_key(node.key)]
+            if node.snap is not None:
+                self._drop_snapshot(node)
             freed.append(node.pages)
             got += len(node.pages)
             self._evictable -= len(node.pages)
@@ -188,6 +193,9 @@ class RadixPrefixCache(BasePrefixCache):
             if not parent.is_root and parent.is_leaf and parent.ref == 0:
                 heapq.heappush(self._heap, (parent.stamp, parent.uid, parent))
         return torch.from_numpy(np.concatenate(freed))
+
+    def _drop_snapshot(self, node: RadixNode) -> None:
+        node.snap = None
 
     def _rebuild_heap(self) -> None:
         self._heap = []
@@ -227,3 +235,74 @@ class RadixPrefixCache(BasePrefixCache):
                 protected += len(node.pages)
         assert evictable == self._evictable, (evictable, self._evictable)
         assert protected == self._protected, (protected, self._protected)
+
+
+class SnapshotRadixCache(RadixPrefixCache):
+    """Prefix cache for models with recurrent layers (gated delta net, Mamba-2). Their per-request
+    state is a running summary that cannot be cut at an arbitrary length, so a cached prefix is
+    only reusable up to a boundary at which a snapshot of the state was taken. Nodes whose end
+    coincides with such a boundary carry the snapshot's id; ``match_prefix`` returns the deepest
+    matched boundary that has one, and the K/V pages of the attention layers up to it
+    (python/minisgl/kvcache/radix_cache.py:119-423, python/minisgl/kvcache/composite_state.py:24).
+
+    ``on_drop(id)`` is called when a snapshot leaves the cache (its node was evicted, replaced, or the
+    ``capacity`` was reached and it was the least recently used)."""
+
+    def __init__(self, page_size: int, capacity: int = 64, on_drop=None) -> None:
+        self.capacity = max(int(capacity), 1)
+        self.on_drop = on_drop
+        self._lru: "collections.OrderedDict[int, RadixNode]" = collections.OrderedDict()
+        super().__init__(page_size)
+
+    def reset(self) -> None:
+        for key in list(getattr(self, "_lru", {})):
+            if self.on_drop is not None:
+                self.on_drop(key)
+        self._lru = collections.OrderedDict()
+        super().reset()
+
+    def _drop_snapshot(self, node: RadixNode) -> None:
+        key, node.snap = node.snap, None
+        if key is not None and self._lru.pop(key, None) is not None and self.on_drop is not None:
+            self.on_drop(key)
+
+    def match_prefix(self, input_ids: torch.Tensor) -> Tuple[RadixHandle, torch.Tensor]:
+        ids = self._as_np(input_ids)
+        node, matched = self._walk(ids)
+        while not node.is_root and node.snap is None:      # back up to a boundary whose state is known
+            matched -= len(node.key)
+            node = node.parent  # type: ignore[assignment]
+        pages: List[np.ndarray] = []
+        cur = node
+        while not cur.is_root:
+            pages.append(cur.pages)
+            cur = cur.parent  # type: ignore[assignment]
+        pages.reverse()
+        flat = np.concatenate(pages) if pages else np.empty(0, dtype=np.int32)
+        if node.snap is not None:
+            self._lru.move_to_end(node.snap)
+        return RadixHandle(matched, node, node.snap), torch.from_numpy(flat.copy())
+
+    def attach_snapshot(self, input_ids: torch.Tensor, length: int, key: int) -> bool:
+        """Mark the cached prefix of exactly ``length`` tokens (a page multiple) with snapshot ``key``.
+        False when that prefix is not in the cache; the caller then drops the snapshot."""
+        if length <= 0 or length % self.page_size:
+            return False
+        ids = self._as_np(input_ids)[:length]
+        if len(ids) < length:
+            return False
+        node, matched = self._walk(ids)        # splits the node that spans the boundary
+        if matched != length or node.is_root:
+            return False
+        if node.snap is not None:
+            self._drop_snapshot(node)
+        node.snap = key
+        self._lru[key] = node
+        while len(self._lru) > self.capacity:
+            _old, victim = next(iter(self._lru.items()))
+            self._drop_snapshot(victim)
+        return True
+
+    @property
+    def num_snapshots(self) -> int:
+        return len(self._lru)

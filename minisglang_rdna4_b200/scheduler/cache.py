@@ -114,7 +114,7 @@ class CacheManager:
         return (self.page_table[slot, pos // self.page_size].astype(np.int64) * self.page_size
                 + pos % self.page_size).astype(np.int32)
 
-    def finish_req(self, req: Req, allocated_len: int, insert: bool = True) -> None:
+    def finish_req(self, req: Req, allocated_len: int, insert: bool = True, snapshots=None) -> list:
         """Return a finished request's pages: insert the page-aligned prefix of what was
         computed into the prefix cache, free pages that duplicate already-cached ones, free
         the unaligned tail, unlock the matched handle
@@ -141,7 +141,15 @@ class CacheManager:
             keep_pages = old_prefix_pages
         if n_alloc_pages > keep_pages:
             self._give(pages[keep_pages:n_alloc_pages])
+        # recurrent models: state snapshots taken while the request ran become reusable prefix
+        # boundaries; the ids of those that found no place in the cache go back to the caller
+        unused = []
+        attach = getattr(self.prefix_cache, "attach_snapshot", None)
+        for length, key in (snapshots or ()):
+            if attach is None or length > keep_pages * ps or not attach(ids, int(length), key):
+                unused.append(key)
         self.unlock(handle)
+        return unused
 
     def check_integrity(self) -> None:
         self.prefix_cache.check_integrity()

@@ -48,6 +48,7 @@ class PrefillAdder:
         self.table = table
         self.others_waiting = others_waiting
         self.new_slots: List[Tuple[int, torch.Tensor, int]] = []  # (slot, prompt ids, cached_len)
+        self.restores: List[Tuple[int, int]] = []                 # (slot, recurrent-state snapshot id)
 
     def _chunk(self, remain: int) -> int:
         chunk = min(self.token_budget, remain)
@@ -83,9 +84,15 @@ class PrefillAdder:
             self.cache.prefix_hit_tokens += cached
             self.cache.prefix_query_tokens += pending.input_len
             self.new_slots.append((slot, pending.input_ids, cached))
+            if getattr(handle, "snap", None) is not None:
+                self.restores.append((slot, handle.snap))     # recurrent state to copy into the slot
             self.reserved += need
         remain = pending.input_len - cached
         chunk = self._chunk(remain)
+        if chunk < remain and (cached + chunk) % ps and chunk > (cached + chunk) % ps:
+            # a chunk that is not the last ends on a page boundary: recurrent-state snapshots and the
+            # prefix cache work in whole pages
+            chunk -= (cached + chunk) % ps
         self.token_budget -= chunk
         final = chunk == remain
         cls = Req if final else ChunkedReq

@@ -55,14 +55,30 @@ class Scheduler:
         eng = self.engine
         self.page_size = eng.page_size
         self.table = TableManager(config.max_running_req)
-        # A recurrent state cannot be rewound to a matched prefix: hybrid models admit every request
-        # with an empty prefix (python/minisgl/engine/config.py:75-133 resolves the same way when
-        # the recurrent-snapshot cache is off).
-        cache_type = "naive" if eng.model_config.is_recurrent else config.cache_type
+        # A recurrent state cannot be rewound to a matched prefix: hybrid models reuse a cached prefix
+        # only up to a boundary at which a snapshot of the state was taken (the snapshot radix cache),
+        # or admit every request with an empty prefix when snapshots are off
+        # (python/minisgl/engine/config.py:75-133).
+        cache_type = config.cache_type
+        self._snap_pending: Dict[int, List] = {}
+        self._snap_ids = 0
+        self._snapshots_on = False
+        if eng.model_config.is_recurrent:
+            self._snapshots_on = (cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0
+                                  and eng.gdn_state is not None)
+            cache_type = "radix_snapshot" if self._snapshots_on else "naive"
         if eng.model_config.is_recurrent and config.spec_algorithm != "none":
             raise ValueError("speculative decoding is not available for models with recurrent layers")
         self.cache = CacheManager(eng.num_pages, eng.page_size, eng.num_slots, eng.max_pages_per_seq,
                                   cache_type)
+        if self._snapshots_on:
+            pc = self.cache.prefix_cache
+            pc.capacity = max(4, (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(eng.gdn_state.slot_nbytes(), 1))
+            pc.on_drop = eng.gdn_state.drop_snapshot
+            every = max(ENV.RECURRENT_SNAPSHOT_TOKENS.value, eng.page_size)
+            self._snap_every = (every + eng.page_size - 1) // eng.page_size * eng.page_size
+            logger.info_rank0("recurrent-state snapshots: every %d tokens and at chunk ends, up to %d kept (%.1f MiB each)",
+                              self._snap_every, pc.capacity, eng.gdn_state.slot_nbytes() / 2 ** 20)
         self.decode = DecodeManager(eng.page_size)
         self.prefill = PrefillManager(self.cache, self.table, self.decode)
         self.max_seq_len = eng.max_seq_len
@@ -157,6 +173,8 @@ class Scheduler:
         batch, adder = self.prefill.schedule_next_batch(self._prefill_budget_now())
         if batch is not None:
             self._upload_prompts(adder.new_slots)
+            if adder.restores:
+                self._restore_states(adder.restores)
             for req in batch.reqs:
                 self.reqs[req.uid] = req
                 self.prefix_len.setdefault(req.uid, req.cached_len)
@@ -177,6 +195,49 @@ class Scheduler:
         else:
             for slot, ids, _cached in new_slots:
                 pool[slot, : ids.numel()].copy_(ids)
+
+    def _restore_states(self, restores) -> None:
+        """Prefix hits of a recurrent model: copy the snapshot of each matched boundary into the
+        request's state slot, on the engine's stream ahead of the forward that continues from it."""
+        st = self.engine.gdn_state
+        if self.engine.device.type == "cuda":
+            with torch.cuda.stream(self.engine.stream):
+                for slot, key in restores:
+                    st.restore(slot, key)
+        else:
+            for slot, key in restores:
+                st.restore(slot, key)
+
+    def _snapshot_states(self, batch: Batch, ends) -> None:
+        """After a step was launched: keep the recurrent state of every request that has just reached
+        a reusable boundary (a page multiple at the end of a prefill chunk, or every
+        ``MSGL_RECURRENT_SNAPSHOT_TOKENS`` tokens). The copies are ordered behind the step on the
+        engine's stream; the ids are attached to the prefix cache when the request finishes."""
+        st = self.engine.gdn_state
+        todo = []
+        for r, end in zip(batch.reqs, ends):
+            if end % self.page_size:
+                continue
+            if isinstance(r, ChunkedReq) or end % self._snap_every == 0:
+                todo.append((r, int(end)))
+        if not todo:
+            return
+
+        def take():
+            for r, end in todo:
+                self._snap_ids += 1
+                st.snapshot(r.table_idx, self._snap_ids, host=False)
+                pend = self._snap_pending.setdefault(r.uid, [])
+                pend.append((end, self._snap_ids))
+                if len(pend) > 6:                      # keep the earliest (shared prompts) and the latest
+                    _, old = pend.pop(3)
+                    st.drop_snapshot(old)
+
+        if self.engine.device.type == "cuda":
+            with torch.cuda.stream(self.engine.stream):
+                take()
+        else:
+            take()
 
     def _make_plan(self, batch: Batch, extra_rows: int = 0) -> StepPlan:
         """Allocate pages and build the step's index arrays. ``extra_rows`` > 0 plans a
@@ -235,6 +296,8 @@ class Scheduler:
         args = self.engine.sampler.prepare(sampled) if sampled else BatchSamplingArgs()
         self._attach_constraints(sampled, args)
         out = self.engine.forward_batch(batch, plan, args)
+        if self._snapshots_on:
+            self._snapshot_states(batch, plan.seq_lens.tolist())
         n_tok = plan.num_tokens
         if batch.is_prefill:
             self.stats["prefill_tokens"] += n_tok
@@ -447,7 +510,9 @@ class Scheduler:
         alloc = self.alloc_len.pop(req.uid, req.cache_handle.cached_len)
         # KV is valid for tokens that were both fed and known on the host
         req.cached_len = min(req.cached_len, int(req.input_ids.numel()))
-        self.cache.finish_req(req, alloc, insert=insert)
+        unused = self.cache.finish_req(req, alloc, insert=insert, snapshots=self._snap_pending.pop(req.uid, None))
+        for key in unused or ():
+            self.engine.gdn_state.drop_snapshot(key)
         self.table.free(req.table_idx)
         self._forget_constraints(req.uid)
         self.reqs.pop(req.uid, None)

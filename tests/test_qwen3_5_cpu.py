@@ -103,3 +103,43 @@ def test_gdn_reference_ops_match_transformers_kernels():
     y1 = ref.causal_conv1d(x[:10], w, conv_state, torch.tensor([0, 10]), z, z)
     y2 = ref.causal_conv1d(x[10:], w, conv_state, torch.tensor([0, 27]), z, torch.tensor([1]))
     assert torch.allclose(torch.cat([y1, y2]), want, atol=1e-5)
+
+
+def test_recurrent_model_reuses_a_prefix_through_state_snapshots(monkeypatch):
+    """A hybrid model can take a prefix-cache hit only at a boundary whose recurrent state was kept.
+    Snapshots are taken at page-aligned chunk ends and every N tokens; a later request that shares
+    the prefix starts from the deepest such boundary, and generates exactly what it generates
+    without any reuse."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    with tempfile.TemporaryDirectory() as tmp:
+        _hf_model(tmp)
+        g = torch.Generator().manual_seed(5)
+        shared = torch.randint(0, 298, (100,), generator=g).tolist()
+        first = shared + torch.randint(0, 298, (9,), generator=g).tolist()
+        second = shared + torch.randint(0, 298, (21,), generator=g).tolist()
+        third = first + [7, 8, 9]                                # a follow-up turn of the first request
+        sp = SamplingParams(max_tokens=6, ignore_eos=True)
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=48)
+        monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "0")
+        plain = LLM(**kw)
+        assert type(plain.cache.prefix_cache).__name__ == "NaivePrefixCache"
+        want = [plain.generate([p], sp)[0].token_ids for p in (first, second, third)]
+        plain.shutdown()
+        monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "64")
+        monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_TOKENS", "32")
+        llm = LLM(**kw)
+        assert type(llm.cache.prefix_cache).__name__ == "SnapshotRadixCache"
+        outs = [llm.generate([p], sp)[0] for p in (first, second, third)]
+        assert [o.token_ids for o in outs] == want
+        assert outs[0].cached_tokens == 0
+        # the shared 100 tokens end inside a page; the deepest kept boundary below them is 96
+        assert outs[1].cached_tokens == 96, outs[1].cached_tokens
+        # the follow-up turn continues from a boundary inside the first request's own output
+        assert outs[2].cached_tokens >= 96
+        assert llm.cache.prefix_cache.num_snapshots > 0
+        assert llm.engine.gdn_state.num_snapshots == llm.cache.prefix_cache.num_snapshots
+        llm.cache.check_integrity()
+        llm.shutdown()

@@ -208,6 +208,7 @@ class Engine:
             from ..kvcache.gdn_state import GDNStateCache
 
             conv_dim, st_heads, st_rows, st_cols = mc.recurrent_geometry
+            conv_dim, st_heads = conv_dim // config.tp_size, st_heads // config.tp_size   # this rank's heads
             self.gdn_state = GDNStateCache(mc.num_linear_layers, self.num_slots, conv_dim, mc.linear_conv_kernel_dim,
                                            st_heads, st_rows, st_cols, self.dtype, self.device)
             self.ledger.add("recurrent state", self.gdn_state.conv.numel() * self.gdn_state.conv.element_size()
@@ -414,6 +415,7 @@ class Engine:
             from ..kvcache.gdn_state import GDNStateCache
 
             conv_dim, st_heads, st_rows, st_cols = mc.recurrent_geometry
+            conv_dim, st_heads = conv_dim // cfg.tp_size, st_heads // cfg.tp_size
             budget -= (cfg.max_running_req + 1) * GDNStateCache.slot_bytes(
                 mc.num_linear_layers, conv_dim, mc.linear_conv_kernel_dim, st_heads, st_rows, st_cols, 2)
         pages = budget // per_page

@@ -35,11 +35,12 @@ from .transformer import _scheme
 
 class Mamba2Mixer(BaseOP):
     def __init__(self, cfg: ModelConfig, state_id: int, dtype, device, prefix: str) -> None:
-        if get_tp_info().size > 1:
-            raise NotImplementedError("Mamba-2 layers run with tensor-parallel size 1")
+        # tensor parallelism: heads and B / C groups are split evenly over the ranks (the grouped norm never
+        # crosses a group), every rank keeps the state of its own heads, the output projection sums
+        tp = get_tp_info().size
         self._state_id = state_id
-        self._h, self._p, self._n, self._g = (cfg.mamba_num_heads, cfg.mamba_head_dim, cfg.ssm_state_size,
-                                              cfg.mamba_n_groups)
+        self._h, self._p, self._n, self._g = (div_even(cfg.mamba_num_heads, tp), cfg.mamba_head_dim,
+                                              cfg.ssm_state_size, div_even(cfg.mamba_n_groups, tp))
         self._inter = self._h * self._p
         self._conv_dim = self._inter + 2 * self._g * self._n
         self._eps = cfg.rms_norm_eps
@@ -55,7 +56,7 @@ class Mamba2Mixer(BaseOP):
         self.A_log = torch.empty((self._h,), dtype=torch.float32, device=device)
         self.D = torch.empty((self._h,), dtype=torch.float32, device=device)
         self.norm_weight = torch.empty((self._inter,), dtype=dtype, device=device)
-        self.out_proj = RowParallelLinear(self._inter, cfg.hidden_size, dtype, device,
+        self.out_proj = RowParallelLinear(cfg.mamba_num_heads * self._p, cfg.hidden_size, dtype, device,
                                           _scheme(cfg, prefix + ".out_proj"), bias=cfg.mamba_proj_bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -66,11 +66,11 @@ class GatedAttention(BaseOP):
 
 class GatedDeltaNet(BaseOP):
     def __init__(self, cfg: ModelConfig, gdn_id: int, dtype, device, prefix: str) -> None:
+        # tensor parallelism: key and value heads are split evenly over the ranks (a value head stays with
+        # its key head), every rank keeps the state of its own heads, the output projection sums
         tp = get_tp_info().size
-        if tp > 1:
-            raise NotImplementedError("gated-delta-net layers run with tensor-parallel size 1")
         self._gdn_id = gdn_id
-        self._hk, self._hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self._hk, self._hv = div_even(cfg.linear_num_key_heads, tp), div_even(cfg.linear_num_value_heads, tp)
         self._dk, self._dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self._key_dim, self._value_dim = self._hk * self._dk, self._hv * self._dv
         self._conv_dim = 2 * self._key_dim + self._value_dim
@@ -86,7 +86,7 @@ class GatedDeltaNet(BaseOP):
         self.dt_bias = torch.empty((self._hv,), dtype=torch.float32, device=device)
         self.A_log = torch.empty((self._hv,), dtype=torch.float32, device=device)
         self.norm_weight = torch.empty((self._dv,), dtype=dtype, device=device)
-        self.out_proj = RowParallelLinear(self._value_dim, cfg.hidden_size, dtype, device,
+        self.out_proj = RowParallelLinear(cfg.linear_num_value_heads * self._dv, cfg.hidden_size, dtype, device,
                                           _scheme(cfg, prefix + ".out_proj"))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -120,6 +120,18 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             return _slice(t, k_dim, tp.rank, tp.size)
         return t
 
+    def shard_segments(t: torch.Tensor, sizes) -> torch.Tensor:
+        """Rows of ``t`` are consecutive segments of ``sizes`` rows (q | k | v ..., one per head group);
+        this rank's equal share of every segment, concatenated in the same order."""
+        if tp.size == 1:
+            return t
+        parts, off = [], 0
+        for n in sizes:
+            per = n // tp.size
+            parts.append(t[off + tp.rank * per: off + (tp.rank + 1) * per])
+            off += n
+        return torch.cat(parts)
+
     def vocab_shard(t: torch.Tensor, per_rank: int) -> torch.Tensor:
         start = tp.rank * per_rank
         rows = t[start : start + per_rank]
@@ -149,19 +161,25 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                 mixer = modules.get(block + ".mixer")
                 if mixer is None:
                     continue
+                m_inter = cfg.mamba_num_heads * cfg.mamba_head_dim
+                m_gn = cfg.mamba_n_groups * cfg.ssm_state_size
                 if tail == "conv1d.weight":
-                    assign(mixer, "conv1d_weight", tensor.reshape(tensor.shape[0], -1), block + ".mixer.conv1d_weight")
+                    assign(mixer, "conv1d_weight",
+                           shard_segments(tensor.reshape(tensor.shape[0], -1), [m_inter, m_gn, m_gn]),
+                           block + ".mixer.conv1d_weight")
                     continue
                 if tail == "conv1d.bias":
-                    assign(mixer, "conv1d_bias", tensor, block + ".mixer.conv1d_bias")
+                    assign(mixer, "conv1d_bias", shard_segments(tensor, [m_inter, m_gn, m_gn]),
+                           block + ".mixer.conv1d_bias")
                     continue
                 if tail == "norm.weight":
-                    assign(mixer, "norm_weight", tensor, block + ".mixer.norm_weight")
+                    assign(mixer, "norm_weight", shard_segments(tensor, [m_inter]), block + ".mixer.norm_weight")
                     continue
                 if tail in ("dt_bias", "A_log", "D"):
-                    assign(mixer, tail, tensor.float(), block + ".mixer." + tail)
+                    assign(mixer, tail, shard_segments(tensor.float(), [cfg.mamba_num_heads]), block + ".mixer." + tail)
                     continue
                 if tail in ("in_proj.weight", "in_proj.bias") and hasattr(mixer, "in_proj"):
+                    tensor = shard_segments(tensor, [m_inter, m_inter, m_gn, m_gn, cfg.mamba_num_heads])
                     rows = getattr(mixer.in_proj, tail.split(".")[1]).shape[0]
                     if tensor.shape[0] < rows:      # the projection is padded to a multiple of 8 output columns
                         pad = torch.zeros((rows - tensor.shape[0],) + tuple(tensor.shape[1:]), dtype=tensor.dtype)
@@ -171,6 +189,8 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                 if tail in ("experts.up_proj", "experts.down_proj") and tensor.dim() == 3:
                     moe = mixer.experts
                     t3 = tensor[moe._e_start:moe._e_start + moe._e_local]
+                    if moe._ep is None and tp.size > 1:       # intermediate dimension split over the ranks
+                        t3 = _slice(t3, 1 if tail.endswith("up_proj") else 2, tp.rank, tp.size)
                     assign(moe, "w13" if tail.endswith("up_proj") else "w2", t3,
                            block + ".mixer.experts." + ("w13" if tail.endswith("up_proj") else "w2"))
                     continue
@@ -190,6 +210,9 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             if tail in ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight"):
                 part = ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight").index(tail)
                 key = block + ".linear_attn.in_proj.weight"
+                qk, vv, hv = cfg.linear_num_key_heads * cfg.linear_key_head_dim, \
+                    cfg.linear_num_value_heads * cfg.linear_value_head_dim, cfg.linear_num_value_heads
+                tensor = shard_segments(tensor, ([qk, qk, vv], [vv], [hv], [hv])[part])
                 col = pending.setdefault(key, _Collector(4))
                 if col.add(part, tensor):
                     w = col.cat(0)
@@ -199,11 +222,15 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                     assign(gdn.in_proj, "weight", w, key)
                     del pending[key]
             elif tail == "conv1d.weight":
-                assign(gdn, "conv1d_weight", tensor.reshape(tensor.shape[0], -1), block + ".linear_attn.conv1d_weight")
+                qk = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+                vv = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+                assign(gdn, "conv1d_weight", shard_segments(tensor.reshape(tensor.shape[0], -1), [qk, qk, vv]),
+                       block + ".linear_attn.conv1d_weight")
             elif tail == "norm.weight":
                 assign(gdn, "norm_weight", tensor, block + ".linear_attn.norm_weight")
             elif tail in ("dt_bias", "A_log"):
-                assign(gdn, tail, tensor.float(), block + ".linear_attn." + tail)
+                assign(gdn, tail, shard_segments(tensor.float(), [cfg.linear_num_value_heads]),
+                       block + ".linear_attn." + tail)
             elif tail == "out_proj.weight":
                 assign(gdn.out_proj, "weight", shard_linear(gdn.out_proj, "weight", tensor, "row", None), name)
             continue

@@ -26,9 +26,13 @@ def _worker(rank, world, port, ckpt, prompts, out_q, ep):
     from minisglang_rdna4_b200 import SamplingParams
     from minisglang_rdna4_b200.llm import LLM
 
-    llm = LLM(model_path=ckpt, device="cpu", tp_size=world, tp_rank=rank, page_size=16, max_running_req=4,
-              num_page_override=64, enable_ep=ep, dtype="fp32")
-    outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    try:
+        llm = LLM(model_path=ckpt, device="cpu", tp_size=world, tp_rank=rank, page_size=16, max_running_req=4,
+                  num_page_override=64, enable_ep=ep, dtype="fp32")
+        outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    except Exception as exc:                     # the parent must not wait out its timeout on a failed rank
+        out_q.put(f"rank {rank}: {type(exc).__name__}: {exc}")
+        raise
     if rank == 0:
         out_q.put([o.token_ids for o in outs])
     llm.shutdown()
@@ -146,3 +150,44 @@ def test_ranks_agree_on_a_collective_timeout_seen_by_one_rank():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == [(0, 0, 3), (1, 0, 3)]
+
+
+def _hybrid_ckpt(tmp, family):
+    import sys
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    if family == "qwen3_5":
+        from test_qwen3_5_cpu import _hf_model
+
+        _hf_model(tmp)
+    else:
+        from safetensors.torch import save_file
+        from test_nemotron_h_cpu import _hf_model
+
+        cfg, hf = _hf_model()
+        cfg.save_pretrained(tmp)
+        save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, f"{tmp}/model.safetensors")
+    return tmp
+
+
+@pytest.mark.parametrize("family", ["qwen3_5", "nemotron_h"])
+def test_hybrid_models_tp2_matches_tp1_on_cpu(family):
+    """Recurrent layers under tensor parallelism: heads (and the convolution channels, gates and state
+    that belong to them) are split over the ranks, the output projection sums."""
+    pytest.importorskip("transformers")
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (9, 21)]
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _hybrid_ckpt(tmp, family)
+        want = _single(ckpt, prompts)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 29800 + (os.getpid() % 1500) + (7 if family == "qwen3_5" else 11)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, False)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=300)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want

@@ -442,9 +442,11 @@ __global__ void __launch_bounds__(kRsThreads) rs_norm_ag_kernel(const RsArgs a) 
       }
     }
   }
-  // publish: the barrier orders the CTA's stores before thread 0; release / acquire at GPU scope
-  // chains the rows of the block, and the release stores of the CTA that completes the block
-  // publish everything system-wide
+  // publish: every thread first makes its own peer stores visible system-wide (a GPU-scope release
+  // does not wait for stores still on their way to another GPU); the barrier then orders them before
+  // thread 0, release / acquire at GPU scope chains the rows of the block, and the CTA that
+  // completes the block raises the flags
+  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     const uint32_t seen = atom_add_acq_rel_gpu(a.count + lblk, 1u);

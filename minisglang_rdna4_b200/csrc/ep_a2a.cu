@@ -109,9 +109,10 @@ __global__ void ep_dispatch_kernel(EpBuffers b, const T* __restrict__ x, const i
                                           ((size_t)b.rank * b.cap + s_slot[kk]) * b.hidden);
     for (int i = threadIdx.x; i < vecs; i += blockDim.x) out[i] = src[i];
   }
-  // last CTA publishes counts and flags (GPU-scope fences chain the CTAs; the release stores of
-  // the last one publish system-wide)
-  __threadfence();
+  // last CTA publishes counts and flags. Every CTA first makes its own peer stores visible
+  // system-wide: a GPU-scope fence does not wait for stores that are still on their way to another
+  // GPU, so the last CTA's flag could overtake a sibling CTA's rows on a different NVLink path.
+  __threadfence_system();
   __syncthreads();
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks], 1u) == gridDim.x - 1;
@@ -210,7 +211,7 @@ __global__ void ep_dispatch_quant_kernel(EpBuffers b, const T* __restrict__ x, c
       sc[threadIdx.x] = s_scale[threadIdx.x];
     }
   }
-  __threadfence();
+  __threadfence_system();   // this CTA's peer stores first (see ep_dispatch_kernel)
   __syncthreads();
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks], 1u) == gridDim.x - 1;
@@ -292,7 +293,7 @@ __global__ void ep_return_kernel(EpBuffers b, const T* __restrict__ y_sorted, co
                                           ((size_t)b.rank * b.cap + pos) * b.hidden);
     for (int i = threadIdx.x; i < b.hidden / 8; i += blockDim.x) out[i] = in[i];
   }
-  __threadfence();
+  __threadfence_system();   // this CTA's peer stores first (see ep_dispatch_kernel)
   __syncthreads();
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_last = atomicAdd(&state[b.nranks + 2], 1u) == gridDim.x - 1;

@@ -32,19 +32,27 @@ def _dummy_step(sched) -> None:
 
 
 def ep_lockstep_loop(sched) -> None:
+    from .scheduler import RequestAllFinished
+
     eng = sched.engine
     group = eng.dp_cpu_group
     ep = eng.ctx.ep
     idle_rounds = 0
+    local_done = False
     while True:
-        has_local = sched.has_work
-        for msg in sched.receive_msg(blocking=False):
-            sched._process_one_msg(msg)
+        # a replica whose own requests are all finished keeps stepping with the others (their tokens
+        # may be routed to its experts) until every replica agrees that nothing is left
+        try:
+            for msg in ([] if local_done else sched.receive_msg(blocking=False)):
+                sched._process_one_msg(msg)
+        except RequestAllFinished:
+            local_done = True
         batch = sched._schedule_next_batch()
         tokens = 0
         if batch is not None:
             tokens = sum(r.extend_len for r in batch.reqs)
-        agree = torch.tensor([tokens, 1 if sched._exit else 0, 1 if (sched.has_work or batch is not None) else 0],
+        agree = torch.tensor([tokens, 1 if sched._exit else 0,
+                              1 if ((sched.has_work or batch is not None) and not (local_done and batch is None)) else 0],
                              dtype=torch.int64)
         dist.all_reduce(agree, op=dist.ReduceOp.MAX, group=group)
         common, any_exit, any_work = int(agree[0]), int(agree[1]), int(agree[2])

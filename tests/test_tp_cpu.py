@@ -85,7 +85,8 @@ def _dp_worker(rank, world, port, ckpt, prompts_by_rank, out_q):
 
     llm = LLM(model_path=ckpt, device="cpu", dp_size=world, dp_rank=rank, page_size=16, max_running_req=4,
               num_page_override=64, enable_ep=True, dtype="fp32")
-    outs = llm.generate(prompts_by_rank[rank], SamplingParams(max_tokens=5, ignore_eos=True))
+    # replica 1 is done after two tokens and has to stay in step with replica 0 until that one is done too
+    outs = llm.generate(prompts_by_rank[rank], SamplingParams(max_tokens=6 if rank == 0 else 2, ignore_eos=True))
     out_q.put((rank, [o.token_ids for o in outs], llm.engine.ctx.ep.calls))
     llm.shutdown()
 
@@ -102,7 +103,8 @@ def test_dp2_expert_parallel_lockstep_matches_single_replica():
         from minisglang_rdna4_b200.llm import LLM
 
         llm = LLM(model_path=ckpt, device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
-        want = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))]
+        want = [o.token_ids for o in llm.generate(prompts[:2], SamplingParams(max_tokens=6, ignore_eos=True))]
+        want += [o.token_ids for o in llm.generate(prompts[2:], SamplingParams(max_tokens=2, ignore_eos=True))]
         ctx = mp.get_context("spawn")
         q = ctx.Queue()
         port = 29900 + os.getpid() % 1000

@@ -33,6 +33,7 @@ class BatchSamplingArgs:
     bitmask: Optional[torch.Tensor] = None        # [bs, ceil(V/32)] int32 allowed-token bits
     bitmask_rows: Optional[torch.Tensor] = None
     generators: Optional[List[Optional[torch.Generator]]] = None
+    seeded_uniform: Optional[torch.Tensor] = None  # [bs] draw of every request that carries a seed, NaN elsewhere
 
     @property
     def greedy(self) -> bool:
@@ -71,6 +72,15 @@ class Sampler:
                 args.top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32).to(dev, non_blocking=True)
             if any(p.min_p > 0.0 for p in params):
                 args.min_p = torch.tensor([p.min_p for p in params], dtype=torch.float32).to(dev, non_blocking=True)
+            if any(p.seed is not None for p in params):
+                # a request with a seed draws u = f(seed, index of the token): the same request gives the
+                # same text whatever it is batched with (python/minisgl/engine/sample.py, per-request seed)
+                import numpy as np
+
+                u = [float("nan") if p.seed is None else
+                     float(np.random.default_rng([int(p.seed) & 0x7FFFFFFF, r.num_generated]).random())
+                     for p, r in zip(params, reqs)]
+                args.seeded_uniform = torch.tensor(u, dtype=torch.float32).to(dev, non_blocking=True)
         pen = [i for i, p in enumerate(params) if p.has_penalty and reqs[i].num_generated > 0]
         if pen:
             width = max(reqs[i].num_generated for i in pen)
@@ -116,8 +126,13 @@ class Sampler:
         if args.greedy:
             out.tokens = ops.argmax(logits)
         else:
+            uniform = None
+            if args.seeded_uniform is not None:
+                uniform = torch.rand((logits.shape[0],), dtype=torch.float32, device=logits.device,
+                                     generator=self.generator)
+                uniform = torch.where(torch.isnan(args.seeded_uniform), uniform, args.seeded_uniform)
             out.tokens = ops.sample(logits, args.temperatures, args.top_k, args.top_p, args.min_p,
-                                    generator=self.generator)
+                                    generator=self.generator, uniform=uniform)
         if args.logprobs > 0:
             out.logprobs = lp.gather(-1, out.tokens.long()[:, None]).squeeze(-1)
         return out

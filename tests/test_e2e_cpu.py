@@ -69,3 +69,28 @@ def test_tiny_llama_matches_dense_oracle_and_hits_prefix_cache():
     info = llm.cache.prefix_cache.size_info
     assert llm.cache.free_pages + info.total_pages == llm.cache.num_pages
     assert info.protected_pages == 0
+
+
+def test_a_seeded_request_is_reproducible_whatever_it_is_batched_with():
+    """``seed`` pins a sampled request's draws to (seed, token index): alone or beside other
+    requests it generates the same tokens; without a seed two runs differ."""
+    from minisglang_rdna4_b200 import LLM, SamplingParams
+    from minisglang_rdna4_b200.models.config import tiny_llama_config
+
+    llm = LLM(model_config=tiny_llama_config(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=128, seed=0)
+    try:
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (12, 30, 7)]
+        sp = SamplingParams(temperature=1.5, max_tokens=12, ignore_eos=True, seed=1234)
+        free = SamplingParams(temperature=1.5, max_tokens=12, ignore_eos=True)
+        alone = llm.generate([prompts[0]], sp)[0].token_ids
+        again = llm.generate([prompts[0]], sp)[0].token_ids
+        mixed = llm.generate([prompts[1], prompts[0], prompts[2]], [free, sp, free])[1].token_ids
+        assert alone == again == mixed
+        other = llm.generate([prompts[0]], SamplingParams(temperature=1.5, max_tokens=12, ignore_eos=True, seed=99))
+        assert other[0].token_ids != alone
+        a, b = llm.generate([prompts[0]], free)[0].token_ids, llm.generate([prompts[0]], free)[0].token_ids
+        assert a != b
+    finally:
+        llm.shutdown()

@@ -18,7 +18,7 @@ def _cfg_dict(moe=False):
     return d
 
 
-def _worker(rank, world, port, ckpt, prompts, out_q, ep):
+def _worker(rank, world, port, ckpt, prompts, out_q, ep, extra=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["RANK"] = str(rank)
@@ -28,7 +28,7 @@ def _worker(rank, world, port, ckpt, prompts, out_q, ep):
 
     try:
         llm = LLM(model_path=ckpt, device="cpu", tp_size=world, tp_rank=rank, page_size=16, max_running_req=4,
-                  num_page_override=64, enable_ep=ep, dtype="fp32")
+                  num_page_override=64, enable_ep=ep, dtype="fp32", **(extra or {}))
         outs = llm.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
     except Exception as exc:                     # the parent must not wait out its timeout on a failed rank
         out_q.put(f"rank {rank}: {type(exc).__name__}: {exc}")
@@ -186,6 +186,30 @@ def test_hybrid_models_tp2_matches_tp1_on_cpu(family):
         q = ctx.Queue()
         port = 29800 + (os.getpid() % 1500) + (7 if family == "qwen3_5" else 11)
         procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, False)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=300)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want
+
+
+def test_speculative_decoding_under_tp2_matches_plain_tp1_on_cpu():
+    """Drafts are proposed from the token history, which is identical on all tensor-parallel ranks,
+    and the verified arg-max ids are agreed across ranks: a speculative TP2 engine generates what a
+    plain single-rank engine generates."""
+    g = torch.Generator().manual_seed(6)
+    base = torch.randint(0, 515, (6,), generator=g).tolist()
+    prompts = [base * 4, torch.randint(0, 515, (17,), generator=g).tolist()]     # one repetitive prompt for the lookup
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, False)
+        want = _single(ckpt, prompts)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 28300 + (os.getpid() % 1500)
+        extra = dict(spec_algorithm="ngram", spec_num_draft=3)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, False, extra)) for r in range(2)]
         for p in procs:
             p.start()
         got = q.get(timeout=300)

@@ -166,8 +166,43 @@ class Scheduler:
             self._free_req_resources(req, insert=True)
 
     # ------------------------------------------------------------------ planning
+    def _free_device_bytes(self) -> Optional[int]:
+        """Device memory a forward can still take: what the driver reports free plus the caching
+        allocator's reserved-but-unallocated blocks (at steady state that cache is most of the headroom)."""
+        if self.engine.device.type != "cuda":
+            return None
+        try:
+            free, _total = torch.cuda.mem_get_info(self.engine.device)
+            return int(free + torch.cuda.memory_reserved(self.engine.device)
+                       - torch.cuda.memory_allocated(self.engine.device))
+        except Exception:      # the guard must never break scheduling
+            return None
+
     def _prefill_budget_now(self) -> int:
-        return self.config.max_extend_tokens
+        """Prefill tokens this step may take: the configured chunk, shrunk when free device memory
+        cannot hold that chunk's activations (python/minisgl/scheduler/scheduler.py:2524-2570). The
+        peak of a prefill step is proportional to its tokens, not to the context behind them, so the
+        largest safe step is ``(free - safety) / bytes per token``; the step shrinks in whole pages
+        and never below 1024 tokens (a step too small to make progress is worse than a failed one)."""
+        base = self.config.max_extend_tokens
+        if not self.prefill.runnable:                  # nothing to prefill: skip the driver query
+            return base
+        free = self._free_device_bytes()
+        if free is None:
+            return base
+        mc, tp = self.engine.model_config, max(self.config.tp_size, 1)
+        widest = max(2 * mc.intermediate_size // tp, mc.q_size + 2 * mc.kv_size, mc.hidden_size * 4)
+        per_token = widest * 2 * 4                       # the engine's sizing rule for a chunk's intermediates
+        affordable = (free - (1 << 30)) // max(per_token, 1)
+        if affordable >= base:
+            return base
+        page = max(1, self.page_size)
+        budget = max(min(base, max(page, 1024)), (int(affordable) // page) * page)
+        self._act_guard_trips = getattr(self, "_act_guard_trips", 0) + 1
+        if self._act_guard_trips <= 3 or self._act_guard_trips % 100 == 0:
+            logger.warning("prefill activation guard: %.2f GiB free affords %d tokens at %d KiB/token: step of %d "
+                           "instead of %d", free / 2 ** 30, affordable, per_token // 1024, budget, base)
+        return budget
 
     def _schedule_next_batch(self) -> Optional[Batch]:
         batch, adder = self.prefill.schedule_next_batch(self._prefill_budget_now())

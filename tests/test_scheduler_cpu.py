@@ -138,3 +138,26 @@ def test_a_chunked_prompt_keeps_its_reservation_against_requests_behind_it():
               num_page_override=8, max_extend_tokens=64, cache_type="naive")
     outs = llm.generate([list(range(90)), list(range(500, 510))], SamplingParams(max_tokens=20, ignore_eos=True))
     assert [len(o.token_ids) for o in outs] == [20, 20]
+
+
+def test_prefill_budget_shrinks_under_memory_pressure():
+    """The activation guard: with little free device memory the prefill step shrinks in whole pages,
+    never below 1024 tokens, and is the configured chunk again once memory is back."""
+    from minisglang_rdna4_b200 import LLM
+    from minisglang_rdna4_b200.models.config import tiny_llama_config
+
+    llm = LLM(model_config=tiny_llama_config(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=4,
+              num_page_override=64, max_extend_tokens=8192)
+    try:
+        assert llm._prefill_budget_now() == 8192                     # no device: the guard stays out of the way
+        llm.prefill.add_one_req(0, torch.arange(40, dtype=torch.int32), SamplingParams(max_tokens=1))
+        mc = llm.engine.model_config
+        per_token = max(2 * mc.intermediate_size, mc.q_size + 2 * mc.kv_size, mc.hidden_size * 4) * 8
+        llm._free_device_bytes = lambda: (1 << 30) + 3000 * per_token
+        assert llm._prefill_budget_now() == 3000 // 16 * 16
+        llm._free_device_bytes = lambda: (1 << 30) + 100 * per_token
+        assert llm._prefill_budget_now() == 1024                      # the floor
+        llm._free_device_bytes = lambda: 64 << 30
+        assert llm._prefill_budget_now() == 8192
+    finally:
+        llm.shutdown()

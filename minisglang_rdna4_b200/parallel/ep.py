@@ -161,6 +161,14 @@ class FusedEPContext(EPContext):
         self.calls += 1
         return out
 
+    def poll_status(self) -> int:
+        """Status word of the exchange kernels on this rank (0 = no wait ran out), cleared on read.
+        The lock-step loop takes the MAX over the replicas before anybody acts on it, so that all of
+        them leave the fused path on the same step."""
+        from ..ops._lib import lib
+
+        return int(lib().msgl_ep_status(1)) if self.healthy else 0
+
     def check_health(self) -> bool:
         from ..ops._lib import lib
 

@@ -14,6 +14,7 @@ import torch.distributed as dist
 
 from ..core import Batch
 from ..engine import BatchSamplingArgs, StepPlan
+from ..env import ENV
 
 
 def _dummy_step(sched) -> None:
@@ -39,6 +40,8 @@ def ep_lockstep_loop(sched) -> None:
     ep = eng.ctx.ep
     idle_rounds = 0
     local_done = False
+    steps = 0
+    health_every = max(1, ENV.COMM_HEALTH_STEPS.value)
     while True:
         # a replica whose own requests are all finished keeps stepping with the others (their tokens
         # may be routed to its experts) until every replica agrees that nothing is left
@@ -51,11 +54,24 @@ def ep_lockstep_loop(sched) -> None:
         tokens = 0
         if batch is not None:
             tokens = sum(r.extend_len for r in batch.reqs)
+        # the status word of the peer-memory exchange rides along every few steps (the host has
+        # synchronised with the device at the end of the previous step, so the read does not stall)
+        poll = getattr(ep, "poll_status", None)
+        status = poll() if poll is not None and steps % health_every == 0 else 0
         agree = torch.tensor([tokens, 1 if sched._exit else 0,
-                              1 if ((sched.has_work or batch is not None) and not (local_done and batch is None)) else 0],
-                             dtype=torch.int64)
+                              1 if ((sched.has_work or batch is not None) and not (local_done and batch is None)) else 0,
+                              status], dtype=torch.int64)
         dist.all_reduce(agree, op=dist.ReduceOp.MAX, group=group)
         common, any_exit, any_work = int(agree[0]), int(agree[1]), int(agree[2])
+        if int(agree[3]) != 0 and getattr(ep, "healthy", False):
+            # a bounded wait ran out on some replica (a peer was more than the limit late): rows of
+            # the steps since the last clean check may be missing from somebody's sums. Every
+            # replica leaves the fused exchange on this step, decode leaves its captured graphs
+            # (they contain the exchange kernels) and the running requests end with an error.
+            ep.healthy = False
+            eng.graph_runner = None
+            sched._fail_running("the expert exchange timed out; the request was ended because its state may be incomplete")
+            batch = None if batch is not None and all(r.finished for r in batch.reqs) else batch
         if common == 0:
             if any_exit and not any_work:
                 break
@@ -76,4 +92,5 @@ def ep_lockstep_loop(sched) -> None:
         else:
             _dummy_step(sched)
         ep.common_tokens = None
+        steps += 1
         sched._maybe_exit_after_steps()

@@ -123,6 +123,56 @@ def test_dp2_expert_parallel_lockstep_matches_single_replica():
     assert calls[0] == calls[1] > 0   # both replicas issued the same number of exchanges
 
 
+def _dp_timeout_worker(rank, world, port, ckpt, prompts_by_rank, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      MSGL_COMM_HEALTH_STEPS="1")
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    llm = LLM(model_path=ckpt, device="cpu", dp_size=world, dp_rank=rank, page_size=16, max_running_req=4,
+              num_page_override=64, enable_ep=True, dtype="fp32")
+    ep = llm.engine.ctx.ep
+    ep.healthy = True
+    polls = [0]
+
+    def poll_status():           # the device status word of a fused exchange: a wait ran out on replica 1 once
+        polls[0] += 1
+        return 407 if rank == 1 and polls[0] == 3 and ep.healthy else 0
+
+    ep.poll_status = poll_status
+    outs = llm.generate(prompts_by_rank[rank], SamplingParams(max_tokens=8, ignore_eos=True))
+    out_q.put((rank, [(o.finish_reason, o.error is not None, len(o.token_ids)) for o in outs], ep.healthy))
+    llm.shutdown()
+
+
+def test_exchange_timeout_on_one_replica_is_agreed_and_ends_running_requests():
+    """A device-side wait that ran out on one replica reaches the others through the per-step
+    agreement: all leave the fused exchange on the same step and the requests that were running
+    end with an error instead of continuing on possibly incomplete sums."""
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 515, (n,), generator=g).tolist() for n in (9, 21, 14)]
+    by_rank = {0: prompts[:2], 1: prompts[2:]}
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, True)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 27100 + os.getpid() % 1000
+        procs = [ctx.Process(target=_dp_timeout_worker, args=(r, 2, port, ckpt, by_rank, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = dict()
+        for _ in procs:
+            r, outs, healthy = q.get(timeout=240)
+            got[r] = (outs, healthy)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    for r in (0, 1):
+        outs, healthy = got[r]
+        assert healthy is False
+        assert all(reason == "error" and has_error and n < 8 for reason, has_error, n in outs), outs
+
+
 def _health_worker(rank, world, port, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist

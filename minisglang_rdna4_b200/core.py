@@ -209,6 +209,9 @@ class Context:
     aux_hidden: Optional[List[torch.Tensor]] = None
     # recurrent state of gated-delta-net layers (kvcache.gdn_state.GDNStateCache), hybrid models only
     gdn_state: Any = None
+    # speculative verify of a hybrid model: every recurrent layer appends (layer, its projected step
+    # input) here, so that the state can be rebuilt for the accepted rows only (list, or None = off)
+    recurrent_journal: Any = None
     _batch: Optional[Batch] = None
 
     @property

@@ -34,6 +34,25 @@ class GDNStateCache:
     def ssm_state(self, layer: int) -> torch.Tensor:
         return self.ssm[layer]
 
+    # ---- speculative verify: keep the state of a batch's slots and put (some of) them back ----
+    def save_slots(self, slots: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Copies of the states of ``slots`` over all layers (``[L, B, ...]``), taken before a verify
+        forward advances them by rows that may be rejected (python/minisgl/gdn/layer.py:640-760,
+        the rollback half of verify-replay)."""
+        idx = slots.long()
+        return self.conv.index_select(1, idx), self.ssm.index_select(1, idx)
+
+    def load_slots(self, slots: torch.Tensor, saved: Tuple[torch.Tensor, torch.Tensor],
+                   which: Optional[torch.Tensor] = None) -> None:
+        """Puts saved states back; ``which`` selects entries of the saved batch."""
+        idx = slots.long()
+        conv, ssm = saved
+        if which is not None:
+            w = which.long()
+            conv, ssm, idx = conv.index_select(1, w), ssm.index_select(1, w), idx.index_select(0, w)
+        self.conv.index_copy_(1, idx, conv)
+        self.ssm.index_copy_(1, idx, ssm)
+
     # ---- snapshots: the state of one slot after exactly ``key`` tokens ----
     def slot_nbytes(self) -> int:
         """Bytes of one request's state over all recurrent layers (= the size of a snapshot)."""

@@ -62,18 +62,27 @@ class Mamba2Mixer(BaseOP):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ctx = get_global_ctx()
         batch = ctx.batch
-        st = ctx.gdn_state
-        md = batch.attn_metadata
         proj = self.in_proj.forward(x)
+        if ctx.recurrent_journal is not None:
+            ctx.recurrent_journal.append((self, proj))
+        y = self._mix(proj, batch.attn_metadata.cu_q, batch.gdn_slots, batch.gdn_has_state)
+        return self.out_proj.forward(y, reduce=True)
+
+    def _mix(self, proj: torch.Tensor, cu_q, slots, has_state) -> torch.Tensor:
+        """Convolution → selective scan → grouped gated norm over the projected rows; advances the two states."""
+        st = get_global_ctx().gdn_state
         i, c, h = self._inter, self._conv_dim, self._h
         z = proj[:, :i]
-        xbc = ops.gdn_conv1d(proj[:, i:i + c], self.conv1d_weight, st.conv_state(self._state_id), md.cu_q,
-                             batch.gdn_slots, batch.gdn_has_state, self.conv1d_bias)
+        xbc = ops.gdn_conv1d(proj[:, i:i + c], self.conv1d_weight, st.conv_state(self._state_id), cu_q,
+                             slots, has_state, self.conv1d_bias)
         dt = proj[:, i + c:i + c + h]
-        y = ops.mamba2_scan(xbc, dt, self.A_log, self.D, self.dt_bias, st.ssm_state(self._state_id), md.cu_q,
-                            batch.gdn_slots, batch.gdn_has_state, self._h, self._g, self._p, self._n, self._dt_min)
-        y = ops.rms_norm_gate_first(y.reshape(y.shape[0], i), z, self.norm_weight, self._eps, i // self._g)
-        return self.out_proj.forward(y, reduce=True)
+        y = ops.mamba2_scan(xbc, dt, self.A_log, self.D, self.dt_bias, st.ssm_state(self._state_id), cu_q,
+                            slots, has_state, self._h, self._g, self._p, self._n, self._dt_min)
+        return ops.rms_norm_gate_first(y.reshape(y.shape[0], i), z, self.norm_weight, self._eps, i // self._g)
+
+    def replay(self, proj: torch.Tensor, cu_q, slots, has_state) -> None:
+        """Re-advance the (restored) states over the kept rows of a verify step."""
+        self._mix(proj, cu_q, slots, has_state)
 
     def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
         self.conv1d_weight = (torch.randn(self.conv1d_weight.shape, generator=gen, device=gen.device) * 0.3).to(

@@ -92,19 +92,28 @@ class GatedDeltaNet(BaseOP):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ctx = get_global_ctx()
         batch = ctx.batch
-        st = ctx.gdn_state
         proj = self.in_proj.forward(x)                                  # [T, q‖k‖v‖z‖b‖a (+pad)]
+        if ctx.recurrent_journal is not None:
+            ctx.recurrent_journal.append((self, proj))
+        vd = self._value_dim
+        o = self._mix(proj, batch.attn_metadata.cu_q, batch.gdn_slots, batch.gdn_has_state)
+        return self.out_proj.forward(o.reshape(o.shape[0], vd), reduce=True)
+
+    def _mix(self, proj: torch.Tensor, cu_q, slots, has_state) -> torch.Tensor:
+        """Convolution → delta rule → gated norm over the projected rows; advances the two states."""
+        st = get_global_ctx().gdn_state
         c, vd, hv = self._conv_dim, self._value_dim, self._hv
-        md = batch.attn_metadata
-        qkv = ops.gdn_conv1d(proj[:, :c], self.conv1d_weight, st.conv_state(self._gdn_id), md.cu_q,
-                             batch.gdn_slots, batch.gdn_has_state)
+        qkv = ops.gdn_conv1d(proj[:, :c], self.conv1d_weight, st.conv_state(self._gdn_id), cu_q, slots, has_state)
         z = proj[:, c:c + vd]
         b = proj[:, c + vd:c + vd + hv]
         a = proj[:, c + vd + hv:c + vd + 2 * hv]
-        o = ops.gdn_recurrent(qkv, a, b, self.A_log, self.dt_bias, st.ssm_state(self._gdn_id), md.cu_q,
-                              batch.gdn_slots, batch.gdn_has_state, self._hk, self._hv, self._dk, self._dv)
-        o = ops.rms_norm_gated(o, z, self.norm_weight, self._eps)
-        return self.out_proj.forward(o.reshape(o.shape[0], vd), reduce=True)
+        o = ops.gdn_recurrent(qkv, a, b, self.A_log, self.dt_bias, st.ssm_state(self._gdn_id), cu_q,
+                              slots, has_state, self._hk, self._hv, self._dk, self._dv)
+        return ops.rms_norm_gated(o, z, self.norm_weight, self._eps)
+
+    def replay(self, proj: torch.Tensor, cu_q, slots, has_state) -> None:
+        """Re-advance the (restored) states over the kept rows of a verify step."""
+        self._mix(proj, cu_q, slots, has_state)
 
     def init_dummy(self, gen: torch.Generator, std: float = 0.02) -> None:
         self.conv1d_weight = (torch.randn(self.conv1d_weight.shape, generator=gen, device=gen.device) * 0.3).to(

@@ -67,8 +67,11 @@ class Scheduler:
             self._snapshots_on = (cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0
                                   and eng.gdn_state is not None)
             cache_type = "radix_snapshot" if self._snapshots_on else "naive"
-        if eng.model_config.is_recurrent and config.spec_algorithm != "none":
-            raise ValueError("speculative decoding is not available for models with recurrent layers")
+        if eng.model_config.is_recurrent and config.spec_algorithm != "none" and getattr(
+                config, "spec_tree_width", 1) > 1:
+            # siblings of a draft tree would each need their own copy of the running state
+            raise ValueError("tree verification is not available for models with recurrent layers; "
+                             "use a draft chain (spec tree width 1)")
         self.cache = CacheManager(eng.num_pages, eng.page_size, eng.num_slots, eng.max_pages_per_seq,
                                   cache_type)
         if self._snapshots_on:

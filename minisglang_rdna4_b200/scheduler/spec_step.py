@@ -89,8 +89,9 @@ def device_runner(sched):
     draft = getattr(proposer, "draft", None)
     tree_width = getattr(proposer, "tree_width", 1)
     # a tree on the device needs the draft head's ranked candidates; n-gram trees stay on the host-driven step
+    # (models with recurrent layers roll their state back on the host-driven step)
     if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and (tree_width <= 1 or draft is not None)
-            and proposer.num_draft >= 1):
+            and proposer.num_draft >= 1 and eng.gdn_state is None):
         from ..spec.device import DeviceSpecRunner
 
         with _engine_stream(eng):
@@ -197,7 +198,18 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
     plan = _verify_plan(sched, batch, drafts)
     sampled = any(not r.sampling_params.is_greedy for r in reqs) and ENV.SPEC_SAMPLED.value
     args = BatchSamplingArgs()
-    out = eng.forward_batch(batch, plan, args, return_logits=True)
+    rec = eng.gdn_state
+    if rec is not None:
+        # recurrent layers: the verify forward advances every request's state over all of its rows.
+        # Keep the states as they are now and let every recurrent layer note its projected input, so
+        # that the state of a request whose draft is cut short can be rebuilt over the kept rows
+        rec_slots = torch.tensor([r.table_idx for r in reqs], dtype=torch.int64).to(eng.device)
+        rec_saved = rec.save_slots(rec_slots)
+        eng.ctx.recurrent_journal = []
+    try:
+        out = eng.forward_batch(batch, plan, args, return_logits=True)
+    finally:
+        journal, eng.ctx.recurrent_journal = eng.ctx.recurrent_journal, None
     logits = eng.sampler.condition_logits(out.logits, args)
     aux = eng.ctx.aux_hidden if capture else None
     eng.ctx.aux_hidden = None
@@ -209,6 +221,7 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
     replies: List[DetokenizeMsg] = []
     cu = plan.cu_q.tolist()
     total_accept = 0
+    kept: List[int] = []
     for i, (r, d) in enumerate(zip(reqs, drafts)):
         rows = target[cu[i]:cu[i + 1]]
         if sampled and not r.sampling_params.is_greedy:
@@ -220,6 +233,7 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
         emitted = emitted[: max(1, min(len(emitted), r.sampling_params.max_tokens - r.num_generated))]
         emitted, hit_eos = eos_truncate(emitted, sched.eos_ids, r.sampling_params.ignore_eos)
         n = len(emitted)
+        kept.append(n)
         total_accept += n - 1
         sched.stats["spec_drafted"] += len(d)
         sched.stats["spec_accepted"] += n - 1
@@ -243,10 +257,32 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
             r.finished, r.finish_reason = True, reason
             proposer.on_finish(r)
             sched._free_req_resources(r, insert=True)
+    if rec is not None:
+        _rollback_recurrent(eng, journal, rec_slots, rec_saved, cu, kept, [r.finished for r in reqs])
     sched._spec_width.update(total_accept / max(len(reqs), 1))
     sched.decode.filter_finished()
     if replies:
         sched.send_result(replies)
+
+
+def _rollback_recurrent(eng, journal, slots, saved, cu, kept, finished) -> None:
+    """Recurrent state after a verify step (python/minisgl/gdn/layer.py:640-760 verify-replay): a
+    request that kept all of its rows has the right state already. For the others the state from
+    before the step is put back and every recurrent layer is advanced again over the kept rows
+    only, from the projected inputs it noted during the verify forward; those inputs depend on
+    earlier positions alone, so they are what a forward over just the kept rows would have seen."""
+    part = [i for i, n in enumerate(kept) if n < cu[i + 1] - cu[i] and not finished[i]]
+    if not part or not journal:
+        return
+    dev = eng.device
+    which = torch.tensor(part, dtype=torch.int64).to(dev)
+    eng.gdn_state.load_slots(slots, saved, which)
+    rows = torch.tensor([cu[i] + j for i in part for j in range(kept[i])], dtype=torch.int64).to(dev)
+    cu_new = torch.tensor(np.concatenate([[0], np.cumsum([kept[i] for i in part])]), dtype=torch.int32).to(dev)
+    sub_slots = slots.index_select(0, which).to(torch.int32)
+    has_state = torch.ones(len(part), dtype=torch.int32, device=dev)
+    for layer, proj in journal:
+        layer.replay(proj.index_select(0, rows), cu_new, sub_slots, has_state)
 
 
 def _verify_plan(sched, batch: Batch, drafts):

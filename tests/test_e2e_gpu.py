@@ -614,3 +614,59 @@ def test_engine_runs_clean_under_the_bounds_checking_build():
     out = subprocess.run([sys.executable, "-c", _CHECKED_ENGINE_CHILD], capture_output=True, text=True, timeout=900,
                          env=dict(os.environ, MSGL_CHECK_BOUNDS="1"), cwd=root)
     assert out.returncode == 0 and "CHECKED-ENGINE-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+def test_speculative_decoding_on_a_hybrid_model_rolls_state_back_exactly():
+    """Hybrid target on the kernel path with drafts that are right for two tokens and wrong at the
+    third: every verify step keeps three of its four rows, so every step restores the recurrent
+    states and re-advances them over the kept rows (convolution and delta-rule kernels in their
+    multi-row form from a given state). The output equals draft-free decoding token for token."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=4, num_qo_heads=4, num_kv_heads=2, head_dim=256, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-6,
+            rotary_config=RotaryConfig(head_dim=256, rotary_dim=64, max_position=2048, base=1e7),
+            model_type="qwen3_5_text", architectures=("Qwen3_5ForCausalLM",), qk_norm=True,
+            max_position_embeddings=2048, attn_output_gate=True, norm_plus_one=True,
+            layer_types=("linear_attention", "linear_attention", "linear_attention", "full_attention"),
+            linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128,
+            linear_conv_kernel_dim=4,
+        )
+
+    prompts = _prompts()
+    sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    kw = dict(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    # baseline: the same engine with a proposer that never drafts (one verify row per request per step, so
+    # both runs take the same kernels and differ only in what the recurrent layers have to undo)
+    plain = LLM(spec_algorithm="ngram", spec_num_draft=3, **kw)
+    plain.proposer.propose = lambda reqs: [[] for _ in reqs]
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    assert plain.stats["spec_drafted"] == 0
+    plain.shutdown()
+    kw["model_config"] = cfg()
+    llm = LLM(spec_algorithm="ngram", spec_num_draft=3, **kw)
+    by_prompt = {tuple(p): w for p, w in zip(prompts, want)}
+
+    def propose(reqs):
+        out = []
+        for r in reqs:
+            truth = by_prompt[tuple(r.input_ids[: r.prompt_len].tolist())]
+            g = r.num_generated                                # tokens generated so far
+            d = list(truth[g:g + 3])
+            if len(d) == 3:
+                d[2] = (d[2] + 1) % 2048                       # the third draft token is wrong
+            out.append(d)
+        return out
+
+    llm.proposer.propose = propose
+    got = [o.token_ids for o in llm.generate(prompts, sp)]
+    stats = dict(llm.stats)
+    llm.shutdown()
+    assert got == want
+    assert stats["spec_accepted"] >= 2 * (stats["spec_steps"] // 2), stats
+    assert stats["spec_accepted"] < stats["spec_drafted"]

@@ -143,3 +143,65 @@ def test_recurrent_model_reuses_a_prefix_through_state_snapshots(monkeypatch):
         assert llm.engine.gdn_state.num_snapshots == llm.cache.prefix_cache.num_snapshots
         llm.cache.check_integrity()
         llm.shutdown()
+
+
+@pytest.mark.parametrize("family", ["qwen3_5", "nemotron_h"])
+def test_speculative_decoding_rolls_the_recurrent_state_back(family, monkeypatch):
+    """A verify step advances the recurrent layers over every draft row. When part of the draft is
+    rejected the states from before the step are put back and advanced again over the kept rows only,
+    so a speculative engine generates what plain decoding generates."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "0")
+    g = torch.Generator().manual_seed(9)
+    base = torch.randint(0, 298, (5,), generator=g).tolist()
+    prompts = [base * 5, torch.randint(0, 298, (23,), generator=g).tolist(), (base[:3] + [11]) * 6]
+    sp = SamplingParams(max_tokens=24, ignore_eos=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        if family == "qwen3_5":
+            _hf_model(tmp)
+        else:
+            from safetensors.torch import save_file
+            from test_nemotron_h_cpu import _hf_model as nemotron
+
+            cfg, hf = nemotron()
+            cfg.save_pretrained(tmp)
+            save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, f"{tmp}/model.safetensors")
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64)
+        plain = LLM(**kw)
+        want = [o.token_ids for o in plain.generate(prompts, sp)]
+        plain.shutdown()
+        llm = LLM(spec_algorithm="ngram", spec_num_draft=3, **kw)
+        got = [o.token_ids for o in llm.generate(prompts, sp)]
+        stats = dict(llm.stats)
+        llm.shutdown()
+    assert got == want
+    assert stats["spec_drafted"] > 0
+    assert 0 < stats["spec_accepted"] < stats["spec_drafted"], stats    # both full and cut-short drafts occurred
+
+
+def test_draft_head_proposers_run_against_a_hybrid_target(monkeypatch):
+    """EAGLE3 / MTP draft heads only need the target's hidden states and the verify step's accept
+    record; with the recurrent rollback they serve hybrid targets too (random head: every draft is
+    rejected, i.e. every step rolls back, and the output still equals plain decoding)."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "0")
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (25, 9)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        _hf_model(tmp)
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64)
+        plain = LLM(**kw)
+        want = [o.token_ids for o in plain.generate(prompts, sp)]
+        plain.shutdown()
+        llm = LLM(spec_algorithm="mtp", spec_num_draft=2, **kw)
+        got = [o.token_ids for o in llm.generate(prompts, sp)]
+        assert llm.stats["spec_steps"] > 0
+        llm.shutdown()
+        with pytest.raises(ValueError, match="tree verification"):
+            LLM(spec_algorithm="ngram", spec_num_draft=2, spec_tree_width=3, **kw)
+    assert got == want

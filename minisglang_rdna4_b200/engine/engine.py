@@ -214,6 +214,8 @@ class Engine:
             self.ledger.add("recurrent state", self.gdn_state.conv.numel() * self.gdn_state.conv.element_size()
                             + self.gdn_state.ssm.numel() * 4)
         self.ctx.gdn_state = self.gdn_state
+        if self.gdn_state is not None and dev_kind == "cuda":
+            self.gdn_state.stream = self.stream
         self.ctx.attn_backend = create_attention_backend(
             config.attention_backend, self.q_heads_local, self.kv_heads_local, mc.head_dim, self.device,
             max_batch=config.max_running_req, max_seq_len=self.max_seq_len,

@@ -22,6 +22,22 @@ class GDNStateCache:
         self.ssm = torch.zeros((num_layers, num_slots, num_v_heads, head_k_dim, head_v_dim), dtype=torch.float32,
                                device=device)
         self._snapshots: Dict[object, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._arena = None                      # pinned frames for snapshots kept on the host
+        self.stream = None                      # the stream the snapshot / restore copies are issued on
+        self._frames: Dict[object, int] = {}    # snapshot key -> frame
+
+    def attach_host_arena(self, budget_bytes: int) -> int:
+        """Keep snapshots in page-locked host frames (one slab, ``budget_bytes`` of it) instead of
+        device memory; returns the number of frames (python/minisgl/kvcache/host_arena.py:132)."""
+        from .host_arena import FrameLayout, PinnedFrameArena
+
+        layout = FrameLayout([("conv", tuple(self.conv[:, 0].shape), self.conv.dtype),
+                              ("ssm", tuple(self.ssm[:, 0].shape), torch.float32)])
+        frames = layout.frames_in(budget_bytes)
+        if frames <= 0:
+            return 0
+        self._arena = PinnedFrameArena(layout, frames, pin=self.conv.is_cuda)
+        return frames
 
     @staticmethod
     def slot_bytes(num_layers: int, conv_dim: int, conv_kernel: int, num_v_heads: int, dk: int, dv: int,
@@ -59,8 +75,18 @@ class GDNStateCache:
         return int(self.conv[:, 0].numel() * self.conv.element_size() + self.ssm[:, 0].numel() * 4)
 
     def snapshot(self, slot: int, key, host: bool = True) -> None:
+        if self._arena is not None:
+            frame = self._arena.alloc()
+            if frame is not None:
+                v = self._arena.views(frame)
+                v["conv"].copy_(self.conv[:, slot], non_blocking=True)
+                v["ssm"].copy_(self.ssm[:, slot], non_blocking=True)
+                self._frames[key] = frame
+                self._snapshots[key] = (v["conv"], v["ssm"])
+                return
+            # every frame is held: this snapshot stays on the device
         conv, ssm = self.conv[:, slot].clone(), self.ssm[:, slot].clone()
-        if host and conv.is_cuda:
+        if host and conv.is_cuda and self._arena is None:
             conv, ssm = conv.to("cpu", non_blocking=True), ssm.to("cpu", non_blocking=True)
         self._snapshots[key] = (conv, ssm)
 
@@ -74,6 +100,14 @@ class GDNStateCache:
 
     def drop_snapshot(self, key) -> None:
         self._snapshots.pop(key, None)
+        frame = self._frames.pop(key, None)
+        if frame is not None:
+            ev = None
+            if self.conv.is_cuda:
+                # a restore from this frame (or the copy that filled it) may still be queued
+                ev = torch.cuda.Event()
+                ev.record(self.stream) if self.stream is not None else ev.record()
+            self._arena.release(frame, ev)
 
     @property
     def num_snapshots(self) -> int:

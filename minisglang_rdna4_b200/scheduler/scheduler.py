@@ -77,6 +77,13 @@ class Scheduler:
         if self._snapshots_on:
             pc = self.cache.prefix_cache
             pc.capacity = max(4, (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(eng.gdn_state.slot_nbytes(), 1))
+            host_mib = ENV.RECURRENT_SNAPSHOT_HOST_MIB.value
+            if host_mib > 0:
+                # snapshots in page-locked host frames: the prefix cache may keep what is left after the
+                # frames that running requests hold for boundaries not attached to the tree yet
+                frames = eng.gdn_state.attach_host_arena(host_mib << 20)
+                if frames > 0:
+                    pc.capacity = max(4, frames - min(frames // 2, 6 * config.max_running_req))
             pc.on_drop = eng.gdn_state.drop_snapshot
             every = max(ENV.RECURRENT_SNAPSHOT_TOKENS.value, eng.page_size)
             self._snap_every = (every + eng.page_size - 1) // eng.page_size * eng.page_size

@@ -54,11 +54,20 @@ class HostExpertTier:
                 files[name] = f
             self.disk = DiskExpertTier(files)
             self.host_cache = SLRUCache(host_experts, protected_fraction)
-            self.h13 = self.arena.put("w13", torch.zeros((host_experts,) + tuple(w13.shape[1:]), dtype=w13.dtype))
-            self.h2 = self.arena.put("w2", torch.zeros((host_experts,) + tuple(w2.shape[1:]), dtype=w2.dtype))
+            rows = host_experts
         else:
-            self.h13 = self.arena.put("w13", w13)
-            self.h2 = self.arena.put("w2", w2)
+            rows = self.num_experts
+        # both families in one page-locked allocation (placement first, then a single pin)
+        self.arena.reserve("w13", (rows,) + tuple(w13.shape[1:]), w13.dtype)
+        self.arena.reserve("w2", (rows,) + tuple(w2.shape[1:]), w2.dtype)
+        self.arena.attach()
+        self.h13, self.h2 = self.arena.get("w13"), self.arena.get("w2")
+        if self.disk is None:
+            self.h13.copy_(w13)
+            self.h2.copy_(w2)
+        else:
+            self.h13.zero_()
+            self.h2.zero_()
         self.d13 = torch.empty((self.slots,) + tuple(w13.shape[1:]), dtype=w13.dtype, device=self.device)
         self.d2 = torch.empty((self.slots,) + tuple(w2.shape[1:]), dtype=w2.dtype, device=self.device)
         self.cache = SLRUCache(self.slots, protected_fraction)

@@ -208,3 +208,63 @@ def test_three_tier_engine_matches_resident_engine(tmp_path):
     finally:
         MoELayer.offload_slots, MoELayer.offload_host_experts, MoELayer.offload_disk_dir = 0, 0, ""
     assert got == want
+
+
+def test_pinned_arena_places_regions_before_it_allocates():
+    """Placement is integer arithmetic (aligned offsets, no region across two chunks, an oversized
+    region alone in its chunk); memory appears at attach(), after which the arena is frozen."""
+    import torch
+
+    from minisglang_rdna4_b200.weights.pinned_arena import ALIGN, ChunkPlan, PinnedArena
+
+    plan = ChunkPlan(chunk_bytes=4096)
+    a = plan.reserve("a", (100,), torch.float32)          # 400 B -> 512
+    b = plan.reserve("b", (3, 500), torch.uint8)          # 1500 B -> 1536
+    c = plan.reserve("c", (600,), torch.float32)          # 2400 B -> does not fit behind a + b
+    d = plan.reserve("d", (3000,), torch.float32)         # 12000 B > chunk: a chunk of its own
+    assert (a.chunk, a.offset, b.chunk, b.offset) == (0, 0, 0, 512)
+    assert (c.chunk, c.offset) == (1, 0) and (d.chunk, d.offset) == (2, 0)
+    assert all(r.offset % ALIGN == 0 for r in plan.regions.values())
+    assert plan.chunk_sizes == [2048, 2560, 12288]
+
+    arena = PinnedArena(pin=False, chunk_bytes=4096)
+    arena.reserve("w13", (4, 8, 16), torch.bfloat16)
+    arena.reserve("w2", (4, 16, 4), torch.bfloat16)
+    assert arena.num_chunks == 0
+    arena.attach()
+    assert arena.num_chunks == 1 and arena.frozen
+    w13, w2 = arena.get("w13"), arena.get("w2")
+    w13.fill_(1.0)
+    w2.fill_(2.0)
+    assert float(w13.float().sum()) == 4 * 8 * 16 and float(w2.float().sum()) == 2 * 4 * 16 * 4   # no overlap
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        arena.reserve("late", (4,), torch.float32)
+    one_call = PinnedArena(pin=False)
+    t = torch.arange(12, dtype=torch.float32).view(3, 4)
+    assert torch.equal(one_call.put("x", t), t) and torch.equal(one_call.put("y", t * 2), t * 2)
+    assert torch.equal(one_call.get("x"), t)
+
+
+def test_frame_arena_recycles_frames_first_released_first():
+    import torch
+
+    from minisglang_rdna4_b200.kvcache.host_arena import FrameLayout, PinnedFrameArena
+
+    layout = FrameLayout([("conv", (2, 6, 3), torch.bfloat16), ("ssm", (2, 4, 8, 8), torch.float32)])
+    assert layout.components[1].offset == 256 and layout.frame_bytes == 256 + 2048
+    assert layout.frames_in(10_000) == 4
+    arena = PinnedFrameArena(layout, 3, pin=False)
+    f = [arena.alloc() for _ in range(3)]
+    assert f == [0, 1, 2] and arena.alloc() is None
+    for i in f:
+        v = arena.views(i)
+        v["conv"].fill_(i + 1)
+        v["ssm"].fill_(10 * (i + 1))
+    assert [float(arena.views(i)["ssm"][0, 0, 0, 0]) for i in f] == [10.0, 20.0, 30.0]   # frames do not overlap
+    arena.release(1)
+    arena.release(1)                      # dropping twice is harmless
+    arena.release(0)
+    assert arena.num_free == 2
+    assert arena.alloc() == 1 and arena.alloc() == 0 and arena.alloc() is None

@@ -143,6 +143,17 @@ def test_recurrent_model_reuses_a_prefix_through_state_snapshots(monkeypatch):
         assert llm.engine.gdn_state.num_snapshots == llm.cache.prefix_cache.num_snapshots
         llm.cache.check_integrity()
         llm.shutdown()
+        # the same with the snapshots in host frames of one slab (room for a few only: the cache evicts)
+        monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_HOST_MIB", "1")
+        host = LLM(**kw)
+        arena = host.engine.gdn_state._arena
+        assert arena is not None and arena.num_frames >= 4
+        outs = [host.generate([p], sp)[0] for p in (first, second, third)]
+        assert [o.token_ids for o in outs] == want
+        assert outs[1].cached_tokens == 96
+        assert arena.num_free < arena.num_frames                     # kept snapshots live in frames
+        assert len(host.engine.gdn_state._frames) == host.engine.gdn_state.num_snapshots
+        host.shutdown()
 
 
 @pytest.mark.parametrize("family", ["qwen3_5", "nemotron_h"])

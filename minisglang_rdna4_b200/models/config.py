@@ -99,6 +99,7 @@ class ModelConfig:
     query_pre_attn_scalar: Optional[float] = None   # attention scale = this ** -0.5 (default head_dim)
     rope_local_base_freq: Optional[float] = None    # RoPE base of the sliding-window layers
     num_nextn_predict_layers: int = 0
+    mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     torch_dtype: str = "bfloat16"
@@ -297,7 +298,8 @@ class ModelConfig:
             moe_intermediate_size=int(g("moe_intermediate_size") or 0),
             norm_topk_prob=bool(g("norm_topk_prob", True)),
             shared_expert_intermediate_size=int(g("shared_expert_intermediate_size") or 0),
-            shared_expert_gate=model_type == "qwen2_moe",
+            # a sigmoid gate on the shared expert's output: Qwen2-MoE and the Qwen3.5 / Qwen3-Next MoE blocks
+            shared_expert_gate=model_type in ("qwen2_moe", "qwen3_5_moe", "qwen3_5_moe_text", "qwen3_next"),
             decoder_sparse_step=int(g("decoder_sparse_step") or 1),
             mlp_only_layers=tuple(g("mlp_only_layers") or ()),
             first_k_dense_replace=int(g("first_k_dense_replace") or 0),
@@ -334,6 +336,7 @@ class ModelConfig:
             query_pre_attn_scalar=g("query_pre_attn_scalar"),
             rope_local_base_freq=float(local_theta) if local_theta else None,
             num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
+            mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             eos_token_ids=eos_ids,
             bos_token_id=g("bos_token_id"),
             torch_dtype=str(g("torch_dtype") or g("dtype") or "bfloat16").replace("torch.", ""),

@@ -194,9 +194,11 @@ class Qwen3_5ForCausalLM(BaseOP):
             if capture is not None and i in capture:
                 seen[i] = x
             x = layer.forward(x)
+        out = self.model.norm.forward(x)
         if capture is not None:
+            seen[len(self.model.layers)] = out      # "layer" num_layers: the final hidden state (the MTP head's input)
             ctx.aux_hidden = [seen[i] for i in capture]
-        return self.model.norm.forward(x)
+        return out
 
     def init_dummy(self, seed: int, std: float = 0.02, gen_device: str = "cpu") -> None:
         gen = torch.Generator(device=gen_device)

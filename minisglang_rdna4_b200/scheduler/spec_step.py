@@ -91,7 +91,7 @@ def device_runner(sched):
     # a tree on the device needs the draft head's ranked candidates; n-gram trees stay on the host-driven step
     # (models with recurrent layers roll their state back on the host-driven step)
     if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and (tree_width <= 1 or draft is not None)
-            and proposer.num_draft >= 1 and eng.gdn_state is None):
+            and proposer.num_draft >= 1 and eng.gdn_state is None and getattr(proposer, "device_step_ok", True)):
         from ..spec.device import DeviceSpecRunner
 
         with _engine_stream(eng):

@@ -49,6 +49,12 @@ def make_proposer(config, scheduler) -> Proposer:
 
         return Eagle3Proposer(config, scheduler)
     if algo == "mtp":
+        mc = scheduler.engine.model_config
+        if mc.mtp_num_hidden_layers > 0 and mc.attn_output_gate and mc.layer_types:
+            # the checkpoint's own head (Qwen3.5 / Qwen3-Next mtp.*)
+            from .mtp import MTPProposer
+
+            return MTPProposer(config, scheduler)
         from .eagle3 import Eagle3Proposer
 
         return Eagle3Proposer(config, scheduler, mtp=True)

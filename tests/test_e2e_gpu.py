@@ -670,3 +670,39 @@ def test_speculative_decoding_on_a_hybrid_model_rolls_state_back_exactly():
     assert got == want
     assert stats["spec_accepted"] >= 2 * (stats["spec_steps"] // 2), stats
     assert stats["spec_accepted"] < stats["spec_drafted"]
+
+
+def test_checkpoint_mtp_head_drafts_for_a_hybrid_target_on_the_gpu():
+    """The target's own next-token head (one gated-attention decoder layer fed with the final hidden
+    state) as the draft model of a hybrid engine: the speculative engine reproduces the output of the
+    same engine with drafting switched off, and the head's draft steps really ran."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=4, num_qo_heads=4, num_kv_heads=2, head_dim=256, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-6,
+            rotary_config=RotaryConfig(head_dim=256, rotary_dim=64, max_position=2048, base=1e7),
+            model_type="qwen3_5_text", architectures=("Qwen3_5ForCausalLM",), qk_norm=True,
+            max_position_embeddings=2048, attn_output_gate=True, norm_plus_one=True,
+            layer_types=("linear_attention", "linear_attention", "linear_attention", "full_attention"),
+            linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128,
+            linear_conv_kernel_dim=4, mtp_num_hidden_layers=1,
+        )
+
+    prompts = _prompts()[:4]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    outs = {}
+    for name in ("off", "mtp"):
+        llm = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                  num_page_override=256, seed=0, spec_algorithm="mtp", spec_num_draft=2)
+        assert type(llm.proposer).__name__ == "MTPProposer"
+        if name == "off":
+            llm.proposer.propose = lambda reqs: [[] for _ in reqs]
+        outs[name] = [o.token_ids for o in llm.generate(prompts, sp)]
+        if name == "mtp":
+            assert llm.stats["spec_drafted"] > 0
+        llm.shutdown()
+    assert outs["mtp"] == outs["off"]

@@ -13,14 +13,22 @@ transformers = pytest.importorskip("transformers")
 def _hf_model(tmp, moe=False):
     from transformers import Qwen3_5ForCausalLM, Qwen3_5TextConfig
 
-    cfg = Qwen3_5TextConfig(
-        vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+    common = dict(
+        vocab_size=300, hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
         num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=16,
         linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4, max_position_embeddings=512,
         rms_norm_eps=1e-6, tie_word_embeddings=False, eos_token_id=299, pad_token_id=None, bos_token_id=None,
     )
     torch.manual_seed(0)
-    model = Qwen3_5ForCausalLM(cfg).float().eval()
+    if moe:
+        from transformers import Qwen3_5MoeForCausalLM, Qwen3_5MoeTextConfig
+
+        cfg = Qwen3_5MoeTextConfig(moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=8,
+                                   num_experts_per_tok=2, **common)
+        model = Qwen3_5MoeForCausalLM(cfg).float().eval()
+    else:
+        cfg = Qwen3_5TextConfig(intermediate_size=128, **common)
+        model = Qwen3_5ForCausalLM(cfg).float().eval()
     with torch.no_grad():
         for name, p in model.named_parameters():
             if name.endswith("norm.weight") and "linear_attn" not in name:
@@ -35,12 +43,13 @@ def _hf_model(tmp, moe=False):
     return model
 
 
-def test_qwen3_5_hybrid_matches_transformers():
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_hybrid_matches_transformers(moe):
     from minisglang_rdna4_b200 import SamplingParams
     from minisglang_rdna4_b200.llm import LLM
 
     with tempfile.TemporaryDirectory() as tmp:
-        hf = _hf_model(tmp)
+        hf = _hf_model(tmp, moe)
         g = torch.Generator().manual_seed(1)
         prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (5, 23, 41)]
         want = []
@@ -215,4 +224,118 @@ def test_draft_head_proposers_run_against_a_hybrid_target(monkeypatch):
         llm.shutdown()
         with pytest.raises(ValueError, match="tree verification"):
             LLM(spec_algorithm="ngram", spec_num_draft=2, spec_tree_width=3, **kw)
+    assert got == want
+
+
+def _add_mtp_head(tmp, hf):
+    """Append a random next-token head (``mtp.*``) to the checkpoint in ``tmp``; returns torch
+    modules that restate it: a Hugging Face full-attention decoder layer between the fusing
+    projection and the final norm."""
+    import json
+
+    from safetensors.torch import load_file, save_file
+
+    cfg = hf.config
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(1)
+    if hasattr(cfg, "num_experts"):
+        from transformers.models.qwen3_5_moe import modeling_qwen3_5_moe as m
+
+        layer_cls, norm_cls, rotary_cls = m.Qwen3_5MoeDecoderLayer, m.Qwen3_5MoeRMSNorm, m.Qwen3_5MoeTextRotaryEmbedding
+    else:
+        from transformers.models.qwen3_5 import modeling_qwen3_5 as m
+
+        layer_cls, norm_cls, rotary_cls = m.Qwen3_5DecoderLayer, m.Qwen3_5RMSNorm, m.Qwen3_5TextRotaryEmbedding
+    layer = layer_cls(cfg, 3).float().eval()                           # layer 3 of the pattern is full attention
+    fc = torch.nn.Linear(2 * cfg.hidden_size, cfg.hidden_size, bias=False)
+    ne, nh, nf = (norm_cls(cfg.hidden_size, eps=cfg.rms_norm_eps) for _ in range(3))
+    with torch.no_grad():
+        for mod in (layer, fc, ne, nh, nf):
+            for p in mod.parameters():
+                p.copy_(torch.randn_like(p) * (0.1 if p.dim() == 1 else 0.08))
+    st = load_file(f"{tmp}/model.safetensors")
+    for k, v in layer.state_dict().items():
+        st["mtp.layers.0." + k] = v.contiguous()
+    st["mtp.fc.weight"] = fc.weight.detach()
+    st["mtp.pre_fc_norm_embedding.weight"] = ne.weight.detach()
+    st["mtp.pre_fc_norm_hidden.weight"] = nh.weight.detach()
+    st["mtp.norm.weight"] = nf.weight.detach()
+    save_file(st, f"{tmp}/model.safetensors")
+    c = json.load(open(f"{tmp}/config.json"))
+    c["mtp_num_hidden_layers"] = 1
+    json.dump(c, open(f"{tmp}/config.json", "w"))
+
+    def head(hidden, embeds):
+        """Dense causal restatement: row i pairs hidden[i] with embeds[i] (the token after it)."""
+        n = hidden.shape[0]
+        with torch.no_grad():
+            x = fc(torch.cat([ne(embeds), nh(hidden)], -1))[None]
+            pos = torch.arange(n)[None]
+            pe = rotary_cls(cfg)(x, pos)
+            mask = torch.full((n, n), float("-inf")).triu(1)[None, None]
+            y = layer(x, position_embeddings=pe, attention_mask=mask, position_ids=pos)
+            y = y[0] if isinstance(y, tuple) else y
+            out = nf(y)[0]
+            return out, hf.lm_head(out)
+
+    return head
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_checkpoint_mtp_head_matches_a_dense_restatement_and_drafts_exactly(moe, monkeypatch):
+    """``--spec-algorithm mtp`` on a checkpoint that carries ``mtp.*`` tensors builds the head from the
+    target's own layer class and loads it through the decoder's loader. Its hidden states and logits
+    equal a dense Hugging Face restatement, the draft it proposes after the prefill is that
+    restatement's arg-max, and generation equals plain decoding."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "0")
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _hf_model(tmp, moe)
+        head = _add_mtp_head(tmp, hf)
+        g = torch.Generator().manual_seed(2)
+        ids = torch.randint(0, 298, (1, 21), generator=g)
+        with torch.no_grad():
+            hid = hf(ids, output_hidden_states=True).hidden_states[-1][0]      # final, normalised
+            emb = hf.model.embed_tokens(ids)[0]
+        want_hidden, want_logits = head(hid[:-1], emb[1:])
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64)
+        llm = LLM(spec_algorithm="mtp", spec_num_draft=2, **kw)
+        prop = llm.proposer
+        assert type(prop).__name__ == "MTPProposer" and prop.loaded_tensors >= 15
+        assert prop.draft.layer._is_moe == moe
+        n = ids.shape[1] - 1
+        got_hidden, got_logits = prop.draft.forward_rows(-7, emb[1:], hid[:-1], torch.arange(n, dtype=torch.int32))
+        prop.draft.drop(-7)
+        assert torch.allclose(got_hidden, want_hidden, atol=1e-5)
+        assert torch.allclose(got_logits, want_logits[-1:], atol=1e-5)
+
+        first = {}
+        inner = prop.propose
+
+        def recording(reqs):
+            out = inner(reqs)
+            for r, d in zip(reqs, out):
+                first.setdefault(r.prompt_len, list(d))
+            return out
+
+        prop.propose = recording
+        prompts = [ids[0].tolist(), torch.randint(0, 298, (9,), generator=g).tolist()]
+        sp = SamplingParams(max_tokens=12, ignore_eos=True)
+        outs = llm.generate(prompts, sp)
+        got = [o.token_ids for o in outs]
+        assert llm.stats["spec_steps"] > 0
+        llm.shutdown()
+        # the first draft of the 21-token prompt: rows 0..20 pair every position's hidden state with the
+        # token after it (the last one is the token the prefill sampled)
+        seq = torch.tensor([prompts[0] + got[0][:1]])
+        with torch.no_grad():
+            hid2 = hf(seq[:, :-1], output_hidden_states=True).hidden_states[-1][0]
+            emb2 = hf.model.embed_tokens(seq)[0]
+        _, logits2 = head(hid2, emb2[1:])
+        assert first[21][0] == int(logits2[-1].argmax())
+        plain = LLM(**kw)
+        want = [o.token_ids for o in plain.generate(prompts, sp)]
+        plain.shutdown()
     assert got == want

@@ -151,6 +151,7 @@ ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-
 ENV.int("THINK_LOOP_SPAN", 48, "a reasoning loop is reported once this many consecutive tokens repeat")
 ENV.int("THINK_LOOP_REPS", 3, "... and the block has repeated this many times")
 ENV.int("TOOLCALL_RUNAWAY_LIMIT", 8192, "tokens one open tool call may run for before the request is ended; 0 = off")
+ENV.int("TOOLCALL_CONT_LIMIT", 49152, "a final assistant message that ends inside an unclosed tool-call block of at least this many characters is refused (0 = no check)")
 ENV.flag("GEMM_L2_AHEAD", False, "decode-sized and grouped GEMMs request a work item's whole weight stream into L2 one "
          "item ahead (dense decode: before they wait for the kernel ahead of them; needs MSGL_PDL)")
 ENV.int("COMM_HEALTH_STEPS", 8, "the tensor-parallel ranks agree on the collectives' status word every this many steps")

@@ -58,6 +58,43 @@ class ChatMessage(BaseModel):
     reasoning_content: Optional[str] = None
 
 
+class RequestRejected(ValueError):
+    """A request field this server cannot honour: answered with 400 and the OpenAI error object
+    ``{"error": {message, type, param, code}}`` (python/minisgl/server/api_server.py:1473-1590)."""
+
+    def __init__(self, message: str, param: Optional[str] = None, code: str = "unsupported_parameter") -> None:
+        super().__init__(message)
+        self.param, self.code = param, code
+
+
+def error_body(message: str, param: Optional[str] = None, code: Optional[str] = None, detail=None) -> Dict[str, Any]:
+    body = {"error": {"message": message, "type": "invalid_request_error", "param": param, "code": code}}
+    body["detail"] = detail if detail is not None else message
+    return body
+
+
+def reject_unclosed_tool_call(messages, fmt: Optional[str]) -> Optional[RequestRejected]:
+    """A final assistant turn that ends inside a very large unclosed tool-call block is a
+    length-truncated call sent back for continuation; the model resumes the runaway and every retry
+    burns another full budget. Small truncated calls (the model can still close them) and prose that
+    merely quotes an opener pass (python/minisgl/server/api_server.py:1506-1541)."""
+    limit = ENV.TOOLCALL_CONT_LIMIT.value
+    if limit <= 0 or not messages:
+        return None
+    last = messages[-1]
+    if last.role != "assistant" or not isinstance(last.content, str) or len(last.content) < limit:
+        return None
+    scan = ToolCallStreamState(fmt=fmt)
+    scan.push(last.content)
+    if scan.in_call is None or scan.held_chars < limit:
+        return None
+    return RequestRejected(
+        f"the final assistant message ends inside an unclosed tool-call block: {scan.held_chars} characters follow "
+        f"the last {scan.in_call[0]!r} with no closer. A block this large cannot be completed by continuation; "
+        "drop the partial call (or raise max_tokens on the original request) instead of re-sending it.",
+        "messages", "unclosed_tool_call")
+
+
 class OpenAICompletionRequest(BaseModel):
     model: Optional[str] = None
     prompt: Union[str, List[int], None] = None
@@ -110,20 +147,20 @@ class OpenAICompletionRequest(BaseModel):
     @model_validator(mode="after")
     def _check(self):
         if self.messages is None and self.prompt is None:
-            raise ValueError("either `messages` or `prompt` is required")
+            raise RequestRejected("either `messages` or `prompt` is required", "messages", "missing_required_parameter")
         mt = self.max_completion_tokens if self.max_completion_tokens is not None else self.max_tokens
         if mt is not None and mt < 1:
-            raise ValueError("max_tokens must be at least 1")
+            raise RequestRejected("max_tokens must be at least 1", "max_tokens", "invalid_value")
         if self.n != 1:
-            raise ValueError("only n=1 is supported")
+            raise RequestRejected(f"n={self.n} is not supported: this server returns a single choice; send n requests", "n")
         if self.logit_bias:
-            raise ValueError("logit_bias is not supported")
+            raise RequestRejected("logit_bias is not supported by this server", "logit_bias")
         if self.echo:
-            raise ValueError("echo is not supported")
+            raise RequestRejected("echo is not supported: this server returns the completion only", "echo")
         if self.suffix:
-            raise ValueError("suffix is not supported")
+            raise RequestRejected("suffix (fill-in-the-middle) is not supported by this server", "suffix")
         if self.best_of not in (None, 1):
-            raise ValueError("best_of is not supported")
+            raise RequestRejected(f"best_of={self.best_of} is not supported: this server samples a single completion", "best_of")
         if isinstance(self.reasoning, dict):
             r = self.reasoning
             if self.reasoning_effort is None and isinstance(r.get("effort"), str):
@@ -140,7 +177,7 @@ class OpenAICompletionRequest(BaseModel):
                 on = {"enabled": True, "disabled": False}.get(str(t.get("type", "")).lower())
                 budget = t.get("budget_tokens")
                 if on is None and "type" in t:
-                    raise ValueError("thinking.type must be `enabled` or `disabled`")
+                    raise RequestRejected("thinking.type must be `enabled` or `disabled`", "thinking", "invalid_value")
             if self.enable_thinking is None and on is not None:
                 self.enable_thinking = on
             if self.reasoning_max_tokens is None and isinstance(budget, int) and budget > 0:
@@ -363,6 +400,28 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
     if tokenizer is not None:
         resolve_tool_format(tokenizer, chat_template)            # log the derived tool-call format once
     created = int(time.time())
+
+    from fastapi.exceptions import RequestValidationError
+
+    @app.exception_handler(RequestValidationError)
+    async def _invalid(request: Request, exc: RequestValidationError):
+        # one OpenAI-shaped error for a body that does not validate; the first problem names the field
+        errs = exc.errors()
+        first = errs[0] if errs else {}
+        cause = (first.get("ctx") or {}).get("error")
+        if isinstance(cause, RequestRejected):
+            msg, param, code = str(cause), cause.param, cause.code
+        else:
+            loc = [str(x) for x in first.get("loc", ()) if x != "body"]
+            msg, param, code = first.get("msg", "invalid request"), (".".join(loc) or None), "invalid_value"
+        detail = [{k: (str(v) if k == "ctx" else v) for k, v in e.items() if k != "input"} for e in errs]
+        return JSONResponse(status_code=400, content=error_body(msg, param, code, detail))
+
+    @app.exception_handler(HTTPException)
+    async def _http_error(request: Request, exc: HTTPException):
+        msg = exc.detail if isinstance(exc.detail, str) else json.dumps(exc.detail)
+        return JSONResponse(status_code=exc.status_code, content=error_body(msg, None, None, exc.detail),
+                            headers=getattr(exc, "headers", None))
 
     @app.on_event("startup")
     async def _startup() -> None:  # pragma: no cover - needs a running loop with sockets
@@ -664,6 +723,10 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
 
     @app.post("/v1/chat/completions")
     async def v1_chat_completions(req: OpenAICompletionRequest, request: Request):
+        bad = reject_unclosed_tool_call(req.messages, resolve_tool_format(tokenizer, chat_template) if (
+            tokenizer is not None or chat_template) else None)
+        if bad is not None:
+            return JSONResponse(status_code=400, content=error_body(str(bad), bad.param, bad.code))
         params = _rsa_params(req)
         if params is not None:
             return await _run_rsa(req, request, params)
@@ -671,6 +734,15 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
 
     @app.post("/v1/completions")
     async def v1_completions(req: OpenAICompletionRequest, request: Request):
+        # the raw-prompt lane: chat-only fields are errors, not silently dropped
+        for cond, msg, param in (
+                (req.messages is not None and req.prompt is None,
+                 "`messages` is not accepted by /v1/completions: this endpoint continues a raw `prompt`", "messages"),
+                (bool(req.tools), "`tools` are not supported by /v1/completions: tool specs are rendered by the chat template",
+                 "tools"),
+                (req.rsa not in (None, False), "`rsa` requires `messages` (chat format), not a raw `prompt`", "rsa")):
+            if cond:
+                return JSONResponse(status_code=400, content=error_body(msg, param, "unsupported_parameter"))
         return await _run(req, request, chat=False)
 
     return app

@@ -203,10 +203,25 @@ def test_completions_endpoint_and_validation():
     r = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 2})
     assert r.json()["choices"][0]["text"] == "xy" and r.json()["object"] == "text_completion"
     assert mgr.sent[0].text == "abc"
-    assert c.post("/v1/completions", json={"max_tokens": 2}).status_code == 422          # no prompt/messages
-    assert c.post("/v1/completions", json={"prompt": "a", "max_tokens": 0}).status_code == 422
-    assert c.post("/v1/completions", json={"prompt": "a", "n": 2}).status_code == 422
-    assert c.post("/v1/completions", json={"prompt": "a", "logit_bias": {"1": 2}}).status_code == 422
+    # what the server cannot honour is a 400 with the OpenAI error object, naming the field
+    for body, param, code in (
+            ({"max_tokens": 2}, "messages", "missing_required_parameter"),          # no prompt / messages
+            ({"prompt": "a", "max_tokens": 0}, "max_tokens", "invalid_value"),
+            ({"prompt": "a", "n": 2}, "n", "unsupported_parameter"),
+            ({"prompt": "a", "logit_bias": {"1": 2}}, "logit_bias", "unsupported_parameter"),
+            ({"prompt": "a", "best_of": 3}, "best_of", "unsupported_parameter"),
+            ({"prompt": "a", "echo": True}, "echo", "unsupported_parameter"),
+            ({"prompt": "a", "suffix": "x"}, "suffix", "unsupported_parameter"),
+            ({"prompt": "a", "temperature": "hot"}, "temperature", "invalid_value"),
+            ({"messages": [{"role": "user", "content": "hi"}]}, "messages", "unsupported_parameter"),   # raw lane
+            ({"prompt": "a", "tools": [{"type": "function", "function": {"name": "f"}}]}, "tools",
+             "unsupported_parameter"),
+            ({"prompt": "a", "rsa": True}, "rsa", "unsupported_parameter")):
+        r = c.post("/v1/completions", json=body)
+        assert r.status_code == 400, body
+        err = r.json()["error"]
+        assert err["type"] == "invalid_request_error" and err["param"] == param and err["code"] == code, (body, err)
+        assert err["message"]
     # ignored OpenAI fields are accepted
     assert c.post("/v1/completions", json={"prompt": "a", "user": "u", "store": False}).status_code == 200
     # default max_tokens applies when none is given
@@ -303,3 +318,26 @@ def test_reasoning_and_thinking_aliases_fold_into_the_canonical_fields():
     c, mgr = _client(lambda m: _words(m.uid, ["a"]))
     c.post("/v1/chat/completions", json={"messages": msgs, "thinking": {"type": "disabled"}})
     assert mgr.sent[0].chat_template_kwargs == {"enable_thinking": False}
+
+
+def test_runaway_tool_call_sent_back_for_continuation_is_refused(monkeypatch):
+    """A final assistant turn that ends inside a very large unclosed tool-call block is refused with a
+    400 that says why; a short truncated call (the model can still close it) and prose that only
+    quotes an opener pass."""
+    monkeypatch.setenv("MSGL_TOOLCALL_CONT_LIMIT", "2000")
+    c, mgr = _client(lambda m: _words(m.uid, ["ok"]))
+    user = {"role": "user", "content": "call it"}
+    runaway = "Sure.<tool_call>\n{\"name\": \"write\", \"arguments\": {\"text\": \"" + "a" * 3000
+    r = c.post("/v1/chat/completions", json={"messages": [user, {"role": "assistant", "content": runaway}]})
+    assert r.status_code == 400
+    err = r.json()["error"]
+    assert err["code"] == "unclosed_tool_call" and err["param"] == "messages" and "<tool_call>" in err["message"]
+    short = "Sure.<tool_call>\n{\"name\": \"write\", \"arguments\": {\"text\": \"abc"
+    assert c.post("/v1/chat/completions",
+                  json={"messages": [user, {"role": "assistant", "content": short}]}).status_code == 200
+    closed = "<tool_call>\n{\"name\": \"write\", \"arguments\": {}}\n</tool_call>" + "b" * 3000
+    assert c.post("/v1/chat/completions",
+                  json={"messages": [user, {"role": "assistant", "content": closed}]}).status_code == 200
+    monkeypatch.setenv("MSGL_TOOLCALL_CONT_LIMIT", "0")
+    assert c.post("/v1/chat/completions",
+                  json={"messages": [user, {"role": "assistant", "content": runaway}]}).status_code == 200

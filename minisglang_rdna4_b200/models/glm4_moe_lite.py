@@ -126,8 +126,10 @@ class GlmMoEBlock(BaseOP):
 
 
 class GlmDecoderLayer(BaseOP):
-    def __init__(self, cfg: ModelConfig, layer_id: int, dtype, device) -> None:
-        prefix = f"model.layers.{layer_id}"
+    def __init__(self, cfg: ModelConfig, layer_id: int, dtype, device, prefix: Optional[str] = None) -> None:
+        # ``prefix``: the layer's name in the checkpoint when that is not its place in the decoder
+        # (the next-token head's layer), for the quantisation scheme lookup
+        prefix = prefix or f"model.layers.{layer_id}"
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.self_attn = LatentAttention(cfg, layer_id, dtype, device, prefix + ".self_attn")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
@@ -179,9 +181,11 @@ class Glm4MoeLiteForCausalLM(BaseOP):
             if capture is not None and i in capture:
                 seen[i] = x
             x = layer.forward(x)
+        out = self.model.norm.forward(x)
         if capture is not None:
+            seen[len(self.model.layers)] = out      # "layer" num_layers: the final hidden state (the next-token head's input)
             ctx.aux_hidden = [seen[i] for i in capture]
-        return self.model.norm.forward(x)
+        return out
 
     def init_dummy(self, seed: int, std: float = 0.02, gen_device: str = "cpu") -> None:
         gen = torch.Generator(device=gen_device)

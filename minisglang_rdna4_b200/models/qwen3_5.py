@@ -125,8 +125,11 @@ class GatedDeltaNet(BaseOP):
 
 
 class HybridDecoderLayer(BaseOP):
-    def __init__(self, cfg: ModelConfig, layer_id: int, attn_id: int, gdn_id: int, dtype, device) -> None:
-        prefix = f"model.layers.{layer_id}"
+    def __init__(self, cfg: ModelConfig, layer_id: int, attn_id: int, gdn_id: int, dtype, device,
+                 prefix: Optional[str] = None) -> None:
+        # ``prefix``: the layer's name in the checkpoint when that is not its place in the decoder
+        # (the next-token head's layer), for the quantisation scheme lookup
+        prefix = prefix or f"model.layers.{layer_id}"
         self._linear = cfg.layer_types[layer_id] == "linear_attention"
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, plus_one=True)
         if self._linear:

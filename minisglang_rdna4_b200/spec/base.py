@@ -50,8 +50,10 @@ def make_proposer(config, scheduler) -> Proposer:
         return Eagle3Proposer(config, scheduler)
     if algo == "mtp":
         mc = scheduler.engine.model_config
-        if mc.mtp_num_hidden_layers > 0 and mc.attn_output_gate and mc.layer_types:
-            # the checkpoint's own head (Qwen3.5 / Qwen3-Next mtp.*)
+        qwen = mc.mtp_num_hidden_layers > 0 and mc.attn_output_gate and mc.layer_types
+        glm = mc.num_nextn_predict_layers > 0 and getattr(mc, "kv_lora_rank", 0)
+        if qwen or glm:
+            # the checkpoint's own head (Qwen3.5 / Qwen3-Next mtp.*; GLM-4.x MoE / DeepSeek model.layers.<L>)
             from .mtp import MTPProposer
 
             return MTPProposer(config, scheduler)

@@ -15,6 +15,11 @@ tensor-parallel ranks and quantised exactly like the decoder; all ranks run the 
 identical inputs. Its self-attention needs the causal context, not just the draft chain: K/V of
 the last ``WINDOW`` positions live in a per-request ring (python/minisgl/spec/mtp.py:98-140).
 
+GLM-4.x MoE / DeepSeek-V3 checkpoints store the head as decoder layer ``model.layers.<num_layers>``
+with ``enorm``, ``hnorm``, ``eh_proj`` and ``shared_head.{norm, head}``: the same fusion, a latent-
+attention layer, and the state handed to the next extrapolation step is the layer's output before
+``shared_head.norm`` (``GlmMTPDraft``).
+
 ``MTPProposer`` reuses the chain-drafting logic of the EAGLE3 proposer (features after every prefill
 and verify forward, K - 1 single-row extrapolation steps); the speculative step is the
 host-driven one.
@@ -56,33 +61,44 @@ def mtp_layer_config(cfg: ModelConfig) -> ModelConfig:
                    first_k_dense_replace=0, decoder_sparse_step=1)
 
 
-class MTPDraft(BaseOP):
-    def __init__(self, cfg: ModelConfig, dtype, device, target) -> None:
-        from ..models.qwen3_5 import HybridDecoderLayer
+def _ring_attention(q, k, v, ring, positions, scale, dtype):
+    """``q [n, hq, d]``, ``k, v [n, hk, d]`` (rotary applied) for ``n`` consecutive positions of one
+    request: writes K/V into the ring (slot = position % WINDOW) and attends causally over the last
+    ``WINDOW`` positions. Returns ``[n, hq * dv]``."""
+    n, hq, d = q.shape
+    hk = k.shape[1]
+    kr, vr = ring
+    pos = positions.long()
+    kr[pos % WINDOW] = k.float()
+    vr[pos % WINDOW] = v.float()
+    last = int(pos[-1])
+    span = torch.arange(max(0, last - WINDOW + 1), last + 1, device=q.device)
+    kk = kr[span % WINDOW].permute(1, 0, 2)                       # [hk, S, d]
+    vv = vr[span % WINDOW].permute(1, 0, 2)
+    g = hq // hk
+    qq = q.float().view(n, hk, g, d).permute(1, 2, 0, 3)          # [hk, g, n, d]
+    s = torch.einsum("hgqd,hkd->hgqk", qq, kk) * scale
+    s = s.masked_fill((span[None, :] > pos[:, None])[None, None], float("-inf"))
+    o = torch.einsum("hgqk,hkd->hgqd", torch.softmax(s, -1), vv)
+    return o.permute(2, 0, 1, 3).reshape(n, hq * vv.shape[-1]).to(dtype)
 
+
+class _MTPBase(BaseOP):
+    """State and plumbing shared by the two checkpoint layouts."""
+
+    def _setup(self, cfg: ModelConfig, dtype, device, target, ring_heads: int, ring_dim: int) -> None:
         self._cfg = cfg
         self._dtype, self._device = dtype, torch.device(device)
         self._target = target
-        h = cfg.hidden_size
-        self.pre_fc_norm_embedding = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
-        self.pre_fc_norm_hidden = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
-        self.fc = ReplicatedLinear(2 * h, h, dtype, device)
-        self._lcfg = mtp_layer_config(cfg)
-        self.layer = HybridDecoderLayer(self._lcfg, 0, 0, 0, dtype, device)
-        self.norm = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
-        tp = get_tp_info().size
-        self._hq, self._hk = div_even(cfg.num_qo_heads, tp), div_even(cfg.num_kv_heads, tp, True)
+        self._ring_shape = (WINDOW, ring_heads, ring_dim)
         self._rings: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._cos_sin = None
-        self._qk_w = None
 
-    # ---- state ----
     def ring(self, uid: int) -> Tuple[torch.Tensor, torch.Tensor]:
         r = self._rings.get(uid)
         if r is None:
-            shape = (WINDOW, self._hk, self._cfg.head_dim)
-            r = (torch.zeros(shape, dtype=torch.float32, device=self._device),
-                 torch.zeros(shape, dtype=torch.float32, device=self._device))
+            r = (torch.zeros(self._ring_shape, dtype=torch.float32, device=self._device),
+                 torch.zeros(self._ring_shape, dtype=torch.float32, device=self._device))
             self._rings[uid] = r
         return r
 
@@ -97,16 +113,44 @@ class MTPDraft(BaseOP):
             fn = getattr(mod, "init_dummy", None)
             if fn is not None:
                 fn(gen, std)
-        for mod in self.modules():
-            if isinstance(mod, RMSNorm):            # (1 + w) convention: the neutral weight is zero
-                mod.weight = torch.zeros_like(mod.weight)
+        if self._cfg.norm_plus_one:
+            for mod in self.modules():
+                if isinstance(mod, RMSNorm):        # (1 + w) convention: the neutral weight is zero
+                    mod.weight = torch.zeros_like(mod.weight)
 
-    # ---- compute ----
     def fuse_features(self, aux: Sequence[torch.Tensor]) -> torch.Tensor:
         return aux[-1]
 
     def to_target(self, draft_ids: torch.Tensor) -> torch.Tensor:
         return draft_ids
+
+    def _mlp(self, layer, h: torch.Tensor) -> torch.Tensor:
+        out = layer.mlp.forward(h)
+        if isinstance(out, tuple):                  # (y, still needs the tensor-parallel sum)
+            m, partial = out
+            return get_comm().all_reduce(m) if partial else m
+        if not layer._is_moe and get_tp_info().size > 1:
+            out = get_comm().all_reduce(out)
+        return out
+
+
+class MTPDraft(_MTPBase):
+    """Qwen3.5 / Qwen3-Next ``mtp.*``."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, target) -> None:
+        from ..models.qwen3_5 import HybridDecoderLayer
+
+        tp = get_tp_info().size
+        self._hq, self._hk = div_even(cfg.num_qo_heads, tp), div_even(cfg.num_kv_heads, tp, True)
+        self._setup(cfg, dtype, device, target, self._hk, cfg.head_dim)
+        h = cfg.hidden_size
+        self.pre_fc_norm_embedding = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
+        self.pre_fc_norm_hidden = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
+        self.fc = ReplicatedLinear(2 * h, h, dtype, device)
+        self._lcfg = mtp_layer_config(cfg)
+        self.layer = HybridDecoderLayer(self._lcfg, 0, 0, 0, dtype, device, prefix="mtp.layers.0")
+        self.norm = RMSNorm(h, cfg.rms_norm_eps, dtype, device, plus_one=True)
+        self._qk_w = None
 
     def _attention(self, uid: int, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         cfg = self._cfg
@@ -120,23 +164,11 @@ class MTPDraft(BaseOP):
         gate = attn.gate_proj.forward(x)
         q, k, v = qkv.split([hq * d, hk * d, hk * d], dim=-1)
         q, k = ref.qk_norm_rope(q, k, self._qk_w[0], self._qk_w[1], positions, self._cos_sin, d,
-                                cfg.rotary_config.rotary_dim, cfg.rms_norm_eps)
+                                cfg.rotary_config.rotary_dim, cfg.rms_norm_eps, cfg.rotary_config.interleaved)
         n = x.shape[0]
-        kr, vr = self.ring(uid)
-        pos = positions.long()
-        kr[pos % WINDOW] = k.float().view(n, hk, d)
-        vr[pos % WINDOW] = v.float().view(n, hk, d)
-        last = int(pos[-1])
-        lo = max(0, last - WINDOW + 1)
-        span = torch.arange(lo, last + 1, device=x.device)
-        kk = kr[span % WINDOW].permute(1, 0, 2)                       # [hk, S, d]
-        vv = vr[span % WINDOW].permute(1, 0, 2)
-        g = hq // hk
-        qq = q.float().view(n, hk, g, d).permute(1, 2, 0, 3)          # [hk, g, n, d]
-        s = torch.einsum("hgqd,hkd->hgqk", qq, kk) * d ** -0.5
-        s = s.masked_fill((span[None, :] > pos[:, None])[None, None], float("-inf"))
-        o = torch.einsum("hgqk,hkd->hgqd", torch.softmax(s, -1), vv).permute(2, 0, 1, 3).reshape(n, hq * d)
-        o = o.to(self._dtype) * torch.sigmoid(gate.float()).to(self._dtype)
+        o = _ring_attention(q.view(n, hq, d), k.view(n, hk, d), v.view(n, hk, d), self.ring(uid), positions,
+                            d ** -0.5, self._dtype)
+        o = o * torch.sigmoid(gate.float()).to(self._dtype)
         return attn.o_proj.forward(o, reduce=True)
 
     def forward_rows(self, uid: int, embeds: torch.Tensor, features: torch.Tensor, positions: torch.Tensor
@@ -148,47 +180,103 @@ class MTPDraft(BaseOP):
         x = self.fc.forward(torch.cat([self.pre_fc_norm_embedding.forward(embeds.to(self._dtype)),
                                        self.pre_fc_norm_hidden.forward(features.to(self._dtype))], dim=-1))
         x = x + self._attention(uid, layer.input_layernorm.forward(x), positions)
-        h = layer.post_attention_layernorm.forward(x)
-        if layer._is_moe:
-            m, partial = layer.mlp.forward(h)
-            if partial:
-                m = get_comm().all_reduce(m)
-        else:
-            m = layer.mlp.forward(h)
-            if get_tp_info().size > 1:
-                m = get_comm().all_reduce(m)
+        m = self._mlp(layer, layer.post_attention_layernorm.forward(x))
         hidden = self.norm.forward(x + m)
         return hidden, self._target.lm_head.forward(hidden[-1:])
 
 
-def mtp_tensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
-    """The checkpoint's ``mtp.*`` tensors; the decoder layer's under the names of ``model.layers.0``."""
+class _SharedHead(BaseOP):
+    def __init__(self, cfg: ModelConfig, dtype, device) -> None:
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+
+
+class GlmMTPDraft(_MTPBase):
+    """GLM-4.x MoE / DeepSeek-V3 next-token layer ``model.layers.<num_layers>``."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, target) -> None:
+        from ..models.glm4_moe_lite import GlmDecoderLayer
+
+        self._lcfg = replace(cfg, num_layers=1, first_k_dense_replace=0, mlp_only_layers=(), decoder_sparse_step=1)
+        self.layer = GlmDecoderLayer(self._lcfg, 0, dtype, device, prefix=f"model.layers.{cfg.num_layers}")
+        attn = self.layer.self_attn
+        self._setup(cfg, dtype, device, target, attn._h, attn._d)
+        h = cfg.hidden_size
+        self.enorm = RMSNorm(h, cfg.rms_norm_eps, dtype, device)
+        self.hnorm = RMSNorm(h, cfg.rms_norm_eps, dtype, device)
+        self.eh_proj = ReplicatedLinear(2 * h, h, dtype, device)
+        self.shared_head = _SharedHead(cfg, dtype, device)
+
+    def _attention(self, uid: int, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        cfg = self._cfg
+        a = self.layer.self_attn
+        t = x.shape[0]
+        h, nope, rope, d = a._h, a._nope, a._rope, a._d
+        if self._cos_sin is None:
+            self._cos_sin = get_rope_cache(cfg.rotary_config, x.device)
+        q = a.q_b_proj.forward(a.q_a_layernorm.forward(a.q_a_proj.forward(x))) if a._q_lora else a.q_proj.forward(x)
+        q = q.view(t, h, d)
+        ckv = a.kv_a_proj_with_mqa.forward(x)
+        latent, k_rot = ckv[:, : a._lora], ckv[:, a._lora:]
+        kv = a.kv_b_proj.forward(a.kv_a_layernorm.forward(latent.contiguous())).view(t, h, nope + a._vd)
+        # [rope ‖ nope] per head, as the decoder's layers lay their heads out: the rotary channels come first
+        qp = torch.cat([q[:, :, nope:], q[:, :, :nope]], dim=-1).reshape(t, h * d)
+        kp = torch.cat([k_rot[:, None, :].expand(t, h, rope), kv[:, :, :nope]], dim=-1).reshape(t, h * d)
+        qp, kp = ref.qk_norm_rope(qp, kp, None, None, positions, self._cos_sin, d, cfg.rotary_config.rotary_dim,
+                                  cfg.rms_norm_eps, cfg.rotary_config.interleaved)
+        o = _ring_attention(qp.view(t, h, d), kp.view(t, h, d), kv[:, :, nope:], self.ring(uid), positions,
+                            a.attn._scale, self._dtype)
+        return a.o_proj.forward(o, reduce=True)
+
+    def forward_rows(self, uid: int, embeds: torch.Tensor, features: torch.Tensor, positions: torch.Tensor
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """As ``MTPDraft.forward_rows``; the returned hidden state is the layer's output before
+        ``shared_head.norm`` (what the next extrapolation step is fed), the logits use the norm."""
+        layer = self.layer
+        x = self.eh_proj.forward(torch.cat([self.enorm.forward(embeds.to(self._dtype)),
+                                            self.hnorm.forward(features.to(self._dtype))], dim=-1))
+        x = x + self._attention(uid, layer.input_layernorm.forward(x), positions)
+        hidden = x + self._mlp(layer, layer.post_attention_layernorm.forward(x))
+        return hidden, self._target.lm_head.forward(self.shared_head.norm.forward(hidden[-1:]))
+
+
+def mtp_tensors(path: str, next_layer: int) -> Iterator[Tuple[str, torch.Tensor]]:
+    """The head's tensors of a checkpoint directory: ``mtp.*`` (Qwen layout) or
+    ``model.layers.<next_layer>.*`` (GLM / DeepSeek layout); the decoder layer's own tensors come
+    out under the names of ``model.layers.0``."""
     from ..models.weight import iter_safetensors
 
+    glm = f"model.layers.{next_layer}."
+    own_glm = ("enorm.", "hnorm.", "eh_proj.", "shared_head.", "embed_tokens.")
     for name, t in iter_safetensors(path):
         for lead in ("model.language_model.", "language_model."):
             if name.startswith(lead):
-                name = name[len(lead):]
+                name = ("model." if lead.startswith("model.") else "") + name[len(lead):]
         if name.startswith("model.mtp."):
             name = name[len("model."):]
-        if not name.startswith("mtp."):
-            continue
         if name.startswith("mtp.layers.0."):
             yield "model.layers.0." + name[len("mtp.layers.0."):], t
-        else:
+        elif name.startswith("mtp."):
             yield name, t
+        elif name.startswith(glm):
+            tail = name[len(glm):]
+            yield ("nextn." + tail if tail.startswith(own_glm) else "model.layers.0." + tail), t
 
 
-def load_mtp(draft: MTPDraft, path: str) -> int:
+def load_mtp(draft: _MTPBase, path: str) -> int:
     """Fill the head from the target's checkpoint directory. Returns the number of tensors used."""
     from ..models.weight import load_weights
 
-    own = {"mtp.fc.weight": (draft.fc, "weight"), "mtp.norm.weight": (draft.norm, "weight"),
-           "mtp.pre_fc_norm_embedding.weight": (draft.pre_fc_norm_embedding, "weight"),
-           "mtp.pre_fc_norm_hidden.weight": (draft.pre_fc_norm_hidden, "weight")}
+    if isinstance(draft, GlmMTPDraft):
+        own = {"nextn.eh_proj.weight": (draft.eh_proj, "weight"), "nextn.enorm.weight": (draft.enorm, "weight"),
+               "nextn.hnorm.weight": (draft.hnorm, "weight"),
+               "nextn.shared_head.norm.weight": (draft.shared_head.norm, "weight")}
+    else:
+        own = {"mtp.fc.weight": (draft.fc, "weight"), "mtp.norm.weight": (draft.norm, "weight"),
+               "mtp.pre_fc_norm_embedding.weight": (draft.pre_fc_norm_embedding, "weight"),
+               "mtp.pre_fc_norm_hidden.weight": (draft.pre_fc_norm_hidden, "weight")}
     layer_tensors: List[Tuple[str, torch.Tensor]] = []
     used = 0
-    for name, t in mtp_tensors(path):
+    for name, t in mtp_tensors(path, draft._cfg.num_layers):
         if name in own:
             mod, attr = own[name]
             cur = getattr(mod, attr)
@@ -198,6 +286,7 @@ def load_mtp(draft: MTPDraft, path: str) -> int:
             used += 1
         elif name.startswith("model.layers.0."):
             layer_tensors.append((name, t))
+        # nextn.embed_tokens / nextn.shared_head.head: copies of the target's embedding and LM head, which are used instead
     if layer_tensors:
         load_weights(_OneLayerModel(draft.layer), path, draft._lcfg, draft._device, tensors=iter(layer_tensors))
         used += len(layer_tensors)
@@ -220,7 +309,8 @@ class MTPProposer(Eagle3Proposer):
         cfg = eng.model_config
         # the head reads the target's final hidden state: "layer" num_layers of the capture list
         self.aux_layers = [cfg.num_layers]
-        self.draft = MTPDraft(cfg, eng.dtype, eng.device, eng.model)
+        glm = cfg.num_nextn_predict_layers > 0 and not cfg.mtp_num_hidden_layers
+        self.draft = (GlmMTPDraft if glm else MTPDraft)(cfg, eng.dtype, eng.device, eng.model)
         path = config.model_path
         used = 0
         if path and not getattr(config, "use_dummy_weight", False):

@@ -48,3 +48,80 @@ def test_glm4_moe_lite_matches_transformers(n_group, topk_group, q_lora):
         got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
         llm.shutdown()
     assert got == want
+
+
+def test_next_token_layer_of_the_checkpoint_drafts_exactly():
+    """``--spec-algorithm mtp`` on a checkpoint with ``num_nextn_predict_layers`` builds the layer stored
+    after the decoder (``model.layers.<L>``: enorm, hnorm, eh_proj, latent attention, experts,
+    shared_head.norm) from the target's own layer class. Its output equals a dense Hugging Face
+    restatement of the same tensors, and generation equals plain decoding."""
+    import json
+
+    from safetensors.torch import load_file, save_file
+    from transformers.models.glm4_moe_lite import modeling_glm4_moe_lite as m
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _hf(tmp)
+        cfg = hf.config
+        cfg._attn_implementation = "eager"
+        torch.manual_seed(3)
+        L = cfg.num_hidden_layers
+        layer = m.Glm4MoeLiteDecoderLayer(cfg, L - 1).float().eval()          # an expert layer, like the stored one
+        eh = torch.nn.Linear(2 * cfg.hidden_size, cfg.hidden_size, bias=False)
+        en, hn, sn = (m.Glm4MoeLiteRMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps) for _ in range(3))
+        with torch.no_grad():
+            for mod in (layer, eh, en, hn, sn):
+                for p in mod.parameters():
+                    p.copy_(torch.randn_like(p) * (0.08 if p.dim() >= 2 else 0.1) + (1.0 if p.dim() == 1 else 0.0))
+            for n, b in layer.named_buffers():
+                if "e_score_correction_bias" in n:
+                    b.copy_(torch.randn_like(b) * 0.1)
+        st = load_file(f"{tmp}/model.safetensors")
+        for k, v in layer.state_dict().items():
+            st[f"model.layers.{L}.{k}"] = v.contiguous()
+        st[f"model.layers.{L}.eh_proj.weight"] = eh.weight.detach()
+        st[f"model.layers.{L}.enorm.weight"] = en.weight.detach()
+        st[f"model.layers.{L}.hnorm.weight"] = hn.weight.detach()
+        st[f"model.layers.{L}.shared_head.norm.weight"] = sn.weight.detach()
+        st[f"model.layers.{L}.shared_head.head.weight"] = hf.lm_head.weight.detach().clone()
+        st[f"model.layers.{L}.embed_tokens.weight"] = hf.model.embed_tokens.weight.detach().clone()
+        save_file(st, f"{tmp}/model.safetensors")
+        c = json.load(open(f"{tmp}/config.json"))
+        c["num_nextn_predict_layers"] = 1
+        json.dump(c, open(f"{tmp}/config.json", "w"))
+
+        g = torch.Generator().manual_seed(2)
+        ids = torch.randint(0, 298, (1, 19), generator=g)
+        n = ids.shape[1] - 1
+        with torch.no_grad():
+            hid = hf(ids, output_hidden_states=True).hidden_states[-1][0]
+            emb = hf.model.embed_tokens(ids)[0]
+            x = eh(torch.cat([en(emb[1:]), hn(hid[:-1])], -1))[None]
+            pos = torch.arange(n)[None]
+            pe = m.Glm4MoeLiteRotaryEmbedding(cfg)(x, pos)
+            mask = torch.full((n, n), float("-inf")).triu(1)[None, None]
+            y = layer(x, position_embeddings=pe, attention_mask=mask, position_ids=pos)
+            y = (y[0] if isinstance(y, tuple) else y)[0]
+            want_logits = hf.lm_head(sn(y[-1:]))
+
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64)
+        llm = LLM(spec_algorithm="mtp", spec_num_draft=2, **kw)
+        prop = llm.proposer
+        assert type(prop).__name__ == "MTPProposer" and type(prop.draft).__name__ == "GlmMTPDraft"
+        assert prop.loaded_tensors >= 10
+        got_hidden, got_logits = prop.draft.forward_rows(-7, emb[1:], hid[:-1], torch.arange(n, dtype=torch.int32))
+        prop.draft.drop(-7)
+        assert torch.allclose(got_hidden, y, atol=2e-5), float((got_hidden - y).abs().max())
+        assert torch.allclose(got_logits, want_logits, atol=2e-5)
+        prompts = [ids[0].tolist(), torch.randint(0, 298, (9,), generator=g).tolist()]
+        sp = SamplingParams(max_tokens=12, ignore_eos=True)
+        got = [o.token_ids for o in llm.generate(prompts, sp)]
+        assert llm.stats["spec_drafted"] > 0
+        llm.shutdown()
+        plain = LLM(**kw)
+        want = [o.token_ids for o in plain.generate(prompts, sp)]
+        plain.shutdown()
+    assert got == want

@@ -60,9 +60,12 @@ class PagedAttentionBackend(BaseAttnBackend):
             prefill_plan=plan,
         )
 
-    def forward(self, q, layer: int, batch: Batch, *, scale: float, window: int = 0):
+    def forward(self, q, layer: int, batch: Batch, *, scale: float, window: int = 0, swa: bool = False):
         md = batch.attn_metadata
-        pool = get_global_ctx().kv_cache
+        ctx = get_global_ctx()
+        # a sliding-window layer with a pool of its own reads that pool through the step's second block table
+        pool = ctx.swa_kv_cache if swa else ctx.kv_cache
+        block_table = batch.swa_block_table if swa else md.block_table
         fp8 = getattr(pool, "fp8", False)
         if md.prefill_plan is not None and not window:
             from ..ops import cuda as K
@@ -70,7 +73,7 @@ class PagedAttentionBackend(BaseAttnBackend):
             k_cache = pool.k_cache(layer)
             if K.prefill_attention_tc_ok(q, k_cache, causal=md.causal, window=window, mask=md.mask, decode=False):
                 return K.prefill_attention_tc(
-                    q, k_cache, pool.v_cache(layer), md.block_table, md.prefill_plan, scale,
+                    q, k_cache, pool.v_cache(layer), block_table, md.prefill_plan, scale,
                     k_scale=pool.k_scale[layer] if fp8 else None, v_scale=pool.v_scale[layer] if fp8 else None)
         splits = 1
         if md.decode and not self.single_split and q.is_cuda:
@@ -78,7 +81,7 @@ class PagedAttentionBackend(BaseAttnBackend):
 
             splits = choose_splits(md.seq_lens.numel(), self.hk, self.max_seq_len or md.max_kv, True)
         return ops.paged_attention(
-            q, pool.k_cache(layer), pool.v_cache(layer), md.block_table, md.cu_q, md.seq_lens, scale,
+            q, pool.k_cache(layer), pool.v_cache(layer), block_table, md.cu_q, md.seq_lens, scale,
             causal=md.causal, window=window, mask=md.mask, mask_window=md.mask_window,
             k_scale=pool.k_scale[layer] if fp8 else None,
             v_scale=pool.v_scale[layer] if fp8 else None,

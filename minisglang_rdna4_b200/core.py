@@ -174,6 +174,9 @@ class Batch:
     tree_mask: Optional[torch.Tensor] = None
     # capture the hidden states of these layer indices (EAGLE3 auxiliary features)
     capture_layers: Optional[List[int]] = None
+    # sliding-window layers with a pool of their own: K/V slot of every row and block table in that pool
+    swa_out_loc: Optional[torch.Tensor] = None
+    swa_block_table: Optional[torch.Tensor] = None
 
     def __post_init__(self) -> None:
         self.padded_reqs = self.reqs
@@ -208,6 +211,8 @@ class Context:
     comm: Any = None
     aux_hidden: Optional[List[torch.Tensor]] = None
     # recurrent state of gated-delta-net layers (kvcache.gdn_state.GDNStateCache), hybrid models only
+    # K/V pool of the sliding-window layers when they have one of their own (kvcache.swa_pages)
+    swa_kv_cache: Any = None
     gdn_state: Any = None
     # speculative verify of a hybrid model: every recurrent layer appends (layer, its projected step
     # input) here, so that the state can be rebuilt for the accepted rows only (list, or None = off)

@@ -177,11 +177,35 @@ class Engine:
             ENV.KV_FP8.value or (mc.quant is not None and mc.quant.kv_cache_fp8)))
         self.kv_calibrating = bool(ENV.KV_FP8_CALIBRATE.value)
         self.kv_fp8 = bool(kv_fp8) and not self.kv_calibrating
+        # sliding-window layers in a pool of their own (MSGL_SWA_POOL): the layers are re-numbered per pool
+        self.swa = None
+        self.swa_kv_cache = None
+        self._swa_layers = 0
+        self.kv_layers = mc.num_kv_layers          # hybrid models keep K/V pages for their attention layers only
+        if ENV.SWA_POOL.value and mc.swa_layers:
+            if config.spec_algorithm != "none":
+                raise ValueError("the sliding-window pool (MSGL_SWA_POOL) does not work with speculative decoding")
+            from ..layers.attention import AttentionLayer
+
+            n_global = n_swa = 0
+            for mod in self.model.modules():
+                if isinstance(mod, AttentionLayer):
+                    if mod._window > 0:
+                        mod._swa, mod._kv_index = True, n_swa
+                        n_swa += 1
+                    else:
+                        mod._swa, mod._kv_index = False, n_global
+                        n_global += 1
+            self._swa_layers = n_swa
+            self.kv_layers = max(n_global, 1)      # a model without global layers keeps a one-layer main pool
+            self._swa_window = int(mc.sliding_window)
+            # pages a request can hold (its window, the page being written, one partly outside the window),
+            # for every request slot, plus the pages of one prefill step
+            self._swa_pages = ((config.max_running_req + 1) * (cdiv(self._swa_window, self.page_size) + 3)
+                               + cdiv(getattr(config, "max_extend_tokens", 8192), self.page_size))
         self.num_pages = self._determine_num_pages()
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
-        # hybrid models keep K/V pages for their full-attention layers only
-        self.kv_layers = mc.num_kv_layers
         self.kv_cache = MHAKVCache(
             self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
             self.dtype, self.device, fp8=self.kv_fp8,
@@ -189,20 +213,40 @@ class Engine:
         if self.kv_fp8:
             from ..kvcache.fp8_scales import resolve_kv_scales
 
-            ks, vs, source = resolve_kv_scales(config.model_path, self.kv_layers, mc.num_kv_heads, config.tp_rank,
-                                               config.tp_size)
+            ks, vs, source = resolve_kv_scales(config.model_path, mc.num_kv_layers if self._swa_layers else self.kv_layers,
+                                               mc.num_kv_heads, config.tp_rank, config.tp_size)
+            self._kv_scales = (ks, vs)
+            if self._swa_layers:                   # the scales of the layers that stay in the main pool
+                keep = [i for i in range(mc.num_kv_layers) if i not in set(mc.swa_layers)] or [0]
+                ks, vs = ks[keep], vs[keep]
             self.kv_cache.set_scales(ks, vs)
             logger.info_rank0("fp8 KV scales: %s", source)
         if self.kv_calibrating:
             self.kv_cache.start_calibration()
             logger.info_rank0("fp8 KV calibration run: 16-bit pool, eager steps")
         self.ledger.add("kv pool", self.kv_cache._buf.numel() * self.kv_cache._buf.element_size())
+        if self._swa_layers:
+            from ..kvcache.swa_pages import SwaPages
+
+            self.swa_kv_cache = MHAKVCache(self._swa_layers, self._swa_pages, self.page_size, self.kv_heads_local,
+                                           mc.head_dim, self.dtype, self.device, fp8=self.kv_fp8)
+            if self.kv_fp8:
+                ids = list(mc.swa_layers)
+                self.swa_kv_cache.set_scales(self._kv_scales[0][ids], self._kv_scales[1][ids])
+            self.swa = SwaPages(config.max_running_req + 1, self.max_pages_per_seq, self._swa_pages, self.page_size,
+                                self._swa_window, self.device)
+            assert self.swa.dummy == self.swa_kv_cache.dummy_page
+            self.ledger.add("sliding-window kv pool",
+                            self.swa_kv_cache._buf.numel() * self.swa_kv_cache._buf.element_size())
+            logger.info_rank0("sliding-window K/V pool: %d layers x %d pages (window %d), main pool %d layers",
+                              self._swa_layers, self._swa_pages, self._swa_window, self.kv_layers)
         self.boot.mark("kv pool")
         # slot max_running_req is the dummy request used to pad graph batches
         self.num_slots = config.max_running_req + 1
         self.token_pool = torch.zeros((self.num_slots, self.max_seq_len), dtype=torch.int32, device=self.device)
         self.ctx = Context(page_size=self.page_size)
         self.ctx.kv_cache = self.kv_cache
+        self.ctx.swa_kv_cache = self.swa_kv_cache
         self.gdn_state = None
         if mc.is_recurrent:
             from ..kvcache.gdn_state import GDNStateCache
@@ -400,7 +444,7 @@ class Engine:
         if cfg.num_page_override is not None:
             return int(cfg.num_page_override)
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
-        per_page = MHAKVCache.token_bytes(mc.num_kv_layers, self.kv_heads_local, mc.head_dim,
+        per_page = MHAKVCache.token_bytes(self.kv_layers, self.kv_heads_local, mc.head_dim,
                                           itemsize) * self.page_size
         if cfg.spec_algorithm in ("eagle3", "mtp"):
             # the draft head keeps one 16-bit, unsharded layer of K/V on the same page table
@@ -413,6 +457,9 @@ class Engine:
         widest = max(2 * mc.intermediate_size // cfg.tp_size, mc.q_size + 2 * mc.kv_size, mc.hidden_size * 4)
         act_reserve = chunk * widest * 2 * 4 + (2 << 30)
         budget = int(total * cfg.memory_ratio) - (total - free) - act_reserve
+        if self._swa_layers:
+            budget -= (self._swa_pages + 1) * self.page_size * MHAKVCache.token_bytes(
+                self._swa_layers, self.kv_heads_local, mc.head_dim, itemsize)
         if mc.is_recurrent:
             from ..kvcache.gdn_state import GDNStateCache
 
@@ -480,6 +527,17 @@ class Engine:
         out = [src[o : o + n] for o, n in views]
         out[5] = out[5].view(plan.block_table.shape)
         return out
+
+    def swa_arrays(self, token_idx: torch.Tensor, positions: torch.Tensor, cu_q: torch.Tensor, n_pages: int):
+        """K/V slot of every row and block table of every request in the sliding-window pool, from the
+        device copy of that pool's page table (rows of the padding request map to the dummy page)."""
+        ps = self.page_size
+        table = self.swa.table_dev
+        row_slot = (token_idx // self.max_seq_len).long()
+        pos = positions.long()
+        out_loc = (table[row_slot, pos // ps].long() * ps + pos % ps).to(torch.int32)
+        req_slot = row_slot[cu_q[:-1].long()]
+        return out_loc, table[req_slot, :n_pages].contiguous()
 
     def _out_buffer(self, n: int) -> torch.Tensor:
         """Pinned landing buffer for the sampled ids of one step (ring, see ``_stage``)."""
@@ -563,6 +621,11 @@ class Engine:
             first = cu_q[:-1].long()
             batch.gdn_slots = (token_idx[first] // self.max_seq_len).to(torch.int32)
             batch.gdn_has_state = (positions[first] > 0).to(torch.int32)
+        if self.swa is not None:
+            self.swa.flush()                       # page changes noted by the scheduler, ahead of this step
+            if not use_graph:
+                batch.swa_out_loc, batch.swa_block_table = self.swa_arrays(token_idx, positions, cu_q,
+                                                                           block_table.shape[1])
         if use_graph:
             logits = self.graph_runner.replay(bs, token_idx, positions, out_loc, seq_lens, block_table)
         else:

@@ -74,6 +74,10 @@ class GraphRunner:
         if eng.gdn_state is not None:
             batch.gdn_slots = (self.token_idx[:bs] // eng.max_seq_len).to(torch.int32)
             batch.gdn_has_state = torch.ones(bs, dtype=torch.int32, device=eng.device)
+        if eng.swa is not None:
+            # inside the graph: derived from the static inputs and the device copy of the pool's page table
+            batch.swa_out_loc, batch.swa_block_table = eng.swa_arrays(
+                self.token_idx[:bs], self.positions[:bs], self.cu_q[: bs + 1], self.block_table.shape[1])
         eng.ctx.attn_backend.prepare_metadata(
             batch, self.block_table[:bs], self.cu_q[: bs + 1], self.seq_lens[:bs], 1, eng.max_seq_len)
         with eng.ctx.forward_batch(batch):

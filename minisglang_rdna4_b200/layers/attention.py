@@ -27,6 +27,10 @@ class AttentionLayer(BaseOP):
         self._scale = scale if scale is not None else head_dim ** -0.5
         self._device = device
         self._cos_sin: Optional[torch.Tensor] = None
+        # which pool holds this layer's K/V and at which layer index: the engine re-numbers the layers
+        # when sliding-window layers get a pool of their own
+        self._swa = False
+        self._kv_index = layer_id
 
     def forward(self, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None,
                 k_norm_w: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -34,17 +38,18 @@ class AttentionLayer(BaseOP):
         batch = ctx.batch
         if self._cos_sin is None:
             self._cos_sin = get_rope_cache(self._rotary, qkv.device)
-        pool = ctx.kv_cache
-        layer = self._layer_id
+        pool = ctx.swa_kv_cache if self._swa else ctx.kv_cache
+        layer = self._kv_index
+        out_loc = batch.swa_out_loc if self._swa else batch.out_loc
         k_scale = pool.k_scale[layer] if pool.fp8 else None
         v_scale = pool.v_scale[layer] if pool.fp8 else None
         q = ops.qk_norm_rope_store(
             qkv, q_norm_w, k_norm_w,
             batch.positions, self._cos_sin, self._hq, self._hk, self._d, self._rotary.rotary_dim,
-            self._eps, pool.k_cache(layer), pool.v_cache(layer), batch.out_loc, k_scale, v_scale,
+            self._eps, pool.k_cache(layer), pool.v_cache(layer), out_loc, k_scale, v_scale,
             self._rotary.interleaved,
         )
         if getattr(pool, "amax", None) is not None:
-            pool.observe_written(layer, batch.out_loc)
-        out = ctx.attn_backend.forward(q, layer, batch, scale=self._scale, window=self._window)
+            pool.observe_written(layer, out_loc)
+        out = ctx.attn_backend.forward(q, layer, batch, scale=self._scale, window=self._window, swa=self._swa)
         return out.reshape(out.shape[0], self._hq * self._d)

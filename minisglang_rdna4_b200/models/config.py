@@ -136,6 +136,15 @@ class ModelConfig:
         return self.num_layers - self.num_linear_layers
 
     @property
+    def swa_layers(self) -> Tuple[int, ...]:
+        """Decoder layers whose attention only looks at the last ``sliding_window`` positions."""
+        if not self.sliding_window or self.is_recurrent:
+            return ()
+        if self.layer_types:
+            return tuple(i for i, t in enumerate(self.layer_types) if t == "sliding_attention")
+        return tuple(range(self.num_layers)) if self.model_type == "mistral" else ()
+
+    @property
     def recurrent_geometry(self) -> Tuple[int, int, int, int]:
         """``(conv channels, heads, rows, cols)`` of one recurrent layer's state: a convolution window
         over ``conv channels`` inputs and a ``[heads, rows, cols]`` fp32 state matrix per request."""

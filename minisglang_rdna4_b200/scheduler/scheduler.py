@@ -67,6 +67,9 @@ class Scheduler:
             self._snapshots_on = (cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0
                                   and eng.gdn_state is not None)
             cache_type = "radix_snapshot" if self._snapshots_on else "naive"
+        if eng.swa is not None:
+            # the sliding-window pool holds no K/V for a matched prefix: every request starts from an empty one
+            cache_type = "naive"
         if eng.model_config.is_recurrent and config.spec_algorithm != "none" and getattr(
                 config, "spec_tree_width", 1) > 1:
             # siblings of a draft tree would each need their own copy of the running state
@@ -301,6 +304,13 @@ class Scheduler:
                 if last > first:
                     self.cache.page_table[r.table_idx, first:last] = self.cache._take(last - first)
                 self.alloc_len[r.uid] = end
+        swa = self.engine.swa
+        if swa is not None:
+            # sliding-window pool: pages that left the window of this step's first query go back before
+            # this step's new pages are taken (earlier steps that read them are ahead on the stream)
+            for r, start, end in zip(reqs, starts.tolist(), ends.tolist()):
+                swa.trim(r.table_idx, start)
+                swa.ensure(r.table_idx, end)
         q_lens = ends - starts
         cu_q = np.zeros(b + 1, dtype=np.int32)
         np.cumsum(q_lens, out=cu_q[1:])
@@ -552,6 +562,8 @@ class Scheduler:
             return
         req.resources_freed = True
         self.decode.remove(req)
+        if self.engine.swa is not None:
+            self.engine.swa.release(req.table_idx)
         alloc = self.alloc_len.pop(req.uid, req.cache_handle.cached_len)
         # KV is valid for tokens that were both fed and known on the host
         req.cached_len = min(req.cached_len, int(req.input_ids.numel()))

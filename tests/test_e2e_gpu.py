@@ -706,3 +706,42 @@ def test_checkpoint_mtp_head_drafts_for_a_hybrid_target_on_the_gpu():
             assert llm.stats["spec_drafted"] > 0
         llm.shutdown()
     assert outs["mtp"] == outs["off"]
+
+
+def test_sliding_window_pool_reproduces_the_one_pool_engine_on_the_gpu(monkeypatch):
+    """Sliding-window layers in a pool of their own (pages recycled as they leave the window, slots and
+    block table derived on the device, inside the decode graphs too): same tokens as the engine that
+    keeps every layer's full-length K/V, eager and under graphs, with chunked prefill."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig, RotaryConfig
+
+    def cfg():
+        return ModelConfig(
+            num_layers=4, num_qo_heads=4, num_kv_heads=2, head_dim=128, hidden_size=512, vocab_size=2048,
+            intermediate_size=1024, rms_norm_eps=1e-6, hidden_act="gelu_pytorch_tanh",
+            rotary_config=RotaryConfig(head_dim=128, rotary_dim=128, max_position=2048, base=1e6),
+            model_type="gemma3_text", architectures=("Gemma3ForCausalLM",), qk_norm=True, tie_word_embeddings=True,
+            max_position_embeddings=2048, sliding_window=64, query_pre_attn_scalar=96.0, rope_local_base_freq=1e4,
+            layer_types=("sliding_attention", "full_attention", "sliding_attention", "full_attention"),
+        )
+
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    outs = {}
+    for name, env, kw in (("one pool", "0", dict()), ("swa graphs", "1", dict()),
+                          ("swa eager", "1", dict(cuda_graph_max_bs=-1, max_extend_tokens=96))):
+        monkeypatch.setenv("MSGL_SWA_POOL", env)
+        llm = LLM(model_config=cfg(), use_dummy_weight=True, device="cuda", page_size=16, max_running_req=8,
+                  num_page_override=256, seed=0, **kw)
+        assert (llm.engine.swa is not None) == (env == "1")
+        outs[name] = [o.token_ids for o in llm.generate(_prompts(), sp)]
+        if env == "1":
+            llm.engine.swa.check()
+            assert llm.engine.swa.in_use == 0 and llm.engine.swa.peak_in_use > 0
+            if name == "swa graphs":
+                assert llm.engine.graph_runner is not None and llm.engine.graph_runner.replays > 0
+        llm.shutdown()
+    assert outs["swa graphs"] == outs["one pool"]
+    # chunked prefill takes the general attention kernel for some rows the one-shot prefill gives to the
+    # tensor-core kernel: the first tokens agree, later ones may part at a near-tie
+    assert sum(a[0] == b[0] for a, b in zip(outs["swa eager"], outs["one pool"])) >= len(outs["one pool"]) - 1

@@ -47,3 +47,38 @@ def test_gemma3_matches_transformers_greedy(tmp_path):
         with torch.no_grad():
             want = hf.generate(ids, max_new_tokens=12, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(prompt):]
         assert out.token_ids == want.tolist(), (out.token_ids, want.tolist())
+
+
+def test_sliding_window_layers_in_a_pool_of_their_own(tmp_path, monkeypatch):
+    """``MSGL_SWA_POOL=1``: the sliding-window layers keep their K/V in a second pool whose pages go
+    back to its free list as they leave the window. Outputs equal the one-pool engine and the
+    reference implementation; a request never holds more than window / page + 3 pages there, however long
+    its context; every page is back when the requests are done."""
+    hf, cfg = _tiny_gemma3(tmp_path)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 150, 23, 77)]
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    kw = dict(model_path=str(tmp_path), device="cpu", page_size=16, max_running_req=4, num_page_override=128,
+              max_extend_tokens=48, seed=0, dtype="float32")
+    plain = LLM(**kw)
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    assert plain.engine.swa is None
+    plain.shutdown()
+    monkeypatch.setenv("MSGL_SWA_POOL", "1")
+    llm = LLM(**kw)
+    eng = llm.engine
+    assert eng.swa is not None and eng.kv_layers == 2 and eng.swa_kv_cache.num_layers == 2
+    assert type(llm.cache.prefix_cache).__name__ == "NaivePrefixCache"
+    got = [o.token_ids for o in llm.generate(prompts, sp)]
+    assert got == want
+    eng.swa.check()
+    assert eng.swa.in_use == 0
+    # window 16, page 16: two pages of window, the page being written, one prefill chunk of 48 tokens
+    assert eng.swa.peak_in_use <= 4 * (1 + 3) + 3, eng.swa.peak_in_use
+    ids = torch.tensor([prompts[1]])
+    with torch.no_grad():
+        ref = hf.generate(ids, max_new_tokens=40, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(prompts[1]):]
+    assert got[1] == ref.tolist()
+    llm.shutdown()
+    with pytest.raises(ValueError, match="speculative"):
+        LLM(spec_algorithm="ngram", spec_num_draft=2, **kw)

@@ -46,6 +46,8 @@ class EngineConfig:
     spec_ngram_max: int = 3
     spec_ngram_min: int = 1
     spec_tree_width: int = 1
+    # block-diffusion models: entries that override the checkpoint's generation_config.json schedule
+    diffusion_overrides: Optional[dict] = None
     # expert offload tiers
     weight_offload_gb: float = 0.0
     expert_cache_gb: float = 0.0

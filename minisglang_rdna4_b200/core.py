@@ -172,6 +172,8 @@ class Batch:
     spec_verify: bool = False
     verify_width: int = 0
     tree_mask: Optional[torch.Tensor] = None
+    # > 0: ``tree_mask`` is ``[rows, mask_window]`` and covers the last mask_window K/V positions of each request
+    mask_window: int = 0
     # capture the hidden states of these layer indices (EAGLE3 auxiliary features)
     capture_layers: Optional[List[int]] = None
     # sliding-window layers with a pool of their own: K/V slot of every row and block table in that pool

@@ -632,7 +632,8 @@ class Engine:
             batch.input_ids = self.token_pool.view(-1)[token_idx.long()]
             self.ctx.attn_backend.prepare_metadata(
                 batch, block_table, cu_q, seq_lens, plan.max_q, plan.max_kv,
-                causal=True, mask=batch.tree_mask, host_cu_q=plan.cu_q, host_seq_lens=plan.seq_lens)
+                causal=True, mask=batch.tree_mask, host_cu_q=plan.cu_q, host_seq_lens=plan.seq_lens,
+                mask_window=batch.mask_window)
             with self.ctx.forward_batch(batch):
                 hidden = self.model.forward(batch.input_ids)
                 if n_sample == 0:

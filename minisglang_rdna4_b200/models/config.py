@@ -100,6 +100,8 @@ class ModelConfig:
     rope_local_base_freq: Optional[float] = None    # RoPE base of the sliding-window layers
     num_nextn_predict_layers: int = 0
     mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
+    canvas_length: int = 0                    # block-diffusion models: tokens written per block
+    mask_token_id: Optional[int] = None       # absorbing-state diffusion models
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     torch_dtype: str = "bfloat16"
@@ -346,6 +348,8 @@ class ModelConfig:
             rope_local_base_freq=float(local_theta) if local_theta else None,
             num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
+            canvas_length=int(g("canvas_length") or g("block_length") or 0),
+            mask_token_id=g("mask_token_id"),
             eos_token_ids=eos_ids,
             bos_token_id=g("bos_token_id"),
             torch_dtype=str(g("torch_dtype") or g("dtype") or "bfloat16").replace("torch.", ""),

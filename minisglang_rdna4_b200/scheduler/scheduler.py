@@ -110,6 +110,11 @@ class Scheduler:
         self._host_stages = HostStages()
         self._dummy_slot = eng.num_slots - 1
         self._use_overlap = not (config.disable_overlap or ENV.DISABLE_OVERLAP.value) and eng.device.type == "cuda"
+        # block-diffusion models run a loop of their own (scheduler/diffusion.py)
+        from .diffusion import make_canvas_manager
+
+        self.diffusion = make_canvas_manager(self)
+        self.canvas_reqs: Dict[int, Req] = {}
         self.proposer = None
         if config.spec_algorithm != "none":
             from ..spec import make_proposer
@@ -655,6 +660,10 @@ class Scheduler:
                 from .ep import ep_lockstep_loop
 
                 ep_lockstep_loop(self)
+            elif self.diffusion is not None:
+                from .diffusion import diffusion_loop
+
+                diffusion_loop(self)
             elif self._use_overlap:
                 self.overlap_loop()
             else:

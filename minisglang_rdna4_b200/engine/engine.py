@@ -158,7 +158,28 @@ class Engine:
         else:
             from ..models.weight import load_weights
 
-            load_weights(self.model, config.model_path, self.model_config, self.device)
+            baked_dir = ENV.BAKED_DIR.value
+            loaded = None
+            if baked_dir:
+                # Stage B: this rank's weights as an earlier boot left them after loading, streamed from
+                # one flat file; Stage A (below) when there is no file for this configuration yet
+                from ..parallel.info import ep_enabled
+                from ..weights import bake
+
+                rank = config.tp_rank + config.tp_size * getattr(config, "dp_rank", 0)
+                mark = bake.fingerprint(self.model_config, config.model_path, self.dtype, config.tp_rank,
+                                        config.tp_size, ep=f"{ep_enabled()}:{getattr(config, 'dp_rank', 0)}/"
+                                                           f"{getattr(config, 'dp_size', 1)}")
+                loaded = bake.load_bake(self.model, baked_dir, rank, mark, self.device,
+                                        verify=ENV.BAKED_VERIFY.value)
+                if loaded is not None:
+                    logger.info_rank0("weights from the baked file in %s (%.2f GiB)", baked_dir, loaded / 2 ** 30)
+            if loaded is None:
+                load_weights(self.model, config.model_path, self.model_config, self.device)
+                if baked_dir:
+                    n = bake.write_bake(self.model, baked_dir, rank, mark)
+                    logger.info_rank0("baked this rank's weights into %s (%.2f GiB)", baked_dir, n / 2 ** 30)
+            self.baked_bytes = loaded
         self._configure_expert_tier()
         self.model.post_load()
         if dev_kind == "cuda":

@@ -147,6 +147,9 @@ ENV.int("RECURRENT_SNAPSHOT_MIB", 2048, "memory for recurrent-state snapshots (p
         "prefix reuse for models with recurrent layers")
 ENV.int("RECURRENT_SNAPSHOT_TOKENS", 512, "a running request's recurrent state is kept every this many tokens")
 ENV.int("RECURRENT_SNAPSHOT_HOST_MIB", 0, "keep recurrent-state snapshots in this much page-locked host memory instead of device memory (0 = on the device)")
+ENV.str("BAKED_DIR", "", "directory of baked checkpoints: a rank's weights as they stand after loading, streamed back on later "
+        "boots instead of parsing, slicing and merging the checkpoint again (written on the first boot)")
+ENV.flag("BAKED_VERIFY", False, "check every baked tensor's checksum while loading")
 ENV.flag("SWA_POOL", False, "sliding-window layers keep their K/V in a pool of their own whose pages are handed back as they "
          "leave the window (long contexts cost the full-attention layers only); no prefix reuse, no speculative decoding")
 ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-loop detector looks for; 0 = off")

@@ -268,3 +268,66 @@ def test_frame_arena_recycles_frames_first_released_first():
     arena.release(0)
     assert arena.num_free == 2
     assert arena.alloc() == 1 and arena.alloc() == 0 and arena.alloc() is None
+
+
+def test_baked_checkpoint_round_trip(tmp_path, monkeypatch):
+    """First boot with MSGL_BAKED_DIR parses the checkpoint and writes the rank's tensors to one flat
+    file; the second boot streams that file instead (same tensors, same tokens); a changed
+    checkpoint (other fingerprint) is loaded the ordinary way and re-baked; a damaged file is caught
+    by the checksums."""
+    import json
+    import os
+    import sys
+
+    import pytest
+    import torch
+
+    sys.path.insert(0, os.path.dirname(__file__))
+    from test_tp_cpu import _make_ckpt
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.weights import bake
+
+    ckpt = _make_ckpt(str(tmp_path / "ckpt"), moe=True)
+    baked = str(tmp_path / "baked")
+    monkeypatch.setenv("MSGL_BAKED_DIR", baked)
+    kw = dict(model_path=ckpt, device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
+    prompts = [[5, 6, 7, 8, 9], list(range(40, 61))]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    first = LLM(**kw)
+    assert first.engine.baked_bytes is None                         # nothing to read yet: parsed, then written
+    data, index = bake.paths(baked, 0)
+    assert os.path.isfile(data) and os.path.isfile(index)
+    meta = json.load(open(index))
+    assert all(e["offset"] % 4096 == 0 for e in meta["tensors"]) and meta["bytes"] == os.path.getsize(data)
+    want_state = {k: v.clone() for k, v in first.engine.model.state_dict().items()}
+    want = [o.token_ids for o in first.generate(prompts, sp)]
+    first.shutdown()
+
+    monkeypatch.setenv("MSGL_BAKED_VERIFY", "1")
+    second = LLM(**kw)
+    assert second.engine.baked_bytes == meta["bytes"]
+    got_state = second.engine.model.state_dict()
+    assert set(got_state) == set(want_state)
+    assert all(torch.equal(got_state[k], want_state[k]) for k in want_state)
+    assert [o.token_ids for o in second.generate(prompts, sp)] == want
+    second.shutdown()
+
+    # a flipped byte inside a tensor
+    with open(data, "r+b") as fh:
+        fh.seek(meta["tensors"][3]["offset"] + 5)
+        b = fh.read(1)
+        fh.seek(meta["tensors"][3]["offset"] + 5)
+        fh.write(bytes([b[0] ^ 0xFF]))
+    with pytest.raises(IOError, match="checksum"):
+        LLM(**kw)
+
+    # another checkpoint in the same place: the fingerprint differs, the old file is not used
+    cfg = json.load(open(os.path.join(ckpt, "config.json")))
+    cfg["rms_norm_eps"] = 2e-6
+    json.dump(cfg, open(os.path.join(ckpt, "config.json"), "w"))
+    third = LLM(**kw)
+    assert third.engine.baked_bytes is None
+    assert json.load(open(index))["fingerprint"] != meta["fingerprint"]
+    third.shutdown()

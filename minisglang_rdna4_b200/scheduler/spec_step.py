@@ -36,7 +36,7 @@ def _engine_stream(eng):
 def req_spec_ok(sched, req: Req) -> bool:
     """May this request take a speculative step? The verify step accepts by arg-max (or, with
     ``MSGL_SPEC_SAMPLED``, by rejection sampling at a plain temperature); it applies no grammar
-    mask, reasoning / tool-call gate, penalty, top-k / top-p / min-p filter, seed or logprob
+    mask, reasoning / tool-call gate, penalty, top-k / top-p / min-p filter or logprob
     capture. A request that needs any of those decodes one token at a time through the normal
     sampler (python/minisgl/scheduler/scheduler.py:3276-3293)."""
     sp = req.sampling_params
@@ -46,7 +46,14 @@ def req_spec_ok(sched, req: Req) -> bool:
         return True
     if not ENV.SPEC_SAMPLED.value:
         return False
-    return sp.top_k <= 0 and sp.top_p >= 1.0 and sp.min_p <= 0.0 and sp.seed is None
+    return sp.top_k <= 0 and sp.top_p >= 1.0 and sp.min_p <= 0.0
+
+
+def _verify_generator(sched, req: Req) -> torch.Generator:
+    seed = req.sampling_params.seed if req.sampling_params.seed is not None else sched.config.seed * 1_000_003 + req.uid
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed((int(seed) * 1_000_003 + req.num_generated) & 0x7FFFFFFFFFFFFFFF)
+    return gen
 
 
 def _plain_decode_step(sched) -> None:
@@ -227,7 +234,9 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
         if sampled and not r.sampling_params.is_greedy:
             temp = max(r.sampling_params.temperature, 1e-6)
             probs = torch.softmax(logits[cu[i]:cu[i + 1]].float() / temp, -1)
-            emitted = accept_rejection_sampling(probs, None, d)
+            # the uniforms come from a generator tied to (engine seed or request seed, request, tokens so
+            # far): every tensor-parallel rank sees the same probabilities and so keeps the same tokens
+            emitted = accept_rejection_sampling(probs, None, d, generator=_verify_generator(sched, r))
         else:
             emitted = accept_greedy(rows, d)
         emitted = emitted[: max(1, min(len(emitted), r.sampling_params.max_tokens - r.num_generated))]

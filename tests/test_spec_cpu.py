@@ -210,3 +210,24 @@ def test_sampled_and_constrained_requests_leave_the_speculative_path():
                                                               top_k=40))[0]
     obj = json.loads(ByteTokenizer().decode(out.token_ids))
     assert isinstance(obj["a"], int) and isinstance(obj["b"], bool) and llm.stats["spec_steps"] == 0
+
+
+def test_sampled_verification_is_reproducible_and_rank_independent(monkeypatch):
+    """With MSGL_SPEC_SAMPLED a plain-temperature request keeps drafts by rejection sampling. The
+    uniforms come from a generator tied to the seed, the request and its length, not from the
+    process-wide generator: two engines (as two tensor-parallel ranks would be, each with its own
+    global generator state) emit the same tokens, and another seed gives another sample."""
+    monkeypatch.setenv("MSGL_SPEC_SAMPLED", "1")
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 1024, (24,), generator=g).tolist()
+    greedy = _llm().generate([prompt], SamplingParams(max_tokens=24, ignore_eos=True))[0].token_ids
+    outs = []
+    for seed, noise in ((5, 1), (5, 2), (6, 3), (None, 4), (None, 5)):
+        torch.manual_seed(noise)                       # the global generator differs between "ranks"
+        spec = _llm(spec_algorithm="ngram", spec_num_draft=4)
+        spec.proposer = _Oracle(4, {0: greedy})
+        outs.append(spec.generate([prompt], SamplingParams(temperature=1.2, max_tokens=24, ignore_eos=True, seed=seed)
+                                  )[0].token_ids)
+        assert spec.stats["spec_steps"] > 0
+    assert outs[0] == outs[1] and outs[0] != outs[2]
+    assert outs[3] == outs[4]                          # unseeded: tied to the engine seed and the request id

@@ -100,6 +100,7 @@ class Scheduler:
         self.alloc_len: Dict[int, int] = {}      # uid -> token positions that own a KV slot
         self.prefix_len: Dict[int, int] = {}     # uid -> cached tokens at admission (reporting)
         self.finished_uids: set = set()
+        self.last_state_digests: Dict[int, dict] = {}   # uid -> digests of its last prefill step (MSGL_STATE_DIGEST)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "finished": 0,
                       "spec_drafted": 0, "spec_accepted": 0, "spec_emitted": 0, "spec_steps": 0}
         self._exit = False
@@ -358,6 +359,7 @@ class Scheduler:
         out = self.engine.forward_batch(batch, plan, args)
         if self._snapshots_on:
             self._snapshot_states(batch, plan.seq_lens.tolist())
+        digest = batch.is_prefill and ENV.STATE_DIGEST.value
         n_tok = plan.num_tokens
         if batch.is_prefill:
             self.stats["prefill_tokens"] += n_tok
@@ -370,6 +372,11 @@ class Scheduler:
                 r.cached_len = r.device_len
             else:
                 r.complete_one()
+        if digest:
+            from ..kvcache import state_digest
+
+            for r in batch.reqs:        # lengths have just moved: cached_len covers what this step computed
+                state_digest.log_request(self, r, "chunk" if isinstance(r, ChunkedReq) else "prefill")
         if batch.is_prefill:
             self.decode.add_reqs(sampled)
         self.decode.filter_finished()

@@ -94,3 +94,40 @@ def test_a_seeded_request_is_reproducible_whatever_it_is_batched_with():
         assert a != b
     finally:
         llm.shutdown()
+
+
+def test_state_digests_separate_the_reused_span_from_the_computed_one(monkeypatch):
+    """MSGL_STATE_DIGEST: after every prefill step the K/V the request holds is hashed per layer and
+    per segment of 256 positions. The same prompt prefilled twice gives the same digests; a value
+    changed in one page of one layer is named by layer and segment."""
+    import numpy as np
+
+    from minisglang_rdna4_b200.kvcache import state_digest
+
+    monkeypatch.setenv("MSGL_STATE_DIGEST", "1")
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, 500, (300,), generator=g).tolist()
+    llm = LLM(model_config=tiny_llama_config(), use_dummy_weight=True, device="cpu", page_size=16, max_running_req=8,
+              num_page_override=256, seed=0)
+    llm.generate([prompt], SamplingParams(max_tokens=2, ignore_eos=True))
+    first = llm.last_state_digests[0]
+    layers = llm.engine.kv_cache.num_layers
+    assert set(first) == {("kv", l, s) for l in range(layers) for s in (0, 1)}        # 300 positions: two segments
+    llm.generate([prompt], SamplingParams(max_tokens=2, ignore_eos=True))            # prefix-cache hit this time
+    second = llm.last_state_digests[1]
+    assert llm.cache.prefix_hit_tokens >= 288
+    # segment 0 (positions 0..255) lies inside the 288 reused positions: handed over unchanged. Segment 1 also
+    # holds the 12 positions this prefill computed itself, as a 12-row step instead of a 300-row one, whose
+    # last bits may differ: a difference may only be there
+    assert all(first[k] == second[k] for k in first if k[2] == 0)
+    diff = state_digest.first_difference(first, second)
+    assert diff is None or diff[2] == 1
+    # direct use: flip one K value of layer 1 at position 270 and name it
+    pool = llm.engine.kv_cache
+    pages = np.arange(19, dtype=np.int64)
+    before = state_digest.kv_digests(pool, pages, 300)
+    ps = pool.page_size
+    pool.k_cache(1)[270 // ps, 0, 270 % ps, 0] += 1.0
+    after = state_digest.kv_digests(pool, pages, 300)
+    assert state_digest.first_difference(before, after) == ("kv", 1, 1)
+    llm.shutdown()

@@ -50,16 +50,31 @@ def ep_lockstep_loop(sched) -> None:
                 sched._process_one_msg(msg)
         except RequestAllFinished:
             local_done = True
-        batch = sched._schedule_next_batch()
+        # a replica whose running requests can all take a speculative step proposes and plans it first, so
+        # that its row count (1 + draft length per request) goes into the agreement
+        spec = None
+        batch = None
         tokens = 0
-        if batch is not None:
-            tokens = sum(r.extend_len for r in batch.reqs)
+        if sched.proposer is not None and not sched.prefill.runnable and sched.decode.runnable:
+            from .spec_step import req_spec_ok, spec_phases
+
+            reqs = sorted(sched.decode.running.values(), key=lambda r: r.uid)
+            limit = ENV.SPEC_MAX_BS.value or sched.proposer.max_batch
+            if reqs and len(reqs) <= limit and all(req_spec_ok(sched, r) for r in reqs) and getattr(
+                    sched.proposer, "tree_width", 1) <= 1:
+                spec = spec_phases(sched, reqs)
+                tokens = next(spec)
+        if spec is None:
+            batch = sched._schedule_next_batch()
+            if batch is not None:
+                tokens = sum(r.extend_len for r in batch.reqs)
         # the status word of the peer-memory exchange rides along every few steps (the host has
         # synchronised with the device at the end of the previous step, so the read does not stall)
         poll = getattr(ep, "poll_status", None)
         status = poll() if poll is not None and steps % health_every == 0 else 0
         agree = torch.tensor([tokens, 1 if sched._exit else 0,
-                              1 if ((sched.has_work or batch is not None) and not (local_done and batch is None)) else 0,
+                              1 if ((sched.has_work or batch is not None or spec is not None)
+                                    and not (local_done and batch is None and spec is None)) else 0,
                               status], dtype=torch.int64)
         dist.all_reduce(agree, op=dist.ReduceOp.MAX, group=group)
         common, any_exit, any_work = int(agree[0]), int(agree[1]), int(agree[2])
@@ -72,6 +87,9 @@ def ep_lockstep_loop(sched) -> None:
             eng.graph_runner = None
             sched._fail_running("the expert exchange timed out; the request was ended because its state may be incomplete")
             batch = None if batch is not None and all(r.finished for r in batch.reqs) else batch
+            if spec is not None:
+                spec.close()                       # its requests were just ended: run a dummy step instead
+                spec = None
         if common == 0:
             if any_exit and not any_work:
                 break
@@ -86,9 +104,15 @@ def ep_lockstep_loop(sched) -> None:
             continue
         idle_rounds = 0
         ep.common_tokens = common
-        if batch is not None:
+        if spec is not None:
+            for _ in spec:                         # verify forward (rows exchanged with the other replicas) + acceptance
+                pass
+        elif batch is not None:
             ongoing = sched._forward(batch)
             sched._process_last_data(ongoing)
+            if sched.proposer is not None and batch.is_prefill:
+                sched._feed_prefill_features(batch)
+                sched.proposer.on_prefill(ongoing.sampled)
         else:
             _dummy_step(sched)
         ep.common_tokens = None

@@ -98,7 +98,8 @@ def device_runner(sched):
     # a tree on the device needs the draft head's ranked candidates; n-gram trees stay on the host-driven step
     # (models with recurrent layers roll their state back on the host-driven step)
     if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and (tree_width <= 1 or draft is not None)
-            and proposer.num_draft >= 1 and eng.gdn_state is None and getattr(proposer, "device_step_ok", True)):
+            and proposer.num_draft >= 1 and eng.gdn_state is None and getattr(proposer, "device_step_ok", True)
+            and not (sched.config.enable_ep and sched.config.dp_size > 1)):
         from ..spec.device import DeviceSpecRunner
 
         with _engine_stream(eng):
@@ -177,6 +178,26 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
             and not getattr(proposer, "capture_layers", None):
         _tree_decode_step(sched, reqs)
         return
+    for _ in _verify_phases(sched, proposer, reqs):
+        pass
+
+
+def spec_phases(sched, reqs: List[Req]):
+    """The host-driven chain step in two halves, for loops that have to agree on a step's row count
+    with other replicas before anybody launches (expert parallelism across replicas): the first
+    ``next()`` proposes, stages the drafts and plans the verify forward, and yields its row count;
+    exhausting the generator runs the forward and the acceptance."""
+    proposer = sched.proposer
+    with _engine_stream(sched.engine):
+        gen = _verify_phases(sched, proposer, reqs)
+        rows = next(gen)
+    yield rows
+    with _engine_stream(sched.engine):
+        for _ in gen:
+            pass
+
+
+def _verify_phases(sched, proposer, reqs: List[Req]):
     if not hasattr(sched, "_spec_width"):
         sched._spec_width = AdaptiveWidth(proposer.num_draft)
     drafts = proposer.propose(reqs)
@@ -214,6 +235,7 @@ def _spec_decode_step_on_stream(sched, proposer, reqs: List[Req]) -> None:
         rec_saved = rec.save_slots(rec_slots)
         eng.ctx.recurrent_journal = []
     try:
+        yield plan.num_tokens                     # planned; what follows launches and accepts
         out = eng.forward_batch(batch, plan, args, return_logits=True)
     finally:
         journal, eng.ctx.recurrent_journal = eng.ctx.recurrent_journal, None

@@ -267,3 +267,54 @@ def test_speculative_decoding_under_tp2_matches_plain_tp1_on_cpu():
             p.join(timeout=60)
             assert p.exitcode == 0
     assert got == want
+
+
+def _dp_spec_worker(rank, world, port, ckpt, prompts_by_rank, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    try:
+        llm = LLM(model_path=ckpt, device="cpu", dp_size=world, dp_rank=rank, page_size=16, max_running_req=4,
+                  num_page_override=64, enable_ep=True, dtype="fp32", spec_algorithm="ngram", spec_num_draft=3)
+        outs = llm.generate(prompts_by_rank[rank], SamplingParams(max_tokens=10 if rank == 0 else 4, ignore_eos=True))
+        out_q.put((rank, [o.token_ids for o in outs], dict(llm.stats), llm.engine.ctx.ep.calls))
+        llm.shutdown()
+    except Exception as exc:
+        out_q.put((rank, f"{type(exc).__name__}: {exc}", {}, 0))
+        raise
+
+
+def test_speculative_decoding_under_dp2_expert_parallel_lockstep():
+    """Replicas that share their experts agree on every step's row count before anybody launches. A
+    replica that takes a speculative step proposes and plans it first (its rows are 1 + draft length
+    per request), the others pad to the agreed count or run a dummy step; outputs equal a single
+    replica that holds all experts and decodes plainly."""
+    g = torch.Generator().manual_seed(4)
+    base = torch.randint(0, 515, (5,), generator=g).tolist()
+    prompts = [base * 4, torch.randint(0, 515, (21,), generator=g).tolist(), (base[:3] + [9]) * 5]
+    by_rank = {0: prompts[:2], 1: prompts[2:]}
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, True)
+        from minisglang_rdna4_b200 import SamplingParams
+        from minisglang_rdna4_b200.llm import LLM
+
+        llm = LLM(model_path=ckpt, device="cpu", page_size=16, max_running_req=4, num_page_override=64, dtype="fp32")
+        want = [o.token_ids for o in llm.generate(prompts[:2], SamplingParams(max_tokens=10, ignore_eos=True))]
+        want += [o.token_ids for o in llm.generate(prompts[2:], SamplingParams(max_tokens=4, ignore_eos=True))]
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 26900 + os.getpid() % 1000
+        procs = [ctx.Process(target=_dp_spec_worker, args=(r, 2, port, ckpt, by_rank, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got, stats, calls = dict(), dict(), dict()
+        for _ in procs:
+            r, toks, st, n = q.get(timeout=300)
+            got[r], stats[r], calls[r] = toks, st, n
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got[0] + got[1] == want, (got, want)
+    assert calls[0] == calls[1] > 0
+    assert stats[0]["spec_steps"] > 0 and stats[0]["spec_drafted"] > 0

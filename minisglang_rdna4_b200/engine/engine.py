@@ -224,6 +224,12 @@ class Engine:
             # for every request slot, plus the pages of one prefill step
             self._swa_pages = ((config.max_running_req + 1) * (cdiv(self._swa_window, self.page_size) + 3)
                                + cdiv(getattr(config, "max_extend_tokens", 8192), self.page_size))
+            # windows kept for prefix reuse pin pages of this pool: room for them on top
+            itemsize_ = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
+            page_bytes = self.page_size * MHAKVCache.token_bytes(n_swa, self.kv_heads_local, mc.head_dim, itemsize_)
+            self._swa_page_bytes = page_bytes
+            if config.cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0:
+                self._swa_pages += (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(page_bytes, 1)
         self.num_pages = self._determine_num_pages()
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
@@ -257,6 +263,7 @@ class Engine:
             self.swa = SwaPages(config.max_running_req + 1, self.max_pages_per_seq, self._swa_pages, self.page_size,
                                 self._swa_window, self.device)
             assert self.swa.dummy == self.swa_kv_cache.dummy_page
+            self.swa.page_nbytes = self._swa_page_bytes
             self.ledger.add("sliding-window kv pool",
                             self.swa_kv_cache._buf.numel() * self.swa_kv_cache._buf.element_size())
             logger.info_rank0("sliding-window K/V pool: %d layers x %d pages (window %d), main pool %d layers",

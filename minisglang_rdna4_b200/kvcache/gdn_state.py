@@ -74,7 +74,7 @@ class GDNStateCache:
         """Bytes of one request's state over all recurrent layers (= the size of a snapshot)."""
         return int(self.conv[:, 0].numel() * self.conv.element_size() + self.ssm[:, 0].numel() * 4)
 
-    def snapshot(self, slot: int, key, host: bool = True) -> None:
+    def snapshot(self, slot: int, key, host: bool = True, end: int = 0) -> None:
         if self._arena is not None:
             frame = self._arena.alloc()
             if frame is not None:

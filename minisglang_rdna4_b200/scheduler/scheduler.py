@@ -63,13 +63,13 @@ class Scheduler:
         self._snap_pending: Dict[int, List] = {}
         self._snap_ids = 0
         self._snapshots_on = False
-        if eng.model_config.is_recurrent:
+        # what keeps and restores per-request state at a prefix boundary: the recurrent-state cache, or the
+        # sliding-window pool (its window pages below the boundary); same interface
+        self._keeper = eng.gdn_state if eng.gdn_state is not None else eng.swa
+        if eng.model_config.is_recurrent or eng.swa is not None:
             self._snapshots_on = (cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0
-                                  and eng.gdn_state is not None)
+                                  and self._keeper is not None)
             cache_type = "radix_snapshot" if self._snapshots_on else "naive"
-        if eng.swa is not None:
-            # the sliding-window pool holds no K/V for a matched prefix: every request starts from an empty one
-            cache_type = "naive"
         if eng.model_config.is_recurrent and config.spec_algorithm != "none" and getattr(
                 config, "spec_tree_width", 1) > 1:
             # siblings of a draft tree would each need their own copy of the running state
@@ -79,19 +79,19 @@ class Scheduler:
                                   cache_type)
         if self._snapshots_on:
             pc = self.cache.prefix_cache
-            pc.capacity = max(4, (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(eng.gdn_state.slot_nbytes(), 1))
+            pc.capacity = max(4, (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(self._keeper.slot_nbytes(), 1))
             host_mib = ENV.RECURRENT_SNAPSHOT_HOST_MIB.value
-            if host_mib > 0:
+            if host_mib > 0 and eng.gdn_state is not None:
                 # snapshots in page-locked host frames: the prefix cache may keep what is left after the
                 # frames that running requests hold for boundaries not attached to the tree yet
                 frames = eng.gdn_state.attach_host_arena(host_mib << 20)
                 if frames > 0:
                     pc.capacity = max(4, frames - min(frames // 2, 6 * config.max_running_req))
-            pc.on_drop = eng.gdn_state.drop_snapshot
+            pc.on_drop = self._keeper.drop_snapshot
             every = max(ENV.RECURRENT_SNAPSHOT_TOKENS.value, eng.page_size)
             self._snap_every = (every + eng.page_size - 1) // eng.page_size * eng.page_size
-            logger.info_rank0("recurrent-state snapshots: every %d tokens and at chunk ends, up to %d kept (%.1f MiB each)",
-                              self._snap_every, pc.capacity, eng.gdn_state.slot_nbytes() / 2 ** 20)
+            logger.info_rank0("prefix-boundary state kept every %d tokens and at chunk ends, up to %d at a time (%.1f MiB each)",
+                              self._snap_every, pc.capacity, self._keeper.slot_nbytes() / 2 ** 20)
         self.decode = DecodeManager(eng.page_size)
         self.prefill = PrefillManager(self.cache, self.table, self.decode)
         self.max_seq_len = eng.max_seq_len
@@ -253,7 +253,7 @@ class Scheduler:
     def _restore_states(self, restores) -> None:
         """Prefix hits of a recurrent model: copy the snapshot of each matched boundary into the
         request's state slot, on the engine's stream ahead of the forward that continues from it."""
-        st = self.engine.gdn_state
+        st = self._keeper
         if self.engine.device.type == "cuda":
             with torch.cuda.stream(self.engine.stream):
                 for slot, key in restores:
@@ -267,7 +267,7 @@ class Scheduler:
         a reusable boundary (a page multiple at the end of a prefill chunk, or every
         ``MSGL_RECURRENT_SNAPSHOT_TOKENS`` tokens). The copies are ordered behind the step on the
         engine's stream; the ids are attached to the prefix cache when the request finishes."""
-        st = self.engine.gdn_state
+        st = self._keeper
         todo = []
         for r, end in zip(batch.reqs, ends):
             if end % self.page_size:
@@ -280,7 +280,7 @@ class Scheduler:
         def take():
             for r, end in todo:
                 self._snap_ids += 1
-                st.snapshot(r.table_idx, self._snap_ids, host=False)
+                st.snapshot(r.table_idx, self._snap_ids, host=False, end=end)
                 pend = self._snap_pending.setdefault(r.uid, [])
                 pend.append((end, self._snap_ids))
                 if len(pend) > 6:                      # keep the earliest (shared prompts) and the latest
@@ -581,7 +581,7 @@ class Scheduler:
         req.cached_len = min(req.cached_len, int(req.input_ids.numel()))
         unused = self.cache.finish_req(req, alloc, insert=insert, snapshots=self._snap_pending.pop(req.uid, None))
         for key in unused or ():
-            self.engine.gdn_state.drop_snapshot(key)
+            self._keeper.drop_snapshot(key)
         self.table.free(req.table_idx)
         self._forget_constraints(req.uid)
         self.reqs.pop(req.uid, None)

@@ -738,7 +738,9 @@ def test_sliding_window_pool_reproduces_the_one_pool_engine_on_the_gpu(monkeypat
         outs[name] = [o.token_ids for o in llm.generate(_prompts(), sp)]
         if env == "1":
             llm.engine.swa.check()
-            assert llm.engine.swa.in_use == 0 and llm.engine.swa.peak_in_use > 0
+            swa = llm.engine.swa
+            # what is still held are windows kept for prefix reuse (64 / 16 = 4 pages each)
+            assert swa.peak_in_use > 0 and swa.in_use <= 4 * swa.num_snapshots
             if name == "swa graphs":
                 assert llm.engine.graph_runner is not None and llm.engine.graph_runner.replays > 0
         llm.shutdown()

@@ -68,17 +68,34 @@ def test_sliding_window_layers_in_a_pool_of_their_own(tmp_path, monkeypatch):
     llm = LLM(**kw)
     eng = llm.engine
     assert eng.swa is not None and eng.kv_layers == 2 and eng.swa_kv_cache.num_layers == 2
-    assert type(llm.cache.prefix_cache).__name__ == "NaivePrefixCache"
+    assert type(llm.cache.prefix_cache).__name__ == "SnapshotRadixCache"
     got = [o.token_ids for o in llm.generate(prompts, sp)]
     assert got == want
     eng.swa.check()
-    assert eng.swa.in_use == 0
+    # what is still held are the windows kept for prefix reuse (two pages each at window 16, page 16)
+    assert eng.swa.in_use == int((eng.swa.refs[: eng.swa.num_pages] > 0).sum()) <= 2 * eng.swa.num_snapshots
     # window 16, page 16: two pages of window, the page being written, one prefill chunk of 48 tokens
     assert eng.swa.peak_in_use <= 4 * (1 + 3) + 3, eng.swa.peak_in_use
     ids = torch.tensor([prompts[1]])
     with torch.no_grad():
         ref = hf.generate(ids, max_new_tokens=40, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(prompts[1]):]
     assert got[1] == ref.tolist()
+    # prefix reuse: a follow-up that extends the 150-token prompt (and its answer) starts from a kept window
+    follow = prompts[1] + got[1][:20] + [7, 8, 9]
+    again = llm.generate([follow], sp)[0]
+    assert again.cached_tokens >= 96, again.cached_tokens
+    eng.swa.check()
     llm.shutdown()
+    monkeypatch.setenv("MSGL_SWA_POOL", "0")
+    plain = LLM(**kw)
+    assert plain.generate([follow], sp)[0].token_ids == again.token_ids
+    plain.shutdown()
+    monkeypatch.setenv("MSGL_SWA_POOL", "1")
+    monkeypatch.setenv("MSGL_RECURRENT_SNAPSHOT_MIB", "0")           # no kept windows: no reuse, nothing retained
+    bare = LLM(**kw)
+    assert type(bare.cache.prefix_cache).__name__ == "NaivePrefixCache"
+    assert [o.token_ids for o in bare.generate(prompts[:2], sp)] == want[:2]
+    assert bare.engine.swa.in_use == 0
+    bare.shutdown()
     with pytest.raises(ValueError, match="speculative"):
         LLM(spec_algorithm="ngram", spec_num_draft=2, **kw)

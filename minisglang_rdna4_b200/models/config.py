@@ -266,7 +266,12 @@ class ModelConfig:
         if g("kv_lora_rank"):
             # latent attention: the pool holds materialised per-head keys of qk_nope + qk_rope channels;
             # the rotary part is GPT-J interleaved unless the checkpoint says otherwise
-            head_dim = int(g("qk_nope_head_dim")) + int(g("qk_rope_head_dim"))
+            # (where the value head is narrower than that, or the width is not one the attention kernels
+            # are built for, keys, queries and values are zero-padded to a common width: DeepSeek-V2/V3's
+            # 128 + 64 key channels and 128 value channels are stored 256 wide)
+            head_dim = max(int(g("qk_nope_head_dim")) + int(g("qk_rope_head_dim")), int(g("v_head_dim") or 0))
+            if head_dim > 64 and head_dim not in (128, 256):
+                head_dim = 128 if head_dim < 128 else 256 if head_dim < 256 else head_dim
             kv_heads = heads
             rotary = RotaryConfig(head_dim=head_dim, rotary_dim=int(g("qk_rope_head_dim")), max_position=max_pos,
                                   base=theta, scaling=scaling, interleaved=bool(g("rope_interleave", True)))

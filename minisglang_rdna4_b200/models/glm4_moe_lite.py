@@ -9,8 +9,10 @@ the normalised latent into a per-head non-rotary key part and a value. A head's 
 ``[k_nope_h ‖ rope(k_rot)]`` and its query ``[q_nope_h ‖ rope(q_rot_h)]``.
 
 This implementation runs the *materialised* form: the per-head keys and values are built for the
-step's tokens and stored in the ordinary paged K/V pool (head dim = ``qk_nope + qk_rope``, which
-must equal ``v_head_dim`` as it does for GLM-4.7-Flash: 192 + 64 = 256), so every attention kernel
+step's tokens and stored in the ordinary paged K/V pool (head width = ``qk_nope + qk_rope`` = 256 =
+``v_head_dim`` for GLM-4.7-Flash; where the value heads are narrower or the width is not one the
+kernels are built for, as with DeepSeek-V2/V3's 192 key and 128 value channels, queries, keys and
+values are zero-padded to a common width, which changes no dot product), so every attention kernel
 of the engine (prefill, extend, decode, verify) serves the family unchanged. The head layout is
 permuted to ``[rope ‖ nope]`` for both queries and keys, which leaves every dot product unchanged
 and puts the rotary channels where the fused RoPE + store kernel expects them (the first
@@ -49,9 +51,10 @@ class LatentAttention(BaseOP):
         self._h = div_even(cfg.num_qo_heads, tp)
         self._nope, self._rope, self._vd = int(cfg.qk_nope_head_dim), int(cfg.qk_rope_head_dim), int(cfg.v_head_dim)
         self._d = self._nope + self._rope
-        if self._vd != self._d:
-            raise NotImplementedError(
-                f"latent attention with v_head_dim {self._vd} != qk head dim {self._d} is not supported")
+        # width of a head in the K/V pool: keys / queries (nope + rope channels) and values zero-padded to it
+        self._pd = int(cfg.head_dim)
+        if self._pd < max(self._d, self._vd):
+            raise ValueError(f"pool head width {self._pd} below the latent-attention head ({self._d}, {self._vd})")
         self._lora = int(cfg.kv_lora_rank)
         if cfg.q_lora_rank:
             self.q_a_proj = ReplicatedLinear(cfg.hidden_size, int(cfg.q_lora_rank), dtype, device,
@@ -76,7 +79,7 @@ class LatentAttention(BaseOP):
         if sc.get("rope_type", sc.get("type", "default")) not in ("default", None) and sc.get("mscale_all_dim"):
             m = _mscale(float(sc.get("factor", 1.0)), float(sc["mscale_all_dim"]))
             scale = scale * m * m
-        self.attn = AttentionLayer(layer_id, self._h, self._h, self._d, cfg.rotary_config, cfg.rms_norm_eps, dtype,
+        self.attn = AttentionLayer(layer_id, self._h, self._h, self._pd, cfg.rotary_config, cfg.rms_norm_eps, dtype,
                                    device, scale=scale)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -91,13 +94,17 @@ class LatentAttention(BaseOP):
         latent, k_rot = ckv[:, : self._lora], ckv[:, self._lora:]
         kv = self.kv_b_proj.forward(self.kv_a_layernorm.forward(latent.contiguous())).view(t, h, nope + self._vd)
         # [rope ‖ nope] layout for q and k (the same permutation on both sides of every dot product)
-        qkv = torch.empty((t, 3 * h, d), dtype=x.dtype, device=x.device)
+        pd, vd = self._pd, self._vd
+        padded = pd != d or pd != vd
+        qkv = (torch.zeros if padded else torch.empty)((t, 3 * h, pd), dtype=x.dtype, device=x.device)
         qkv[:, :h, :rope] = q[:, :, nope:]
-        qkv[:, :h, rope:] = q[:, :, :nope]
+        qkv[:, :h, rope:d] = q[:, :, :nope]
         qkv[:, h:2 * h, :rope] = k_rot[:, None, :]
-        qkv[:, h:2 * h, rope:] = kv[:, :, :nope]
-        qkv[:, 2 * h:] = kv[:, :, nope:]
-        o = self.attn.forward(qkv.view(t, 3 * h * d))
+        qkv[:, h:2 * h, rope:d] = kv[:, :, :nope]
+        qkv[:, 2 * h:, :vd] = kv[:, :, nope:]
+        o = self.attn.forward(qkv.view(t, 3 * h * pd))
+        if pd != vd:                               # the padding channels of the value heads come back as zeros
+            o = o.view(t, h, pd)[:, :, :vd].reshape(t, h * vd)
         return self.o_proj.forward(o, reduce=True)
 
 

@@ -223,8 +223,12 @@ class GlmMTPDraft(_MTPBase):
         kp = torch.cat([k_rot[:, None, :].expand(t, h, rope), kv[:, :, :nope]], dim=-1).reshape(t, h * d)
         qp, kp = ref.qk_norm_rope(qp, kp, None, None, positions, self._cos_sin, d, cfg.rotary_config.rotary_dim,
                                   cfg.rms_norm_eps, cfg.rotary_config.interleaved)
-        o = _ring_attention(qp.view(t, h, d), kp.view(t, h, d), kv[:, :, nope:], self.ring(uid), positions,
-                            a.attn._scale, self._dtype)
+        v = kv[:, :, nope:]
+        if a._vd < d:                              # one ring shape for K and V: narrower values are zero-padded
+            v = torch.cat([v, v.new_zeros((t, h, d - a._vd))], dim=-1)
+        o = _ring_attention(qp.view(t, h, d), kp.view(t, h, d), v, self.ring(uid), positions, a.attn._scale, self._dtype)
+        if a._vd < d:
+            o = o.view(t, h, d)[:, :, : a._vd].reshape(t, h * a._vd)
         return a.o_proj.forward(o, reduce=True)
 
     def forward_rows(self, uid: int, embeds: torch.Tensor, features: torch.Tensor, positions: torch.Tensor

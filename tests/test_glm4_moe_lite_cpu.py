@@ -125,3 +125,46 @@ def test_next_token_layer_of_the_checkpoint_drafts_exactly():
         want = [o.token_ids for o in plain.generate(prompts, sp)]
         plain.shutdown()
     assert got == want
+
+
+def test_deepseek_v3_with_narrower_value_heads_matches_transformers():
+    """DeepSeek-V3 geometry: the value heads (16 here, 128 in the released models) are narrower than
+    the key heads (nope + rope = 32 here, 192 there). Queries, keys and values are zero-padded to one
+    width in the paged pool, which changes no dot product; the padding channels of the output are dropped
+    before the output projection."""
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.models.config import ModelConfig
+
+    cfg = DeepseekV3Config(
+        vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=2.5,
+        kv_lora_rank=32, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=24, n_group=2,
+        topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1, max_position_embeddings=512, eos_token_id=299,
+        bos_token_id=None, pad_token_id=None)
+    torch.manual_seed(0)
+    hf = DeepseekV3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+    # the released geometry is stored 256 wide (192 key channels, 128 value channels)
+    real = ModelConfig.from_hf(dict(cfg.to_dict(), qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                                    num_attention_heads=16, hidden_size=512, kv_lora_rank=512, q_lora_rank=None))
+    assert real.head_dim == 256 and real.rotary_config.rotary_dim == 64
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (5, 23, 41)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=32)
+        assert llm.engine.model_config.head_dim == 32
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+        llm.shutdown()
+    assert got == want

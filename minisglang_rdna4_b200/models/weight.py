@@ -207,20 +207,38 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             gdn = modules.get(block + ".linear_attn")
             if gdn is None:
                 continue
-            if tail in ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight"):
-                part = ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight").index(tail)
+            if tail in ("in_proj_qkvz.weight", "in_proj_ba.weight"):
+                # Qwen3-Next stores the projections grouped per key head: [q ‖ k ‖ v of its value heads ‖ z of
+                # them] and [b ‖ a of its value heads]; regroup into the per-kind blocks the layer uses
+                hk_, dk_, dv_ = cfg.linear_num_key_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+                r_ = cfg.linear_num_value_heads // hk_
+                w = tensor.view(hk_, -1, tensor.shape[-1])
+                if tail == "in_proj_qkvz.weight":
+                    q_, k_, v_, z_ = w.split([dk_, dk_, r_ * dv_, r_ * dv_], dim=1)
+                    flat = lambda t_: t_.reshape(-1, tensor.shape[-1])          # noqa: E731
+                    pieces = {0: torch.cat([flat(q_), flat(k_), flat(v_)]), 1: flat(z_)}
+                else:
+                    b_, a_ = w.split([r_, r_], dim=1)
+                    pieces = {2: b_.reshape(-1, tensor.shape[-1]), 3: a_.reshape(-1, tensor.shape[-1])}
+            elif tail in ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight"):
+                pieces = {("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight").index(tail):
+                          tensor}
+            else:
+                pieces = None
+            if pieces is not None:
                 key = block + ".linear_attn.in_proj.weight"
                 qk, vv, hv = cfg.linear_num_key_heads * cfg.linear_key_head_dim, \
                     cfg.linear_num_value_heads * cfg.linear_value_head_dim, cfg.linear_num_value_heads
-                tensor = shard_segments(tensor, ([qk, qk, vv], [vv], [hv], [hv])[part])
-                col = pending.setdefault(key, _Collector(4))
-                if col.add(part, tensor):
-                    w = col.cat(0)
-                    rows = gdn.in_proj.weight.shape[0]
-                    if w.shape[0] < rows:   # the projection is padded to a multiple of 8 output columns
-                        w = torch.cat([w, w.new_zeros((rows - w.shape[0], w.shape[1]))])
-                    assign(gdn.in_proj, "weight", w, key)
-                    del pending[key]
+                for part, piece in pieces.items():
+                    piece = shard_segments(piece.contiguous(), ([qk, qk, vv], [vv], [hv], [hv])[part])
+                    col = pending.setdefault(key, _Collector(4))
+                    if col.add(part, piece):
+                        w = col.cat(0)
+                        rows = gdn.in_proj.weight.shape[0]
+                        if w.shape[0] < rows:   # the projection is padded to a multiple of 8 output columns
+                            w = torch.cat([w, w.new_zeros((rows - w.shape[0], w.shape[1]))])
+                        assign(gdn.in_proj, "weight", w, key)
+                        del pending[key]
             elif tail == "conv1d.weight":
                 qk = cfg.linear_num_key_heads * cfg.linear_key_head_dim
                 vv = cfg.linear_num_value_heads * cfg.linear_value_head_dim

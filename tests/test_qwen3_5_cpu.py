@@ -339,3 +339,43 @@ def test_checkpoint_mtp_head_matches_a_dense_restatement_and_drafts_exactly(moe,
         want = [o.token_ids for o in plain.generate(prompts, sp)]
         plain.shutdown()
     assert got == want
+
+
+def test_qwen3_next_grouped_projections_match_transformers():
+    """Qwen3-Next stores the linear-attention input projections grouped per key head
+    (``in_proj_qkvz``: q ‖ k ‖ v ‖ z of one key head's value heads; ``in_proj_ba``); the loader regroups
+    them into the per-kind blocks of the layer. Greedy decoding equals the Hugging Face model."""
+    from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    cfg = Qwen3NextConfig(
+        vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=16,
+        linear_num_key_heads=2, linear_num_value_heads=4, max_position_embeddings=512, rms_norm_eps=1e-6,
+        tie_word_embeddings=False, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=8,
+        num_experts_per_tok=2, eos_token_id=299, pad_token_id=None, bos_token_id=None, decoder_sparse_step=1,
+        mlp_only_layers=[])
+    torch.manual_seed(0)
+    hf = Qwen3NextForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if name.endswith("norm.weight") and "linear_attn" not in name:
+                p.copy_(torch.randn_like(p) * 0.1)
+            elif "A_log" in name:
+                p.copy_(torch.log(torch.empty_like(p).uniform_(1.0, 8.0)))
+            elif "dt_bias" in name:
+                p.copy_(torch.randn_like(p) * 0.5)
+            elif p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (5, 23, 41)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=16)
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+        llm.shutdown()
+    assert got == want

@@ -377,6 +377,7 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma3": ["Gemma3ForCausalLM"],
         "gemma3_text": ["Gemma3ForCausalLM"],
         "glm4_moe_lite": ["Glm4MoeLiteForCausalLM"],
+        "glm4_moe": ["Glm4MoeForCausalLM"],
         "deepseek_v2": ["DeepseekV2ForCausalLM"],
         "deepseek_v3": ["DeepseekV3ForCausalLM"],
         "qwen3_5": ["Qwen3_5ForCausalLM"],

@@ -122,7 +122,14 @@ class DecoderLayer(BaseOP):
         self.self_attn = SelfAttention(cfg, layer_id, dtype, device, prefix + ".self_attn")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self._is_moe = cfg.layer_is_moe(layer_id)
-        if self._is_moe:
+        # GLM-4.5-style experts: sigmoid scores with a selection bias, group-limited routing, shared experts
+        # (the block of models/glm4_moe_lite.py, which sums over the tensor-parallel ranks itself)
+        self._glm_moe = self._is_moe and cfg.model_type == "glm4_moe"
+        if self._glm_moe:
+            from .glm4_moe_lite import GlmMoEBlock
+
+            self.mlp = GlmMoEBlock(cfg, dtype, device, prefix + ".mlp")
+        elif self._is_moe:
             self.mlp = SparseMoEBlock(cfg, dtype, device, prefix + ".mlp")
         else:
             self.mlp = GatedMLP(cfg, cfg.intermediate_size, dtype, device, prefix + ".mlp")
@@ -133,6 +140,8 @@ class DecoderLayer(BaseOP):
         h = self.self_attn.forward(h)
         if self._is_moe:
             h, residual = self.post_attention_layernorm.forward_fused(h, residual, partial=True)
+            if self._glm_moe:
+                return self.mlp.forward(h), residual, False
             h, part = self.mlp.forward(h)
             return h, residual, part
         h, residual = self.post_attention_layernorm.forward_fused(

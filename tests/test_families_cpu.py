@@ -25,6 +25,12 @@ FAMILIES = {
     "gemma2": ("Gemma2Config", "Gemma2ForCausalLM",
                dict(head_dim=16, sliding_window=16, query_pre_attn_scalar=16, final_logit_softcapping=30.0,
                     attn_logit_softcapping=50.0, tie_word_embeddings=True)),
+    # GLM-4.5: partial rotary embedding, q/k/v biases, optional QK norm, sigmoid routing with a selection bias,
+    # routing groups, a shared expert, a dense first layer
+    "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM",
+                 dict(head_dim=32, moe_intermediate_size=32, n_shared_experts=1, n_routed_experts=8,
+                      routed_scaling_factor=1.7, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+                      use_qk_norm=True, attention_bias=True)),
 }
 
 
@@ -47,6 +53,9 @@ def test_family_matches_transformers(family):
                 p.copy_(torch.randn_like(p) * 0.1)
             elif "norm" in name:                  # away from the neutral weight (zero for the (1 + w) families)
                 p.copy_(0.1 * torch.randn_like(p) + (0.0 if family.startswith("gemma") else 1.0))
+        for name, b in hf.named_buffers():
+            if "e_score_correction_bias" in name:
+                b.copy_(torch.randn_like(b) * 0.1)
     with tempfile.TemporaryDirectory() as tmp:
         hf.save_pretrained(tmp, safe_serialization=True)
         g = torch.Generator().manual_seed(1)

@@ -323,7 +323,8 @@ class ModelConfig:
             routed_scaling_factor=float(g("routed_scaling_factor") or 1.0),
             scoring_func=g("scoring_func", "sigmoid" if model_type in ("glm4_moe_lite", "glm4_moe", "deepseek_v3")
                            else "softmax"),
-            n_group=int(g("n_group") or 1),
+            # DeepSeek-V2's plain "greedy" top-k ignores the routing groups its config still lists
+            n_group=1 if g("topk_method") == "greedy" else int(g("n_group") or 1),
             topk_group=int(g("topk_group") or 1),
             kv_lora_rank=g("kv_lora_rank"),
             q_lora_rank=g("q_lora_rank"),

@@ -112,8 +112,9 @@ class GlmMoEBlock(BaseOP):
     def __init__(self, cfg: ModelConfig, dtype, device, prefix: str) -> None:
         self.experts = MoELayer(
             cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts, cfg.num_experts_per_tok, cfg.norm_topk_prob,
-            dtype, device, "sigmoid", cfg.routed_scaling_factor, _scheme(cfg, prefix + ".experts"),
-            n_group=cfg.n_group, topk_group=cfg.topk_group, selection_bias=True,
+            dtype, device, cfg.scoring_func, cfg.routed_scaling_factor, _scheme(cfg, prefix + ".experts"),
+            # DeepSeek-V2 scores with a softmax and has no selection bias; V3 / GLM use sigmoid scores and one
+            n_group=cfg.n_group, topk_group=cfg.topk_group, selection_bias=cfg.scoring_func == "sigmoid",
         )
         self._shared = cfg.n_shared_experts > 0
         if self._shared:

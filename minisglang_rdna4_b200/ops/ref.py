@@ -372,12 +372,15 @@ def moe_route_grouped(router_logits: torch.Tensor, top_k: int, renormalize: bool
                       ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Group-limited routing (DeepSeek-V3 / GLM-4 MoE): experts are split into ``n_group`` groups,
     a group's score is the sum of its two best choice scores, only the best ``topk_group`` groups
-    stay eligible, then top-k over the eligible experts; weights are the un-biased scores."""
+    stay eligible, then top-k over the eligible experts; weights are the un-biased scores.
+    Without a selection bias (DeepSeek-V2's ``group_limited_greedy``) a group's score is its best
+    expert's score."""
     g = router_logits.float()
     scores = torch.softmax(g, dim=-1) if scoring == "softmax" else torch.sigmoid(g)
     choice = scores + bias.float() if bias is not None else scores
     t, e = choice.shape
-    group_scores = choice.view(t, n_group, e // n_group).topk(2, dim=-1)[0].sum(-1)
+    grouped = choice.view(t, n_group, e // n_group)
+    group_scores = grouped.max(-1)[0] if bias is None else grouped.topk(2, dim=-1)[0].sum(-1)
     keep = torch.zeros_like(group_scores)
     keep.scatter_(1, group_scores.topk(topk_group, dim=-1, sorted=False)[1], 1.0)
     mask = keep[:, :, None].expand(t, n_group, e // n_group).reshape(t, e).bool()

@@ -168,3 +168,47 @@ def test_deepseek_v3_with_narrower_value_heads_matches_transformers():
         got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
         llm.shutdown()
     assert got == want
+
+
+def test_deepseek_v2_softmax_routing_matches_transformers():
+    """DeepSeek-V2: the same latent attention, experts scored with a softmax and no selection bias,
+    plain top-k (``topk_method: greedy`` ignores the groups the config lists), weights times the
+    routed scaling factor without renormalisation."""
+    from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.ops import ref
+
+    cfg = DeepseekV2Config(
+        vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=1.3,
+        kv_lora_rank=32, q_lora_rank=None, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=24, n_group=2,
+        topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1, topk_method="greedy", norm_topk_prob=False,
+        max_position_embeddings=512, eos_token_id=299, bos_token_id=None, pad_token_id=None)
+    torch.manual_seed(0)
+    hf = DeepseekV2ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(3, 298, (n,), generator=g).tolist() for n in (5, 41, 23)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0
+                            )[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=32)
+        mc = llm.engine.model_config
+        assert mc.scoring_func == "softmax" and mc.n_group == 1
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))]
+        llm.shutdown()
+    assert got == want
+    # group_limited_greedy: a group is as good as its best expert; only the best groups' experts are eligible
+    logits = torch.tensor([[3.0, 0.0, 0.0, 0.0, 2.9, 2.8, 2.7, 2.6]])
+    w, ids = ref.moe_route_grouped(logits, 2, False, "softmax", None, 1.0, n_group=2, topk_group=1)
+    assert min(ids[0].tolist()) == 0 and max(ids[0].tolist()) < 4     # the first group holds the single best expert
+    bias = torch.zeros(8)
+    w2, ids2 = ref.moe_route_grouped(logits, 2, False, "softmax", bias, 1.0, n_group=2, topk_group=1)
+    assert min(ids2[0].tolist()) >= 4               # with a selection bias: the sum of the two best decides

@@ -14,7 +14,7 @@ def _register_defaults() -> None:
 
     for arch in (
         "LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM",
-        "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "Glm4MoeForCausalLM",
+        "Qwen2MoeForCausalLM", "Qwen3MoeForCausalLM", "Glm4MoeForCausalLM", "MixtralForCausalLM",
     ):
         if arch not in MODEL_REGISTRY:
             MODEL_REGISTRY.register(arch)(CausalLM)

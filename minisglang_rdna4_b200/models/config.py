@@ -311,7 +311,8 @@ class ModelConfig:
             qk_norm=qk_norm,
             num_experts=num_experts,
             num_experts_per_tok=int(g("num_experts_per_tok") or 0),
-            moe_intermediate_size=int(g("moe_intermediate_size") or 0),
+            # Mixtral's experts have the width its config calls intermediate_size
+            moe_intermediate_size=int(g("moe_intermediate_size") or (g("intermediate_size") if model_type == "mixtral" else 0) or 0),
             norm_topk_prob=bool(g("norm_topk_prob", True)),
             shared_expert_intermediate_size=int(g("shared_expert_intermediate_size") or 0),
             # a sigmoid gate on the shared expert's output: Qwen2-MoE and the Qwen3.5 / Qwen3-Next MoE blocks
@@ -370,6 +371,7 @@ def _default_arch(model_type: str) -> List[str]:
     return {
         "llama": ["LlamaForCausalLM"],
         "mistral": ["MistralForCausalLM"],
+        "mixtral": ["MixtralForCausalLM"],
         "qwen2": ["Qwen2ForCausalLM"],
         "qwen2_moe": ["Qwen2MoeForCausalLM"],
         "qwen3": ["Qwen3ForCausalLM"],

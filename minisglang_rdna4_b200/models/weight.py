@@ -144,6 +144,11 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
     for name, tensor in stream:
         if _DROP.search(name):
             continue
+        if ".block_sparse_moe." in name:
+            # Mixtral: experts under block_sparse_moe with w1 / w3 / w2 for gate / up / down
+            name = name.replace(".block_sparse_moe.", ".mlp.")
+            for short, full in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):
+                name = name.replace(short, full)
         if name.startswith("language_model."):
             name = name[len("language_model."):]
         if name.startswith("model.language_model."):

@@ -25,6 +25,8 @@ FAMILIES = {
     "gemma2": ("Gemma2Config", "Gemma2ForCausalLM",
                dict(head_dim=16, sliding_window=16, query_pre_attn_scalar=16, final_logit_softcapping=30.0,
                     attn_logit_softcapping=50.0, tie_word_embeddings=True)),
+    "mixtral": ("MixtralConfig", "MixtralForCausalLM",
+                dict(head_dim=16, intermediate_size=96, num_local_experts=8, num_experts_per_tok=2, sliding_window=None)),
     # GLM-4.5: partial rotary embedding, q/k/v biases, optional QK norm, sigmoid routing with a selection bias,
     # routing groups, a shared expert, a dense first layer
     "glm4_moe": ("Glm4MoeConfig", "Glm4MoeForCausalLM",

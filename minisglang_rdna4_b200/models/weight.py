@@ -149,10 +149,13 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
             name = name.replace(".block_sparse_moe.", ".mlp.")
             for short, full in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):
                 name = name.replace(short, full)
-        if name.startswith("language_model."):
-            name = name[len("language_model."):]
-        if name.startswith("model.language_model."):
-            name = "model." + name[len("model.language_model."):]
+        # the text decoder of a multimodal checkpoint: language_model.model.*, model.language_model.* or
+        # model.language_model.model.* depending on the exporting version
+        for lead in ("model.language_model.", "language_model."):
+            if name.startswith(lead):
+                rest = name[len(lead):]
+                name = rest if rest.startswith(("model.", "lm_head.")) else "model." + rest
+                break
         if name.startswith("model.visual."):
             continue
         # ---- Nemotron-H (Mamba-2 hybrid): backbone.* names, one "mixer" per layer

@@ -99,3 +99,37 @@ def test_sliding_window_layers_in_a_pool_of_their_own(tmp_path, monkeypatch):
     bare.shutdown()
     with pytest.raises(ValueError, match="speculative"):
         LLM(spec_algorithm="ngram", spec_num_draft=2, **kw)
+
+
+def test_multimodal_gemma3_checkpoint_serves_its_text_decoder(tmp_path):
+    """A ``Gemma3ForConditionalGeneration`` checkpoint (nested ``text_config``, tensors under
+    ``model.language_model.*``, a vision tower and projector that are skipped) loads as the text
+    decoder and generates what the Hugging Face model generates from token ids."""
+    try:
+        from transformers import Gemma3Config, Gemma3ForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers build has no Gemma3 multimodal model")
+    tc = dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, max_position_embeddings=512, rms_norm_eps=1e-6, sliding_window=16,
+              query_pre_attn_scalar=48, rope_theta=1e6, rope_local_base_freq=1e4,
+              layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+              tie_word_embeddings=True, pad_token_id=0, bos_token_id=2, eos_token_id=1)
+    vc = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=28, patch_size=14)
+    cfg = Gemma3Config(text_config=tc, vision_config=vc, mm_tokens_per_image=4, image_token_index=500,
+                       boi_token_index=501, eoi_token_index=502)
+    torch.manual_seed(0)
+    hf = Gemma3ForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if "norm" in name:
+                p.copy_(0.1 * torch.randn_like(p))
+    hf.save_pretrained(tmp_path, safe_serialization=True)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 490, (n,), generator=g).tolist() for n in (9, 40)]
+    want = [hf.generate(input_ids=torch.tensor([p]), max_new_tokens=8, do_sample=False, eos_token_id=None,
+                        pad_token_id=0)[0, len(p):].tolist() for p in prompts]
+    llm = LLM(model_path=str(tmp_path), device="cpu", page_size=16, max_running_req=4, num_page_override=64,
+              max_extend_tokens=32, dtype="float32")
+    got = [o.token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))]
+    llm.shutdown()
+    assert got == want

@@ -204,8 +204,10 @@ class Engine:
         self._swa_layers = 0
         self.kv_layers = mc.num_kv_layers          # hybrid models keep K/V pages for their attention layers only
         if ENV.SWA_POOL.value and mc.swa_layers:
-            if config.spec_algorithm != "none":
-                raise ValueError("the sliding-window pool (MSGL_SWA_POOL) does not work with speculative decoding")
+            if config.spec_algorithm != "none" and getattr(config, "spec_tree_width", 1) > 1:
+                # a tree's attention mask replaces the window rule of the sliding layers
+                raise ValueError("the sliding-window pool (MSGL_SWA_POOL) does not work with tree verification; "
+                                 "use a draft chain (spec tree width 1)")
             from ..layers.attention import AttentionLayer
 
             n_global = n_swa = 0

@@ -152,7 +152,7 @@ ENV.str("BAKED_DIR", "", "directory of baked checkpoints: a rank's weights as th
         "boots instead of parsing, slicing and merging the checkpoint again (written on the first boot)")
 ENV.flag("BAKED_VERIFY", False, "check every baked tensor's checksum while loading")
 ENV.flag("SWA_POOL", False, "sliding-window layers keep their K/V in a pool of their own whose pages are handed back as they "
-         "leave the window (long contexts cost the full-attention layers only); no prefix reuse, no speculative decoding")
+         "leave the window (long contexts cost the full-attention layers only)")
 ENV.int("THINK_LOOP_PERIOD", 64, "longest repeated block (tokens) the reasoning-loop detector looks for; 0 = off")
 ENV.int("THINK_LOOP_SPAN", 48, "a reasoning loop is reported once this many consecutive tokens repeat")
 ENV.int("THINK_LOOP_REPS", 3, "... and the block has repeated this many times")

@@ -98,7 +98,8 @@ def device_runner(sched):
     # a tree on the device needs the draft head's ranked candidates; n-gram trees stay on the host-driven step
     # (models with recurrent layers roll their state back on the host-driven step)
     if (eng.device.type == "cuda" and not ENV.SPEC_HOST_STEP.value and (tree_width <= 1 or draft is not None)
-            and proposer.num_draft >= 1 and eng.gdn_state is None and getattr(proposer, "device_step_ok", True)
+            and proposer.num_draft >= 1 and eng.gdn_state is None and eng.swa is None
+            and getattr(proposer, "device_step_ok", True)
             and not (sched.config.enable_ep and sched.config.dp_size > 1)):
         from ..spec.device import DeviceSpecRunner
 
@@ -335,6 +336,13 @@ def _verify_plan(sched, batch: Batch, drafts):
             if last > first:
                 sched.cache.page_table[r.table_idx, first:last] = sched.cache._take(last - first)
             sched.alloc_len[r.uid] = end
+    swa = sched.engine.swa
+    if swa is not None:
+        # sliding-window pool: as in Scheduler._make_plan; pages of rejected draft rows simply stay with the
+        # request and are written again when those positions are fed the next time
+        for r, start, end in zip(reqs, starts.tolist(), ends.tolist()):
+            swa.trim(r.table_idx, start)
+            swa.ensure(r.table_idx, end)
     q_lens = ends - starts
     cu_q = np.zeros(b + 1, dtype=np.int32)
     np.cumsum(q_lens, out=cu_q[1:])

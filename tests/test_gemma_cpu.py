@@ -97,8 +97,20 @@ def test_sliding_window_layers_in_a_pool_of_their_own(tmp_path, monkeypatch):
     assert [o.token_ids for o in bare.generate(prompts[:2], sp)] == want[:2]
     assert bare.engine.swa.in_use == 0
     bare.shutdown()
-    with pytest.raises(ValueError, match="speculative"):
-        LLM(spec_algorithm="ngram", spec_num_draft=2, **kw)
+    # a draft chain works with the pool (verify rows take pages like any other rows); a tree does not
+    rep = [prompts[0][:6] * 8, prompts[2]]
+    monkeypatch.setenv("MSGL_SWA_POOL", "0")
+    ref_llm = LLM(**kw)
+    want_rep = [o.token_ids for o in ref_llm.generate(rep, sp)]
+    ref_llm.shutdown()
+    monkeypatch.setenv("MSGL_SWA_POOL", "1")
+    spec = LLM(spec_algorithm="ngram", spec_num_draft=3, **kw)
+    assert [o.token_ids for o in spec.generate(rep, sp)] == want_rep
+    assert spec.stats["spec_drafted"] > 0
+    spec.engine.swa.check()
+    spec.shutdown()
+    with pytest.raises(ValueError, match="tree verification"):
+        LLM(spec_algorithm="ngram", spec_num_draft=2, spec_tree_width=3, **kw)
 
 
 def test_multimodal_gemma3_checkpoint_serves_its_text_decoder(tmp_path):

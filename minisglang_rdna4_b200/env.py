@@ -136,6 +136,10 @@ ENV.flag("DISABLE_TC_PREFILL", False, "prefill attention on the general (warp-le
 # --- distributed --------------------------------------------------------------------------
 ENV.int("PYNCCL_MAX_BUFFER_SIZE", 1 << 30, "upper bound of the registered all-reduce staging buffer")
 ENV.flag("DISABLE_FUSED_COMM", False, "route every collective through NCCL (the baseline data plane)")
+ENV.flag("TP_OVERLAP", False, "prefill steps of MoE layers under tensor parallelism reduce their output row chunk by row chunk "
+         "on a second stream, under the experts of the next chunk")
+ENV.int("TP_OVERLAP_MIN_ROWS", 1024, "smallest step (rows) that takes the chunked overlap")
+ENV.int("TP_OVERLAP_CHUNKS", 4, "row chunks of an overlapped step")
 ENV.flag("DISABLE_ROW_SHARD", False, "prefill chunks use all-reduce instead of the fused reduce-scatter / all-gather GEMMs")
 ENV.flag("PDL", True, "programmatic dependent launch: a kernel's prologue overlaps the tail of the kernel ahead of it")
 ENV.int("EP_REGION_GIB", 6, "per-rank budget of the expert-parallel exchange regions (sets the largest fused step)")

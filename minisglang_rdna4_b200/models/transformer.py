@@ -20,6 +20,7 @@ from ..layers import (
     AttentionLayer, BaseOP, GatedActivation, MergedColumnParallelLinear, MoELayer, ParallelLMHead,
     QKVParallelLinear, RMSNorm, RowParallelLinear, VocabParallelEmbedding,
 )
+from ..layers import tp_overlap
 from ..parallel.comm import get_comm
 from ..parallel.info import get_tp_info
 from ..utils import div_even
@@ -98,6 +99,12 @@ class SparseMoEBlock(BaseOP):
 
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, bool]:
         """Returns ``(y, partial)``: ``partial`` tells whether ``y`` still needs the TP sum."""
+        if self.experts.needs_tp_reduce and tp_overlap.applies(x.shape[0]):
+            # a large prefill step: reduce finished row chunks while the experts run on the next ones
+            return tp_overlap.chunked_all_reduce(self._partial_rows, x), False
+        return self._partial_rows(x), self.experts.needs_tp_reduce
+
+    def _partial_rows(self, x: torch.Tensor) -> torch.Tensor:
         y = self.experts.forward(x)
         partial = self.experts.needs_tp_reduce
         if self._has_shared:
@@ -108,7 +115,7 @@ class SparseMoEBlock(BaseOP):
             if get_tp_info().size > 1 and not partial:
                 s = get_comm().all_reduce(s)
             y = y + s
-        return y, partial
+        return y
 
     def init_dummy(self, gen, std=0.02) -> None:
         if self._has_shared and self._shared_gate:

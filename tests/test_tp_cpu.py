@@ -318,3 +318,39 @@ def test_speculative_decoding_under_dp2_expert_parallel_lockstep():
     assert got[0] + got[1] == want, (got, want)
     assert calls[0] == calls[1] > 0
     assert stats[0]["spec_steps"] > 0 and stats[0]["spec_drafted"] > 0
+
+
+def test_chunked_all_reduce_of_moe_prefill_matches_tp1(monkeypatch):
+    """MSGL_TP_OVERLAP: a large prefill step of a MoE layer under tensor parallelism reduces its
+    output row chunk by row chunk (on the GPU: on a second stream, under the experts of the next
+    chunk) and hands finished rows to the next norm. Same tokens as a single rank."""
+    monkeypatch.setenv("MSGL_TP_OVERLAP", "1")
+    monkeypatch.setenv("MSGL_TP_OVERLAP_MIN_ROWS", "16")
+    monkeypatch.setenv("MSGL_TP_OVERLAP_CHUNKS", "3")
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 515, (n,), generator=g).tolist() for n in (9, 37)]
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, True)
+        want = _single(ckpt, prompts)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 25300 + (os.getpid() % 1500)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, False)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=240)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want
+
+    from minisglang_rdna4_b200.layers import tp_overlap
+    from minisglang_rdna4_b200.parallel import info
+
+    info.set_tp_info(0, 2)
+    try:
+        assert tp_overlap.applies(16) and not tp_overlap.applies(15)
+        monkeypatch.setenv("MSGL_TP_OVERLAP", "0")
+        assert not tp_overlap.applies(4096)
+    finally:
+        info.reset_parallel_info()

@@ -74,6 +74,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--rsa-max-retries", type=int, default=1)
     p.add_argument("--rsa-effort-ladder", action="store_true",
                    help="`reasoning_effort` medium / high / max runs the request through self-aggregation")
+    # shorthands for environment switches (the engine processes inherit the environment)
+    p.add_argument("--swa-pool", action="store_true",
+                   help="sliding-window layers keep their K/V in a pool of their own with recycled pages (MSGL_SWA_POOL)")
+    p.add_argument("--baked-dir", default="",
+                   help="directory of baked checkpoints: written on the first boot, streamed on later ones (MSGL_BAKED_DIR)")
+    p.add_argument("--tp-overlap", action="store_true",
+                   help="MoE prefill steps under tensor parallelism reduce row chunks on a second stream (MSGL_TP_OVERLAP)")
     p.add_argument("--print-env", action="store_true", help="list every MSGL_* variable and exit")
     return p
 
@@ -87,6 +94,12 @@ def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
         print(ENV.describe())
         raise SystemExit(0)
     ns = build_parser().parse_args(argv)
+    import os
+
+    for flag, var, value in ((ns.swa_pool, "MSGL_SWA_POOL", "1"), (ns.baked_dir, "MSGL_BAKED_DIR", ns.baked_dir),
+                             (ns.tp_overlap, "MSGL_TP_OVERLAP", "1")):
+        if flag:
+            os.environ[var] = value
     if ns.enable_ep and ns.tp_size * ns.dp_size == 1:
         raise SystemExit("--enable-ep needs --tp-size > 1 or --dp-size > 1")
     kwargs = json.loads(ns.chat_template_kwargs) if ns.chat_template_kwargs else None

@@ -354,3 +354,33 @@ def test_chunked_all_reduce_of_moe_prefill_matches_tp1(monkeypatch):
         assert not tp_overlap.applies(4096)
     finally:
         info.reset_parallel_info()
+
+
+def test_block_diffusion_under_tp2_matches_tp1_on_cpu():
+    """Block-diffusion decoding on two tensor-parallel ranks: both gather the canvas logits, hold the same
+    per-request generator state and so advance their canvases identically; tokens equal a single rank's."""
+    import json
+
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (9, 21)]
+    with tempfile.TemporaryDirectory() as tmp:
+        ckpt = _make_ckpt(tmp, False)
+        cfg = json.load(open(os.path.join(ckpt, "config.json")))
+        cfg.update(canvas_length=4, mask_token_id=514)
+        json.dump(cfg, open(os.path.join(ckpt, "config.json"), "w"))
+        json.dump({"max_denoising_steps": 3, "confidence_threshold": 0.7, "mask_token_id": 514,
+                   "sampler_config": {"_cls_name": "MaskConfidenceSamplerConfig"}},
+                  open(os.path.join(ckpt, "generation_config.json"), "w"))
+        want = _single(ckpt, prompts)
+        assert all(len(w) == 6 for w in want)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 24300 + (os.getpid() % 1500)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ckpt, prompts, q, False)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=240)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want

@@ -69,3 +69,39 @@ def test_family_matches_transformers(family):
         got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))]
         llm.shutdown()
     assert got == want
+
+
+ROPE = {
+    "llama3": dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                   original_max_position_embeddings=64, rope_theta=10000.0),
+    "yarn": dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=64, rope_theta=10000.0),
+    "linear": dict(rope_type="linear", factor=2.0, rope_theta=10000.0),
+}
+
+
+@pytest.mark.parametrize("kind", sorted(ROPE))
+def test_rope_scaling_matches_transformers(kind):
+    """Long-context rotary scalings (Llama-3 frequency bands, YaRN with its attention factor, linear
+    position interpolation) with prompts well past the original context length."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    cfg = T.LlamaConfig(**{**COMMON, "num_hidden_layers": 2, "head_dim": 16, "max_position_embeddings": 256},
+                        rope_parameters=ROPE[kind])
+    torch.manual_seed(0)
+    hf = T.LlamaForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.1)
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(3, 298, (n,), generator=g).tolist() for n in (5, 150, 90)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None,
+                            pad_token_id=0)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=64)
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))]
+        llm.shutdown()
+    assert got == want

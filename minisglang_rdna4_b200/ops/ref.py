@@ -114,7 +114,17 @@ def build_cos_sin_cache(rotary_dim: int, max_position: int, base: float,
             ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
             mask = 1.0 - ramp
             inv_freq = inv_freq / factor * (1 - mask) + inv_freq * mask
-            mscale = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+            def yarn_mscale(m: float = 1.0) -> float:
+                return 0.1 * m * math.log(factor) + 1.0 if factor > 1 else 1.0
+
+            if scaling.get("attention_factor"):
+                mscale = float(scaling["attention_factor"])
+            elif scaling.get("mscale") and scaling.get("mscale_all_dim"):
+                # DeepSeek-style YaRN: the table carries the ratio of the two magnitude factors (the softmax
+                # scale of the attention layer carries mscale_all_dim squared)
+                mscale = yarn_mscale(float(scaling["mscale"])) / yarn_mscale(float(scaling["mscale_all_dim"]))
+            else:
+                mscale = yarn_mscale()
         elif kind in ("default", "dynamic", None):
             pass
         else:

@@ -127,11 +127,14 @@ def test_next_token_layer_of_the_checkpoint_drafts_exactly():
     assert got == want
 
 
-def test_deepseek_v3_with_narrower_value_heads_matches_transformers():
+@pytest.mark.parametrize("yarn", [False, True])
+def test_deepseek_v3_with_narrower_value_heads_matches_transformers(yarn):
     """DeepSeek-V3 geometry: the value heads (16 here, 128 in the released models) are narrower than
     the key heads (nope + rope = 32 here, 192 there). Queries, keys and values are zero-padded to one
     width in the paged pool, which changes no dot product; the padding channels of the output are dropped
-    before the output projection."""
+    before the output projection. With YaRN as DeepSeek configures it (``mscale`` and ``mscale_all_dim``: the
+    rotary table carries the ratio of the two magnitude factors, the softmax scale the square of the second)
+    and prompts past the original context length."""
     from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
 
     from minisglang_rdna4_b200 import SamplingParams
@@ -143,7 +146,9 @@ def test_deepseek_v3_with_narrower_value_heads_matches_transformers():
         num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=2.5,
         kv_lora_rank=32, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=24, n_group=2,
         topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1, max_position_embeddings=512, eos_token_id=299,
-        bos_token_id=None, pad_token_id=None)
+        bos_token_id=None, pad_token_id=None,
+        **(dict(rope_parameters=dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=64, beta_fast=32,
+                                     beta_slow=1, mscale=1.0, mscale_all_dim=0.7, rope_theta=10000.0)) if yarn else {}))
     torch.manual_seed(0)
     hf = DeepseekV3ForCausalLM(cfg).float().eval()
     with torch.no_grad():
@@ -160,7 +165,7 @@ def test_deepseek_v3_with_narrower_value_heads_matches_transformers():
     with tempfile.TemporaryDirectory() as tmp:
         hf.save_pretrained(tmp, safe_serialization=True)
         g = torch.Generator().manual_seed(1)
-        prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (5, 23, 41)]
+        prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in ((5, 150, 90) if yarn else (5, 23, 41))]
         want = [hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist() for p in prompts]
         llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
                   max_extend_tokens=32)

@@ -38,9 +38,12 @@ class SelfAttention(BaseOP):
             cfg.hidden_size, cfg.head_dim, cfg.num_qo_heads, cfg.num_kv_heads, dtype, device,
             _scheme(cfg, prefix + ".qkv_proj"), bias=cfg.attention_bias,
         )
+        # the output projection has a bias where the family's attention_bias covers it (Llama, Qwen3); Qwen2 and
+        # GLM-4.5 put biases on q / k / v only
         self.o_proj = RowParallelLinear(
             cfg.num_qo_heads * cfg.head_dim, cfg.hidden_size, dtype, device,
-            _scheme(cfg, prefix + ".o_proj"), bias=False,
+            _scheme(cfg, prefix + ".o_proj"),
+            bias=bool(cfg.attention_bias) and cfg.model_type not in ("qwen2", "qwen2_moe", "glm4_moe"),
         )
         if cfg.qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device)

@@ -16,12 +16,20 @@ COMMON = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_
 MOE = dict(moe_intermediate_size=32, num_experts=8, num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[])
 FAMILIES = {
     "llama": ("LlamaConfig", "LlamaForCausalLM", dict(head_dim=16)),
+    "llama_biases": ("LlamaConfig", "LlamaForCausalLM", dict(head_dim=16, attention_bias=True, mlp_bias=True)),
+    "llama_tied": ("LlamaConfig", "LlamaForCausalLM", dict(head_dim=16, tie_word_embeddings=True)),
     "mistral": ("MistralConfig", "MistralForCausalLM", dict(sliding_window=16, head_dim=16)),        # window < context
     "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict()),                                           # q/k/v biases
     "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=32)),                                # per-head QK norm
     "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM",
                   dict(shared_expert_intermediate_size=48, norm_topk_prob=False, **MOE)),           # gated shared expert
     "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(head_dim=32, norm_topk_prob=True, **MOE)),
+    # experts on every second layer, one of those forced dense
+    "qwen3_moe_mixed": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM",
+                        dict(head_dim=32, norm_topk_prob=False, num_hidden_layers=4,
+                             **{**MOE, "decoder_sparse_step": 2, "mlp_only_layers": [1]})),
+    "qwen2_window": ("Qwen2Config", "Qwen2ForCausalLM",
+                     dict(use_sliding_window=True, sliding_window=16, max_window_layers=2, num_hidden_layers=4)),
     "gemma2": ("Gemma2Config", "Gemma2ForCausalLM",
                dict(head_dim=16, sliding_window=16, query_pre_attn_scalar=16, final_logit_softcapping=30.0,
                     attn_logit_softcapping=50.0, tie_word_embeddings=True)),

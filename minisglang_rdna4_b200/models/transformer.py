@@ -126,8 +126,10 @@ class SparseMoEBlock(BaseOP):
 
 
 class DecoderLayer(BaseOP):
-    def __init__(self, cfg: ModelConfig, layer_id: int, dtype, device) -> None:
-        prefix = f"model.layers.{layer_id}"
+    def __init__(self, cfg: ModelConfig, layer_id: int, dtype, device, prefix: Optional[str] = None) -> None:
+        # ``prefix``: the layer's name in the checkpoint when that is not its place in the decoder
+        # (the next-token head's layer), for the quantisation scheme lookup
+        prefix = prefix or f"model.layers.{layer_id}"
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
         self.self_attn = SelfAttention(cfg, layer_id, dtype, device, prefix + ".self_attn")
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
@@ -204,9 +206,10 @@ class CausalLM(BaseOP):
                 # hidden state entering layer i = residual + pending block output
                 seen[i] = self._materialise(x, residual, partial)
             x, residual, partial = layer.forward(x, residual, partial)
-        if capture is not None:
-            ctx.aux_hidden = [seen[i] for i in capture]
         out, _ = self.model.norm.forward_fused(x, residual, partial=partial)
+        if capture is not None:
+            seen[len(self.model.layers)] = out      # "layer" num_layers: the final hidden state (the next-token head's input)
+            ctx.aux_hidden = [seen[i] for i in capture]
         return out
 
     @staticmethod

@@ -51,7 +51,7 @@ def make_proposer(config, scheduler) -> Proposer:
     if algo == "mtp":
         mc = scheduler.engine.model_config
         qwen = mc.mtp_num_hidden_layers > 0 and mc.attn_output_gate and mc.layer_types
-        glm = mc.num_nextn_predict_layers > 0 and getattr(mc, "kv_lora_rank", 0)
+        glm = mc.num_nextn_predict_layers > 0 and (getattr(mc, "kv_lora_rank", 0) or mc.model_type == "glm4_moe")
         if qwen or glm:
             # the checkpoint's own head (Qwen3.5 / Qwen3-Next mtp.*; GLM-4.x MoE / DeepSeek model.layers.<L>)
             from .mtp import MTPProposer

@@ -243,6 +243,41 @@ class GlmMTPDraft(_MTPBase):
         return hidden, self._target.lm_head.forward(self.shared_head.norm.forward(hidden[-1:]))
 
 
+class Glm4MoeMTPDraft(GlmMTPDraft):
+    """GLM-4.5 / 4.6: the same ``model.layers.<num_layers>`` layout around an ordinary grouped-query
+    attention layer (q / k / v biases, optional QK norm, partial rotary embedding) and the GLM expert block."""
+
+    def __init__(self, cfg: ModelConfig, dtype, device, target) -> None:
+        from ..models.transformer import DecoderLayer
+
+        self._lcfg = replace(cfg, num_layers=1, first_k_dense_replace=0, mlp_only_layers=(), decoder_sparse_step=1,
+                             layer_types=None)
+        self.layer = DecoderLayer(self._lcfg, 0, dtype, device, prefix=f"model.layers.{cfg.num_layers}")
+        tp = get_tp_info().size
+        self._hq, self._hk = div_even(cfg.num_qo_heads, tp), div_even(cfg.num_kv_heads, tp, True)
+        self._setup(cfg, dtype, device, target, self._hk, cfg.head_dim)
+        h = cfg.hidden_size
+        self.enorm = RMSNorm(h, cfg.rms_norm_eps, dtype, device)
+        self.hnorm = RMSNorm(h, cfg.rms_norm_eps, dtype, device)
+        self.eh_proj = ReplicatedLinear(2 * h, h, dtype, device)
+        self.shared_head = _SharedHead(cfg, dtype, device)
+
+    def _attention(self, uid: int, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        cfg = self._cfg
+        attn = self.layer.self_attn
+        hq, hk, d = self._hq, self._hk, cfg.head_dim
+        if self._cos_sin is None:
+            self._cos_sin = get_rope_cache(cfg.rotary_config, x.device)
+        q, k, v = attn.qkv_proj.forward(x).split([hq * d, hk * d, hk * d], dim=-1)
+        qw, kw = (attn.q_norm.weight, attn.k_norm.weight) if cfg.qk_norm else (None, None)
+        q, k = ref.qk_norm_rope(q, k, qw, kw, positions, self._cos_sin, d, cfg.rotary_config.rotary_dim,
+                                cfg.rms_norm_eps, cfg.rotary_config.interleaved)
+        n = x.shape[0]
+        o = _ring_attention(q.view(n, hq, d), k.view(n, hk, d), v.reshape(n, hk, d), self.ring(uid), positions,
+                            d ** -0.5, self._dtype)
+        return attn.o_proj.forward(o, reduce=True)
+
+
 def mtp_tensors(path: str, next_layer: int) -> Iterator[Tuple[str, torch.Tensor]]:
     """The head's tensors of a checkpoint directory: ``mtp.*`` (Qwen layout) or
     ``model.layers.<next_layer>.*`` (GLM / DeepSeek layout); the decoder layer's own tensors come
@@ -313,8 +348,11 @@ class MTPProposer(Eagle3Proposer):
         cfg = eng.model_config
         # the head reads the target's final hidden state: "layer" num_layers of the capture list
         self.aux_layers = [cfg.num_layers]
-        glm = cfg.num_nextn_predict_layers > 0 and not cfg.mtp_num_hidden_layers
-        self.draft = (GlmMTPDraft if glm else MTPDraft)(cfg, eng.dtype, eng.device, eng.model)
+        if cfg.mtp_num_hidden_layers:
+            kind = MTPDraft
+        else:
+            kind = GlmMTPDraft if getattr(cfg, "kv_lora_rank", 0) else Glm4MoeMTPDraft
+        self.draft = kind(cfg, eng.dtype, eng.device, eng.model)
         path = config.model_path
         used = 0
         if path and not getattr(config, "use_dummy_weight", False):

@@ -217,3 +217,86 @@ def test_deepseek_v2_softmax_routing_matches_transformers():
     bias = torch.zeros(8)
     w2, ids2 = ref.moe_route_grouped(logits, 2, False, "softmax", bias, 1.0, n_group=2, topk_group=1)
     assert min(ids2[0].tolist()) >= 4               # with a selection bias: the sum of the two best decides
+
+
+def test_glm4_moe_next_token_layer_drafts_exactly():
+    """GLM-4.5's next-token layer (``model.layers.<L>`` with enorm / hnorm / eh_proj around an ordinary
+    grouped-query attention layer with q/k/v biases, QK norm and partial rotary embedding, the expert
+    block, shared_head.norm) against a Hugging Face restatement; generation equals plain decoding."""
+    import json
+
+    import transformers as T
+    from safetensors.torch import load_file, save_file
+    from transformers.models.glm4_moe import modeling_glm4_moe as m
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    cfg = T.Glm4MoeConfig(
+        vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=32, n_shared_experts=1, n_routed_experts=8,
+        routed_scaling_factor=1.7, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+        use_qk_norm=True, attention_bias=True, max_position_embeddings=512, eos_token_id=299, bos_token_id=None,
+        pad_token_id=None, tie_word_embeddings=False)
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = T.Glm4MoeForCausalLM(cfg).float().eval()
+    L = cfg.num_hidden_layers
+    layer = m.Glm4MoeDecoderLayer(cfg, L - 1).float().eval()
+    eh = torch.nn.Linear(2 * cfg.hidden_size, cfg.hidden_size, bias=False)
+    en, hn, sn = (m.Glm4MoeRMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps) for _ in range(3))
+    with torch.no_grad():
+        for mod in (hf, layer, eh, en, hn, sn):
+            for name, p in mod.named_parameters():
+                if p.dim() >= 2:
+                    p.copy_(torch.randn_like(p) * 0.1)
+                elif "bias" in name:
+                    p.copy_(torch.randn_like(p) * 0.1)
+                else:
+                    p.copy_(0.1 * torch.randn_like(p) + 1.0)
+            for name, b in mod.named_buffers():
+                if "e_score_correction_bias" in name:
+                    b.copy_(torch.randn_like(b) * 0.1)
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        st = load_file(f"{tmp}/model.safetensors")
+        for k, v in layer.state_dict().items():
+            st[f"model.layers.{L}.{k}"] = v.contiguous()
+        st[f"model.layers.{L}.eh_proj.weight"] = eh.weight.detach()
+        st[f"model.layers.{L}.enorm.weight"] = en.weight.detach()
+        st[f"model.layers.{L}.hnorm.weight"] = hn.weight.detach()
+        st[f"model.layers.{L}.shared_head.norm.weight"] = sn.weight.detach()
+        save_file(st, f"{tmp}/model.safetensors")
+        c = json.load(open(f"{tmp}/config.json"))
+        c["num_nextn_predict_layers"] = 1
+        json.dump(c, open(f"{tmp}/config.json", "w"))
+        g = torch.Generator().manual_seed(2)
+        ids = torch.randint(0, 298, (1, 19), generator=g)
+        n = ids.shape[1] - 1
+        with torch.no_grad():
+            hid = hf(ids, output_hidden_states=True).hidden_states[-1][0]
+            emb = hf.model.embed_tokens(ids)[0]
+            x = eh(torch.cat([en(emb[1:]), hn(hid[:-1])], -1))[None]
+            pos = torch.arange(n)[None]
+            pe = m.Glm4MoeRotaryEmbedding(cfg)(x, pos)
+            mask = torch.full((n, n), float("-inf")).triu(1)[None, None]
+            y = layer(x, position_embeddings=pe, attention_mask=mask, position_ids=pos)
+            y = (y[0] if isinstance(y, tuple) else y)[0]
+            want_logits = hf.lm_head(sn(y[-1:]))
+        kw = dict(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64)
+        llm = LLM(spec_algorithm="mtp", spec_num_draft=2, **kw)
+        prop = llm.proposer
+        assert type(prop.draft).__name__ == "Glm4MoeMTPDraft" and prop.loaded_tensors >= 10
+        got_hidden, got_logits = prop.draft.forward_rows(-7, emb[1:], hid[:-1], torch.arange(n, dtype=torch.int32))
+        prop.draft.drop(-7)
+        assert torch.allclose(got_hidden, y, atol=2e-5), float((got_hidden - y).abs().max())
+        assert torch.allclose(got_logits, want_logits, atol=2e-5)
+        prompts = [ids[0].tolist(), torch.randint(0, 298, (9,), generator=g).tolist()]
+        sp = SamplingParams(max_tokens=12, ignore_eos=True)
+        got = [o.token_ids for o in llm.generate(prompts, sp)]
+        assert llm.stats["spec_drafted"] > 0
+        llm.shutdown()
+        plain = LLM(**kw)
+        want = [o.token_ids for o in plain.generate(prompts, sp)]
+        plain.shutdown()
+    assert got == want

@@ -384,3 +384,41 @@ def test_block_diffusion_under_tp2_matches_tp1_on_cpu():
             p.join(timeout=60)
             assert p.exitcode == 0
     assert got == want
+
+
+@pytest.mark.parametrize("ep", [False, True])
+def test_deepseek_v3_tp2_matches_tp1_on_cpu(ep):
+    """Latent attention with zero-padded value heads and the grouped sigmoid routing under tensor parallelism
+    (heads and expert width split) and with the experts split over the ranks instead."""
+    T = pytest.importorskip("transformers")
+    cfg = T.DeepseekV3Config(
+        vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+        num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8, routed_scaling_factor=2.5,
+        kv_lora_rank=32, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=24, n_group=2,
+        topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1, max_position_embeddings=512, eos_token_id=299,
+        bos_token_id=None, pad_token_id=None)
+    torch.manual_seed(0)
+    hf = T.DeepseekV3ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (9, 21)]
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        want = _single(tmp, prompts)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 23100 + (os.getpid() % 1500) + (3 if ep else 0)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, tmp, prompts, q, ep)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=240)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want

@@ -177,6 +177,9 @@ class Batch:
     # capture the hidden states of these layer indices (EAGLE3 auxiliary features)
     capture_layers: Optional[List[int]] = None
     # sliding-window layers with a pool of their own: K/V slot of every row and block table in that pool
+    # rows of this step whose embedding is given (image placeholder tokens) and the vectors that replace it
+    mm_rows: Optional[torch.Tensor] = None
+    mm_values: Optional[torch.Tensor] = None
     swa_out_loc: Optional[torch.Tensor] = None
     swa_block_table: Optional[torch.Tensor] = None
 

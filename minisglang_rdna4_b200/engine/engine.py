@@ -182,6 +182,20 @@ class Engine:
             self.baked_bytes = loaded
         self._configure_expert_tier()
         self.model.post_load()
+        # vision tower of a multimodal checkpoint: replicated on every rank, runs once per image at admission
+        self.vision = None
+        if self.model_config.vision is not None:
+            from ..models.siglip import VisionTower
+
+            self.vision = VisionTower(self.model_config.vision, self.dtype, self.device)
+            if config.use_dummy_weight or not config.model_path or config.model_path in NAMED_CONFIGS:
+                self.vision.init_dummy(config.seed + 29)
+            else:
+                try:
+                    self.vision.load(config.model_path)
+                except KeyError as exc:
+                    logger.warning("%s: serving the text decoder only", exc)
+                    self.vision = None
         if dev_kind == "cuda":
             torch.cuda.synchronize()
             torch.cuda.empty_cache()

@@ -83,7 +83,10 @@ class LLM(Scheduler):
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int], torch.Tensor]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                 ) -> List[RequestOutput]:
+                 images: Optional[Sequence] = None) -> List[RequestOutput]:
+        """``images``: per prompt ``None`` or a list of images (encoded bytes, PIL images or uint8
+        tensors). A token-id prompt carries one begin-of-image marker per image; the placeholder
+        tokens are filled in here."""
         if sampling_params is None:
             sampling_params = SamplingParams()
         if isinstance(sampling_params, SamplingParams):
@@ -97,8 +100,19 @@ class LLM(Scheduler):
             uid = self._next_uid
             self._next_uid += 1
             uids.append(uid)
+            pixels = None
+            mine = images[len(uids) - 1] if images is not None else None
+            if mine:
+                from .tokenizer.vision import VisionPreprocessor
+
+                vc = self.engine.model_config.vision
+                if vc is None:
+                    raise ValueError("this model takes no image input")
+                pre = VisionPreprocessor.from_vision_config(vc)
+                pixels = pre.batch(mine)
+                ids = torch.tensor(pre.expand_placeholders(ids.tolist(), len(mine)), dtype=torch.int32)
             self._outputs[uid] = RequestOutput(uid, ids.tolist())
-            self._queue.append(UserMsg(uid, ids, sp))
+            self._queue.append(UserMsg(uid, ids, sp, images=pixels))
             self._unfinished += 1
         self._exit = False
         self.run_forever()

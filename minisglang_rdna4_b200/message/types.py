@@ -25,6 +25,7 @@ class TokenizeMsg(BaseMsg):
     chat_template_kwargs: Optional[Dict[str, Any]] = None
     tools: Optional[List[Dict[str, Any]]] = None
     add_generation_prompt: bool = True
+    images: Optional[List[bytes]] = None    # encoded image files, in the order their placeholders appear
 
 
 @dataclass
@@ -38,6 +39,7 @@ class UserMsg(BaseMsg):
     uid: int
     input_ids: torch.Tensor         # 1-D int32 CPU
     sampling_params: SamplingParams
+    images: Optional[torch.Tensor] = None   # [n, 3, S, S] uint8, resized; one block of placeholder tokens per image
 
 
 @dataclass

@@ -101,6 +101,7 @@ class ModelConfig:
     num_nextn_predict_layers: int = 0
     mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
     canvas_length: int = 0                    # block-diffusion models: tokens written per block
+    vision: Any = None                        # models.siglip.VisionConfig of a multimodal checkpoint
     mask_token_id: Optional[int] = None       # absorbing-state diffusion models
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
@@ -202,7 +203,12 @@ class ModelConfig:
                 cfg = json.load(fh)
         if not isinstance(cfg, dict):
             cfg = cfg.to_dict()
+        vision = None
         if "text_config" in cfg and isinstance(cfg["text_config"], dict):
+            if str(cfg.get("model_type", "")).startswith("gemma3") and cfg.get("vision_config"):
+                from .siglip import VisionConfig
+
+                vision = VisionConfig.from_hf(cfg)
             inner = dict(cfg["text_config"])
             for key in ("quantization_config", "architectures", "torch_dtype", "tie_word_embeddings"):
                 if key in cfg and key not in inner:
@@ -356,6 +362,7 @@ class ModelConfig:
             num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             canvas_length=int(g("canvas_length") or g("block_length") or 0),
+            vision=vision,
             mask_token_id=g("mask_token_id"),
             eos_token_ids=eos_ids,
             bos_token_id=g("bos_token_id"),

@@ -128,6 +128,9 @@ class GemmaForCausalLM(BaseOP):
             self._embed_scale_rounded = float(torch.tensor(self._embed_scale, dtype=x.dtype))
             self._embed_scale_dtype = x.dtype
         x = x * self._embed_scale_rounded
+        if ctx.batch.mm_rows is not None:
+            # image placeholder rows take the projected vision features as they are (not scaled)
+            x = x.index_copy(0, ctx.batch.mm_rows, ctx.batch.mm_values.to(x.dtype))
         seen = {}
         for i, layer in enumerate(self.model.layers):
             if capture is not None and i in capture:

@@ -15,6 +15,8 @@ Speculative decoding and expert-parallel lockstep are mixed in from ``spec_step.
 """
 from __future__ import annotations
 
+import contextlib
+
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -100,6 +102,7 @@ class Scheduler:
         self.alloc_len: Dict[int, int] = {}      # uid -> token positions that own a KV slot
         self.prefix_len: Dict[int, int] = {}     # uid -> cached tokens at admission (reporting)
         self.finished_uids: set = set()
+        self.mm: Dict[int, tuple] = {}          # uid -> (placeholder positions, image features) of multimodal requests
         self.last_state_digests: Dict[int, dict] = {}   # uid -> digests of its last prefill step (MSGL_STATE_DIGEST)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "steps": 0, "finished": 0,
                       "spec_drafted": 0, "spec_accepted": 0, "spec_emitted": 0, "spec_steps": 0}
@@ -167,13 +170,71 @@ class Scheduler:
             self.send_result([DetokenizeMsg(msg.uid, 0, True, "error",
                                             error="request does not fit in the KV cache")])
             return
+        if getattr(msg, "images", None) is not None:
+            ids = self._admit_images(msg.uid, ids, msg.images)
+            if ids is None:
+                return
         self.prefill.add_one_req(msg.uid, ids, params)
         from ..utils.tracing import log_request
 
         log_request("admit", msg.uid, prompt=n, max_new=max_new)
 
+    def _admit_images(self, uid: int, ids: torch.Tensor, images: torch.Tensor) -> Optional[torch.Tensor]:
+        """Run the vision tower over a request's images (``[n, 3, S, S]`` uint8) and remember the
+        projected features for the placeholder positions of its prompt. The placeholder ids are
+        replaced by ids outside the vocabulary derived from the image content: the embedding of
+        such an id is zero (it is overwritten by the image feature) and the prefix cache tells two
+        images apart (python/minisgl/tokenizer/vision.py:92 expands the placeholders; the reference
+        runs its tower in the model's forward)."""
+        import hashlib
+
+        eng = self.engine
+        tower = eng.vision
+        if tower is None:
+            self.send_result([DetokenizeMsg(uid, 0, True, "error", error="this model takes no image input")])
+            return None
+        vc = tower.cfg
+        per = vc.tokens_per_image
+        pos = (ids == vc.image_token_id).nonzero().flatten()
+        n = int(images.shape[0])
+        if int(pos.numel()) != n * per or tuple(images.shape[1:]) != (3, vc.image_size, vc.image_size):
+            self.send_result([DetokenizeMsg(uid, 0, True, "error", error=(
+                f"{n} image(s) of shape {tuple(images.shape[1:])} against {int(pos.numel())} placeholder tokens "
+                f"({per} per {vc.image_size}x{vc.image_size} image expected)"))])
+            return None
+        ctx = torch.cuda.stream(eng.stream) if eng.stream is not None else contextlib.nullcontext()
+        with ctx:
+            px = images.to(eng.device, non_blocking=True).to(torch.float32) / 255.0
+            emb = tower.image_embeddings((px - 0.5) / 0.5)
+        ids = ids.clone()
+        vocab = eng.model_config.vocab_size
+        for i in range(n):
+            h = int.from_bytes(hashlib.sha1(images[i].contiguous().numpy().tobytes()).digest()[:4], "little")
+            ids[pos[i * per:(i + 1) * per]] = (vocab + h % (1 << 29) + torch.arange(per)).to(ids.dtype)
+        self.mm[uid] = (pos.numpy().astype(np.int64), emb)
+        return ids
+
+    def _image_rows(self, batch: Batch, plan: StepPlan) -> None:
+        """Rows of a prefill step that are image placeholders, and the features that go there."""
+        rows, vals = [], []
+        for i, r in enumerate(batch.reqs):
+            entry = self.mm.get(r.uid)
+            if entry is None:
+                continue
+            pos, emb = entry
+            lo, hi = int(r.cached_len), int(r.device_len)
+            sel = np.nonzero((pos >= lo) & (pos < hi))[0]
+            if sel.size:
+                rows.append(int(plan.cu_q[i]) + (pos[sel] - lo))
+                vals.append(emb[torch.as_tensor(sel, device=emb.device)])
+        if rows:
+            batch.mm_rows = torch.as_tensor(np.concatenate(rows), dtype=torch.int64).to(self.engine.device)
+            batch.mm_values = torch.cat(vals)
+
     def _abort(self, uid: int) -> None:
         pending = self.prefill.abort(uid)
+        if pending is not None:
+            self.mm.pop(uid, None)
         if pending is not None:
             if pending.chunked is not None:
                 self._free_req_resources(pending.chunked, insert=False)
@@ -349,6 +410,8 @@ class Scheduler:
     # ------------------------------------------------------------------ forward
     def _forward(self, batch: Batch) -> Ongoing:
         plan = self._make_plan(batch)
+        if self.mm and batch.is_prefill:
+            self._image_rows(batch, plan)
         capture = getattr(self.proposer, "capture_layers", None)
         if capture:
             batch.capture_layers = list(capture)
@@ -574,6 +637,7 @@ class Scheduler:
             return
         req.resources_freed = True
         self.decode.remove(req)
+        self.mm.pop(req.uid, None)
         if self.engine.swa is not None:
             self.engine.swa.release(req.table_idx)
         alloc = self.alloc_len.pop(req.uid, req.cache_handle.cached_len)

@@ -58,6 +58,39 @@ class ChatMessage(BaseModel):
     reasoning_content: Optional[str] = None
 
 
+def extract_images(messages: List[Dict[str, Any]]) -> List[bytes]:
+    """Encoded image files of a chat request, in prompt order. OpenAI ``image_url`` parts (``data:``
+    URLs only: this server fetches nothing) and ``{"type": "image", "image": <data URL>}`` parts are
+    rewritten in place to bare ``{"type": "image"}`` parts, which is what chat templates render as
+    the begin-of-image marker (python/minisgl/tokenizer/vision.py:92-140)."""
+    import base64
+
+    out: List[bytes] = []
+    for m in messages:
+        parts = m.get("content")
+        if not isinstance(parts, list):
+            continue
+        for i, part in enumerate(parts):
+            kind = part.get("type")
+            url = None
+            if kind == "image_url":
+                url = (part.get("image_url") or {}).get("url") if isinstance(part.get("image_url"), dict) else part.get(
+                    "image_url")
+            elif kind == "image" and isinstance(part.get("image"), str):
+                url = part["image"]
+            if url is None:
+                continue
+            if not str(url).startswith("data:") or "," not in url:
+                raise RequestRejected("images are accepted as data: URLs only (this server fetches nothing)", "messages",
+                                      "invalid_image_url")
+            try:
+                out.append(base64.b64decode(url.split(",", 1)[1], validate=False))
+            except Exception:
+                raise RequestRejected("an image part does not hold base64 data", "messages", "invalid_image_url")
+            parts[i] = {"type": "image"}
+    return out
+
+
 class RequestRejected(ValueError):
     """A request field this server cannot honour: answered with 400 and the OpenAI error object
     ``{"error": {message, type, param, code}}`` (python/minisgl/server/api_server.py:1473-1590)."""
@@ -484,6 +517,13 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
             payload: Any = [m.model_dump(exclude_none=True) for m in req.messages]
         else:
             payload = req.prompt if req.prompt is not None else [m.model_dump(exclude_none=True) for m in req.messages]
+        images: List[bytes] = []
+        if chat:
+            try:
+                images = extract_images(payload)
+            except RequestRejected as bad:
+                state.queues.pop(uid, None)
+                return JSONResponse(status_code=400, content=error_body(str(bad), bad.param, bad.code))
         cam = getattr(app.state, "cam", None)
         if cam is not None:
             ns = request.headers.get("x-cam-namespace") or "default"
@@ -494,7 +534,7 @@ def create_app(args: ServerArgs, manager: Optional[FrontendManager] = None, chat
         kwargs = dict(req.chat_template_kwargs or {})
         if req.enable_thinking is not None:
             kwargs.setdefault("enable_thinking", req.enable_thinking)
-        await state.send_one(TokenizeMsg(uid, payload, sp, kwargs or None, req.tools))
+        await state.send_one(TokenizeMsg(uid, payload, sp, kwargs or None, req.tools, images=images or None))
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
         model = req.model or args.model_name
         obj = "chat.completion" if chat else "text_completion"

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional
 
+import torch
+
 from ..config import ServerArgs
 from ..message import (
     AbortBackendMsg, AbortMsg, BatchMsg, DetokenizeMsg, ExitMsg, StatsMsg, TokenizeMsg, UserMsg, UserReply,
@@ -39,13 +41,34 @@ class TokenizerWorker:
             ids = self.tok.tokenize(msg.text, msg.chat_template_kwargs, msg.tools, msg.add_generation_prompt)
         except Exception as exc:
             return None, UserReply(msg.uid, "", True, "error", error=str(exc))
+        pixels = None
+        if getattr(msg, "images", None):
+            try:
+                pre = self._vision()
+                pixels = pre.batch(msg.images)
+                ids = torch.tensor(pre.expand_placeholders(ids.tolist(), len(msg.images)), dtype=torch.int32)
+            except Exception as exc:
+                return None, UserReply(msg.uid, "", True, "error", error=f"image input: {exc}")
         sp = msg.sampling_params
         self.detok.register(msg.uid, sp.stop, sp.stop_keep)
         replica = self.next_replica
         self.next_replica = (self.next_replica + 1) % max(self.args.dp_size, 1)
         self.route[msg.uid] = replica
         self.logprob_n[msg.uid] = sp.logprobs
-        return replica, UserMsg(msg.uid, ids, sp)
+        return replica, UserMsg(msg.uid, ids, sp, images=pixels)
+
+    def _vision(self):
+        """Image preprocessor of the served checkpoint (built on the first request with an image)."""
+        pre = getattr(self, "_vision_pre", None)
+        if pre is None:
+            from ..models.config import ModelConfig
+            from .vision import VisionPreprocessor
+
+            vc = ModelConfig.from_hf(self.args.model_path).vision
+            if vc is None:
+                raise ValueError("this model takes no image input")
+            pre = self._vision_pre = VisionPreprocessor.from_vision_config(vc)
+        return pre
 
     def on_detokenize(self, msg: DetokenizeMsg):
         """Returns ``(UserReply or None, abort uid or None)``."""

@@ -113,3 +113,32 @@ def test_rope_scaling_matches_transformers(kind):
         got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))]
         llm.shutdown()
     assert got == want
+
+
+def test_all_sliding_model_with_the_window_pool(monkeypatch):
+    """Mistral (every layer has the window): with MSGL_SWA_POOL all K/V live in the recycled pool, the main
+    pool keeps one unused layer; contexts several windows long still match the Hugging Face model."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    cfg = T.MistralConfig(**{**COMMON, "head_dim": 16, "sliding_window": 16})
+    torch.manual_seed(0)
+    hf = T.MistralForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.1)
+    monkeypatch.setenv("MSGL_SWA_POOL", "1")
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(3, 298, (n,), generator=g).tolist() for n in (5, 100, 41)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=20, do_sample=False, eos_token_id=None,
+                            pad_token_id=0)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=32)
+        assert llm.engine.swa is not None and llm.engine.kv_layers == 1 and llm.engine.swa_kv_cache.num_layers == 3
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=20, ignore_eos=True))]
+        llm.engine.swa.check()
+        llm.shutdown()
+    assert got == want

@@ -21,6 +21,7 @@ class AttnMetadata:
     causal: bool = True
     mask: Optional[torch.Tensor] = None   # additive [T, >= max_kv] bias for tree verification
     mask_window: int = 0                  # > 0: mask rows [T, mask_window] cover the last mask_window KV positions only
+    mask_swa: Optional[torch.Tensor] = None   # the mask sliding-window layers take instead (a mask replaces the window rule)
     workspace: Optional[torch.Tensor] = None
     prefill_plan: Optional[object] = None  # ops.cuda.PrefillPlan of a prefill-phase step on a GPU
 

@@ -35,7 +35,7 @@ class PagedAttentionBackend(BaseAttnBackend):
 
     def prepare_metadata(self, batch: Batch, block_table, cu_q, seq_lens, max_q: int, max_kv: int,
                          causal: bool = True, mask: Optional[torch.Tensor] = None,
-                         host_cu_q=None, host_seq_lens=None, mask_window: int = 0) -> None:
+                         host_cu_q=None, host_seq_lens=None, mask_window: int = 0, mask_swa=None) -> None:
         """``host_cu_q`` / ``host_seq_lens`` are the same lengths as numpy arrays: a prefill-phase
         step on a GPU builds the tables of the tensor-core prefill kernel from them (every such
         step whose KV rows number at most 16 times its query rows: every prefill and chunked-prefill
@@ -55,7 +55,7 @@ class PagedAttentionBackend(BaseAttnBackend):
                     plan = K.PrefillPlan(host_cu_q, host_seq_lens, self.device)
         batch.attn_metadata = AttnMetadata(
             cu_q=cu_q, seq_lens=seq_lens, block_table=block_table, max_q=max_q, max_kv=max_kv,
-            decode=(max_q == 1 and plan is None), causal=causal, mask=mask, mask_window=mask_window,
+            decode=(max_q == 1 and plan is None), causal=causal, mask=mask, mask_window=mask_window, mask_swa=mask_swa,
             workspace=self._workspace,
             prefill_plan=plan,
         )
@@ -80,9 +80,10 @@ class PagedAttentionBackend(BaseAttnBackend):
             from ..ops.cuda import choose_splits
 
             splits = choose_splits(md.seq_lens.numel(), self.hk, self.max_seq_len or md.max_kv, True)
+        mask = md.mask_swa if (window and md.mask_swa is not None) else md.mask
         return ops.paged_attention(
             q, pool.k_cache(layer), pool.v_cache(layer), block_table, md.cu_q, md.seq_lens, scale,
-            causal=md.causal, window=window, mask=md.mask, mask_window=md.mask_window,
+            causal=md.causal, window=window, mask=mask, mask_window=md.mask_window,
             k_scale=pool.k_scale[layer] if fp8 else None,
             v_scale=pool.v_scale[layer] if fp8 else None,
             max_q=md.max_q, max_kv=md.max_kv, decode=md.decode, workspace=md.workspace, splits=splits,

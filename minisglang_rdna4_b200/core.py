@@ -172,6 +172,8 @@ class Batch:
     spec_verify: bool = False
     verify_width: int = 0
     tree_mask: Optional[torch.Tensor] = None
+    # the mask sliding-window layers take instead of ``tree_mask`` (a mask replaces their window rule too)
+    tree_mask_swa: Optional[torch.Tensor] = None
     # > 0: ``tree_mask`` is ``[rows, mask_window]`` and covers the last mask_window K/V positions of each request
     mask_window: int = 0
     # capture the hidden states of these layer indices (EAGLE3 auxiliary features)

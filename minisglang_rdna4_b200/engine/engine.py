@@ -677,7 +677,7 @@ class Engine:
             self.ctx.attn_backend.prepare_metadata(
                 batch, block_table, cu_q, seq_lens, plan.max_q, plan.max_kv,
                 causal=True, mask=batch.tree_mask, host_cu_q=plan.cu_q, host_seq_lens=plan.seq_lens,
-                mask_window=batch.mask_window)
+                mask_window=batch.mask_window, mask_swa=batch.tree_mask_swa)
             with self.ctx.forward_batch(batch):
                 hidden = self.model.forward(batch.input_ids)
                 if n_sample == 0:

@@ -151,6 +151,7 @@ ENV.int("RECURRENT_SNAPSHOT_MIB", 2048, "memory for recurrent-state snapshots (p
         "prefix reuse for models with recurrent layers")
 ENV.int("RECURRENT_SNAPSHOT_TOKENS", 512, "a running request's recurrent state is kept every this many tokens")
 ENV.int("RECURRENT_SNAPSHOT_HOST_MIB", 0, "keep recurrent-state snapshots in this much page-locked host memory instead of device memory (0 = on the device)")
+ENV.flag("IMAGE_BIDIRECTIONAL", True, "the placeholder tokens of one image attend to each other in both directions during the prefill (as the published Gemma-3 does); off = causal")
 ENV.flag("STATE_DIGEST", False, "log exact per-layer digests of the K/V and recurrent state every prefill leaves behind (diagnostic; slow)")
 ENV.str("BAKED_DIR", "", "directory of baked checkpoints: a rank's weights as they stand after loading, streamed back on later "
         "boots instead of parsing, slicing and merging the checkpoint again (written on the first boot)")

@@ -29,6 +29,7 @@ class PendingReq:
     input_ids: torch.Tensor
     sampling_params: SamplingParams
     chunked: Optional[ChunkedReq] = None
+    spans: Optional[object] = None          # [n, 2] positions of image placeholder runs
 
     @property
     def input_len(self) -> int:
@@ -93,6 +94,15 @@ class PrefillAdder:
             # a chunk that is not the last ends on a page boundary: recurrent-state snapshots and the
             # prefix cache work in whole pages
             chunk -= (cached + chunk) % ps
+        spans = getattr(pending, "spans", None)
+        if spans is not None and chunk < remain:
+            # the tokens of one image are computed in one step (they attend to each other): a chunk that
+            # would end inside an image stops before it, or takes all of it when the image comes first
+            end = cached + chunk
+            for a, b in spans.tolist():
+                if a < end < b:
+                    chunk = (a - cached) if a > cached else min(remain, b - cached)
+                    break
         self.token_budget -= chunk
         final = chunk == remain
         cls = Req if final else ChunkedReq

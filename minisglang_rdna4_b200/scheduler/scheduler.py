@@ -175,6 +175,8 @@ class Scheduler:
             if ids is None:
                 return
         self.prefill.add_one_req(msg.uid, ids, params)
+        if msg.uid in self.mm:
+            self.prefill.pending[-1].spans = self.mm[msg.uid][2]      # a prefill chunk must not cut an image
         from ..utils.tracing import log_request
 
         log_request("admit", msg.uid, prompt=n, max_new=max_new)
@@ -211,7 +213,9 @@ class Scheduler:
         for i in range(n):
             h = int.from_bytes(hashlib.sha1(images[i].contiguous().numpy().tobytes()).digest()[:4], "little")
             ids[pos[i * per:(i + 1) * per]] = (vocab + h % (1 << 29) + torch.arange(per)).to(ids.dtype)
-        self.mm[uid] = (pos.numpy().astype(np.int64), emb)
+        where = pos.numpy().astype(np.int64)
+        spans = np.stack([where[0::per], where[per - 1::per] + 1], axis=1) if n else np.zeros((0, 2), dtype=np.int64)
+        self.mm[uid] = (where, emb, spans)
         return ids
 
     def _image_rows(self, batch: Batch, plan: StepPlan) -> None:
@@ -221,7 +225,7 @@ class Scheduler:
             entry = self.mm.get(r.uid)
             if entry is None:
                 continue
-            pos, emb = entry
+            pos, emb, _spans = entry
             lo, hi = int(r.cached_len), int(r.device_len)
             sel = np.nonzero((pos >= lo) & (pos < hi))[0]
             if sel.size:
@@ -230,6 +234,43 @@ class Scheduler:
         if rows:
             batch.mm_rows = torch.as_tensor(np.concatenate(rows), dtype=torch.int64).to(self.engine.device)
             batch.mm_values = torch.cat(vals)
+            if ENV.IMAGE_BIDIRECTIONAL.value:
+                self._image_masks(batch, plan)
+
+    def _image_masks(self, batch: Batch, plan: StepPlan) -> None:
+        """Additive masks of a prefill step that computes image rows: causal everywhere, and the tokens of
+        one image see each other in both directions (the published Gemma-3 prefill). A mask replaces the
+        kernel's causal and window rules for every row of the step, so both are written out here, and the
+        sliding-window layers get a mask of their own with their window in it."""
+        mc = self.engine.model_config
+        window = int(mc.sliding_window) if (mc.sliding_window and mc.swa_layers) else 0
+        total, max_kv = plan.num_tokens, int(plan.max_kv)
+        neg = float("-inf")
+        full = torch.full((total, max_kv), neg, dtype=torch.float32)
+        local = torch.full((total, max_kv), neg, dtype=torch.float32) if window else None
+        k = torch.arange(max_kv)[None, :]
+        for i, r in enumerate(batch.reqs):
+            lo, hi = int(r.cached_len), int(r.device_len)
+            q = torch.arange(lo, hi)[:, None]
+            seen = (k <= q)
+            same = torch.zeros_like(seen)
+            entry = self.mm.get(r.uid)
+            if entry is not None:
+                image_of = torch.full((max(hi, 1),), -1, dtype=torch.int64)
+                for j, (a, b) in enumerate(entry[2].tolist()):
+                    image_of[a:min(b, hi)] = j
+                iq = image_of[lo:hi][:, None]
+                ik = torch.full((max_kv,), -2, dtype=torch.int64)
+                ik[:hi] = image_of[:hi]
+                same = (iq == ik[None, :]) & (iq >= 0)
+            rows = slice(int(plan.cu_q[i]), int(plan.cu_q[i + 1]))
+            inside = k < hi
+            full[rows] = torch.where((seen | same) & inside, 0.0, neg)
+            if local is not None:
+                local[rows] = torch.where(((seen & (k > q - window)) | same) & inside, 0.0, neg)
+        dev = self.engine.device
+        batch.tree_mask = full.to(dev)
+        batch.tree_mask_swa = local.to(dev) if local is not None else None
 
     def _abort(self, uid: int) -> None:
         pending = self.prefill.abort(uid)

@@ -64,14 +64,18 @@ def test_vision_tower_and_projector_match_transformers():
         assert torch.allclose(got, want.reshape(-1, want.shape[-1]), atol=1e-5)
 
 
-def test_prompts_with_images_match_transformers_and_the_prefix_cache_tells_images_apart():
+@pytest.mark.parametrize("bidirectional", [True, False])
+def test_prompts_with_images_match_transformers_and_the_prefix_cache_tells_images_apart(bidirectional, monkeypatch):
     """Image placeholder rows take the projected vision features (unscaled, as the published model inserts
-    them); a 16-token prefill chunk cuts through image spans; the same prompt with another image must not
-    hit the first one's cached pages, the same image again does. Attention over image tokens is causal
-    here (the published implementation also offers a bidirectional form within an image)."""
+    them); prefill chunks of 16 tokens stop before an image or take all of it; the same prompt with another
+    image must not hit the first one's cached pages, the same image again does. The tokens of one image
+    attend to each other in both directions during the prefill, as the published model does when it is
+    given ``token_type_ids`` (global and sliding-window layers get their own masks); with
+    MSGL_IMAGE_BIDIRECTIONAL=0 attention stays causal, which is the published model without them."""
     from minisglang_rdna4_b200 import SamplingParams
     from minisglang_rdna4_b200.llm import LLM
 
+    monkeypatch.setenv("MSGL_IMAGE_BIDIRECTIONAL", "1" if bidirectional else "0")
     with tempfile.TemporaryDirectory() as tmp:
         hf = _tiny(tmp)
         g = torch.Generator().manual_seed(3)
@@ -82,11 +86,13 @@ def test_prompts_with_images_match_transformers_and_the_prefix_cache_tells_image
 
         pa = text(5) + [501] + text(20) + [501] + text(7)        # two images inside the text
         pb = text(30)                                           # none
-        pc = [501] + text(11)                                   # an image first
+        pc = [501] + text(30)                                   # an image first
 
         def reference(p, im):
             ids = torch.tensor([_expand(p)])
             kw = {} if im is None else {"pixel_values": _norm(im)}
+            if im is not None and bidirectional:
+                kw["token_type_ids"] = (ids == 500).long()
             with torch.no_grad():
                 out = hf.generate(input_ids=ids, max_new_tokens=8, do_sample=False, eos_token_id=None, pad_token_id=0,
                                   **kw)
@@ -102,7 +108,7 @@ def test_prompts_with_images_match_transformers_and_the_prefix_cache_tells_image
         other = llm.generate([pc], sp, images=[[imgs[0]]])[0]
         assert other.token_ids == reference(pc, imgs[:1]) and other.cached_tokens == 0
         again = llm.generate([pc], sp, images=[[imgs[2]]])[0]
-        assert again.token_ids == want[2] and again.cached_tokens == 16
+        assert again.token_ids == want[2] and again.cached_tokens == 32
         assert not llm.mm                                         # features are dropped with the request
         with pytest.raises(ValueError, match="image marker"):    # an image without its marker in the prompt
             llm.generate([pb], sp, images=[[imgs[0]]])

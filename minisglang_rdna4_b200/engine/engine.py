@@ -246,13 +246,29 @@ class Engine:
             self._swa_page_bytes = page_bytes
             if config.cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0:
                 self._swa_pages += (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(page_bytes, 1)
+        # latent-attention models can keep the compressed latent per token instead of per-head K/V
+        # (MSGL_MLA_LATENT): absorbed attention through tensor ops, eager steps, no draft verification
+        self.mla_latent = bool(ENV.MLA_LATENT.value and mc.is_mla)
+        if self.mla_latent:
+            if self.kv_fp8 or self.kv_calibrating:
+                raise ValueError("the latent pool (MSGL_MLA_LATENT) is 16-bit only")
+            if config.spec_algorithm != "none":
+                raise ValueError("the latent pool (MSGL_MLA_LATENT) does not verify drafts; turn speculation off")
         self.num_pages = self._determine_num_pages()
         self.max_seq_len = self._resolve_max_seq_len()
         self.max_pages_per_seq = cdiv(self.max_seq_len, self.page_size)
-        self.kv_cache = MHAKVCache(
-            self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
-            self.dtype, self.device, fp8=self.kv_fp8,
-        )
+        if self.mla_latent:
+            from ..kvcache.mla_pool import MLALatentCache
+
+            self.kv_cache = MLALatentCache(self.kv_layers, self.num_pages, self.page_size, int(mc.kv_lora_rank),
+                                           int(mc.qk_rope_head_dim), self.dtype, self.device)
+            logger.info_rank0("latent K/V pool: %d values per token and layer (per-head K/V would take %d)",
+                              self.kv_cache.width, 2 * self.kv_heads_local * mc.head_dim)
+        else:
+            self.kv_cache = MHAKVCache(
+                self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
+                self.dtype, self.device, fp8=self.kv_fp8,
+            )
         if self.kv_fp8:
             from ..kvcache.fp8_scales import resolve_kv_scales
 
@@ -374,7 +390,7 @@ class Engine:
             # host tier: only then must a GEMM wait for the stream before it reads its weights
             K.gemm_static_weights((2 if ENV.GEMM_L2_AHEAD.value else 1) if (ENV.PDL.value and not host_tier) else 0)
         if (dev_kind == "cuda" and not ENV.DISABLE_GRAPH.value and not self.kv_calibrating and (config.cuda_graph_max_bs or 0) >= 0
-                and not ep_replicas and not host_tier):
+                and not ep_replicas and not host_tier and not self.mla_latent):
             from .graph import GraphRunner
 
             before = self._free_memory()
@@ -490,6 +506,11 @@ class Engine:
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
         per_page = MHAKVCache.token_bytes(self.kv_layers, self.kv_heads_local, mc.head_dim,
                                           itemsize) * self.page_size
+        if self.mla_latent:
+            from ..kvcache.mla_pool import MLALatentCache
+
+            per_page = MLALatentCache.token_bytes(self.kv_layers, int(mc.kv_lora_rank), int(mc.qk_rope_head_dim),
+                                                  itemsize) * self.page_size
         if cfg.spec_algorithm in ("eagle3", "mtp"):
             # the draft head keeps one 16-bit, unsharded layer of K/V on the same page table
             per_page += MHAKVCache.token_bytes(1, mc.num_kv_heads, mc.head_dim, 2) * self.page_size

@@ -92,6 +92,8 @@ class LatentAttention(BaseOP):
         q = q.view(t, h, d)
         ckv = self.kv_a_proj_with_mqa.forward(x)
         latent, k_rot = ckv[:, : self._lora], ckv[:, self._lora:]
+        if getattr(get_global_ctx().kv_cache, "latent", False):
+            return self._forward_absorbed(q, latent, k_rot)
         kv = self.kv_b_proj.forward(self.kv_a_layernorm.forward(latent.contiguous())).view(t, h, nope + self._vd)
         # [rope ‖ nope] layout for q and k (the same permutation on both sides of every dot product)
         pd, vd = self._pd, self._vd
@@ -106,6 +108,33 @@ class LatentAttention(BaseOP):
         if pd != vd:                               # the padding channels of the value heads come back as zeros
             o = o.view(t, h, pd)[:, :, :vd].reshape(t, h * vd)
         return self.o_proj.forward(o, reduce=True)
+
+
+    def _forward_absorbed(self, q: torch.Tensor, latent: torch.Tensor, k_rot: torch.Tensor) -> torch.Tensor:
+        """The pool holds the normalised latent and the shared rotary key of every token
+        (``kvcache/mla_pool.py``); queries go into the latent space through the key half of ``kv_b_proj``,
+        the attended latents come back through its value half."""
+        from ..layers.rotary import get_rope_cache
+        from ..ops import ref
+
+        ctx = get_global_ctx()
+        batch, md, pool = ctx.batch, ctx.batch.attn_metadata, ctx.kv_cache
+        t, h, nope, rope, vd, lora = q.shape[0], self._h, self._nope, self._rope, self._vd, self._lora
+        w = getattr(self.kv_b_proj, "weight", None)
+        if w is None or w.dtype not in (torch.float32, torch.bfloat16, torch.float16) or w.shape[1] != lora:
+            raise NotImplementedError("the latent pool needs kv_b_proj in a 16- or 32-bit dense form")
+        w = w.view(h, nope + vd, lora)
+        rot_cfg = self.attn._rotary
+        cos_sin = get_rope_cache(rot_cfg, q.device)
+        q_rot, k_rot = ref.qk_norm_rope(q[:, :, nope:].reshape(t, h * rope), k_rot.contiguous(), None, None,
+                                        batch.positions, cos_sin, rope, rope, 0.0, rot_cfg.interleaved)
+        layer = self.attn._kv_index
+        pool.store(layer, self.kv_a_layernorm.forward(latent.contiguous()), k_rot, batch.out_loc)
+        q_lat = torch.einsum("thn,hnl->thl", q[:, :, :nope].float(), w[:, :nope].float()).to(q.dtype)
+        o_lat = ref.mla_attention(q_lat, q_rot.view(t, h, rope), pool.rows(layer), md.block_table, md.cu_q,
+                                  md.seq_lens, self.attn._scale, lora)
+        o = torch.einsum("thl,hvl->thv", o_lat.float(), w[:, nope:].float()).to(q.dtype)
+        return self.o_proj.forward(o.reshape(t, h * vd), reduce=True)
 
 
 class GlmMoEBlock(BaseOP):

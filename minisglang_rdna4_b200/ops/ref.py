@@ -255,6 +255,38 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out.to(q.dtype)
 
 
+def mla_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, rows: torch.Tensor, block_table: torch.Tensor,
+                  cu_q: torch.Tensor, seq_lens: torch.Tensor, scale: float, lora_rank: int) -> torch.Tensor:
+    """Absorbed latent attention over a paged pool of ``[latent ‖ rotary key]`` rows.
+
+    ``q_lat`` ``[T, H, lora]`` (queries already multiplied by the key half of ``kv_b_proj``), ``q_rot``
+    ``[T, H, rope]``, ``rows`` ``[pages, page_size, lora + rope]``. Every head attends to the same
+    single key per position: score = ``q_lat . latent + q_rot . k_rot``; causal; the result is the
+    softmax-weighted sum of the latents ``[T, H, lora]`` (the value half of ``kv_b_proj`` is applied by
+    the caller). Written with tensor ops that run on either device
+    (python/minisgl/attention/mla.py:99-161)."""
+    t, h, _ = q_lat.shape
+    ps = rows.shape[1]
+    out = torch.zeros((t, h, lora_rank), dtype=torch.float32, device=q_lat.device)
+    cu = cu_q.tolist()
+    lens = seq_lens.tolist()
+    for b in range(len(lens)):
+        qs, qe, kv_len = cu[b], cu[b + 1], lens[b]
+        q_len = qe - qs
+        if q_len == 0 or kv_len == 0:
+            continue
+        n_pages = -(-kv_len // ps)
+        kv = rows[block_table[b, :n_pages].long()].reshape(n_pages * ps, -1)[:kv_len].float()
+        lat, rot = kv[:, :lora_rank], kv[:, lora_rank:]
+        s = (torch.einsum("qhl,kl->hqk", q_lat[qs:qe].float(), lat)
+             + torch.einsum("qhr,kr->hqk", q_rot[qs:qe].float(), rot)) * scale
+        q_pos = torch.arange(kv_len - q_len, kv_len, device=s.device)[:, None]
+        k_pos = torch.arange(kv_len, device=s.device)[None, :]
+        s = s.masked_fill((k_pos > q_pos)[None], float("-inf"))
+        out[qs:qe] = torch.einsum("hqk,kl->qhl", torch.softmax(s, dim=-1), lat)
+    return out.to(q_lat.dtype)
+
+
 # ------------------------------------------------------------------------------------------
 # quantised GEMMs (reference dequantises the weight and multiplies in fp32)
 # ------------------------------------------------------------------------------------------

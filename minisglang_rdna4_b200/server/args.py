@@ -77,6 +77,9 @@ def build_parser() -> argparse.ArgumentParser:
     # shorthands for environment switches (the engine processes inherit the environment)
     p.add_argument("--swa-pool", action="store_true",
                    help="sliding-window layers keep their K/V in a pool of their own with recycled pages (MSGL_SWA_POOL)")
+    p.add_argument("--mla-latent", action="store_true",
+                   help="latent-attention models keep the compressed latent per token instead of per-head K/V: far more "
+                        "tokens in the pool, attention through tensor ops on eager steps (MSGL_MLA_LATENT)")
     p.add_argument("--baked-dir", default="",
                    help="directory of baked checkpoints: written on the first boot, streamed on later ones (MSGL_BAKED_DIR)")
     p.add_argument("--tp-overlap", action="store_true",
@@ -97,7 +100,7 @@ def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
     import os
 
     for flag, var, value in ((ns.swa_pool, "MSGL_SWA_POOL", "1"), (ns.baked_dir, "MSGL_BAKED_DIR", ns.baked_dir),
-                             (ns.tp_overlap, "MSGL_TP_OVERLAP", "1")):
+                             (ns.tp_overlap, "MSGL_TP_OVERLAP", "1"), (ns.mla_latent, "MSGL_MLA_LATENT", "1")):
         if flag:
             os.environ[var] = value
     if ns.enable_ep and ns.tp_size * ns.dp_size == 1:

@@ -300,3 +300,66 @@ def test_glm4_moe_next_token_layer_drafts_exactly():
         want = [o.token_ids for o in plain.generate(prompts, sp)]
         plain.shutdown()
     assert got == want
+
+
+@pytest.mark.parametrize("family", ["glm_lite", "deepseek_v3"])
+def test_latent_pool_with_absorbed_attention_matches_transformers(family, monkeypatch):
+    """MSGL_MLA_LATENT: the pool holds kv_lora_rank + rope values per token and layer (40 here against
+    256 for per-head keys and values); queries go through the key half of kv_b_proj into the latent
+    space and the attended latents come back through its value half. Chunked prefill (the second
+    chunk attends to latents stored by the first), batched decode and prefix reuse give the tokens of the
+    Hugging Face model, which expands the latents per head."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.kvcache.mla_pool import MLALatentCache
+    from minisglang_rdna4_b200.llm import LLM
+
+    monkeypatch.setenv("MSGL_MLA_LATENT", "1")
+    with tempfile.TemporaryDirectory() as tmp:
+        if family == "glm_lite":
+            hf = _hf(tmp, 4, 2, 24)
+        else:
+            from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+
+            cfg = DeepseekV3Config(
+                vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
+                num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1, n_routed_experts=8,
+                routed_scaling_factor=2.5, kv_lora_rank=32, q_lora_rank=None, qk_rope_head_dim=8, v_head_dim=16,
+                qk_nope_head_dim=24, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+                max_position_embeddings=512, eos_token_id=299, bos_token_id=None, pad_token_id=None,
+                rope_parameters=dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=64, beta_fast=32,
+                                     beta_slow=1, mscale=1.0, mscale_all_dim=0.7, rope_theta=10000.0))
+            torch.manual_seed(0)
+            hf = DeepseekV3ForCausalLM(cfg).float().eval()
+            with torch.no_grad():
+                for _, p in hf.named_parameters():
+                    if p.dim() >= 2:
+                        p.copy_(torch.randn_like(p) * 0.08)
+            hf.save_pretrained(tmp, safe_serialization=True)
+        g = torch.Generator().manual_seed(1)
+        shared = torch.randint(0, 298, (48,), generator=g).tolist()
+        prompts = [torch.randint(0, 298, (n,), generator=g).tolist() for n in (5, 90, 41)]
+        prompts.append(shared + [7, 8, 9])
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=32)
+        pool = llm.engine.kv_cache
+        assert isinstance(pool, MLALatentCache) and pool.width == 40 and llm.engine.graph_runner is None
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+        # a second request over the same 48-token prefix reads the latents the first one left in the pool
+        again = shared + [11, 12]
+        want2 = hf.generate(torch.tensor([again]), max_new_tokens=6, do_sample=False)[0, len(again):].tolist()
+        got2 = llm.generate([again], SamplingParams(max_tokens=6, ignore_eos=True))[0]
+        llm.shutdown()
+    assert got == want
+    assert got2.token_ids == want2 and got2.cached_tokens >= 32
+
+
+def test_latent_pool_refuses_what_it_cannot_serve(monkeypatch):
+    from minisglang_rdna4_b200.llm import LLM
+
+    monkeypatch.setenv("MSGL_MLA_LATENT", "1")
+    with tempfile.TemporaryDirectory() as tmp:
+        _hf(tmp)
+        with pytest.raises(ValueError, match="does not verify drafts"):
+            LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                spec_algorithm="ngram")

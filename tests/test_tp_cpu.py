@@ -386,10 +386,13 @@ def test_block_diffusion_under_tp2_matches_tp1_on_cpu():
     assert got == want
 
 
-@pytest.mark.parametrize("ep", [False, True])
-def test_deepseek_v3_tp2_matches_tp1_on_cpu(ep):
+@pytest.mark.parametrize("mode", ["tp", "ep", "tp_latent"])
+def test_deepseek_v3_tp2_matches_tp1_on_cpu(mode, monkeypatch):
     """Latent attention with zero-padded value heads and the grouped sigmoid routing under tensor parallelism
-    (heads and expert width split) and with the experts split over the ranks instead."""
+    (heads and expert width split) and with the experts split over the ranks instead. ``tp_latent``: the two
+    ranks keep the compressed latents (each its own copy; its heads' slices of kv_b_proj absorb and expand)
+    and give the tokens of one rank with per-head K/V."""
+    ep = mode == "ep"
     T = pytest.importorskip("transformers")
     cfg = T.DeepseekV3Config(
         vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=3,
@@ -411,9 +414,11 @@ def test_deepseek_v3_tp2_matches_tp1_on_cpu(ep):
     with tempfile.TemporaryDirectory() as tmp:
         hf.save_pretrained(tmp, safe_serialization=True)
         want = _single(tmp, prompts)
+        if mode == "tp_latent":
+            monkeypatch.setenv("MSGL_MLA_LATENT", "1")      # the spawned ranks inherit it
         ctx = mp.get_context("spawn")
         q = ctx.Queue()
-        port = 23100 + (os.getpid() % 1500) + (3 if ep else 0)
+        port = 23100 + (os.getpid() % 1500) + {"tp": 0, "ep": 3, "tp_latent": 6}[mode]
         procs = [ctx.Process(target=_worker, args=(r, 2, port, tmp, prompts, q, ep)) for r in range(2)]
         for p in procs:
             p.start()

@@ -226,7 +226,7 @@ class Engine:
 
             n_global = n_swa = 0
             for mod in self.model.modules():
-                if isinstance(mod, AttentionLayer):
+                if isinstance(mod, AttentionLayer) and mod._kv_donor is None:
                     if mod._window > 0:
                         mod._swa, mod._kv_index = True, n_swa
                         n_swa += 1
@@ -246,6 +246,32 @@ class Engine:
             self._swa_page_bytes = page_bytes
             if config.cache_type == "radix" and ENV.RECURRENT_SNAPSHOT_MIB.value > 0:
                 self._swa_pages += (ENV.RECURRENT_SNAPSHOT_MIB.value << 20) // max(page_bytes, 1)
+        # layers that read an earlier layer's K/V take that layer's pool and row
+        if mc.num_kv_shared_layers:
+            from ..layers.attention import AttentionLayer
+
+            by_id = {m._layer_id: m for m in self.model.modules() if isinstance(m, AttentionLayer)}
+            for m in by_id.values():
+                if m._kv_donor is not None:
+                    m._swa, m._kv_index = by_id[m._kv_donor]._swa, by_id[m._kv_donor]._kv_index
+        # (kv heads, head width) of the main pool and, with two pools, of the sliding-window one
+        tp_ = config.tp_size
+        geoms = [mc.attn_geometry(i) for i in range(mc.num_kv_layers)] if mc.global_head_dim else None
+        self._main_geometry = None
+        self._swa_geometry = (self.kv_heads_local, mc.head_dim)
+        if geoms:
+            local = [(div_even(h, tp_, allow_replicate=True), d) for h, d in geoms]
+            if self._swa_layers:
+                swa_set = set(mc.swa_layers)
+                self._main_geometry = [g_ for i, g_ in enumerate(local) if i not in swa_set] or [local[0]]
+                self._swa_geometry = next(g_ for i, g_ in enumerate(local) if i in swa_set)
+            else:
+                self._main_geometry = local
+            widths = {d for _, d in local}
+            if self.device.type == "cuda" and (len(set(self._main_geometry)) > 1 or not widths <= {64, 128, 256}):
+                raise NotImplementedError(
+                    f"attention head widths {sorted(widths)}: the attention kernels are built for 64 / 128 / 256 "
+                    "and one geometry per pool; this model runs on the CPU oracle path only")
         # latent-attention models can keep the compressed latent per token instead of per-head K/V
         # (MSGL_MLA_LATENT): absorbed attention through tensor ops, eager steps, no draft verification
         self.mla_latent = bool(ENV.MLA_LATENT.value and mc.is_mla)
@@ -267,7 +293,7 @@ class Engine:
         else:
             self.kv_cache = MHAKVCache(
                 self.kv_layers, self.num_pages, self.page_size, self.kv_heads_local, mc.head_dim,
-                self.dtype, self.device, fp8=self.kv_fp8,
+                self.dtype, self.device, fp8=self.kv_fp8, geometry=self._main_geometry,
             )
         if self.kv_fp8:
             from ..kvcache.fp8_scales import resolve_kv_scales
@@ -287,8 +313,8 @@ class Engine:
         if self._swa_layers:
             from ..kvcache.swa_pages import SwaPages
 
-            self.swa_kv_cache = MHAKVCache(self._swa_layers, self._swa_pages, self.page_size, self.kv_heads_local,
-                                           mc.head_dim, self.dtype, self.device, fp8=self.kv_fp8)
+            self.swa_kv_cache = MHAKVCache(self._swa_layers, self._swa_pages, self.page_size, self._swa_geometry[0],
+                                           self._swa_geometry[1], self.dtype, self.device, fp8=self.kv_fp8)
             if self.kv_fp8:
                 ids = list(mc.swa_layers)
                 self.swa_kv_cache.set_scales(self._kv_scales[0][ids], self._kv_scales[1][ids])
@@ -506,6 +532,9 @@ class Engine:
         itemsize = 1 if self.kv_fp8 else torch.empty((), dtype=self.dtype).element_size()
         per_page = MHAKVCache.token_bytes(self.kv_layers, self.kv_heads_local, mc.head_dim,
                                           itemsize) * self.page_size
+        if self._main_geometry:
+            per_page = MHAKVCache.token_bytes(self.kv_layers, 1, max(h * d for h, d in self._main_geometry),
+                                              itemsize) * self.page_size
         if self.mla_latent:
             from ..kvcache.mla_pool import MLALatentCache
 

@@ -28,7 +28,22 @@ class MHAKVCache(BaseKVCachePool):
         dtype: torch.dtype,
         device: torch.device,
         fp8: bool = False,
+        geometry=None,
     ) -> None:
+        # geometry: (kv heads, head width) per layer for models whose layers differ (Gemma-4: wide global
+        # heads, narrower sliding ones). Every layer then gets rows of the widest layer's size and views the
+        # front of each page as its own [heads, page_size, width] block. 16-bit, tensor-op paths only: the
+        # views are strided and the kernels take dense pools.
+        self._views = None
+        if geometry is not None and len(set(geometry)) > 1:
+            if fp8:
+                raise ValueError("a pool with per-layer head geometry is 16-bit only")
+            if len(geometry) != num_layers:
+                raise ValueError("one (heads, width) pair per layer")
+            self.geometry = [(int(h), int(d)) for h, d in geometry]
+            num_kv_heads, head_dim = 1, max(h * d for h, d in self.geometry)
+        elif geometry is not None:
+            num_kv_heads, head_dim = geometry[0]
         self.num_layers = num_layers
         self.num_pages = num_pages
         self.page_size = page_size
@@ -47,6 +62,10 @@ class MHAKVCache(BaseKVCachePool):
         self.v_scale = torch.ones((num_layers, num_kv_heads), dtype=torch.float32, device=device)
         # calibration run (16-bit pool only): running |max| per (layer, head) of every row written
         self.amax: Optional[torch.Tensor] = None
+        if getattr(self, "geometry", None) is not None:
+            pages, ps, width = num_pages + 1, page_size, head_dim
+            self._views = [[self._buf[which, layer].view(pages, ps * width)[:, : h * ps * d].view(pages, h, ps, d)
+                            for layer, (h, d) in enumerate(self.geometry)] for which in (0, 1)]
 
     # ---- calibration of the fp8 descales (python/minisgl/kvcache/mha_pool.py:123-270) ----
     def start_calibration(self) -> None:
@@ -86,10 +105,10 @@ class MHAKVCache(BaseKVCachePool):
         return self.num_pages
 
     def k_cache(self, layer: int) -> torch.Tensor:
-        return self._buf[0, layer]
+        return self._buf[0, layer] if self._views is None else self._views[0][layer]
 
     def v_cache(self, layer: int) -> torch.Tensor:
-        return self._buf[1, layer]
+        return self._buf[1, layer] if self._views is None else self._views[1][layer]
 
     @property
     def device(self) -> torch.device:
@@ -118,7 +137,7 @@ class MHAKVCache(BaseKVCachePool):
         from ..ops import store_kv
 
         store_kv(
-            k, v, self._buf[0, layer], self._buf[1, layer], out_loc,
+            k, v, self.k_cache(layer), self.v_cache(layer), out_loc,
             self.k_scale[layer] if self.fp8 else None,
             self.v_scale[layer] if self.fp8 else None,
         )

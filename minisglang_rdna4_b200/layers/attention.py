@@ -31,6 +31,9 @@ class AttentionLayer(BaseOP):
         # when sliding-window layers get a pool of their own
         self._swa = False
         self._kv_index = layer_id
+        # a layer that reads the K/V another layer stored (same positions, same pool rows) and stores nothing:
+        # the other layer's decoder index; the engine resolves it to that layer's pool and row
+        self._kv_donor: Optional[int] = None
 
     def forward(self, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor] = None,
                 k_norm_w: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -41,6 +44,11 @@ class AttentionLayer(BaseOP):
         pool = ctx.swa_kv_cache if self._swa else ctx.kv_cache
         layer = self._kv_index
         out_loc = batch.swa_out_loc if self._swa else batch.out_loc
+        if self._kv_donor is not None:          # qkv holds the queries only
+            q = ops.q_norm_rope(qkv, q_norm_w, batch.positions, self._cos_sin, self._hq, self._d,
+                                self._rotary.rotary_dim, self._eps, self._rotary.interleaved)
+            out = ctx.attn_backend.forward(q, layer, batch, scale=self._scale, window=self._window, swa=self._swa)
+            return out.reshape(out.shape[0], self._hq * self._d)
         k_scale = pool.k_scale[layer] if pool.fp8 else None
         v_scale = pool.v_scale[layer] if pool.fp8 else None
         q = ops.qk_norm_rope_store(

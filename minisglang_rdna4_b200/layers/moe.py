@@ -120,6 +120,13 @@ class MoELayer(BaseOP):
             from ..ops.moe_kernels import moe_forward_quant
 
             return moe_forward_quant(self._quant_kind, x, packed, topk_w, topk_ids, self._e_start, counts)
+        if self._act != "silu":
+            # GELU-gated experts (Gemma-4): the grouped-GEMM kernels apply SiLU in their epilogue
+            if x.is_cuda:
+                raise NotImplementedError(f"no expert kernel with a {self._act} gate")
+            from ..ops import ref
+
+            return ref.moe_forward(x, self.w13, self.w2, topk_w, topk_ids, self._e_start, act=self._act)
         if x.is_cuda:
             from ..ops import cuda as K
 

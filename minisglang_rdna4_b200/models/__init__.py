@@ -25,6 +25,12 @@ def _register_defaults() -> None:
             MODEL_REGISTRY.register(arch)(GemmaForCausalLM)
 
 
+    from .gemma4 import Gemma4ForCausalLM
+
+    for arch in ("Gemma4ForCausalLM", "Gemma4ForConditionalGeneration"):
+        if arch not in MODEL_REGISTRY:
+            MODEL_REGISTRY.register(arch)(Gemma4ForCausalLM)
+
     from .qwen3_5 import Qwen3_5ForCausalLM
 
     for arch in ("Qwen3_5ForCausalLM", "Qwen3_5ForConditionalGeneration", "Qwen3_5MoeForCausalLM",

@@ -98,6 +98,16 @@ class ModelConfig:
     # Gemma family
     query_pre_attn_scalar: Optional[float] = None   # attention scale = this ** -0.5 (default head_dim)
     rope_local_base_freq: Optional[float] = None    # RoPE base of the sliding-window layers
+    # Gemma-4: global layers with their own head width / K/V head count, keys reused as values, the last
+    # layers reading the K/V of an earlier layer of their kind, per-layer input embeddings
+    global_head_dim: Optional[int] = None
+    num_global_kv_heads: Optional[int] = None
+    attention_k_eq_v: bool = False
+    num_kv_shared_layers: int = 0
+    hidden_size_per_layer_input: int = 0
+    vocab_size_per_layer_input: int = 0
+    use_double_wide_mlp: bool = False
+    enable_moe_block: bool = False
     num_nextn_predict_layers: int = 0
     mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
     canvas_length: int = 0                    # block-diffusion models: tokens written per block
@@ -136,16 +146,39 @@ class ModelConfig:
         """Layers that keep K/V pages."""
         if self.model_type == "nemotron_h":
             return sum(1 for t in (self.layer_types or ()) if t == "attention")
-        return self.num_layers - self.num_linear_layers
+        return self.num_layers - self.num_linear_layers - self.num_kv_shared_layers
 
     @property
     def swa_layers(self) -> Tuple[int, ...]:
-        """Decoder layers whose attention only looks at the last ``sliding_window`` positions."""
+        """Decoder layers whose attention only looks at the last ``sliding_window`` positions (of those
+        that keep K/V of their own)."""
         if not self.sliding_window or self.is_recurrent:
             return ()
         if self.layer_types:
-            return tuple(i for i, t in enumerate(self.layer_types) if t == "sliding_attention")
+            own = self.num_layers - self.num_kv_shared_layers
+            return tuple(i for i, t in enumerate(self.layer_types[:own]) if t == "sliding_attention")
         return tuple(range(self.num_layers)) if self.model_type == "mistral" else ()
+
+    def kv_donor(self, layer: int) -> Optional[int]:
+        """The earlier layer whose K/V ``layer`` reads instead of keeping its own: the last layer of the
+        same kind before the shared range (Gemma-4). ``None`` for a layer with K/V of its own."""
+        first = self.num_layers - self.num_kv_shared_layers
+        if not self.num_kv_shared_layers or layer < first:
+            return None
+        kind = self.layer_types[layer]
+        return max(i for i in range(first) if self.layer_types[i] == kind)
+
+    def attn_geometry(self, layer: int) -> Tuple[int, int]:
+        """``(kv heads, head width)`` of a layer's attention."""
+        if self.global_head_dim and self.layer_types and self.layer_types[layer] != "sliding_attention":
+            heads = self.num_global_kv_heads if (self.attention_k_eq_v and self.num_global_kv_heads) \
+                else self.num_kv_heads
+            return int(heads), int(self.global_head_dim)
+        return self.num_kv_heads, self.head_dim
+
+    @property
+    def mixed_kv_geometry(self) -> bool:
+        return len({self.attn_geometry(i) for i in range(self.num_kv_layers)}) > 1 if self.global_head_dim else False
 
     @property
     def recurrent_geometry(self) -> Tuple[int, int, int, int]:
@@ -261,14 +294,27 @@ class ModelConfig:
         local_theta = g("rope_local_base_freq")
         if local_theta is None and isinstance(rope_params.get("sliding_attention"), dict):
             local_theta = rope_params["sliding_attention"].get("rope_theta")
+        gemma4 = model_type in ("gemma4", "gemma4_text")
         if isinstance(rope_params.get("full_attention"), dict):  # per-layer-type RoPE tables
             full = rope_params["full_attention"]
             theta = float(full.get("rope_theta", theta))
             scaling = {k: v for k, v in full.items() if k != "rope_theta"} or None
             if scaling and scaling.get("rope_type", "default") in ("default", None):
                 scaling = None
-            rotary = RotaryConfig(head_dim=head_dim, rotary_dim=rope_dim, max_position=max_pos, base=theta,
-                                  scaling=scaling)
+            g_dim = int(g("global_head_dim") or head_dim) if gemma4 else head_dim
+            rotary = RotaryConfig(head_dim=g_dim, rotary_dim=g_dim if gemma4 else rope_dim, max_position=max_pos,
+                                  base=theta, scaling=scaling)
+        if gemma4:
+            if layer_types is None:
+                layer_types = ["sliding_attention" if (i + 1) % 6 else "full_attention"
+                               for i in range(int(g("num_hidden_layers")))]
+            layer_types = list(layer_types)
+            layer_types[-1] = "full_attention"
+            cfg = dict(cfg, hidden_act=g("hidden_activation", "gelu_pytorch_tanh"),
+                       num_experts_per_tok=g("top_k_experts"), tie_word_embeddings=g("tie_word_embeddings", True),
+                       num_experts=g("num_experts") if g("enable_moe_block") else 0)
+            g = cfg.get
+            num_experts = int(g("num_experts") or 0)
         if g("kv_lora_rank"):
             # latent attention: the pool holds materialised per-head keys of qk_nope + qk_rope channels;
             # the rotary part is GPT-J interleaved unless the checkpoint says otherwise
@@ -359,6 +405,14 @@ class ModelConfig:
             final_logit_softcapping=g("final_logit_softcapping"),
             query_pre_attn_scalar=g("query_pre_attn_scalar"),
             rope_local_base_freq=float(local_theta) if local_theta else None,
+            global_head_dim=int(g("global_head_dim") or 0) or None if gemma4 else None,
+            num_global_kv_heads=g("num_global_key_value_heads") if gemma4 else None,
+            attention_k_eq_v=bool(g("attention_k_eq_v", False)) if gemma4 else False,
+            num_kv_shared_layers=int(g("num_kv_shared_layers") or 0) if gemma4 else 0,
+            hidden_size_per_layer_input=int(g("hidden_size_per_layer_input") or 0) if gemma4 else 0,
+            vocab_size_per_layer_input=int(g("vocab_size_per_layer_input") or 0) if gemma4 else 0,
+            use_double_wide_mlp=bool(g("use_double_wide_mlp", False)) if gemma4 else False,
+            enable_moe_block=bool(g("enable_moe_block", False)) if gemma4 else False,
             num_nextn_predict_layers=int(g("num_nextn_predict_layers") or 0),
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             canvas_length=int(g("canvas_length") or g("block_length") or 0),
@@ -386,6 +440,8 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma2": ["Gemma2ForCausalLM"],
         "gemma3": ["Gemma3ForCausalLM"],
         "gemma3_text": ["Gemma3ForCausalLM"],
+        "gemma4": ["Gemma4ForCausalLM"],
+        "gemma4_text": ["Gemma4ForCausalLM"],
         "glm4_moe_lite": ["Glm4MoeLiteForCausalLM"],
         "glm4_moe": ["Glm4MoeForCausalLM"],
         "deepseek_v2": ["DeepseekV2ForCausalLM"],

@@ -294,7 +294,16 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                 assign(moe, "e_score_correction_bias", tensor.float(),
                        name[: -len(".gate.e_score_correction_bias")] + ".experts.e_score_correction_bias")
             continue
-        if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")) and tensor.dim() == 3:
+        if name.endswith(".router.proj.weight") and (name[: -len(".router.proj.weight")] + ".experts") in modules:
+            # Gemma-4: the router's projection is the expert layer's gate
+            moe = modules[name[: -len(".router.proj.weight")] + ".experts"]
+            assign(moe.gate, "weight", tensor, name[: -len(".router.proj.weight")] + ".experts.gate.weight")
+            continue
+        if name == "model.embed_tokens_per_layer.weight" and hasattr(model.model, "embed_tokens_per_layer"):
+            emb = model.model.embed_tokens_per_layer
+            assign(emb, "weight", vocab_shard(tensor, emb._per_rank), name)
+            continue
+        if name.endswith((".experts.gate_up_proj", ".experts.down_proj")) and tensor.dim() == 3:
             # expert stacks stored fused: [E, 2I, H] (gate rows then up rows) and [E, H, I]
             moe = modules.get(name.rsplit(".", 1)[0])
             if moe is None:

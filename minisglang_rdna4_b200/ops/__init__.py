@@ -102,6 +102,17 @@ def qk_norm_rope_store(qkv, q_w, k_w, positions, cos_sin, num_q_heads: int, num_
     return q.reshape(-1, num_q_heads, head_dim)
 
 
+def q_norm_rope(q, q_w, positions, cos_sin, num_q_heads: int, head_dim: int, rotary_dim: int, eps: float,
+                interleaved: bool = False):
+    """Per-head RMSNorm + rotary embedding of the queries alone ``[T, Hq * D]`` → ``[T, Hq, D]``: the form a
+    layer takes that reads another layer's K/V (Gemma-4's shared layers) and so has nothing to store."""
+    if q.is_cuda:
+        raise NotImplementedError("no kernel for the query-only norm + rotary step of a layer that shares K/V")
+    dummy_k = q[:, :head_dim]
+    out, _ = ref.qk_norm_rope(q, dummy_k, q_w, q_w, positions, cos_sin, head_dim, rotary_dim, eps, interleaved)
+    return out.reshape(-1, num_q_heads, head_dim)
+
+
 def store_kv(k, v, k_cache, v_cache, out_loc, k_scale=None, v_scale=None):
     if k.is_cuda:
         return _cuda().store_kv(k, v, k_cache, v_cache, out_loc, k_scale, v_scale)

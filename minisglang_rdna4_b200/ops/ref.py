@@ -125,6 +125,11 @@ def build_cos_sin_cache(rotary_dim: int, max_position: int, base: float,
                 mscale = yarn_mscale(float(scaling["mscale"])) / yarn_mscale(float(scaling["mscale_all_dim"]))
             else:
                 mscale = yarn_mscale()
+        elif kind == "proportional":
+            # Gemma-4 global layers: the first partial_rotary_factor of the pairs (i, i + dim/2) rotate with
+            # the frequencies of the full width, the others keep angle zero
+            angles = int(float(scaling.get("partial_rotary_factor", 1.0)) * rotary_dim // 2)
+            inv_freq = torch.where(torch.arange(half) < angles, inv_freq, torch.zeros_like(inv_freq)) / factor
         elif kind in ("default", "dynamic", None):
             pass
         else:
@@ -434,10 +439,10 @@ def moe_route_grouped(router_logits: torch.Tensor, top_k: int, renormalize: bool
 
 
 def moe_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
-                topk_ids: torch.Tensor, expert_offset: int = 0) -> torch.Tensor:
-    """``sum_k w_k * down_e(silu(gate_e x) * up_e x)`` over the experts held locally
+                topk_ids: torch.Tensor, expert_offset: int = 0, act: str = "silu") -> torch.Tensor:
+    """``sum_k w_k * down_e(act(gate_e x) * up_e x)`` over the experts held locally
     (``w13`` ``[E_local, 2I, H]``, ``w2`` ``[E_local, H, I]``); ids outside the local range
-    contribute nothing."""
+    contribute nothing. ``act``: ``silu`` or ``gelu_pytorch_tanh`` (Gemma-4 experts)."""
     t, h = x.shape
     out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
     e_local = w13.shape[0]
@@ -450,8 +455,9 @@ def moe_forward(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: to
         wt = (topk_w * sel).sum(-1)[rows]
         hcur = xf[rows] @ w13[e].float().t()
         gate, up = hcur.chunk(2, dim=-1)
-        act = (F.silu(gate) * up).to(x.dtype).float()
-        out[rows] += (act @ w2[e].float().t()) * wt[:, None]
+        g_act = F.silu(gate) if act == "silu" else F.gelu(gate, approximate="tanh")
+        hid = (g_act * up).to(x.dtype).float()
+        out[rows] += (hid @ w2[e].float().t()) * wt[:, None]
     return out.to(x.dtype)
 
 

@@ -182,6 +182,9 @@ class Batch:
     # rows of this step whose embedding is given (image placeholder tokens) and the vectors that replace it
     mm_rows: Optional[torch.Tensor] = None
     mm_values: Optional[torch.Tensor] = None
+    # a denoising step of a block-diffusion model with self-conditioning: the probability-weighted mean
+    # embedding each canvas row predicted one step earlier, ``[rows, hidden]`` (zeros on a block's first step)
+    canvas_signal: Optional[torch.Tensor] = None
     swa_out_loc: Optional[torch.Tensor] = None
     swa_block_table: Optional[torch.Tensor] = None
 

@@ -112,6 +112,11 @@ class Canvas:
         self.steps_taken = 0
         self.finished = False
         self.mean_entropy = float("nan")
+        # models with self-conditioning: the distribution every row predicted in the last step is kept for
+        # the caller (which turns it into the next step's signal and clears it)
+        self.keep_probs = False
+        self.probs: Optional[torch.Tensor] = None
+        self.signal: Optional[torch.Tensor] = None
         self._history: List[torch.Tensor] = []
         if cfg.kind == "entropy_bound":
             self.tokens = self._noise()
@@ -142,6 +147,8 @@ class Canvas:
         logp = scaled - scaled.logsumexp(-1, keepdim=True)
         p = torch.softmax(logp, -1)
         entropy = -(p * logp).sum(-1)
+        if self.keep_probs:
+            self.probs = p
         top = scaled.argmax(-1)
         drawn = torch.multinomial(p, 1, generator=self.generator).squeeze(-1)     # before the re-noise: draw order
         fresh = self._noise()
@@ -167,6 +174,8 @@ class Canvas:
             return
         t = cfg.temperature(self.steps_left)
         p = torch.softmax(logits, -1)
+        if self.keep_probs:
+            self.probs = p
         if t > 0:
             choice = torch.multinomial(torch.softmax(logits / t, -1), 1, generator=self.generator).squeeze(-1)
         else:

@@ -25,7 +25,10 @@ def _register_defaults() -> None:
             MODEL_REGISTRY.register(arch)(GemmaForCausalLM)
 
 
-    from .gemma4 import Gemma4ForCausalLM
+    from .gemma4 import DiffusionGemmaForBlockDiffusion, Gemma4ForCausalLM
+
+    if "DiffusionGemmaForBlockDiffusion" not in MODEL_REGISTRY:
+        MODEL_REGISTRY.register("DiffusionGemmaForBlockDiffusion")(DiffusionGemmaForBlockDiffusion)
 
     for arch in ("Gemma4ForCausalLM", "Gemma4ForConditionalGeneration"):
         if arch not in MODEL_REGISTRY:

@@ -243,7 +243,8 @@ class ModelConfig:
 
                 vision = VisionConfig.from_hf(cfg)
             inner = dict(cfg["text_config"])
-            for key in ("quantization_config", "architectures", "torch_dtype", "tie_word_embeddings"):
+            for key in ("quantization_config", "architectures", "torch_dtype", "tie_word_embeddings", "canvas_length",
+                        "mask_token_id"):
                 if key in cfg and key not in inner:
                     inner[key] = cfg[key]
             cfg = inner
@@ -294,7 +295,12 @@ class ModelConfig:
         local_theta = g("rope_local_base_freq")
         if local_theta is None and isinstance(rope_params.get("sliding_attention"), dict):
             local_theta = rope_params["sliding_attention"].get("rope_theta")
-        gemma4 = model_type in ("gemma4", "gemma4_text")
+        gemma4 = model_type in ("gemma4", "gemma4_text", "diffusion_gemma", "diffusion_gemma_text")
+        if model_type.startswith("diffusion_gemma") and "attention_k_eq_v" not in cfg:
+            # the block-diffusion variant's config does not carry the field; its global layers have no
+            # value projection all the same
+            cfg = dict(cfg, attention_k_eq_v=True)
+            g = cfg.get
         if isinstance(rope_params.get("full_attention"), dict):  # per-layer-type RoPE tables
             full = rope_params["full_attention"]
             theta = float(full.get("rope_theta", theta))
@@ -442,6 +448,8 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma3_text": ["Gemma3ForCausalLM"],
         "gemma4": ["Gemma4ForCausalLM"],
         "gemma4_text": ["Gemma4ForCausalLM"],
+        "diffusion_gemma": ["DiffusionGemmaForBlockDiffusion"],
+        "diffusion_gemma_text": ["DiffusionGemmaForBlockDiffusion"],
         "glm4_moe_lite": ["Glm4MoeLiteForCausalLM"],
         "glm4_moe": ["Glm4MoeForCausalLM"],
         "deepseek_v2": ["DeepseekV2ForCausalLM"],

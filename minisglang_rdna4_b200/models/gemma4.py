@@ -228,6 +228,7 @@ class Gemma4ForCausalLM(BaseOP):
             self._scales = (x.dtype, _rounded(float(cfg.hidden_size) ** 0.5, x.dtype),
                             _rounded(float(max(self._ple, 1)) ** 0.5, x.dtype))
         x = x * self._scales[1]
+        x = self._condition(x, ctx.batch)
         per_layer = None
         if self._ple:
             t, n = x.shape[0], cfg.num_layers
@@ -250,6 +251,9 @@ class Gemma4ForCausalLM(BaseOP):
             ctx.aux_hidden = [seen[i] for i in capture]
         return x
 
+    def _condition(self, x: torch.Tensor, batch) -> torch.Tensor:
+        return x
+
     def init_dummy(self, seed: int, std: float = 0.02, gen_device: str = "cpu") -> None:
         gen = torch.Generator(device=gen_device)
         gen.manual_seed(seed)
@@ -259,3 +263,59 @@ class Gemma4ForCausalLM(BaseOP):
             fn = getattr(mod, "init_dummy", None)
             if fn is not None:
                 fn(gen, std)
+
+
+class SelfConditioning(BaseOP):
+    """The block a denoising step puts between the embedding and the first layer
+    (python/minisgl/models/diffusion_gemma.py:68-100): a dense GeGLU MLP of the decoder's width over the
+    normalised signal of the previous step, added to the embedding; the sum is RMS-normalised without a
+    weight on every denoising step, the first one (signal zero: the MLP contributes exactly zero) included."""
+    _non_persistent = ("_unit",)
+
+    def __init__(self, cfg: ModelConfig, dtype, device) -> None:
+        prefix = "model.self_conditioning"
+        self.gate_up_proj = MergedColumnParallelLinear(cfg.hidden_size, [cfg.intermediate_size] * 2, dtype, device,
+                                                       _scheme(cfg, prefix + ".gate_up_proj"))
+        self.down_proj = RowParallelLinear(cfg.intermediate_size, cfg.hidden_size, dtype, device,
+                                           _scheme(cfg, prefix + ".down_proj"))
+        self.pre_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device)
+        self._act = GatedActivation(cfg.hidden_act)
+        self._eps = cfg.rms_norm_eps
+        self._unit = None
+
+    def forward(self, embeds: torch.Tensor, signal: Optional[torch.Tensor]) -> torch.Tensor:
+        if signal is not None:
+            h = self._act(self.gate_up_proj.forward(self.pre_norm.forward(signal.to(embeds.dtype))))
+            embeds = embeds + self.down_proj.forward(h, reduce=True)
+        if self._unit is None:
+            self._unit = _ones(embeds.shape[-1], embeds)
+        return ops.rms_norm(embeds, self._unit, self._eps)
+
+
+class DiffusionGemmaForBlockDiffusion(Gemma4ForCausalLM):
+    """Block diffusion on the Gemma-4 stack (python/minisgl/models/diffusion_gemma.py:103-250). The
+    checkpoint's encoder and decoder are one set of weights: the causal pass that writes K/V is the inherited
+    forward; a denoising step (``batch.canvas_signal`` set by the diffusion loop) differs only in the
+    self-conditioning block on its input and in the batch's attention mask."""
+
+    def __init__(self, cfg: ModelConfig, dtype: torch.dtype, device) -> None:
+        super().__init__(cfg, dtype, device)
+        self.model.self_conditioning = SelfConditioning(cfg, dtype, device)
+        self.self_conditioning_width = cfg.hidden_size
+
+    def _condition(self, x: torch.Tensor, batch) -> torch.Tensor:
+        signal = batch.canvas_signal
+        if signal is None:
+            return x
+        return self.model.self_conditioning.forward(x, signal if signal.numel() else None)
+
+    def soft_embedding(self, probs: torch.Tensor) -> torch.Tensor:
+        """What a canvas row carries into its next denoising step: its predicted distribution times the
+        embedding table, scaled like an embedding. ``probs`` ``[rows, vocab]`` fp32; each rank contracts
+        its slice of the vocabulary and the partial sums are added."""
+        emb = self.model.embed_tokens
+        w = emb.weight[: emb._len]
+        local = probs[:, emb._start: emb._start + emb._len].to(w.dtype) @ w
+        if emb._tp.size > 1:
+            local = get_comm().all_reduce(local)
+        return local * _rounded(float(self._cfg.hidden_size) ** 0.5, w.dtype)

@@ -158,6 +158,12 @@ def load_weights(model, path: str, cfg: ModelConfig, device, tensors: Optional[I
                 break
         if name.startswith("model.visual."):
             continue
+        # block-diffusion Gemma: encoder and decoder share every weight and the checkpoint keeps the decoder's
+        # names; the encoder side only has loose copies of the layer scalars
+        if name.startswith("model.encoder."):
+            continue
+        if name.startswith("model.decoder."):
+            name = "model." + name[len("model.decoder."):]
         # ---- Nemotron-H (Mamba-2 hybrid): backbone.* names, one "mixer" per layer
         if cfg.model_type == "nemotron_h":
             if name.startswith("backbone."):

@@ -216,7 +216,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     ``window`` > 0 additionally hides positions <= p - window. ``mask`` is an additive
     ``[T, >=max_kv]`` float bias (tree verification); when given it replaces the causal rule.
     With ``mask_window`` > 0 the mask is ``[T, mask_window]`` and covers only the last
-    ``mask_window`` KV positions of each request; earlier positions are visible to every row.
+    ``mask_window`` KV positions of each request; earlier positions are visible to every row
+    (of a sliding-window layer: to the rows that have them inside their window).
     """
     t, hq, d = q.shape
     hk, ps = k_cache.shape[1], k_cache.shape[2]
@@ -245,6 +246,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             w = min(mask_window, kv_len)
             full = torch.zeros(q_len, kv_len, dtype=torch.float32, device=q.device)
             full[:, kv_len - w:] = mask[qs:qe, mask_window - w:mask_window].float()
+            if window and window > 0 and kv_len > w:
+                early = (k_pos <= q_pos - window) & (k_pos < kv_len - w)
+                full = full.masked_fill(early, float("-inf"))
             s = s + full[None, None]
         elif mask is not None:
             s = s + mask[qs:qe, :kv_len].float()[None, None]

@@ -21,7 +21,9 @@ Prompts are admitted and chunked by the ordinary prefill manager (prefix-cache h
 final chunk is run without a sampled row. Denoising rows go through the engine's verification
 path: a zero additive mask over the last ``block`` K/V positions replaces the causal rule for
 those rows (``Batch.mask_window``), which is the attention form the tree-verification step uses.
-Models with sliding-window layers are refused: a mask replaces the window rule as well.
+Sliding-window layers take a second mask (the canvas whole, committed text inside the row's window); the
+window rule for positions the masks do not cover is applied by the tensor-op attention path only, so such
+models are refused on a GPU.
 """
 from __future__ import annotations
 
@@ -84,8 +86,14 @@ def make_canvas_manager(sched) -> Optional[CanvasManager]:
     mc = eng.model_config
     if not mc.canvas_length:
         return None
-    if mc.swa_layers or mc.is_recurrent:
-        raise ValueError("block-diffusion decoding needs a model whose layers all use full attention")
+    if mc.is_recurrent:
+        raise ValueError("block-diffusion decoding needs a model without recurrent layers")
+    if mc.swa_layers and (eng.device.type == "cuda" or eng.swa is not None):
+        # canvas rows of a sliding-window layer see the whole canvas and the text inside their window: a
+        # second mask plus the window rule for the positions the mask does not cover, which only the
+        # tensor-op attention path applies
+        raise ValueError("block-diffusion decoding with sliding-window layers runs on the CPU oracle path only "
+                         "(and without the sliding-window pool)")
     if sched.config.spec_algorithm != "none":
         raise ValueError("block-diffusion decoding and speculative decoding exclude each other")
     cfg = DenoiseConfig.from_model(sched.config.model_path, mc, getattr(sched.config, "diffusion_overrides", None))
@@ -135,17 +143,45 @@ def _denoise(sched, mgr: CanvasManager, reqs: List[Req]) -> None:
     total = plan.num_tokens
     # zero bias over the last `width` K/V positions of every request: its canvas (all of it, in both
     # directions) and, for a shorter last block, the committed text just ahead of it
-    mask = torch.zeros((total, width), dtype=torch.float32)
+    window = int(eng.model_config.sliding_window or 0) if eng.model_config.swa_layers else 0
+    span = width + window                          # K/V positions the masks cover
+    mask = torch.zeros((total, span), dtype=torch.float32)
+    mask_swa = None
+    cu = plan.cu_q.tolist()
+    if window:
+        # sliding-window layers: the canvas in both directions, committed text only inside the row's window
+        mask_swa = torch.zeros((total, span), dtype=torch.float32)
+        for i, (r, n) in enumerate(zip(reqs, lens)):
+            kv_len = r.device_len + n
+            k_pos = torch.arange(kv_len - span, kv_len)[None, :]
+            q_pos = torch.arange(r.device_len, kv_len)[:, None]
+            hidden = (k_pos < r.device_len) & (k_pos <= q_pos - window)
+            mask_swa[cu[i]:cu[i + 1]] = torch.where(hidden, float("-inf"), 0.0)
+    soft = getattr(eng.model, "soft_embedding", None)
     stream_ctx = torch.cuda.stream(eng.stream) if eng.stream is not None else _null()
     with stream_ctx:
         pool[idx.to(eng.device, non_blocking=True)] = tok.to(eng.device, non_blocking=True)
         batch.tree_mask = mask.to(eng.device)
-        batch.mask_window = width
+        batch.tree_mask_swa = mask_swa.to(eng.device) if mask_swa is not None else None
+        batch.mask_window = span
+        if soft is not None:
+            # rows of a block's first step carry a zero signal (the block contributes exactly nothing then)
+            states = [mgr.get(r.uid) for r in reqs]
+            if all(st.signal is None for st in states):
+                batch.canvas_signal = torch.empty((0,), device=eng.device)
+            else:
+                h = eng.model.self_conditioning_width
+                batch.canvas_signal = torch.cat([
+                    st.signal if st.signal is not None else torch.zeros((st.length, h), dtype=eng.dtype,
+                                                                        device=eng.device) for st in states])
         out = eng.forward_batch(batch, plan, BatchSamplingArgs(), return_logits=True)
         logits = eng.sampler.condition_logits(out.logits, BatchSamplingArgs())
-        cu = plan.cu_q.tolist()
         for i, r in enumerate(reqs):
-            mgr.get(r.uid).advance(logits[cu[i]:cu[i + 1]])
+            st = mgr.get(r.uid)
+            st.keep_probs = soft is not None
+            st.advance(logits[cu[i]:cu[i + 1]])
+            if soft is not None and st.probs is not None:
+                st.signal, st.probs = soft(st.probs), None
     sched.stats["steps"] += 1
     sched.stats["decode_tokens"] += total
     sched.stats["denoise_steps"] = sched.stats.get("denoise_steps", 0) + 1

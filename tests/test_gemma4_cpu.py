@@ -117,3 +117,121 @@ def test_gemma4_moe_tp2_matches_transformers():
             p.join(timeout=60)
             assert p.exitcode == 0
     assert got == want
+
+
+def _diffusion_gemma(tmp):
+    """A block-diffusion checkpoint in miniature: the Gemma-4 text weights under ``model.decoder.*``, loose layer
+    scalars on the encoder side, the self-conditioning block, ``canvas_length`` on the top-level config and no
+    ``attention_k_eq_v`` field although the global layers have no value projection."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+    from transformers import Gemma4ForCausalLM, Gemma4TextConfig
+
+    cfg = Gemma4TextConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_attention_heads=4, head_dim=16,
+                           global_head_dim=32, sliding_window=8, max_position_embeddings=512, eos_token_id=298,
+                           bos_token_id=None, pad_token_id=0, num_hidden_layers=3, num_key_value_heads=2,
+                           num_global_key_value_heads=1, attention_k_eq_v=True, enable_moe_block=True, num_experts=4,
+                           top_k_experts=2, moe_intermediate_size=16, hidden_size_per_layer_input=0,
+                           final_logit_softcapping=30.0,
+                           layer_types=["sliding_attention", "sliding_attention", "full_attention"])
+    torch.manual_seed(0)
+    hf = Gemma4ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+            elif "norm" in name or "scale" in name:
+                p.copy_(1.0 + torch.randn_like(p) * 0.1)
+    g = torch.Generator().manual_seed(5)
+    sc = {"gate_proj.weight": torch.randn(96, 64, generator=g) * 0.08, "up_proj.weight": torch.randn(96, 64, generator=g) * 0.08,
+          "down_proj.weight": torch.randn(64, 96, generator=g) * 0.08, "pre_norm.weight": 1.0 + torch.randn(64, generator=g) * 0.1}
+    tensors = {}
+    for name, t in hf.state_dict().items():
+        if name == "lm_head.weight":
+            continue
+        tensors["model.decoder." + name[len("model."):]] = t.detach().clone().contiguous()
+        if name.endswith("layer_scalar"):
+            tensors["model.encoder." + name[len("model."):]] = t.detach().clone()
+    for name, t in sc.items():
+        tensors["model.self_conditioning." + name] = t.contiguous()
+    save_file(tensors, os.path.join(tmp, "model.safetensors"))
+    text = {k: v for k, v in cfg.to_dict().items() if k != "attention_k_eq_v"}
+    text["model_type"] = "diffusion_gemma_text"
+    json.dump({"model_type": "diffusion_gemma", "architectures": ["DiffusionGemmaForBlockDiffusion"], "canvas_length": 5,
+               "mask_token_id": 299, "tie_word_embeddings": True, "text_config": text},
+              open(os.path.join(tmp, "config.json"), "w"))
+    json.dump({"max_denoising_steps": 3, "confidence_threshold": 0.6, "mask_token_id": 299,
+               "sampler_config": {"_cls_name": "MaskConfidenceSamplerConfig"}},
+              open(os.path.join(tmp, "generation_config.json"), "w"))
+    return hf, sc
+
+
+def _dense_self_conditioned_decode(hf, sc, prompt, cfg, max_tokens, window):
+    """Full-sequence forwards of the Hugging Face layers with explicit masks: committed text causal (inside
+    the window on sliding layers), canvas rows see the whole canvas and the text (inside their window on
+    sliding layers); the canvas embeddings go through the self-conditioning block with the previous step's
+    probability-weighted embedding."""
+    import torch.nn.functional as F
+
+    from minisglang_rdna4_b200.diffusion import Canvas
+
+    def unit_norm(x):
+        return x * torch.pow(x.pow(2).mean(-1, keepdim=True) + 1e-6, -0.5)
+
+    emb = hf.model.embed_tokens
+    ids, out = list(prompt), []
+    while len(out) < max_tokens:
+        n = min(cfg.block, max_tokens - len(out))
+        st = Canvas(cfg, n, "cpu", torch.Generator().manual_seed(0))
+        signal = None
+        while not st.finished:
+            c, t = len(ids), len(ids) + n
+            x = emb(torch.tensor([ids + st.tokens.tolist()]))[0]
+            canvas = x[c:]
+            if signal is not None:
+                s = unit_norm(signal) * sc["pre_norm.weight"]
+                mlp = F.gelu(s @ sc["gate_proj.weight"].t(), approximate="tanh") * (s @ sc["up_proj.weight"].t())
+                canvas = canvas + mlp @ sc["down_proj.weight"].t()
+            x = torch.cat([x[:c], unit_norm(canvas)])
+            q, k = torch.arange(t)[:, None], torch.arange(t)[None, :]
+            full = torch.where(k > q, float("-inf"), 0.0)
+            full[c:, :] = 0.0
+            sliding = torch.where((k > q) | (k <= q - window), float("-inf"), 0.0)
+            sliding[c:, c:] = 0.0
+            with torch.no_grad():
+                h = hf.model(inputs_embeds=x[None], attention_mask={"full_attention": full[None, None],
+                                                                    "sliding_attention": sliding[None, None]},
+                             use_cache=False).last_hidden_state
+                logits = torch.tanh(hf.lm_head(h[0, c:]) / 30.0) * 30.0
+            st.advance(logits.float())
+            signal = torch.softmax(logits.float(), -1) @ emb.weight * (64 ** 0.5)
+        for tok in st.emit.tolist():
+            out.append(tok)
+            ids.append(tok)
+            if len(out) >= max_tokens:
+                break
+    return out
+
+
+def test_diffusion_gemma_with_self_conditioning_equals_a_dense_restatement():
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf, sc = _diffusion_gemma(tmp)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(1, 290, (n,), generator=g).tolist() for n in (7, 33, 18)]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=24)
+        mc = llm.engine.model_config
+        assert type(llm.engine.model).__name__ == "DiffusionGemmaForBlockDiffusion"
+        assert mc.attention_k_eq_v and mc.canvas_length == 5 and llm.diffusion.cfg.kind == "mask_confidence"
+        cfg = llm.diffusion.cfg
+        budgets = (12, 10, 7)
+        outs = llm.generate(prompts, [SamplingParams(max_tokens=m, ignore_eos=True) for m in budgets])
+        got = [o.token_ids for o in outs]
+        llm.shutdown()
+    for p, m, have in zip(prompts, budgets, got):
+        assert have == _dense_self_conditioned_decode(hf, sc, p, cfg, m, window=8), (len(p), m)

@@ -44,6 +44,12 @@ def make_proposer(config, scheduler) -> Proposer:
 
         return NgramProposer(config.spec_num_draft, config.spec_ngram_max, config.spec_ngram_min,
                              tree_width=max(1, int(getattr(config, "spec_tree_width", 1) or 1)))
+    if algo in ("eagle3", "mtp"):
+        from .gemma4_assistant import Gemma4AssistantProposer, is_gemma4_assistant
+
+        if is_gemma4_assistant(getattr(config, "spec_draft_model_path", None)):
+            # a drafter that reads the target's K/V (Gemma-4 "assistant" checkpoints)
+            return Gemma4AssistantProposer(config, scheduler)
     if algo == "eagle3":
         from .eagle3 import Eagle3Proposer
 

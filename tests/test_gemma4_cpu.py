@@ -235,3 +235,136 @@ def test_diffusion_gemma_with_self_conditioning_equals_a_dense_restatement():
         llm.shutdown()
     for p, m, have in zip(prompts, budgets, got):
         assert have == _dense_self_conditioned_decode(hf, sc, p, cfg, m, window=8), (len(p), m)
+
+
+def _assistant_ckpt(tmp, layer_types=("sliding_attention", "full_attention")):
+    """A drafter checkpoint with random weights in the published naming."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    hid, inter, heads, d_s, d_g, backbone = 32, 48, 4, 16, 32, 64
+    g = torch.Generator().manual_seed(9)
+    rnd = lambda *shape: torch.randn(*shape, generator=g) * 0.15
+    w = {"pre_projection.weight": rnd(hid, 2 * backbone), "post_projection.weight": rnd(backbone, hid),
+         "model.norm.weight": 1.0 + rnd(hid), "model.embed_tokens.weight": rnd(300, hid)}
+    for i, kind in enumerate(layer_types):
+        d = d_s if kind == "sliding_attention" else d_g
+        p = f"model.layers.{i}."
+        for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            w[p + n + ".weight"] = 1.0 + rnd(hid)
+        w[p + "self_attn.q_norm.weight"] = 1.0 + rnd(d)
+        w[p + "self_attn.q_proj.weight"] = rnd(heads * d, hid)
+        w[p + "self_attn.o_proj.weight"] = rnd(hid, heads * d)
+        w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"] = rnd(inter, hid), rnd(inter, hid)
+        w[p + "mlp.down_proj.weight"] = rnd(hid, inter)
+        w[p + "layer_scalar"] = torch.rand(1, generator=g) * 0.5 + 0.75
+    os.makedirs(tmp, exist_ok=True)
+    save_file({k: v.contiguous() for k, v in w.items()}, os.path.join(tmp, "model.safetensors"))
+    json.dump({"model_type": "gemma4_assistant", "backbone_hidden_size": backbone,
+               "text_config": {"model_type": "gemma4_text", "hidden_size": hid, "intermediate_size": inter,
+                               "num_attention_heads": heads, "num_key_value_heads": 1, "head_dim": d_s,
+                               "global_head_dim": d_g, "num_hidden_layers": len(layer_types), "vocab_size": 300,
+                               "layer_types": list(layer_types), "rms_norm_eps": 1e-6, "sliding_window": 16,
+                               "hidden_size_per_layer_input": 0, "max_position_embeddings": 512,
+                               "tie_word_embeddings": True}}, open(os.path.join(tmp, "config.json"), "w"))
+    return w
+
+
+def _restate_draft_chain(hf, w, ids, k, window=16):
+    """The drafter's chain for a request whose first ``len(ids) - 1`` tokens have K/V in the target: queries
+    only, over the keys and values the Hugging Face target computes in its last layers that keep K/V."""
+    import torch.nn.functional as F
+
+    from transformers.models.gemma4.modeling_gemma4 import apply_rotary_pos_emb
+
+    rms = lambda x, wt=None: (x * torch.pow(x.pow(2).mean(-1, keepdim=True) + 1e-6, -0.5)) * (1.0 if wt is None else wt)
+    tcfg = hf.config
+    L = len(ids) - 1
+    with torch.no_grad():
+        # with a cache: without one the Hugging Face layers that share K/V compute their own
+        out = hf.model(torch.tensor([ids[:L]]), output_hidden_states=True, use_cache=True)
+        seed = out.last_hidden_state[0, L - 1]
+        pos = torch.arange(L)[None]
+        own = tcfg.num_hidden_layers - tcfg.num_kv_shared_layers
+        kv = {}
+        for kind in ("sliding_attention", "full_attention"):
+            li = max(i for i in range(own) if tcfg.layer_types[i] == kind)
+            layer = hf.model.layers[li]
+            att = layer.self_attn
+            h = layer.input_layernorm(out.hidden_states[li])
+            cos, sin = hf.model.rotary_emb(h, pos, kind)
+            kk = att.k_proj(h).view(1, L, -1, att.head_dim)
+            vv = att.v_proj(h).view(1, L, -1, att.head_dim) if att.v_proj is not None else kk
+            kv[kind] = (apply_rotary_pos_emb(att.k_norm(kk), cos, sin, unsqueeze_dim=2)[0], att.v_norm(vv)[0],
+                        (cos[0, L - 1], sin[0, L - 1]))
+        tok, drafts = ids[L], []
+        kinds = [t for t in ("sliding_attention", "full_attention")]
+        n_layers = sum(1 for name in w if name.endswith("self_attn.q_proj.weight"))
+        for _ in range(k):
+            e = hf.model.embed_tokens(torch.tensor([tok]))[0]
+            x = w["pre_projection.weight"] @ torch.cat([e, seed])
+            for i in range(n_layers):
+                p = f"model.layers.{i}."
+                d = w[p + "self_attn.q_norm.weight"].numel()
+                kind = "sliding_attention" if d == 16 else "full_attention"
+                keys, vals, (cos, sin) = kv[kind]
+                q = (w[p + "self_attn.q_proj.weight"] @ rms(x, w[p + "input_layernorm.weight"])).view(-1, d)
+                q = rms(q, w[p + "self_attn.q_norm.weight"])
+                q = q * cos + torch.cat([-q[:, d // 2:], q[:, : d // 2]], -1) * sin
+                lo = max(0, L - window) if kind == "sliding_attention" else 0
+                kh = keys[lo:, 0]                                   # one K/V head in the target
+                prob = torch.softmax(q @ kh.t(), -1)
+                a = w[p + "self_attn.o_proj.weight"] @ (prob @ vals[lo:, 0]).reshape(-1)
+                x = x + rms(a, w[p + "post_attention_layernorm.weight"])
+                hm = rms(x, w[p + "pre_feedforward_layernorm.weight"])
+                m = w[p + "mlp.down_proj.weight"] @ (F.gelu(w[p + "mlp.gate_proj.weight"] @ hm, approximate="tanh")
+                                                     * (w[p + "mlp.up_proj.weight"] @ hm))
+                x = (x + rms(m, w[p + "post_feedforward_layernorm.weight"])) * w[p + "layer_scalar"]
+            dn = rms(x, w["model.norm.weight"])
+            tok = int((w["model.embed_tokens.weight"] @ dn).argmax())
+            seed = w["post_projection.weight"] @ dn
+            drafts.append(tok)
+    return drafts
+
+
+def test_gemma4_assistant_drafter_reads_the_targets_kv():
+    """Speculative decoding with the query-only drafter: tokens equal the target's own greedy decoding
+    (verification decides), and the drafter's chains equal a restatement over the keys and values the Hugging
+    Face target computes, whether the drafted tokens were accepted or not."""
+    import os
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.spec.gemma4_assistant import Gemma4AssistantProposer
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _hf(tmp, "shared_kv_ple")
+        w = _assistant_ckpt(os.path.join(tmp, "assistant"))
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(1, 298, (n,), generator=g).tolist() for n in (6, 45)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=32, spec_algorithm="mtp", spec_num_draft=3,
+                  spec_draft_model_path=os.path.join(tmp, "assistant"))
+        prop = llm.proposer
+        assert isinstance(prop, Gemma4AssistantProposer)
+        seen = []
+        inner = prop.propose
+
+        def spy(reqs):
+            out = inner(reqs)
+            for r, d in zip(reqs, out):
+                if d:
+                    L = prop._len[r.uid]
+                    seen.append((r.input_ids[: L + 1].tolist(), list(d)))
+            return out
+
+        prop.propose = spy
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))]
+        llm.shutdown()
+    assert got == want
+    assert len(seen) >= 4
+    for ids, drafts in seen[:6]:
+        assert drafts == _restate_draft_chain(hf, w, ids, len(drafts)), len(ids)

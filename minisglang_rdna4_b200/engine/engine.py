@@ -185,7 +185,10 @@ class Engine:
         # vision tower of a multimodal checkpoint: replicated on every rank, runs once per image at admission
         self.vision = None
         if self.model_config.vision is not None:
-            from ..models.siglip import VisionTower
+            if getattr(self.model_config.vision, "kind", "") == "gemma4":
+                from ..models.gemma4_vision import Gemma4VisionTower as VisionTower
+            else:
+                from ..models.siglip import VisionTower
 
             self.vision = VisionTower(self.model_config.vision, self.dtype, self.device)
             if config.use_dummy_weight or not config.model_path or config.model_path in NAMED_CONFIGS:

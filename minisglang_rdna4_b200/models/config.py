@@ -112,6 +112,8 @@ class ModelConfig:
     mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
     canvas_length: int = 0                    # block-diffusion models: tokens written per block
     vision: Any = None                        # models.siglip.VisionConfig of a multimodal checkpoint
+    image_bidirectional: bool = True          # the tokens of one image see each other in both directions in the prefill
+    pad_token_id: int = 0
     mask_token_id: Optional[int] = None       # absorbing-state diffusion models
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
@@ -242,6 +244,10 @@ class ModelConfig:
                 from .siglip import VisionConfig
 
                 vision = VisionConfig.from_hf(cfg)
+            elif str(cfg.get("model_type", "")) in ("gemma4", "diffusion_gemma") and cfg.get("vision_config"):
+                from .gemma4_vision import Gemma4VisionConfig
+
+                vision = Gemma4VisionConfig.from_hf(cfg)
             inner = dict(cfg["text_config"])
             for key in ("quantization_config", "architectures", "torch_dtype", "tie_word_embeddings", "canvas_length",
                         "mask_token_id"):
@@ -423,6 +429,8 @@ class ModelConfig:
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             canvas_length=int(g("canvas_length") or g("block_length") or 0),
             vision=vision,
+            image_bidirectional=(g("use_bidirectional_attention") == "vision") if gemma4 else True,
+            pad_token_id=int(g("pad_token_id") or 0),
             mask_token_id=g("mask_token_id"),
             eos_token_ids=eos_ids,
             bos_token_id=g("bos_token_id"),

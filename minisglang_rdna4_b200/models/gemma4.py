@@ -228,14 +228,18 @@ class Gemma4ForCausalLM(BaseOP):
             self._scales = (x.dtype, _rounded(float(cfg.hidden_size) ** 0.5, x.dtype),
                             _rounded(float(max(self._ple, 1)) ** 0.5, x.dtype))
         x = x * self._scales[1]
+        if ctx.batch.mm_rows is not None:
+            # image placeholder rows take the projected vision features as they are (not scaled)
+            x = x.index_copy(0, ctx.batch.mm_rows, ctx.batch.mm_values.to(x.dtype))
         x = self._condition(x, ctx.batch)
         per_layer = None
         if self._ple:
             t, n = x.shape[0], cfg.num_layers
             ids = input_ids
             limit = cfg.vocab_size_per_layer_input or cfg.vocab_size
-            if limit < cfg.vocab_size:          # ids the second table does not have (soft tokens) read row 0
-                ids = torch.where(ids < limit, ids, torch.zeros_like(ids))
+            # image placeholder rows (ids past the vocabulary) and ids the second table does not have read the
+            # padding token's row, as the published model does for soft tokens
+            ids = torch.where(ids < min(limit, cfg.vocab_size), ids, torch.full_like(ids, cfg.pad_token_id))
             tok = body.embed_tokens_per_layer.forward(ids) * self._scales[2]
             proj = body.per_layer_model_projection.forward(x) * (float(cfg.hidden_size) ** -0.5)
             proj = body.per_layer_projection_norm.forward(proj.reshape(t * n, self._ple)).view(t, n, self._ple)

@@ -234,7 +234,7 @@ class Scheduler:
         if rows:
             batch.mm_rows = torch.as_tensor(np.concatenate(rows), dtype=torch.int64).to(self.engine.device)
             batch.mm_values = torch.cat(vals)
-            if ENV.IMAGE_BIDIRECTIONAL.value:
+            if ENV.IMAGE_BIDIRECTIONAL.value and self.engine.model_config.image_bidirectional:
                 self._image_masks(batch, plan)
 
     def _image_masks(self, batch: Batch, plan: StepPlan) -> None:

@@ -368,3 +368,58 @@ def test_gemma4_assistant_drafter_reads_the_targets_kv():
     assert len(seen) >= 4
     for ids, drafts in seen[:6]:
         assert drafts == _restate_draft_chain(hf, w, ids, len(drafts)), len(ids)
+
+
+@pytest.mark.parametrize("bidirectional", [False, True])
+def test_gemma4_image_input_matches_transformers(bidirectional):
+    """A multimodal Gemma-4 checkpoint in miniature (vision tower with the two-dimensional rotary embedding and
+    k x k pooling, projector, text decoder with per-layer inputs): image features equal the Hugging Face
+    tower's, and greedy generation over a prompt with an image equals Hugging Face's with the same patches.
+    ``bidirectional``: the larger models let the tokens of one image see each other in both directions."""
+    from transformers import Gemma4Config, Gemma4ForConditionalGeneration
+    from transformers.models.gemma4.image_processing_gemma4 import convert_image_to_patches
+
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    text = dict(vocab_size=300, hidden_size=64, intermediate_size=96, num_attention_heads=4, head_dim=16,
+                global_head_dim=32, sliding_window=16, max_position_embeddings=512, eos_token_id=299, bos_token_id=None,
+                pad_token_id=0, use_bidirectional_attention="vision" if bidirectional else None, **_KINDS["shared_kv_ple"])
+    vision = dict(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                  num_key_value_heads=2, head_dim=16, patch_size=4, pooling_kernel_size=2, position_embedding_size=64)
+    cfg = Gemma4Config(text_config=text, vision_config=vision, audio_config=None, image_token_id=290, boi_token_id=291,
+                       eoi_token_id=292, vision_soft_tokens_per_image=9)
+    torch.manual_seed(0)
+    hf = Gemma4ForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+            elif "norm" in name or "scale" in name:
+                p.copy_(1.0 + torch.randn_like(p) * 0.1)
+    g = torch.Generator().manual_seed(6)
+    side = 3 * 2 * 4                                            # 3 soft tokens per side x pooling 2 x patch 4
+    image = torch.randint(0, 256, (3, side, side), generator=g, dtype=torch.uint8)
+    patches = convert_image_to_patches(image.float() / 255.0, 4)[None]
+    grid = side // 4
+    pos = torch.stack(torch.meshgrid(torch.arange(grid), torch.arange(grid), indexing="xy"), -1).reshape(1, -1, 2)
+    head = torch.randint(1, 280, (7,), generator=g).tolist()
+    tail = torch.randint(1, 280, (12,), generator=g).tolist()
+    ids = head + [291] + [290] * 9 + [292] + tail
+    kinds = torch.tensor([[1 if t == 290 else 0 for t in ids]])
+    with torch.no_grad():
+        want_feats = hf.model.get_image_features(patches, pos).pooler_output
+        want = hf.generate(torch.tensor([ids]), pixel_values=patches, image_position_ids=pos, mm_token_type_ids=kinds,
+                           max_new_tokens=8, do_sample=False)[0, len(ids):].tolist()
+    with tempfile.TemporaryDirectory() as tmp:
+        hf.save_pretrained(tmp, safe_serialization=True)
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=64)
+        eng = llm.engine
+        assert eng.vision is not None and eng.vision.cfg.tokens_per_image == 9 and eng.vision.cfg.image_size == side
+        assert eng.model_config.image_bidirectional == bidirectional
+        feats = eng.vision.image_embeddings((image[None].float() / 255.0 - 0.5) / 0.5)
+        torch.testing.assert_close(feats, want_feats.reshape(-1, 64), rtol=2e-4, atol=2e-4)
+        out = llm.generate([head + [291] + tail], SamplingParams(max_tokens=8, ignore_eos=True), images=[[image]])[0]
+        llm.shutdown()
+    assert out.token_ids == want

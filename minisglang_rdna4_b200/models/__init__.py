@@ -34,6 +34,11 @@ def _register_defaults() -> None:
         if arch not in MODEL_REGISTRY:
             MODEL_REGISTRY.register(arch)(Gemma4ForCausalLM)
 
+    from .muse_glimmer import MuseGlimmerForConditionalGeneration
+
+    if "MuseGlimmerForConditionalGeneration" not in MODEL_REGISTRY:
+        MODEL_REGISTRY.register("MuseGlimmerForConditionalGeneration")(MuseGlimmerForConditionalGeneration)
+
     from .qwen3_5 import Qwen3_5ForCausalLM
 
     for arch in ("Qwen3_5ForCausalLM", "Qwen3_5ForConditionalGeneration", "Qwen3_5MoeForCausalLM",

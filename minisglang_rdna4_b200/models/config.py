@@ -112,6 +112,12 @@ class ModelConfig:
     mtp_num_hidden_layers: int = 0            # Qwen3.5 / Qwen3-Next: decoder layers stored under mtp.*
     canvas_length: int = 0                    # block-diffusion models: tokens written per block
     vision: Any = None                        # models.siglip.VisionConfig of a multimodal checkpoint
+    # Muse-Glimmer: the two post-norms of a layer have an epsilon of their own, layers whose rotary base is 0
+    # have no positional encoding, logits are multiplied before the soft cap, queries are scaled after their norm
+    post_norm_eps: Optional[float] = None
+    layer_rope_theta: Optional[Tuple[float, ...]] = None
+    output_multiplier: Optional[float] = None
+    qk_scale_factor: Optional[float] = None
     image_bidirectional: bool = True          # the tokens of one image see each other in both directions in the prefill
     pad_token_id: int = 0
     mask_token_id: Optional[int] = None       # absorbing-state diffusion models
@@ -301,6 +307,10 @@ class ModelConfig:
         local_theta = g("rope_local_base_freq")
         if local_theta is None and isinstance(rope_params.get("sliding_attention"), dict):
             local_theta = rope_params["sliding_attention"].get("rope_theta")
+        muse = model_type in ("muse_glimmer", "muse_glimmer_text")
+        if muse:
+            cfg = dict(cfg, hidden_act=g("hidden_act") or g("hidden_activation") or "silu")
+            g = cfg.get
         gemma4 = model_type in ("gemma4", "gemma4_text", "diffusion_gemma", "diffusion_gemma_text")
         if model_type.startswith("diffusion_gemma") and "attention_k_eq_v" not in cfg:
             # the block-diffusion variant's config does not carry the field; its global layers have no
@@ -429,6 +439,10 @@ class ModelConfig:
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             canvas_length=int(g("canvas_length") or g("block_length") or 0),
             vision=vision,
+            post_norm_eps=g("post_norm_eps") if muse else None,
+            layer_rope_theta=tuple(float(x) for x in g("layer_rope_theta")) if muse and g("layer_rope_theta") else None,
+            output_multiplier=g("output_multiplier") if muse else None,
+            qk_scale_factor=float(g("qk_scale_factor") or 3.87) if muse else None,
             image_bidirectional=(g("use_bidirectional_attention") == "vision") if gemma4 else True,
             pad_token_id=int(g("pad_token_id") or 0),
             mask_token_id=g("mask_token_id"),
@@ -456,6 +470,8 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma3_text": ["Gemma3ForCausalLM"],
         "gemma4": ["Gemma4ForCausalLM"],
         "gemma4_text": ["Gemma4ForCausalLM"],
+        "muse_glimmer": ["MuseGlimmerForConditionalGeneration"],
+        "muse_glimmer_text": ["MuseGlimmerForConditionalGeneration"],
         "diffusion_gemma": ["DiffusionGemmaForBlockDiffusion"],
         "diffusion_gemma_text": ["DiffusionGemmaForBlockDiffusion"],
         "glm4_moe_lite": ["Glm4MoeLiteForCausalLM"],

@@ -34,6 +34,10 @@ def _register_defaults() -> None:
         if arch not in MODEL_REGISTRY:
             MODEL_REGISTRY.register(arch)(Gemma4ForCausalLM)
 
+    from .laguna import LagunaForCausalLM
+
+    if "LagunaForCausalLM" not in MODEL_REGISTRY:
+        MODEL_REGISTRY.register("LagunaForCausalLM")(LagunaForCausalLM)
     from .muse_glimmer import MuseGlimmerForConditionalGeneration
 
     if "MuseGlimmerForConditionalGeneration" not in MODEL_REGISTRY:

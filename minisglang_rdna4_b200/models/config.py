@@ -114,6 +114,9 @@ class ModelConfig:
     vision: Any = None                        # models.siglip.VisionConfig of a multimodal checkpoint
     # Muse-Glimmer: the two post-norms of a layer have an epsilon of their own, layers whose rotary base is 0
     # have no positional encoding, logits are multiplied before the soft cap, queries are scaled after their norm
+    # Laguna: a query-head count per layer and a rotary table of their own for the sliding layers
+    attn_head_counts: Optional[Tuple[int, ...]] = None
+    sliding_rotary: Optional[RotaryConfig] = None
     post_norm_eps: Optional[float] = None
     layer_rope_theta: Optional[Tuple[float, ...]] = None
     output_multiplier: Optional[float] = None
@@ -304,6 +307,7 @@ class ModelConfig:
         if layer_types is None and model_type == "gemma2":
             layer_types = ["sliding_attention" if i % 2 == 0 else "full_attention"
                            for i in range(int(g("num_hidden_layers")))]
+        sliding_rotary = None
         local_theta = g("rope_local_base_freq")
         if local_theta is None and isinstance(rope_params.get("sliding_attention"), dict):
             local_theta = rope_params["sliding_attention"].get("rope_theta")
@@ -324,8 +328,19 @@ class ModelConfig:
             if scaling and scaling.get("rope_type", "default") in ("default", None):
                 scaling = None
             g_dim = int(g("global_head_dim") or head_dim) if gemma4 else head_dim
+            if full.get("partial_rotary_factor") and not gemma4:
+                rope_dim = int(head_dim * float(full["partial_rotary_factor"]))
             rotary = RotaryConfig(head_dim=g_dim, rotary_dim=g_dim if gemma4 else rope_dim, max_position=max_pos,
                                   base=theta, scaling=scaling)
+            sub = rope_params.get("sliding_attention")
+            if isinstance(sub, dict) and model_type == "laguna":
+                sub_scaling = {k: v for k, v in sub.items() if k != "rope_theta"} or None
+                if sub_scaling and sub_scaling.get("rope_type", "default") in ("default", None):
+                    sub_scaling = None
+                sliding_rotary = RotaryConfig(head_dim=head_dim,
+                                              rotary_dim=int(head_dim * float(sub.get("partial_rotary_factor") or 1.0)),
+                                              max_position=max_pos, base=float(sub.get("rope_theta", theta)),
+                                              scaling=sub_scaling)
         if gemma4:
             if layer_types is None:
                 layer_types = ["sliding_attention" if (i + 1) % 6 else "full_attention"
@@ -396,7 +411,7 @@ class ModelConfig:
             first_k_dense_replace=int(g("first_k_dense_replace") or 0),
             n_shared_experts=int(g("n_shared_experts") or 0),
             routed_scaling_factor=float(g("routed_scaling_factor") or 1.0),
-            scoring_func=g("scoring_func", "sigmoid" if model_type in ("glm4_moe_lite", "glm4_moe", "deepseek_v3")
+            scoring_func=g("scoring_func", "sigmoid" if model_type in ("glm4_moe_lite", "glm4_moe", "deepseek_v3", "laguna")
                            else "softmax"),
             # DeepSeek-V2's plain "greedy" top-k ignores the routing groups its config still lists
             n_group=1 if g("topk_method") == "greedy" else int(g("n_group") or 1),
@@ -439,6 +454,8 @@ class ModelConfig:
             mtp_num_hidden_layers=int(g("mtp_num_hidden_layers") or 0),
             canvas_length=int(g("canvas_length") or g("block_length") or 0),
             vision=vision,
+            attn_head_counts=tuple(int(h) for h in g("num_attention_heads_per_layer")) if g("num_attention_heads_per_layer") else None,
+            sliding_rotary=sliding_rotary,
             post_norm_eps=g("post_norm_eps") if muse else None,
             layer_rope_theta=tuple(float(x) for x in g("layer_rope_theta")) if muse and g("layer_rope_theta") else None,
             output_multiplier=g("output_multiplier") if muse else None,
@@ -470,6 +487,7 @@ def _default_arch(model_type: str) -> List[str]:
         "gemma3_text": ["Gemma3ForCausalLM"],
         "gemma4": ["Gemma4ForCausalLM"],
         "gemma4_text": ["Gemma4ForCausalLM"],
+        "laguna": ["LagunaForCausalLM"],
         "muse_glimmer": ["MuseGlimmerForConditionalGeneration"],
         "muse_glimmer_text": ["MuseGlimmerForConditionalGeneration"],
         "diffusion_gemma": ["DiffusionGemmaForBlockDiffusion"],

@@ -2,6 +2,8 @@
 plane with per-namespace bearer tokens."""
 import json
 
+import pytest
+
 from fastapi import FastAPI
 from fastapi.testclient import TestClient
 
@@ -91,3 +93,34 @@ def test_ambient_read_and_write_hooks_on_the_completion_endpoints(monkeypatch, t
     monkeypatch.setenv("MSGL_CAM_AUTO", "1")
     c.post("/generate", json={"prompt": "Tell me about Zephyrina's mother tongue", "max_tokens": 4})
     assert "Klingon" in mgr.sent[-1].text and mgr.sent[-1].text.endswith("Tell me about Zephyrina's mother tongue")
+
+
+def test_client_against_the_rest_plane(monkeypatch):
+    """The client's calls, headers and error mapping against the mounted router (an in-process transport
+    stands in for the socket)."""
+    from minisglang_rdna4_b200.cam import CamClient, CamError
+
+    monkeypatch.setenv("MSGL_CAM_TOKENS", json.dumps({"tok-a": "alpha", "tok-admin": "*"}))
+    app = FastAPI()
+    app.include_router(make_cam_router(CamMemory()))
+    http = TestClient(app)
+
+    def transport(method, path, headers, body):
+        r = http.request(method, path, headers=headers, json=body)
+        return r.status_code, r.json()
+
+    alpha = CamClient(token="tok-a", namespace="alpha", transport=transport)
+    assert alpha.remember("Kite", "teal", prompt="colour") == {"stored": True, "replaced": False}
+    assert alpha.ask("what colour is the Kite?")["text"] == "teal"
+    assert alpha.facts() == [{"subject": "Kite", "prompt": "colour", "object": "teal"}]
+    with pytest.raises(CamError) as err:
+        alpha.namespace("beta").facts()
+    assert err.value.status == 403
+    with pytest.raises(CamError) as err:
+        CamClient(namespace="alpha", transport=transport).facts()
+    assert err.value.status == 401
+    admin = CamClient(token="tok-admin", namespace="beta", transport=transport)
+    admin.remember("Moss bank", "green")
+    assert admin.namespaces() == ["alpha", "beta"] and alpha.namespaces() == ["alpha"]
+    assert admin.forget("Moss bank") is True and admin.facts() == []
+    assert admin.undo().startswith("undid forget") and len(admin.facts()) == 1

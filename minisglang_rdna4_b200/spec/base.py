@@ -50,6 +50,12 @@ def make_proposer(config, scheduler) -> Proposer:
         if is_gemma4_assistant(getattr(config, "spec_draft_model_path", None)):
             # a drafter that reads the target's K/V (Gemma-4 "assistant" checkpoints)
             return Gemma4AssistantProposer(config, scheduler)
+    if algo in ("eagle3", "mtp", "dflash"):
+        from .dflash import DFlashProposer, is_dflash
+
+        if algo == "dflash" or is_dflash(getattr(config, "spec_draft_model_path", None)):
+            # a block-diffusion drafter: one forward proposes the whole chain
+            return DFlashProposer(config, scheduler)
     if algo == "eagle3":
         from .eagle3 import Eagle3Proposer
 

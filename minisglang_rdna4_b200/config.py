@@ -40,7 +40,7 @@ class EngineConfig:
     device: str = "auto"                     # auto | cuda | cpu
     seed: int = 0
     # speculative decode
-    spec_algorithm: str = "none"             # none | ngram | eagle3 | mtp | dflash
+    spec_algorithm: str = "none"             # none | ngram | eagle3 | mtp | dflash | tidar
     spec_draft_model_path: Optional[str] = None
     spec_num_draft: int = 4
     spec_ngram_max: int = 3

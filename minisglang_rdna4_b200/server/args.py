@@ -51,7 +51,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--chat-template", default=None)
     p.add_argument("--chat-template-kwargs", default=None, help="JSON object merged into every template call")
     p.add_argument("--reasoning-parser", default="auto")
-    p.add_argument("--spec-algorithm", default="none", choices=["none", "ngram", "mtp", "eagle3", "dflash"])
+    p.add_argument("--spec-algorithm", default="none", choices=["none", "ngram", "mtp", "eagle3", "dflash", "tidar"])
     p.add_argument("--spec-draft-model-path", "--spec-draft-model", dest="spec_draft_model_path", default=None)
     p.add_argument("--spec-num-draft", type=int, default=4)
     p.add_argument("--spec-ngram-max", type=int, default=3)

@@ -56,6 +56,10 @@ def make_proposer(config, scheduler) -> Proposer:
         if algo == "dflash" or is_dflash(getattr(config, "spec_draft_model_path", None)):
             # a block-diffusion drafter: one forward proposes the whole chain
             return DFlashProposer(config, scheduler)
+    if algo == "tidar":
+        from .tidar import TiDARProposer
+
+        return TiDARProposer(config, scheduler)
     if algo == "eagle3":
         from .eagle3 import Eagle3Proposer
 

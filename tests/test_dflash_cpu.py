@@ -123,3 +123,46 @@ def test_dflash_block_drafter():
     assert len(seen) >= 4
     for ids, drafts in seen[:6]:
         assert drafts == _restate(hf, w, ids, len(drafts)), len(ids)
+
+
+def test_tidar_self_drafting():
+    """The target drafts for itself: one causal forward over [confirmed token, mask x k]; the arg-max at the
+    mask rows are the drafts. Output equals plain greedy decoding; the drafts equal a Hugging Face forward over
+    the same rows; the drafting forward leaves lengths and page accounting untouched."""
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+    from minisglang_rdna4_b200.spec.tidar import TiDARProposer
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _target(tmp)
+        json.dump({"mask_token_id": MASK, "block_size": 3}, open(os.path.join(tmp, "tidar_config.json"), "w"))
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(0, 190, (n,), generator=g).tolist() for n in (6, 41)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=9, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=16, spec_algorithm="tidar", spec_num_draft=4)
+        prop = llm.proposer
+        assert isinstance(prop, TiDARProposer) and prop.block == 3 and prop.mask_token_id == MASK
+        seen = []
+        inner = prop.propose
+
+        def spy(reqs):
+            before = [(r.cached_len, r.device_len) for r in reqs]
+            out = inner(reqs)
+            assert before == [(r.cached_len, r.device_len) for r in reqs]
+            for r, d in zip(reqs, out):
+                if d:
+                    seen.append((r.input_ids[: r.device_len].tolist(), list(d)))
+            return out
+
+        prop.propose = spy
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=9, ignore_eos=True))]
+        llm.cache.check_integrity()
+        llm.shutdown()
+    assert got == want
+    assert len(seen) >= 4 and max(len(d) for _, d in seen) == 3
+    for ids, drafts in seen[:6]:
+        k = len(drafts)
+        with torch.no_grad():
+            logits = hf(torch.tensor([ids + [MASK] * k])).logits[0]
+        assert drafts == logits[len(ids):len(ids) + k].argmax(-1).tolist(), len(ids)

@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -37,7 +37,8 @@ class TiDARProposer(Proposer):
 
     def __init__(self, config, scheduler) -> None:
         super().__init__(config.spec_num_draft)
-        self.tree_width = 1
+        # > 1: a draft tree from the top tokens of every position instead of the arg-max chain
+        self.tree_width = max(1, int(getattr(config, "spec_tree_width", 1) or 1))
         self.sched, self.engine = scheduler, scheduler.engine
         raw = tidar_config(getattr(config, "spec_draft_model_path", None), config.model_path)
         mask = raw.get("mask_token_id", self.engine.model_config.mask_token_id)
@@ -50,10 +51,30 @@ class TiDARProposer(Proposer):
                                       "sliding-window pool")
 
     def propose(self, reqs: Sequence[Req]) -> List[List[int]]:
+        return [lp.argmax(-1).tolist() if lp is not None else [] for lp in self._block_logits(reqs)]
+
+    def propose_paths(self, reqs: Sequence[Req]) -> List[List[List[int]]]:
+        """Per request the most probable prefixes under the per-position distributions of the drafting
+        forward (``spec/ddtree.py``), best first: ``num_draft x tree_width`` tree nodes from the top
+        ``tree_width`` tokens of every position."""
+        from .ddtree import build_draft_paths
+
+        out = []
+        for lp in self._block_logits(reqs):
+            if lp is None:
+                out.append([])
+                continue
+            val, idx = torch.log_softmax(lp, -1).topk(min(self.tree_width, lp.shape[-1]), -1)
+            out.append(build_draft_paths(val.tolist(), idx.tolist(), self.num_draft * self.tree_width))
+        return out
+
+    def _block_logits(self, reqs: Sequence[Req]) -> List[Optional[torch.Tensor]]:
+        """One drafting forward; per request the fp32 logits ``[k_i, vocab]`` of its mask rows (``None`` for a
+        request with no budget)."""
         from ..engine import BatchSamplingArgs
         from ..scheduler.spec_step import _engine_stream
 
-        out: List[List[int]] = [[] for _ in reqs]
+        out: List[Optional[torch.Tensor]] = [None for _ in reqs]
         rows = [i for i, r in enumerate(reqs) if min(self.budget(r), self.block) > 0]
         if not rows:
             return out
@@ -74,10 +95,10 @@ class TiDARProposer(Proposer):
             eng.token_pool.view(-1)[idx.to(eng.device)] = self.mask_token_id
             res = eng.forward_batch(batch, plan, BatchSamplingArgs(), return_logits=True)
             logits = eng.sampler.condition_logits(res.logits, BatchSamplingArgs())
-            preds = logits.float().argmax(-1).cpu()
+            logits = logits.float().cpu()
         cu = plan.cu_q.tolist()
         for j, i in enumerate(rows):
             first = cu[j + 1] - k                  # the mask rows are the last k of the request
-            out[i] = preds[first:first + min(self.budget(reqs[i]), self.block, k)].tolist()
+            out[i] = logits[first:first + min(self.budget(reqs[i]), self.block, k)]
         sched.stats["steps"] += 1
         return out

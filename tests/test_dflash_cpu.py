@@ -166,3 +166,46 @@ def test_tidar_self_drafting():
         with torch.no_grad():
             logits = hf(torch.tensor([ids + [MASK] * k])).logits[0]
         assert drafts == logits[len(ids):len(ids) + k].argmax(-1).tolist(), len(ids)
+
+
+def test_draft_tree_keeps_the_most_probable_prefixes():
+    """Best-first enumeration against brute force: the kept prefixes are the highest-scoring ones under the
+    product of the per-position distributions, each after its parent."""
+    import itertools
+
+    from minisglang_rdna4_b200.spec.ddtree import build_draft_paths
+
+    g = torch.Generator().manual_seed(0)
+    logp = torch.log_softmax(torch.randn(4, 3, generator=g) * 2, -1).sort(-1, descending=True).values
+    ids = torch.arange(12).view(4, 3) + 100
+    every = []
+    for d in range(1, 5):
+        for ranks in itertools.product(range(3), repeat=d):
+            every.append((sum(float(logp[i, r]) for i, r in enumerate(ranks)), [int(ids[i, r]) for i, r in enumerate(ranks)]))
+    every.sort(key=lambda t: -t[0])
+    for budget in (1, 5, 17):
+        got = build_draft_paths(logp.tolist(), ids.tolist(), budget)
+        assert len(got) == budget and sorted(map(tuple, got)) == sorted(tuple(p) for _, p in every[:budget])
+        for i, p in enumerate(got):
+            assert len(p) == 1 or p[:-1] in got[:i]
+    assert build_draft_paths([], [], 4) == [] and build_draft_paths(logp.tolist(), ids.tolist(), 0) == []
+
+
+def test_tidar_with_a_draft_tree():
+    from minisglang_rdna4_b200 import SamplingParams
+    from minisglang_rdna4_b200.llm import LLM
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _target(tmp)
+        json.dump({"mask_token_id": MASK, "block_size": 3}, open(os.path.join(tmp, "tidar_config.json"), "w"))
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(0, 190, (n,), generator=g).tolist() for n in (6, 41)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=9, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        llm = LLM(model_path=tmp, device="cpu", dtype="fp32", page_size=16, max_running_req=4, num_page_override=64,
+                  max_extend_tokens=16, spec_algorithm="tidar", spec_num_draft=3, spec_tree_width=2)
+        assert llm.proposer.tree_width == 2
+        got = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_tokens=9, ignore_eos=True))]
+        assert llm.stats["spec_drafted"] > 0
+        llm.cache.check_integrity()
+        llm.shutdown()
+    assert got == want

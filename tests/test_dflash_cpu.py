@@ -209,3 +209,34 @@ def test_tidar_with_a_draft_tree():
         llm.cache.check_integrity()
         llm.shutdown()
     assert got == want
+
+
+@pytest.mark.parametrize("algo", ["dflash", "tidar"])
+def test_block_drafters_on_two_tensor_parallel_ranks(algo):
+    """Both ranks run the (replicated) drafter or the self-drafting forward and reach the same drafts; tokens
+    equal the target's greedy decoding."""
+    import multiprocessing as mp
+
+    from test_tp_cpu import _worker
+
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _target(tmp)
+        json.dump({"mask_token_id": MASK, "block_size": 3}, open(os.path.join(tmp, "tidar_config.json"), "w"))
+        _drafter(os.path.join(tmp, "drafter"))
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 190, (n,), generator=g).tolist() for n in (7, 30)]
+        want = [hf.generate(torch.tensor([p]), max_new_tokens=6, do_sample=False)[0, len(p):].tolist() for p in prompts]
+        extra = {"spec_algorithm": algo, "spec_num_draft": 3}
+        if algo == "dflash":
+            extra["spec_draft_model_path"] = os.path.join(tmp, "drafter")
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = 19100 + (os.getpid() % 1500) + (5 if algo == "tidar" else 0)
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, tmp, prompts, q, False, extra)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = q.get(timeout=240)
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    assert got == want

@@ -156,6 +156,7 @@ ENV.flag("STATE_DIGEST", False, "log exact per-layer digests of the K/V and recu
 ENV.str("BAKED_DIR", "", "directory of baked checkpoints: a rank's weights as they stand after loading, streamed back on later "
         "boots instead of parsing, slicing and merging the checkpoint again (written on the first boot)")
 ENV.flag("BAKED_VERIFY", False, "check every baked tensor's checksum while loading")
+ENV.flag("HUB_OFFLINE", False, "a model path that names a hub repository is looked up in the local hub cache only (no download)")
 ENV.flag("MLA_LATENT", False, "latent-attention models keep the compressed latent and the shared rotary key per token instead of "
          "per-head keys and values (absorbed attention through tensor ops, eager steps only: a capacity mode, not a fast one)")
 ENV.flag("SWA_POOL", False, "sliding-window layers keep their K/V in a pool of their own whose pages are handed back as they "

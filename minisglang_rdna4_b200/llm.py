@@ -32,6 +32,11 @@ class RequestOutput:
 
 class LLM(Scheduler):
     def __init__(self, model_path: str = "", **kwargs: Any) -> None:
+        from .utils.hub import resolve_model_path
+
+        model_path = resolve_model_path(model_path) or ""
+        if kwargs.get("spec_draft_model_path"):
+            kwargs["spec_draft_model_path"] = resolve_model_path(kwargs["spec_draft_model_path"])
         config = kwargs.pop("config", None)
         if config is None:
             config = SchedulerConfig(model_path=model_path, offline_mode=True, **kwargs)

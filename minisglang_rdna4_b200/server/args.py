@@ -103,6 +103,10 @@ def parse_args(argv: Optional[List[str]] = None) -> ServerArgs:
                              (ns.tp_overlap, "MSGL_TP_OVERLAP", "1"), (ns.mla_latent, "MSGL_MLA_LATENT", "1")):
         if flag:
             os.environ[var] = value
+    from ..utils.hub import resolve_model_path
+
+    ns.model_path = resolve_model_path(ns.model_path)
+    ns.spec_draft_model_path = resolve_model_path(ns.spec_draft_model_path)
     if ns.enable_ep and ns.tp_size * ns.dp_size == 1:
         raise SystemExit("--enable-ep needs --tp-size > 1 or --dp-size > 1")
     kwargs = json.loads(ns.chat_template_kwargs) if ns.chat_template_kwargs else None

@@ -72,3 +72,33 @@ def test_server_applies_generation_defaults_to_unset_fields(tmp_path):
     sp = S.sampling_from_request(S.OpenAICompletionRequest(model="m", messages=[{"role": "user", "content": "hi"}]),
                                  None, None)
     assert (sp.temperature, sp.top_p, sp.top_k) == (0.0, 1.0, -1)
+
+
+def test_hub_names_resolve_through_the_local_cache_or_fail_clearly(tmp_path, monkeypatch):
+    """A directory or a built-in shape passes through; a repository name is looked up in the local hub cache
+    (a snapshot laid out the way the hub client stores it) and, with downloads off, fails with a message that
+    says what was tried."""
+    import pytest
+
+    from minisglang_rdna4_b200.utils.hub import looks_like_repo, resolve_model_path
+
+    assert resolve_model_path(str(tmp_path)) == str(tmp_path)
+    assert resolve_model_path("qwen3-4b") == "qwen3-4b" and resolve_model_path("") == "" and resolve_model_path(None) is None
+    assert looks_like_repo("acme/tiny-model") and not looks_like_repo("/abs/path") and not looks_like_repo("a/b/c")
+    cache = tmp_path / "hub"
+    snap = cache / "models--acme--tiny-model" / "snapshots" / "abc123"
+    snap.mkdir(parents=True)
+    (snap / "config.json").write_text("{}")
+    refs = cache / "models--acme--tiny-model" / "refs"
+    refs.mkdir()
+    (refs / "main").write_text("abc123")
+    monkeypatch.setenv("HF_HUB_CACHE", str(cache))
+    monkeypatch.setenv("HF_HOME", str(tmp_path))
+    import huggingface_hub.constants as C
+
+    monkeypatch.setattr(C, "HF_HUB_CACHE", str(cache))
+    got = resolve_model_path("acme/tiny-model")
+    assert got is not None and got.endswith("abc123") and (tmp_path / "hub").as_posix() in got
+    monkeypatch.setenv("MSGL_HUB_OFFLINE", "1")
+    with pytest.raises(FileNotFoundError, match="downloads are off"):
+        resolve_model_path("acme/other-model")

@@ -423,3 +423,29 @@ def test_gemma4_image_input_matches_transformers(bidirectional):
         out = llm.generate([head + [291] + tail], SamplingParams(max_tokens=8, ignore_eos=True), images=[[image]])[0]
         llm.shutdown()
     assert out.token_ids == want
+
+
+def test_published_gemma4_shapes_parse():
+    """The default Hugging Face configurations (the small multimodal model's shape) and the dense large model's
+    geometry go through the config parser: per-layer geometry, K/V sharing, rotary tables, vision budget."""
+    from transformers import Gemma4Config, Gemma4TextConfig, Gemma4VisionConfig
+
+    from minisglang_rdna4_b200.models.config import ModelConfig
+
+    small = Gemma4Config(text_config=Gemma4TextConfig(num_hidden_layers=35, num_kv_shared_layers=20, num_key_value_heads=1,
+                                                      hidden_size=1536, use_double_wide_mlp=True).to_dict(),
+                         vision_config=Gemma4VisionConfig().to_dict(), audio_config=None)
+    mc = ModelConfig.from_hf(small.to_dict())
+    assert mc.architectures[0].startswith("Gemma4") and mc.num_kv_layers == 15 and mc.mixed_kv_geometry
+    assert mc.attn_geometry(0) == (1, 256) and mc.attn_geometry(5) == (1, 512) and mc.layer_types[-1] == "full_attention"
+    assert mc.kv_donor(14) is None and mc.kv_donor(15) == 14 and mc.kv_donor(34) == 11      # last own sliding / full layer
+    assert mc.rotary_config.head_dim == 512 and mc.rotary_config.scaling["rope_type"] == "proportional"
+    assert mc.rope_local_base_freq == 10000.0 and mc.hidden_size_per_layer_input == 256 and not mc.image_bidirectional
+    v = mc.vision
+    assert v.kind == "gemma4" and v.tokens_per_image == 256 and v.image_size == 16 * 3 * 16 and v.head_dim == 64
+    dense = Gemma4TextConfig(num_hidden_layers=60, hidden_size=5376, num_attention_heads=32, num_key_value_heads=16,
+                             num_global_key_value_heads=4, attention_k_eq_v=True, hidden_size_per_layer_input=0,
+                             use_bidirectional_attention="vision")
+    mc = ModelConfig.from_hf(dense.to_dict())
+    assert mc.attn_geometry(0) == (16, 256) and mc.attn_geometry(5) == (4, 512) and mc.num_kv_layers == 60
+    assert mc.image_bidirectional and mc.hidden_size_per_layer_input == 0 and mc.swa_layers[:6] == (0, 1, 2, 3, 4, 6)

@@ -449,3 +449,28 @@ def test_published_gemma4_shapes_parse():
     mc = ModelConfig.from_hf(dense.to_dict())
     assert mc.attn_geometry(0) == (16, 256) and mc.attn_geometry(5) == (4, 512) and mc.num_kv_layers == 60
     assert mc.image_bidirectional and mc.hidden_size_per_layer_input == 0 and mc.swa_layers[:6] == (0, 1, 2, 3, 4, 6)
+
+
+def test_published_gemma4_shapes_build_on_the_meta_device():
+    """The three published text shapes instantiate (no memory behind them) with the parameter counts their
+    names promise."""
+    from transformers import Gemma4TextConfig
+
+    from minisglang_rdna4_b200.models import ModelConfig, create_model
+
+    shapes = {
+        "31b": (dict(num_hidden_layers=60, hidden_size=5376, intermediate_size=21504, num_attention_heads=32,
+                     num_key_value_heads=16, num_global_key_value_heads=4, attention_k_eq_v=True,
+                     hidden_size_per_layer_input=0), 30.7),
+        "26b-a4b": (dict(num_hidden_layers=30, hidden_size=2816, intermediate_size=2112, num_attention_heads=16,
+                         num_key_value_heads=8, num_global_key_value_heads=2, attention_k_eq_v=True,
+                         hidden_size_per_layer_input=0, enable_moe_block=True, num_experts=128, top_k_experts=8,
+                         moe_intermediate_size=704), 25.2),
+        "e2b": (dict(num_hidden_layers=35, num_kv_shared_layers=20, num_key_value_heads=1, hidden_size=1536,
+                     intermediate_size=6144, use_double_wide_mlp=True), 4.6),
+    }
+    for name, (kw, billions) in shapes.items():
+        mc = ModelConfig.from_hf(Gemma4TextConfig(**kw).to_dict())
+        model = create_model(mc, torch.bfloat16, "meta")
+        n = sum(t.numel() for _, t, _, _ in model.named_parameters())
+        assert abs(n / 1e9 - billions) < 0.1, (name, n)
